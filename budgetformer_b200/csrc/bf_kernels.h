@@ -1,0 +1,74 @@
+// C interface of the sm_100a kernels.  Every launcher takes raw device pointers and a stream,
+// allocates nothing and returns a cudaError_t value (0 = success) unless stated otherwise, so the
+// same entry points serve the PyTorch bindings (bindings.cpp) and callers that own their memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BF_BF16 0
+#define BF_FP16 1
+#define BF_FP32 2
+
+#define BF_HUB_DEGREE 1024   // rows longer than this use the chunked hub kernels
+#define BF_HUB_CHUNK 8192    // edges per hub chunk (one thread block)
+
+// ---- edge attention (edge_attn.cu) ----------------------------------------------------------
+typedef struct {
+  const void *q, *k, *v;            // [n, hl, hn], inner two dims contiguous, row strides in elements
+  long long ldq, ldk, ldv;
+  void* out;                        // [n, hl, hn] contiguous
+  float* z;                         // [n, hl] softmax normaliser
+  const int* rowptr;                // [n+1] CSR over queries
+  const int* col;                   // [E] key ids
+  const uint8_t* etype;             // [E] or NULL
+  const float* etab;                // [2, hl, hn] fp32 or NULL (Exphormer edge-type table)
+  int n, hl, hn, dtype, variant;    // variant: 0 plain, 1 gps, 2 exphormer
+  float dropout_p;
+  uint32_t dropout_seed;
+  const int* hub_rows;              // rows with degree > BF_HUB_DEGREE (may be NULL when n_hub == 0)
+  int n_hub, max_hub_degree;
+  float* hub_scratch;               // zero-filled [n_hub, hl*hn + hl] fp32
+} bf_attn_params;
+
+typedef struct {
+  const void* dout;                 // [n, hl, hn] contiguous
+  void *dq, *dk, *dv;               // [n, hl, hn] contiguous
+  float* zd;                        // [n, hl, 2] fp32 workspace (written by the dQ pass)
+  const int *t_rowptr, *t_row, *t_eid;  // transposed CSR over keys
+  float* detab;                     // zero-filled [2, hl, hn] fp32 or NULL
+  const int* t_hub_rows;
+  int n_t_hub, max_t_hub_degree;
+  float* hub_scratch_q;             // zero-filled [n_hub, hl*hn]
+  float* hub_scratch_kv;            // zero-filled [n_t_hub, 2*hl*hn]
+} bf_attn_bwd_params;
+
+int bf_edge_attn_fwd(const bf_attn_params* p, cudaStream_t st);
+int bf_edge_attn_bwd(const bf_attn_params* p, const bf_attn_bwd_params* q, cudaStream_t st);
+
+// ---- attention-graph construction (edge_build.cu) -------------------------------------------
+typedef struct {
+  const int *in_rowptr, *in_src;    // CSR over destinations (multiplicity kept)
+  const int *out_rowptr, *out_col;  // coalesced CSR over sources (random walks)
+  int n;
+  int b_real, b_rw;                 // per-query budgets, each in [0, 32]
+  int walks, walk_len;              // W walks of length L (L <= 16) from every node
+  int exphormer;                    // 1: typed rows (real 0 | walk 1 | self 0) without dedup
+  long long seed;                   // epoch seed; +17 ranks real edges, +37 ranks walk edges
+  int cap;                          // row capacity >= b_real + b_rw (+1 for exphormer)
+  int* ell_col;                     // [n, cap]
+  uint8_t* ell_type;                // [n, cap] (exphormer) or NULL
+  int* ell_cnt;                     // [n]
+  unsigned long long* totals;       // zero-filled [2]: selected real / walk edges
+} bf_build_params;
+
+int bf_budget_select(const bf_build_params* p, cudaStream_t st);
+int bf_ell_to_csr(const int* ell_col, const uint8_t* ell_type, const int* rowptr, int n, int cap, int* col,
+                  uint8_t* etype, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

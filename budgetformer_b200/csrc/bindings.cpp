@@ -1,0 +1,179 @@
+// PyTorch bindings: tensor checks, allocation of workspaces and stream plumbing around the C
+// launchers declared in bf_kernels.h.  No kernel code lives here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "bf_kernels.h"
+
+extern "C" int bf_budget_select_cpu(const int*, const int*, const int*, const int*, int, int, int, int, int, int,
+                                    long long, int, int*, uint8_t*, int*, unsigned long long*, int);
+extern "C" int bf_ell_to_csr_cpu(const int*, const uint8_t*, const int*, int, int, int*, uint8_t*);
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+void check_cuda(int err, const char* what) {
+  TORCH_CHECK(err == 0, what, " failed: ", cudaGetErrorString((cudaError_t)err));
+}
+
+int dtype_code(const Tensor& t) {
+  if (t.scalar_type() == torch::kBFloat16) return BF_BF16;
+  if (t.scalar_type() == torch::kHalf) return BF_FP16;
+  if (t.scalar_type() == torch::kFloat) return BF_FP32;
+  TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+}
+
+void check_qkv(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 3, name, " must be a CUDA [n, heads, head_dim] tensor");
+  TORCH_CHECK(t.stride(2) == 1 && t.stride(1) == t.size(2), name, " must be contiguous in its last two dims");
+  TORCH_CHECK((t.stride(0) * t.element_size()) % 16 == 0 && ((uintptr_t)t.data_ptr()) % 16 == 0, name,
+              " rows must be 16-byte aligned");
+}
+
+const int* iptr(const Tensor& t) { return t.data_ptr<int>(); }
+
+struct HubInfo {
+  Tensor rows;
+  int n = 0;
+  int max_deg = 0;
+};
+
+// Rows of a CSR longer than BF_HUB_DEGREE.  `known_max` >= 0 skips the device query.
+HubInfo find_hubs(const Tensor& rowptr, int64_t known_max) {
+  HubInfo h;
+  if (known_max >= 0 && known_max <= BF_HUB_DEGREE) return h;
+  auto deg = rowptr.slice(0, 1) - rowptr.slice(0, 0, rowptr.size(0) - 1);
+  auto rows = torch::nonzero(deg > BF_HUB_DEGREE).flatten().to(torch::kInt);
+  h.n = (int)rows.size(0);
+  if (h.n > 0) {
+    h.rows = rows;
+    h.max_deg = deg.max().item<int>();
+  }
+  return h;
+}
+
+void fill_common(bf_attn_params& p, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                 const Tensor& z, const Tensor& rowptr, const Tensor& col, const OptTensor& etype,
+                 const OptTensor& etab, int64_t variant, double dropout_p, int64_t seed) {
+  check_qkv(q, "q"); check_qkv(k, "k"); check_qkv(v, "v");
+  TORCH_CHECK(out.is_contiguous() && z.is_contiguous());
+  TORCH_CHECK(rowptr.scalar_type() == torch::kInt && col.scalar_type() == torch::kInt, "graph indices must be int32");
+  p.q = q.data_ptr(); p.k = k.data_ptr(); p.v = v.data_ptr();
+  p.ldq = q.stride(0); p.ldk = k.stride(0); p.ldv = v.stride(0);
+  p.out = out.data_ptr(); p.z = z.data_ptr<float>();
+  p.rowptr = iptr(rowptr); p.col = iptr(col);
+  p.etype = etype.has_value() ? etype->data_ptr<uint8_t>() : nullptr;
+  p.etab = etab.has_value() ? etab->data_ptr<float>() : nullptr;
+  p.n = (int)q.size(0); p.hl = (int)q.size(1); p.hn = (int)q.size(2);
+  p.dtype = dtype_code(q); p.variant = (int)variant;
+  p.dropout_p = (float)dropout_p; p.dropout_seed = (uint32_t)seed;
+  TORCH_CHECK(variant != 2 || (p.etype && p.etab), "exphormer variant needs edge types and a type table");
+}
+
+void edge_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor rowptr, Tensor col, OptTensor etype,
+                   OptTensor etab, int64_t variant, double dropout_p, int64_t seed, int64_t known_max_degree) {
+  c10::cuda::CUDAGuard guard(q.device());
+  bf_attn_params p{};
+  fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed);
+  HubInfo hub = find_hubs(rowptr, known_max_degree);
+  Tensor scratch;
+  if (hub.n > 0) {
+    scratch = torch::zeros({hub.n, (int64_t)p.hl * p.hn + p.hl}, q.options().dtype(torch::kFloat));
+    p.hub_rows = iptr(hub.rows); p.n_hub = hub.n; p.max_hub_degree = hub.max_deg;
+    p.hub_scratch = scratch.data_ptr<float>();
+  }
+  check_cuda(bf_edge_attn_fwd(&p, at::cuda::getCurrentCUDAStream()), "edge_attn_fwd");
+}
+
+void edge_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor dout, Tensor dq, Tensor dk, Tensor dv,
+                   Tensor zd, Tensor rowptr, Tensor col, OptTensor etype, Tensor t_rowptr, Tensor t_row, Tensor t_eid,
+                   OptTensor etab, OptTensor detab, int64_t variant, double dropout_p, int64_t seed,
+                   int64_t known_max_degree) {
+  c10::cuda::CUDAGuard guard(q.device());
+  bf_attn_params p{};
+  fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed);
+  TORCH_CHECK(dout.is_contiguous() && dq.is_contiguous() && dk.is_contiguous() && dv.is_contiguous());
+  TORCH_CHECK(zd.is_contiguous() && zd.numel() == 2 * z.numel());
+  bf_attn_bwd_params b{};
+  b.dout = dout.data_ptr(); b.dq = dq.data_ptr(); b.dk = dk.data_ptr(); b.dv = dv.data_ptr();
+  b.zd = zd.data_ptr<float>();
+  b.t_rowptr = iptr(t_rowptr); b.t_row = iptr(t_row); b.t_eid = iptr(t_eid);
+  b.detab = detab.has_value() ? detab->data_ptr<float>() : nullptr;
+  HubInfo hub = find_hubs(rowptr, known_max_degree);
+  HubInfo thub = find_hubs(t_rowptr, -1);
+  Tensor sq, skv;
+  const int64_t w = (int64_t)p.hl * p.hn;
+  if (hub.n > 0) {
+    sq = torch::zeros({hub.n, w}, q.options().dtype(torch::kFloat));
+    p.hub_rows = iptr(hub.rows); p.n_hub = hub.n; p.max_hub_degree = hub.max_deg;
+    b.hub_scratch_q = sq.data_ptr<float>();
+  }
+  if (thub.n > 0) {
+    skv = torch::zeros({thub.n, 2 * w}, q.options().dtype(torch::kFloat));
+    b.t_hub_rows = iptr(thub.rows); b.n_t_hub = thub.n; b.max_t_hub_degree = thub.max_deg;
+    b.hub_scratch_kv = skv.data_ptr<float>();
+  }
+  check_cuda(bf_edge_attn_bwd(&p, &b, at::cuda::getCurrentCUDAStream()), "edge_attn_bwd");
+}
+
+// Returns (rowptr int32 [n+1], col int32 [E], etype uint8 [E] or empty, totals int64 [2]).
+std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col, int64_t n,
+                                     int64_t b_real, int64_t b_rw, int64_t walks, int64_t walk_len, bool exphormer,
+                                     int64_t seed, int64_t num_threads) {
+  TORCH_CHECK(b_real >= 0 && b_rw >= 0 && b_real <= 32 && b_rw <= 32, "per-side budgets must be in [0, 32]");
+  TORCH_CHECK(walk_len <= 16, "walk_length must be <= 16");
+  for (const Tensor* t : {&in_rowptr, &in_src, &out_rowptr, &out_col})
+    TORCH_CHECK(t->scalar_type() == torch::kInt && t->is_contiguous(), "topology must be contiguous int32");
+  const int cap = (int)(b_real + b_rw + (exphormer ? 1 : 0));
+  auto iopt = in_src.options();
+  Tensor ell_col = torch::empty({n, std::max(cap, 1)}, iopt);
+  Tensor ell_type = exphormer ? torch::empty({n, std::max(cap, 1)}, iopt.dtype(torch::kUInt8)) : Tensor();
+  Tensor ell_cnt = torch::zeros({n}, iopt);
+  Tensor totals = torch::zeros({2}, iopt.dtype(torch::kLong));
+  const bool cuda = in_src.is_cuda();
+  if (cuda) {
+    c10::cuda::CUDAGuard guard(in_src.device());
+    bf_build_params p{};
+    p.in_rowptr = iptr(in_rowptr); p.in_src = iptr(in_src); p.out_rowptr = iptr(out_rowptr); p.out_col = iptr(out_col);
+    p.n = (int)n; p.b_real = (int)b_real; p.b_rw = (int)b_rw; p.walks = (int)walks; p.walk_len = (int)walk_len;
+    p.exphormer = exphormer ? 1 : 0; p.seed = seed; p.cap = std::max(cap, 1);
+    p.ell_col = ell_col.data_ptr<int>(); p.ell_type = exphormer ? ell_type.data_ptr<uint8_t>() : nullptr;
+    p.ell_cnt = ell_cnt.data_ptr<int>();
+    p.totals = reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>());
+    check_cuda(bf_budget_select(&p, at::cuda::getCurrentCUDAStream()), "budget_select");
+  } else {
+    bf_budget_select_cpu(iptr(in_rowptr), iptr(in_src), iptr(out_rowptr), iptr(out_col), (int)n, (int)b_real,
+                         (int)b_rw, (int)walks, (int)walk_len, exphormer ? 1 : 0, seed, std::max(cap, 1),
+                         ell_col.data_ptr<int>(), exphormer ? ell_type.data_ptr<uint8_t>() : nullptr,
+                         ell_cnt.data_ptr<int>(), reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>()),
+                         (int)num_threads);
+  }
+  Tensor rowptr = torch::zeros({n + 1}, iopt);
+  rowptr.slice(0, 1).copy_(torch::cumsum(ell_cnt, 0, torch::kInt));
+  // The edge count sizes the output; this is the one host read of the build.
+  const int64_t n_edges = n > 0 ? rowptr[n].item<int64_t>() : 0;
+  Tensor col = torch::empty({n_edges}, iopt);
+  Tensor etype = exphormer ? torch::empty({n_edges}, iopt.dtype(torch::kUInt8)) : Tensor();
+  if (cuda) {
+    check_cuda(bf_ell_to_csr(ell_col.data_ptr<int>(), exphormer ? ell_type.data_ptr<uint8_t>() : nullptr,
+                             rowptr.data_ptr<int>(), (int)n, std::max(cap, 1), col.data_ptr<int>(),
+                             exphormer ? etype.data_ptr<uint8_t>() : nullptr, at::cuda::getCurrentCUDAStream()),
+               "ell_to_csr");
+  } else {
+    bf_ell_to_csr_cpu(ell_col.data_ptr<int>(), exphormer ? ell_type.data_ptr<uint8_t>() : nullptr,
+                      rowptr.data_ptr<int>(), (int)n, std::max(cap, 1), col.data_ptr<int>(),
+                      exphormer ? etype.data_ptr<uint8_t>() : nullptr);
+  }
+  return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("edge_attn_fwd", &edge_attn_fwd);
+  m.def("edge_attn_bwd", &edge_attn_bwd);
+  m.def("build_attn_graph", &build_attn_graph);
+}

@@ -1,0 +1,102 @@
+// C++/OpenMP twin of edge_build.cu: the same per-query selection, walk and merge rules evaluated
+// with std::sort per query.  Used by the CPU edge policies of the execution planner (the raw
+// topology stays in host memory and only the compact per-query rows are uploaded) and as the
+// integer oracle for the CUDA builder — outputs are bit-identical.
+// Reference behaviour restated: utils/fullgraph_sp_support.py:1119-1192 (CPU per-query sampler),
+// gt_sp/utils.py:1198-1248 (walk edge emission), gt_sp/utils.py:1396-1442 (CPU walker).
+#include <algorithm>
+#include <cstdint>
+#include <vector>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#include "../edge_spec.h"
+
+extern "C" int bf_budget_select_cpu(const int* in_rowptr, const int* in_src, const int* out_rowptr,
+                                    const int* out_col, int n, int b_real, int b_rw, int walks, int walk_len,
+                                    int exphormer, long long seed, int cap, int* ell_col, uint8_t* ell_type,
+                                    int* ell_cnt, unsigned long long* totals, int num_threads) {
+  unsigned long long tot_r = 0, tot_w = 0;
+#ifdef _OPENMP
+  if (num_threads > 0) omp_set_num_threads(num_threads);
+#endif
+#pragma omp parallel reduction(+ : tot_r, tot_w)
+  {
+    std::vector<uint64_t> rc, wc;
+    std::vector<uint32_t> merged;
+#pragma omp for schedule(dynamic, 1024)
+    for (int v = 0; v < n; ++v) {
+      rc.clear();
+      wc.clear();
+      if (b_real > 0) {
+        const int beg = in_rowptr[v], end = in_rowptr[v + 1];
+        for (int e = beg; e < end; ++e)
+          rc.push_back(bf_edge_composite((uint32_t)in_src[e], (uint32_t)v, seed + BF_REAL_SEED_OFFSET));
+        if ((int)rc.size() > b_real) {
+          std::nth_element(rc.begin(), rc.begin() + b_real, rc.end());
+          rc.resize(b_real);
+        }
+      }
+      if (b_rw > 0 && walks > 0 && walk_len > 0) {
+        for (int w = 0; w < walks; ++w) {
+          const uint64_t walk_id = (uint64_t)v * (uint64_t)walks + (uint64_t)w;
+          int cur = v;
+          for (int d = 1; d <= walk_len; ++d) {
+            const int prev = cur;
+            const int ob = out_rowptr[cur], oe = out_rowptr[cur + 1];
+            const uint32_t deg = (uint32_t)(oe - ob);
+            if (deg > 0) cur = out_col[ob + (int)bf_mulhi32(bf_walk_uniform32(walk_id, (uint32_t)d, (uint64_t)seed), deg)];
+            if (d == 1 || cur != prev) wc.push_back(bf_edge_composite((uint32_t)cur, (uint32_t)v, seed + BF_RW_SEED_OFFSET));
+          }
+        }
+        if ((int)wc.size() > b_rw) {
+          std::nth_element(wc.begin(), wc.begin() + b_rw, wc.end());
+          wc.resize(b_rw);
+        }
+      }
+      tot_r += rc.size();
+      tot_w += wc.size();
+      int* row = ell_col + (long long)v * cap;
+      if (exphormer) {
+        uint8_t* trow = ell_type + (long long)v * cap;
+        int c = 0;
+        merged.clear();
+        for (uint64_t x : rc) merged.push_back((uint32_t)x);
+        std::sort(merged.begin(), merged.end());
+        for (uint32_t s : merged) { row[c] = (int)s; trow[c++] = 0; }
+        merged.clear();
+        for (uint64_t x : wc) merged.push_back((uint32_t)x);
+        std::sort(merged.begin(), merged.end());
+        for (uint32_t s : merged) { row[c] = (int)s; trow[c++] = 1; }
+        row[c] = v; trow[c++] = 0;
+        ell_cnt[v] = c;
+      } else {
+        merged.clear();
+        for (uint64_t x : rc) merged.push_back((uint32_t)x);
+        for (uint64_t x : wc) merged.push_back((uint32_t)x);
+        std::sort(merged.begin(), merged.end());
+        merged.erase(std::unique(merged.begin(), merged.end()), merged.end());
+        for (size_t i = 0; i < merged.size(); ++i) row[i] = (int)merged[i];
+        ell_cnt[v] = (int)merged.size();
+      }
+    }
+  }
+  totals[0] = tot_r;
+  totals[1] = tot_w;
+  return 0;
+}
+
+extern "C" int bf_ell_to_csr_cpu(const int* ell_col, const uint8_t* ell_type, const int* rowptr, int n, int cap,
+                                 int* col, uint8_t* etype) {
+#pragma omp parallel for schedule(static)
+  for (int v = 0; v < n; ++v) {
+    const int beg = rowptr[v], cnt = rowptr[v + 1] - beg;
+    for (int s = 0; s < cnt; ++s) {
+      col[beg + s] = ell_col[(long long)v * cap + s];
+      if (etype) etype[beg + s] = ell_type[(long long)v * cap + s];
+    }
+  }
+  return 0;
+}

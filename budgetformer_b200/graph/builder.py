@@ -1,0 +1,70 @@
+"""Per-epoch attention-graph construction: dispatch between the CUDA builder, its C++/OpenMP
+twin and the numpy specification.
+
+All three implement the same rules (see ``builder_spec``) and return identical ``AttnGraph``
+objects for identical ``(topology, budgets, seed)``, which is why no rank ever has to
+broadcast edges: every rank calls ``build_attn_graph`` with the epoch seed
+(utils/fullgraph_sp_runtime.py:221-226 in the reference) and gets the same graph.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .attn_graph import AttnGraph, Topology, add_virtual_node
+from .builder_spec import build_attn_graph_spec
+
+MAX_SIDE_BUDGET = 32
+MAX_WALK_LEN = 16
+
+
+def native_supported(b_real: Optional[int], b_rw: Optional[int], walk_length: int) -> bool:
+    if b_real is None or b_rw is None:
+        return False
+    return 0 <= b_real <= MAX_SIDE_BUDGET and 0 <= b_rw <= MAX_SIDE_BUDGET and walk_length <= MAX_WALK_LEN
+
+
+def build_attn_graph(
+    topo: Topology,
+    b_real: Optional[int],
+    b_rw: Optional[int],
+    walks_per_node: int,
+    walk_length: int,
+    seed: int,
+    *,
+    use_real: bool = True,
+    use_rw: bool = True,
+    exphormer: bool = False,
+    num_threads: int = 0,
+    force_spec: bool = False,
+) -> AttnGraph:
+    """Build on whatever device ``topo`` lives on.  ``None`` budgets (unsampled, the legacy
+    ``--include_real_edges`` path) and budgets above 32 per side fall back to the specification."""
+    br = 0 if not use_real else b_real
+    bw = 0 if (not use_rw or walks_per_node <= 0 or walk_length <= 0) else b_rw
+    if force_spec or not native_supported(br, bw, walk_length):
+        g = build_attn_graph_spec(topo, b_real, b_rw, walks_per_node, walk_length, seed,
+                                  use_real=use_real, use_rw=use_rw, exphormer=exphormer)
+        return g.to(topo.device) if topo.device.type != "cpu" else g
+    from ..ops import _ext
+    ext = _ext.load()
+    rowptr, col, etype, totals = ext.build_attn_graph(
+        topo.in_rowptr, topo.in_src, topo.out_rowptr, topo.out_col, int(topo.num_nodes),
+        int(br), int(bw), int(walks_per_node), int(walk_length), bool(exphormer), int(seed), int(num_threads))
+    g = AttnGraph(int(topo.num_nodes), rowptr, col, etype if exphormer else None,
+                  max_degree=int(br) + int(bw) + (1 if exphormer else 0))
+    g._totals = totals  # device tensor; read lazily to avoid a sync on the hot path
+    return g
+
+
+def graph_totals(g: AttnGraph):
+    """(selected real edges, selected walk edges) of a natively built graph."""
+    t = getattr(g, "_totals", None)
+    if t is not None:
+        r, w = (int(x) for x in t.tolist())
+        g.n_real, g.n_rw = r, w
+    return g.n_real, g.n_rw
+
+
+__all__ = ["build_attn_graph", "graph_totals", "add_virtual_node", "native_supported"]
