@@ -1,0 +1,320 @@
+"""Edge construction engine: budget resolution, placement policies, prefetch and caching.
+
+One ``EdgeEngine`` per rank owns the raw ``Topology`` (host copy in pinned memory, optional device
+copy) and produces the epoch's ``AttnGraph`` on the training device.  Placement policies are the
+reference's (utils/fullgraph_sp_support.py:394-402, gt_sp/multi_tier.py:1210-1223):
+
+=========================  ====================================================================
+``gpu_persist``            topology resident in HBM, sample + walk on the GPU every epoch
+``gpu_ephemeral``          topology uploaded from pinned memory each epoch, built on GPU, freed
+``cpu_rank_local_prefetch``  every rank builds on CPU (C++/OpenMP) in a background thread and
+                           uploads the compact CSR (int32, ``4*(N+1+E_m)`` bytes) asynchronously
+``cpu_broadcast_prefetch`` the source rank builds on CPU in the background and broadcasts
+``cpu_broadcast``          same, synchronously (baseline while the budget is still moving)
+=========================  ====================================================================
+
+Because the builders are counter-based and bit-identical on CPU and GPU, the rank-local policies
+need no communication; broadcast exists for parity and for ``--force_edge_broadcast``.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from concurrent.futures import Future, ThreadPoolExecutor
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..utils.comm_profiler import profile_call, record_scalar
+from .attn_graph import AttnGraph, Topology, add_virtual_node
+from .builder import build_attn_graph, graph_totals
+
+EDGE_POLICY_CHOICES = ("gpu_persist", "gpu_ephemeral", "cpu_rank_local_prefetch", "cpu_broadcast_prefetch",
+                       "cpu_broadcast")
+_CPU_POLICIES = ("cpu_rank_local_prefetch", "cpu_broadcast_prefetch", "cpu_broadcast")
+
+
+@dataclass(frozen=True)
+class BudgetState:
+    """Resolved per-query budgets for one build.  ``None`` = unsampled (all candidates)."""
+    use_real: bool
+    use_rw: bool
+    b_real: Optional[int]
+    b_rw: Optional[int]
+    walk_length: int
+
+    def key(self) -> tuple:
+        return (self.use_real, self.use_rw, self.b_real, self.b_rw, self.walk_length)
+
+
+def resolve_budget_state(args, controller_state: Optional[dict] = None) -> BudgetState:
+    """Decision table of utils/fullgraph_sp_support.py:830-915.
+
+    * fixed / adaptive state given  -> that split (0 drops a side);
+    * ``--random_edge_blocks --max_total_edges_per_query B`` -> ``(B+1)//2`` real, ``B//2`` walk
+      (all ``B`` to real when ``walks_per_node == 0``);
+    * otherwise -> all real edges iff ``--include_real_edges 1``, the full walk pool iff ``walks_per_node > 0``.
+    """
+    wl = int(getattr(args, "walk_length", 4))
+    wpn = int(getattr(args, "walks_per_node", 0))
+    if controller_state is not None:
+        r = int(controller_state.get("real_edges_per_query", 0))
+        w = int(controller_state.get("rw_edges_per_query", 0))
+        wl = int(controller_state.get("walk_length", getattr(args, "fixed_walk_length", None) or wl))
+        return BudgetState(r > 0, w > 0 and wpn > 0, r, w, wl)
+    total = int(getattr(args, "max_total_edges_per_query", 0) or 0)
+    if getattr(args, "random_edge_blocks", False) and total > 0:
+        if wpn <= 0:
+            return BudgetState(True, False, total, 0, wl)
+        return BudgetState(True, True, (total + 1) // 2, total // 2, wl)
+    return BudgetState(bool(int(getattr(args, "include_real_edges", 0))), wpn > 0, None, None, wl)
+
+
+def edge_seed_for_epoch(args, epoch: int, static_seed_epochs: int = 0) -> int:
+    """``seed`` while ``epoch <= static_seed_epochs`` else ``seed + epoch`` (utils/fullgraph_sp_runtime.py:221-226)."""
+    return int(args.seed) if epoch <= int(static_seed_epochs) else int(args.seed) + int(epoch)
+
+
+class EdgeEngine:
+    def __init__(self, args, edge_index_global: torch.Tensor, num_nodes: int, device, *, nodes_per_rank: int,
+                 sp_group=None, sp_rank: int = 0, sp_src_rank: int = 0, sp_world: int = 1,
+                 expander_edges: Optional[torch.Tensor] = None):
+        self.args = args
+        self.device = torch.device(device)
+        self.num_nodes = int(num_nodes)                 # padded node count
+        self.nodes_per_rank = int(nodes_per_rank)
+        self.group, self.rank, self.src_rank, self.world = sp_group, int(sp_rank), int(sp_src_rank), int(sp_world)
+        self.model = str(getattr(args, "model", "gt"))
+        self.virtual_node = self.model == "graphormer" and int(getattr(args, "num_global_node", 0)) > 0
+        self.exphormer = self.model == "exphormer"
+        self.expander_edges = expander_edges
+        t0 = time.perf_counter()
+        self.topo_cpu = Topology.from_edge_index(edge_index_global.cpu(), self.num_nodes)
+        if self.device.type == "cuda":
+            try:
+                self.topo_cpu = self.topo_cpu.pin_memory()
+            except RuntimeError:
+                pass
+        self.t_topology_build = time.perf_counter() - t0
+        self.topo_gpu: Optional[Topology] = None
+        self.policy = self._initial_policy()
+        self.policy_locked = False
+        self.force_broadcast = bool(getattr(args, "force_edge_broadcast", False))
+        self._cache: Dict[tuple, AttnGraph] = {}        # up to 2 finished host-side builds (prefetch hand-off)
+        self._cache_lock = threading.Lock()
+        self._pool: Optional[ThreadPoolExecutor] = None
+        self._future: Optional[Tuple[tuple, Future]] = None
+        self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        self.last_build_s = 0.0
+        self.last_prefetch_wait_s = 0.0
+        self.last_graph_bytes = 0
+        self.gpu_build_failed = False
+
+    # ------------------------------------------------------------------ policy
+    def _initial_policy(self) -> str:
+        dev = str(getattr(self.args, "edge_build_device", "gpu")).lower()
+        if self.device.type != "cuda" or dev == "cpu":
+            return "cpu_rank_local_prefetch"
+        return "gpu_persist"
+
+    def set_policy(self, policy: str, lock: bool = False) -> None:
+        if policy not in EDGE_POLICY_CHOICES:
+            raise ValueError(f"unknown edge policy {policy!r}")
+        if self.device.type != "cuda" and policy.startswith("gpu"):
+            policy = "cpu_rank_local_prefetch"
+        if policy != self.policy:
+            self.clear_cache()
+        self.policy = policy
+        self.policy_locked = bool(lock)
+        if policy != "gpu_persist":
+            self.topo_gpu = None
+
+    def build_devices(self) -> Tuple[str, str]:
+        """(final device, walk device) of the active policy (utils/fullgraph_sp_support.py:394-402)."""
+        if self.policy in ("cpu_broadcast", "cpu_broadcast_prefetch"):
+            return "cpu", "cpu"
+        if self.policy == "cpu_rank_local_prefetch":
+            return str(self.device), "cpu"
+        return str(self.device), str(self.device)
+
+    def uses_prefetch(self) -> bool:
+        return (self.policy in ("cpu_rank_local_prefetch", "cpu_broadcast_prefetch")
+                and not getattr(self.args, "disable_edge_prefetch", False)
+                and not getattr(self.args, "profile_sp_comm", False))
+
+    # ------------------------------------------------------------------ cache / prefetch
+    @staticmethod
+    def _key(seed: int, state: BudgetState) -> tuple:
+        return (int(seed),) + state.key()
+
+    def clear_cache(self) -> None:
+        with self._cache_lock:
+            self._cache.clear()
+
+    def _store(self, key: tuple, g: AttnGraph) -> None:
+        with self._cache_lock:
+            if len(self._cache) >= 2:
+                self._cache.pop(next(iter(self._cache)))
+            self._cache[key] = g
+
+    def submit_prefetch(self, seed: int, state: BudgetState) -> bool:
+        """Start building the next epoch's graph on a CPU thread (main_node_fullgraph_sp.py:512-636)."""
+        if not self.uses_prefetch():
+            return False
+        if self.policy == "cpu_broadcast_prefetch" and self.world > 1 and self.rank != 0:
+            return False
+        key = self._key(seed, state)
+        if self._future is not None and self._future[0] == key:
+            return True
+        if self._pool is None:
+            self._pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="bf-edge-prefetch")
+        self._future = (key, self._pool.submit(self._build_host, seed, state))
+        return True
+
+    def _wait_prefetch(self, key: tuple) -> Optional[AttnGraph]:
+        if self._future is None:
+            return None
+        fkey, fut = self._future
+        t0 = time.perf_counter()
+        g = fut.result()
+        self.last_prefetch_wait_s = time.perf_counter() - t0
+        self._future = None
+        self._store(fkey, g)
+        return g if fkey == key else None
+
+    def shutdown(self) -> None:
+        if self._pool is not None:
+            self._pool.shutdown(wait=True)
+            self._pool = None
+        self._future = None
+
+    # ------------------------------------------------------------------ builds
+    def _build_host(self, seed: int, state: BudgetState) -> AttnGraph:
+        g = build_attn_graph(self.topo_cpu, state.b_real, state.b_rw, int(getattr(self.args, "walks_per_node", 0)),
+                             state.walk_length, seed, use_real=state.use_real, use_rw=state.use_rw,
+                             exphormer=self.exphormer and self.expander_edges is None)
+        graph_totals(g)
+        if self.device.type == "cuda":
+            for name in ("rowptr", "col", "etype"):
+                t = getattr(g, name)
+                if t is not None and not t.is_pinned():
+                    try:
+                        setattr(g, name, t.pin_memory())
+                    except RuntimeError:
+                        pass
+        return g
+
+    def _topology_on_device(self) -> Topology:
+        if self.topo_gpu is not None:
+            return self.topo_gpu
+        nbytes = self.topo_cpu.nbytes()
+        topo = profile_call("edge_full_h2d", lambda: self.topo_cpu.to(self.device, non_blocking=True),
+                            device=self.device, payload_bytes=nbytes)
+        if self.policy == "gpu_persist":
+            self.topo_gpu = topo
+        return topo
+
+    def _build_device(self, seed: int, state: BudgetState) -> AttnGraph:
+        topo = self._topology_on_device()
+        return build_attn_graph(topo, state.b_real, state.b_rw, int(getattr(self.args, "walks_per_node", 0)),
+                                state.walk_length, seed, use_real=state.use_real, use_rw=state.use_rw,
+                                exphormer=self.exphormer and self.expander_edges is None)
+
+    def _upload(self, g: AttnGraph) -> AttnGraph:
+        if self.device.type != "cuda":
+            return g
+        if self._copy_stream is not None:
+            cur = torch.cuda.current_stream(self.device)
+            with torch.cuda.stream(self._copy_stream):
+                out = g.to(self.device, non_blocking=True)
+            cur.wait_stream(self._copy_stream)
+            for t in (out.rowptr, out.col, out.etype):
+                if t is not None:
+                    t.record_stream(cur)
+            return out
+        return g.to(self.device)
+
+    def _broadcast(self, g: Optional[AttnGraph]) -> AttnGraph:
+        """Source rank ships (sizes, rowptr, col[, etype]) to the others (utils/fullgraph_sp_support.py:3318-3332)."""
+        nccl = dist.get_backend(self.group) == "nccl"
+        dev = self.device if nccl else torch.device("cpu")
+        is_src = self.rank == 0
+        meta = torch.zeros(4, dtype=torch.int64, device=dev)
+        if is_src:
+            meta = torch.tensor([g.num_rows, g.num_edges, 1 if g.etype is not None else 0,
+                                 -1 if g.max_degree is None else g.max_degree], dtype=torch.int64, device=dev)
+        dist.broadcast(meta, src=self.src_rank, group=self.group)
+        n_rows, n_edges, has_type, maxdeg = (int(v) for v in meta.tolist())
+        def _bc(t, shape, dtype):
+            buf = t.to(dev) if is_src else torch.empty(shape, dtype=dtype, device=dev)
+            dist.broadcast(buf, src=self.src_rank, group=self.group)
+            return buf
+        rowptr = _bc(g.rowptr if is_src else None, (n_rows + 1,), torch.int32)
+        col = _bc(g.col if is_src else None, (n_edges,), torch.int32)
+        etype = _bc(g.etype if is_src else None, (n_edges,), torch.uint8) if has_type else None
+        return AttnGraph(n_rows, rowptr, col, etype, max_degree=None if maxdeg < 0 else maxdeg)
+
+    def _finalize(self, g: AttnGraph) -> AttnGraph:
+        """Model-specific assembly on the final device."""
+        if self.exphormer and self.expander_edges is not None:
+            # sampled + self loops are type 0, expander edges type 1 (main_node_fullgraph_sp.py:1170-1185)
+            ei = g.edge_index()[:2]
+            self_ids = torch.arange(self.num_nodes, device=ei.device)
+            exp = self.expander_edges.to(ei.device)
+            allei = torch.cat([ei, torch.stack([self_ids, self_ids]), exp], dim=1)
+            typ = torch.cat([torch.zeros(ei.size(1) + self.num_nodes, dtype=torch.long, device=ei.device),
+                             torch.ones(exp.size(1), dtype=torch.long, device=ei.device)])
+            g = AttnGraph.from_edge_index(torch.cat([allei, typ.unsqueeze(0)], 0), self.num_nodes)
+        if self.virtual_node:
+            g = add_virtual_node(g, self.num_nodes, self.nodes_per_rank)
+        return g
+
+    def build(self, seed: int, state: BudgetState, record: bool = True) -> AttnGraph:
+        """The epoch's attention graph on the training device (utils/fullgraph_sp_support.py:3171-3362)."""
+        t0 = time.perf_counter()
+        self.last_prefetch_wait_s = 0.0
+        key = self._key(seed, state)
+        broadcast = self.world > 1 and (self.force_broadcast or self.policy in ("cpu_broadcast", "cpu_broadcast_prefetch"))
+        g: Optional[AttnGraph] = None
+        with self._cache_lock:
+            host = self._cache.get(key)
+        if host is None and self._future is not None:
+            host = self._wait_prefetch(key)
+        if broadcast:
+            if self.rank == 0 and host is None:
+                host = profile_call("edge_build_local", lambda: self._build_host(seed, state), device="cpu")
+                self._store(key, host)
+            g = profile_call("edge_broadcast", lambda: self._broadcast(host), device=self.device)
+            if g.device != self.device:
+                g = self._upload(g)
+        elif self.policy in _CPU_POLICIES or self.device.type != "cuda":
+            if host is None:
+                host = profile_call("edge_build_local", lambda: self._build_host(seed, state), device="cpu")
+                self._store(key, host)
+            g = self._upload(host)
+        else:
+            try:
+                g = profile_call("edge_build_local", lambda: self._build_device(seed, state), device=self.device)
+            except torch.cuda.OutOfMemoryError:
+                # sticky CPU fallback, reported to the planner by the caller (utils/fullgraph_sp_support.py:1334-1491)
+                self.gpu_build_failed = True
+                self.topo_gpu = None
+                torch.cuda.empty_cache()
+                host = self._build_host(seed, state)
+                g = self._upload(host)
+        g = profile_call("edge_merge", lambda: self._finalize(g), device=self.device)
+        self.last_build_s = time.perf_counter() - t0
+        self.last_graph_bytes = g.nbytes()
+        if record:
+            record_scalar("edge_merged_edges", g.num_edges, reduce="max")
+        return g
+
+    def estimate_working_set_bytes(self, state: BudgetState) -> int:
+        """First-principles GPU footprint of one device build: topology + fixed-width rows + CSR
+        (the analogue of ``_estimate_rw_working_set_bytes``, gt_sp/utils.py:160-236, for this builder)."""
+        cap = (state.b_real or 0) + (state.b_rw or 0) + 1
+        topo = self.topo_cpu.nbytes()
+        rows = self.num_nodes * cap * 5 + self.num_nodes * 12
+        return int(topo + 2 * rows)

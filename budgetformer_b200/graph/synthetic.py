@@ -1,0 +1,137 @@
+"""Synthetic graph generators for the benchmark configurations (no dataset download is possible in
+the target environment): stochastic block model, Chung-Lu power law (directed / undirected) and a
+citation-like DAG with power-law out-degree.  ``write_dataset`` stores a graph in the on-disk data
+contract so that the command-line driver (and the reference) can train on it."""
+from __future__ import annotations
+
+import os
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+
+def sbm_graph(num_nodes: int = 2048, blocks: int = 7, p_in: float = 0.02, p_out: float = 0.001, feat_dim: int = 128,
+              seed: int = 42) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Symmetrised SBM with equal blocks; labels = block id; N(0,1) features plus a weak class signal."""
+    rng = np.random.default_rng(seed)
+    n = int(num_nodes)
+    label = (np.arange(n) * blocks // n).astype(np.int64)
+    iu, ju = np.triu_indices(n, k=1)
+    p = np.where(label[iu] == label[ju], p_in, p_out)
+    keep = rng.random(iu.size) < p
+    s, d = iu[keep], ju[keep]
+    ei = np.stack([np.concatenate([s, d]), np.concatenate([d, s])])
+    x = rng.standard_normal((n, feat_dim)).astype(np.float32)
+    centers = rng.standard_normal((blocks, feat_dim)).astype(np.float32)
+    x += 0.5 * centers[label]
+    return torch.from_numpy(x), torch.from_numpy(label), torch.from_numpy(ei.astype(np.int64))
+
+
+def _power_law_weights(n: int, exponent: float, rng, w_min: float = 1.0) -> np.ndarray:
+    u = rng.random(n)
+    return w_min * (1.0 - u) ** (-1.0 / (exponent - 1.0))
+
+
+def chung_lu_edges(num_nodes: int, num_edges: int, exponent: float = 2.1, directed: bool = True, seed: int = 0,
+                   chunk: int = 1 << 24) -> torch.Tensor:
+    """Sample ``num_edges`` (src, dst) pairs with endpoint probabilities proportional to power-law
+    weights (the Chung-Lu model in its fast multigraph form; duplicates and self loops dropped, so the
+    result has slightly fewer edges).  Undirected graphs return both directions."""
+    rng = np.random.default_rng(seed)
+    n = int(num_nodes)
+    w_out = _power_law_weights(n, exponent, rng)
+    w_in = _power_law_weights(n, exponent, rng) if directed else w_out
+    cdf_out = np.cumsum(w_out / w_out.sum())
+    cdf_in = np.cumsum(w_in / w_in.sum())
+    parts = []
+    remaining = int(num_edges)
+    while remaining > 0:
+        m = min(remaining, chunk)
+        s = np.searchsorted(cdf_out, rng.random(m)).clip(0, n - 1)
+        d = np.searchsorted(cdf_in, rng.random(m)).clip(0, n - 1)
+        ok = s != d
+        parts.append((s[ok].astype(np.int64) * n + d[ok].astype(np.int64)))
+        remaining -= m
+    key = np.unique(np.concatenate(parts))
+    s, d = key // n, key % n
+    if not directed:
+        key = np.unique(np.concatenate([s * n + d, d * n + s]))
+        s, d = key // n, key % n
+    return torch.from_numpy(np.stack([s, d]).astype(np.int64))
+
+
+def citation_dag_edges(num_nodes: int, num_edges: int, exponent: float = 2.2, seed: int = 0) -> torch.Tensor:
+    """Heterophilous citation-like DAG: node i cites uniformly chosen earlier nodes j < i; the number of
+    citations per node follows a power law scaled to ``num_edges`` in total."""
+    rng = np.random.default_rng(seed)
+    n = int(num_nodes)
+    w = _power_law_weights(n, exponent, rng)
+    out_deg = np.floor(w / w.sum() * num_edges).astype(np.int64)
+    out_deg = np.minimum(out_deg, np.arange(n))           # node i has only i predecessors
+    short = int(num_edges - out_deg.sum())
+    if short > 0:
+        extra = rng.integers(1, n, size=short)
+        np.add.at(out_deg, extra, 1)
+        out_deg = np.minimum(out_deg, np.arange(n))
+    src = np.repeat(np.arange(n, dtype=np.int64), out_deg)
+    dst = (rng.random(src.size) * src).astype(np.int64)
+    key = np.unique(src * n + dst)
+    return torch.from_numpy(np.stack([key // n, key % n]).astype(np.int64))
+
+
+def random_features(num_nodes: int, dim: int, seed: int = 0, dtype=torch.float32) -> torch.Tensor:
+    g = torch.Generator().manual_seed(int(seed))
+    return torch.randn(int(num_nodes), int(dim), generator=g, dtype=dtype)
+
+
+def random_labels(num_nodes: int, num_classes: int, seed: int = 0, multilabel_p: Optional[float] = None) -> torch.Tensor:
+    g = torch.Generator().manual_seed(int(seed) + 1)
+    if multilabel_p is not None:
+        return (torch.rand(int(num_nodes), int(num_classes), generator=g) < multilabel_p).to(torch.float32)
+    return torch.randint(0, int(num_classes), (int(num_nodes),), generator=g)
+
+
+BENCH_CONFIGS = {
+    # name: model/graph shape of the five benchmark configurations
+    "sbm2k": dict(model="gt", n_layers=2, hidden_dim=64, num_heads=4, nodes=2048, feat=128, classes=7,
+                  budget=8, walk_length=4, walks_per_node=2, graph="sbm"),
+    "arxiv_like": dict(model="graphormer", n_layers=4, hidden_dim=128, num_heads=8, nodes=169_343, edges=1_166_243,
+                       feat=128, classes=40, budget=8, walk_length=4, walks_per_node=2, graph="chung_lu_directed"),
+    "products_like": dict(model="graphgps", n_layers=4, hidden_dim=256, num_heads=8, nodes=2_449_029,
+                          edges=61_859_140, feat=100, classes=47, budget=16, walk_length=6, walks_per_node=4,
+                          graph="chung_lu_undirected"),
+    "amazon_like": dict(model="exphormer", n_layers=3, hidden_dim=256, num_heads=8, nodes=1_569_960,
+                        edges=264_339_468, feat=200, classes=107, budget=32, walk_length=4, walks_per_node=2,
+                        graph="chung_lu_directed", multilabel=True),
+    "patents_like": dict(model="gt", n_layers=4, hidden_dim=128, num_heads=8, nodes=2_923_922, edges=13_975_788,
+                         feat=269, classes=5, budget=8, walk_length=4, walks_per_node=2, graph="dag"),
+}
+
+
+def make_bench_graph(name: str, seed: int = 42, scale: float = 1.0):
+    """(x, y, edge_index, cfg) for a named configuration; ``scale`` < 1 shrinks nodes and edges for tests."""
+    cfg = dict(BENCH_CONFIGS[name])
+    n = max(64, int(cfg["nodes"] * scale))
+    if cfg["graph"] == "sbm":
+        x, y, ei = sbm_graph(n, feat_dim=cfg["feat"], seed=seed)
+        return x, y, ei, cfg
+    e = max(n, int(cfg["edges"] * scale))
+    if cfg["graph"] == "chung_lu_directed":
+        ei = chung_lu_edges(n, e, 2.1, True, seed)
+    elif cfg["graph"] == "chung_lu_undirected":
+        ei = chung_lu_edges(n, e, 2.1, False, seed)
+    else:
+        ei = citation_dag_edges(n, e, 2.2, seed)
+    x = random_features(n, cfg["feat"], seed)
+    y = random_labels(n, cfg["classes"], seed, 0.05 if cfg.get("multilabel") else None)
+    return x, y, ei, cfg
+
+
+def write_dataset(root: str, name: str, x: torch.Tensor, y: torch.Tensor, edge_index: torch.Tensor) -> str:
+    path = os.path.join(root, name)
+    os.makedirs(path, exist_ok=True)
+    torch.save(x, os.path.join(path, "x.pt"))
+    torch.save(y, os.path.join(path, "y.pt"))
+    torch.save(edge_index, os.path.join(path, "edge_index.pt"))
+    return path

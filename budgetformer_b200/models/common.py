@@ -1,0 +1,163 @@
+"""Pieces shared by every node-level model: initialisation, the sparse core attention, the
+activation-tier plumbing and the encoder loop."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from torch import nn
+from torch.nn import functional as F
+from torch.utils.checkpoint import checkpoint
+
+from ..graph.attn_graph import AttnGraph, as_attn_graph
+from ..ops.edge_attention import edge_attention
+from ..parallel import comm
+from ..parallel.initialize import (
+    get_sequence_parallel_group,
+    get_sequence_parallel_rank,
+    get_sequence_parallel_world_size,
+)
+
+
+def init_params(module: nn.Module, n_layers: int) -> None:
+    """Linear ~ N(0, 0.02/sqrt(n_layers)) with zero bias, Embedding ~ N(0, 0.02)
+    (models/graphormer_dist_node_level.py:39-45)."""
+    if isinstance(module, nn.Linear):
+        module.weight.data.normal_(mean=0.0, std=0.02 / math.sqrt(n_layers))
+        if module.bias is not None:
+            module.bias.data.zero_()
+    if isinstance(module, nn.Embedding):
+        module.weight.data.normal_(mean=0.0, std=0.02)
+
+
+class SparseCoreAttention(nn.Module):
+    """Local attention over this rank's ``H/P`` heads and all nodes.
+
+    ``variant`` selects the per-model numerics (see ``ops/edge_attention.py``).  Dense ``full`` attention
+    is kept as a plain-PyTorch option for small graphs, as in the reference
+    (models/graphormer_dist_node_level.py:267-337)."""
+
+    variant = "plain"
+
+    def __init__(self, hidden_size: int, attention_dropout_rate: float, num_heads: int):
+        super().__init__()
+        p = get_sequence_parallel_world_size()
+        self.hidden_size_per_attention_head = hidden_size // num_heads
+        self.num_attention_heads_per_partition = num_heads // p
+        self.num_heads = num_heads
+        self.scale = math.sqrt(self.hidden_size_per_attention_head)
+        self.att_dropout = nn.Dropout(attention_dropout_rate)
+        self.attention_dropout_rate = attention_dropout_rate
+        self._dropout_calls = 0
+
+    def _next_dropout_seed(self) -> int:
+        # drawn from torch's generator so that runs are reproducible under torch.manual_seed
+        return int(torch.randint(0, 2**31 - 1, (1,)).item())
+
+    def edge_table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def full_attention(self, q, k, v, attn_bias=None):
+        q = q.transpose(1, 2)
+        k = k.transpose(1, 2).transpose(2, 3)
+        v = v.transpose(1, 2)
+        x = torch.matmul(q / self.scale, k)
+        if attn_bias is not None:
+            x = x + attn_bias
+        x = self.att_dropout(torch.softmax(x, dim=3))
+        return x.matmul(v).transpose(1, 2).contiguous()
+
+    def sparse(self, q, k, v, graph: AttnGraph, edge_bias=None):
+        b, s, hl, hn = q.shape
+        assert b == 1, "full-graph attention runs with a single sequence"
+        p_drop = self.attention_dropout_rate if (self.variant == "gps" and self.training) else 0.0
+        seed = self._next_dropout_seed() if p_drop > 0 else 0
+        out = edge_attention(q[0], k[0], v[0], graph, variant=self.variant, etable=self.edge_table(),
+                             edge_bias=edge_bias, dropout_p=p_drop, dropout_seed=seed)
+        return out.unsqueeze(0)
+
+    def forward(self, q, k, v, attn_bias=None, edge_index=None, attn_type=None, **kw):
+        b, s = q.size(0), q.size(1)
+        attn_type = "sparse" if attn_type is None else str(attn_type).lower()
+        if attn_type == "full":
+            x = self.full_attention(q, k, v, attn_bias)
+        elif attn_type == "sparse":
+            graph = as_attn_graph(edge_index, s)
+            x = self.sparse(q, k, v, graph, edge_bias=kw.get("edge_bias"))
+        else:
+            raise ValueError(f"unsupported attn_type {attn_type!r}")
+        return x.reshape(b, s, -1)
+
+
+def apply_tier(layer, mode: str, x, **kwargs):
+    """Run one encoder layer under an activation tier (gt_sp/multi_tier.py:31-53):
+    ``retain`` keeps everything, ``keep_mha``/``ffn_only`` keeps the attention half and recomputes
+    the FFN, anything else recomputes the whole layer (including its two all-to-alls)."""
+    if mode == "retain" or mode == "none":
+        return layer(x, **kwargs)
+    if mode in ("keep_mha", "ffn_only"):
+        x = layer.forward_attn_only(x, **kwargs)
+        return layer.forward_ffn_checkpointed(x)
+
+    def _full(h):
+        return layer(h, **kwargs)
+
+    return checkpoint(_full, x, use_reentrant=False)
+
+
+class NodeModelBase(nn.Module):
+    """Activation-checkpoint control shared by all models
+    (e.g. models/gt_dist_node_level.py:741-775)."""
+
+    def _init_ckpt_state(self):
+        self.activation_checkpoint = False
+        self.activation_checkpoint_mode = "none"
+        self._comm_ckpt = None
+
+    def set_activation_checkpoint(self, enabled: bool = True, mode: Optional[str] = None, deferred: bool = False) -> None:
+        aliases = {None: "none", "none": "none", "all": "layer", "layer": "layer", "ffn_only": "ffn_only",
+                   "multi_tier": "multi_tier", "adaptive": "comm_aware", "comm_aware": "comm_aware"}
+        if mode not in aliases:
+            raise ValueError(f"activation_checkpoint_mode must be one of all/ffn_only/adaptive/multi_tier, got {mode!r}")
+        resolved = aliases[mode]
+        enabled = bool(enabled) and resolved != "none"
+        self.activation_checkpoint = enabled
+        self.activation_checkpoint_mode = resolved if enabled else "none"
+        if self.activation_checkpoint_mode == "multi_tier":
+            from ..control.multi_tier import _MultiTierResourceManager
+            self._comm_ckpt = _MultiTierResourceManager(len(self.layers), deferred=deferred)
+        elif self.activation_checkpoint_mode == "comm_aware":
+            from ..control.multi_tier import CommAwareCheckpointer
+            self._comm_ckpt = CommAwareCheckpointer(len(self.layers))
+        else:
+            self._comm_ckpt = None
+
+    def comm_aware_notify_budget_frozen(self, reuse_deferred_baseline: bool = False) -> None:
+        if self._comm_ckpt is not None and hasattr(self._comm_ckpt, "notify_budget_frozen"):
+            self._comm_ckpt.notify_budget_frozen(reuse_deferred_baseline=reuse_deferred_baseline)
+
+    def comm_aware_notify_step_end(self, device, t_bwd: float = None, t_fwd: float = None) -> None:
+        if self._comm_ckpt is not None:
+            self._comm_ckpt.notify_step_end(device, t_bwd=t_bwd, t_fwd=t_fwd)
+
+    def _run_layers(self, x, **kwargs):
+        use_ckpt = self.activation_checkpoint and self.training and torch.is_grad_enabled()
+        mode = self.activation_checkpoint_mode
+        managed = use_ckpt and mode in ("multi_tier", "comm_aware") and self._comm_ckpt is not None
+        if managed:
+            self._comm_ckpt.plan(x.device)
+        for i, layer in enumerate(self.layers):
+            if not use_ckpt:
+                x = layer(x, **kwargs)
+                continue
+            layer_mode = self._comm_ckpt.mode(i) if managed else mode
+            x = apply_tier(layer, layer_mode, x, **kwargs)
+        if managed:
+            self._comm_ckpt.record_post_forward_memory(x.device)
+        return x
+
+    def core_attention_modules(self):
+        for layer in self.layers:
+            d = layer.self_attention.dist_attn
+            yield getattr(d, "local_attn", d)
