@@ -13,6 +13,8 @@ extern "C" {
 #define BF_FP16 1
 #define BF_FP32 2
 
+#define BF_MAX_PEERS 8
+
 #define BF_HUB_DEGREE 1024   // rows longer than this use the chunked hub kernels
 #define BF_HUB_CHUNK 8192    // edges per hub chunk (one thread block)
 
@@ -68,6 +70,33 @@ typedef struct {
 int bf_budget_select(const bf_build_params* p, cudaStream_t st);
 int bf_ell_to_csr(const int* ell_col, const uint8_t* ell_type, const int* rowptr, int n, int cap, int* col,
                   uint8_t* etype, cudaStream_t st);
+
+// ---- tcgen05 GEMM with fused epilogue / fused nodes->heads all-to-all (gemm_tcgen05.cu) ---------
+typedef struct {
+  const void* A;                    // [M, K] 16-bit, row stride lda (elements)
+  const void* B;                    // [N, K] 16-bit (nn.Linear weight layout), row stride ldb
+  long long lda, ldb;
+  int M, N, K;                      // K % 64 == 0, N % 16 == 0
+  int dtype;                        // BF_BF16 or BF_FP16
+  const float* bias;                // [N] fp32 or NULL
+  int act;                          // 0 none, 1 ReLU, 2 GELU (erf)
+  float dropout_p;                  // after the activation; mask = hash(seed, row, col)
+  uint32_t dropout_seed;
+  const void* residual;             // [M, ldr] 16-bit added last, or NULL
+  long long ldr;
+  const void* relu_mask;            // [M, ldm] 16-bit: result zeroed where mask <= 0, or NULL
+  long long ldm;
+  float out_scale;                  // multiplies the accumulator (0 means 1)
+  int out_fp32;                     // 1: fp32 output
+  int n_dest;                       // >1: columns [d*N/n_dest, (d+1)*N/n_dest) go to dst[d] (peer buffers)
+  long long dst_row_offset;         // added to the row index in every destination
+  long long ldc;                    // destination row stride (elements)
+  void* dst[BF_MAX_PEERS];
+  int* status;                      // device int[4]; non-zero after a bounded wait expired
+} bf_gemm_params;
+
+int bf_gemm_supported(int M, int N, int K);
+int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,443 @@
+// Persistent tcgen05 GEMM for sm_100a with fused epilogues and a fused nodes->heads all-to-all.
+//
+//   C[M, N] = A[M, K] * B[N, K]^T      bf16 / fp16 operands, fp32 accumulation in tensor memory
+//
+// * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, one 64-element K panel per
+//   stage) into a 4-deep shared-memory ring; one elected thread issues tcgen05.mma (M = 128, N = BLOCK_N
+//   <= 256, K = 16 per instruction) and releases ring stages with tcgen05.commit;
+// * two accumulators of BLOCK_N columns alternate in tensor memory, so the epilogue warps drain tile i
+//   (tcgen05.ld) while tile i+1 is being multiplied;
+// * epilogue (per thread = one output row): + bias, ReLU / GELU, counter-based dropout, + residual,
+//   ReLU-gradient mask, then 16-byte stores.  With `n_dest > 1` the columns of a tile are routed to the
+//   owning rank's buffer through peer pointers: this is the sequence-parallel nodes->heads all-to-all
+//   (3 projections + 3 all-to-alls + 6 copies in the reference: gt_sp/layer.py:35-41,264-266) executed
+//   by the GEMM itself, tile by tile, with plain st.global over NVLink;
+// * every mbarrier wait is bounded: on expiry the kernel records a status word, stops issuing work,
+//   lets copies in flight land, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "bf_kernels.h"
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;          // one 128-byte swizzle panel of 16-bit elements
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int NUM_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+struct GemmArgs {
+  int M, N, K;
+  int block_n, n_chunks, m_tiles;
+  int is_fp16;
+  // epilogue
+  const float* bias;             // [N] or null
+  int act;                       // 0 none, 1 relu, 2 gelu
+  float dropout_p;               // applied after activation
+  uint32_t dropout_seed;
+  const void* residual;          // [M, ldr] 16-bit or null
+  long long ldr;
+  const void* relu_mask;         // [M, ldm] 16-bit: out = mask > 0 ? acc : 0
+  long long ldm;
+  float out_scale;
+  int out_fp32;
+  // output routing
+  int n_dest;                    // 1 = plain row-major output
+  int cols_per_dest;             // N / n_dest
+  long long dst_row_offset;      // row offset inside every destination buffer
+  long long ldc;                 // destination row stride (elements)
+  void* dst[BF_MAX_PEERS];
+  int* status;                   // [4] device status words (0 = ok)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait on a phase parity.  Returns false when the limit expires or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows at 128-byte pitch, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                               // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                               // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ uint32_t make_instr_desc(int block_n, int is_fp16) {
+  uint32_t d = 0;
+  d |= 1u << 4;                                  // accumulator fp32
+  d |= (is_fp16 ? 0u : 1u) << 7;                 // A format: 0 fp16, 1 bf16
+  d |= (is_fp16 ? 0u : 1u) << 10;                // B format
+  d |= (uint32_t)(block_n >> 3) << 17;           // N / 8
+  d |= (uint32_t)(BLOCK_M >> 4) << 24;           // M / 16
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x = (x ^ (x >> 16)) * 0x7FEB352Du;
+  x = (x ^ (x >> 15)) * 0x846CA68Bu;
+  return x ^ (x >> 16);
+}
+// keep decision for element (row, col) — identical to ops/dropout.py::hash_keep_mask
+__device__ __forceinline__ bool keep_elem(uint32_t seed, uint32_t row, uint32_t col, uint32_t thresh) {
+  return mix32(row * 0x9E3779B1u + col * 0x85EBCA77u + seed) >= thresh;
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+__device__ __forceinline__ float ld16_as_float(const void* p, int is_fp16) {
+  const unsigned short u = *reinterpret_cast<const unsigned short*>(p);
+  if (is_fp16) return __half2float(__ushort_as_half(u));
+  return __uint_as_float(((uint32_t)u) << 16);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, int is_fp16) {
+  if (is_fp16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct __align__(1024) SmemLayout {
+  // operand ring follows at offset 0 of the dynamic buffer (A stages then B stages), then this control block
+};
+
+struct Control {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const GemmArgs g) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t a_stage_bytes = BLOCK_M * BLOCK_K * 2;
+  const uint32_t b_stage_bytes = (uint32_t)g.block_n * BLOCK_K * 2;
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * a_stage_bytes;
+  Control* ctl = reinterpret_cast<Control*>(smem_b + STAGES * b_stage_bytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int k_panels = g.K / BLOCK_K;
+  const int total_tiles = g.m_tiles * g.n_chunks;
+  const uint32_t tmem_cols = (2 * g.block_n <= 32) ? 32 : (2 * g.block_n <= 64) ? 64 : (2 * g.block_n <= 128) ? 128
+                            : (2 * g.block_n <= 256) ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4); }
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m_tile = t / g.n_chunks, n_chunk = t % g.n_chunks;
+        for (int kp = 0; kp < k_panels; ++kp) {
+          if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&ctl->full[stage], a_stage_bytes + b_stage_bytes);
+          tma_load_2d(smem_a + stage * a_stage_bytes, &map_a, &ctl->full[stage], kp * BLOCK_K, m_tile * BLOCK_M);
+          tma_load_2d(smem_b + stage * b_stage_bytes, &map_b, &ctl->full[stage], kp * BLOCK_K, n_chunk * g.block_n);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(g.status, 1); }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc(g.block_n, g.is_fp16);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * (uint32_t)g.block_n;
+        for (int kp = 0; kp < k_panels; ++kp) {
+          if (!mbar_wait(&ctl->full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * a_stage_bytes));
+          const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * b_stage_bytes));
+#pragma unroll
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            // advance 32 bytes (16 elements) along K inside the swizzle atom: +2 in 16-byte units
+            umma_f16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kp > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&ctl->empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&ctl->tmem_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(g.status, 2); }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (2..5)
+    const int quarter = warp & 3;                       // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t thresh = g.dropout_p > 0.f ? (uint32_t)(g.dropout_p * 4294967296.0) : 0u;
+    const float keep_scale = g.dropout_p > 0.f ? 1.f / (1.f - g.dropout_p) : 1.f;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int m_tile = t / g.n_chunks, n_chunk = t % g.n_chunks;
+      if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const long long row = (long long)m_tile * BLOCK_M + row_in_tile;
+      const bool row_ok = row < g.M;
+      const uint32_t taddr = tmem_base + acc * (uint32_t)g.block_n + ((uint32_t)(quarter * 32) << 16);
+      for (int c0 = 0; c0 < g.block_n; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        const int col0 = n_chunk * g.block_n + c0;
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]) * g.out_scale;
+        if (g.bias) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] += __ldg(g.bias + col0 + i);
+        }
+        if (g.act == 1) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+        } else if (g.act == 2) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = gelu_erf(v[i]);
+        }
+        if (thresh) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            v[i] = keep_elem(g.dropout_seed, (uint32_t)row, (uint32_t)(col0 + i), thresh) ? v[i] * keep_scale : 0.f;
+        }
+        if (g.relu_mask) {
+          const uint4* mp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.relu_mask) + row * g.ldm + col0);
+          uint4 m0 = __ldg(mp), m1 = __ldg(mp + 1);
+          const unsigned short* ms0 = reinterpret_cast<const unsigned short*>(&m0);
+          const unsigned short* ms1 = reinterpret_cast<const unsigned short*>(&m1);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            // positive and non-zero in either 16-bit float format: sign bit clear and magnitude non-zero
+            if (!((ms0[i] & 0x8000u) == 0 && (ms0[i] & 0x7FFFu) != 0)) v[i] = 0.f;
+            if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
+          }
+        }
+        if (g.residual) {
+          const unsigned short* rp = static_cast<const unsigned short*>(g.residual) + row * g.ldr + col0;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] += ld16_as_float(rp + i, g.is_fp16);
+        }
+        // route the 16 columns: they never straddle a destination because cols_per_dest % 16 == 0
+        const int dest = g.n_dest > 1 ? col0 / g.cols_per_dest : 0;
+        const int dcol = g.n_dest > 1 ? col0 - dest * g.cols_per_dest : col0;
+        const long long drow = g.dst_row_offset + row;
+        if (g.out_fp32) {
+          float4* op = reinterpret_cast<float4*>(static_cast<float*>(g.dst[dest]) + drow * g.ldc + dcol);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) op[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+          uint4* op = reinterpret_cast<uint4*>(static_cast<unsigned short*>(g.dst[dest]) + drow * g.ldc + dcol);
+          uint4 o0, o1;
+          o0.x = pack2(v[0], v[1], g.is_fp16); o0.y = pack2(v[2], v[3], g.is_fp16);
+          o0.z = pack2(v[4], v[5], g.is_fp16); o0.w = pack2(v[6], v[7], g.is_fp16);
+          o1.x = pack2(v[8], v[9], g.is_fp16); o1.y = pack2(v[10], v[11], g.is_fp16);
+          o1.z = pack2(v[12], v[13], g.is_fp16); o1.w = pack2(v[14], v[15], g.is_fp16);
+          op[0] = o0;
+          op[1] = o1;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(g.status, 3); }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before shared memory is released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// 2-D row-major 16-bit tensor [rows, cols] with row stride ld (elements); box = [box_rows, 64 cols], swizzle 128B.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows,
+             int is_fp16) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+int pick_block_n(int n, int cols_per_dest) {
+  const int cands[] = {256, 192, 128, 96, 64, 48, 32, 16};
+  for (int c : cands)
+    if (n % c == 0) return c;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int bf_gemm_supported(int M, int N, int K) {
+  return (M > 0 && K >= BLOCK_K && K % BLOCK_K == 0 && N >= 16 && pick_block_n(N, N) > 0) ? 1 : 0;
+}
+
+extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
+  if (!bf_gemm_supported(p->M, p->N, p->K)) return (int)cudaErrorInvalidValue;
+  if (p->n_dest < 1 || p->n_dest > BF_MAX_PEERS || p->N % p->n_dest != 0) return (int)cudaErrorInvalidValue;
+  const int cols_per_dest = p->N / p->n_dest;
+  if (p->n_dest > 1 && cols_per_dest % 16 != 0) return (int)cudaErrorInvalidValue;
+  if ((p->lda * 2) % 16 != 0 || (p->ldb * 2) % 16 != 0 || ((uintptr_t)p->A) % 16 != 0 || ((uintptr_t)p->B) % 16 != 0)
+    return (int)cudaErrorInvalidValue;
+  GemmArgs g;
+  g.M = p->M; g.N = p->N; g.K = p->K;
+  g.block_n = pick_block_n(p->N, cols_per_dest);
+  g.n_chunks = p->N / g.block_n;
+  g.m_tiles = (p->M + BLOCK_M - 1) / BLOCK_M;
+  g.is_fp16 = p->dtype == BF_FP16 ? 1 : 0;
+  g.bias = p->bias; g.act = p->act; g.dropout_p = p->dropout_p; g.dropout_seed = p->dropout_seed;
+  g.residual = p->residual; g.ldr = p->ldr; g.relu_mask = p->relu_mask; g.ldm = p->ldm;
+  g.out_scale = p->out_scale == 0.f ? 1.f : p->out_scale;
+  g.out_fp32 = p->out_fp32;
+  g.n_dest = p->n_dest; g.cols_per_dest = cols_per_dest; g.dst_row_offset = p->dst_row_offset; g.ldc = p->ldc;
+  for (int i = 0; i < BF_MAX_PEERS; ++i) g.dst[i] = i < p->n_dest ? p->dst[i] : nullptr;
+  g.status = p->status;
+  CUtensorMap map_a, map_b;
+  if (make_map(&map_a, p->A, p->M, p->K, p->lda, BLOCK_M, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
+  if (make_map(&map_b, p->B, p->N, p->K, p->ldb, g.block_n, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
+  const size_t smem = 1024 + STAGES * (BLOCK_M * BLOCK_K * 2 + (size_t)g.block_n * BLOCK_K * 2) + sizeof(Control) + 64;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int total = g.m_tiles * g.n_chunks;
+  const int grid = total < sms ? total : sms;
+  gemm_tn_tcgen05_kernel<<<grid, NUM_THREADS, smem, st>>>(map_a, map_b, g);
+  return (int)cudaGetLastError();
+}

@@ -52,6 +52,8 @@ def build_attn_graph(
     rowptr, col, etype, totals = ext.build_attn_graph(
         topo.in_rowptr, topo.in_src, topo.out_rowptr, topo.out_col, int(topo.num_nodes),
         int(br), int(bw), int(walks_per_node), int(walk_length), bool(exphormer), int(seed), int(num_threads))
+    if topo.device.type == "cuda":
+        _ext.count_launches(2)
     g = AttnGraph(int(topo.num_nodes), rowptr, col, etype if exphormer else None,
                   max_degree=int(br) + int(bw) + (1 if exphormer else 0))
     g._totals = totals  # device tensor; read lazily to avoid a sync on the hot path

@@ -136,3 +136,22 @@ def available() -> bool:
         return _MOD is not None or is_built()
     except Exception:
         return False
+
+
+# ---- launch accounting ------------------------------------------------------------------------------
+_LAUNCHES = 0
+
+
+def count_launches(n: int) -> None:
+    """Called by the op wrappers with the number of kernels of this package they just launched."""
+    global _LAUNCHES
+    _LAUNCHES += int(n)
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def reset_launch_count() -> None:
+    global _LAUNCHES
+    _LAUNCHES = 0

@@ -1,0 +1,114 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same ops."""
+import pytest
+import torch
+
+from budgetformer_b200.graph.builder import build_attn_graph
+from budgetformer_b200.ops.edge_attention import edge_attention, edge_attention_reference
+from tests.helpers import random_attn_graph, random_topology
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: (2e-4, 2e-4), torch.bfloat16: (3e-2, 3e-2), torch.float16: (5e-3, 5e-3)}
+
+
+def _run(variant, dtype, hl, hn, hub_row=0, hub_col=0, dropout=0.0, n=257, e=2100):
+    dev = torch.device("cuda")
+    g = random_attn_graph(n, e, hub_row, hub_col, seed=hl * 7 + hn, typed=(variant == "exphormer")).to(dev)
+    torch.manual_seed(1)
+    q, k, v = (torch.randn(n, hl, hn, device=dev).mul(1.5).to(dtype).requires_grad_(True) for _ in range(3))
+    etab = torch.randn(2, hl, hn, device=dev, requires_grad=True) if variant == "exphormer" else None
+    dout = torch.randn(n, hl, hn, device=dev).to(dtype)
+    out = edge_attention(q, k, v, g, variant=variant, etable=etab, dropout_p=dropout, dropout_seed=1234)
+    out.backward(dout)
+    got = [out.detach().float(), q.grad.float(), k.grad.float(), v.grad.float()]
+    if etab is not None:
+        got.append(etab.grad.float())
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    e2 = etab.detach().clone().requires_grad_(True) if etab is not None else None
+    ref = edge_attention_reference(q2, k2, v2, g, variant=variant, etable=e2, dropout_p=dropout, dropout_seed=1234)
+    ref.backward(dout.float())
+    want = [ref.detach(), q2.grad, k2.grad, v2.grad] + ([e2.grad] if e2 is not None else [])
+    rtol, atol = TOL[dtype]
+    names = ["out", "dq", "dk", "dv", "detab"]
+    for name, a, b in zip(names, got, want):
+        scale = max(1.0, float(b.abs().max()))
+        err = float((a - b).abs().max())
+        assert err <= atol * scale + rtol * scale, f"{variant}/{dtype}/{name}: max err {err} (scale {scale})"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hl,hn", [(8, 16), (1, 16), (4, 32), (2, 64), (3, 16), (1, 32)])
+def test_edge_attention_plain(dtype, hl, hn):
+    _run("plain", dtype, hl, hn)
+
+
+@pytest.mark.parametrize("variant", ["gps", "exphormer"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_edge_attention_variants(variant, dtype):
+    _run(variant, dtype, 4, 16)
+    _run(variant, dtype, 1, 32)
+
+
+def test_edge_attention_gps_dropout():
+    _run("gps", torch.float32, 4, 16, dropout=0.4)
+    _run("gps", torch.bfloat16, 2, 32, dropout=0.25)
+
+
+@pytest.mark.parametrize("variant", ["plain", "gps", "exphormer"])
+def test_edge_attention_hub_rows(variant):
+    """A query with 5000 in-edges and a key used by 4000 queries take the chunked hub kernels."""
+    _run(variant, torch.float32, 4, 16, hub_row=5000, hub_col=4000, n=4500, e=9000)
+    _run(variant, torch.bfloat16, 1, 16, hub_row=20000, hub_col=3000, n=4500, e=9000)
+
+
+def test_edge_attention_strided_qkv_views():
+    dev = torch.device("cuda")
+    n, hl, hn = 300, 4, 16
+    g = random_attn_graph(n, 2000, seed=3).to(dev)
+    qkv = torch.randn(n, 3, hl, hn, device=dev, dtype=torch.bfloat16)
+    q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+    out = edge_attention(q, k, v, g)
+    ref = edge_attention_reference(q.float(), k.float(), v.float(), g)
+    assert torch.allclose(out.float(), ref, atol=3e-2, rtol=3e-2)
+
+
+def test_edge_attention_empty_rows_and_determinism():
+    dev = torch.device("cuda")
+    n, hl, hn = 128, 2, 16
+    g = random_attn_graph(n, 100, seed=5).to(dev)          # most queries have no in-edges
+    q, k, v = (torch.randn(n, hl, hn, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    a = edge_attention(q, k, v, g)
+    b = edge_attention(q, k, v, g)
+    assert torch.equal(a, b)
+    deg = (g.rowptr[1:] - g.rowptr[:-1])
+    assert float(a[deg == 0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("exph", [False, True])
+@pytest.mark.parametrize("cfg", [(4, 4, 2, 4), (2, 6, 3, 5), (8, 0, 2, 4), (0, 5, 2, 3), (32, 32, 8, 8), (16, 16, 4, 6)])
+def test_gpu_builder_matches_cpu_builder(cfg, exph):
+    br, bw, w, l = cfg
+    topo, _ = random_topology(700, 6000, hub_in=900, hub_out=400, seed=11)
+    cpu = build_attn_graph(topo, br, bw, w, l, 77, exphormer=exph)
+    gpu = build_attn_graph(topo.to("cuda"), br, bw, w, l, 77, exphormer=exph)
+    assert torch.equal(cpu.rowptr, gpu.rowptr.cpu())
+    assert torch.equal(cpu.col, gpu.col.cpu())
+    if exph:
+        assert torch.equal(cpu.etype, gpu.etype.cpu())
+    assert cpu._totals.tolist() == gpu._totals.cpu().tolist()
+
+
+def test_gpu_builder_seed_changes_graph_and_is_reproducible():
+    topo, _ = random_topology(500, 5000, seed=2)
+    t = topo.to("cuda")
+    a = build_attn_graph(t, 4, 4, 2, 4, 1)
+    b = build_attn_graph(t, 4, 4, 2, 4, 1)
+    c = build_attn_graph(t, 4, 4, 2, 4, 2)
+    assert torch.equal(a.col, b.col) and torch.equal(a.rowptr, b.rowptr)
+    assert not (a.col.numel() == c.col.numel() and torch.equal(a.col, c.col))
+
+
+def test_extension_is_loaded_from_tree():
+    from budgetformer_b200.ops import _ext
+    mod = _ext.load()
+    assert "budgetformer_b200/csrc/build" in mod.__file__.replace("\\", "/")
