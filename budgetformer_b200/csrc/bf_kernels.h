@@ -14,6 +14,7 @@ extern "C" {
 #define BF_FP32 2
 
 #define BF_MAX_PEERS 8
+#define BF_FLAG_CHANNELS 64      // barrier channels per flag page (uint32[BF_FLAG_CHANNELS][BF_MAX_PEERS])
 
 #define BF_HUB_DEGREE 1024   // rows longer than this use the chunked hub kernels
 #define BF_HUB_CHUNK 8192    // edges per hub chunk (one thread block)
@@ -97,6 +98,27 @@ typedef struct {
 
 int bf_gemm_supported(int M, int N, int K);
 int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st);
+
+// ---- peer-memory collectives (symm_comm.cu) ----------------------------------------------------
+// `flag_pages[r]` / `bufs[r]` are this process's mappings of rank r's symmetric allocation.
+int bf_peer_barrier(void* const* flag_pages, int rank, int world, int channel, uint32_t epoch, int* status,
+                    cudaStream_t st);
+int bf_allreduce_mean(void* const* bufs, float* multicast_ptr, int rank, int world, long long n_floats,
+                      cudaStream_t st);
+int bf_peer_gather_cols(void* const* src, int world, long long row0, long long rows, int cols_bytes,
+                        long long src_ld_bytes, void* dst, long long dst_ld_bytes, cudaStream_t st);
+int bf_peer_scatter_cols(void* const* dst, int world, long long row0, long long rows, int cols_bytes,
+                         long long dst_ld_bytes, const void* src, long long src_ld_bytes, cudaStream_t st);
+
+// ---- row kernels (norm_fused.cu) -----------------------------------------------------------------
+int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma, const float* beta, void* y, long long ldy,
+                     float* stats /* [rows, 2] mean, rstd or NULL */, long long rows, int h, float eps, int dtype,
+                     cudaStream_t st);
+int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* stats,
+                     const float* gamma, void* dx, long long lddx, float* dgamma /* += */, float* dbeta /* += */,
+                     long long rows, int h, int dtype, cudaStream_t st);
+int bf_hash_dropout(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, uint32_t seed,
+                    float p, int dtype, cudaStream_t st);
 
 #ifdef __cplusplus
 }

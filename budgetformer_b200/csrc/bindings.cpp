@@ -170,10 +170,135 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
   return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
 }
 
+// C = A * W^T with fused epilogue.  `dst_ptrs` holds one device pointer per destination (1 = plain output).
+void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, int64_t seed, OptTensor residual,
+             OptTensor relu_mask, double out_scale, bool out_fp32, std::vector<int64_t> dst_ptrs, int64_t dst_row_offset,
+             int64_t ldc, Tensor status) {
+  TORCH_CHECK(A.is_cuda() && W.is_cuda() && A.dim() == 2 && W.dim() == 2, "gemm_tn: A [M,K], W [N,K] on CUDA");
+  TORCH_CHECK(A.scalar_type() == W.scalar_type() && (A.scalar_type() == torch::kBFloat16 || A.scalar_type() == torch::kHalf),
+              "gemm_tn: bf16/fp16 operands");
+  TORCH_CHECK(A.stride(1) == 1 && W.stride(1) == 1 && A.size(1) == W.size(1), "gemm_tn: K-contiguous operands");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt && status.numel() >= 4);
+  TORCH_CHECK(!dst_ptrs.empty() && (int)dst_ptrs.size() <= BF_MAX_PEERS);
+  c10::cuda::CUDAGuard guard(A.device());
+  bf_gemm_params p{};
+  p.A = A.data_ptr(); p.B = W.data_ptr(); p.lda = A.stride(0); p.ldb = W.stride(0);
+  p.M = (int)A.size(0); p.N = (int)W.size(0); p.K = (int)A.size(1);
+  p.dtype = dtype_code(A);
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == torch::kFloat && bias->is_contiguous() && bias->numel() == p.N);
+    p.bias = bias->data_ptr<float>();
+  }
+  p.act = (int)act; p.dropout_p = (float)dropout_p; p.dropout_seed = (uint32_t)seed;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == A.scalar_type() && residual->stride(1) == 1 && residual->size(0) == p.M &&
+                residual->size(1) == p.N && dst_ptrs.size() == 1);
+    p.residual = residual->data_ptr(); p.ldr = residual->stride(0);
+  }
+  if (relu_mask.has_value()) {
+    TORCH_CHECK(relu_mask->scalar_type() == A.scalar_type() && relu_mask->stride(1) == 1 && relu_mask->size(0) == p.M &&
+                relu_mask->size(1) == p.N && (relu_mask->stride(0) * 2) % 16 == 0 && ((uintptr_t)relu_mask->data_ptr()) % 16 == 0);
+    p.relu_mask = relu_mask->data_ptr(); p.ldm = relu_mask->stride(0);
+  }
+  p.out_scale = (float)out_scale; p.out_fp32 = out_fp32 ? 1 : 0;
+  p.n_dest = (int)dst_ptrs.size(); p.dst_row_offset = dst_row_offset; p.ldc = ldc;
+  TORCH_CHECK((ldc * (out_fp32 ? 4 : 2)) % 16 == 0, "gemm_tn: destination rows must be 16-byte aligned");
+  for (size_t i = 0; i < dst_ptrs.size(); ++i) {
+    TORCH_CHECK(((uintptr_t)dst_ptrs[i]) % 16 == 0);
+    p.dst[i] = reinterpret_cast<void*>(dst_ptrs[i]);
+  }
+  p.status = status.data_ptr<int>();
+  TORCH_CHECK(bf_gemm_supported(p.M, p.N, p.K), "gemm_tn: unsupported shape M=", p.M, " N=", p.N, " K=", p.K);
+  check_cuda(bf_gemm_tn(&p, at::cuda::getCurrentCUDAStream()), "gemm_tn");
+}
+
+std::vector<void*> as_ptrs(const std::vector<int64_t>& v) {
+  std::vector<void*> o(BF_MAX_PEERS, nullptr);
+  TORCH_CHECK(v.size() <= BF_MAX_PEERS, "at most ", BF_MAX_PEERS, " peers");
+  for (size_t i = 0; i < v.size(); ++i) o[i] = reinterpret_cast<void*>(v[i]);
+  return o;
+}
+
+void peer_barrier(std::vector<int64_t> flag_pages, int64_t rank, int64_t channel, int64_t epoch, Tensor status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  auto p = as_ptrs(flag_pages);
+  check_cuda(bf_peer_barrier(p.data(), (int)rank, (int)flag_pages.size(), (int)channel, (uint32_t)epoch,
+                             status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()), "peer_barrier");
+}
+
+void allreduce_mean(std::vector<int64_t> bufs, int64_t multicast_ptr, int64_t rank, int64_t n_floats, Tensor anchor) {
+  c10::cuda::CUDAGuard guard(anchor.device());
+  auto p = as_ptrs(bufs);
+  check_cuda(bf_allreduce_mean(p.data(), reinterpret_cast<float*>(multicast_ptr), (int)rank, (int)bufs.size(), n_floats,
+                               at::cuda::getCurrentCUDAStream()), "allreduce_mean");
+}
+
+void peer_gather_cols(std::vector<int64_t> src, int64_t row0, int64_t rows, int64_t cols_bytes, int64_t src_ld_bytes,
+                      Tensor dst) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  TORCH_CHECK(dst.dim() == 2 && dst.stride(1) == 1 && dst.size(0) >= rows);
+  auto p = as_ptrs(src);
+  check_cuda(bf_peer_gather_cols(p.data(), (int)src.size(), row0, rows, (int)cols_bytes, src_ld_bytes, dst.data_ptr(),
+                                 dst.stride(0) * dst.element_size(), at::cuda::getCurrentCUDAStream()), "peer_gather_cols");
+}
+
+void peer_scatter_cols(std::vector<int64_t> dstp, int64_t row0, int64_t rows, int64_t cols_bytes, int64_t dst_ld_bytes,
+                       Tensor src) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.dim() == 2 && src.stride(1) == 1 && src.size(0) >= rows);
+  auto p = as_ptrs(dstp);
+  check_cuda(bf_peer_scatter_cols(p.data(), (int)dstp.size(), row0, rows, (int)cols_bytes, dst_ld_bytes, src.data_ptr(),
+                                  src.stride(0) * src.element_size(), at::cuda::getCurrentCUDAStream()), "peer_scatter_cols");
+}
+
+std::vector<Tensor> layernorm_fwd(Tensor x, Tensor gamma, Tensor beta, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty({x.size(0), x.size(1)}, x.options());
+  Tensor stats = torch::empty({x.size(0), 2}, x.options().dtype(torch::kFloat));
+  check_cuda(bf_layernorm_fwd(x.data_ptr(), x.stride(0), gamma.data_ptr<float>(), beta.data_ptr<float>(), y.data_ptr(),
+                              y.stride(0), stats.data_ptr<float>(), x.size(0), (int)x.size(1), (float)eps, dtype_code(x),
+                              at::cuda::getCurrentCUDAStream()), "layernorm_fwd");
+  return {y, stats};
+}
+
+std::vector<Tensor> layernorm_bwd(Tensor dy, Tensor x, Tensor stats, Tensor gamma) {
+  TORCH_CHECK(dy.is_cuda() && dy.dim() == 2 && dy.stride(1) == 1 && x.stride(1) == 1 && dy.scalar_type() == x.scalar_type());
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = torch::empty({x.size(0), x.size(1)}, x.options());
+  Tensor dgamma = torch::zeros({x.size(1)}, x.options().dtype(torch::kFloat));
+  Tensor dbeta = torch::zeros({x.size(1)}, x.options().dtype(torch::kFloat));
+  check_cuda(bf_layernorm_bwd(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), stats.data_ptr<float>(),
+                              gamma.data_ptr<float>(), dx.data_ptr(), dx.stride(0), dgamma.data_ptr<float>(),
+                              dbeta.data_ptr<float>(), x.size(0), (int)x.size(1), dtype_code(x),
+                              at::cuda::getCurrentCUDAStream()), "layernorm_bwd");
+  return {dx, dgamma, dbeta};
+}
+
+Tensor hash_dropout(Tensor x, int64_t seed, double p) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty({x.size(0), x.size(1)}, x.options());
+  check_cuda(bf_hash_dropout(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.size(0), (int)x.size(1),
+                             (uint32_t)seed, (float)p, dtype_code(x), at::cuda::getCurrentCUDAStream()), "hash_dropout");
+  return y;
+}
+
+bool gemm_supported(int64_t M, int64_t N, int64_t K) { return bf_gemm_supported((int)M, (int)N, (int)K) != 0; }
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("edge_attn_fwd", &edge_attn_fwd);
   m.def("edge_attn_bwd", &edge_attn_bwd);
   m.def("build_attn_graph", &build_attn_graph);
+  m.def("gemm_tn", &gemm_tn);
+  m.def("gemm_supported", &gemm_supported);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("hash_dropout", &hash_dropout);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("allreduce_mean", &allreduce_mean);
+  m.def("peer_gather_cols", &peer_gather_cols);
+  m.def("peer_scatter_cols", &peer_scatter_cols);
 }

@@ -29,7 +29,7 @@ constexpr int BLOCK_K = 64;          // one 128-byte swizzle panel of 16-bit ele
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
 constexpr int NUM_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct GemmArgs {
   int M, N, K;

@@ -1,0 +1,69 @@
+"""Feed-forward block on the tcgen05 GEMM: ``y = residual + drop2(W2 drop1(act(W1 x + b1)) + b2)``.
+
+Forward is two kernels (activation + dropout in the first epilogue, bias + dropout + residual in the
+second).  Backward for ReLU uses the mask epilogue: ``dh = (g W2) * [h > 0] / (1 - p1)`` comes out of
+the GEMM directly, so the hidden gradient is never touched by a separate elementwise pass.  GELU keeps
+the pre-activation and differentiates it with PyTorch.  Replaces Linear -> act -> Dropout -> Linear ->
+Dropout -> add of the reference layers (e.g. models/gt_dist_node_level.py:655-660)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import gemm
+from .norm import hash_dropout, new_seed
+
+
+class _FusedFFNRelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, residual, p1, p2, seed1, seed2):
+        w1h, w2h = w1.to(x.dtype), w2.to(x.dtype)
+        h = gemm.gemm_tn(x, w1h, b1, "relu", dropout_p=p1, dropout_seed=seed1)
+        y = gemm.gemm_tn(h, w2h, b2, None, dropout_p=p2, dropout_seed=seed2, residual=residual)
+        ctx.save_for_backward(x, h, w1h, w2h)
+        ctx.cfg = (float(p1), float(p2), int(seed1), int(seed2), residual is not None, w1.dtype,
+                   b1 is not None, b2 is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, h, w1h, w2h = ctx.saved_tensors
+        p1, p2, seed1, seed2, has_res, wdtype, has_b1, has_b2 = ctx.cfg
+        dy = dy.contiguous()
+        g2 = hash_dropout(dy, seed2, p2) if p2 > 0 else dy
+        dh = gemm.gemm_tn(g2, w2h.t().contiguous(), relu_mask=h, out_scale=1.0 / (1.0 - p1) if p1 > 0 else 1.0)
+        dx = gemm.gemm_tn(dh, w1h.t().contiguous())
+        dw2 = torch.matmul(g2.t(), h).to(wdtype)
+        dw1 = torch.matmul(dh.t(), x).to(wdtype)
+        db2 = g2.float().sum(0).to(wdtype) if has_b2 else None
+        db1 = dh.float().sum(0).to(wdtype) if has_b1 else None
+        return dx, dw1, db1, dw2, db2, (dy if has_res else None), None, None, None, None
+
+
+def fused_ffn(x: torch.Tensor, w1, b1, w2, b2, *, act: str = "relu", residual: Optional[torch.Tensor] = None,
+              p1: float = 0.0, p2: float = 0.0, training: bool = True) -> torch.Tensor:
+    """2-D ``x`` ``[rows, h]``; ``residual`` is added last (pass ``x`` for a residual FFN)."""
+    if not training:
+        p1 = p2 = 0.0
+    n1, k1 = w1.shape
+    ok = x.is_cuda and x.stride(1) == 1 and gemm.supported(x.size(0), n1, k1, x.dtype) \
+        and gemm.supported(x.size(0), w2.size(0), w2.size(1), x.dtype)
+    if ok and act == "relu":
+        return _FusedFFNRelu.apply(x, w1, b1, w2, b2, residual, p1, p2, new_seed() if p1 > 0 else 0,
+                                   new_seed() if p2 > 0 else 0)
+    if ok and act == "gelu":
+        z = gemm.fused_linear(x, w1, b1)
+        hdn = F.gelu(z)
+        if p1 > 0:
+            hdn = hash_dropout(hdn, new_seed(), p1)
+        y = gemm.fused_linear(hdn, w2, b2)
+        if p2 > 0:
+            y = hash_dropout(y, new_seed(), p2)
+        return y if residual is None else residual + y
+    hdn = F.linear(x, w1.to(x.dtype), None if b1 is None else b1.to(x.dtype))
+    hdn = F.relu(hdn) if act == "relu" else F.gelu(hdn)
+    hdn = F.dropout(hdn, p1, training and p1 > 0)
+    y = F.dropout(F.linear(hdn, w2.to(x.dtype), None if b2 is None else b2.to(x.dtype)), p2, training and p2 > 0)
+    return y if residual is None else residual + y

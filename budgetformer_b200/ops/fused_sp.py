@@ -1,0 +1,373 @@
+"""Fused sequence-parallel attention block for B200.
+
+Per encoder layer the portable path runs 3 projection GEMMs, 3 all-to-alls (each with two staging
+copies), the edge attention, a fourth all-to-all and the output projection
+(gt_sp/layer.py:264-280, models/gt_dist_node_level.py:558-560,650-653).  Here:
+
+``QKV push``    one tcgen05 GEMM over the packed ``[Wq;Wk;Wv]`` (rows permuted so that the columns of one
+                destination rank are contiguous) whose epilogue stores every tile straight into the owning
+                rank's packed ``[N, 3*h/P]`` buffer over NVLink — the nodes->heads all-to-all *is* the epilogue;
+``attention``   the edge-attention kernels read q|k|v from that packed buffer and write the context into a
+                second symmetric buffer;
+``ctx pull``    each rank pulls its rows of every peer's context with peer loads and feeds the output
+                projection GEMM (bias, dropout and residual fused in its epilogue);
+backward        mirrors it: the d(context) GEMM pushes to the head owners, the attention backward writes
+                dq|dk|dv packed, and the input-gradient GEMM consumes the pulled rows.
+
+Device-side barriers (bounded spins) order producers and consumers; no host synchronisation and no NCCL
+call happens inside a layer.
+"""
+from __future__ import annotations
+
+import types
+from typing import List, Optional
+
+import torch
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from ..graph.attn_graph import AttnGraph, as_attn_graph
+from ..parallel import symm
+from . import _ext, gemm
+from .edge_attention import _VARIANTS
+from .ffn import fused_ffn
+from .norm import hash_dropout, layer_norm, new_seed
+
+
+class SPContext:
+    """Symmetric buffers and geometry shared by all layers of one model."""
+
+    def __init__(self, group, device, world: int, rows_local: int, hidden: int, heads: int, n_layers: int, dtype,
+                 token_rows: Optional[List[int]] = None):
+        self.sw = symm.get_world(group, device)
+        self.P, self.rank = self.sw.world, self.sw.rank
+        assert self.P == world
+        self.rows_local, self.total_rows = int(rows_local), int(rows_local) * self.P
+        self.h, self.H = int(hidden), int(heads)
+        self.hl_heads = self.H // self.P
+        self.hn = self.h // self.H
+        self.hl = self.hl_heads * self.hn                 # columns of one head slice
+        self.dtype = dtype
+        self.token_rows = token_rows
+        self.qkv = [self.sw.alloc((self.total_rows, 3 * self.hl), dtype) for _ in range(n_layers)]
+        self.ctx = [self.sw.alloc((self.total_rows, self.hl), dtype) for _ in range(n_layers)]
+        self.dqkv = self.sw.alloc((self.total_rows, 3 * self.hl), dtype)
+        self.dctx = self.sw.alloc((self.total_rows, self.hl), dtype)
+        # row permutation of the packed [Wq;Wk;Wv]: destination-rank major, then q|k|v, then head columns
+        idx = []
+        for r in range(self.P):
+            for part in range(3):
+                base = part * self.h + r * self.hl
+                idx.extend(range(base, base + self.hl))
+        self.perm = torch.tensor(idx, dtype=torch.long, device=device)
+        self.inv_perm = torch.empty_like(self.perm)
+        self.inv_perm[self.perm] = torch.arange(3 * self.h, device=device)
+
+    @property
+    def row0(self) -> int:
+        return self.rank * self.rows_local
+
+
+def _push_gemm(x, w, bias, dst_ptrs, row0, ldc, dropout_p=0.0, seed=0):
+    ext = _ext.load()
+    ext.gemm_tn(x, w, None if bias is None else bias.float().contiguous(), 0, float(dropout_p), int(seed), None, None,
+                1.0, False, dst_ptrs, int(row0), int(ldc), gemm.status_tensor(x.device))
+    _ext.count_launches(1)
+
+
+class _QKVPush(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv, bq, bk, bv, sp: SPContext, layer: int):
+        w = torch.cat([wq, wk, wv], 0).to(x.dtype)[sp.perm].contiguous()
+        b = None
+        if bq is not None:
+            b = torch.cat([bq, bk, bv], 0).float()[sp.perm].contiguous()
+        buf = sp.qkv[layer]
+        _push_gemm(x, w, b, buf.ptrs, sp.row0, 3 * sp.hl)
+        sp.sw.barrier(0)
+        ctx.sp, ctx.has_bias, ctx.wdtype = sp, bq is not None, wq.dtype
+        ctx.save_for_backward(x, w)
+        return buf.tensor.detach()
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        sp: SPContext = ctx.sp
+        x, w = ctx.saved_tensors
+        buf = sp.dqkv
+        if dqkv.data_ptr() != buf.tensor.data_ptr():
+            buf.tensor.copy_(dqkv)
+        if sp.P > 1:
+            sp.sw.barrier(0)                                         # every rank's dq|dk|dv is complete
+            dloc = torch.empty((sp.rows_local, 3 * sp.h), dtype=x.dtype, device=x.device)
+            _ext.load().peer_gather_cols(buf.ptrs, sp.row0, sp.rows_local, 3 * sp.hl * x.element_size(),
+                                         3 * sp.hl * x.element_size(), dloc)
+            _ext.count_launches(1)
+            sp.sw.barrier(0)                                         # all reads done before the buffer is reused
+        else:
+            dloc = buf.tensor
+        dx = gemm.gemm_tn(dloc, w.t().contiguous())
+        dw = torch.matmul(dloc.t(), x).float()[sp.inv_perm]
+        dwq, dwk, dwv = (t.to(ctx.wdtype) for t in dw.split(sp.h, 0))
+        if ctx.has_bias:
+            db = dloc.float().sum(0)[sp.inv_perm]
+            dbq, dbk, dbv = (t.to(ctx.wdtype) for t in db.split(sp.h, 0))
+        else:
+            dbq = dbk = dbv = None
+        return dx, dwq, dwk, dwv, dbq, dbk, dbv, None, None
+
+
+class _PackedEdgeAttention(torch.autograd.Function):
+    """Edge attention on the packed q|k|v buffer; context and gradients live in symmetric buffers."""
+
+    @staticmethod
+    def forward(ctx, qkv, etable, graph: AttnGraph, sp: SPContext, layer: int, variant_id, dropout_p, seed):
+        ext = _ext.load()
+        r, hlh, hn, hl = sp.total_rows, sp.hl_heads, sp.hn, sp.hl
+        q = qkv[:, 0:hl].view(r, hlh, hn)
+        k = qkv[:, hl:2 * hl].view(r, hlh, hn)
+        v = qkv[:, 2 * hl:3 * hl].view(r, hlh, hn)
+        out = sp.ctx[layer].tensor
+        z = torch.empty((r, hlh), dtype=torch.float32, device=qkv.device)
+        kmax = -1 if graph.max_degree is None else int(graph.max_degree)
+        ext.edge_attn_fwd(q, k, v, out.view(r, hlh, hn), z, graph.rowptr, graph.col, graph.etype, etable,
+                          int(variant_id), float(dropout_p), int(seed), kmax)
+        _ext.count_launches(1)
+        if sp.token_rows is not None and len(sp.token_rows) > 1:
+            out[sp.token_rows[1:]] = out[sp.token_rows[0]]          # copy_global_token0 (gt_sp/utils.py:2365-2386)
+        ctx.sp, ctx.graph, ctx.layer = sp, graph, layer
+        ctx.cfg = (int(variant_id), float(dropout_p), int(seed), etable is not None, kmax)
+        ctx.save_for_backward(qkv, z, etable if etable is not None else qkv.new_empty(0))
+        return out.detach()
+
+    @staticmethod
+    def backward(ctx, dout):
+        ext = _ext.load()
+        sp: SPContext = ctx.sp
+        qkv, z, etable = ctx.saved_tensors
+        variant_id, dropout_p, seed, has_tab, kmax = ctx.cfg
+        graph = ctx.graph.ensure_transpose()
+        r, hlh, hn, hl = sp.total_rows, sp.hl_heads, sp.hn, sp.hl
+        dout = dout.contiguous()
+        if sp.token_rows is not None and len(sp.token_rows) > 1:
+            dout = dout.clone()
+            dout[sp.token_rows[0]] += dout[sp.token_rows[1:]].sum(0)
+            dout[sp.token_rows[1:]] = 0
+        out = sp.ctx[ctx.layer].tensor
+        q = qkv[:, 0:hl].view(r, hlh, hn)
+        k = qkv[:, hl:2 * hl].view(r, hlh, hn)
+        v = qkv[:, 2 * hl:3 * hl].view(r, hlh, hn)
+        # gradients land packed in the symmetric buffer so that peers can pull their rows
+        dq = torch.empty((r, hlh, hn), dtype=qkv.dtype, device=qkv.device)
+        dk = torch.empty_like(dq)
+        dv = torch.empty_like(dq)
+        zd = torch.empty((r, hlh, 2), dtype=torch.float32, device=qkv.device)
+        detab = torch.zeros(etable.shape, dtype=torch.float32, device=qkv.device) if has_tab else None
+        ext.edge_attn_bwd(q, k, v, out.view(r, hlh, hn), z, dout.view(r, hlh, hn), dq, dk, dv, zd, graph.rowptr, graph.col,
+                          graph.etype, graph.t_rowptr, graph.t_row, graph.t_eid, etable if has_tab else None, detab,
+                          variant_id, dropout_p, seed, kmax)
+        _ext.count_launches(2)
+        dbuf = sp.dqkv.tensor
+        dbuf[:, 0:hl] = dq.view(r, hl)
+        dbuf[:, hl:2 * hl] = dk.view(r, hl)
+        dbuf[:, 2 * hl:3 * hl] = dv.view(r, hl)
+        return dbuf, (detab.to(etable.dtype) if has_tab else None), None, None, None, None, None, None
+
+
+class _CtxPullOutProj(torch.autograd.Function):
+    """heads->nodes pull + (optional) output projection with fused bias / dropout / residual.
+
+    ``y = residual + drop_post(W_o drop_pre(a) + b_o)`` where ``a`` is this rank's rows of the context gathered from
+    all head owners.  Without a projection (Exphormer) ``y = residual + drop_post(a)``."""
+
+    @staticmethod
+    def forward(ctx, ctx_full, wo, bo, residual, sp: SPContext, p_pre, p_post, seed_pre, seed_post):
+        dt = ctx_full.dtype
+        if sp.P > 1:
+            sp.sw.barrier(0)                                         # every head owner has written its context
+            a = torch.empty((sp.rows_local, sp.h), dtype=dt, device=ctx_full.device)
+            esz = ctx_full.element_size()
+            _ext.load().peer_gather_cols(sp.ctx_ptrs_for(ctx_full), sp.row0, sp.rows_local, sp.hl * esz, sp.hl * esz, a)
+            _ext.count_launches(1)
+        else:
+            a = ctx_full
+        if p_pre > 0:
+            a = hash_dropout(a, seed_pre, p_pre)
+        if wo is not None:
+            w = wo.to(dt)
+            y = gemm.gemm_tn(a, w, bo, None, dropout_p=p_post, dropout_seed=seed_post, residual=residual)
+            ctx.save_for_backward(a, w)
+        else:
+            y = hash_dropout(a, seed_post, p_post) if p_post > 0 else a
+            if residual is not None:
+                y = y + residual
+            ctx.save_for_backward()
+        ctx.sp = sp
+        ctx.cfg = (float(p_pre), float(p_post), int(seed_pre), int(seed_post), residual is not None, wo is not None,
+                   bo is not None, wo.dtype if wo is not None else None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        sp: SPContext = ctx.sp
+        p_pre, p_post, seed_pre, seed_post, has_res, has_w, has_b, wdtype = ctx.cfg
+        dy = dy.contiguous()
+        g = hash_dropout(dy, seed_post, p_post) if p_post > 0 else dy
+        dbuf = sp.dctx
+        dw = db = None
+        if has_w:
+            a, w = ctx.saved_tensors
+            # d(context) = (g W_o) [* pre-dropout mask], pushed to the head owners by the GEMM epilogue
+            _push_gemm(g, w.t().contiguous(), None, dbuf.ptrs, sp.row0, sp.hl, dropout_p=p_pre, seed=seed_pre)
+            dw = torch.matmul(g.t(), a).to(wdtype)
+            db = g.float().sum(0).to(wdtype) if has_b else None
+        else:
+            da = hash_dropout(g, seed_pre, p_pre) if p_pre > 0 else g
+            esz = da.element_size()
+            _ext.load().peer_scatter_cols(dbuf.ptrs, sp.row0, sp.rows_local, sp.hl * esz, sp.hl * esz, da.contiguous())
+            _ext.count_launches(1)
+        sp.sw.barrier(0)                                             # all d(context) rows have landed
+        return dbuf.tensor, dw, db, (dy if has_res else None), None, None, None, None, None
+
+
+def _ctx_ptrs_for(self, t):
+    for b in self.ctx:
+        if b.tensor.data_ptr() == t.data_ptr():
+            return b.ptrs
+    raise RuntimeError("context tensor is not one of the symmetric context buffers")
+
+
+SPContext.ctx_ptrs_for = _ctx_ptrs_for
+
+
+# ---------------------------------------------------------------------------------------------------
+# per-model fused layers
+# ---------------------------------------------------------------------------------------------------
+def _core(layer):
+    d = layer.self_attention.dist_attn
+    return getattr(d, "local_attn", d)
+
+
+def _attention(layer, x2d, graph: AttnGraph, sp: SPContext, idx: int):
+    mha = layer.self_attention
+    core = _core(layer)
+    qkv = _QKVPush.apply(x2d, mha.linear_q.weight, mha.linear_k.weight, mha.linear_v.weight, mha.linear_q.bias,
+                         mha.linear_k.bias, mha.linear_v.bias, sp, idx)
+    variant = core.variant
+    etab = core.edge_table() if variant == "exphormer" else None
+    if variant == "exphormer" and (etab is None or graph.etype is None):
+        variant, etab = "plain", None
+    p_att = core.attention_dropout_rate if (variant == "gps" and layer.training) else 0.0
+    tab = etab.to(torch.float32).contiguous() if etab is not None else None
+    return _PackedEdgeAttention.apply(qkv, tab, graph, sp, idx, _VARIANTS[variant], p_att, new_seed() if p_att > 0 else 0)
+
+
+def _p(module, training) -> float:
+    return float(module.p) if (training and module is not None) else 0.0
+
+
+def _gt_attn(layer, x, graph, sp, idx):
+    ctx = _attention(layer, x, graph, sp, idx)
+    p = _p(layer.self_attention_dropout, layer.training)
+    s = _CtxPullOutProj.apply(ctx, layer.O.weight, layer.O.bias, x, sp, p, 0.0, new_seed() if p > 0 else 0, 0)
+    return layer_norm(s, layer.layer_norm1.weight, layer.layer_norm1.bias, layer.layer_norm1.eps)
+
+
+def _gt_ffn(layer, x1):
+    p = _p(layer.self_attention_dropout, layer.training)
+    s = fused_ffn(x1, layer.FFN_layer1.weight, layer.FFN_layer1.bias, layer.FFN_layer2.weight, layer.FFN_layer2.bias,
+                  act="relu", residual=x1, p1=p, p2=0.0, training=layer.training)
+    return layer_norm(s, layer.layer_norm2.weight, layer.layer_norm2.bias, layer.layer_norm2.eps)
+
+
+def _graphormer_attn(layer, x, graph, sp, idx):
+    n = layer.self_attention_norm
+    y = layer_norm(x, n.weight, n.bias, n.eps)
+    ctx = _attention(layer, y, graph, sp, idx)
+    p = _p(layer.self_attention_dropout, layer.training)
+    o = layer.self_attention.output_layer
+    return _CtxPullOutProj.apply(ctx, o.weight, o.bias, x, sp, 0.0, p, 0, new_seed() if p > 0 else 0)
+
+
+def _graphormer_ffn(layer, x):
+    n = layer.ffn_norm
+    y = layer_norm(x, n.weight, n.bias, n.eps)
+    p = _p(layer.ffn_dropout, layer.training)
+    return fused_ffn(y, layer.ffn.layer1.weight, layer.ffn.layer1.bias, layer.ffn.layer2.weight, layer.ffn.layer2.bias,
+                     act="gelu", residual=x, p1=0.0, p2=p, training=layer.training)
+
+
+def _bn(norm, x):
+    return norm(x.float()).to(x.dtype)
+
+
+def _gps_attn(layer, x, graph, sp, idx):
+    ctx = _attention(layer, x, graph, sp, idx)
+    p = _p(layer.dropout1, layer.training)
+    o = getattr(layer.self_attention, "out_proj", None)
+    s = _CtxPullOutProj.apply(ctx, None if o is None else o.weight, None if o is None else o.bias, x, sp, 0.0, p, 0,
+                              new_seed() if p > 0 else 0)
+    return _bn(layer.norm1, s)
+
+
+def _gps_ffn(layer, x1):
+    s = fused_ffn(x1, layer.ffn1.weight, layer.ffn1.bias, layer.ffn2.weight, layer.ffn2.bias, act="relu", residual=x1,
+                  p1=_p(layer.ff_dropout1, layer.training), p2=_p(layer.ff_dropout2, layer.training),
+                  training=layer.training)
+    return _bn(layer.norm2, s)
+
+
+_LAYER_IMPL = {"gt": (_gt_attn, _gt_ffn), "graphormer": (_graphormer_attn, _graphormer_ffn),
+               "graphgps": (_gps_attn, _gps_ffn), "exphormer": (_gps_attn, _gps_ffn)}
+
+
+def _install(layer, idx: int, sp: SPContext, attn_fn, ffn_fn):
+    portable_forward = layer.forward
+    portable_attn_only = layer.forward_attn_only
+    portable_ffn_ckpt = layer.forward_ffn_checkpointed
+
+    def usable(x, edge_index, attn_type, attn_bias):
+        return (x.is_cuda and x.dtype == sp.dtype and x.dim() == 3 and x.size(0) == 1 and x.size(1) == sp.rows_local
+                and attn_bias is None and str(attn_type or "sparse").lower() == "sparse" and edge_index is not None)
+
+    def forward_attn_only(self, x, attn_bias=None, edge_index=None, attn_type=None, **kw):
+        if not usable(x, edge_index, attn_type, attn_bias):
+            return portable_attn_only(x, attn_bias, edge_index, attn_type, **kw)
+        graph = as_attn_graph(edge_index, sp.total_rows)
+        return attn_fn(self, x[0], graph, sp, idx).unsqueeze(0)
+
+    def forward_ffn_checkpointed(self, x):
+        if not (x.is_cuda and x.dtype == sp.dtype):
+            return portable_ffn_ckpt(x)
+        return checkpoint(lambda t: ffn_fn(self, t[0]).unsqueeze(0), x, use_reentrant=False)
+
+    def forward(self, x, attn_bias=None, edge_index=None, attn_type=None, **kw):
+        if not usable(x, edge_index, attn_type, attn_bias):
+            return portable_forward(x, attn_bias, edge_index, attn_type, **kw)
+        graph = as_attn_graph(edge_index, sp.total_rows)
+        return ffn_fn(self, attn_fn(self, x[0], graph, sp, idx)).unsqueeze(0)
+
+    layer.forward = types.MethodType(forward, layer)
+    layer.forward_attn_only = types.MethodType(forward_attn_only, layer)
+    layer.forward_ffn_checkpointed = types.MethodType(forward_ffn_checkpointed, layer)
+
+
+def enable_for_model(model, args, group, world: int, nodes_per_rank: int, amp_dtype) -> bool:
+    """Install the fused layer path on ``model`` when the configuration allows it; returns whether it did."""
+    name = str(args.model).lower()
+    if name not in _LAYER_IMPL or amp_dtype not in (torch.bfloat16, torch.float16):
+        return False
+    h, heads = int(args.hidden_dim), int(args.num_heads)
+    hl = (heads // world) * (h // heads)
+    if h % 64 != 0 or hl % 16 != 0 or (3 * hl) % 16 != 0 or (h // heads) not in (8, 16, 32, 64, 128):
+        return False
+    if name == "graphgps" and str(getattr(args, "attn_type", "sparse")).lower() != "sparse":
+        return False
+    dev = next(model.parameters()).device
+    rows_local = nodes_per_rank + (1 if (name == "graphormer" and int(args.num_global_node) > 0) else 0)
+    token_rows = [r * rows_local for r in range(world)] if rows_local != nodes_per_rank else None
+    sp = SPContext(group, dev, world, rows_local, h, heads, len(model.layers), amp_dtype, token_rows)
+    attn_fn, ffn_fn = _LAYER_IMPL[name]
+    for i, layer in enumerate(model.layers):
+        _install(layer, i, sp, attn_fn, ffn_fn)
+    model._fused_sp_context = sp
+    return True

@@ -1,0 +1,108 @@
+"""Linear layers on the tcgen05 GEMM (``csrc/gemm_tcgen05.cu``).
+
+``gemm_tn`` is the raw call ``C = A @ W.T`` with the fused epilogue; ``fused_linear`` is the autograd
+function used by the models on B200: forward and the input-gradient GEMM run on the tcgen05 kernel,
+the weight gradient ``dW = dY^T X`` (a plain tall-skinny reduction without any fusion opportunity) uses
+the library GEMM.  Shapes the kernel does not cover (K not a multiple of 64, N not a multiple of 16,
+fp32 operands) fall back to ``torch.nn.functional.linear``."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _ext
+
+ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
+_STATUS = {}
+
+
+def status_tensor(device) -> torch.Tensor:
+    """Per-device int32[4] written by kernels whose bounded waits expired (0 = healthy)."""
+    key = torch.device(device).index or 0
+    t = _STATUS.get(key)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=device)
+        _STATUS[key] = t
+    return t
+
+
+def check_status(device) -> None:
+    """Host read of the status word; raises if any kernel gave up waiting."""
+    t = _STATUS.get(torch.device(device).index or 0)
+    if t is not None:
+        code = int(t[0].item())
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(f"a device-side bounded wait expired (status {code}); results of that launch are invalid")
+
+
+def supported(m: int, n: int, k: int, dtype) -> bool:
+    return dtype in (torch.bfloat16, torch.float16) and m > 0 and k % 64 == 0 and k >= 64 and n % 16 == 0 and n >= 16
+
+
+def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
+            dropout_p: float = 0.0, dropout_seed: int = 0, residual: Optional[torch.Tensor] = None,
+            relu_mask: Optional[torch.Tensor] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``act(dropout(a @ w.T * out_scale + bias)) [masked] + residual`` in one kernel."""
+    ext = _ext.load()
+    m, n = a.size(0), w.size(0)
+    fp32_out = (out_dtype or (out.dtype if out is not None else a.dtype)) == torch.float32
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32 if fp32_out else a.dtype, device=a.device)
+    if m == 0:
+        return out
+    ext.gemm_tn(a, w, None if bias is None else bias.float().contiguous(), ACT[act], float(dropout_p), int(dropout_seed),
+                residual, relu_mask, float(out_scale), bool(fp32_out), [out.data_ptr()], 0, out.stride(0),
+                status_tensor(a.device))
+    _ext.count_launches(1)
+    return out
+
+
+def hash_keep_mask(seed: int, rows: int, cols: int, p: float, device) -> torch.Tensor:
+    """The epilogue's dropout keep mask, restated in PyTorch (tests and the fallback path)."""
+    r = torch.arange(rows, device=device, dtype=torch.int64)[:, None]
+    c = torch.arange(cols, device=device, dtype=torch.int64)[None, :]
+    x = (r * 0x9E3779B1 + c * 0x85EBCA77 + (int(seed) & 0xFFFFFFFF)) & 0xFFFFFFFF
+    x = ((x ^ (x >> 16)) * 0x7FEB352D) & 0xFFFFFFFF
+    x = ((x ^ (x >> 15)) * 0x846CA68B) & 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    return x >= int(p * 4294967296.0)
+
+
+class _FusedLinear(torch.autograd.Function):
+    """y = residual + dropout(x W^T + b): one GEMM forward, one GEMM (dx) + one library GEMM (dW) backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, dropout_p, dropout_seed):
+        w16 = weight.to(x.dtype)
+        y = gemm_tn(x, w16, bias, None, dropout_p=dropout_p, dropout_seed=dropout_seed, residual=residual)
+        ctx.cfg = (residual is not None, float(dropout_p), int(dropout_seed), weight.dtype, bias is not None)
+        ctx.save_for_backward(x, w16)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .norm import hash_dropout
+        x, w16 = ctx.saved_tensors
+        has_res, p, seed, wdtype, has_bias = ctx.cfg
+        dy = dy.contiguous()
+        g = hash_dropout(dy, seed, p) if p > 0 else dy
+        dx = gemm_tn(g, w16.t().contiguous())            # dx = g @ W, expressed as g @ (W^T)^T
+        dw = torch.matmul(g.t(), x).to(wdtype)
+        db = g.float().sum(0).to(wdtype) if has_bias else None
+        return dx, dw, db, (dy if has_res else None), None, None
+
+
+def fused_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None, dropout_p: float = 0.0, dropout_seed: int = 0) -> torch.Tensor:
+    """2-D ``x``: ``residual + dropout(x @ weight.T + bias)``.  tcgen05 kernel when shape/dtype allow, else PyTorch."""
+    if x.is_cuda and supported(x.size(0), weight.size(0), x.size(1), x.dtype) and x.stride(1) == 1 \
+            and (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0:
+        return _FusedLinear.apply(x, weight, bias, residual, dropout_p, dropout_seed)
+    y = torch.nn.functional.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
+    if dropout_p > 0:
+        keep = hash_keep_mask(dropout_seed, y.size(0), y.size(1), dropout_p, y.device)
+        y = torch.where(keep, y / (1.0 - dropout_p), torch.zeros_like(y))
+    return y if residual is None else y + residual

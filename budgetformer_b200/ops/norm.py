@@ -1,0 +1,70 @@
+"""LayerNorm and counter-based dropout on the row kernels of ``csrc/norm_fused.cu``.
+
+``layer_norm`` keeps fp32 statistics per row and recomputes the normalised input in backward from
+the saved input; ``hash_dropout`` derives its keep mask from ``(seed, row, col)`` exactly like the
+GEMM epilogue does, so nothing but the seed is saved.  CPU tensors (and widths above 512) use the
+PyTorch implementations."""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _ext
+from .gemm import hash_keep_mask
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        ext = _ext.load()
+        g32, b32 = gamma.float().contiguous(), beta.float().contiguous()
+        y, stats = ext.layernorm_fwd(x, g32, b32, float(eps))
+        _ext.count_launches(1)
+        ctx.save_for_backward(x, stats, g32)
+        ctx.pdtype = gamma.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ext = _ext.load()
+        x, stats, g32 = ctx.saved_tensors
+        dy = dy if dy.stride(-1) == 1 else dy.contiguous()
+        dx, dg, db = ext.layernorm_bwd(dy.to(x.dtype), x, stats, g32)
+        _ext.count_launches(1)
+        return dx, dg.to(ctx.pdtype), db.to(ctx.pdtype), None
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """2-D ``x`` ``[rows, h]``."""
+    if x.is_cuda and x.dim() == 2 and x.size(1) <= 512 and x.stride(1) == 1 and \
+            x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        return _LayerNorm.apply(x, weight, bias, eps)
+    return F.layer_norm(x.float(), (x.size(-1),), weight.float(), bias.float(), eps).to(x.dtype)
+
+
+class _HashDropout(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, seed, p):
+        ctx.seed, ctx.p = int(seed), float(p)
+        _ext.count_launches(1)
+        return _ext.load().hash_dropout(x, int(seed), float(p))
+
+    @staticmethod
+    def backward(ctx, dy):
+        _ext.count_launches(1)
+        dy = dy if dy.stride(-1) == 1 else dy.contiguous()
+        return _ext.load().hash_dropout(dy, ctx.seed, ctx.p), None, None
+
+
+def hash_dropout(x: torch.Tensor, seed: int, p: float) -> torch.Tensor:
+    if p <= 0.0:
+        return x
+    if x.is_cuda and x.dim() == 2 and x.stride(1) == 1:
+        return _HashDropout.apply(x, seed, p)
+    keep = hash_keep_mask(seed, x.size(0), x.size(1), p, x.device)
+    return torch.where(keep, x / (1.0 - p), torch.zeros_like(x))
+
+
+def new_seed() -> int:
+    """31-bit seed from torch's CPU generator (reproducible under ``torch.manual_seed``, no device sync)."""
+    return int(torch.randint(0, 2 ** 31 - 1, (1,)).item())

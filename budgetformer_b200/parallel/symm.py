@@ -1,0 +1,129 @@
+"""Symmetric (peer-mapped) device memory and the collectives built on it.
+
+``SymmWorld`` allocates buffers that every rank of the group can address directly over
+NVLink / NVSwitch (``torch.distributed._symmetric_memory`` does the handle exchange; all data
+movement is done by this package's kernels with peer loads/stores or NVSwitch ``multimem``
+instructions).  It owns one flag page for ``barrier()`` — a device-side barrier with a bounded spin
+whose expiry is reported through the status word checked by ``ops.gemm.check_status``.
+
+With a world of one (single GPU) the same interface degenerates to ordinary tensors, so the fused
+model path is identical at every scale.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext
+from ..ops.gemm import status_tensor
+from . import comm
+
+_WORLDS: Dict[int, "SymmWorld"] = {}
+FLAG_CHANNELS = 64
+MAX_PEERS = 8
+
+
+class SymmBuffer:
+    """One symmetric allocation: the local tensor plus every rank's mapped pointer."""
+
+    def __init__(self, tensor: torch.Tensor, ptrs: List[int], multicast_ptr: int = 0, handle=None):
+        self.tensor, self.ptrs, self.multicast_ptr, self.handle = tensor, ptrs, int(multicast_ptr), handle
+
+    def nbytes(self) -> int:
+        return self.tensor.numel() * self.tensor.element_size()
+
+
+class SymmWorld:
+    def __init__(self, group, device):
+        self.group = group
+        self.device = torch.device(device)
+        self.world = comm.group_size(group)
+        self.rank = comm.group_rank(group)
+        if self.world > MAX_PEERS:
+            raise RuntimeError(f"symmetric-memory kernels support up to {MAX_PEERS} ranks, got {self.world}")
+        self.bytes_allocated = 0
+        self._epoch = 0
+        self.use_multimem = os.environ.get("BF_DISABLE_MULTIMEM", "0") != "1"
+        self.flags = self.alloc((FLAG_CHANNELS * MAX_PEERS,), torch.int32, zero=True)
+        if self.world > 1:
+            # every rank must have zeroed its flag page before anyone raises a flag in it
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+
+    def alloc(self, shape, dtype, zero: bool = False) -> SymmBuffer:
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        numel = max(numel, 1)
+        if self.world == 1:
+            t = (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=self.device)
+            buf = SymmBuffer(t.view(*shape) if numel == t.numel() and shape else t, [t.data_ptr()], 0, None)
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            t = symm_mem.empty(numel, dtype=dtype, device=self.device)
+            if zero:
+                t.zero_()
+            hdl = symm_mem.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            mc = int(hdl.multicast_ptr) if (self.use_multimem and getattr(hdl, "has_multicast_support", False)
+                                            and hdl.multicast_ptr) else 0
+            buf = SymmBuffer(t.view(*shape), ptrs, mc, hdl)
+        self.bytes_allocated += buf.nbytes()
+        return buf
+
+    def barrier(self, channel: int = 0) -> None:
+        """Device-side barrier over all ranks on the current stream (no host synchronisation)."""
+        if self.world == 1:
+            return
+        self._epoch += 1
+        _ext.load().peer_barrier(self.flags.ptrs, self.rank, int(channel), self._epoch & 0x7FFFFFFF,
+                                 status_tensor(self.device))
+        _ext.count_launches(1)
+
+
+def get_world(group, device) -> SymmWorld:
+    key = id(group) if group is not None else 0
+    w = _WORLDS.get(key)
+    if w is None or w.device != torch.device(device):
+        w = SymmWorld(group, device)
+        _WORLDS[key] = w
+    return w
+
+
+def reset_worlds() -> None:
+    _WORLDS.clear()
+
+
+def symmetric_bytes() -> int:
+    """Bytes held in symmetric buffers by this process (outside PyTorch's caching allocator for world > 1);
+    the execution planner adds them to its memory readings."""
+    return sum(w.bytes_allocated for w in _WORLDS.values())
+
+
+# ---- gradient buckets ------------------------------------------------------------------------------
+def attach_buckets(buckets, group) -> bool:
+    """Move the reducer's flat fp32 buckets into symmetric memory so that ``bucket_all_reduce_mean`` can run."""
+    if not buckets or buckets[0].flat.device.type != "cuda" or comm.group_size(group) == 1:
+        return False
+    world = get_world(group, buckets[0].flat.device)
+    for b in buckets:
+        if b.flat.dtype != torch.float32:
+            continue
+        sb = world.alloc((b.flat.numel(),), torch.float32, zero=True)
+        b.rebind_to(sb.tensor)
+        b.symm = (world, sb)
+    return True
+
+
+def bucket_all_reduce_mean(bucket) -> None:
+    """In-place mean over ranks of a symmetric fp32 bucket: barrier, fused scale + two-shot (or in-switch
+    multimem) all-reduce, barrier."""
+    world, sb = bucket.symm
+    ext = _ext.load()
+    world.barrier(1)                       # every rank's gradients are complete
+    ext.allreduce_mean(sb.ptrs, sb.multicast_ptr, world.rank, sb.tensor.numel(), sb.tensor)
+    _ext.count_launches(1)
+    world.barrier(1)                       # every slice has been written everywhere

@@ -1,0 +1,74 @@
+"""Fused B200 layer path against the portable PyTorch path of the same model (single GPU)."""
+import copy
+
+import pytest
+import torch
+
+from budgetformer_b200.config import parse_fullgraph_args
+from budgetformer_b200.graph.synthetic import sbm_graph
+from budgetformer_b200.ops import gemm
+from budgetformer_b200.train.data import GraphData, random_split_idx
+from budgetformer_b200.train.engine import FullGraphTrainer
+
+pytestmark = pytest.mark.gpu
+
+
+def _trainer(model, fused, extra=()):
+    n = 1536
+    x, y, ei = sbm_graph(n, feat_dim=64, seed=3)
+    data = GraphData(x, y, ei, random_split_idx(n, 3), n, 7)
+    argv = ["--model", model, "--dataset", "t", "--n_layers", "2", "--hidden_dim", "128", "--num_heads", "8",
+            "--ffn_dim", "256", "--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4",
+            "--amp_dtype", "bf16", "--force_random_split", "--device", "cuda:0", "--fused_sp", "on" if fused else "off",
+            "--dropout_rate", "0.0", "--attention_dropout_rate", "0.0", "--input_dropout_rate", "0.0", "--seed", "5"]
+    argv += list(extra)
+    return FullGraphTrainer(parse_fullgraph_args(argv), data=data, log=lambda *a, **k: None)
+
+
+@pytest.mark.parametrize("model", ["gt", "graphormer", "graphgps", "exphormer"])
+def test_fused_forward_backward_matches_portable(model):
+    a = _trainer(model, fused=False)
+    b = _trainer(model, fused=True)
+    assert b.fused_sp and not a.fused_sp
+    b.model.load_state_dict(a.model.state_dict())
+    graph = a.build_edges(1)
+    la, outa = a._loss(graph, a.local_idx["train"])
+    lb, outb = b._loss(graph, b.local_idx["train"])
+    assert torch.allclose(outa.float(), outb.float(), atol=6e-2, rtol=6e-2), float((outa.float() - outb.float()).abs().max())
+    a.reducer.prepare_backward(); b.reducer.prepare_backward()
+    la.backward(); lb.backward()
+    gemm.check_status("cuda")
+    gmax = max(float(p.grad.abs().max()) for p in a.model.parameters() if p.grad is not None)
+    for (na, pa), (nb, pb) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        if pa.grad is None:
+            continue
+        ga, gb = pa.grad.float(), pb.grad.float()
+        err = float((ga - gb).abs().max())
+        # gradients that are analytically ~0 (e.g. the key bias under a normalised softmax) are pure rounding noise:
+        # accept either a small relative error or an error far below the model's gradient scale
+        ok = err <= 0.12 * max(float(ga.abs().max()), 1e-6) or err <= 5e-3 * gmax
+        assert ok, f"{model}: grad mismatch on {na}: err {err} vs max {float(ga.abs().max())} (global {gmax})"
+    assert abs(float(la.detach()) - float(lb.detach())) < 2e-2
+
+
+@pytest.mark.parametrize("model", ["gt", "graphormer"])
+def test_fused_training_reduces_loss(model):
+    t = _trainer(model, fused=True, extra=["--peak_lr", "5e-3", "--dropout_rate", "0.1"])
+    losses = [t.train_step(e)["loss"] for e in range(1, 26)]
+    gemm.check_status("cuda")
+    assert losses[-1] < losses[0] - 0.05, losses
+
+
+def test_fused_path_with_activation_tiers():
+    t = _trainer("gt", fused=True, extra=["--activation_checkpoint_mode", "all"])
+    u = _trainer("gt", fused=True, extra=["--activation_checkpoint_mode", "ffn_only"])
+    u.model.load_state_dict(t.model.state_dict())
+    g = t.build_edges(1)
+    t.model.train(); u.model.train()
+    lt, _ = t._loss(g, t.local_idx["train"])
+    lu, _ = u._loss(g, u.local_idx["train"])
+    t.reducer.prepare_backward(); u.reducer.prepare_backward()
+    lt.backward(); lu.backward()
+    assert abs(float(lt) - float(lu)) < 1e-3
+    for pa, pb in zip(t.model.parameters(), u.model.parameters()):
+        assert torch.allclose(pa.grad, pb.grad, atol=1e-3 + 0.02 * float(pa.grad.abs().max()))

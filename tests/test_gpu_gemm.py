@@ -1,0 +1,164 @@
+"""tcgen05 GEMM against fp32 PyTorch matmul of the same operands."""
+import pytest
+import torch
+
+from budgetformer_b200.ops import gemm
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, w, bias=None, act=None, residual=None, mask=None, drop=None, scale=1.0):
+    y = a.float() @ w.float().t() * scale
+    if bias is not None:
+        y = y + bias.float()
+    if act == "relu":
+        y = torch.relu(y)
+    elif act == "gelu":
+        y = torch.nn.functional.gelu(y)
+    if drop is not None:
+        p, seed = drop
+        keep = gemm.hash_keep_mask(seed, y.size(0), y.size(1), p, y.device)
+        y = torch.where(keep, y / (1 - p), torch.zeros_like(y))
+    if mask is not None:
+        y = torch.where(mask.float() > 0, y, torch.zeros_like(y))
+    if residual is not None:
+        y = y + residual.float()
+    return y
+
+
+def _close(got, want, dtype):
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    scale = max(1.0, float(want.abs().max()))
+    err = float((got.float() - want).abs().max())
+    assert err <= tol * scale, f"max err {err} scale {scale}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (1000, 384, 128), (333, 256, 256), (4096, 768, 256),
+                                   (129, 64, 64), (70000, 128, 256), (257, 192, 512), (64, 16, 64), (5000, 48, 128)])
+def test_gemm_plain(m, n, k, dtype):
+    torch.manual_seed(0)
+    a = torch.randn(m, k, device="cuda").to(dtype)
+    w = (torch.randn(n, k, device="cuda") / k ** 0.5).to(dtype)
+    out = gemm.gemm_tn(a, w)
+    gemm.check_status("cuda")
+    _close(out, _ref(a, w), dtype)
+
+
+def test_gemm_fp32_output_and_scale():
+    a = torch.randn(500, 128, device="cuda").bfloat16()
+    w = torch.randn(128, 128, device="cuda").bfloat16() * 0.1
+    out = gemm.gemm_tn(a, w, out_scale=0.5, out_dtype=torch.float32)
+    gemm.check_status("cuda")
+    assert out.dtype == torch.float32
+    assert torch.allclose(out, _ref(a, w, scale=0.5), atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("act", [None, "relu", "gelu"])
+def test_gemm_epilogues(act):
+    torch.manual_seed(1)
+    m, n, k = 3000, 256, 128
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(n, device="cuda")
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    out = gemm.gemm_tn(a, w, bias, act, residual=res)
+    _close(out, _ref(a, w, bias, act, res), torch.bfloat16)
+    out = gemm.gemm_tn(a, w, bias, act, dropout_p=0.3, dropout_seed=77)
+    _close(out, _ref(a, w, bias, act, drop=(0.3, 77)), torch.bfloat16)
+    mask = torch.randn(m, n, device="cuda").bfloat16()
+    out = gemm.gemm_tn(a, w, relu_mask=mask)
+    _close(out, _ref(a, w, mask=mask), torch.bfloat16)
+    gemm.check_status("cuda")
+
+
+def test_gemm_strided_input_rows():
+    big = torch.randn(700, 3 * 128, device="cuda").bfloat16()
+    a = big[:, 128:256]
+    w = (torch.randn(64, 128, device="cuda") * 0.1).bfloat16()
+    _close(gemm.gemm_tn(a, w), _ref(a, w), torch.bfloat16)
+
+
+def test_fused_linear_autograd():
+    torch.manual_seed(2)
+    x = torch.randn(1500, 128, device="cuda").bfloat16().requires_grad_(True)
+    lin = torch.nn.Linear(128, 256).cuda()
+    res = torch.randn(1500, 256, device="cuda").bfloat16().requires_grad_(True)
+    y = gemm.fused_linear(x, lin.weight, lin.bias, res, dropout_p=0.25, dropout_seed=5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    x2 = x.detach().float().requires_grad_(True)
+    r2 = res.detach().float().requires_grad_(True)
+    w2 = lin.weight.detach().bfloat16().float().requires_grad_(True)
+    b2 = lin.bias.detach().clone().requires_grad_(True)
+    keep = gemm.hash_keep_mask(5, 1500, 256, 0.25, "cuda")
+    y2 = torch.where(keep, (x2 @ w2.t() + b2) / 0.75, torch.zeros(1, device="cuda")) + r2
+    y2.backward(dy.float())
+    _close(y.detach(), y2.detach(), torch.bfloat16)
+    _close(x.grad, x2.grad, torch.bfloat16)
+    _close(res.grad, r2.grad, torch.bfloat16)
+    assert torch.allclose(lin.weight.grad, w2.grad, atol=0.03 * float(w2.grad.abs().max()), rtol=5e-2)
+    assert torch.allclose(lin.bias.grad, b2.grad, atol=0.03 * float(b2.grad.abs().max()), rtol=5e-2)
+
+
+def test_fused_ffn_autograd():
+    from budgetformer_b200.ops.ffn import fused_ffn
+    from budgetformer_b200.ops import norm as bnorm
+    torch.manual_seed(3)
+    m, h = 2000, 128
+    x = torch.randn(m, h, device="cuda").bfloat16().requires_grad_(True)
+    l1, l2 = torch.nn.Linear(h, 2 * h).cuda(), torch.nn.Linear(2 * h, h).cuda()
+    torch.manual_seed(11)
+    y = fused_ffn(x, l1.weight, l1.bias, l2.weight, l2.bias, act="relu", residual=x, p1=0.2, p2=0.1, training=True)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    torch.manual_seed(11)
+    s1, s2 = bnorm.new_seed(), bnorm.new_seed()
+    x2 = x.detach().float().requires_grad_(True)
+    w1 = l1.weight.detach().bfloat16().float().requires_grad_(True)
+    w2 = l2.weight.detach().bfloat16().float().requires_grad_(True)
+    hdn = torch.relu(x2 @ w1.t() + l1.bias.detach())
+    hdn = torch.where(gemm.hash_keep_mask(s1, m, 2 * h, 0.2, "cuda"), hdn / 0.8, torch.zeros(1, device="cuda"))
+    hdn = hdn.bfloat16().float()
+    o = hdn @ w2.t() + l2.bias.detach()
+    o = torch.where(gemm.hash_keep_mask(s2, m, h, 0.1, "cuda"), o / 0.9, torch.zeros(1, device="cuda")) + x2
+    o.backward(dy.float())
+    _close(y.detach(), o.detach(), torch.bfloat16)
+    _close(x.grad, x2.grad, torch.bfloat16)
+    assert torch.allclose(l1.weight.grad, w1.grad, atol=0.03 * float(w1.grad.abs().max()), rtol=5e-2)
+    assert torch.allclose(l2.weight.grad, w2.grad, atol=0.03 * float(w2.grad.abs().max()), rtol=5e-2)
+    gemm.check_status("cuda")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("h", [64, 128, 200, 512])
+def test_layernorm_kernel(dtype, h):
+    from budgetformer_b200.ops.norm import layer_norm
+    torch.manual_seed(4)
+    x = (torch.randn(3001, h, device="cuda") * 2 + 0.5).to(dtype).requires_grad_(True)
+    ln = torch.nn.LayerNorm(h).cuda()
+    with torch.no_grad():
+        ln.weight.uniform_(0.5, 1.5)
+        ln.bias.uniform_(-0.5, 0.5)
+    y = layer_norm(x, ln.weight, ln.bias, ln.eps)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    gw, gb = ln.weight.grad.clone(), ln.bias.grad.clone()
+    ln.zero_grad()
+    x2 = x.detach().float().requires_grad_(True)
+    y2 = torch.nn.functional.layer_norm(x2, (h,), ln.weight, ln.bias, ln.eps)
+    y2.backward(dy.float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 2e-4
+    assert torch.allclose(y.float(), y2, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), x2.grad, atol=tol * max(1.0, float(x2.grad.abs().max())), rtol=tol)
+    assert torch.allclose(gw, ln.weight.grad, atol=2e-2 * float(ln.weight.grad.abs().max()), rtol=2e-2)
+    assert torch.allclose(gb, ln.bias.grad, atol=2e-2 * float(ln.bias.grad.abs().max()), rtol=2e-2)
+
+
+def test_hash_dropout_matches_epilogue_mask():
+    from budgetformer_b200.ops.norm import hash_dropout
+    x = torch.ones(777, 96, device="cuda", dtype=torch.bfloat16)
+    y = hash_dropout(x, 99, 0.3)
+    keep = gemm.hash_keep_mask(99, 777, 96, 0.3, "cuda")
+    assert torch.equal(y > 0, keep)
+    assert abs(float(keep.float().mean()) - 0.7) < 0.02
