@@ -39,7 +39,8 @@ typedef struct {
 
 typedef struct {
   const void* dout;                 // [n, hl, hn] contiguous
-  void *dq, *dk, *dv;               // [n, hl, hn] contiguous
+  void *dq, *dk, *dv;               // [n, hl, hn], common row stride ldg (elements; 0 = hl*hn)
+  long long ldg;
   float* zd;                        // [n, hl, 2] fp32 workspace (written by the dQ pass)
   const int *t_rowptr, *t_row, *t_eid;  // transposed CSR over keys
   float* detab;                     // zero-filled [2, hl, hn] fp32 or NULL
@@ -47,6 +48,12 @@ typedef struct {
   int n_t_hub, max_t_hub_degree;
   float* hub_scratch_q;             // zero-filled [n_hub, hl*hn]
   float* hub_scratch_kv;            // zero-filled [n_t_hub, 2*hl*hn]
+  // Optional balanced dK/dV work list (replaces the t_hub_* path when kv_task != NULL)
+  const int* kv_task;               // [n_kv_task, 4] int32, 16-byte aligned: key row, first edge, end edge, slot (-1 direct)
+  int n_kv_task;
+  const int* kv_split;              // [n_kv_split, 3] int32: key row, first slot, slot count
+  int n_kv_split;
+  float* kv_partial;                // [total slots, 2*hl*hn] fp32 scratch
 } bf_attn_bwd_params;
 
 int bf_edge_attn_fwd(const bf_attn_params* p, cudaStream_t st);

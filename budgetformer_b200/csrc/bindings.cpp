@@ -91,20 +91,34 @@ void edge_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor ro
 void edge_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor dout, Tensor dq, Tensor dk, Tensor dv,
                    Tensor zd, Tensor rowptr, Tensor col, OptTensor etype, Tensor t_rowptr, Tensor t_row, Tensor t_eid,
                    OptTensor etab, OptTensor detab, int64_t variant, double dropout_p, int64_t seed,
-                   int64_t known_max_degree) {
+                   int64_t known_max_degree, OptTensor kv_task, OptTensor kv_split, int64_t kv_slots) {
   c10::cuda::CUDAGuard guard(q.device());
   bf_attn_params p{};
   fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed);
-  TORCH_CHECK(dout.is_contiguous() && dq.is_contiguous() && dk.is_contiguous() && dv.is_contiguous());
+  TORCH_CHECK(dout.is_contiguous());
+  check_qkv(dq, "dq"); check_qkv(dk, "dk"); check_qkv(dv, "dv");
+  TORCH_CHECK(dq.stride(0) == dk.stride(0) && dq.stride(0) == dv.stride(0), "dq/dk/dv must share one row stride");
   TORCH_CHECK(zd.is_contiguous() && zd.numel() == 2 * z.numel());
   bf_attn_bwd_params b{};
   b.dout = dout.data_ptr(); b.dq = dq.data_ptr(); b.dk = dk.data_ptr(); b.dv = dv.data_ptr();
+  b.ldg = dq.stride(0);
   b.zd = zd.data_ptr<float>();
   b.t_rowptr = iptr(t_rowptr); b.t_row = iptr(t_row); b.t_eid = iptr(t_eid);
   b.detab = detab.has_value() ? detab->data_ptr<float>() : nullptr;
   HubInfo hub = find_hubs(rowptr, known_max_degree);
-  HubInfo thub = find_hubs(t_rowptr, -1);
-  Tensor sq, skv;
+  const bool use_tasks = kv_task.has_value() && kv_task->numel() > 0;
+  HubInfo thub = use_tasks ? HubInfo() : find_hubs(t_rowptr, -1);
+  Tensor sq, skv, partial;
+  if (use_tasks) {
+    TORCH_CHECK(kv_task->scalar_type() == torch::kInt && kv_task->is_contiguous() && kv_task->size(1) == 4 &&
+                ((uintptr_t)kv_task->data_ptr()) % 16 == 0, "kv_task must be contiguous int32 [T, 4]");
+    b.kv_task = kv_task->data_ptr<int>(); b.n_kv_task = (int)kv_task->size(0);
+    if (kv_split.has_value() && kv_split->numel() > 0 && kv_slots > 0) {
+      b.kv_split = kv_split->data_ptr<int>(); b.n_kv_split = (int)kv_split->size(0);
+      partial = torch::empty({kv_slots, 2 * (int64_t)p.hl * p.hn}, q.options().dtype(torch::kFloat));
+      b.kv_partial = partial.data_ptr<float>();
+    }
+  }
   const int64_t w = (int64_t)p.hl * p.hn;
   if (hub.n > 0) {
     sq = torch::zeros({hub.n, w}, q.options().dtype(torch::kFloat));

@@ -281,7 +281,8 @@ __global__ void edge_attn_fwd_hub_finalize(AttnArgs a) {
 struct BwdArgs {
   AttnArgs f;
   const void* dout;            // [n, Hl, HN] contiguous
-  void *dq, *dk, *dv;          // [n, Hl, HN] contiguous
+  void *dq, *dk, *dv;          // [n, Hl, HN], row stride ldg (elements)
+  long long ldg;
   float2* zd;                  // [n, Hl]: (1/(Z+eps), D = <dout,out>)
   const int *t_rowptr, *t_row, *t_eid;
   float* detab;                // [T, Hl, HN] fp32 or null
@@ -289,6 +290,12 @@ struct BwdArgs {
   int n_t_hub;
   float* hub_scratch_q;        // [n_hub, Hl*HN]
   float* hub_scratch_kv;       // [n_t_hub, 2*Hl*HN]
+  // balanced dK/dV work list
+  const int4* kv_task;         // [n_kv_task]: key row, first edge, end edge, partial slot (-1 = direct store)
+  int n_kv_task;
+  const int* kv_split;         // [n_kv_split, 3]: key row, first slot, number of slots
+  int n_kv_split;
+  float* kv_partial;           // [slots, 2*Hl*HN] fp32
 };
 
 // One edge of the dQ pass for one task lane.
@@ -375,7 +382,7 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_q_kernel(BwdArgs b) {
   if (hub) end = beg;
   for (int e = beg; e < end; ++e)
     dq_edge<T, HN>(b, e, hsafe, off, qs0, qs1, qraw, dof, invz, dterm, dq, de0, de1, hm);
-  if (head_ok && !hub) store_vec<T>(static_cast<T*>(b.dq) + (long long)row * w_row + off, dq);
+  if (head_ok && !hub) store_vec<T>(static_cast<T*>(b.dq) + (long long)row * b.ldg + off, dq);
   if (a.variant == 2) {
     if (head_ok) {
 #pragma unroll
@@ -485,6 +492,60 @@ __device__ __forceinline__ void dkv_edge(const BwdArgs& b, int te, int head, int
   }
 }
 
+// dK/dV over the balanced work list: one lane group per (work item, head chunk).
+template <typename T, int HN>
+__global__ void __launch_bounds__(256) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
+  constexpr int VN = Vec<T>::N;
+  constexpr int LPH = HN / VN;
+  const AttnArgs& a = b.f;
+  const Geo g = make_geo<T, HN>(a.hl);
+  const int w_row = a.hl * HN;
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int tpw = 32 / g.tl;
+  const long long task = warp * tpw + lane / g.tl;
+  const int lt = lane % g.tl;
+  const long long n_task = (long long)b.n_kv_task * g.n_hc;
+  const bool live = task < n_task;
+  const int item = live ? (int)(task / g.n_hc) : 0;
+  const int hc = live ? (int)(task % g.n_hc) : 0;
+  const int head = hc * g.hpt + lt / LPH;
+  const bool head_ok = live && head < a.hl;
+  if (!head_ok) return;                       // whole head groups leave together; shuffles use head masks
+  const int off = head * HN + (lt % LPH) * VN;
+  const int4 it = __ldg(b.kv_task + item);
+  const int row = it.x, beg = it.y, end = it.z, slot = it.w;
+  float kf[VN], vf[VN], dk[VN], dv[VN];
+  load_vec<T>(static_cast<const T*>(a.k) + (long long)row * a.ldk + off, kf);
+  load_vec<T>(static_cast<const T*>(a.v) + (long long)row * a.ldv + off, vf);
+#pragma unroll
+  for (int i = 0; i < VN; ++i) { dk[i] = 0.f; dv[i] = 0.f; }
+  const unsigned hm = head_mask<LPH>();
+  for (int e = beg; e < end; ++e) dkv_edge<T, HN>(b, e, head, off, kf, vf, dk, dv, hm);
+  if (slot < 0) {
+    store_vec<T>(static_cast<T*>(b.dk) + (long long)row * b.ldg + off, dk);
+    store_vec<T>(static_cast<T*>(b.dv) + (long long)row * b.ldg + off, dv);
+  } else {
+    float* pp = b.kv_partial + (long long)slot * 2 * w_row;
+#pragma unroll
+    for (int i = 0; i < VN; ++i) { pp[off + i] = dk[i]; pp[w_row + off + i] = dv[i]; }
+  }
+}
+
+// Adds the partials of every split key row in slot order (fixed order => bit-reproducible).
+template <typename T>
+__global__ void __launch_bounds__(256) edge_attn_bwd_kv_reduce_kernel(BwdArgs b, int w_row) {
+  const int s = blockIdx.x;
+  const int row = b.kv_split[3 * s], first = b.kv_split[3 * s + 1], n = b.kv_split[3 * s + 2];
+  for (int c = threadIdx.x; c < 2 * w_row; c += blockDim.x) {
+    float acc = 0.f;
+    const float* pp = b.kv_partial + (long long)first * 2 * w_row + c;
+    for (int j = 0; j < n; ++j) acc += pp[(long long)j * 2 * w_row];
+    T* dst = c < w_row ? static_cast<T*>(b.dk) : static_cast<T*>(b.dv);
+    dst[(long long)row * b.ldg + (c < w_row ? c : c - w_row)] = from_float<T>(acc);
+  }
+}
+
 template <typename T, int HN>
 __global__ void __launch_bounds__(256) edge_attn_bwd_kv_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
@@ -517,8 +578,8 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_kernel(BwdArgs b) {
   const unsigned hm = head_mask<LPH>();
   for (int e = beg; e < end; ++e) dkv_edge<T, HN>(b, e, hsafe, off, kf, vf, dk, dv, hm);
   if (head_ok && !hub) {
-    store_vec<T>(static_cast<T*>(b.dk) + (long long)row * w_row + off, dk);
-    store_vec<T>(static_cast<T*>(b.dv) + (long long)row * w_row + off, dv);
+    store_vec<T>(static_cast<T*>(b.dk) + (long long)row * b.ldg + off, dk);
+    store_vec<T>(static_cast<T*>(b.dv) + (long long)row * b.ldg + off, dv);
   }
 }
 
@@ -566,11 +627,11 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_hub_kernel(BwdArgs b, in
 
 template <typename T>
 __global__ void hub_scatter_rows(const float* scratch, int scratch_ld, int scratch_off, const int* rows, T* dst,
-                                 int width) {
+                                 int width, long long ld_dst) {
   const int hub_i = blockIdx.x;
   const int row = rows[hub_i];
   for (int c = threadIdx.x; c < width; c += blockDim.x)
-    dst[(long long)row * width + c] = from_float<T>(scratch[(long long)hub_i * scratch_ld + scratch_off + c]);
+    dst[(long long)row * ld_dst + c] = from_float<T>(scratch[(long long)hub_i * scratch_ld + scratch_off + c]);
 }
 
 template <typename T, int HN>
@@ -601,13 +662,21 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
   if (blocks > 0) edge_attn_bwd_q_kernel<T, HN><<<(unsigned)blocks, 256, smem, st>>>(b);
   if (a.n_hub > 0) {
     edge_attn_bwd_q_hub_kernel<T, HN><<<a.n_hub * chunks_q, 256, 0, st>>>(b, chunks_q);
-    hub_scatter_rows<T><<<a.n_hub, 256, 0, st>>>(b.hub_scratch_q, w_row, 0, a.hub_rows, static_cast<T*>(b.dq), w_row);
+    hub_scatter_rows<T><<<a.n_hub, 256, 0, st>>>(b.hub_scratch_q, w_row, 0, a.hub_rows, static_cast<T*>(b.dq), w_row, b.ldg);
+  }
+  if (b.kv_task) {
+    const long long kv_tasks = (long long)b.n_kv_task * g.n_hc;
+    const long long kv_warps = (kv_tasks + tpw - 1) / tpw;
+    const long long kv_blocks = (kv_warps + 7) / 8;
+    if (kv_blocks > 0) edge_attn_bwd_kv_task_kernel<T, HN><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+    if (b.n_kv_split > 0) edge_attn_bwd_kv_reduce_kernel<T><<<b.n_kv_split, 256, 0, st>>>(b, w_row);
+    return cudaGetLastError();
   }
   if (blocks > 0) edge_attn_bwd_kv_kernel<T, HN><<<(unsigned)blocks, 256, 0, st>>>(b);
   if (b.n_t_hub > 0) {
     edge_attn_bwd_kv_hub_kernel<T, HN><<<b.n_t_hub * chunks_kv, 256, 0, st>>>(b, chunks_kv);
-    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, 0, b.t_hub_rows, static_cast<T*>(b.dk), w_row);
-    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, w_row, b.t_hub_rows, static_cast<T*>(b.dv), w_row);
+    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, 0, b.t_hub_rows, static_cast<T*>(b.dk), w_row, b.ldg);
+    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, w_row, b.t_hub_rows, static_cast<T*>(b.dv), w_row, b.ldg);
   }
   return cudaGetLastError();
 }
@@ -656,10 +725,13 @@ extern "C" int bf_edge_attn_bwd(const bf_attn_params* p, const bf_attn_bwd_param
   BwdArgs b;
   b.f = to_args(*p);
   b.dout = q->dout; b.dq = q->dq; b.dk = q->dk; b.dv = q->dv;
+  b.ldg = q->ldg > 0 ? q->ldg : (long long)p->hl * p->hn;
   b.zd = reinterpret_cast<float2*>(q->zd);
   b.t_rowptr = q->t_rowptr; b.t_row = q->t_row; b.t_eid = q->t_eid; b.detab = q->detab;
   b.t_hub_rows = q->t_hub_rows; b.n_t_hub = q->n_t_hub;
   b.hub_scratch_q = q->hub_scratch_q; b.hub_scratch_kv = q->hub_scratch_kv;
+  b.kv_task = reinterpret_cast<const int4*>(q->kv_task); b.n_kv_task = q->n_kv_task;
+  b.kv_split = q->kv_split; b.n_kv_split = q->n_kv_split; b.kv_partial = q->kv_partial;
   const int cq = p->max_hub_degree > 0 ? (p->max_hub_degree + BF_HUB_CHUNK - 1) / BF_HUB_CHUNK : 1;
   const int ckv = q->max_t_hub_degree > 0 ? (q->max_t_hub_degree + BF_HUB_CHUNK - 1) / BF_HUB_CHUNK : 1;
 #define CALL_BWD(T, H) (int)launch_bwd_t<T, H>(b, cq, ckv, st)

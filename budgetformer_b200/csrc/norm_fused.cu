@@ -28,87 +28,167 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 constexpr int LN_MAX_PER_LANE = 16;   // h <= 512
 
-template <typename T>
+// Column owned by (lane, i): contiguous chunks of `per` elements per lane when h == 32*per (vector-friendly,
+// the common case h = 64/128/256/512), otherwise lane-strided.
+__device__ __forceinline__ int ln_col(int lane, int i, int per, bool packed) { return packed ? lane * per + i : lane + 32 * i; }
+
+template <typename T, int PER>
+__device__ __forceinline__ void ln_load_row(const T* __restrict__ p, int lane, float* v) {
+  // PER contiguous elements starting at p + lane*PER, loaded as one or more 16/8/4-byte vectors
+  constexpr int BYTES = PER * (int)sizeof(T);
+  const T* q = p + lane * PER;
+  if constexpr (BYTES % 16 == 0) {
+    T tmp[PER];
+#pragma unroll
+    for (int j = 0; j < BYTES / 16; ++j) reinterpret_cast<uint4*>(tmp)[j] = reinterpret_cast<const uint4*>(q)[j];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = to_f<T>(tmp[i]);
+  } else if constexpr (BYTES % 8 == 0) {
+    T tmp[PER];
+#pragma unroll
+    for (int j = 0; j < BYTES / 8; ++j) reinterpret_cast<uint2*>(tmp)[j] = reinterpret_cast<const uint2*>(q)[j];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = to_f<T>(tmp[i]);
+  } else {
+    T tmp[PER];
+#pragma unroll
+    for (int j = 0; j < BYTES / 4; ++j) reinterpret_cast<uint32_t*>(tmp)[j] = reinterpret_cast<const uint32_t*>(q)[j];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = to_f<T>(tmp[i]);
+  }
+}
+template <typename T, int PER>
+__device__ __forceinline__ void ln_store_row(T* __restrict__ p, int lane, const float* v) {
+  constexpr int BYTES = PER * (int)sizeof(T);
+  T tmp[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) tmp[i] = from_f<T>(v[i]);
+  T* q = p + lane * PER;
+  if constexpr (BYTES % 16 == 0) {
+#pragma unroll
+    for (int j = 0; j < BYTES / 16; ++j) reinterpret_cast<uint4*>(q)[j] = reinterpret_cast<const uint4*>(tmp)[j];
+  } else if constexpr (BYTES % 8 == 0) {
+#pragma unroll
+    for (int j = 0; j < BYTES / 8; ++j) reinterpret_cast<uint2*>(q)[j] = reinterpret_cast<const uint2*>(tmp)[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < BYTES / 4; ++j) reinterpret_cast<uint32_t*>(q)[j] = reinterpret_cast<const uint32_t*>(tmp)[j];
+  }
+}
+
+// PER > 0: packed layout with h == 32*PER (rows must be 16-byte aligned); PER == 0: generic lane-strided layout.
+template <typename T, int PER>
 __global__ void __launch_bounds__(256) ln_fwd_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ gamma,
                                                      const float* __restrict__ beta, T* __restrict__ y, long long ldy,
                                                      float* __restrict__ stats, long long rows, int h, float eps) {
-  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  constexpr int NV = PER > 0 ? PER : LN_MAX_PER_LANE;
   const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  const T* xr = x + row * ldx;
-  float v[LN_MAX_PER_LANE];
-  float s = 0.f;
-  const int per = (h + 31) / 32;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int per = PER > 0 ? PER : (h + 31) / 32;
+  for (long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
+    const T* xr = x + row * ldx;
+    float v[NV];
+    if constexpr (PER > 0) {
+      ln_load_row<T, PER>(xr, lane, v);
+    } else {
 #pragma unroll
-  for (int i = 0; i < LN_MAX_PER_LANE; ++i) {
-    const int c = lane + 32 * i;
-    v[i] = (i < per && c < h) ? to_f<T>(xr[c]) : 0.f;
-    s += v[i];
-  }
-  const float mean = warp_sum(s) / h;
-  float q = 0.f;
+      for (int i = 0; i < NV; ++i) { const int c = lane + 32 * i; v[i] = (i < per && c < h) ? to_f<T>(xr[c]) : 0.f; }
+    }
+    float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < LN_MAX_PER_LANE; ++i) {
-    const int c = lane + 32 * i;
-    const float d = (i < per && c < h) ? v[i] - mean : 0.f;
-    q += d * d;
-  }
-  const float rstd = rsqrtf(warp_sum(q) / h + eps);
-  T* yr = y + row * ldy;
+    for (int i = 0; i < NV; ++i) s += v[i];
+    const float mean = warp_sum(s) / h;
+    float q = 0.f;
 #pragma unroll
-  for (int i = 0; i < LN_MAX_PER_LANE; ++i) {
-    const int c = lane + 32 * i;
-    if (i < per && c < h) yr[c] = from_f<T>((v[i] - mean) * rstd * gamma[c] + beta[c]);
+    for (int i = 0; i < NV; ++i) {
+      const int c = ln_col(lane, i, per, PER > 0);
+      const float d = (i < per && c < h) ? v[i] - mean : 0.f;
+      q += d * d;
+    }
+    const float rstd = rsqrtf(warp_sum(q) / h + eps);
+    T* yr = y + row * ldy;
+    if constexpr (PER > 0) {
+      float o[NV];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) { const int c = lane * PER + i; o[i] = (v[i] - mean) * rstd * gamma[c] + beta[c]; }
+      ln_store_row<T, PER>(yr, lane, o);
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (i < per && c < h) yr[c] = from_f<T>((v[i] - mean) * rstd * gamma[c] + beta[c]);
+      }
+    }
+    if (lane == 0 && stats) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
   }
-  if (lane == 0 && stats) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
 }
 
-// dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)); dgamma += dy*xhat; dbeta += dy
-template <typename T>
+// dx = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)); dgamma += dy*xhat; dbeta += dy.
+// Persistent grid: every warp walks many rows and keeps its dgamma/dbeta partials in registers, so the global
+// atomics at the end number (blocks * h), not (rows * h / 128).
+template <typename T, int PER>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict__ x,
                                                      long long ldx, const float* __restrict__ stats,
                                                      const float* __restrict__ gamma, T* __restrict__ dx, long long lddx,
                                                      float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                                     long long rows, int h, int rows_per_warp) {
+                                                     long long rows, int h) {
+  constexpr int NV = PER > 0 ? PER : LN_MAX_PER_LANE;
   extern __shared__ float s_acc[];      // [2, h]
   for (int i = threadIdx.x; i < 2 * h; i += blockDim.x) s_acc[i] = 0.f;
   __syncthreads();
-  const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  const int per = (h + 31) / 32;
-  float dg[LN_MAX_PER_LANE], db[LN_MAX_PER_LANE];
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int per = PER > 0 ? PER : (h + 31) / 32;
+  float dg[NV], db[NV], gam[NV];
 #pragma unroll
-  for (int i = 0; i < LN_MAX_PER_LANE; ++i) { dg[i] = 0.f; db[i] = 0.f; }
-  for (int rr = 0; rr < rows_per_warp; ++rr) {
-    const long long row = warp_id * rows_per_warp + rr;
-    if (row >= rows) break;
+  for (int i = 0; i < NV; ++i) {
+    dg[i] = 0.f; db[i] = 0.f;
+    const int c = ln_col(lane, i, per, PER > 0);
+    gam[i] = (i < per && c < h) ? gamma[c] : 0.f;
+  }
+  for (long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
     const float mean = stats[2 * row], rstd = stats[2 * row + 1];
-    float xh[LN_MAX_PER_LANE], gdy[LN_MAX_PER_LANE];
+    float xv[NV], dv[NV];
+    if constexpr (PER > 0) {
+      ln_load_row<T, PER>(x + row * ldx, lane, xv);
+      ln_load_row<T, PER>(dy + row * lddy, lane, dv);
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        const bool ok = i < per && c < h;
+        xv[i] = ok ? to_f<T>(x[row * ldx + c]) : mean;
+        dv[i] = ok ? to_f<T>(dy[row * lddy + c]) : 0.f;
+      }
+    }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < LN_MAX_PER_LANE; ++i) {
-      const int c = lane + 32 * i;
-      if (i < per && c < h) {
-        const float d = to_f<T>(dy[row * lddy + c]);
-        xh[i] = (to_f<T>(x[row * ldx + c]) - mean) * rstd;
-        gdy[i] = d * gamma[c];
-        dg[i] += d * xh[i];
-        db[i] += d;
-        s1 += gdy[i];
-        s2 += gdy[i] * xh[i];
-      } else { xh[i] = 0.f; gdy[i] = 0.f; }
+    for (int i = 0; i < NV; ++i) {
+      xv[i] = (xv[i] - mean) * rstd;            // xhat
+      dg[i] += dv[i] * xv[i];
+      db[i] += dv[i];
+      dv[i] *= gam[i];                          // g * dy
+      s1 += dv[i];
+      s2 += dv[i] * xv[i];
     }
     s1 = warp_sum(s1) / h;
     s2 = warp_sum(s2) / h;
+    if constexpr (PER > 0) {
+      float o[NV];
 #pragma unroll
-    for (int i = 0; i < LN_MAX_PER_LANE; ++i) {
-      const int c = lane + 32 * i;
-      if (i < per && c < h) dx[row * lddx + c] = from_f<T>(rstd * (gdy[i] - s1 - xh[i] * s2));
+      for (int i = 0; i < NV; ++i) o[i] = rstd * (dv[i] - s1 - xv[i] * s2);
+      ln_store_row<T, PER>(dx + row * lddx, lane, o);
+    } else {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (i < per && c < h) dx[row * lddx + c] = from_f<T>(rstd * (dv[i] - s1 - xv[i] * s2));
+      }
     }
   }
 #pragma unroll
-  for (int i = 0; i < LN_MAX_PER_LANE; ++i) {
-    const int c = lane + 32 * i;
+  for (int i = 0; i < NV; ++i) {
+    const int c = ln_col(lane, i, per, PER > 0);
     if (i < per && c < h) { atomicAdd(&s_acc[c], dg[i]); atomicAdd(&s_acc[h + c], db[i]); }
   }
   __syncthreads();
@@ -146,13 +226,33 @@ __global__ void __launch_bounds__(256) hash_dropout_kernel(const T* __restrict__
   else if (DT == BF_FP32) { CALL(float); }                              \
   else return (int)cudaErrorInvalidValue;
 
+static bool ln_packed_ok(int h, int dtype, const void* a, long long lda, const void* b2, long long ldb) {
+  const int esz = dtype == BF_FP32 ? 4 : 2;
+  if (h % 32 != 0) return false;
+  const int per = h / 32;
+  if (!(per == 2 || per == 4 || per == 8 || per == 16)) return false;
+  if ((per * esz) % 4 != 0) return false;
+  return ((uintptr_t)a % 16 == 0) && ((uintptr_t)b2 % 16 == 0) && ((lda * esz) % 16 == 0) && ((ldb * esz) % 16 == 0);
+}
+
+#define BF_LN_PER_SWITCH(T, PERV, KERNEL_CALL)              \
+  switch (PERV) {                                            \
+    case 2: { constexpr int P_ = 2; KERNEL_CALL; break; }    \
+    case 4: { constexpr int P_ = 4; KERNEL_CALL; break; }    \
+    case 8: { constexpr int P_ = 8; KERNEL_CALL; break; }    \
+    case 16: { constexpr int P_ = 16; KERNEL_CALL; break; }  \
+    default: { constexpr int P_ = 0; KERNEL_CALL; break; }   \
+  }
+
 extern "C" int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma, const float* beta, void* y,
                                 long long ldy, float* stats, long long rows, int h, float eps, int dtype,
                                 cudaStream_t st) {
   if (h > 32 * LN_MAX_PER_LANE || h < 1) return (int)cudaErrorInvalidValue;
   if (rows == 0) return 0;
-  const long long blocks = (rows * 32 + 255) / 256;
-#define CALL(T) ln_fwd_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, gamma, beta, (T*)y, ldy, stats, rows, h, eps)
+  long long blocks = (rows * 32 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const int per = ln_packed_ok(h, dtype, x, ldx, y, ldy) ? h / 32 : 0;
+#define CALL(T) BF_LN_PER_SWITCH(T, per, (ln_fwd_kernel<T, P_><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, gamma, beta, (T*)y, ldy, stats, rows, h, eps)))
   BF_DT_SWITCH(dtype, CALL)
 #undef CALL
   return (int)cudaGetLastError();
@@ -163,11 +263,11 @@ extern "C" int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, l
                                 long long rows, int h, int dtype, cudaStream_t st) {
   if (h > 32 * LN_MAX_PER_LANE || h < 1) return (int)cudaErrorInvalidValue;
   if (rows == 0) return 0;
-  const int rows_per_warp = 16;
-  const long long warps = (rows + rows_per_warp - 1) / rows_per_warp;
-  const long long blocks = (warps * 32 + 255) / 256;
+  long long blocks = (rows * 32 + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
   const size_t smem = sizeof(float) * 2 * h;
-#define CALL(T) ln_bwd_kernel<T><<<(unsigned)blocks, 256, smem, st>>>((const T*)dy, lddy, (const T*)x, ldx, stats, gamma, (T*)dx, lddx, dgamma, dbeta, rows, h, rows_per_warp)
+  const int per = (ln_packed_ok(h, dtype, x, ldx, dy, lddy) && ln_packed_ok(h, dtype, dx, lddx, dx, lddx)) ? h / 32 : 0;
+#define CALL(T) BF_LN_PER_SWITCH(T, per, (ln_bwd_kernel<T, P_><<<(unsigned)blocks, 256, smem, st>>>((const T*)dy, lddy, (const T*)x, ldx, stats, gamma, (T*)dx, lddx, dgamma, dbeta, rows, h)))
   BF_DT_SWITCH(dtype, CALL)
 #undef CALL
   return (int)cudaGetLastError();

@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t SPIN_LIMIT = 1u << 21;   // x (128 ns sleep + one system-scope load): a few seconds
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -47,7 +47,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flag_pages, int rank, int world, in
     for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
       // epochs only grow; signed distance handles wrap-around
       if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) { ok = true; break; }
-      __nanosleep(64);
+      __nanosleep(128);
     }
     if (!ok) { atomicExch(status, 16 + t); atomicExch(status + 1, (int)epoch); }
   }

@@ -21,6 +21,7 @@ from typing import Optional
 import torch
 
 HUB_DEGREE = 1024  # rows longer than this take the chunked hub path in the kernels
+KV_TASK_EDGES = 64  # edges per work item of the dK/dV pass
 
 
 @dataclass
@@ -92,9 +93,13 @@ class AttnGraph:
     t_rowptr: Optional[torch.Tensor] = field(default=None, repr=False)
     t_row: Optional[torch.Tensor] = field(default=None, repr=False)   # query id per transposed slot
     t_eid: Optional[torch.Tensor] = field(default=None, repr=False)   # position in ``col``
+    # balanced work list over the transpose (chunks of <= KV_TASK_EDGES edges); see ensure_transpose
+    t_task: Optional[torch.Tensor] = field(default=None, repr=False)        # [T, 4] int32: row, beg, end, partial slot
+    t_split: Optional[torch.Tensor] = field(default=None, repr=False)       # [S, 3] int32: row, first slot, n slots
     max_degree: Optional[int] = None     # known upper bound on query in-degree (None = unknown)
     n_real: int = -1
     n_rw: int = -1
+    kv_slots: int = 0                    # number of fp32 partial slots the dK/dV pass needs
 
     @property
     def device(self):
@@ -106,7 +111,7 @@ class AttnGraph:
 
     def nbytes(self) -> int:
         tot = 0
-        for t in (self.rowptr, self.col, self.etype, self.t_rowptr, self.t_row, self.t_eid):
+        for t in (self.rowptr, self.col, self.etype, self.t_rowptr, self.t_row, self.t_eid, self.t_task, self.t_split):
             if t is not None:
                 tot += int(t.numel()) * t.element_size()
         return tot
@@ -114,7 +119,8 @@ class AttnGraph:
     def to(self, device, non_blocking: bool = False) -> "AttnGraph":
         f = lambda t: None if t is None else t.to(device, non_blocking=non_blocking)
         return AttnGraph(self.num_rows, f(self.rowptr), f(self.col), f(self.etype), f(self.t_rowptr),
-                         f(self.t_row), f(self.t_eid), self.max_degree, self.n_real, self.n_rw)
+                         f(self.t_row), f(self.t_eid), f(self.t_task), f(self.t_split), self.max_degree,
+                         self.n_real, self.n_rw, self.kv_slots)
 
     def row_ids(self) -> torch.Tensor:
         """Query id of every edge (int64), i.e. ``edge_index[1]`` of the COO form."""
@@ -142,7 +148,34 @@ class AttnGraph:
         if self.num_edges:
             t_rowptr[1:] = torch.cumsum(torch.bincount(col64, minlength=self.num_rows), 0)
         self.t_rowptr = t_rowptr.to(torch.int32)
+        self._build_kv_tasks(t_rowptr)
         return self
+
+    def _build_kv_tasks(self, t_rowptr: torch.Tensor) -> None:
+        """Work list of the dK/dV pass.  Key popularity is heavy-tailed (a hub is the key of 10^4-10^5 edges), so a
+        row-per-lane-group mapping leaves most of the GPU idle behind a few long rows.  Every key row is cut into
+        chunks of at most ``KV_TASK_EDGES`` edges; rows with one chunk store their result directly, rows with
+        several write fp32 partials that a second small kernel adds up in a fixed order (deterministic, no atomics)."""
+        dev = self.device
+        deg = t_rowptr[1:] - t_rowptr[:-1]
+        n_chunks = torch.clamp((deg + KV_TASK_EDGES - 1) // KV_TASK_EDGES, min=1)
+        first = torch.zeros(self.num_rows + 1, dtype=torch.int64, device=dev)
+        first[1:] = torch.cumsum(n_chunks, 0)
+        total = int(first[-1].item()) if self.num_rows else 0
+        rows = torch.repeat_interleave(torch.arange(self.num_rows, device=dev), n_chunks, output_size=total)
+        chunk = torch.arange(total, device=dev) - first[rows]
+        beg = t_rowptr[rows] + chunk * KV_TASK_EDGES
+        end = torch.minimum(beg + KV_TASK_EDGES, t_rowptr[rows + 1])
+        split_row = n_chunks > 1
+        is_split = split_row[rows]
+        slot = torch.cumsum(is_split.to(torch.int64), 0) - 1
+        slot = torch.where(is_split, slot, torch.full_like(slot, -1))
+        self.t_task = torch.stack([rows, beg, end, slot], 1).to(torch.int32).contiguous()
+        srows = torch.nonzero(split_row).flatten()
+        nsl = n_chunks[srows]
+        sfirst = torch.cumsum(nsl, 0) - nsl
+        self.t_split = torch.stack([srows, sfirst, nsl], 1).to(torch.int32).contiguous()
+        self.kv_slots = int(nsl.sum().item()) if srows.numel() else 0
 
     @staticmethod
     def from_edge_index(edge_index: torch.Tensor, num_rows: int) -> "AttnGraph":

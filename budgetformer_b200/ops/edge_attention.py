@@ -124,8 +124,8 @@ class _EdgeAttentionCUDA(torch.autograd.Function):
                           graph.rowptr, graph.col, graph.etype,
                           graph.t_rowptr, graph.t_row, graph.t_eid,
                           etable if has_tab else None, detab,
-                          variant_id, dropout_p, dropout_seed, kmax)
-        _ext.count_launches(2)
+                          variant_id, dropout_p, dropout_seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots))
+        _ext.count_launches(3)
         return dq, dk, dv, (detab.to(etable.dtype) if has_tab else None), None, None, None, None
 
 

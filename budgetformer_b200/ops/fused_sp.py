@@ -109,7 +109,7 @@ class _QKVPush(torch.autograd.Function):
         dw = torch.matmul(dloc.t(), x).float()[sp.inv_perm]
         dwq, dwk, dwv = (t.to(ctx.wdtype) for t in dw.split(sp.h, 0))
         if ctx.has_bias:
-            db = dloc.float().sum(0)[sp.inv_perm]
+            db = torch.sum(dloc, dim=0, dtype=torch.float32)[sp.inv_perm]
             dbq, dbk, dbv = (t.to(ctx.wdtype) for t in db.split(sp.h, 0))
         else:
             dbq = dbk = dbv = None
@@ -157,19 +157,16 @@ class _PackedEdgeAttention(torch.autograd.Function):
         k = qkv[:, hl:2 * hl].view(r, hlh, hn)
         v = qkv[:, 2 * hl:3 * hl].view(r, hlh, hn)
         # gradients land packed in the symmetric buffer so that peers can pull their rows
-        dq = torch.empty((r, hlh, hn), dtype=qkv.dtype, device=qkv.device)
-        dk = torch.empty_like(dq)
-        dv = torch.empty_like(dq)
+        dbuf = sp.dqkv.tensor
+        dq = dbuf[:, 0:hl].view(r, hlh, hn)
+        dk = dbuf[:, hl:2 * hl].view(r, hlh, hn)
+        dv = dbuf[:, 2 * hl:3 * hl].view(r, hlh, hn)
         zd = torch.empty((r, hlh, 2), dtype=torch.float32, device=qkv.device)
         detab = torch.zeros(etable.shape, dtype=torch.float32, device=qkv.device) if has_tab else None
         ext.edge_attn_bwd(q, k, v, out.view(r, hlh, hn), z, dout.view(r, hlh, hn), dq, dk, dv, zd, graph.rowptr, graph.col,
                           graph.etype, graph.t_rowptr, graph.t_row, graph.t_eid, etable if has_tab else None, detab,
-                          variant_id, dropout_p, seed, kmax)
-        _ext.count_launches(2)
-        dbuf = sp.dqkv.tensor
-        dbuf[:, 0:hl] = dq.view(r, hl)
-        dbuf[:, hl:2 * hl] = dk.view(r, hl)
-        dbuf[:, 2 * hl:3 * hl] = dv.view(r, hl)
+                          variant_id, dropout_p, seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots))
+        _ext.count_launches(3)
         return dbuf, (detab.to(etable.dtype) if has_tab else None), None, None, None, None, None, None
 
 
@@ -219,7 +216,7 @@ class _CtxPullOutProj(torch.autograd.Function):
             # d(context) = (g W_o) [* pre-dropout mask], pushed to the head owners by the GEMM epilogue
             _push_gemm(g, w.t().contiguous(), None, dbuf.ptrs, sp.row0, sp.hl, dropout_p=p_pre, seed=seed_pre)
             dw = torch.matmul(g.t(), a).to(wdtype)
-            db = g.float().sum(0).to(wdtype) if has_b else None
+            db = torch.sum(g, dim=0, dtype=torch.float32).to(wdtype) if has_b else None
         else:
             da = hash_dropout(g, seed_pre, p_pre) if p_pre > 0 else g
             esz = da.element_size()

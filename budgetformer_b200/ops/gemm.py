@@ -91,7 +91,7 @@ class _FusedLinear(torch.autograd.Function):
         g = hash_dropout(dy, seed, p) if p > 0 else dy
         dx = gemm_tn(g, w16.t().contiguous())            # dx = g @ W, expressed as g @ (W^T)^T
         dw = torch.matmul(g.t(), x).to(wdtype)
-        db = g.float().sum(0).to(wdtype) if has_bias else None
+        db = torch.sum(g, dim=0, dtype=torch.float32).to(wdtype) if has_bias else None
         return dx, dw, db, (dy if has_res else None), None, None
 
 

@@ -375,6 +375,7 @@ class FullGraphTrainer:
         x_local = None
         if x_host is not None:
             x_local = x_host.to(self.device, non_blocking=True)
+        self._align_ranks()
         with StepTimer(self.device, sync_timers) as t_rw:
             graph = self.build_edges(epoch)
         timers["rw"] = t_rw.elapsed
@@ -400,6 +401,15 @@ class FullGraphTrainer:
         out["edges"] = float(graph.num_edges)
         return out
 
+    def _align_ranks(self) -> None:
+        """Stream-ordered NCCL rendezvous before a fused forward.  The in-kernel barriers of the fused path use
+        bounded spins (a few seconds); this keeps host-side skew between ranks (evaluation on rank 0, logging, a
+        slow CPU edge build) out of those spins, leaving NCCL's own watchdog as the detector for a lost rank."""
+        if self.fused_sp and self.sp_world > 1:
+            if not hasattr(self, "_align_buf"):
+                self._align_buf = torch.zeros(1, device=self.device)
+            dist.all_reduce(self._align_buf, group=self.sp_group)
+
     def _next_budget_known(self) -> bool:
         """Prefetch only when the next epoch's budget cannot change (main_node_fullgraph_sp.py:545-555)."""
         return (not self.budget_cfg.enabled) or self.controller.frozen or self.epoch <= int(self.args.warmup_updates)
@@ -415,6 +425,7 @@ class FullGraphTrainer:
         graph = getattr(self, "last_graph", None)
         if graph is None:
             graph = self.build_edges(epoch)
+        self._align_ranks()
         attn_type = getattr(self.args, "attn_type", "sparse")
         with autocast_context(self.device, self.amp_dtype):
             if self.multilabel:
@@ -455,6 +466,7 @@ class FullGraphTrainer:
         """Loss / accuracy of the current weights on the probe nodes under budget ``state``
         (``_probe_loss_sp``, utils/fullgraph_sp_support.py:2318-2358): three SUM reductions packed into one."""
         graph = self.edge_engine.build(seed, resolve_budget_state(self.args, state), record=False)
+        self._align_ranks()
         idx = self.probe_local_idx
         was_training = self.model.training
         self.model.eval()

@@ -1,0 +1,84 @@
+"""Child program of tests/test_gpu_multi.py: run under torchrun with one rank per GPU.
+
+Checks, on every rank: (1) the peer-memory mean all-reduce equals NCCL's; (2) the fused sequence-parallel
+layer path (GEMM epilogue push, peer pull, device barriers) reproduces the portable NCCL all-to-all path:
+same loss, same parameter gradients after reduction; (3) a few fused training steps stay finite and the
+device status word stays clean."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from budgetformer_b200.config import parse_fullgraph_args  # noqa: E402
+from budgetformer_b200.graph.synthetic import sbm_graph  # noqa: E402
+from budgetformer_b200.ops import gemm  # noqa: E402
+from budgetformer_b200.parallel import symm  # noqa: E402
+from budgetformer_b200.train.data import GraphData, random_split_idx  # noqa: E402
+from budgetformer_b200.train.engine import FullGraphTrainer  # noqa: E402
+
+
+def trainer(model, fused, extra=()):
+    n = 4096
+    x, y, ei = sbm_graph(n, feat_dim=64, seed=3)
+    data = GraphData(x, y, ei, random_split_idx(n, 3), n, 7)
+    argv = ["--model", model, "--dataset", "t", "--n_layers", "2", "--hidden_dim", "128", "--num_heads", "8",
+            "--ffn_dim", "256", "--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4",
+            "--amp_dtype", "bf16", "--force_random_split", "--fused_sp", "on" if fused else "off",
+            "--dropout_rate", "0.0", "--attention_dropout_rate", "0.0", "--input_dropout_rate", "0.0", "--seed", "5"]
+    return FullGraphTrainer(parse_fullgraph_args(argv + list(extra)), data=data, log=lambda *a, **k: None)
+
+
+def main():
+    models = sys.argv[1].split(",") if len(sys.argv) > 1 else ["gt"]
+    first = trainer(models[0], fused=False)
+    rank, world, dev = first.rank, first.sp_world, first.device
+    # ---- (1) all-reduce ---------------------------------------------------------------------------
+    sw = symm.get_world(first.sp_group, dev)
+    buf = sw.alloc((1 << 20,), torch.float32)
+    torch.manual_seed(100 + rank)
+    buf.tensor.copy_(torch.randn(1 << 20, device=dev))
+    ref = buf.tensor.clone()
+    dist.all_reduce(ref)
+    ref /= world
+    class B: pass
+    b = B(); b.symm = (sw, buf)
+    symm.bucket_all_reduce_mean(b)
+    torch.cuda.synchronize()
+    err = float((buf.tensor - ref).abs().max())
+    assert err < 1e-5, f"rank {rank}: all-reduce mismatch {err} (multimem={bool(buf.multicast_ptr)})"
+    # ---- (2) fused vs portable ----------------------------------------------------------------------
+    for m in models:
+        a = first if m == models[0] else trainer(m, fused=False)
+        f = trainer(m, fused=True)
+        assert f.fused_sp and not a.fused_sp
+        f.model.load_state_dict(a.model.state_dict())
+        g = a.build_edges(1)
+        la, oa = a._loss(g, a.local_idx["train"])
+        lf, of = f._loss(g, f.local_idx["train"])
+        assert torch.allclose(oa.float(), of.float(), atol=6e-2, rtol=6e-2), f"{m}: forward mismatch on rank {rank}"
+        a.reducer.prepare_backward(); f.reducer.prepare_backward()
+        la.backward(); lf.backward()
+        a.reducer.finalize_backward(); f.reducer.finalize_backward()
+        torch.cuda.synchronize()
+        gemm.check_status(dev)
+        gmax = max(float(p.grad.abs().max()) for p in a.model.parameters())
+        for (na, pa), (_, pf) in zip(a.model.named_parameters(), f.model.named_parameters()):
+            e = float((pa.grad - pf.grad).abs().max())
+            assert e <= 0.12 * max(float(pa.grad.abs().max()), 1e-6) or e <= 5e-3 * gmax, \
+                f"{m}: grad mismatch on {na} rank {rank}: {e} vs {float(pa.grad.abs().max())}"
+        # ---- (3) a few fused steps ------------------------------------------------------------------
+        losses = [f.train_step(e)["loss"] for e in range(1, 6)]
+        gemm.check_status(dev)
+        assert all(l == l for l in losses), losses
+        if rank == 0:
+            print(f"OK {m}: world={world} loss {float(la):.4f}/{float(lf):.4f} allreduce_err={err:.2e} "
+                  f"multimem={bool(buf.multicast_ptr)} steps={['%.3f' % l for l in losses]}", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
