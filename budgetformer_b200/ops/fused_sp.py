@@ -133,7 +133,7 @@ class _PackedEdgeAttention(torch.autograd.Function):
                           int(variant_id), float(dropout_p), int(seed), kmax)
         _ext.count_launches(1)
         if sp.token_rows is not None and len(sp.token_rows) > 1:
-            out[sp.token_rows[1:]] = out[sp.token_rows[0]]          # copy_global_token0 (gt_sp/utils.py:2365-2386)
+            out[sp.token_rows[1:]] = out[sp.token_rows[0]].clone()  # copy_global_token0 (gt_sp/utils.py:2365-2386)
         ctx.sp, ctx.graph, ctx.layer = sp, graph, layer
         ctx.cfg = (int(variant_id), float(dropout_p), int(seed), etable is not None, kmax)
         ctx.save_for_backward(qkv, z, etable if etable is not None else qkv.new_empty(0))
