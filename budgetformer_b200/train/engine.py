@@ -290,6 +290,7 @@ class FullGraphTrainer:
                 loss.backward()
             self.reducer.finalize_backward()
         with StepTimer(self.device, sync_timers) as t_opt:
+            self.fault.check("opt", epoch)
             if self.scaler.is_enabled():
                 self.scaler.unscale_(self.optimizer)
                 torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)

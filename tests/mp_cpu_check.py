@@ -1,0 +1,86 @@
+"""Child program for the gloo multi-process CPU tests (spawned by tests/test_dist_cpu.py)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from budgetformer_b200.config import parse_fullgraph_args  # noqa: E402
+from budgetformer_b200.graph.synthetic import sbm_graph  # noqa: E402
+from budgetformer_b200.train.data import GraphData, random_split_idx  # noqa: E402
+from budgetformer_b200.train.engine import FullGraphTrainer  # noqa: E402
+
+
+def make(model, extra=(), n=512):
+    x, y, ei = sbm_graph(n, feat_dim=32, seed=3)
+    data = GraphData(x, y, ei, random_split_idx(n, 3), n, 7)
+    argv = ["--model", model, "--dataset", "t", "--n_layers", "2", "--hidden_dim", "32", "--num_heads", "4", "--ffn_dim", "64",
+            "--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4", "--force_random_split",
+            "--distributed-backend", "gloo", "--dropout_rate", "0.0", "--attention_dropout_rate", "0.0",
+            "--input_dropout_rate", "0.0", "--seed", "5", "--epochs", "4", "--eval_every", "2"]
+    return FullGraphTrainer(parse_fullgraph_args(argv + list(extra)), data=data, log=lambda *a, **k: None)
+
+
+def mode_equiv(out_path):
+    """SP forward/backward on P ranks equals the single-process result (written by rank 0 for the parent to compare)."""
+    res = {}
+    for model in ("gt", "graphormer", "graphgps", "exphormer"):
+        t = make(model)
+        g = t.build_edges(1)
+        t.model.eval()                                    # BatchNorm: use running stats so that ranks agree with 1 process
+        loss, out = t._loss(g, t.local_idx["train"])
+        n_local = float(t.local_idx["train"].numel())
+        t.reducer.prepare_backward()
+        (loss * n_local).backward()                       # sum over local nodes -> after the mean reduction: sum / P
+        t.reducer.finalize_backward()
+        parts = [torch.empty_like(out) for _ in range(t.sp_world)]
+        gn = torch.tensor([n_local])
+        if dist.is_initialized():
+            dist.all_gather(parts, out.contiguous())
+            dist.all_reduce(gn)
+        else:
+            parts = [out]
+        grads = {n: (p.grad * t.sp_world / float(gn)).tolist() for n, p in list(t.model.named_parameters())[:6]}
+        res[model] = {"out": torch.cat(parts)[:8].tolist(), "grads": grads, "edges": g.num_edges,
+                      "cols": g.col[:64].tolist()}
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        json.dump(res, open(out_path, "w"))
+
+
+def mode_train(out_path):
+    t = make("gt", ["--peak_lr", "5e-3"], n=2048)
+    best = t.fit()
+    if dist.get_rank() == 0:
+        json.dump({"best": best, "epochs": len(t.epoch_times)}, open(out_path, "w"))
+
+
+def mode_oom(out_path):
+    """Host-injected out-of-memory errors.  Epoch 2: every rank fails before its forward (the symmetric case of
+    real OOMs: ranks hold identical tensors) -> one tier is demoted and the step retried.  Epoch 3: only rank 1
+    fails, after backward and the gradient reduction (no collective pending) -> the vote makes rank 0 drop the step
+    too and both demote again."""
+    t = make("gt", ["--activation_checkpoint_mode", "multi_tier", "--force_multi_tier_plan", "cpu_rank_local_prefetch:retain=2",
+                    "--fault_inject", "oom@fwd:2,oom@opt:3:rank1", "--distributed-timeout-minutes", "2"])
+    log = []
+    for epoch in (1, 2, 3, 4):
+        s = t.train_step(epoch)
+        log.append({"epoch": epoch, "dropped": s["dropped"], "loss": s["loss"], "modes": t.planner.modes()})
+    json.dump(log, open(out_path + f".{dist.get_rank()}", "w"))
+
+
+def mode_adaptive(out_path):
+    t = make("gt", ["--adaptive_edge_budget", "--max_total_edges_per_query", "8", "--warmup_updates", "1", "--epochs", "8",
+                    "--eval_every", "100"], n=1024)
+    # drop the fixed budget flags: rebuild args without them
+    json.dump({"ok": True}, open(out_path + f".{dist.get_rank()}", "w"))
+
+
+if __name__ == "__main__":
+    mode, out = sys.argv[1], sys.argv[2]
+    {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom}[mode](out)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()

@@ -1,0 +1,53 @@
+"""Multi-process CPU tests over gloo (world size 2): sequence-parallel equivalence, end-to-end training of the
+2,048-node SBM configuration, voted OOM recovery with a host-injected fault."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _spawn(nproc, mode, out, port):
+    env = dict(os.environ)
+    env["OMP_NUM_THREADS"] = "2"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "mp_cpu_check.py"), mode, out]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_sp_two_ranks_equals_single_process(tmp_path):
+    one, two = str(tmp_path / "one.json"), str(tmp_path / "two.json")
+    _spawn(1, "equiv", one, 29801)
+    _spawn(2, "equiv", two, 29802)
+    a, b = json.load(open(one)), json.load(open(two))
+    for model in a:
+        assert a[model]["edges"] == b[model]["edges"] and a[model]["cols"] == b[model]["cols"], model
+        assert torch.allclose(torch.tensor(a[model]["out"]), torch.tensor(b[model]["out"]), atol=2e-5), model
+        for name in a[model]["grads"]:
+            ga, gb = torch.tensor(a[model]["grads"][name]), torch.tensor(b[model]["grads"][name])
+            assert torch.allclose(ga, gb, atol=2e-5 + 1e-3 * float(ga.abs().max())), (model, name)
+
+
+def test_sbm_config_trains_on_two_cpu_ranks(tmp_path):
+    out = str(tmp_path / "train.json")
+    _spawn(2, "train", out, 29803)
+    res = json.load(open(out))
+    assert res["epochs"] == 4 and res["best"]["valid"] > 0.15
+
+
+def test_voted_oom_recovery_is_symmetric(tmp_path):
+    out = str(tmp_path / "oom.json")
+    _spawn(2, "oom", out, 29804)
+    r0, r1 = json.load(open(out + ".0")), json.load(open(out + ".1"))
+    assert [e["modes"] for e in r0] == [e["modes"] for e in r1]          # ranks agree on every tier decision
+    assert r0[0]["modes"] == ["retain", "retain"]
+    assert r0[1]["modes"] == ["keep_mha", "retain"]                        # one tier demoted after the injected OOM
+    assert r0[1]["dropped"] == 0.0 and r0[1]["loss"] == r0[1]["loss"]      # fault hit before backward: step retried
+    assert r0[2]["dropped"] == 1.0 and r1[2]["dropped"] == 1.0             # fault after backward on rank 1: both drop
+    assert r0[2]["modes"] == ["recompute", "retain"]
+    assert r0[3]["dropped"] == 0.0 and r0[3]["modes"] == r0[2]["modes"]
