@@ -739,3 +739,67 @@ extern "C" int bf_edge_attn_bwd(const bf_attn_params* p, const bf_attn_bwd_param
 #undef CALL_BWD
   return (int)cudaErrorInvalidValue;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the forward entry point (declared and documented in bf_noalloc.h).
+// ---------------------------------------------------------------------------------------------------
+#include "bf_noalloc.h"
+
+#include <mutex>
+
+// Scratch of the long-row kernels for callers that cannot allocate.  In host code this name is only a handle for
+// the runtime (it is not a device address); the address is resolved per device below.
+static __device__ __align__(256) float g_bf_noalloc_scratch[BF_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device (looked up once per device).
+int noalloc_scratch_ptr(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return BF_NOALLOC_ERR_SETUP;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_bf_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return BF_NOALLOC_ERR_SETUP;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int bf_edge_attn_fwd_noalloc(const bf_attn_params* p, cudaStream_t stream) {
+  if (p == nullptr) return (int)cudaErrorInvalidValue;
+  const long long width = (long long)p->hl * p->hn;
+  if (p->n_hub < 0 || p->n_hub > BF_NOALLOC_MAX_HUBS || width > BF_NOALLOC_MAX_WIDTH || p->hl > BF_NOALLOC_MAX_HEADS)
+    return BF_NOALLOC_ERR_TOO_LARGE;
+  bf_attn_params q = *p;
+  q.hub_scratch = nullptr;
+  if (p->n_hub > 0) {
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch_ptr(&scratch);
+    if (rc != 0) return rc;
+    // the array keeps the previous call's sums: clear the part this call accumulates into
+    const size_t bytes = sizeof(float) * (size_t)p->n_hub * (size_t)(width + p->hl);
+    const cudaError_t e = cudaMemsetAsync(scratch, 0, bytes, stream);
+    if (e != cudaSuccess) return (int)e;
+    q.hub_scratch = scratch;
+  }
+  return bf_edge_attn_fwd(&q, stream);
+}
+
+extern "C" const char* bf_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "success";
+    case BF_NOALLOC_ERR_TOO_LARGE:
+      return "bf_edge_attn_fwd_noalloc: problem exceeds the built-in scratch (n_hub <= 64, hl*hn <= 1024, hl <= 64)";
+    case BF_NOALLOC_ERR_SETUP:
+      return "bf_edge_attn_fwd_noalloc: could not resolve the device address of the built-in scratch array";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+  }
+}
