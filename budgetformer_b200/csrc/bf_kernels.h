@@ -127,6 +127,12 @@ int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, long long ld
 int bf_hash_dropout(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, uint32_t seed,
                     float p, int dtype, cudaStream_t st);
 
+// ---- optimizer on flat fp32 buckets (optim.cu) -----------------------------------------------------
+int bf_grad_sumsq(const float* g, long long n, float* out /* += sum g^2 */, cudaStream_t st);
+int bf_adamw_flat(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1, float beta2,
+                  float eps, float weight_decay, int step, const float* sumsq /* or NULL */, float max_norm,
+                  cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -298,6 +298,23 @@ Tensor hash_dropout(Tensor x, int64_t seed, double p) {
   return y;
 }
 
+void grad_sumsq(Tensor g, Tensor out) {
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == torch::kFloat && g.is_contiguous() && out.scalar_type() == torch::kFloat);
+  c10::cuda::CUDAGuard guard(g.device());
+  check_cuda(bf_grad_sumsq(g.data_ptr<float>(), g.numel(), out.data_ptr<float>(), at::cuda::getCurrentCUDAStream()), "grad_sumsq");
+}
+
+void adamw_flat(Tensor p, Tensor g, Tensor m, Tensor v, int64_t n, double lr, double beta1, double beta2, double eps,
+                double wd, int64_t step, OptTensor sumsq, double max_norm) {
+  for (const Tensor* t : {&p, &g, &m, &v})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat && t->is_contiguous() && t->numel() >= n);
+  c10::cuda::CUDAGuard guard(p.device());
+  check_cuda(bf_adamw_flat(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), n, (float)lr,
+                           (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
+                           sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr, (float)max_norm,
+                           at::cuda::getCurrentCUDAStream()), "adamw_flat");
+}
+
 bool gemm_supported(int64_t M, int64_t N, int64_t K) { return bf_gemm_supported((int)M, (int)N, (int)K) != 0; }
 
 }  // namespace
@@ -311,6 +328,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("hash_dropout", &hash_dropout);
+  m.def("grad_sumsq", &grad_sumsq);
+  m.def("adamw_flat", &adamw_flat);
   m.def("peer_barrier", &peer_barrier);
   m.def("allreduce_mean", &allreduce_mean);
   m.def("peer_gather_cols", &peer_gather_cols);

@@ -38,14 +38,15 @@ def build_attn_graph(
     exphormer: bool = False,
     num_threads: int = 0,
     force_spec: bool = False,
+    fanout=None,
 ) -> AttnGraph:
     """Build on whatever device ``topo`` lives on.  ``None`` budgets (unsampled, the legacy
     ``--include_real_edges`` path) and budgets above 32 per side fall back to the specification."""
     br = 0 if not use_real else b_real
     bw = 0 if (not use_rw or walks_per_node <= 0 or walk_length <= 0) else b_rw
-    if force_spec or not native_supported(br, bw, walk_length):
+    if force_spec or fanout or not native_supported(br, bw, walk_length):
         g = build_attn_graph_spec(topo, b_real, b_rw, walks_per_node, walk_length, seed,
-                                  use_real=use_real, use_rw=use_rw, exphormer=exphormer)
+                                  use_real=use_real, use_rw=use_rw, exphormer=exphormer, fanout=fanout)
         return g.to(topo.device) if topo.device.type != "cpu" else g
     from ..ops import _ext
     ext = _ext.load()

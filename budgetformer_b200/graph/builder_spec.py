@@ -89,6 +89,51 @@ def select_per_query(src: np.ndarray, dst: np.ndarray, k: Optional[int], seed: i
     return s[o2], d[o2]
 
 
+def khop_neighbor_candidates(topo: Topology, fanout, seed: int):
+    """``--rw_edge_mode dgl_neighbor``: fan-out k-hop expansion with origin tracking (gt_sp/utils.py:1281-1384).
+    From every node, hop h keeps at most ``fanout[h]`` out-neighbours of each frontier node (-1 = all) and emits
+    ``(reached node -> origin)``.  Neighbour choice is a seeded hash ranking, so it is reproducible on every rank."""
+    n = topo.num_nodes
+    rowptr = topo.out_rowptr.cpu().numpy().astype(np.int64)
+    col = topo.out_col.cpu().numpy().astype(np.int64)
+    deg = np.diff(rowptr)
+    e_src = np.repeat(np.arange(n, dtype=np.int64), deg)
+    origin = np.arange(n, dtype=np.int64)
+    frontier = np.arange(n, dtype=np.int64)
+    srcs, dsts = [], []
+    for h, f in enumerate(fanout):
+        # expand every (origin, frontier) pair along the frontier node's out-edges
+        cnt = deg[frontier]
+        rep_o = np.repeat(origin, cnt)
+        rep_f = np.repeat(frontier, cnt)
+        starts = np.repeat(rowptr[frontier], cnt)
+        within = np.arange(rep_f.size) - np.repeat(np.cumsum(cnt) - cnt, cnt)
+        nbr = col[starts + within]
+        if f is not None and int(f) >= 0:
+            key = edge_hash31(nbr, rep_f, int(seed) + 101 * (h + 1)) ^ (rep_o.astype(np.uint64) * np.uint64(2654435761) & np.uint64(0x7FFFFFFF))
+            pair = rep_o * n + rep_f
+            order = np.lexsort((key, pair))
+            p_sorted = pair[order]
+            new = np.ones(p_sorted.size, dtype=bool)
+            new[1:] = p_sorted[1:] != p_sorted[:-1]
+            first = np.maximum.accumulate(np.where(new, np.arange(p_sorted.size), 0))
+            keep = order[(np.arange(p_sorted.size) - first) < int(f)]
+            rep_o, nbr = rep_o[keep], nbr[keep]
+        uniq = np.unique(rep_o * n + nbr)
+        origin, frontier = uniq // n, uniq % n
+        srcs.append(frontier.copy())
+        dsts.append(origin.copy())
+        if frontier.size == 0:
+            break
+    if not srcs:
+        return np.zeros(0, np.int64), np.zeros(0, np.int64)
+    return np.concatenate(srcs), np.concatenate(dsts)
+
+
+def parse_fanout(text) -> list:
+    return [int(t) for t in str(text).split(",") if t.strip()]
+
+
 def build_attn_graph_spec(
     topo: Topology,
     b_real: Optional[int],
@@ -100,6 +145,7 @@ def build_attn_graph_spec(
     use_real: bool = True,
     use_rw: bool = True,
     exphormer: bool = False,
+    fanout=None,
 ) -> AttnGraph:
     n = topo.num_nodes
     in_rowptr = topo.in_rowptr.cpu().numpy().astype(np.int64)
@@ -110,8 +156,10 @@ def build_attn_graph_spec(
     else:
         rs, rd = np.zeros(0, np.int64), np.zeros(0, np.int64)
     if use_rw and walks_per_node > 0 and walk_length > 0 and (b_rw is None or b_rw > 0):
-        walks = random_walks(topo, walks_per_node, walk_length, seed)
-        ws, wd = rw_candidates(walks)
+        if fanout:
+            ws, wd = khop_neighbor_candidates(topo, fanout, seed)
+        else:
+            ws, wd = rw_candidates(random_walks(topo, walks_per_node, walk_length, seed))
         ws, wd = select_per_query(ws, wd, b_rw, int(seed) + RW_SEED_OFFSET)
     else:
         ws, wd = np.zeros(0, np.int64), np.zeros(0, np.int64)

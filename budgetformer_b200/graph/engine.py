@@ -90,6 +90,10 @@ class EdgeEngine:
         self.virtual_node = self.model == "graphormer" and int(getattr(args, "num_global_node", 0)) > 0
         self.exphormer = self.model == "exphormer"
         self.expander_edges = expander_edges
+        self.fanout = None
+        if str(getattr(args, "rw_edge_mode", "random_walk")) == "dgl_neighbor":
+            from .builder_spec import parse_fanout
+            self.fanout = parse_fanout(getattr(args, "fanout", "10,5"))
         t0 = time.perf_counter()
         self.topo_cpu = Topology.from_edge_index(edge_index_global.cpu(), self.num_nodes)
         if self.device.type == "cuda":
@@ -194,7 +198,7 @@ class EdgeEngine:
     def _build_host(self, seed: int, state: BudgetState) -> AttnGraph:
         g = build_attn_graph(self.topo_cpu, state.b_real, state.b_rw, int(getattr(self.args, "walks_per_node", 0)),
                              state.walk_length, seed, use_real=state.use_real, use_rw=state.use_rw,
-                             exphormer=self.exphormer and self.expander_edges is None)
+                             exphormer=self.exphormer and self.expander_edges is None, fanout=self.fanout)
         graph_totals(g)
         if self.device.type == "cuda":
             for name in ("rowptr", "col", "etype"):
@@ -217,6 +221,8 @@ class EdgeEngine:
         return topo
 
     def _build_device(self, seed: int, state: BudgetState) -> AttnGraph:
+        if self.fanout:                                 # fan-out sampling runs through the CPU specification
+            return self._upload(self._build_host(seed, state))
         topo = self._topology_on_device()
         return build_attn_graph(topo, state.b_real, state.b_rw, int(getattr(self.args, "walks_per_node", 0)),
                                 state.walk_length, seed, use_real=state.use_real, use_rw=state.use_rw,

@@ -1,0 +1,71 @@
+"""AdamW with global-norm clipping on the gradient reducer's flat buckets.
+
+Parameters are re-pointed into one flat fp32 buffer per bucket (their ``.grad`` already lives in the matching
+flat gradient bucket), so a whole optimizer step is: one sum-of-squares kernel and one AdamW kernel per bucket.
+The clip coefficient ``min(1, max_norm / (||g|| + 1e-6))`` is evaluated inside the AdamW kernel from the
+device-resident norm, so the step never synchronises with the host.  Same update rule as
+``torch.optim.AdamW`` preceded by ``clip_grad_norm_`` (main_node_fullgraph_sp.py:1284-1293 in the reference)."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from . import _ext
+
+
+class FlatAdamW(torch.optim.Optimizer):
+    def __init__(self, buckets, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, max_grad_norm: float = 1.0):
+        params = [p for b in buckets for p in b.params]
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.buckets = buckets
+        self.max_grad_norm = float(max_grad_norm)
+        self._step = 0
+        self._flat_p: List[torch.Tensor] = []
+        self._m: List[torch.Tensor] = []
+        self._v: List[torch.Tensor] = []
+        for b in buckets:
+            flat = torch.zeros_like(b.flat)
+            off = 0
+            for p in b.params:
+                n = p.numel()
+                flat[off:off + n].copy_(p.data.reshape(-1))
+                p.data = flat[off:off + n].view_as(p)
+                off += n
+            self._flat_p.append(flat)
+            self._m.append(torch.zeros_like(flat))
+            self._v.append(torch.zeros_like(flat))
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=buckets[0].flat.device)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        ext = _ext.load()
+        self._step += 1
+        g0 = self.param_groups[0]
+        lr, (b1, b2), eps, wd = g0["lr"], g0["betas"], g0["eps"], g0["weight_decay"]
+        clip = self.max_grad_norm > 0
+        if clip:
+            self._sumsq.zero_()
+            for b in self.buckets:
+                ext.grad_sumsq(b.flat, self._sumsq)
+        for b, p, m, v in zip(self.buckets, self._flat_p, self._m, self._v):
+            ext.adamw_flat(p, b.flat, m, v, int(b.n_valid), float(lr), float(b1), float(b2), float(eps), float(wd),
+                           int(self._step), self._sumsq if clip else None, self.max_grad_norm)
+        _ext.count_launches(len(self.buckets) * (2 if clip else 1))
+
+    def grad_norm(self) -> torch.Tensor:
+        """Device tensor holding the global gradient norm of the last step."""
+        return self._sumsq.sqrt()
+
+    def state_dict(self):
+        return {"step": self._step, "m": [t.cpu() for t in self._m], "v": [t.cpu() for t in self._v],
+                "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
+
+    def load_state_dict(self, sd):
+        self._step = int(sd["step"])
+        for dst, src in zip(self._m, sd["m"]):
+            dst.copy_(src)
+        for dst, src in zip(self._v, sd["v"]):
+            dst.copy_(src)
+        for g, s in zip(self.param_groups, sd.get("param_groups", [])):
+            g.update(s)

@@ -140,9 +140,16 @@ class FullGraphTrainer:
         self._configure_fused_sp()
         sync_params_and_buffers(self.model, self.sp_group, self.sp_src)
         self.reducer = build_gradient_reducer(self.model, self.sp_group, 25.0, self.sp_world)
-        self.optimizer = torch.optim.AdamW(self.model.parameters(), lr=args.peak_lr, weight_decay=args.weight_decay)
-        self.lr_scheduler = build_lr_scheduler(args, self.optimizer, self.n_train_global)
         self.scaler = torch.amp.GradScaler("cuda", enabled=(self.amp_dtype == torch.float16 and self.device.type == "cuda"))
+        self.flat_optimizer = False
+        if self.device.type == "cuda" and not self.scaler.is_enabled() and all(
+                b.flat.dtype == torch.float32 for b in self.reducer.buckets):
+            from ..ops.optim import FlatAdamW
+            self.optimizer = FlatAdamW(self.reducer.buckets, lr=args.peak_lr, weight_decay=args.weight_decay, max_grad_norm=1.0)
+            self.flat_optimizer = True
+        else:
+            self.optimizer = torch.optim.AdamW(self.model.parameters(), lr=args.peak_lr, weight_decay=args.weight_decay)
+        self.lr_scheduler = build_lr_scheduler(args, self.optimizer, self.n_train_global)
         self._apply_memory_limit()
         self._apply_forced_plan()
 
@@ -296,6 +303,8 @@ class FullGraphTrainer:
                 torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)
                 self.scaler.step(self.optimizer)
                 self.scaler.update()
+            elif self.flat_optimizer:
+                self.optimizer.step()                      # clipping is fused into the step
             else:
                 torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)
                 self.optimizer.step()

@@ -1,0 +1,70 @@
+import os
+
+import numpy as np
+import torch
+
+from budgetformer_b200.train.data import (GraphData, compute_multihop_features, generate_expander_edges,
+                                          pad_to_sequence_parallel_world, random_split_idx, to_bidirected_edge_index)
+from budgetformer_b200.utils.prepare_snap_patents import even_quantile_labels, prepare_labels
+from budgetformer_b200.utils.preprocess_data import get_dataset, rand_train_test_idx
+from budgetformer_b200.utils.split_utils import load_default_split
+
+
+def test_random_split_is_seeded_60_20_20():
+    a, b = random_split_idx(1000, 42), random_split_idx(1000, 42)
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    assert (a["train"].numel(), a["valid"].numel(), a["test"].numel()) == (600, 200, 200)
+    assert torch.cat(list(a.values())).unique().numel() == 1000
+
+
+def test_padding_and_bidirected():
+    d = GraphData(torch.randn(10, 3), torch.arange(10), torch.tensor([[0, 1], [1, 2]]), random_split_idx(10, 0), 10, 10)
+    p = pad_to_sequence_parallel_world(d, 4)
+    assert p.x.size(0) == 12 and p.y[-1] == -1 and float(p.x[-1].abs().sum()) == 0
+    bi = to_bidirected_edge_index(torch.tensor([[0, 1, 1], [1, 0, 2]]), 3)
+    assert set(map(tuple, bi.t().tolist())) == {(0, 1), (1, 0), (1, 2), (2, 1)}
+
+
+def test_multihop_features_and_expander():
+    ei = torch.tensor([[0, 1, 2], [1, 2, 3]])
+    x = torch.eye(4)
+    mh = compute_multihop_features(ei, 4, x, hops=2, rank=1)
+    assert mh.shape == (4, 3, 4) and torch.allclose(mh[:, 0], x)
+    assert torch.allclose(mh[:, 1].sum(1), mh[:, 1].sum(1))             # finite
+    e = generate_expander_edges(50, 3, seed=1)
+    deg = torch.bincount(e[0], minlength=50)
+    assert int(deg.min()) >= 4 and int(deg.max()) <= 6 and bool((e[0] != e[1]).all())
+
+
+def test_even_quantile_labels_and_cli(tmp_path):
+    vals = np.arange(100, dtype=np.float64)
+    lab = even_quantile_labels(vals, 5)
+    assert np.bincount(lab).tolist() == [20, 20, 20, 20, 20]
+    path = tmp_path / "snap-patents"
+    os.makedirs(path)
+    torch.save(torch.arange(1970, 2070), path / "y.pt")
+    assert prepare_labels(str(path))
+    y = torch.load(path / "y.pt")
+    assert y.unique().tolist() == [0, 1, 2, 3, 4] and (path / "y_raw_year.pt").exists()
+    assert not prepare_labels(str(path))                                  # idempotent
+
+
+def test_split_discovery_layouts(tmp_path):
+    root = tmp_path / "ds"
+    os.makedirs(root / "a")
+    torch.save({"train": torch.tensor([0, 1]), "val": torch.tensor([2]), "test": torch.tensor([3])}, root / "a" / "split_idx.pt")
+    s = load_default_split("a", str(root))
+    assert s["valid"].tolist() == [2]
+    os.makedirs(root / "b")
+    m = torch.zeros(5, 2, dtype=torch.bool); m[1, 1] = True
+    for n in ("train", "val", "test"):
+        torch.save(m, root / "b" / f"{n}_mask.pt")
+    assert load_default_split("b", str(root), split_id=1)["train"].tolist() == [1]
+    assert load_default_split("missing", str(root)) is None
+    sp = rand_train_test_idx(100, seed=3)
+    assert sp["train"].numel() == 50 and sp["valid"].numel() == 25
+
+
+def test_synthetic_dataset_cli(tmp_path):
+    p = get_dataset("synthetic:sbm2k", str(tmp_path))
+    assert torch.load(os.path.join(p, "x.pt")).shape == (2048, 128)

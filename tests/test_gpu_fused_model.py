@@ -72,3 +72,25 @@ def test_fused_path_with_activation_tiers():
     assert abs(float(lt) - float(lu)) < 1e-3
     for pa, pb in zip(t.model.parameters(), u.model.parameters()):
         assert torch.allclose(pa.grad, pb.grad, atol=1e-3 + 0.02 * float(pa.grad.abs().max()))
+
+
+def test_flat_adamw_matches_torch_adamw_with_clipping():
+    from budgetformer_b200.ops.optim import FlatAdamW
+    from budgetformer_b200.parallel.reducer import GradientReducer
+    torch.manual_seed(0)
+    net_a = torch.nn.Sequential(torch.nn.Linear(37, 64), torch.nn.LayerNorm(64), torch.nn.Linear(64, 5)).cuda()
+    net_b = copy.deepcopy(net_a)
+    red = GradientReducer(net_a, None, world_size=1)
+    opt_a = FlatAdamW(red.buckets, lr=3e-3, weight_decay=0.05, max_grad_norm=0.5)
+    opt_b = torch.optim.AdamW(net_b.parameters(), lr=3e-3, weight_decay=0.05)
+    x = torch.randn(256, 37, device="cuda")
+    for _ in range(5):
+        red.prepare_backward()
+        (net_a(x) ** 2).sum().backward()
+        opt_a.step()
+        opt_b.zero_grad()
+        (net_b(x) ** 2).sum().backward()
+        torch.nn.utils.clip_grad_norm_(net_b.parameters(), 0.5)
+        opt_b.step()
+    for pa, pb in zip(net_a.parameters(), net_b.parameters()):
+        assert torch.allclose(pa, pb, atol=2e-6, rtol=2e-5), float((pa - pb).abs().max())
