@@ -200,13 +200,16 @@ void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, 
   p.M = (int)A.size(0); p.N = (int)W.size(0); p.K = (int)A.size(1);
   p.dtype = dtype_code(A);
   if (bias.has_value()) {
-    TORCH_CHECK(bias->scalar_type() == torch::kFloat && bias->is_contiguous() && bias->numel() == p.N);
+    TORCH_CHECK(bias->scalar_type() == torch::kFloat && bias->is_contiguous() && bias->numel() == p.N &&
+                ((uintptr_t)bias->data_ptr()) % 16 == 0, "gemm_tn: bias must be contiguous fp32 [N], 16-byte aligned");
     p.bias = bias->data_ptr<float>();
   }
   p.act = (int)act; p.dropout_p = (float)dropout_p; p.dropout_seed = (uint32_t)seed;
   if (residual.has_value()) {
     TORCH_CHECK(residual->scalar_type() == A.scalar_type() && residual->stride(1) == 1 && residual->size(0) == p.M &&
                 residual->size(1) == p.N && dst_ptrs.size() == 1);
+    TORCH_CHECK(((uintptr_t)residual->data_ptr()) % 16 == 0 && (residual->stride(0) * 2) % 16 == 0,
+                "gemm_tn: residual rows must be 16-byte aligned");
     p.residual = residual->data_ptr(); p.ldr = residual->stride(0);
   }
   if (relu_mask.has_value()) {

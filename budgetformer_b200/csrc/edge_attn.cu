@@ -338,6 +338,58 @@ __device__ __forceinline__ void dq_edge(const BwdArgs& b, int e, int head, int o
   }
 }
 
+// Four edges of one query at a time (see dkv_edge4).
+template <typename T, int HN>
+__device__ __forceinline__ void dq_edge4(const BwdArgs& b, int e, int end, int head, int off, const float* qs0,
+                                         const float* qs1, const float* qraw, const float* dof, float invz, float dterm,
+                                         float* dq, float* de0, float* de1, unsigned hm) {
+  constexpr int VN = Vec<T>::N;
+  constexpr int LPH = HN / VN;
+  const AttnArgs& a = b.f;
+  const float scale = inv_sqrt_hn<HN>();
+  int j[4], ty[4];
+  bool ok[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    ok[u] = e + u < end;
+    j[u] = ok[u] ? __ldg(a.col + e + u) : 0;
+    ty[u] = (a.variant == 2 && ok[u]) ? a.etype[e + u] : 0;
+  }
+  float kf[4][VN], vf[4][VN];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    load_vec<T>(static_cast<const T*>(a.k) + (long long)j[u] * a.ldk + off, kf[u]);
+    load_vec<T>(static_cast<const T*>(a.v) + (long long)j[u] * a.ldv + off, vf[u]);
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    float d = 0.f, dv = 0.f;
+#pragma unroll
+    for (int i = 0; i < VN; ++i) { d += (ty[u] ? qs1[i] : qs0[i]) * kf[u][i]; dv += dof[i] * vf[u][i]; }
+    d = head_sum<LPH>(d, hm);
+    dv = head_sum<LPH>(dv, hm);
+    const bool inr = (d > -kClamp) && (d < kClamp);
+    const float w = ok[u] ? __expf(fminf(fmaxf(d, -kClamp), kClamp)) : 0.f;
+    float mf = 1.f;
+    if (a.variant == 1 && a.thresh) mf = keep_edge(a.seed, (uint32_t)(e + u), (uint32_t)head, a.thresh) ? a.inv_keep : 0.f;
+    else if (a.variant == 1) mf = a.inv_keep;
+    const float ds = inr ? (dv * mf - dterm) * invz * w : 0.f;
+    if (a.variant == 2) {
+      const float* et = a.etab + (ty[u] ? a.hl * HN : 0) + off;
+#pragma unroll
+      for (int i = 0; i < VN; ++i) {
+        dq[i] += ds * scale * kf[u][i] * et[i];
+        const float gg = ds * scale * qraw[i] * kf[u][i];
+        de0[i] += ty[u] ? 0.f : gg;
+        de1[i] += ty[u] ? gg : 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < VN; ++i) dq[i] += ds * scale * kf[u][i];
+    }
+  }
+}
+
 template <typename T, int HN>
 __global__ void __launch_bounds__(256) edge_attn_bwd_q_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
@@ -380,8 +432,8 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_q_kernel(BwdArgs b) {
   const float invz = 1.f / (zsum + kEps);
   if (head_ok && (lt % LPH) == 0) b.zd[(long long)row * a.hl + head] = make_float2(invz, dterm);
   if (hub) end = beg;
-  for (int e = beg; e < end; ++e)
-    dq_edge<T, HN>(b, e, hsafe, off, qs0, qs1, qraw, dof, invz, dterm, dq, de0, de1, hm);
+  for (int e = beg; e < end; e += 4)
+    dq_edge4<T, HN>(b, e, end, hsafe, off, qs0, qs1, qraw, dof, invz, dterm, dq, de0, de1, hm);
   if (head_ok && !hub) store_vec<T>(static_cast<T*>(b.dq) + (long long)row * b.ldg + off, dq);
   if (a.variant == 2) {
     if (head_ok) {
@@ -492,6 +544,64 @@ __device__ __forceinline__ void dkv_edge(const BwdArgs& b, int te, int head, int
   }
 }
 
+// Four transposed edges at a time: all index and row loads are issued before any arithmetic so that a lane group
+// keeps 8 independent 16-byte gathers in flight (the pass is bound by gather latency, not by math).
+template <typename T, int HN>
+__device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int head, int off, const float* kf,
+                                          const float* vf, float* dk, float* dv, unsigned hm) {
+  constexpr int VN = Vec<T>::N;
+  constexpr int LPH = HN / VN;
+  const AttnArgs& a = b.f;
+  const float scale = inv_sqrt_hn<HN>();
+  const int w_row = a.hl * HN;
+  int i_row[4], eid[4];
+  bool ok[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    ok[u] = te + u < end;
+    i_row[u] = ok[u] ? __ldg(b.t_row + te + u) : 0;
+    eid[u] = ok[u] ? __ldg(b.t_eid + te + u) : 0;
+  }
+  float qf[4][VN], dof[4][VN];
+  float2 zd[4];
+  int ty[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    load_vec<T>(static_cast<const T*>(a.q) + (long long)i_row[u] * a.ldq + off, qf[u]);
+    load_vec<T>(static_cast<const T*>(b.dout) + (long long)i_row[u] * w_row + off, dof[u]);
+    zd[u] = __ldg(b.zd + (long long)i_row[u] * a.hl + head);
+    ty[u] = (a.variant == 2 && ok[u]) ? a.etype[eid[u]] : 0;
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    float et[VN];
+    if (a.variant == 2) {
+#pragma unroll
+      for (int i = 0; i < VN; ++i) et[i] = a.etab[(ty[u] ? w_row : 0) + off + i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < VN; ++i) et[i] = 1.f;
+    }
+    float d = 0.f, dotv = 0.f;
+#pragma unroll
+    for (int i = 0; i < VN; ++i) { d += qf[u][i] * kf[i] * et[i]; dotv += dof[u][i] * vf[i]; }
+    d = head_sum<LPH>(d, hm) * scale;
+    dotv = head_sum<LPH>(dotv, hm);
+    const bool inr = (d > -kClamp) && (d < kClamp);
+    const float w = ok[u] ? __expf(fminf(fmaxf(d, -kClamp), kClamp)) : 0.f;
+    float mf = 1.f;
+    if (a.variant == 1 && a.thresh) mf = keep_edge(a.seed, (uint32_t)eid[u], (uint32_t)head, a.thresh) ? a.inv_keep : 0.f;
+    else if (a.variant == 1) mf = a.inv_keep;
+    const float ds = inr ? (dotv * mf - zd[u].y) * zd[u].x * w : 0.f;
+    const float wn = w * mf * zd[u].x;
+#pragma unroll
+    for (int i = 0; i < VN; ++i) {
+      dk[i] += ds * scale * qf[u][i] * et[i];
+      dv[i] += wn * dof[u][i];
+    }
+  }
+}
+
 // dK/dV over the balanced work list: one lane group per (work item, head chunk).
 template <typename T, int HN>
 __global__ void __launch_bounds__(256) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
@@ -521,7 +631,7 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
 #pragma unroll
   for (int i = 0; i < VN; ++i) { dk[i] = 0.f; dv[i] = 0.f; }
   const unsigned hm = head_mask<LPH>();
-  for (int e = beg; e < end; ++e) dkv_edge<T, HN>(b, e, head, off, kf, vf, dk, dv, hm);
+  for (int e = beg; e < end; e += 4) dkv_edge4<T, HN>(b, e, end, head, off, kf, vf, dk, dv, hm);
   if (slot < 0) {
     store_vec<T>(static_cast<T*>(b.dk) + (long long)row * b.ldg + off, dk);
     store_vec<T>(static_cast<T*>(b.dv) + (long long)row * b.ldg + off, dv);

@@ -28,7 +28,7 @@ constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;          // one 128-byte swizzle panel of 16-bit elements
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
-constexpr int NUM_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int NUM_THREADS = 320;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue (two column halves)
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct GemmArgs {
@@ -196,7 +196,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], (g.block_n % 32 == 0) ? 8 : 4); }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -259,79 +259,103 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       if (!ok) { *abort_flag = 1; atomicExch(g.status, 2); }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue warps (2..5)
-    const int quarter = warp & 3;                       // TMEM lane quarter this warp may access
+    // ------------------------------------------------------------------ epilogue warps (2..9)
+    // Warps 2-5 drain the first half of the tile's columns, warps 6-9 the second half (a warp may only touch the
+    // TMEM lane quarter given by warp % 4).  Tiles whose width is not a multiple of 32 use the first group only.
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const bool two_groups = (g.block_n % 32) == 0;
+    const int cols_per_group = two_groups ? g.block_n / 2 : g.block_n;
+    const int col_begin = group * cols_per_group;
+    const bool group_active = two_groups || group == 0;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t thresh = g.dropout_p > 0.f ? (uint32_t)(g.dropout_p * 4294967296.0) : 0u;
     const float keep_scale = g.dropout_p > 0.f ? 1.f / (1.f - g.dropout_p) : 1.f;
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles && ok && group_active; t += gridDim.x) {
       const int m_tile = t / g.n_chunks, n_chunk = t % g.n_chunks;
       if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const long long row = (long long)m_tile * BLOCK_M + row_in_tile;
       const bool row_ok = row < g.M;
       const uint32_t taddr = tmem_base + acc * (uint32_t)g.block_n + ((uint32_t)(quarter * 32) << 16);
-      for (int c0 = 0; c0 < g.block_n; c0 += 16) {
-        uint32_t r[16];
+      for (int c0 = col_begin; c0 < col_begin + cols_per_group; c0 += 32) {
+        // two 16-column loads in flight before one wait
+        uint32_t r[32];
+        const bool second = c0 + 16 < col_begin + cols_per_group;
         tmem_ld_32x32b_x16(taddr + (uint32_t)c0, r);
+        if (second) tmem_ld_32x32b_x16(taddr + (uint32_t)(c0 + 16), r + 16);
         tmem_ld_wait();
         if (!row_ok) continue;
-        const int col0 = n_chunk * g.block_n + c0;
-        float v[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]) * g.out_scale;
-        if (g.bias) {
+        for (int hseg = 0; hseg < 2; ++hseg) {
+          if (hseg == 1 && !second) break;
+          const int col0 = n_chunk * g.block_n + c0 + 16 * hseg;
+          float v[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] += __ldg(g.bias + col0 + i);
-        }
-        if (g.act == 1) {
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[16 * hseg + i]) * g.out_scale;
+          if (g.bias) {
+            const float4* bp = reinterpret_cast<const float4*>(g.bias + col0);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
-        } else if (g.act == 2) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = gelu_erf(v[i]);
-        }
-        if (thresh) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            v[i] = keep_elem(g.dropout_seed, (uint32_t)row, (uint32_t)(col0 + i), thresh) ? v[i] * keep_scale : 0.f;
-        }
-        if (g.relu_mask) {
-          const uint4* mp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.relu_mask) + row * g.ldm + col0);
-          uint4 m0 = __ldg(mp), m1 = __ldg(mp + 1);
-          const unsigned short* ms0 = reinterpret_cast<const unsigned short*>(&m0);
-          const unsigned short* ms1 = reinterpret_cast<const unsigned short*>(&m1);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            // positive and non-zero in either 16-bit float format: sign bit clear and magnitude non-zero
-            if (!((ms0[i] & 0x8000u) == 0 && (ms0[i] & 0x7FFFu) != 0)) v[i] = 0.f;
-            if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
+            for (int i = 0; i < 4; ++i) {
+              const float4 b4 = __ldg(bp + i);
+              v[4 * i] += b4.x; v[4 * i + 1] += b4.y; v[4 * i + 2] += b4.z; v[4 * i + 3] += b4.w;
+            }
           }
-        }
-        if (g.residual) {
-          const unsigned short* rp = static_cast<const unsigned short*>(g.residual) + row * g.ldr + col0;
+          if (g.act == 1) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] += ld16_as_float(rp + i, g.is_fp16);
-        }
-        // route the 16 columns: they never straddle a destination because cols_per_dest % 16 == 0
-        const int dest = g.n_dest > 1 ? col0 / g.cols_per_dest : 0;
-        const int dcol = g.n_dest > 1 ? col0 - dest * g.cols_per_dest : col0;
-        const long long drow = g.dst_row_offset + row;
-        if (g.out_fp32) {
-          float4* op = reinterpret_cast<float4*>(static_cast<float*>(g.dst[dest]) + drow * g.ldc + dcol);
+            for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+          } else if (g.act == 2) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) op[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        } else {
-          uint4* op = reinterpret_cast<uint4*>(static_cast<unsigned short*>(g.dst[dest]) + drow * g.ldc + dcol);
-          uint4 o0, o1;
-          o0.x = pack2(v[0], v[1], g.is_fp16); o0.y = pack2(v[2], v[3], g.is_fp16);
-          o0.z = pack2(v[4], v[5], g.is_fp16); o0.w = pack2(v[6], v[7], g.is_fp16);
-          o1.x = pack2(v[8], v[9], g.is_fp16); o1.y = pack2(v[10], v[11], g.is_fp16);
-          o1.z = pack2(v[12], v[13], g.is_fp16); o1.w = pack2(v[14], v[15], g.is_fp16);
-          op[0] = o0;
-          op[1] = o1;
+            for (int i = 0; i < 16; ++i) v[i] = gelu_erf(v[i]);
+          }
+          if (thresh) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              v[i] = keep_elem(g.dropout_seed, (uint32_t)row, (uint32_t)(col0 + i), thresh) ? v[i] * keep_scale : 0.f;
+          }
+          if (g.relu_mask) {
+            const uint4* mp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.relu_mask) + row * g.ldm + col0);
+            uint4 m0 = __ldg(mp), m1 = __ldg(mp + 1);
+            const unsigned short* ms0 = reinterpret_cast<const unsigned short*>(&m0);
+            const unsigned short* ms1 = reinterpret_cast<const unsigned short*>(&m1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              // positive in either 16-bit float format: sign bit clear and magnitude non-zero
+              if (!((ms0[i] & 0x8000u) == 0 && (ms0[i] & 0x7FFFu) != 0)) v[i] = 0.f;
+              if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
+            }
+          }
+          if (g.residual) {
+            const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.residual) + row * g.ldr + col0);
+            uint4 r0 = __ldg(rp), r1 = __ldg(rp + 1);
+            const unsigned short* rs0 = reinterpret_cast<const unsigned short*>(&r0);
+            const unsigned short* rs1 = reinterpret_cast<const unsigned short*>(&r1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              v[i] += ld16_as_float(rs0 + i, g.is_fp16);
+              v[8 + i] += ld16_as_float(rs1 + i, g.is_fp16);
+            }
+          }
+          // route the 16 columns: they never straddle a destination because cols_per_dest % 16 == 0
+          const int dest = g.n_dest > 1 ? col0 / g.cols_per_dest : 0;
+          const int dcol = g.n_dest > 1 ? col0 - dest * g.cols_per_dest : col0;
+          const long long drow = g.dst_row_offset + row;
+          if (g.out_fp32) {
+            float4* op = reinterpret_cast<float4*>(static_cast<float*>(g.dst[dest]) + drow * g.ldc + dcol);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) op[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else {
+            uint4* op = reinterpret_cast<uint4*>(static_cast<unsigned short*>(g.dst[dest]) + drow * g.ldc + dcol);
+            uint4 o0, o1;
+            o0.x = pack2(v[0], v[1], g.is_fp16); o0.y = pack2(v[2], v[3], g.is_fp16);
+            o0.z = pack2(v[4], v[5], g.is_fp16); o0.w = pack2(v[6], v[7], g.is_fp16);
+            o1.x = pack2(v[8], v[9], g.is_fp16); o1.y = pack2(v[10], v[11], g.is_fp16);
+            o1.z = pack2(v[12], v[13], g.is_fp16); o1.w = pack2(v[14], v[15], g.is_fp16);
+            op[0] = o0;
+            op[1] = o1;
+          }
         }
       }
       tc_fence_before();

@@ -38,19 +38,19 @@ __device__ __forceinline__ void ln_load_row(const T* __restrict__ p, int lane, f
   constexpr int BYTES = PER * (int)sizeof(T);
   const T* q = p + lane * PER;
   if constexpr (BYTES % 16 == 0) {
-    T tmp[PER];
+    __align__(16) T tmp[PER];
 #pragma unroll
     for (int j = 0; j < BYTES / 16; ++j) reinterpret_cast<uint4*>(tmp)[j] = reinterpret_cast<const uint4*>(q)[j];
 #pragma unroll
     for (int i = 0; i < PER; ++i) v[i] = to_f<T>(tmp[i]);
   } else if constexpr (BYTES % 8 == 0) {
-    T tmp[PER];
+    __align__(16) T tmp[PER];
 #pragma unroll
     for (int j = 0; j < BYTES / 8; ++j) reinterpret_cast<uint2*>(tmp)[j] = reinterpret_cast<const uint2*>(q)[j];
 #pragma unroll
     for (int i = 0; i < PER; ++i) v[i] = to_f<T>(tmp[i]);
   } else {
-    T tmp[PER];
+    __align__(16) T tmp[PER];
 #pragma unroll
     for (int j = 0; j < BYTES / 4; ++j) reinterpret_cast<uint32_t*>(tmp)[j] = reinterpret_cast<const uint32_t*>(q)[j];
 #pragma unroll
@@ -60,7 +60,7 @@ __device__ __forceinline__ void ln_load_row(const T* __restrict__ p, int lane, f
 template <typename T, int PER>
 __device__ __forceinline__ void ln_store_row(T* __restrict__ p, int lane, const float* v) {
   constexpr int BYTES = PER * (int)sizeof(T);
-  T tmp[PER];
+  __align__(16) T tmp[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) tmp[i] = from_f<T>(v[i]);
   T* q = p + lane * PER;
@@ -208,13 +208,32 @@ template <typename T>
 __global__ void __launch_bounds__(256) hash_dropout_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ y,
                                                            long long ldy, long long rows, int cols, uint32_t seed,
                                                            uint32_t thresh, float scale) {
-  const long long total = rows * cols;
+  // one thread per 8 consecutive columns of a row (2-D indexing: no 64-bit division per element)
+  const int chunks = (cols + 7) / 8;
+  const long long total = rows * chunks;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const long long r = i / cols;
-    const int c = (int)(i - r * cols);
-    const bool keep = mix32((uint32_t)r * 0x9E3779B1u + (uint32_t)c * 0x85EBCA77u + seed) >= thresh;
-    y[r * ldy + c] = from_f<T>(keep ? to_f<T>(x[r * ldx + c]) * scale : 0.f);
+    const long long r = i / chunks;
+    const int c0 = (int)(i - r * chunks) * 8;
+    const uint32_t rh = (uint32_t)r * 0x9E3779B1u + seed;
+    const T* xp = x + r * ldx + c0;
+    T* yp = y + r * ldy + c0;
+    const bool full = c0 + 8 <= cols && sizeof(T) == 2 && ((reinterpret_cast<uintptr_t>(xp) | reinterpret_cast<uintptr_t>(yp)) & 15) == 0;
+    if (full) {
+      __align__(16) T tmp[8];
+      *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(xp);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const bool keep = mix32(rh + (uint32_t)(c0 + k) * 0x85EBCA77u) >= thresh;
+        tmp[k] = from_f<T>(keep ? to_f<T>(tmp[k]) * scale : 0.f);
+      }
+      *reinterpret_cast<uint4*>(yp) = *reinterpret_cast<const uint4*>(tmp);
+    } else {
+      for (int k = 0; k < 8 && c0 + k < cols; ++k) {
+        const bool keep = mix32(rh + (uint32_t)(c0 + k) * 0x85EBCA77u) >= thresh;
+        yp[k] = from_f<T>(keep ? to_f<T>(xp[k]) * scale : 0.f);
+      }
+    }
   }
 }
 
@@ -278,7 +297,7 @@ extern "C" int bf_hash_dropout(const void* x, long long ldx, void* y, long long 
   if (rows * cols == 0) return 0;
   const uint32_t thresh = (uint32_t)(p * 4294967296.0);
   const float scale = 1.f / (1.f - p);
-  long long blocks = (rows * cols + 255) / 256;
+  long long blocks = (rows * ((cols + 7) / 8) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
 #define CALL(T) hash_dropout_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, (T*)y, ldy, rows, cols, seed, thresh, scale)
   BF_DT_SWITCH(dtype, CALL)

@@ -53,7 +53,11 @@ def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         out = torch.empty((m, n), dtype=torch.float32 if fp32_out else a.dtype, device=a.device)
     if m == 0:
         return out
-    ext.gemm_tn(a, w, None if bias is None else bias.float().contiguous(), ACT[act], float(dropout_p), int(dropout_seed),
+    if bias is not None:
+        bias = bias.float().contiguous()
+        if bias.data_ptr() % 16:                      # the epilogue reads the bias with 16-byte loads
+            bias = bias.clone()
+    ext.gemm_tn(a, w, bias, ACT[act], float(dropout_p), int(dropout_seed),
                 residual, relu_mask, float(out_scale), bool(fp32_out), [out.data_ptr()], 0, out.stride(0),
                 status_tensor(a.device))
     _ext.count_launches(1)

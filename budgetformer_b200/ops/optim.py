@@ -26,12 +26,10 @@ class FlatAdamW(torch.optim.Optimizer):
         self._v: List[torch.Tensor] = []
         for b in buckets:
             flat = torch.zeros_like(b.flat)
-            off = 0
-            for p in b.params:
+            for p, off in zip(b.params, b.offsets):
                 n = p.numel()
                 flat[off:off + n].copy_(p.data.reshape(-1))
                 p.data = flat[off:off + n].view_as(p)
-                off += n
             self._flat_p.append(flat)
             self._m.append(torch.zeros_like(flat))
             self._v.append(torch.zeros_like(flat))

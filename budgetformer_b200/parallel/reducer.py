@@ -45,21 +45,24 @@ def sync_params_and_buffers(model: torch.nn.Module, group=None, src: Optional[in
 
 
 class _Bucket:
+    ALIGN = 8                                      # elements: every tensor starts on a 16-byte boundary (fp32/16-bit)
+
     def __init__(self, params: List[torch.nn.Parameter], device, dtype):
         self.params = params
-        n = sum(p.numel() for p in params)
-        self.n_valid = n
-        n_pad = (n + 1023) // 1024 * 1024          # 16-byte multiples for vector loads on every dtype
+        self.offsets = []
+        off = 0
+        for p in params:
+            self.offsets.append(off)
+            off += (p.numel() + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        self.n_valid = off                         # padded slots stay zero and are harmless to reduce / update
+        n_pad = (off + 1023) // 1024 * 1024
         self.flat = torch.zeros(n_pad, dtype=dtype, device=device)
         self.symm = None                           # filled by parallel.symm when available
         self._bind()
 
     def _bind(self):
-        off = 0
-        for p in self.params:
-            n = p.numel()
-            p.grad = self.flat[off:off + n].view_as(p)
-            off += n
+        for p, off in zip(self.params, self.offsets):
+            p.grad = self.flat[off:off + p.numel()].view_as(p)
 
     def rebind_to(self, flat: torch.Tensor):
         flat[: self.flat.numel()].copy_(self.flat)
