@@ -339,7 +339,7 @@ __device__ __forceinline__ void dq_edge(const BwdArgs& b, int e, int head, int o
 }
 
 // Four edges of one query at a time (see dkv_edge4).
-template <typename T, int HN>
+template <typename T, int HN, bool EXPH, int NB>
 __device__ __forceinline__ void dq_edge4(const BwdArgs& b, int e, int end, int head, int off, const float* qs0,
                                          const float* qs1, const float* qraw, const float* dof, float invz, float dterm,
                                          float* dq, float* de0, float* de1, unsigned hm) {
@@ -347,25 +347,25 @@ __device__ __forceinline__ void dq_edge4(const BwdArgs& b, int e, int end, int h
   constexpr int LPH = HN / VN;
   const AttnArgs& a = b.f;
   const float scale = inv_sqrt_hn<HN>();
-  int j[4], ty[4];
-  bool ok[4];
+  int j[NB], ty[NB];
+  bool ok[NB];
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < NB; ++u) {
     ok[u] = e + u < end;
     j[u] = ok[u] ? __ldg(a.col + e + u) : 0;
-    ty[u] = (a.variant == 2 && ok[u]) ? a.etype[e + u] : 0;
+    ty[u] = (EXPH && ok[u]) ? a.etype[e + u] : 0;
   }
-  float kf[4][VN], vf[4][VN];
+  float kf[NB][VN], vf[NB][VN];
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < NB; ++u) {
     load_vec<T>(static_cast<const T*>(a.k) + (long long)j[u] * a.ldk + off, kf[u]);
     load_vec<T>(static_cast<const T*>(a.v) + (long long)j[u] * a.ldv + off, vf[u]);
   }
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < NB; ++u) {
     float d = 0.f, dv = 0.f;
 #pragma unroll
-    for (int i = 0; i < VN; ++i) { d += (ty[u] ? qs1[i] : qs0[i]) * kf[u][i]; dv += dof[i] * vf[u][i]; }
+    for (int i = 0; i < VN; ++i) { d += ((EXPH && ty[u]) ? qs1[i] : qs0[i]) * kf[u][i]; dv += dof[i] * vf[u][i]; }
     d = head_sum<LPH>(d, hm);
     dv = head_sum<LPH>(dv, hm);
     const bool inr = (d > -kClamp) && (d < kClamp);
@@ -374,7 +374,7 @@ __device__ __forceinline__ void dq_edge4(const BwdArgs& b, int e, int end, int h
     if (a.variant == 1 && a.thresh) mf = keep_edge(a.seed, (uint32_t)(e + u), (uint32_t)head, a.thresh) ? a.inv_keep : 0.f;
     else if (a.variant == 1) mf = a.inv_keep;
     const float ds = inr ? (dv * mf - dterm) * invz * w : 0.f;
-    if (a.variant == 2) {
+    if (EXPH) {
       const float* et = a.etab + (ty[u] ? a.hl * HN : 0) + off;
 #pragma unroll
       for (int i = 0; i < VN; ++i) {
@@ -390,14 +390,14 @@ __device__ __forceinline__ void dq_edge4(const BwdArgs& b, int e, int end, int h
   }
 }
 
-template <typename T, int HN>
-__global__ void __launch_bounds__(256) edge_attn_bwd_q_kernel(BwdArgs b) {
+template <typename T, int HN, bool EXPH>
+__global__ void __launch_bounds__(256, 3) edge_attn_bwd_q_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
   constexpr int LPH = HN / VN;
   const AttnArgs& a = b.f;
   extern __shared__ float s_detab[];   // [2, Hl*HN] when exphormer
   const int w_row = a.hl * HN;
-  if (a.variant == 2) {
+  if (EXPH) {
     for (int i = threadIdx.x; i < 2 * w_row; i += blockDim.x) s_detab[i] = 0.f;
     __syncthreads();
   }
@@ -432,10 +432,10 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_q_kernel(BwdArgs b) {
   const float invz = 1.f / (zsum + kEps);
   if (head_ok && (lt % LPH) == 0) b.zd[(long long)row * a.hl + head] = make_float2(invz, dterm);
   if (hub) end = beg;
-  for (int e = beg; e < end; e += 4)
-    dq_edge4<T, HN>(b, e, end, hsafe, off, qs0, qs1, qraw, dof, invz, dterm, dq, de0, de1, hm);
+  for (int e = beg; e < end; e += 2)
+    dq_edge4<T, HN, EXPH, 2>(b, e, end, hsafe, off, qs0, qs1, qraw, dof, invz, dterm, dq, de0, de1, hm);
   if (head_ok && !hub) store_vec<T>(static_cast<T*>(b.dq) + (long long)row * b.ldg + off, dq);
-  if (a.variant == 2) {
+  if (EXPH) {
     if (head_ok) {
 #pragma unroll
       for (int i = 0; i < VN; ++i) {
@@ -546,7 +546,7 @@ __device__ __forceinline__ void dkv_edge(const BwdArgs& b, int te, int head, int
 
 // Four transposed edges at a time: all index and row loads are issued before any arithmetic so that a lane group
 // keeps 8 independent 16-byte gathers in flight (the pass is bound by gather latency, not by math).
-template <typename T, int HN>
+template <typename T, int HN, bool EXPH, int NB>
 __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int head, int off, const float* kf,
                                           const float* vf, float* dk, float* dv, unsigned hm) {
   constexpr int VN = Vec<T>::N;
@@ -554,34 +554,29 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
   const AttnArgs& a = b.f;
   const float scale = inv_sqrt_hn<HN>();
   const int w_row = a.hl * HN;
-  int i_row[4], eid[4];
-  bool ok[4];
+  int i_row[NB], eid[NB];
+  bool ok[NB];
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < NB; ++u) {
     ok[u] = te + u < end;
     i_row[u] = ok[u] ? __ldg(b.t_row + te + u) : 0;
     eid[u] = ok[u] ? __ldg(b.t_eid + te + u) : 0;
   }
-  float qf[4][VN], dof[4][VN];
-  float2 zd[4];
-  int ty[4];
+  float qf[NB][VN], dof[NB][VN];
+  float2 zd[NB];
+  int ty[NB];
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < NB; ++u) {
     load_vec<T>(static_cast<const T*>(a.q) + (long long)i_row[u] * a.ldq + off, qf[u]);
     load_vec<T>(static_cast<const T*>(b.dout) + (long long)i_row[u] * w_row + off, dof[u]);
     zd[u] = __ldg(b.zd + (long long)i_row[u] * a.hl + head);
-    ty[u] = (a.variant == 2 && ok[u]) ? a.etype[eid[u]] : 0;
+    ty[u] = (EXPH && ok[u]) ? a.etype[eid[u]] : 0;
   }
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < NB; ++u) {
     float et[VN];
-    if (a.variant == 2) {
 #pragma unroll
-      for (int i = 0; i < VN; ++i) et[i] = a.etab[(ty[u] ? w_row : 0) + off + i];
-    } else {
-#pragma unroll
-      for (int i = 0; i < VN; ++i) et[i] = 1.f;
-    }
+    for (int i = 0; i < VN; ++i) et[i] = EXPH ? a.etab[(ty[u] ? w_row : 0) + off + i] : 1.f;
     float d = 0.f, dotv = 0.f;
 #pragma unroll
     for (int i = 0; i < VN; ++i) { d += qf[u][i] * kf[i] * et[i]; dotv += dof[u][i] * vf[i]; }
@@ -603,8 +598,8 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
 }
 
 // dK/dV over the balanced work list: one lane group per (work item, head chunk).
-template <typename T, int HN>
-__global__ void __launch_bounds__(256) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
+template <typename T, int HN, bool EXPH>
+__global__ void __launch_bounds__(256, 3) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
   constexpr int LPH = HN / VN;
   const AttnArgs& a = b.f;
@@ -631,7 +626,7 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
 #pragma unroll
   for (int i = 0; i < VN; ++i) { dk[i] = 0.f; dv[i] = 0.f; }
   const unsigned hm = head_mask<LPH>();
-  for (int e = beg; e < end; e += 4) dkv_edge4<T, HN>(b, e, end, head, off, kf, vf, dk, dv, hm);
+  for (int e = beg; e < end; e += 2) dkv_edge4<T, HN, EXPH, 2>(b, e, end, head, off, kf, vf, dk, dv, hm);
   if (slot < 0) {
     store_vec<T>(static_cast<T*>(b.dk) + (long long)row * b.ldg + off, dk);
     store_vec<T>(static_cast<T*>(b.dv) + (long long)row * b.ldg + off, dv);
@@ -769,7 +764,10 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
   const long long blocks = (warps + 7) / 8;
   const int w_row = a.hl * HN;
   const size_t smem = a.variant == 2 ? sizeof(float) * 2 * w_row : 0;
-  if (blocks > 0) edge_attn_bwd_q_kernel<T, HN><<<(unsigned)blocks, 256, smem, st>>>(b);
+  if (blocks > 0) {
+    if (a.variant == 2) edge_attn_bwd_q_kernel<T, HN, true><<<(unsigned)blocks, 256, smem, st>>>(b);
+    else edge_attn_bwd_q_kernel<T, HN, false><<<(unsigned)blocks, 256, smem, st>>>(b);
+  }
   if (a.n_hub > 0) {
     edge_attn_bwd_q_hub_kernel<T, HN><<<a.n_hub * chunks_q, 256, 0, st>>>(b, chunks_q);
     hub_scatter_rows<T><<<a.n_hub, 256, 0, st>>>(b.hub_scratch_q, w_row, 0, a.hub_rows, static_cast<T*>(b.dq), w_row, b.ldg);
@@ -778,7 +776,10 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
     const long long kv_tasks = (long long)b.n_kv_task * g.n_hc;
     const long long kv_warps = (kv_tasks + tpw - 1) / tpw;
     const long long kv_blocks = (kv_warps + 7) / 8;
-    if (kv_blocks > 0) edge_attn_bwd_kv_task_kernel<T, HN><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+    if (kv_blocks > 0) {
+      if (a.variant == 2) edge_attn_bwd_kv_task_kernel<T, HN, true><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      else edge_attn_bwd_kv_task_kernel<T, HN, false><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+    }
     if (b.n_kv_split > 0) edge_attn_bwd_kv_reduce_kernel<T><<<b.n_kv_split, 256, 0, st>>>(b, w_row);
     return cudaGetLastError();
   }
