@@ -124,6 +124,8 @@ int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma, const flo
 int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* stats,
                      const float* gamma, void* dx, long long lddx, float* dgamma /* += */, float* dbeta /* += */,
                      long long rows, int h, int dtype, cudaStream_t st);
+int bf_colsum(const void* x, long long ldx, long long rows, int cols /* % 8 == 0 */, float* out /* += */, int dtype,
+              cudaStream_t st);
 int bf_hash_dropout(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, uint32_t seed,
                     float p, int dtype, cudaStream_t st);
 

@@ -292,6 +292,15 @@ std::vector<Tensor> layernorm_bwd(Tensor dy, Tensor x, Tensor stats, Tensor gamm
   return {dx, dgamma, dbeta};
 }
 
+Tensor colsum(Tensor x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::zeros({x.size(1)}, x.options().dtype(torch::kFloat));
+  check_cuda(bf_colsum(x.data_ptr(), x.stride(0), x.size(0), (int)x.size(1), out.data_ptr<float>(), dtype_code(x),
+                       at::cuda::getCurrentCUDAStream()), "colsum");
+  return out;
+}
+
 Tensor hash_dropout(Tensor x, int64_t seed, double p) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1);
   c10::cuda::CUDAGuard guard(x.device());
@@ -331,6 +340,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("hash_dropout", &hash_dropout);
+  m.def("colsum", &colsum);
   m.def("grad_sumsq", &grad_sumsq);
   m.def("adamw_flat", &adamw_flat);
   m.def("peer_barrier", &peer_barrier);

@@ -643,9 +643,16 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_reduce_kernel(BwdArgs b,
   const int s = blockIdx.x;
   const int row = b.kv_split[3 * s], first = b.kv_split[3 * s + 1], n = b.kv_split[3 * s + 2];
   for (int c = threadIdx.x; c < 2 * w_row; c += blockDim.x) {
-    float acc = 0.f;
+    // eight independent partial sums keep eight loads in flight (hub keys own thousands of slots)
+    float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const float* pp = b.kv_partial + (long long)first * 2 * w_row + c;
-    for (int j = 0; j < n; ++j) acc += pp[(long long)j * 2 * w_row];
+    int j = 0;
+    for (; j + 8 <= n; j += 8) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a8[u] += pp[(long long)(j + u) * 2 * w_row];
+    }
+    for (; j < n; ++j) a8[0] += pp[(long long)j * 2 * w_row];
+    const float acc = ((a8[0] + a8[1]) + (a8[2] + a8[3])) + ((a8[4] + a8[5]) + (a8[6] + a8[7]));
     T* dst = c < w_row ? static_cast<T*>(b.dk) : static_cast<T*>(b.dv);
     dst[(long long)row * b.ldg + (c < w_row ? c : c - w_row)] = from_float<T>(acc);
   }

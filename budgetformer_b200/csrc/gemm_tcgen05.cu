@@ -19,6 +19,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "bf_kernels.h"
 
@@ -27,7 +28,7 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;          // one 128-byte swizzle panel of 16-bit elements
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 4;
 constexpr int NUM_THREADS = 320;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue (two column halves)
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
@@ -53,6 +54,14 @@ struct GemmArgs {
   long long ldc;                 // destination row stride (elements)
   void* dst[BF_MAX_PEERS];
   int* status;                   // [4] device status words (0 = ok)
+  // shared-memory plan (host decides what fits in 227 KB)
+  int stages;                    // operand ring depth (3 or 4)
+  int tma_store;                 // 1: epilogue stages 64-column panels in shared memory and writes them with TMA
+  int out_bufs;                  // staging buffers (1 or 2) when tma_store
+};
+
+struct OutMaps {
+  CUtensorMap m[BF_MAX_PEERS];   // one per destination; row extent = dst_row_offset + M so that tail rows are clipped
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -162,13 +171,26 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int is_fp16) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
 struct __align__(1024) SmemLayout {
   // operand ring follows at offset 0 of the dynamic buffer (A stages then B stages), then this control block
 };
 
 struct Control {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -177,15 +199,18 @@ struct Control {
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                       const GemmArgs g) {
+                       const __grid_constant__ OutMaps omaps, const GemmArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t a_stage_bytes = BLOCK_M * BLOCK_K * 2;
   const uint32_t b_stage_bytes = (uint32_t)g.block_n * BLOCK_K * 2;
+  const int STAGES = g.stages;
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + STAGES * a_stage_bytes;
-  Control* ctl = reinterpret_cast<Control*>(smem_b + STAGES * b_stage_bytes);
+  uint8_t* smem_out = smem_b + STAGES * b_stage_bytes;              // [out_bufs][block_n/64][128 rows][128 B], swizzled
+  const uint32_t out_buf_bytes = g.tma_store ? (uint32_t)(g.block_n / 64) * BLOCK_M * 128u : 0u;
+  Control* ctl = reinterpret_cast<Control*>(smem_out + (size_t)g.out_bufs * out_buf_bytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -224,7 +249,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           mbar_expect_tx(&ctl->full[stage], a_stage_bytes + b_stage_bytes);
           tma_load_2d(smem_a + stage * a_stage_bytes, &map_a, &ctl->full[stage], kp * BLOCK_K, m_tile * BLOCK_M);
           tma_load_2d(smem_b + stage * b_stage_bytes, &map_b, &ctl->full[stage], kp * BLOCK_K, n_chunk * g.block_n);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == (uint32_t)STAGES) { stage = 0; phase ^= 1u; }
         }
       }
       if (!ok) { *abort_flag = 1; atomicExch(g.status, 1); }
@@ -250,7 +275,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             umma_f16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kp > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(&ctl->empty[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == (uint32_t)STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&ctl->tmem_full[acc]);
@@ -272,6 +297,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t thresh = g.dropout_p > 0.f ? (uint32_t)(g.dropout_p * 4294967296.0) : 0u;
     const float keep_scale = g.dropout_p > 0.f ? 1.f / (1.f - g.dropout_p) : 1.f;
     uint32_t acc = 0, acc_phase = 0;
+    int out_sel = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok && group_active; t += gridDim.x) {
       const int m_tile = t / g.n_chunks, n_chunk = t % g.n_chunks;
@@ -280,6 +306,14 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const long long row = (long long)m_tile * BLOCK_M + row_in_tile;
       const bool row_ok = row < g.M;
       const uint32_t taddr = tmem_base + acc * (uint32_t)g.block_n + ((uint32_t)(quarter * 32) << 16);
+      uint8_t* stage_out = smem_out + (size_t)out_sel * out_buf_bytes;
+      if (g.tma_store) {
+        // the staging buffer about to be overwritten must have been read by its previous bulk store
+        if (warp == 2 && lane == 0) {
+          if (g.out_bufs == 2) tma_store_wait_read<1>(); else tma_store_wait_read<0>();
+        }
+        epilogue_bar_sync();
+      }
       for (int c0 = col_begin; c0 < col_begin + cols_per_group; c0 += 32) {
         // two 16-column loads in flight before one wait
         uint32_t r[32];
@@ -287,7 +321,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tmem_ld_32x32b_x16(taddr + (uint32_t)c0, r);
         if (second) tmem_ld_32x32b_x16(taddr + (uint32_t)(c0 + 16), r + 16);
         tmem_ld_wait();
-        if (!row_ok) continue;
+        if (!row_ok && !g.tma_store) continue;
 #pragma unroll
         for (int hseg = 0; hseg < 2; ++hseg) {
           if (hseg == 1 && !second) break;
@@ -315,7 +349,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             for (int i = 0; i < 16; ++i)
               v[i] = keep_elem(g.dropout_seed, (uint32_t)row, (uint32_t)(col0 + i), thresh) ? v[i] * keep_scale : 0.f;
           }
-          if (g.relu_mask) {
+          if (g.relu_mask && row_ok) {
             const uint4* mp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.relu_mask) + row * g.ldm + col0);
             uint4 m0 = __ldg(mp), m1 = __ldg(mp + 1);
             const unsigned short* ms0 = reinterpret_cast<const unsigned short*>(&m0);
@@ -327,7 +361,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
             }
           }
-          if (g.residual) {
+          if (g.residual && row_ok) {
             const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.residual) + row * g.ldr + col0);
             uint4 r0 = __ldg(rp), r1 = __ldg(rp + 1);
             const unsigned short* rs0 = reinterpret_cast<const unsigned short*>(&r0);
@@ -337,6 +371,20 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               v[i] += ld16_as_float(rs0 + i, g.is_fp16);
               v[8 + i] += ld16_as_float(rs1 + i, g.is_fp16);
             }
+          }
+          if (g.tma_store) {
+            // 16-bit result into the swizzled staging panel: 16-byte chunk c of row r lives at chunk (c ^ (r & 7))
+            const int ct = c0 + 16 * hseg;                       // column inside the tile
+            uint8_t* panel = stage_out + (size_t)(ct >> 6) * (BLOCK_M * 128) + (size_t)row_in_tile * 128;
+            const int ch = (ct & 63) >> 3;
+            uint4 o0, o1;
+            o0.x = pack2(v[0], v[1], g.is_fp16); o0.y = pack2(v[2], v[3], g.is_fp16);
+            o0.z = pack2(v[4], v[5], g.is_fp16); o0.w = pack2(v[6], v[7], g.is_fp16);
+            o1.x = pack2(v[8], v[9], g.is_fp16); o1.y = pack2(v[10], v[11], g.is_fp16);
+            o1.z = pack2(v[12], v[13], g.is_fp16); o1.w = pack2(v[14], v[15], g.is_fp16);
+            *reinterpret_cast<uint4*>(panel + ((ch ^ (row_in_tile & 7)) << 4)) = o0;
+            *reinterpret_cast<uint4*>(panel + (((ch + 1) ^ (row_in_tile & 7)) << 4)) = o1;
+            continue;
           }
           // route the 16 columns: they never straddle a destination because cols_per_dest % 16 == 0
           const int dest = g.n_dest > 1 ? col0 / g.cols_per_dest : 0;
@@ -361,8 +409,25 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+      if (g.tma_store) {
+        fence_async_smem();                                  // generic-proxy writes -> visible to the bulk copy engine
+        epilogue_bar_sync();
+        if (warp == 2 && lane == 0) {
+          const int tile_col0 = n_chunk * g.block_n;
+          const int y = (int)(g.dst_row_offset + (long long)m_tile * BLOCK_M);
+          for (int pnl = 0; pnl < g.block_n / 64; ++pnl) {
+            const int gc = tile_col0 + pnl * 64;
+            const int dest = g.n_dest > 1 ? gc / g.cols_per_dest : 0;
+            const int dcol = g.n_dest > 1 ? gc - dest * g.cols_per_dest : gc;
+            tma_store_2d(&omaps.m[dest], stage_out + (size_t)pnl * (BLOCK_M * 128), dcol, y);
+          }
+          tma_store_commit();
+        }
+        if (g.out_bufs == 2) out_sel ^= 1;
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (g.tma_store && warp == 2 && lane == 0) tma_store_wait_all();
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(g.status, 3); }
   }
 
@@ -450,7 +515,32 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   CUtensorMap map_a, map_b;
   if (make_map(&map_a, p->A, p->M, p->K, p->lda, BLOCK_M, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
   if (make_map(&map_b, p->B, p->N, p->K, p->ldb, g.block_n, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
-  const size_t smem = 1024 + STAGES * (BLOCK_M * BLOCK_K * 2 + (size_t)g.block_n * BLOCK_K * 2) + sizeof(Control) + 64;
+  // ---- shared-memory plan -------------------------------------------------------------------------
+  const size_t stage_bytes = (size_t)BLOCK_M * BLOCK_K * 2 + (size_t)g.block_n * BLOCK_K * 2;
+  const size_t out_bytes = (size_t)g.block_n * 256;                       // block_n/64 panels of 128 rows x 128 bytes
+  const size_t budget = 227 * 1024 - 1024 /*alignment slack*/ - sizeof(Control) - 64;
+  bool tma_ok = !p->out_fp32 && g.block_n % 64 == 0 && (p->n_dest == 1 || cols_per_dest % 64 == 0) &&
+                (p->ldc * 2) % 16 == 0;
+  for (int i = 0; i < p->n_dest && tma_ok; ++i) tma_ok = ((uintptr_t)p->dst[i]) % 16 == 0;
+  g.tma_store = 0; g.out_bufs = 0; g.stages = MAX_STAGES;
+  if (tma_ok) {
+    const int plans[4][2] = {{4, 2}, {3, 2}, {4, 1}, {3, 1}};
+    for (const auto& pl : plans) {
+      if (pl[0] * stage_bytes + pl[1] * out_bytes <= budget) { g.stages = pl[0]; g.out_bufs = pl[1]; g.tma_store = 1; break; }
+    }
+  }
+  OutMaps omaps;
+  memset(&omaps, 0, sizeof(omaps));
+  if (g.tma_store) {
+    for (int d = 0; d < p->n_dest; ++d) {
+      // rows beyond this call's region are out of range for the map, so the tail of the last row tile is clipped
+      if (make_map(&omaps.m[d], p->dst[d], p->dst_row_offset + p->M, cols_per_dest, p->ldc, BLOCK_M, g.is_fp16) != 0) {
+        g.tma_store = 0; g.out_bufs = 0; g.stages = MAX_STAGES;
+        break;
+      }
+    }
+  }
+  const size_t smem = 1024 + g.stages * stage_bytes + (size_t)g.out_bufs * out_bytes + sizeof(Control) + 64;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -462,6 +552,6 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int total = g.m_tiles * g.n_chunks;
   const int grid = total < sms ? total : sms;
-  gemm_tn_tcgen05_kernel<<<grid, NUM_THREADS, smem, st>>>(map_a, map_b, g);
+  gemm_tn_tcgen05_kernel<<<grid, NUM_THREADS, smem, st>>>(map_a, map_b, omaps, g);
   return (int)cudaGetLastError();
 }

@@ -237,6 +237,42 @@ __global__ void __launch_bounds__(256) hash_dropout_kernel(const T* __restrict__
   }
 }
 
+// out[c] += sum_r x[r, c] (fp32 accumulation): bias gradients without an fp32 copy of the activation gradient.
+// Each thread owns 8 consecutive columns and strides over rows; partials meet in shared memory, then one atomic
+// per column and block.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ x, long long ldx, long long rows, int cols,
+                                                     float* __restrict__ out) {
+  extern __shared__ float s_sum[];            // [cols]
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) s_sum[i] = 0.f;
+  __syncthreads();
+  const int chunks = cols / 8;
+  const int row_lanes = blockDim.x / chunks;  // threads that share one column chunk
+  const int chunk = threadIdx.x % chunks;
+  const int rl = threadIdx.x / chunks;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  if (rl < row_lanes) {
+    const long long rstride = (long long)gridDim.x * row_lanes;
+    for (long long r = (long long)blockIdx.x * row_lanes + rl; r < rows; r += rstride) {
+      __align__(16) T tmp[8];
+      if (sizeof(T) == 2) {
+        *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(x + r * ldx + chunk * 8);
+      } else {
+        reinterpret_cast<uint4*>(tmp)[0] = reinterpret_cast<const uint4*>(x + r * ldx + chunk * 8)[0];
+        reinterpret_cast<uint4*>(tmp)[1] = reinterpret_cast<const uint4*>(x + r * ldx + chunk * 8)[1];
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += to_f<T>(tmp[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) atomicAdd(&s_sum[chunk * 8 + k], acc[k]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) atomicAdd(out + i, s_sum[i]);
+}
+
 }  // namespace
 
 #define BF_DT_SWITCH(DT, CALL)                                          \
@@ -269,7 +305,7 @@ extern "C" int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma
   if (h > 32 * LN_MAX_PER_LANE || h < 1) return (int)cudaErrorInvalidValue;
   if (rows == 0) return 0;
   long long blocks = (rows * 32 + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > 148 * 64) blocks = 148 * 64;      // many short-lived warps hide the row-load latency better than a few long ones
   const int per = ln_packed_ok(h, dtype, x, ldx, y, ldy) ? h / 32 : 0;
 #define CALL(T) BF_LN_PER_SWITCH(T, per, (ln_fwd_kernel<T, P_><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, gamma, beta, (T*)y, ldy, stats, rows, h, eps)))
   BF_DT_SWITCH(dtype, CALL)
@@ -283,7 +319,7 @@ extern "C" int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, l
   if (h > 32 * LN_MAX_PER_LANE || h < 1) return (int)cudaErrorInvalidValue;
   if (rows == 0) return 0;
   long long blocks = (rows * 32 + 255) / 256;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > 148 * 8) blocks = 148 * 8;
   const size_t smem = sizeof(float) * 2 * h;
   const int per = (ln_packed_ok(h, dtype, x, ldx, dy, lddy) && ln_packed_ok(h, dtype, dx, lddx, dx, lddx)) ? h / 32 : 0;
 #define CALL(T) BF_LN_PER_SWITCH(T, per, (ln_bwd_kernel<T, P_><<<(unsigned)blocks, 256, smem, st>>>((const T*)dy, lddy, (const T*)x, ldx, stats, gamma, (T*)dx, lddx, dgamma, dbeta, rows, h)))
@@ -300,6 +336,24 @@ extern "C" int bf_hash_dropout(const void* x, long long ldx, void* y, long long 
   long long blocks = (rows * ((cols + 7) / 8) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
 #define CALL(T) hash_dropout_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, (T*)y, ldy, rows, cols, seed, thresh, scale)
+  BF_DT_SWITCH(dtype, CALL)
+#undef CALL
+  return (int)cudaGetLastError();
+}
+
+extern "C" int bf_colsum(const void* x, long long ldx, long long rows, int cols, float* out, int dtype, cudaStream_t st) {
+  const int esz = dtype == BF_FP32 ? 4 : 2;
+  if (cols % 8 != 0 || cols > 2048 || cols < 8 || ((uintptr_t)x) % 16 != 0 || (ldx * esz) % 16 != 0)
+    return (int)cudaErrorInvalidValue;
+  if (rows == 0) return 0;
+  const int chunks = cols / 8;
+  if (chunks > 256) return (int)cudaErrorInvalidValue;
+  const int row_lanes = 256 / chunks;
+  long long blocks = (rows + row_lanes * 16 - 1) / (row_lanes * 16);
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  const size_t smem = sizeof(float) * cols;
+#define CALL(T) colsum_kernel<T><<<(unsigned)blocks, 256, smem, st>>>((const T*)x, ldx, rows, cols, out)
   BF_DT_SWITCH(dtype, CALL)
 #undef CALL
   return (int)cudaGetLastError();

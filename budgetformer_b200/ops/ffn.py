@@ -13,7 +13,7 @@ import torch
 import torch.nn.functional as F
 
 from . import gemm
-from .norm import hash_dropout, new_seed
+from .norm import column_sum, hash_dropout, new_seed
 
 
 class _FusedFFNRelu(torch.autograd.Function):
@@ -37,8 +37,8 @@ class _FusedFFNRelu(torch.autograd.Function):
         dx = gemm.gemm_tn(dh, w1h.t().contiguous())
         dw2 = torch.matmul(g2.t(), h).to(wdtype)
         dw1 = torch.matmul(dh.t(), x).to(wdtype)
-        db2 = torch.sum(g2, dim=0, dtype=torch.float32).to(wdtype) if has_b2 else None
-        db1 = torch.sum(dh, dim=0, dtype=torch.float32).to(wdtype) if has_b1 else None
+        db2 = column_sum(g2).to(wdtype) if has_b2 else None
+        db1 = column_sum(dh).to(wdtype) if has_b1 else None
         return dx, dw1, db1, dw2, db2, (dy if has_res else None), None, None, None, None
 
 

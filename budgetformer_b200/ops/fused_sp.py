@@ -31,7 +31,7 @@ from ..parallel import symm
 from . import _ext, gemm
 from .edge_attention import _VARIANTS
 from .ffn import fused_ffn
-from .norm import hash_dropout, layer_norm, new_seed
+from .norm import column_sum, hash_dropout, layer_norm, new_seed
 
 
 class SPContext:
@@ -113,7 +113,7 @@ class _QKVPush(torch.autograd.Function):
         dw = torch.matmul(dloc.t(), x).float()[sp.inv_perm]
         dwq, dwk, dwv = (t.to(ctx.wdtype) for t in dw.split(sp.h, 0))
         if ctx.has_bias:
-            db = torch.sum(dloc, dim=0, dtype=torch.float32)[sp.inv_perm]
+            db = column_sum(dloc)[sp.inv_perm]
             dbq, dbk, dbv = (t.to(ctx.wdtype) for t in db.split(sp.h, 0))
         else:
             dbq = dbk = dbv = None
@@ -220,7 +220,7 @@ class _CtxPullOutProj(torch.autograd.Function):
             # d(context) = (g W_o) [* pre-dropout mask], pushed to the head owners by the GEMM epilogue
             _push_gemm(g, w.t().contiguous(), None, dbuf.ptrs, sp.row0, sp.hl, dropout_p=p_pre, seed=seed_pre)
             dw = torch.matmul(g.t(), a).to(wdtype)
-            db = torch.sum(g, dim=0, dtype=torch.float32).to(wdtype) if has_b else None
+            db = column_sum(g).to(wdtype) if has_b else None
         else:
             da = hash_dropout(g, seed_pre, p_pre) if p_pre > 0 else g
             esz = da.element_size()

@@ -88,14 +88,14 @@ class _FusedLinear(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from .norm import hash_dropout
+        from .norm import column_sum, hash_dropout
         x, w16 = ctx.saved_tensors
         has_res, p, seed, wdtype, has_bias = ctx.cfg
         dy = dy.contiguous()
         g = hash_dropout(dy, seed, p) if p > 0 else dy
         dx = gemm_tn(g, w16.t().contiguous())            # dx = g @ W, expressed as g @ (W^T)^T
         dw = torch.matmul(g.t(), x).to(wdtype)
-        db = torch.sum(g, dim=0, dtype=torch.float32).to(wdtype) if has_bias else None
+        db = column_sum(g).to(wdtype) if has_bias else None
         return dx, dw, db, (dy if has_res else None), None, None
 
 

@@ -68,3 +68,13 @@ def hash_dropout(x: torch.Tensor, seed: int, p: float) -> torch.Tensor:
 def new_seed() -> int:
     """31-bit seed from torch's CPU generator (reproducible under ``torch.manual_seed``, no device sync)."""
     return int(torch.randint(0, 2 ** 31 - 1, (1,)).item())
+
+
+def column_sum(x: torch.Tensor) -> torch.Tensor:
+    """fp32 column sums of a 2-D tensor (bias gradients) without materialising an fp32 copy."""
+    if x.is_cuda and x.dim() == 2 and x.stride(1) == 1 and x.size(1) % 8 == 0 and 8 <= x.size(1) <= 2048 \
+            and x.data_ptr() % 16 == 0 and (x.stride(0) * x.element_size()) % 16 == 0 \
+            and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        _ext.count_launches(1)
+        return _ext.load().colsum(x)
+    return torch.sum(x, dim=0, dtype=torch.float32)

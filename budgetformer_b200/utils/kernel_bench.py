@@ -1,0 +1,173 @@
+"""Microbenchmarks of the package's kernels against the measured roofline of the machine.
+
+    python -m budgetformer_b200.utils.kernel_bench gemm --m 2923922 --n 384 --k 128
+    python -m budgetformer_b200.utils.kernel_bench attn --nodes 2923922 --heads 8 --head_dim 16 --degree 8
+    python -m budgetformer_b200.utils.kernel_bench ln --rows 2923922 --hidden 128
+    python -m budgetformer_b200.utils.kernel_bench build --nodes 2923922 --edges 13975788
+
+Each case runs ``--warmup`` untimed and ``--iters`` timed launches bracketed by CUDA events on the launching
+stream, with operands larger than the 126 MB L2 (or ``--flush_l2``), and prints one JSON line: milliseconds,
+algorithmic bytes / FLOPs, achieved GB/s / TFLOP/s and their fraction of the copy bandwidth and bf16 GEMM rate
+in ``MEASURED_PEAKS.json`` (fallback 6650 GB/s, 1590 TFLOP/s when the file is absent).  ``--once`` launches every
+kernel of the case a single time after warm-up (for profilers)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def timed(fn, warmup, iters, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tot = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        tot += s.elapsed_time(e)
+    return tot / max(1, iters)
+
+
+def report(name, ms, nbytes, flops, extra):
+    bw, tf, src = peaks()
+    gbs = nbytes / ms / 1e6
+    tfl = flops / ms / 1e9
+    rec = {"kernel": name, "ms": round(ms, 4), "bytes": int(nbytes), "flops": int(flops), "GBps": round(gbs, 1),
+           "TFLOPs": round(tfl, 2), "frac_hbm": round(gbs / bw, 3), "frac_bf16": round(tfl / tf, 3), "peaks": src}
+    rec.update(extra)
+    print(json.dumps(rec), flush=True)
+
+
+def case_gemm(a):
+    from ..ops import gemm
+    dev = "cuda"
+    x = torch.randn(a.m, a.k, device=dev).bfloat16()
+    w = (torch.randn(a.n, a.k, device=dev) * 0.05).bfloat16()
+    bias = torch.zeros(a.n, device=dev)
+    res = torch.randn(a.m, a.n, device=dev).bfloat16() if a.residual else None
+    out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+    fn = lambda: gemm.gemm_tn(x, w, bias, a.act or None, residual=res, out=out)
+    ms = timed(fn, a.warmup, 1 if a.once else a.iters)
+    nbytes = 2 * (a.m * a.k + a.n * a.k + a.m * a.n * (2 if a.residual else 1))
+    report("gemm_tn_tcgen05", ms, nbytes, 2.0 * a.m * a.n * a.k, {"m": a.m, "n": a.n, "k": a.k})
+    if a.compare:
+        ms2 = timed(lambda: torch.nn.functional.linear(x, w, bias.bfloat16()), a.warmup, a.iters)
+        report("cublas_linear", ms2, nbytes, 2.0 * a.m * a.n * a.k, {"m": a.m, "n": a.n, "k": a.k})
+    gemm.check_status(dev)
+
+
+def _graph(nodes, degree, seed=0):
+    from ..graph.attn_graph import AttnGraph
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    col = torch.randint(0, nodes, (nodes * degree,), device="cuda", generator=g, dtype=torch.int32)
+    rowptr = torch.arange(0, nodes * degree + 1, degree, device="cuda", dtype=torch.int32)
+    return AttnGraph(nodes, rowptr, col, None, max_degree=degree).ensure_transpose()
+
+
+def case_attn(a):
+    from ..ops.edge_attention import edge_attention
+    n, hl, hn = a.nodes, a.heads, a.head_dim
+    g = _graph(n, a.degree)
+    qkv = torch.randn(n, 3, hl, hn, device="cuda").bfloat16()
+    q, k, v = (qkv[:, i].detach().requires_grad_(True) for i in range(3))
+    e = n * a.degree
+    w = hl * hn * 2
+    fwd = lambda: edge_attention(q, k, v, g)
+    ms = timed(fwd, a.warmup, 1 if a.once else a.iters)
+    report("edge_attn_fwd", ms, e * (2 * w + 4) + n * 2 * w, 4.0 * e * hl * hn, {"nodes": n, "edges": e, "hl": hl, "hn": hn})
+    out = fwd()
+    dout = torch.randn_like(out)
+    def bwd():
+        q.grad = k.grad = v.grad = None
+        out.backward(dout, retain_graph=True)
+    ms = timed(bwd, a.warmup, 1 if a.once else a.iters)
+    report("edge_attn_bwd(q+kv passes)", ms, 2 * e * (2 * w + 12) + n * 8 * w, 12.0 * e * hl * hn,
+           {"nodes": n, "edges": e, "hl": hl, "hn": hn})
+
+
+def case_ln(a):
+    from ..ops.norm import layer_norm
+    x = torch.randn(a.rows, a.hidden, device="cuda").bfloat16().requires_grad_(True)
+    ln = torch.nn.LayerNorm(a.hidden).cuda()
+    fwd = lambda: layer_norm(x, ln.weight, ln.bias, ln.eps)
+    ms = timed(fwd, a.warmup, 1 if a.once else a.iters)
+    report("ln_fwd", ms, 4 * a.rows * a.hidden, 0, {"rows": a.rows, "h": a.hidden})
+    y = fwd()
+    dy = torch.randn_like(y)
+    def bwd():
+        x.grad = None
+        y.backward(dy, retain_graph=True)
+    ms = timed(bwd, a.warmup, 1 if a.once else a.iters)
+    report("ln_bwd", ms, 6 * a.rows * a.hidden, 0, {"rows": a.rows, "h": a.hidden})
+
+
+def case_build(a):
+    from ..graph.attn_graph import Topology
+    from ..graph.builder import build_attn_graph
+    from ..graph.synthetic import citation_dag_edges
+    ei = citation_dag_edges(a.nodes, a.edges, seed=1)
+    topo = Topology.from_edge_index(ei, a.nodes).to("cuda")
+    seeds = iter(range(10 ** 6))
+    fn = lambda: build_attn_graph(topo, a.b_real, a.b_rw, a.walks, a.walk_len, next(seeds))
+    ms = timed(fn, a.warmup, 1 if a.once else a.iters)
+    g = fn()
+    report("budget_select+ell_to_csr", ms, topo.nbytes() + g.nbytes(), 0, {"nodes": a.nodes, "raw_edges": int(ei.size(1)),
+                                                                             "graph_edges": g.num_edges})
+    ms = timed(lambda: build_attn_graph(topo, a.b_real, a.b_rw, a.walks, a.walk_len, 7).ensure_transpose(), a.warmup, a.iters)
+    report("build+transpose+kv_tasks", ms, 0, 0, {"nodes": a.nodes})
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="case", required=True)
+    common = dict(warmup=3, iters=10)
+    for name in ("gemm", "attn", "ln", "build"):
+        p = sub.add_parser(name)
+        p.add_argument("--warmup", type=int, default=common["warmup"])
+        p.add_argument("--iters", type=int, default=common["iters"])
+        p.add_argument("--once", action="store_true")
+        if name == "gemm":
+            p.add_argument("--m", type=int, default=1_000_000)
+            p.add_argument("--n", type=int, default=384)
+            p.add_argument("--k", type=int, default=128)
+            p.add_argument("--act", default="")
+            p.add_argument("--residual", action="store_true")
+            p.add_argument("--compare", action="store_true")
+        elif name == "attn":
+            p.add_argument("--nodes", type=int, default=1_000_000)
+            p.add_argument("--heads", type=int, default=8)
+            p.add_argument("--head_dim", type=int, default=16)
+            p.add_argument("--degree", type=int, default=8)
+        elif name == "ln":
+            p.add_argument("--rows", type=int, default=1_000_000)
+            p.add_argument("--hidden", type=int, default=128)
+        else:
+            p.add_argument("--nodes", type=int, default=1_000_000)
+            p.add_argument("--edges", type=int, default=5_000_000)
+            p.add_argument("--b_real", type=int, default=4)
+            p.add_argument("--b_rw", type=int, default=4)
+            p.add_argument("--walks", type=int, default=2)
+            p.add_argument("--walk_len", type=int, default=4)
+    a = ap.parse_args(argv)
+    {"gemm": case_gemm, "attn": case_attn, "ln": case_ln, "build": case_build}[a.case](a)
+
+
+if __name__ == "__main__":
+    main()

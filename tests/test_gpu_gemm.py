@@ -162,3 +162,14 @@ def test_hash_dropout_matches_epilogue_mask():
     keep = gemm.hash_keep_mask(99, 777, 96, 0.3, "cuda")
     assert torch.equal(y > 0, keep)
     assert abs(float(keep.float().mean()) - 0.7) < 0.02
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_column_sum_kernel(dtype):
+    from budgetformer_b200.ops.norm import column_sum
+    x = torch.randn(50001, 384, device="cuda").to(dtype)
+    got = column_sum(x)
+    want = x.double().sum(0)
+    assert torch.allclose(got.double(), want, atol=0.2 if dtype == torch.bfloat16 else 2e-2, rtol=1e-3)
+    view = x[:, 128:256]
+    assert torch.allclose(column_sum(view).double(), view.double().sum(0), atol=0.2, rtol=1e-3)
