@@ -58,6 +58,7 @@ struct GemmArgs {
   int stages;                    // operand ring depth (3 or 4)
   int tma_store;                 // 1: epilogue stages 64-column panels in shared memory and writes them with TMA
   int out_bufs;                  // staging buffers (1 or 2) when tma_store
+  int bias_in_smem;              // bias copied to shared memory once per CTA (N <= 1024)
 };
 
 struct OutMaps {
@@ -211,6 +212,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   uint8_t* smem_out = smem_b + STAGES * b_stage_bytes;              // [out_bufs][block_n/64][128 rows][128 B], swizzled
   const uint32_t out_buf_bytes = g.tma_store ? (uint32_t)(g.block_n / 64) * BLOCK_M * 128u : 0u;
   Control* ctl = reinterpret_cast<Control*>(smem_out + (size_t)g.out_bufs * out_buf_bytes);
+  float* s_bias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctl) + ((sizeof(Control) + 15) & ~size_t(15)));  // [N]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -224,6 +226,9 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], (g.block_n % 32 == 0) ? 8 : 4); }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (g.bias != nullptr && g.bias_in_smem) {
+    for (int i = threadIdx.x; i < g.N; i += blockDim.x) s_bias[i] = g.bias[i];
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
@@ -320,6 +325,14 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const bool second = c0 + 16 < col_begin + cols_per_group;
         tmem_ld_32x32b_x16(taddr + (uint32_t)c0, r);
         if (second) tmem_ld_32x32b_x16(taddr + (uint32_t)(c0 + 16), r + 16);
+        // residual for these 32 columns: four independent 16-byte loads issued while the TMEM loads are in flight
+        uint4 resv[4];
+        if (g.residual && row_ok) {
+          const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.residual) + row * g.ldr +
+                                                          n_chunk * g.block_n + c0);
+          resv[0] = __ldg(rp); resv[1] = __ldg(rp + 1);
+          if (second) { resv[2] = __ldg(rp + 2); resv[3] = __ldg(rp + 3); }
+        }
         tmem_ld_wait();
         if (!row_ok && !g.tma_store) continue;
 #pragma unroll
@@ -330,11 +343,20 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[16 * hseg + i]) * g.out_scale;
           if (g.bias) {
-            const float4* bp = reinterpret_cast<const float4*>(g.bias + col0);
+            if (g.bias_in_smem) {
+              const float4* bp = reinterpret_cast<const float4*>(s_bias + col0);      // broadcast read
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float4 b4 = __ldg(bp + i);
-              v[4 * i] += b4.x; v[4 * i + 1] += b4.y; v[4 * i + 2] += b4.z; v[4 * i + 3] += b4.w;
+              for (int i = 0; i < 4; ++i) {
+                const float4 b4 = bp[i];
+                v[4 * i] += b4.x; v[4 * i + 1] += b4.y; v[4 * i + 2] += b4.z; v[4 * i + 3] += b4.w;
+              }
+            } else {
+              const float4* bp = reinterpret_cast<const float4*>(g.bias + col0);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float4 b4 = __ldg(bp + i);
+                v[4 * i] += b4.x; v[4 * i + 1] += b4.y; v[4 * i + 2] += b4.z; v[4 * i + 3] += b4.w;
+              }
             }
           }
           if (g.act == 1) {
@@ -362,10 +384,8 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
           }
           if (g.residual && row_ok) {
-            const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.residual) + row * g.ldr + col0);
-            uint4 r0 = __ldg(rp), r1 = __ldg(rp + 1);
-            const unsigned short* rs0 = reinterpret_cast<const unsigned short*>(&r0);
-            const unsigned short* rs1 = reinterpret_cast<const unsigned short*>(&r1);
+            const unsigned short* rs0 = reinterpret_cast<const unsigned short*>(&resv[2 * hseg]);
+            const unsigned short* rs1 = reinterpret_cast<const unsigned short*>(&resv[2 * hseg + 1]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               v[i] += ld16_as_float(rs0 + i, g.is_fp16);
@@ -518,7 +538,9 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   // ---- shared-memory plan -------------------------------------------------------------------------
   const size_t stage_bytes = (size_t)BLOCK_M * BLOCK_K * 2 + (size_t)g.block_n * BLOCK_K * 2;
   const size_t out_bytes = (size_t)g.block_n * 256;                       // block_n/64 panels of 128 rows x 128 bytes
-  const size_t budget = 227 * 1024 - 1024 /*alignment slack*/ - sizeof(Control) - 64;
+  g.bias_in_smem = (p->bias != nullptr && p->N <= 1024) ? 1 : 0;
+  const size_t bias_bytes = g.bias_in_smem ? (size_t)p->N * 4 + 16 : 0;
+  const size_t budget = 227 * 1024 - 1024 /*alignment slack*/ - sizeof(Control) - 64 - bias_bytes;
   bool tma_ok = !p->out_fp32 && g.block_n % 64 == 0 && (p->n_dest == 1 || cols_per_dest % 64 == 0) &&
                 (p->ldc * 2) % 16 == 0;
   for (int i = 0; i < p->n_dest && tma_ok; ++i) tma_ok = ((uintptr_t)p->dst[i]) % 16 == 0;
@@ -540,7 +562,7 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
       }
     }
   }
-  const size_t smem = 1024 + g.stages * stage_bytes + (size_t)g.out_bufs * out_bytes + sizeof(Control) + 64;
+  const size_t smem = 1024 + g.stages * stage_bytes + (size_t)g.out_bufs * out_bytes + sizeof(Control) + 64 + bias_bytes;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
