@@ -18,21 +18,33 @@ namespace {
 
 constexpr uint64_t kInf = ~0ull;
 
-// Insert every candidate (valid, comp) held by the warp's lanes into the sorted lane-distributed list.
-__device__ __forceinline__ void warp_insert(uint64_t& list, int K, bool valid, uint64_t comp, int lane) {
+// Lane groups: WIDTH lanes (8 or 32) cooperate on one query.  Every *_sync primitive names only the group's lanes,
+// so groups of one warp may diverge from each other (different degrees, different insertion counts).
+template <int WIDTH> __device__ __forceinline__ unsigned group_mask(int lane) {
+  return WIDTH == 32 ? 0xffffffffu : (((1u << WIDTH) - 1u) << (lane & ~(WIDTH - 1)));
+}
+template <int WIDTH> __device__ __forceinline__ unsigned group_ballot(unsigned gm, int lane, bool pred) {
+  const unsigned b = __ballot_sync(gm, pred);
+  return WIDTH == 32 ? b : ((b >> (lane & ~(WIDTH - 1))) & ((1u << WIDTH) - 1u));
+}
+
+// Insert every candidate (valid, comp) held by the group's lanes into the sorted lane-distributed list
+// (lane i of the group holds the i-th smallest composite; K <= WIDTH).
+template <int WIDTH>
+__device__ __forceinline__ void group_insert(uint64_t& list, int K, bool valid, uint64_t comp, int gl, unsigned gm, int lane) {
   const unsigned kmask = K >= 32 ? 0xffffffffu : ((1u << K) - 1u);
-  for (int guard = 0; guard < 33; ++guard) {
-    const uint64_t kth = __shfl_sync(0xffffffffu, list, K - 1);
-    const unsigned ball = __ballot_sync(0xffffffffu, valid && comp < kth);
+  for (int guard = 0; guard <= WIDTH; ++guard) {
+    const uint64_t kth = __shfl_sync(gm, list, K - 1, WIDTH);
+    const unsigned ball = group_ballot<WIDTH>(gm, lane, valid && comp < kth);
     if (ball == 0) break;
     const int src_lane = __ffs(ball) - 1;
-    const uint64_t c = __shfl_sync(0xffffffffu, comp, src_lane);
-    const unsigned le = __ballot_sync(0xffffffffu, list <= c) & kmask;
+    const uint64_t c = __shfl_sync(gm, comp, src_lane, WIDTH);
+    const unsigned le = group_ballot<WIDTH>(gm, lane, list <= c) & kmask;
     const int p = __popc(le);
-    const uint64_t up = __shfl_up_sync(0xffffffffu, list, 1);
-    if (lane == p) list = c;
-    else if (lane > p && lane < K) list = up;
-    if (lane == src_lane) valid = false;
+    const uint64_t up = __shfl_up_sync(gm, list, 1, WIDTH);
+    if (gl == p) list = c;
+    else if (gl > p && gl < K) list = up;
+    if (gl == src_lane) valid = false;
   }
 }
 
@@ -48,12 +60,15 @@ struct BuildArgs {
   unsigned long long* totals;  // [2] selected real / rw edges (with multiplicity)
 };
 
+template <int WIDTH>
 __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
   __shared__ unsigned s_tot[2];
   if (threadIdx.x < 2) s_tot[threadIdx.x] = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31;
-  const long long v = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int gl = lane & (WIDTH - 1);                       // lane inside the group
+  const unsigned gm = group_mask<WIDTH>(lane);
+  const long long v = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / WIDTH;
   if (v < a.n) {
     const uint32_t q = (uint32_t)v;
     // ---- real edges ----
@@ -62,11 +77,11 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
     if (a.b_real > 0) {
       const int beg = a.in_rowptr[v], end = a.in_rowptr[v + 1];
       const int64_t rs = a.seed + BF_REAL_SEED_OFFSET;
-      for (int base = beg; base < end; base += 32) {
-        const int e = base + lane;
+      for (int base = beg; base < end; base += WIDTH) {
+        const int e = base + gl;
         const bool valid = e < end;
         const uint32_t s = valid ? (uint32_t)__ldg(a.in_src + e) : 0u;
-        warp_insert(rlist, a.b_real, valid, valid ? bf_edge_composite(s, q, rs) : kInf, lane);
+        group_insert<WIDTH>(rlist, a.b_real, valid, valid ? bf_edge_composite(s, q, rs) : kInf, gl, gm, lane);
       }
       r_cnt = min(end - beg, a.b_real);
     }
@@ -76,8 +91,8 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
     if (a.b_rw > 0 && a.walks > 0 && a.walk_len > 0) {
       const int64_t ws = a.seed + BF_RW_SEED_OFFSET;
       int n_cand = 0;
-      for (int wbase = 0; wbase < a.walks; wbase += 32) {
-        const int w = wbase + lane;
+      for (int wbase = 0; wbase < a.walks; wbase += WIDTH) {
+        const int w = wbase + gl;
         const bool active = w < a.walks;
         const uint64_t walk_id = (uint64_t)v * (uint64_t)a.walks + (uint64_t)w;
         int cur = (int)v, prev = (int)v;
@@ -93,44 +108,44 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
             }
             emit = (d == 1) || (cur != prev);
           }
-          n_cand += __popc(__ballot_sync(0xffffffffu, emit));
-          warp_insert(wlist, a.b_rw, emit, emit ? bf_edge_composite((uint32_t)cur, q, ws) : kInf, lane);
+          n_cand += __popc(group_ballot<WIDTH>(gm, lane, emit));
+          group_insert<WIDTH>(wlist, a.b_rw, emit, emit ? bf_edge_composite((uint32_t)cur, q, ws) : kInf, gl, gm, lane);
         }
       }
       w_cnt = min(n_cand, a.b_rw);
     }
     // ---- merge ----
-    const bool has_r = lane < r_cnt, has_w = lane < w_cnt;
+    const bool has_r = gl < r_cnt, has_w = gl < w_cnt;
     const uint32_t sr = (uint32_t)rlist, sw = (uint32_t)wlist;
     int* row = a.ell_col + (long long)v * a.cap;
     if (a.exphormer) {
       int rank_r = 0, rank_w = 0;
-      for (int t = 0; t < 32; ++t) {
-        const uint32_t yr = __shfl_sync(0xffffffffu, sr, t);
-        const uint32_t yw = __shfl_sync(0xffffffffu, sw, t);
-        if (t < r_cnt && (yr < sr || (yr == sr && t < lane))) ++rank_r;
-        if (t < w_cnt && (yw < sw || (yw == sw && t < lane))) ++rank_w;
+      for (int t = 0; t < WIDTH; ++t) {
+        const uint32_t yr = __shfl_sync(gm, sr, t, WIDTH);
+        const uint32_t yw = __shfl_sync(gm, sw, t, WIDTH);
+        if (t < r_cnt && (yr < sr || (yr == sr && t < gl))) ++rank_r;
+        if (t < w_cnt && (yw < sw || (yw == sw && t < gl))) ++rank_w;
       }
       uint8_t* trow = a.ell_type + (long long)v * a.cap;
       if (has_r) { row[rank_r] = (int)sr; trow[rank_r] = 0; }
       if (has_w) { row[r_cnt + rank_w] = (int)sw; trow[r_cnt + rank_w] = 1; }
-      if (lane == 0) { row[r_cnt + w_cnt] = (int)v; trow[r_cnt + w_cnt] = 0; a.ell_cnt[v] = r_cnt + w_cnt + 1; }
+      if (gl == 0) { row[r_cnt + w_cnt] = (int)v; trow[r_cnt + w_cnt] = 0; a.ell_cnt[v] = r_cnt + w_cnt + 1; }
     } else {
       bool dup_r = false, dup_w = false;
-      for (int t = 0; t < 32; ++t) {
-        const uint32_t yr = __shfl_sync(0xffffffffu, sr, t);
-        const uint32_t yw = __shfl_sync(0xffffffffu, sw, t);
-        if (t < r_cnt && t < lane && yr == sr) dup_r = true;
+      for (int t = 0; t < WIDTH; ++t) {
+        const uint32_t yr = __shfl_sync(gm, sr, t, WIDTH);
+        const uint32_t yw = __shfl_sync(gm, sw, t, WIDTH);
+        if (t < r_cnt && t < gl && yr == sr) dup_r = true;
         if (t < r_cnt && yr == sw) dup_w = true;
-        if (t < w_cnt && t < lane && yw == sw) dup_w = true;
+        if (t < w_cnt && t < gl && yw == sw) dup_w = true;
       }
       const bool keep_r = has_r && !dup_r, keep_w = has_w && !dup_w;
       int rank_r = 0, rank_w = 0;
-      for (int t = 0; t < 32; ++t) {
-        const uint32_t yr = __shfl_sync(0xffffffffu, sr, t);
-        const uint32_t yw = __shfl_sync(0xffffffffu, sw, t);
-        const bool kr = __shfl_sync(0xffffffffu, (int)keep_r, t) != 0;
-        const bool kw = __shfl_sync(0xffffffffu, (int)keep_w, t) != 0;
+      for (int t = 0; t < WIDTH; ++t) {
+        const uint32_t yr = __shfl_sync(gm, sr, t, WIDTH);
+        const uint32_t yw = __shfl_sync(gm, sw, t, WIDTH);
+        const bool kr = __shfl_sync(gm, (int)keep_r, t, WIDTH) != 0;
+        const bool kw = __shfl_sync(gm, (int)keep_w, t, WIDTH) != 0;
         if (kr && yr < sr) ++rank_r;
         if (kw && yw < sr) ++rank_r;
         if (kr && yr < sw) ++rank_w;
@@ -138,10 +153,10 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
       }
       if (keep_r) row[rank_r] = (int)sr;
       if (keep_w) row[rank_w] = (int)sw;
-      const int total = __popc(__ballot_sync(0xffffffffu, keep_r)) + __popc(__ballot_sync(0xffffffffu, keep_w));
-      if (lane == 0) a.ell_cnt[v] = total;
+      const int total = __popc(group_ballot<WIDTH>(gm, lane, keep_r)) + __popc(group_ballot<WIDTH>(gm, lane, keep_w));
+      if (gl == 0) a.ell_cnt[v] = total;
     }
-    if (lane == 0) { atomicAdd(&s_tot[0], (unsigned)r_cnt); atomicAdd(&s_tot[1], (unsigned)w_cnt); }
+    if (gl == 0) { atomicAdd(&s_tot[0], (unsigned)r_cnt); atomicAdd(&s_tot[1], (unsigned)w_cnt); }
   }
   __syncthreads();
   if (threadIdx.x < 2 && s_tot[threadIdx.x]) atomicAdd(a.totals + threadIdx.x, (unsigned long long)s_tot[threadIdx.x]);
@@ -170,8 +185,14 @@ extern "C" int bf_budget_select(const bf_build_params* p, cudaStream_t st) {
   a.exphormer = p->exphormer; a.seed = p->seed; a.cap = p->cap;
   a.ell_col = p->ell_col; a.ell_type = p->ell_type; a.ell_cnt = p->ell_cnt;
   a.totals = reinterpret_cast<unsigned long long*>(p->totals);
-  const long long blocks = ((long long)p->n * 32 + 255) / 256;
-  if (blocks > 0) budget_select_kernel<<<(unsigned)blocks, 256, 0, st>>>(a);
+  // eight lanes per query when both budgets and the walk count fit in eight slots, else a full warp
+  const bool narrow = p->b_real <= 8 && p->b_rw <= 8 && p->walks <= 8;
+  const int width = narrow ? 8 : 32;
+  const long long blocks = ((long long)p->n * width + 255) / 256;
+  if (blocks > 0) {
+    if (narrow) budget_select_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else budget_select_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(a);
+  }
   return (int)cudaGetLastError();
 }
 
