@@ -138,6 +138,9 @@ class FullGraphTrainer:
         self.model.set_activation_checkpoint(ckpt_mode is not None, ckpt_mode, deferred=budget_moving)
         self.planner = self.model._comm_ckpt if ckpt_mode == "multi_tier" else None
         self._configure_fused_sp()
+        if self.planner is not None and self.sp_world > 1 and self.device.type == "cuda":
+            from ..parallel import symm
+            self.planner.probe.extra_bytes_fn = symm.symmetric_bytes   # peer-mapped buffers live outside the allocator
         sync_params_and_buffers(self.model, self.sp_group, self.sp_src)
         self.reducer = build_gradient_reducer(self.model, self.sp_group, 25.0, self.sp_world)
         self.scaler = torch.amp.GradScaler("cuda", enabled=(self.amp_dtype == torch.float16 and self.device.type == "cuda"))
@@ -384,7 +387,7 @@ class FullGraphTrainer:
         t0 = time.perf_counter()
         x_local = None
         if x_host is not None:
-            x_local = x_host.to(self.device, non_blocking=True)
+            x_local = self._stage_input(x_host)
         self._align_ranks()
         with StepTimer(self.device, sync_timers) as t_rw:
             graph = self.build_edges(epoch)
@@ -410,6 +413,38 @@ class FullGraphTrainer:
         out.update({f"t_{k}": v for k, v in timers.items()})
         out["edges"] = float(graph.num_edges)
         return out
+
+    def _stage_input(self, x_host: torch.Tensor) -> torch.Tensor:
+        """Host -> device input pipeline: this step's features were uploaded from pinned memory on a copy stream while
+        the previous step computed (double buffer); the upload for the next step is started before returning.  Every
+        step therefore consumes exactly one full host -> device copy, overlapped with compute."""
+        if self.device.type != "cuda":
+            return x_host.to(self.device)
+        st = getattr(self, "_input_pipe", None)
+        if st is None or st["shape"] != tuple(x_host.shape):
+            st = {"shape": tuple(x_host.shape), "stream": torch.cuda.Stream(self.device), "bufs": [
+                torch.empty(x_host.shape, dtype=x_host.dtype, device=self.device) for _ in range(2)],
+                "events": [None, None], "src": [None, None], "next": 0}
+            self._input_pipe = st
+        cur_stream = torch.cuda.current_stream(self.device)
+
+        def upload(slot):
+            st["stream"].wait_stream(cur_stream)            # the buffer's previous consumer has been enqueued before
+            with torch.cuda.stream(st["stream"]):
+                st["bufs"][slot].copy_(x_host, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(st["stream"])
+            st["events"][slot], st["src"][slot] = ev, x_host.data_ptr()
+
+        slot = st["next"]
+        if st["events"][slot] is None or st["src"][slot] != x_host.data_ptr():
+            upload(slot)                                     # first step (or a new host tensor): nothing prefetched yet
+        cur_stream.wait_event(st["events"][slot])
+        x = st["bufs"][slot]
+        st["events"][slot] = None
+        st["next"] = slot ^ 1
+        upload(slot ^ 1)                                     # prefetch for the next step
+        return x
 
     def _align_ranks(self) -> None:
         """Stream-ordered NCCL rendezvous before a fused forward.  The in-kernel barriers of the fused path use

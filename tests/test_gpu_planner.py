@@ -1,0 +1,63 @@
+"""Execution planner and budget controller end to end on a GPU (small graph)."""
+import pytest
+import torch
+
+from budgetformer_b200.config import parse_fullgraph_args
+from budgetformer_b200.graph.synthetic import sbm_graph
+from budgetformer_b200.ops import gemm
+from budgetformer_b200.train.data import GraphData, random_split_idx
+from budgetformer_b200.train.engine import FullGraphTrainer
+
+pytestmark = pytest.mark.gpu
+
+
+def _trainer(extra, n=4096, logs=None):
+    x, y, ei = sbm_graph(n, feat_dim=64, seed=3)
+    data = GraphData(x, y, ei, random_split_idx(n, 3), n, 7)
+    argv = ["--model", "gt", "--dataset", "t", "--n_layers", "3", "--hidden_dim", "128", "--num_heads", "8", "--ffn_dim", "256",
+            "--amp_dtype", "bf16", "--force_random_split", "--device", "cuda:0", "--seed", "5", "--peak_lr", "3e-3",
+            "--eval_every", "100", "--epochs", "14"] + list(extra)
+    log = (lambda *a, **k: logs.append(" ".join(str(v) for v in a))) if logs is not None else (lambda *a, **k: None)
+    return FullGraphTrainer(parse_fullgraph_args(argv), data=data, log=log)
+
+
+def test_multi_tier_calibrates_and_activates_on_gpu():
+    logs = []
+    t = _trainer(["--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4",
+                  "--activation_checkpoint_mode", "multi_tier"], logs=logs)
+    assert t.planner is not None and t.planner.state_name() == "WARMUP_RECOMPUTE"
+    t.profile_edge_policies()
+    t.fit()
+    gemm.check_status("cuda")
+    assert t.planner.is_active()
+    assert t.planner.edge_policy in ("gpu_persist", "gpu_ephemeral", "cpu_rank_local_prefetch")
+    assert t.edge_engine.policy == t.planner.edge_policy and t.edge_engine.policy_locked
+    assert t.planner.modes() == ["retain"] * 3            # a 4k-node graph fits: everything is retained
+    assert any("ACTIVE plan" in l for l in logs) and any("edge policy gpu_persist: build=" in l for l in logs)
+
+
+def test_forced_plan_and_cpu_policy_on_gpu():
+    t = _trainer(["--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4",
+                  "--activation_checkpoint_mode", "multi_tier",
+                  "--force_multi_tier_plan", "cpu_rank_local_prefetch:keep_mha=1"])
+    assert t.planner.is_active() and t.planner.modes() == ["recompute", "recompute", "keep_mha"]
+    assert t.edge_engine.policy == "cpu_rank_local_prefetch"
+    losses = [t.train_step(e)["loss"] for e in range(1, 6)]
+    assert losses[-1] < losses[0]
+    # the CPU-built graph equals the GPU-built one
+    g_cpu = t.edge_engine.build(99, t.budget_state())
+    t.edge_engine.set_policy("gpu_persist")
+    g_gpu = t.edge_engine.build(99, t.budget_state())
+    assert torch.equal(g_cpu.col, g_gpu.col) and torch.equal(g_cpu.rowptr, g_gpu.rowptr)
+    t.edge_engine.shutdown()
+
+
+def test_adaptive_budget_with_deferred_planner_on_gpu():
+    logs = []
+    t = _trainer(["--adaptive_edge_budget", "--max_total_edges_per_query", "6", "--warmup_updates", "1",
+                  "--activation_checkpoint_mode", "multi_tier", "--epochs", "22"], logs=logs)
+    assert t.planner.state_name() == "DEFERRED"
+    t.fit()
+    assert t.controller.frozen
+    assert t.planner.state_name() != "DEFERRED"          # the frozen budget released the planner
+    assert any("BudgetCtrl" in l for l in logs)
