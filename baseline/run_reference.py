@@ -128,12 +128,13 @@ def run(ns) -> None:
     peak = torch.cuda.max_memory_allocated() / 2 ** 20
     rec = {"metric": "fullgraph_train_nodes_per_s", "value": n_nodes / (ms / 1e3), "unit": "nodes/s", "n_gpus": world,
            "steps": steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-           "vs_baseline": None, "dtype": "bf16", "data": "synthetic citation-like DAG (power-law out-degree), random-init weights",
+           "vs_baseline": None, "dtype": "bf16", "data": f"synthetic {cfg['graph']} graph, N(0,1) features, random-init weights",
            "impl": "reference", "impl_note": "unmodified reference sources + pure-PyTorch stand-ins for torch_scatter/"
            "torch_sparse/torch_cluster/PyG/DGL; timed by the reference's own epoch timer (host clock incl. device sync)",
            "config": {"model": f"{cfg['model'].upper()} L{cfg['n_layers']} h{cfg['hidden_dim']} H{cfg['num_heads']}",
                       "nodes": int(n_nodes), "edges": int(n_edges), "global_batch": int(n_nodes), "seq_len": int(n_nodes),
-                      "budget": "4 real + 4 random-walk per query, rebuilt every epoch", "parallelism": f"sp{world}",
+                      "budget": f"{(b + 1) // 2} real + {b // 2} random-walk per query, rebuilt every epoch",
+                      "name": ns.config, "parallelism": f"sp{world}",
                       "scale": ns.scale},
            "epoch_ms": ms, "peak_hbm_mib_per_gpu": peak, "gpu_launches": 0,
            "e2e": {"value": n_nodes / (ms / 1e3), "unit": "nodes/s", "note": "the reference keeps its inputs resident; "

@@ -25,6 +25,9 @@ import threading
 import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
+MODEL_NAMES = {"gt": "GT", "graphormer": "Graphormer", "graphgps": "GraphGPS", "exphormer": "Exphormer"}
+GRAPH_DESC = {"dag": "citation-like DAG (power-law out-degree)", "chung_lu_directed": "Chung-Lu power-law directed graph",
+              "chung_lu_undirected": "Chung-Lu power-law undirected graph", "sbm": "stochastic block model"}
 sys.path.insert(0, REPO)
 
 
@@ -184,11 +187,13 @@ def run_ours(ns):
             "metric": "fullgraph_train_nodes_per_s", "value": n / (ms_step / 1e3), "unit": "nodes/s",
             "n_gpus": world, "steps": ns.steps, "warmup": max(3, ns.warmup), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic citation-like DAG (power-law out-degree), random-init weights",
+            "data": f"synthetic {GRAPH_DESC.get(cfg['graph'], cfg['graph'])}, N(0,1) features, random-init weights",
             "impl": "ours",
-            "config": {"model": f"GT L{cfg['n_layers']} h{cfg['hidden_dim']} H{cfg['num_heads']}", "nodes": n,
+            "config": {"name": ns.config, "model": f"{MODEL_NAMES.get(cfg['model'], cfg['model'])} L{cfg['n_layers']} "
+                                                  f"h{cfg['hidden_dim']} H{cfg['num_heads']}", "nodes": n,
                        "edges": int(ei.size(1)), "global_batch": n, "seq_len": n, "feat_dim": int(x.size(1)),
-                       "budget": "4 real + 4 random-walk per query (B=8 ceiling of the adaptive search), rebuilt every epoch",
+                       "budget": f"{(int(cfg['budget']) + 1) // 2} real + {int(cfg['budget']) // 2} random-walk per query "
+                                 f"(B={cfg['budget']} ceiling of the adaptive search), rebuilt every epoch",
                        "parallelism": f"sp{world}", "fused_sp": bool(trainer.fused_sp),
                        "activation_checkpoint": ns.ckpt or "none (retain)", "scale": ns.scale,
                        "l2": "working set per step (>= 750 MB activations per layer) exceeds the 126 MB L2; no flush needed"},

@@ -135,6 +135,12 @@ int bf_adamw_flat(float* p, const float* g, float* m, float* v, long long n, flo
                   float eps, float weight_decay, int step, const float* sumsq /* or NULL */, float max_norm,
                   cudaStream_t st);
 
+// ---- readout loss (loss.cu) ---------------------------------------------------------------------------
+// loss_sum += sum over rows with mask != 0 of -log softmax(logits[row])[y[row]]; when dlogits != NULL it receives
+// (softmax - onehot) * grad_scale on those rows and zeros elsewhere (contiguous [rows, classes]).
+int bf_nll_fwd_bwd(const void* logits, long long ld, const long long* y, const uint8_t* mask, long long rows, int classes,
+                   float* loss_sum, void* dlogits, float grad_scale, int dtype, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -327,6 +327,20 @@ void adamw_flat(Tensor p, Tensor g, Tensor m, Tensor v, int64_t n, double lr, do
                            at::cuda::getCurrentCUDAStream()), "adamw_flat");
 }
 
+// Returns (loss_sum [1] fp32, dlogits or empty).
+std::vector<Tensor> nll_fwd_bwd(Tensor logits, Tensor y, Tensor mask, bool want_grad, double grad_scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(y.scalar_type() == torch::kLong && y.is_contiguous() && mask.scalar_type() == torch::kUInt8 && mask.is_contiguous());
+  TORCH_CHECK(y.numel() == logits.size(0) && mask.numel() == logits.size(0));
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor loss = torch::zeros({1}, logits.options().dtype(torch::kFloat));
+  Tensor d = want_grad ? torch::empty({logits.size(0), logits.size(1)}, logits.options()) : Tensor();
+  check_cuda(bf_nll_fwd_bwd(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(y.data_ptr<int64_t>()), mask.data_ptr<uint8_t>(), logits.size(0),
+                            (int)logits.size(1), loss.data_ptr<float>(), want_grad ? d.data_ptr() : nullptr, (float)grad_scale,
+                            dtype_code(logits), at::cuda::getCurrentCUDAStream()), "nll_fwd_bwd");
+  return {loss, want_grad ? d : torch::empty({0}, logits.options())};
+}
+
 bool gemm_supported(int64_t M, int64_t N, int64_t K) { return bf_gemm_supported((int)M, (int)N, (int)K) != 0; }
 
 }  // namespace
@@ -341,6 +355,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("hash_dropout", &hash_dropout);
   m.def("colsum", &colsum);
+  m.def("nll_fwd_bwd", &nll_fwd_bwd);
   m.def("grad_sumsq", &grad_sumsq);
   m.def("adamw_flat", &adamw_flat);
   m.def("peer_barrier", &peer_barrier);

@@ -257,10 +257,29 @@ class FullGraphTrainer:
                 if idx.numel() == 0:
                     return out.sum() * 0, out
                 return F.binary_cross_entropy_with_logits(out[idx].float(), self.local_y[idx].float()), out
+            if self.device.type == "cuda" and hasattr(self.model, "forward_logits"):
+                # fused log-softmax + NLL (+ gradient) over this rank's rows of `idx`; `out` are logits, whose argmax
+                # equals the argmax of the log-probabilities the model would return
+                from ..ops.loss import masked_nll
+                out = self.model.forward_logits(x, None, graph, attn_type=attn_type)
+                if idx.numel() == 0:
+                    return out.sum() * 0, out
+                return masked_nll(out, self.local_y, idx, self._loss_mask(idx)), out
             out = self.model(x, None, graph, attn_type=attn_type)
             if idx.numel() == 0:
                 return out.sum() * 0, out
             return F.nll_loss(out[idx].float(), self.local_y[idx]), out
+
+    def _loss_mask(self, idx: torch.Tensor) -> torch.Tensor:
+        """uint8 row mask of ``idx`` (cached per index tensor: the train / probe sets are fixed)."""
+        cache = self.__dict__.setdefault("_mask_cache", {})
+        key = (idx.data_ptr(), int(idx.numel()))
+        m = cache.get(key)
+        if m is None:
+            m = torch.zeros(self.nodes_per_rank, dtype=torch.uint8, device=self.device)
+            m[idx] = 1
+            cache[key] = m
+        return m
 
     def _any_rank(self, flag: bool) -> bool:
         """MAX-vote over SP ranks (``_sp_any_oom``, main_node_fullgraph_sp.py:1313-1318)."""

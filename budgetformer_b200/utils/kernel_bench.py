@@ -134,11 +134,107 @@ def case_build(a):
     report("build+transpose+kv_tasks", ms, 0, 0, {"nodes": a.nodes})
 
 
+def case_sp(a):
+    """Fused sequence-parallel ops against their NCCL + cuBLAS equivalents.  Run under torchrun, one rank per GPU."""
+    import torch.distributed as dist
+    from ..ops import fused_sp, gemm
+    from ..parallel import symm
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_loc = a.nodes // world
+    h, heads = a.hidden, a.heads
+    sp = fused_sp.SPContext(dist.group.WORLD if world > 1 else None, dev, world, n_loc, h, heads, 1, torch.bfloat16)
+    x = torch.randn(n_loc, h, device=dev).bfloat16()
+    wq, wk, wv = (torch.randn(h, h, device=dev) * 0.05 for _ in range(3))
+    wo = (torch.randn(h, h, device=dev) * 0.05)
+    link_gbs = 770.0
+    esz = 2
+
+    def tmax(ms):
+        t = torch.tensor([ms], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def emit(name, ms, link_bytes, flops):
+        if rank != 0:
+            return
+        _, tf, src = peaks()
+        t_link = link_bytes / (link_gbs * 1e6)           # ms
+        t_flop = flops / (tf * 1e9)
+        bound = max(t_link, t_flop, 1e-9)
+        print(json.dumps({"op": name, "world": world, "ms": round(ms, 4), "nvlink_bytes_per_rank": int(link_bytes),
+                          "flops": int(flops), "roofline_ms": round(bound, 4), "frac_of_roofline": round(bound / ms, 3),
+                          "bound": "nvlink" if t_link >= t_flop else "compute", "link_GBps_assumed": link_gbs,
+                          "peaks": src}), flush=True)
+
+    frac = (world - 1) / world
+    # ---- nodes -> heads: fused GEMM + push vs cuBLAS + 3 NCCL all-to-alls -----------------------------------
+    fused = lambda: fused_sp._QKVPush.apply(x, wq, wk, wv, None, None, None, sp, 0)
+    ms = tmax(timed(fused, a.warmup, a.iters))
+    emit("qkv_gemm_push (fused)", ms, frac * n_loc * 3 * h * esz, 2.0 * n_loc * h * 3 * h)
+    w16 = [w.bfloat16() for w in (wq, wk, wv)]
+
+    def baseline_push():
+        outs = []
+        for w in w16:
+            y = torch.nn.functional.linear(x, w)
+            if world > 1:
+                send = y.view(n_loc, world, h // world).permute(1, 0, 2).contiguous()
+                recv = torch.empty_like(send)
+                dist.all_to_all_single(recv, send)
+                outs.append(recv)
+            else:
+                outs.append(y)
+        return outs
+    ms = tmax(timed(baseline_push, a.warmup, a.iters))
+    emit("qkv cuBLAS + 3x NCCL all_to_all (baseline)", ms, frac * n_loc * 3 * h * esz, 2.0 * n_loc * h * 3 * h)
+    # ---- heads -> nodes: pull + out-proj GEMM vs NCCL all-to-all + cuBLAS ---------------------------------------
+    ctx_full = sp.ctx[0].tensor
+    ctx_full.normal_()
+    pull = lambda: fused_sp._CtxPullOutProj.apply(ctx_full, wo, None, x, sp, 0.0, 0.0, 0, 0)
+    ms = tmax(timed(pull, a.warmup, a.iters))
+    emit("ctx_pull_outproj (fused)", ms, frac * n_loc * h * esz, 2.0 * n_loc * h * h)
+    wo16 = wo.bfloat16()
+
+    def baseline_pull():
+        c = ctx_full
+        if world > 1:
+            send = c.view(world, n_loc, h // world).contiguous()
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send)
+            c = recv.permute(1, 0, 2).reshape(n_loc, h)
+        return torch.nn.functional.linear(c, wo16) + x
+    ms = tmax(timed(baseline_pull, a.warmup, a.iters))
+    emit("NCCL all_to_all + cuBLAS out-proj (baseline)", ms, frac * n_loc * h * esz, 2.0 * n_loc * h * h)
+    # ---- gradient all-reduce -----------------------------------------------------------------------------------
+    if world > 1:
+        for mib in (2.2, 8.4, 64.0):
+            nfl = int(mib * 2 ** 20 / 4) // 1024 * 1024
+            buf = sp.sw.alloc((nfl,), torch.float32)
+            class _B: pass
+            b = _B(); b.symm = (sp.sw, buf)
+            ms = tmax(timed(lambda: symm.bucket_all_reduce_mean(b), a.warmup, a.iters))
+            emit(f"grad all-reduce {mib} MiB (own kernel, multimem={bool(buf.multicast_ptr)})", ms, 2 * frac * nfl * 4, 0)
+            t = torch.randn(nfl, device=dev)
+            def nccl():
+                t.div_(world)
+                dist.all_reduce(t)
+            ms = tmax(timed(nccl, a.warmup, a.iters))
+            emit(f"grad all-reduce {mib} MiB (div_ + NCCL baseline)", ms, 2 * frac * nfl * 4, 0)
+        gemm.check_status(dev)
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="case", required=True)
     common = dict(warmup=3, iters=10)
-    for name in ("gemm", "attn", "ln", "build"):
+    for name in ("gemm", "attn", "ln", "build", "sp"):
         p = sub.add_parser(name)
         p.add_argument("--warmup", type=int, default=common["warmup"])
         p.add_argument("--iters", type=int, default=common["iters"])
@@ -155,6 +251,10 @@ def main(argv=None):
             p.add_argument("--heads", type=int, default=8)
             p.add_argument("--head_dim", type=int, default=16)
             p.add_argument("--degree", type=int, default=8)
+        elif name == "sp":
+            p.add_argument("--nodes", type=int, default=2_923_920)
+            p.add_argument("--hidden", type=int, default=128)
+            p.add_argument("--heads", type=int, default=8)
         elif name == "ln":
             p.add_argument("--rows", type=int, default=1_000_000)
             p.add_argument("--hidden", type=int, default=128)
@@ -166,7 +266,7 @@ def main(argv=None):
             p.add_argument("--walks", type=int, default=2)
             p.add_argument("--walk_len", type=int, default=4)
     a = ap.parse_args(argv)
-    {"gemm": case_gemm, "attn": case_attn, "ln": case_ln, "build": case_build}[a.case](a)
+    {"gemm": case_gemm, "attn": case_attn, "ln": case_ln, "build": case_build, "sp": case_sp}[a.case](a)
 
 
 if __name__ == "__main__":

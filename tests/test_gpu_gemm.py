@@ -173,3 +173,23 @@ def test_column_sum_kernel(dtype):
     assert torch.allclose(got.double(), want, atol=0.2 if dtype == torch.bfloat16 else 2e-2, rtol=1e-3)
     view = x[:, 128:256]
     assert torch.allclose(column_sum(view).double(), view.double().sum(0), atol=0.2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("classes", [5, 40, 107])
+def test_fused_nll_loss(dtype, classes):
+    from budgetformer_b200.ops.loss import masked_nll
+    torch.manual_seed(0)
+    n = 5000
+    logits = (torch.randn(n, classes, device="cuda") * 2).to(dtype).requires_grad_(True)
+    y = torch.randint(0, classes, (n,), device="cuda")
+    y[::7] = -1                                               # padded rows carry label -1 and are never selected
+    idx = torch.nonzero(y >= 0).flatten()[::2].contiguous()
+    loss = masked_nll(logits, y, idx)
+    loss.backward()
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.nll_loss(torch.log_softmax(ref_in[idx], 1), y[idx])
+    ref.backward()
+    assert abs(float(loss) - float(ref)) < (2e-2 if dtype == torch.bfloat16 else 1e-5)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-6
+    assert torch.allclose(logits.grad.float(), ref_in.grad, atol=tol * float(ref_in.grad.abs().max()) + 1e-9)
