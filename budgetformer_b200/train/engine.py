@@ -102,6 +102,10 @@ class FullGraphTrainer:
         self.local_y = y_local.to(self.device)
         self.x_host = data.x[self.rank_start:self.rank_end].float().contiguous()
         if self.device.type == "cuda":
+            if self.amp_dtype is not None:
+                # under mixed precision the first layer consumes the features in the compute dtype anyway: keep the
+                # host copy (and every upload) in that dtype instead of casting on the device every step
+                self.x_host = self.x_host.to(self.amp_dtype)
             self.x_host = self.x_host.pin_memory()
         self.x_local = self.x_host.to(self.device, non_blocking=True)
         if args.model == "graphormer" and args.num_global_node > 0:
