@@ -422,7 +422,11 @@ class FullGraphTrainer:
         out: Dict[str, float] = {"dropped": 0.0}
         try:
             loss = self._step_with_oom_recovery(graph, epoch, x_local, timers, sync_timers)
-            if read_loss:
+            if read_loss == "async":
+                # device -> host copy of this step's loss into pinned memory without stalling the launch queue; the
+                # value returned is the previous step's (its copy has completed by now), the last one via flush_loss()
+                out["loss"] = self._read_loss_async(loss.detach())
+            elif read_loss:
                 out["loss"] = float(loss.item())
                 self.loss_ema = out["loss"] if self.loss_ema is None else 0.9 * self.loss_ema + 0.1 * out["loss"]
             else:
@@ -436,6 +440,35 @@ class FullGraphTrainer:
         out.update({f"t_{k}": v for k, v in timers.items()})
         out["edges"] = float(graph.num_edges)
         return out
+
+    def _read_loss_async(self, loss: torch.Tensor) -> float:
+        if self.device.type != "cuda":
+            return float(loss)
+        st = self.__dict__.setdefault("_loss_pipe", {"buf": torch.zeros(2, dtype=torch.float32).pin_memory(),
+                                                     "events": [None, None], "slot": 0})
+        slot = st["slot"]
+        prev = float("nan")
+        other = slot ^ 1
+        if st["events"][other] is not None:
+            st["events"][other].synchronize()
+            prev = float(st["buf"][other])
+        st["buf"][slot:slot + 1].copy_(loss.reshape(1).float(), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        st["events"][slot] = ev
+        st["slot"] = other
+        return prev
+
+    def flush_loss(self) -> float:
+        """Value of the most recent asynchronous loss read (waits for its copy)."""
+        st = self.__dict__.get("_loss_pipe")
+        if st is None:
+            return float("nan")
+        last = st["slot"] ^ 1
+        if st["events"][last] is None:
+            return float("nan")
+        st["events"][last].synchronize()
+        return float(st["buf"][last])
 
     def _stage_input(self, x_host: torch.Tensor) -> torch.Tensor:
         """Host -> device input pipeline: this step's features were uploaded from pinned memory on a copy stream while
