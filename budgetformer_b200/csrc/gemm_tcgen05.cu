@@ -29,7 +29,7 @@ constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;          // one 128-byte swizzle panel of 16-bit elements
 constexpr int UMMA_K = 16;
 constexpr int MAX_STAGES = 4;
-constexpr int NUM_THREADS = 320;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue (two column halves)
+constexpr int NUM_THREADS = 576;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-17: epilogue (four column groups)
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct GemmArgs {
@@ -57,8 +57,9 @@ struct GemmArgs {
   // shared-memory plan (host decides what fits in 227 KB)
   int stages;                    // operand ring depth (3 or 4)
   int tma_store;                 // 1: epilogue stages 64-column panels in shared memory and writes them with TMA
-  int out_bufs;                  // staging buffers (1 or 2) when tma_store
+  int out_bufs;                  // staging buffers (1 to 3) when tma_store
   int bias_in_smem;              // bias copied to shared memory once per CTA (N <= 1024)
+  int n_groups;                  // epilogue column groups in use (4, 2 or 1)
 };
 
 struct OutMaps {
@@ -158,12 +159,16 @@ __device__ __forceinline__ bool keep_elem(uint32_t seed, uint32_t row, uint32_t 
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
 
-__device__ __forceinline__ float ld16_as_float(const void* p, int is_fp16) {
-  const unsigned short u = *reinterpret_cast<const unsigned short*>(p);
-  if (is_fp16) return __half2float(__ushort_as_half(u));
-  return __uint_as_float(((uint32_t)u) << 16);
+// the two 16-bit floats packed in one 32-bit word, widened
+__device__ __forceinline__ float lo16_as_float(uint32_t w, bool is_fp16) {
+  if (is_fp16) return __half2float(__ushort_as_half((unsigned short)(w & 0xFFFFu)));
+  return __uint_as_float(w << 16);
 }
-__device__ __forceinline__ uint32_t pack2(float a, float b, int is_fp16) {
+__device__ __forceinline__ float hi16_as_float(uint32_t w, bool is_fp16) {
+  if (is_fp16) return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
+  return __uint_as_float(w & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, bool is_fp16) {
   if (is_fp16) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -182,8 +187,14 @@ template <int N> __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_bar_sync(int threads) { asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory"); }
 
 struct __align__(1024) SmemLayout {
   // operand ring follows at offset 0 of the dynamic buffer (A stages then B stages), then this control block
@@ -198,9 +209,15 @@ struct Control {
   int abort_flag;
 };
 
+// Epilogue features fixed at compile time in the specialised instantiations (bf16 only); EPI < 0 reads all of
+// them from the arguments at run time (any dtype, any combination).
+constexpr int EPI_BIAS = 1, EPI_RELU = 2, EPI_GELU = 4, EPI_DROP = 8, EPI_RES = 16, EPI_MASK = 32, EPI_SCALE = 64;
+
+template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ OutMaps omaps, const GemmArgs g) {
+  constexpr bool GEN = EPI < 0;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -223,7 +240,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], (g.block_n % 32 == 0) ? 8 : 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4 * g.n_groups); }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -289,150 +306,205 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       if (!ok) { *abort_flag = 1; atomicExch(g.status, 2); }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue warps (2..9)
-    // Warps 2-5 drain the first half of the tile's columns, warps 6-9 the second half (a warp may only touch the
-    // TMEM lane quarter given by warp % 4).  Tiles whose width is not a multiple of 32 use the first group only.
+    // ------------------------------------------------------------------ epilogue warps (2..17)
+    // Sixteen warps in four column groups: a warp may only touch the TMEM lane quarter given by warp % 4, so four
+    // consecutive warps cover the 128 rows of a tile and every group of four drains block_n / n_groups columns.
+    // Four warps per scheduler hide the latency of tcgen05.ld and of the conversion chain; tiles whose width is
+    // not a multiple of 64 use fewer groups.
     const int quarter = warp & 3;
     const int group = (warp - 2) >> 2;
-    const bool two_groups = (g.block_n % 32) == 0;
-    const int cols_per_group = two_groups ? g.block_n / 2 : g.block_n;
-    const int col_begin = group * cols_per_group;
-    const bool group_active = two_groups || group == 0;
+    const int n_groups = g.n_groups;
+    const int cpg = g.block_n / n_groups;                  // columns per group, a multiple of 16, at most 64
+    const int col_begin = group * cpg;
+    const bool group_active = group < n_groups;
     const int row_in_tile = quarter * 32 + lane;
-    const uint32_t thresh = g.dropout_p > 0.f ? (uint32_t)(g.dropout_p * 4294967296.0) : 0u;
-    const float keep_scale = g.dropout_p > 0.f ? 1.f / (1.f - g.dropout_p) : 1.f;
+    const int epi_threads = n_groups * 128;
+    const bool leader = (warp == 2 && lane == 0);
+    const bool is_fp16 = GEN ? (g.is_fp16 != 0) : false;
+    const bool has_bias = GEN ? (g.bias != nullptr) : ((EPI & EPI_BIAS) != 0);
+    const int act = GEN ? g.act : ((EPI & EPI_RELU) ? 1 : (EPI & EPI_GELU) ? 2 : 0);
+    const bool has_res = GEN ? (g.residual != nullptr) : ((EPI & EPI_RES) != 0);
+    const bool has_mask = GEN ? (g.relu_mask != nullptr) : ((EPI & EPI_MASK) != 0);
+    const bool has_scale = GEN ? (g.out_scale != 1.f) : ((EPI & EPI_SCALE) != 0);
+    const bool may_drop = GEN ? true : ((EPI & EPI_DROP) != 0);
+    const uint32_t thresh = (may_drop && g.dropout_p > 0.f) ? (uint32_t)(g.dropout_p * 4294967296.0) : 0u;
+    const float keep_scale = thresh ? 1.f / (1.f - g.dropout_p) : 1.f;
+    // operand fetched ahead of the arithmetic: the residual, else the ReLU mask
+    const bool pre_is_res = has_res;
+    const bool pre_any = has_res || has_mask;
+    const unsigned short* pre_base = static_cast<const unsigned short*>(pre_is_res ? g.residual : g.relu_mask);
+    const long long pre_ld = pre_is_res ? g.ldr : g.ldm;
+    // With TMA stores the warp's block of the residual (else: mask) tile goes global -> staging buffer with 16-byte
+    // asynchronous copies, lanes running along rows so that a request covers whole lines, and lands at the swizzled
+    // place where the result will be written; only this warp reads or writes that block.  The copy is issued before
+    // the wait for the accumulator (one whole tile earlier when there are three buffers).
+    const bool staged = pre_any && g.tma_store;
+    const bool ahead = staged && g.out_bufs == 3;
+    auto stage_operand = [&](int tile, uint8_t* buf) {
+      const int mt = tile / g.n_chunks, nc = tile % g.n_chunks;
+      const int L = cpg >> 3;                                     // 16-byte chunks per row of the block
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < L) {
+          const int q = j * 32 + lane;
+          const int rr = quarter * 32 + q / L, cc = q % L;
+          const long long grow = (long long)mt * BLOCK_M + rr;
+          if (grow < g.M) {
+            const int ct = col_begin + cc * 8;
+            uint8_t* dstp = buf + (size_t)(ct >> 6) * (BLOCK_M * 128) + (size_t)rr * 128 + ((((ct & 63) >> 3) ^ (rr & 7)) << 4);
+            cp_async_16(dstp, pre_base + grow * pre_ld + nc * g.block_n + ct);
+          }
+        }
+      }
+    };
     uint32_t acc = 0, acc_phase = 0;
     int out_sel = 0;
     bool ok = true;
+    if (ahead && group_active && (int)blockIdx.x < total_tiles) {
+      stage_operand(blockIdx.x, smem_out);
+      cp_async_commit();
+    }
     for (int t = blockIdx.x; t < total_tiles && ok && group_active; t += gridDim.x) {
       const int m_tile = t / g.n_chunks, n_chunk = t % g.n_chunks;
-      if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
-      tc_fence_after();
       const long long row = (long long)m_tile * BLOCK_M + row_in_tile;
       const bool row_ok = row < g.M;
-      const uint32_t taddr = tmem_base + acc * (uint32_t)g.block_n + ((uint32_t)(quarter * 32) << 16);
-      uint8_t* stage_out = smem_out + (size_t)out_sel * out_buf_bytes;
-      if (g.tma_store) {
-        // the staging buffer about to be overwritten must have been read by its previous bulk store
-        if (warp == 2 && lane == 0) {
-          if (g.out_bufs == 2) tma_store_wait_read<1>(); else tma_store_wait_read<0>();
-        }
-        epilogue_bar_sync();
+      const int gcol_begin = n_chunk * g.block_n + col_begin;   // first global column of this thread's slice
+      if (g.tma_store && g.out_bufs == 1) {
+        // single staging buffer: its previous bulk store must have been read before it is overwritten
+        if (leader) tma_store_wait_read<0>();
+        epilogue_bar_sync(epi_threads);
       }
-      for (int c0 = col_begin; c0 < col_begin + cols_per_group; c0 += 32) {
-        // two 16-column loads in flight before one wait
-        uint32_t r[32];
-        const bool second = c0 + 16 < col_begin + cols_per_group;
+      uint8_t* stage_out = smem_out + (size_t)out_sel * out_buf_bytes;
+      if (ahead) {
+        // three staging buffers: the next tile's operand is fetched now (its buffer's last store drained before the
+        // barrier that ended the previous tile), this tile's was fetched one tile ago
+        const int tn = t + gridDim.x;
+        if (tn < total_tiles) stage_operand(tn, smem_out + (size_t)((out_sel + 1) % 3) * out_buf_bytes);
+        cp_async_commit();
+      } else if (staged) {
+        stage_operand(t, stage_out);
+        cp_async_commit();
+      }
+      if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (staged) {
+        if (ahead) cp_async_wait_group<1>(); else cp_async_wait_group<0>();
+        __syncwarp();
+      }
+      const uint32_t taddr = tmem_base + acc * (uint32_t)g.block_n + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col_begin;
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int c0 = it * 16;                                 // column inside the group's slice
+        if (c0 >= cpg) break;
+        uint32_t r[16];
         tmem_ld_32x32b_x16(taddr + (uint32_t)c0, r);
-        if (second) tmem_ld_32x32b_x16(taddr + (uint32_t)(c0 + 16), r + 16);
-        // residual for these 32 columns: four independent 16-byte loads issued while the TMEM loads are in flight
-        uint4 resv[4];
-        if (g.residual && row_ok) {
-          const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.residual) + row * g.ldr +
-                                                          n_chunk * g.block_n + c0);
-          resv[0] = __ldg(rp); resv[1] = __ldg(rp + 1);
-          if (second) { resv[2] = __ldg(rp + 2); resv[3] = __ldg(rp + 3); }
+        const int col0 = gcol_begin + c0;
+        // where this thread's 16 results go in the staging buffer (and where a staged residual / mask waits)
+        const int ct0 = col_begin + c0;
+        uint8_t* panel = stage_out + (size_t)(ct0 >> 6) * (BLOCK_M * 128) + (size_t)row_in_tile * 128;
+        uint4* slot0 = reinterpret_cast<uint4*>(panel + ((((ct0 & 63) >> 3) ^ (row_in_tile & 7)) << 4));
+        uint4* slot1 = reinterpret_cast<uint4*>(panel + (((((ct0 & 63) >> 3) + 1) ^ (row_in_tile & 7)) << 4));
+        uint4 pre0 = make_uint4(0, 0, 0, 0), pre1 = pre0;
+        if (pre_any && row_ok) {
+          if (staged) { pre0 = *slot0; pre1 = *slot1; }
+          else {
+            const uint4* pp = reinterpret_cast<const uint4*>(pre_base + row * pre_ld + col0);
+            pre0 = __ldg(pp); pre1 = __ldg(pp + 1);
+          }
         }
         tmem_ld_wait();
+        if (it * 16 + 16 >= cpg) {
+          // last read of this accumulator by the warp: hand it back to the MMA issuer before the arithmetic
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+        }
         if (!row_ok && !g.tma_store) continue;
+        float v[16];
 #pragma unroll
-        for (int hseg = 0; hseg < 2; ++hseg) {
-          if (hseg == 1 && !second) break;
-          const int col0 = n_chunk * g.block_n + c0 + 16 * hseg;
-          float v[16];
+        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+        if (has_scale) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[16 * hseg + i]) * g.out_scale;
-          if (g.bias) {
-            if (g.bias_in_smem) {
-              const float4* bp = reinterpret_cast<const float4*>(s_bias + col0);      // broadcast read
+          for (int i = 0; i < 16; ++i) v[i] *= g.out_scale;
+        }
+        if (has_bias) {
+          const float4* bp = reinterpret_cast<const float4*>((g.bias_in_smem ? s_bias : g.bias) + col0);
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float4 b4 = bp[i];
-                v[4 * i] += b4.x; v[4 * i + 1] += b4.y; v[4 * i + 2] += b4.z; v[4 * i + 3] += b4.w;
-              }
-            } else {
-              const float4* bp = reinterpret_cast<const float4*>(g.bias + col0);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float4 b4 = __ldg(bp + i);
-                v[4 * i] += b4.x; v[4 * i + 1] += b4.y; v[4 * i + 2] += b4.z; v[4 * i + 3] += b4.w;
-              }
-            }
+          for (int i = 0; i < 4; ++i) {
+            const float4 b4 = g.bias_in_smem ? bp[i] : __ldg(bp + i);
+            v[4 * i] += b4.x; v[4 * i + 1] += b4.y; v[4 * i + 2] += b4.z; v[4 * i + 3] += b4.w;
           }
-          if (g.act == 1) {
+        }
+        if (act == 1) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
-          } else if (g.act == 2) {
+          for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+        } else if (act == 2) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = gelu_erf(v[i]);
-          }
-          if (thresh) {
+          for (int i = 0; i < 16; ++i) v[i] = gelu_erf(v[i]);
+        }
+        if (thresh) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              v[i] = keep_elem(g.dropout_seed, (uint32_t)row, (uint32_t)(col0 + i), thresh) ? v[i] * keep_scale : 0.f;
-          }
-          if (g.relu_mask && row_ok) {
+          for (int i = 0; i < 16; ++i)
+            v[i] = keep_elem(g.dropout_seed, (uint32_t)row, (uint32_t)(col0 + i), thresh) ? v[i] * keep_scale : 0.f;
+        }
+        if (has_mask && row_ok) {
+          uint4 m0, m1;
+          if (!pre_is_res) { m0 = pre0; m1 = pre1; }
+          else {
             const uint4* mp = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(g.relu_mask) + row * g.ldm + col0);
-            uint4 m0 = __ldg(mp), m1 = __ldg(mp + 1);
-            const unsigned short* ms0 = reinterpret_cast<const unsigned short*>(&m0);
-            const unsigned short* ms1 = reinterpret_cast<const unsigned short*>(&m1);
+            m0 = __ldg(mp); m1 = __ldg(mp + 1);
+          }
+          const unsigned short* ms0 = reinterpret_cast<const unsigned short*>(&m0);
+          const unsigned short* ms1 = reinterpret_cast<const unsigned short*>(&m1);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              // positive in either 16-bit float format: sign bit clear and magnitude non-zero
-              if (!((ms0[i] & 0x8000u) == 0 && (ms0[i] & 0x7FFFu) != 0)) v[i] = 0.f;
-              if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
-            }
+          for (int i = 0; i < 8; ++i) {
+            // positive in either 16-bit float format: sign bit clear and magnitude non-zero
+            if (!((ms0[i] & 0x8000u) == 0 && (ms0[i] & 0x7FFFu) != 0)) v[i] = 0.f;
+            if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
           }
-          if (g.residual && row_ok) {
-            const unsigned short* rs0 = reinterpret_cast<const unsigned short*>(&resv[2 * hseg]);
-            const unsigned short* rs1 = reinterpret_cast<const unsigned short*>(&resv[2 * hseg + 1]);
+        }
+        if (has_res && row_ok) {
+          const uint4 q0 = pre0, q1 = pre1;
+          const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w}, w1[4] = {q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              v[i] += ld16_as_float(rs0 + i, g.is_fp16);
-              v[8 + i] += ld16_as_float(rs1 + i, g.is_fp16);
-            }
+          for (int i = 0; i < 4; ++i) {
+            v[2 * i] += lo16_as_float(w0[i], is_fp16);     v[2 * i + 1] += hi16_as_float(w0[i], is_fp16);
+            v[8 + 2 * i] += lo16_as_float(w1[i], is_fp16); v[8 + 2 * i + 1] += hi16_as_float(w1[i], is_fp16);
           }
-          if (g.tma_store) {
-            // 16-bit result into the swizzled staging panel: 16-byte chunk c of row r lives at chunk (c ^ (r & 7))
-            const int ct = c0 + 16 * hseg;                       // column inside the tile
-            uint8_t* panel = stage_out + (size_t)(ct >> 6) * (BLOCK_M * 128) + (size_t)row_in_tile * 128;
-            const int ch = (ct & 63) >> 3;
-            uint4 o0, o1;
-            o0.x = pack2(v[0], v[1], g.is_fp16); o0.y = pack2(v[2], v[3], g.is_fp16);
-            o0.z = pack2(v[4], v[5], g.is_fp16); o0.w = pack2(v[6], v[7], g.is_fp16);
-            o1.x = pack2(v[8], v[9], g.is_fp16); o1.y = pack2(v[10], v[11], g.is_fp16);
-            o1.z = pack2(v[12], v[13], g.is_fp16); o1.w = pack2(v[14], v[15], g.is_fp16);
-            *reinterpret_cast<uint4*>(panel + ((ch ^ (row_in_tile & 7)) << 4)) = o0;
-            *reinterpret_cast<uint4*>(panel + (((ch + 1) ^ (row_in_tile & 7)) << 4)) = o1;
-            continue;
-          }
+        }
+        if (g.out_fp32) {
+          const int dest = g.n_dest > 1 ? col0 / g.cols_per_dest : 0;
+          const int dcol = g.n_dest > 1 ? col0 - dest * g.cols_per_dest : col0;
+          float4* op = reinterpret_cast<float4*>(static_cast<float*>(g.dst[dest]) + (g.dst_row_offset + row) * g.ldc + dcol);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) op[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          continue;
+        }
+        uint4 o0, o1;
+        o0.x = pack2(v[0], v[1], is_fp16); o0.y = pack2(v[2], v[3], is_fp16);
+        o0.z = pack2(v[4], v[5], is_fp16); o0.w = pack2(v[6], v[7], is_fp16);
+        o1.x = pack2(v[8], v[9], is_fp16); o1.y = pack2(v[10], v[11], is_fp16);
+        o1.z = pack2(v[12], v[13], is_fp16); o1.w = pack2(v[14], v[15], is_fp16);
+        if (g.tma_store) {
+          // 16-bit result into the swizzled staging panel: 16-byte chunk c of row r lives at chunk (c ^ (r & 7))
+          *slot0 = o0;
+          *slot1 = o1;
+        } else {
           // route the 16 columns: they never straddle a destination because cols_per_dest % 16 == 0
           const int dest = g.n_dest > 1 ? col0 / g.cols_per_dest : 0;
           const int dcol = g.n_dest > 1 ? col0 - dest * g.cols_per_dest : col0;
-          const long long drow = g.dst_row_offset + row;
-          if (g.out_fp32) {
-            float4* op = reinterpret_cast<float4*>(static_cast<float*>(g.dst[dest]) + drow * g.ldc + dcol);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) op[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          } else {
-            uint4* op = reinterpret_cast<uint4*>(static_cast<unsigned short*>(g.dst[dest]) + drow * g.ldc + dcol);
-            uint4 o0, o1;
-            o0.x = pack2(v[0], v[1], g.is_fp16); o0.y = pack2(v[2], v[3], g.is_fp16);
-            o0.z = pack2(v[4], v[5], g.is_fp16); o0.w = pack2(v[6], v[7], g.is_fp16);
-            o1.x = pack2(v[8], v[9], g.is_fp16); o1.y = pack2(v[10], v[11], g.is_fp16);
-            o1.z = pack2(v[12], v[13], g.is_fp16); o1.w = pack2(v[14], v[15], g.is_fp16);
-            op[0] = o0;
-            op[1] = o1;
-          }
+          uint4* op = reinterpret_cast<uint4*>(static_cast<unsigned short*>(g.dst[dest]) + (g.dst_row_offset + row) * g.ldc + dcol);
+          op[0] = o0;
+          op[1] = o1;
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
       if (g.tma_store) {
         fence_async_smem();                                  // generic-proxy writes -> visible to the bulk copy engine
-        epilogue_bar_sync();
-        if (warp == 2 && lane == 0) {
+        // with several staging buffers the store issued one tile ago must have drained before the barrier lets a
+        // later tile write (or prefetch) there; it was issued a whole tile earlier, so this rarely waits
+        if (leader && g.out_bufs >= 2) tma_store_wait_read<0>();
+        epilogue_bar_sync(epi_threads);
+        if (leader) {
           const int tile_col0 = n_chunk * g.block_n;
           const int y = (int)(g.dst_row_offset + (long long)m_tile * BLOCK_M);
           for (int pnl = 0; pnl < g.block_n / 64; ++pnl) {
@@ -443,11 +515,12 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           }
           tma_store_commit();
         }
-        if (g.out_bufs == 2) out_sel ^= 1;
+        if (g.out_bufs >= 2) out_sel = (out_sel + 1 == g.out_bufs) ? 0 : out_sel + 1;
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-    if (g.tma_store && warp == 2 && lane == 0) tma_store_wait_all();
+    if (!ok) cp_async_wait_all();                            // staged copies of the abandoned tile
+    if (g.tma_store && leader) tma_store_wait_all();
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(g.status, 3); }
   }
 
@@ -499,17 +572,17 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-int pick_block_n(int n, int cols_per_dest) {
+int pick_block_n(int n, int cap) {
   const int cands[] = {256, 192, 128, 96, 64, 48, 32, 16};
   for (int c : cands)
-    if (n % c == 0) return c;
+    if (c <= cap && n % c == 0) return c;
   return 0;
 }
 
 }  // namespace
 
 extern "C" int bf_gemm_supported(int M, int N, int K) {
-  return (M > 0 && K >= BLOCK_K && K % BLOCK_K == 0 && N >= 16 && pick_block_n(N, N) > 0) ? 1 : 0;
+  return (M > 0 && K >= BLOCK_K && K % BLOCK_K == 0 && N >= 16 && pick_block_n(N, 256) > 0) ? 1 : 0;
 }
 
 extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
@@ -521,7 +594,13 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
     return (int)cudaErrorInvalidValue;
   GemmArgs g;
   g.M = p->M; g.N = p->N; g.K = p->K;
-  g.block_n = pick_block_n(p->N, cols_per_dest);
+  // a residual / mask tile is staged in the output buffers: 128-wide tiles leave room for three of them
+  const bool wants_staging = (p->residual != nullptr || p->relu_mask != nullptr) && !p->out_fp32;
+  g.block_n = pick_block_n(p->N, 256);
+  if (wants_staging) {
+    const int capped = pick_block_n(p->N, 128);
+    if (capped > 0 && capped % 64 == 0) g.block_n = capped;
+  }
   g.n_chunks = p->N / g.block_n;
   g.m_tiles = (p->M + BLOCK_M - 1) / BLOCK_M;
   g.is_fp16 = p->dtype == BF_FP16 ? 1 : 0;
@@ -546,8 +625,9 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   for (int i = 0; i < p->n_dest && tma_ok; ++i) tma_ok = ((uintptr_t)p->dst[i]) % 16 == 0;
   g.tma_store = 0; g.out_bufs = 0; g.stages = MAX_STAGES;
   if (tma_ok) {
-    const int plans[4][2] = {{4, 2}, {3, 2}, {4, 1}, {3, 1}};
+    const int plans[6][2] = {{4, 3}, {3, 3}, {4, 2}, {3, 2}, {4, 1}, {3, 1}};
     for (const auto& pl : plans) {
+      if (pl[1] == 3 && !wants_staging) continue;
       if (pl[0] * stage_bytes + pl[1] * out_bytes <= budget) { g.stages = pl[0]; g.out_bufs = pl[1]; g.tma_store = 1; break; }
     }
   }
@@ -563,17 +643,47 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
     }
   }
   const size_t smem = 1024 + g.stages * stage_bytes + (size_t)g.out_bufs * out_bytes + sizeof(Control) + 64 + bias_bytes;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+  g.n_groups = (g.block_n % 64 == 0) ? 4 : (g.block_n % 32 == 0) ? 2 : 1;
+  // epilogue specialisation: the combinations the model layers use on bf16; everything else takes the generic kernel
+  int epi = -1;
+  if (!g.is_fp16 && !p->out_fp32) {
+    int f = 0;
+    if (p->bias) f |= EPI_BIAS;
+    if (p->act == 1) f |= EPI_RELU;
+    if (p->act == 2) f |= EPI_GELU;
+    if (p->dropout_p > 0.f) f |= EPI_DROP;
+    if (p->residual) f |= EPI_RES;
+    if (p->relu_mask) f |= EPI_MASK;
+    if (g.out_scale != 1.f) f |= EPI_SCALE;
+    if (f == 0 || f == EPI_BIAS) epi = f;
+    else if ((f | EPI_DROP) == (EPI_BIAS | EPI_DROP | EPI_RES)) epi = EPI_BIAS | EPI_DROP | EPI_RES;
+    else if ((f | EPI_DROP) == (EPI_BIAS | EPI_RELU | EPI_DROP)) epi = EPI_BIAS | EPI_RELU | EPI_DROP;
+    else if ((f | EPI_SCALE) == (EPI_MASK | EPI_SCALE)) epi = EPI_MASK | EPI_SCALE;
+  }
+  void (*kern)(const CUtensorMap, const CUtensorMap, const OutMaps, const GemmArgs) = gemm_tn_tcgen05_kernel<-1>;
+  switch (epi) {
+    case 0: kern = gemm_tn_tcgen05_kernel<0>; break;
+    case EPI_BIAS: kern = gemm_tn_tcgen05_kernel<EPI_BIAS>; break;
+    case EPI_BIAS | EPI_DROP | EPI_RES: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_DROP | EPI_RES>; break;
+    case EPI_BIAS | EPI_RELU | EPI_DROP: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_RELU | EPI_DROP>; break;
+    case EPI_MASK | EPI_SCALE: kern = gemm_tn_tcgen05_kernel<EPI_MASK | EPI_SCALE>; break;
+    default: break;
+  }
+  {
+    static bool attr_set[8] = {false, false, false, false, false, false, false, false};
+    const int slot = epi < 0 ? 0 : epi == 0 ? 1 : epi == EPI_BIAS ? 2 : epi == (EPI_BIAS | EPI_DROP | EPI_RES) ? 3
+                     : epi == (EPI_BIAS | EPI_RELU | EPI_DROP) ? 4 : 5;
+    if (!attr_set[slot]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return (int)e;
+      attr_set[slot] = true;
+    }
   }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int total = g.m_tiles * g.n_chunks;
   const int grid = total < sms ? total : sms;
-  gemm_tn_tcgen05_kernel<<<grid, NUM_THREADS, smem, st>>>(map_a, map_b, omaps, g);
+  kern<<<grid, NUM_THREADS, smem, st>>>(map_a, map_b, omaps, g);
   return (int)cudaGetLastError();
 }
