@@ -123,6 +123,7 @@ int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma, const flo
                      cudaStream_t st);
 int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* stats,
                      const float* gamma, void* dx, long long lddx, float* dgamma /* += */, float* dbeta /* += */,
+                     float* dxsum /* += column sums of dx, or NULL; 16-bit rows of 64/128/256 columns only */,
                      long long rows, int h, int dtype, cudaStream_t st);
 int bf_colsum(const void* x, long long ldx, long long rows, int cols /* % 8 == 0 */, float* out /* += */, int dtype,
               cudaStream_t st);

@@ -279,16 +279,24 @@ std::vector<Tensor> layernorm_fwd(Tensor x, Tensor gamma, Tensor beta, double ep
   return {y, stats};
 }
 
-std::vector<Tensor> layernorm_bwd(Tensor dy, Tensor x, Tensor stats, Tensor gamma) {
+std::vector<Tensor> layernorm_bwd(Tensor dy, Tensor x, Tensor stats, Tensor gamma, bool want_dxsum) {
   TORCH_CHECK(dy.is_cuda() && dy.dim() == 2 && dy.stride(1) == 1 && x.stride(1) == 1 && dy.scalar_type() == x.scalar_type());
   c10::cuda::CUDAGuard guard(x.device());
   Tensor dx = torch::empty({x.size(0), x.size(1)}, x.options());
   Tensor dgamma = torch::zeros({x.size(1)}, x.options().dtype(torch::kFloat));
   Tensor dbeta = torch::zeros({x.size(1)}, x.options().dtype(torch::kFloat));
+  const int64_t h = x.size(1);
+  const bool wide = x.scalar_type() != torch::kFloat && (h == 64 || h == 128 || h == 256) &&
+                    (dy.stride(0) * 2) % 16 == 0 && (x.stride(0) * 2) % 16 == 0 &&
+                    ((uintptr_t)dy.data_ptr()) % 16 == 0 && ((uintptr_t)x.data_ptr()) % 16 == 0;
+  Tensor dxsum;
+  if (want_dxsum && wide) dxsum = torch::zeros({h}, x.options().dtype(torch::kFloat));
   check_cuda(bf_layernorm_bwd(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), stats.data_ptr<float>(),
                               gamma.data_ptr<float>(), dx.data_ptr(), dx.stride(0), dgamma.data_ptr<float>(),
-                              dbeta.data_ptr<float>(), x.size(0), (int)x.size(1), dtype_code(x),
-                              at::cuda::getCurrentCUDAStream()), "layernorm_bwd");
+                              dbeta.data_ptr<float>(), dxsum.defined() ? dxsum.data_ptr<float>() : nullptr,
+                              x.size(0), (int)h, dtype_code(x), at::cuda::getCurrentCUDAStream()), "layernorm_bwd");
+  if (want_dxsum && !wide) dxsum = dx.sum(0, /*keepdim=*/false, torch::kFloat);
+  if (want_dxsum) return {dx, dgamma, dbeta, dxsum};
   return {dx, dgamma, dbeta};
 }
 

@@ -233,7 +233,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int k_panels = g.K / BLOCK_K;
+  const int k_panels = (g.K + BLOCK_K - 1) / BLOCK_K;   // a ragged last panel is zero-filled by TMA (both operands)
   const int total_tiles = g.m_tiles * g.n_chunks;
   const uint32_t tmem_cols = (2 * g.block_n <= 32) ? 32 : (2 * g.block_n <= 64) ? 64 : (2 * g.block_n <= 128) ? 128
                             : (2 * g.block_n <= 256) ? 256 : 512;
@@ -582,7 +582,8 @@ int pick_block_n(int n, int cap) {
 }  // namespace
 
 extern "C" int bf_gemm_supported(int M, int N, int K) {
-  return (M > 0 && K >= BLOCK_K && K % BLOCK_K == 0 && N >= 16 && pick_block_n(N, 256) > 0) ? 1 : 0;
+  // K only has to keep rows 16-byte aligned: the tensor maps zero-fill the tail of the last 64-element panel
+  return (M > 0 && K >= BLOCK_K && K % 8 == 0 && N >= 16 && pick_block_n(N, 256) > 0) ? 1 : 0;
 }
 
 extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {

@@ -198,6 +198,152 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const T* __restrict__ dy, l
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Wide variants for 16-bit rows of 64 / 128 / 256 columns: LPR = h / 8 lanes share a row (one 16-byte vector per
+// lane), so a warp covers 32 / LPR rows per pass and U passes are loaded before any arithmetic.  A warp therefore
+// keeps U * 32 independent 16-byte loads in flight instead of one row's worth, which is what a bandwidth-bound
+// row kernel needs on 8 TB/s memory; gamma / beta live in registers for the whole kernel.
+// ---------------------------------------------------------------------------------------------------
+template <int LPR> __device__ __forceinline__ float row_sum(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const T* t = reinterpret_cast<const T*>(&u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = to_f<T>(t[i]);
+}
+template <typename T> __device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  T* t = reinterpret_cast<T*>(&u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) t[i] = from_f<T>(f[i]);
+  return u;
+}
+
+template <typename T, int LPR>
+__global__ void __launch_bounds__(256, 3) ln_fwd_wide_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ gamma,
+                                                          const float* __restrict__ beta, T* __restrict__ y, long long ldy,
+                                                          float* __restrict__ stats, long long rows, float eps) {
+  constexpr int RPW = 32 / LPR, U = 4, H = LPR * 8;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LPR, c0 = (lane % LPR) * 8;
+  float gam[8], bet[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { gam[i] = gamma[c0 + i]; bet[i] = beta[c0 + i]; }
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r0 = warp * (U * RPW); r0 < rows; r0 += warps * (U * RPW)) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + sub;
+      raw[u] = row < rows ? *reinterpret_cast<const uint4*>(x + row * ldx + c0) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + sub;
+      float v[8];
+      unpack8<T>(raw[u], v);
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += v[i];
+      const float mean = row_sum<LPR>(s) * (1.f / H);
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { v[i] -= mean; q += v[i] * v[i]; }
+      const float rstd = rsqrtf(row_sum<LPR>(q) * (1.f / H) + eps);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd * gam[i] + bet[i];
+      if (row < rows) {
+        *reinterpret_cast<uint4*>(y + row * ldy + c0) = pack8<T>(v);
+        if (stats && (lane % LPR) == 0) *reinterpret_cast<float2*>(stats + 2 * row) = make_float2(mean, rstd);
+      }
+    }
+  }
+}
+
+// dxsum (optional) receives the column sums of dx: the bias gradient of the linear layer that produced the
+// normalised row, for free.
+template <typename T, int LPR>
+__global__ void __launch_bounds__(256, 2) ln_bwd_wide_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict__ x,
+                                                          long long ldx, const float* __restrict__ stats,
+                                                          const float* __restrict__ gamma, T* __restrict__ dx, long long lddx,
+                                                          float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                          float* __restrict__ dxsum, long long rows) {
+  constexpr int RPW = 32 / LPR, U = 2, H = LPR * 8;
+  extern __shared__ float s_acc[];      // [3, H]
+  for (int i = threadIdx.x; i < 3 * H; i += blockDim.x) s_acc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LPR, c0 = (lane % LPR) * 8;
+  float gam[8], dg[8], db[8], dxs[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { gam[i] = gamma[c0 + i]; dg[i] = 0.f; db[i] = 0.f; dxs[i] = 0.f; }
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r0 = warp * (U * RPW); r0 < rows; r0 += warps * (U * RPW)) {
+    uint4 rx[U], rd[U];
+    float2 st[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + sub;
+      const bool ok = row < rows;
+      rx[u] = ok ? *reinterpret_cast<const uint4*>(x + row * ldx + c0) : make_uint4(0, 0, 0, 0);
+      rd[u] = ok ? *reinterpret_cast<const uint4*>(dy + row * lddy + c0) : make_uint4(0, 0, 0, 0);
+      st[u] = ok ? *reinterpret_cast<const float2*>(stats + 2 * row) : make_float2(0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r0 + u * RPW + sub;
+      const float mean = st[u].x, rstd = st[u].y;
+      float xv[8], dv[8];
+      unpack8<T>(rx[u], xv);
+      unpack8<T>(rd[u], dv);
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        xv[i] = (xv[i] - mean) * rstd;            // xhat (0 for rows past the end: rstd = 0)
+        dg[i] += dv[i] * xv[i];
+        db[i] += dv[i];
+        dv[i] *= gam[i];                          // g * dy
+        s1 += dv[i];
+        s2 += dv[i] * xv[i];
+      }
+      s1 = row_sum<LPR>(s1) * (1.f / H);
+      s2 = row_sum<LPR>(s2) * (1.f / H);
+      uint4 o;
+      {
+        float ov[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ov[i] = rstd * (dv[i] - s1 - xv[i] * s2);
+        o = pack8<T>(ov);
+        if (dxsum) {
+          // sum what is stored (the rounded value), like a column sum of the stored tensor would
+          float rv[8];
+          unpack8<T>(o, rv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dxs[i] += rv[i];
+        }
+      }
+      if (row < rows) *reinterpret_cast<uint4*>(dx + row * lddx + c0) = o;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    atomicAdd(&s_acc[c0 + i], dg[i]);
+    atomicAdd(&s_acc[H + c0 + i], db[i]);
+    if (dxsum) atomicAdd(&s_acc[2 * H + c0 + i], dxs[i]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    atomicAdd(dgamma + i, s_acc[i]);
+    atomicAdd(dbeta + i, s_acc[H + i]);
+    if (dxsum) atomicAdd(dxsum + i, s_acc[2 * H + i]);
+  }
+}
+
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x = (x ^ (x >> 16)) * 0x7FEB352Du;
   x = (x ^ (x >> 15)) * 0x846CA68Bu;
@@ -290,6 +436,20 @@ static bool ln_packed_ok(int h, int dtype, const void* a, long long lda, const v
   return ((uintptr_t)a % 16 == 0) && ((uintptr_t)b2 % 16 == 0) && ((lda * esz) % 16 == 0) && ((ldb * esz) % 16 == 0);
 }
 
+static bool ln_wide_ok(int h, int dtype, const void* a, long long lda, const void* b2, long long ldb) {
+  if (dtype == BF_FP32 || !(h == 64 || h == 128 || h == 256)) return false;
+  return ((uintptr_t)a % 16 == 0) && ((uintptr_t)b2 % 16 == 0) && ((lda * 2) % 16 == 0) && ((ldb * 2) % 16 == 0);
+}
+
+#define BF_LN_WIDE_SWITCH(DT, LPRV, CALL)                                                      \
+  if (DT == BF_BF16) {                                                                         \
+    if (LPRV == 8) { CALL(__nv_bfloat16, 8); } else if (LPRV == 16) { CALL(__nv_bfloat16, 16); } \
+    else { CALL(__nv_bfloat16, 32); }                                                          \
+  } else {                                                                                     \
+    if (LPRV == 8) { CALL(__half, 8); } else if (LPRV == 16) { CALL(__half, 16); }             \
+    else { CALL(__half, 32); }                                                                 \
+  }
+
 #define BF_LN_PER_SWITCH(T, PERV, KERNEL_CALL)              \
   switch (PERV) {                                            \
     case 2: { constexpr int P_ = 2; KERNEL_CALL; break; }    \
@@ -304,6 +464,15 @@ extern "C" int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma
                                 cudaStream_t st) {
   if (h > 32 * LN_MAX_PER_LANE || h < 1) return (int)cudaErrorInvalidValue;
   if (rows == 0) return 0;
+  if (ln_wide_ok(h, dtype, x, ldx, y, ldy)) {
+    const int lpr = h / 8;
+    long long wb = (rows + 8 * 4 * (32 / lpr) - 1) / (8 * 4 * (32 / lpr));
+    if (wb > 148 * 16) wb = 148 * 16;
+#define WIDE(T, L) ln_fwd_wide_kernel<T, L><<<(unsigned)wb, 256, 0, st>>>((const T*)x, ldx, gamma, beta, (T*)y, ldy, stats, rows, eps)
+    BF_LN_WIDE_SWITCH(dtype, lpr, WIDE)
+#undef WIDE
+    return (int)cudaGetLastError();
+  }
   long long blocks = (rows * 32 + 255) / 256;
   if (blocks > 148 * 64) blocks = 148 * 64;      // many short-lived warps hide the row-load latency better than a few long ones
   const int per = ln_packed_ok(h, dtype, x, ldx, y, ldy) ? h / 32 : 0;
@@ -315,9 +484,20 @@ extern "C" int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma
 
 extern "C" int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* stats,
                                 const float* gamma, void* dx, long long lddx, float* dgamma, float* dbeta,
-                                long long rows, int h, int dtype, cudaStream_t st) {
+                                float* dxsum, long long rows, int h, int dtype, cudaStream_t st) {
   if (h > 32 * LN_MAX_PER_LANE || h < 1) return (int)cudaErrorInvalidValue;
   if (rows == 0) return 0;
+  if (ln_wide_ok(h, dtype, x, ldx, dy, lddy) && ln_wide_ok(h, dtype, dx, lddx, dx, lddx)) {
+    const int lpr = h / 8;
+    long long wb = (rows + 8 * 2 * (32 / lpr) - 1) / (8 * 2 * (32 / lpr));
+    if (wb > 148 * 8) wb = 148 * 8;
+    const size_t wsm = sizeof(float) * 3 * h;
+#define WIDE(T, L) ln_bwd_wide_kernel<T, L><<<(unsigned)wb, 256, wsm, st>>>((const T*)dy, lddy, (const T*)x, ldx, stats, gamma, (T*)dx, lddx, dgamma, dbeta, dxsum, rows)
+    BF_LN_WIDE_SWITCH(dtype, lpr, WIDE)
+#undef WIDE
+    return (int)cudaGetLastError();
+  }
+  if (dxsum) return (int)cudaErrorNotSupported;   // only the wide kernels produce the extra column sums
   long long blocks = (rows * 32 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   const size_t smem = sizeof(float) * 2 * h;

@@ -106,6 +106,24 @@ def apply_tier(layer, mode: str, x, **kwargs):
     return checkpoint(_full, x, use_reentrant=False)
 
 
+def encode_features(encoder: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """``encoder(x)`` for a 2-D feature matrix whose columns may have been zero-padded by the caller.
+
+    Feature widths such as 269 leave rows unaligned, which sends the library GEMM to slow legacy kernels; the
+    trainer therefore pads the feature matrix once to a multiple of 8 columns and the weight is padded to match
+    here (the gradient of the padding is dropped by autograd).  16-bit CUDA inputs take the tcgen05 GEMM."""
+    w = encoder.weight
+    extra = x.size(-1) - w.size(1)
+    if extra < 0:
+        raise ValueError(f"feature matrix has {x.size(-1)} columns, encoder expects {w.size(1)}")
+    if extra:
+        w = F.pad(w, (0, extra))
+    if x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16):
+        from ..ops.gemm import fused_linear
+        return fused_linear(x, w, encoder.bias)
+    return F.linear(x, w, encoder.bias)
+
+
 class NodeModelBase(nn.Module):
     """Activation-checkpoint control shared by all models
     (e.g. models/gt_dist_node_level.py:741-775)."""

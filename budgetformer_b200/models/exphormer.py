@@ -14,7 +14,7 @@ from torch.utils.checkpoint import checkpoint
 
 from ..parallel.initialize import get_sequence_parallel_group, get_sequence_parallel_rank
 from ..parallel.sp_ops import DistributedAttentionNodeLevel
-from .common import NodeModelBase, SparseCoreAttention, init_params
+from .common import NodeModelBase, SparseCoreAttention, encode_features, init_params
 
 
 class ExphormerCoreAttention(SparseCoreAttention):
@@ -105,9 +105,9 @@ class Exphormer(NodeModelBase):
         self._init_ckpt_state()
 
     def forward_logits(self, x, attn_bias, edge_index, attn_type=None):
-        x = self.input_dropout(self.node_encoder(x.unsqueeze(0)))
+        x = self.input_dropout(encode_features(self.node_encoder, x).unsqueeze(0))
         x = self._run_layers(x, attn_bias=attn_bias, edge_index=edge_index, attn_type=attn_type)
-        return self.output_proj(x[0])
+        return self.output_proj(x.squeeze(0))
 
     def forward(self, x, attn_bias, edge_index, attn_type=None):
         return F.log_softmax(self.forward_logits(x, attn_bias, edge_index, attn_type), dim=1)

@@ -16,7 +16,7 @@ from torch.utils.checkpoint import checkpoint
 
 from ..parallel.initialize import get_sequence_parallel_group
 from ..parallel.sp_ops import DistributedAttentionNodeLevel
-from .common import NodeModelBase, SparseCoreAttention
+from .common import NodeModelBase, SparseCoreAttention, encode_features
 
 
 def _gaussian_orthogonal_random_matrix(nb_rows, nb_columns, device=None):
@@ -161,9 +161,9 @@ class GraphGPS(NodeModelBase):
                 core.performer.redraw_projection_matrix(device=device)
 
     def forward_logits(self, x, attn_bias, edge_index, attn_type=None):
-        x = self.node_encoder(x.unsqueeze(0))
+        x = encode_features(self.node_encoder, x).unsqueeze(0)
         x = self._run_layers(x, attn_bias=attn_bias, edge_index=edge_index, attn_type=attn_type)
-        return self.output_proj(x[0])
+        return self.output_proj(x.squeeze(0))
 
     def forward(self, x, attn_bias, edge_index, attn_type=None):
         return F.log_softmax(self.forward_logits(x, attn_bias, edge_index, attn_type), dim=1)

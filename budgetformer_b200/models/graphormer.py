@@ -14,7 +14,7 @@ from torch.utils.checkpoint import checkpoint
 
 from ..parallel.initialize import get_sequence_parallel_group
 from ..parallel.sp_ops import DistributedAttentionNoMerge
-from .common import NodeModelBase, SparseCoreAttention, init_params
+from .common import NodeModelBase, SparseCoreAttention, encode_features, init_params
 
 
 class FeedForwardNetwork(nn.Module):
@@ -129,7 +129,7 @@ class Graphormer(NodeModelBase):
         return proj.permute(2, 0, 1).unsqueeze(0)                               # [1, H, S_q, S_k]
 
     def forward_logits(self, x, attn_bias, edge_index, perturb=None, attn_type=None):
-        x = self.node_encoder(x.unsqueeze(0))
+        x = encode_features(self.node_encoder, x).unsqueeze(0)
         if perturb is not None:
             x = x + perturb
         if self.num_global_node > 0:

@@ -13,7 +13,7 @@ from torch.utils.checkpoint import checkpoint
 
 from ..parallel.initialize import get_sequence_parallel_group
 from ..parallel.sp_ops import DistributedAttentionNodeLevel
-from .common import NodeModelBase, SparseCoreAttention, init_params
+from .common import NodeModelBase, SparseCoreAttention, encode_features, init_params
 
 
 class CoreAttention(SparseCoreAttention):
@@ -105,12 +105,12 @@ class GT(NodeModelBase):
         self._init_ckpt_state()
 
     def forward_logits(self, x, attn_bias, edge_index, perturb=None, attn_type=None):
-        x = self.node_encoder(x.unsqueeze(0))
+        x = encode_features(self.node_encoder, x).unsqueeze(0)
         if perturb is not None:
             x = x - perturb
         x = self.input_dropout(x)
         x = self._run_layers(x, edge_index=edge_index, attn_type=attn_type)
-        return self.MLP_layer(x[0])
+        return self.MLP_layer(x.squeeze(0))
 
     def forward(self, x, attn_bias, edge_index, perturb=None, attn_type=None):
         return F.log_softmax(self.forward_logits(x, attn_bias, edge_index, perturb, attn_type), dim=1)

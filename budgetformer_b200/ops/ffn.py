@@ -18,33 +18,44 @@ from .norm import column_sum, hash_dropout, new_seed
 
 class _FusedFFNRelu(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w1, b1, w2, b2, residual, p1, p2, seed1, seed2):
+    def forward(ctx, x, w1, b1, w2, b2, residual, p1, p2, seed1, seed2, slot=None):
         w1h, w2h = w1.to(x.dtype), w2.to(x.dtype)
         h = gemm.gemm_tn(x, w1h, b1, "relu", dropout_p=p1, dropout_seed=seed1)
         y = gemm.gemm_tn(h, w2h, b2, None, dropout_p=p2, dropout_seed=seed2, residual=residual)
         ctx.save_for_backward(x, h, w1h, w2h)
+        # residual FFN (the residual is the input itself): backward adds the pass-through gradient in the epilogue of
+        # the input-gradient GEMM instead of leaving a separate full-size addition to autograd
+        res_is_x = residual is not None and residual.data_ptr() == x.data_ptr() and residual.shape == x.shape \
+            and residual.stride() == x.stride()
         ctx.cfg = (float(p1), float(p2), int(seed1), int(seed2), residual is not None, w1.dtype,
-                   b1 is not None, b2 is not None)
+                   b1 is not None, b2 is not None, res_is_x)
+        ctx.slot = slot
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, h, w1h, w2h = ctx.saved_tensors
-        p1, p2, seed1, seed2, has_res, wdtype, has_b1, has_b2 = ctx.cfg
+        p1, p2, seed1, seed2, has_res, wdtype, has_b1, has_b2, res_is_x = ctx.cfg
+        handed = ctx.slot.take(dy) if ctx.slot is not None else None
         dy = dy.contiguous()
         g2 = hash_dropout(dy, seed2, p2) if p2 > 0 else dy
         dh = gemm.gemm_tn(g2, w2h.t().contiguous(), relu_mask=h, out_scale=1.0 / (1.0 - p1) if p1 > 0 else 1.0)
-        dx = gemm.gemm_tn(dh, w1h.t().contiguous())
+        dx = gemm.gemm_tn(dh, w1h.t().contiguous(), residual=dy if res_is_x else None)
         dw2 = torch.matmul(g2.t(), h).to(wdtype)
         dw1 = torch.matmul(dh.t(), x).to(wdtype)
-        db2 = column_sum(g2).to(wdtype) if has_b2 else None
+        if has_b2:
+            db2 = (handed if (handed is not None and p2 == 0) else column_sum(g2)).to(wdtype)
+        else:
+            db2 = None
         db1 = column_sum(dh).to(wdtype) if has_b1 else None
-        return dx, dw1, db1, dw2, db2, (dy if has_res else None), None, None, None, None
+        dres = dy if (has_res and not res_is_x) else None
+        return dx, dw1, db1, dw2, db2, dres, None, None, None, None, None
 
 
 def fused_ffn(x: torch.Tensor, w1, b1, w2, b2, *, act: str = "relu", residual: Optional[torch.Tensor] = None,
-              p1: float = 0.0, p2: float = 0.0, training: bool = True) -> torch.Tensor:
-    """2-D ``x`` ``[rows, h]``; ``residual`` is added last (pass ``x`` for a residual FFN)."""
+              p1: float = 0.0, p2: float = 0.0, training: bool = True, out_grad_colsum=None) -> torch.Tensor:
+    """2-D ``x`` ``[rows, h]``; ``residual`` is added last (pass ``x`` for a residual FFN).  ``out_grad_colsum`` is an
+    optional ``ops.norm.ColsumSlot`` filled by the LayerNorm that consumes the result (bias gradient for free)."""
     if not training:
         p1 = p2 = 0.0
     n1, k1 = w1.shape
@@ -52,7 +63,7 @@ def fused_ffn(x: torch.Tensor, w1, b1, w2, b2, *, act: str = "relu", residual: O
         and gemm.supported(x.size(0), w2.size(0), w2.size(1), x.dtype)
     if ok and act == "relu":
         return _FusedFFNRelu.apply(x, w1, b1, w2, b2, residual, p1, p2, new_seed() if p1 > 0 else 0,
-                                   new_seed() if p2 > 0 else 0)
+                                   new_seed() if p2 > 0 else 0, out_grad_colsum)
     if ok and act == "gelu":
         z = gemm.fused_linear(x, w1, b1)
         hdn = F.gelu(z)

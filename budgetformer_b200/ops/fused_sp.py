@@ -31,7 +31,7 @@ from ..parallel import symm
 from . import _ext, gemm
 from .edge_attention import _VARIANTS
 from .ffn import fused_ffn
-from .norm import column_sum, hash_dropout, layer_norm, new_seed
+from .norm import ColsumSlot, column_sum, hash_dropout, layer_norm, new_seed
 
 
 class SPContext:
@@ -81,7 +81,7 @@ def _push_gemm(x, w, bias, dst_ptrs, row0, ldc, dropout_p=0.0, seed=0):
 
 class _QKVPush(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, wq, wk, wv, bq, bk, bv, sp: SPContext, layer: int):
+    def forward(ctx, x, wq, wk, wv, bq, bk, bv, sp: SPContext, layer: int, passthrough: bool = False):
         w = torch.cat([wq, wk, wv], 0).to(x.dtype)[sp.perm].contiguous()
         b = None
         if bq is not None:
@@ -91,10 +91,14 @@ class _QKVPush(torch.autograd.Function):
         sp.sw.barrier(0)
         ctx.sp, ctx.has_bias, ctx.wdtype = sp, bq is not None, wq.dtype
         ctx.save_for_backward(x, w)
+        if passthrough:
+            # the input doubles as the residual of the output projection: handing it through this function routes the
+            # residual's gradient back here, where the input-gradient GEMM adds it in its epilogue
+            return buf.tensor.detach(), x
         return buf.tensor.detach()
 
     @staticmethod
-    def backward(ctx, dqkv):
+    def backward(ctx, dqkv, dres=None):
         sp: SPContext = ctx.sp
         x, w = ctx.saved_tensors
         buf = sp.dqkv
@@ -109,7 +113,9 @@ class _QKVPush(torch.autograd.Function):
             sp.sw.barrier(0)                                         # all reads done before the buffer is reused
         else:
             dloc = buf.tensor
-        dx = gemm.gemm_tn(dloc, w.t().contiguous())
+        if dres is not None:
+            dres = dres.to(x.dtype).contiguous()
+        dx = gemm.gemm_tn(dloc, w.t().contiguous(), residual=dres)
         dw = torch.matmul(dloc.t(), x).float()[sp.inv_perm]
         dwq, dwk, dwv = (t.to(ctx.wdtype) for t in dw.split(sp.h, 0))
         if ctx.has_bias:
@@ -117,7 +123,7 @@ class _QKVPush(torch.autograd.Function):
             dbq, dbk, dbv = (t.to(ctx.wdtype) for t in db.split(sp.h, 0))
         else:
             dbq = dbk = dbv = None
-        return dx, dwq, dwk, dwv, dbq, dbk, dbv, None, None
+        return dx, dwq, dwk, dwv, dbq, dbk, dbv, None, None, None
 
 
 class _PackedEdgeAttention(torch.autograd.Function):
@@ -181,7 +187,7 @@ class _CtxPullOutProj(torch.autograd.Function):
     all head owners.  Without a projection (Exphormer) ``y = residual + drop_post(a)``."""
 
     @staticmethod
-    def forward(ctx, ctx_full, wo, bo, residual, sp: SPContext, p_pre, p_post, seed_pre, seed_post):
+    def forward(ctx, ctx_full, wo, bo, residual, sp: SPContext, p_pre, p_post, seed_pre, seed_post, slot=None):
         dt = ctx_full.dtype
         if sp.P > 1:
             sp.sw.barrier(0)                                         # every head owner has written its context
@@ -202,7 +208,7 @@ class _CtxPullOutProj(torch.autograd.Function):
             if residual is not None:
                 y = y + residual
             ctx.save_for_backward()
-        ctx.sp = sp
+        ctx.sp, ctx.slot = sp, slot
         ctx.cfg = (float(p_pre), float(p_post), int(seed_pre), int(seed_post), residual is not None, wo is not None,
                    bo is not None, wo.dtype if wo is not None else None)
         return y
@@ -211,6 +217,7 @@ class _CtxPullOutProj(torch.autograd.Function):
     def backward(ctx, dy):
         sp: SPContext = ctx.sp
         p_pre, p_post, seed_pre, seed_post, has_res, has_w, has_b, wdtype = ctx.cfg
+        handed = ctx.slot.take(dy) if ctx.slot is not None else None
         dy = dy.contiguous()
         g = hash_dropout(dy, seed_post, p_post) if p_post > 0 else dy
         dbuf = sp.dctx
@@ -220,14 +227,15 @@ class _CtxPullOutProj(torch.autograd.Function):
             # d(context) = (g W_o) [* pre-dropout mask], pushed to the head owners by the GEMM epilogue
             _push_gemm(g, w.t().contiguous(), None, dbuf.ptrs, sp.row0, sp.hl, dropout_p=p_pre, seed=seed_pre)
             dw = torch.matmul(g.t(), a).to(wdtype)
-            db = column_sum(g).to(wdtype) if has_b else None
+            if has_b:
+                db = (handed if (handed is not None and p_post == 0) else column_sum(g)).to(wdtype)
         else:
             da = hash_dropout(g, seed_pre, p_pre) if p_pre > 0 else g
             esz = da.element_size()
             _ext.load().peer_scatter_cols(dbuf.ptrs, sp.row0, sp.rows_local, sp.hl * esz, sp.hl * esz, da.contiguous())
             _ext.count_launches(1)
         sp.sw.barrier(0)                                             # all d(context) rows have landed
-        return dbuf.tensor, dw, db, (dy if has_res else None), None, None, None, None, None
+        return dbuf.tensor, dw, db, (dy if has_res else None), None, None, None, None, None, None
 
 
 def _ctx_ptrs_for(self, t):
@@ -248,18 +256,24 @@ def _core(layer):
     return getattr(d, "local_attn", d)
 
 
-def _attention(layer, x2d, graph: AttnGraph, sp: SPContext, idx: int):
+def _attention(layer, x2d, graph: AttnGraph, sp: SPContext, idx: int, passthrough: bool = False):
+    """Context of the layer's attention; with ``passthrough`` also the input routed through the projection function
+    (use it as the residual so that its gradient is added inside the input-gradient GEMM)."""
     mha = layer.self_attention
     core = _core(layer)
     qkv = _QKVPush.apply(x2d, mha.linear_q.weight, mha.linear_k.weight, mha.linear_v.weight, mha.linear_q.bias,
-                         mha.linear_k.bias, mha.linear_v.bias, sp, idx)
+                         mha.linear_k.bias, mha.linear_v.bias, sp, idx, passthrough)
+    xr = None
+    if passthrough:
+        qkv, xr = qkv
     variant = core.variant
     etab = core.edge_table() if variant == "exphormer" else None
     if variant == "exphormer" and (etab is None or graph.etype is None):
         variant, etab = "plain", None
     p_att = core.attention_dropout_rate if (variant == "gps" and layer.training) else 0.0
     tab = etab.to(torch.float32).contiguous() if etab is not None else None
-    return _PackedEdgeAttention.apply(qkv, tab, graph, sp, idx, _VARIANTS[variant], p_att, new_seed() if p_att > 0 else 0)
+    out = _PackedEdgeAttention.apply(qkv, tab, graph, sp, idx, _VARIANTS[variant], p_att, new_seed() if p_att > 0 else 0)
+    return (out, xr) if passthrough else out
 
 
 def _p(module, training) -> float:
@@ -267,17 +281,19 @@ def _p(module, training) -> float:
 
 
 def _gt_attn(layer, x, graph, sp, idx):
-    ctx = _attention(layer, x, graph, sp, idx)
+    ctx, xr = _attention(layer, x, graph, sp, idx, passthrough=True)
     p = _p(layer.self_attention_dropout, layer.training)
-    s = _CtxPullOutProj.apply(ctx, layer.O.weight, layer.O.bias, x, sp, p, 0.0, new_seed() if p > 0 else 0, 0)
-    return layer_norm(s, layer.layer_norm1.weight, layer.layer_norm1.bias, layer.layer_norm1.eps)
+    slot = ColsumSlot()                                   # LayerNorm backward -> bias gradient of the projection
+    s = _CtxPullOutProj.apply(ctx, layer.O.weight, layer.O.bias, xr, sp, p, 0.0, new_seed() if p > 0 else 0, 0, slot)
+    return layer_norm(s, layer.layer_norm1.weight, layer.layer_norm1.bias, layer.layer_norm1.eps, slot)
 
 
 def _gt_ffn(layer, x1):
     p = _p(layer.self_attention_dropout, layer.training)
+    slot = ColsumSlot()
     s = fused_ffn(x1, layer.FFN_layer1.weight, layer.FFN_layer1.bias, layer.FFN_layer2.weight, layer.FFN_layer2.bias,
-                  act="relu", residual=x1, p1=p, p2=0.0, training=layer.training)
-    return layer_norm(s, layer.layer_norm2.weight, layer.layer_norm2.bias, layer.layer_norm2.eps)
+                  act="relu", residual=x1, p1=p, p2=0.0, training=layer.training, out_grad_colsum=slot)
+    return layer_norm(s, layer.layer_norm2.weight, layer.layer_norm2.bias, layer.layer_norm2.eps, slot)
 
 
 def _graphormer_attn(layer, x, graph, sp, idx):
@@ -302,10 +318,10 @@ def _bn(norm, x):
 
 
 def _gps_attn(layer, x, graph, sp, idx):
-    ctx = _attention(layer, x, graph, sp, idx)
+    ctx, xr = _attention(layer, x, graph, sp, idx, passthrough=True)
     p = _p(layer.dropout1, layer.training)
     o = getattr(layer.self_attention, "out_proj", None)
-    s = _CtxPullOutProj.apply(ctx, None if o is None else o.weight, None if o is None else o.bias, x, sp, 0.0, p, 0,
+    s = _CtxPullOutProj.apply(ctx, None if o is None else o.weight, None if o is None else o.bias, xr, sp, 0.0, p, 0,
                               new_seed() if p > 0 else 0)
     return _bn(layer.norm1, s)
 
@@ -334,18 +350,19 @@ def _install(layer, idx: int, sp: SPContext, attn_fn, ffn_fn):
         if not usable(x, edge_index, attn_type, attn_bias):
             return portable_attn_only(x, attn_bias, edge_index, attn_type, **kw)
         graph = as_attn_graph(edge_index, sp.total_rows)
-        return attn_fn(self, x[0], graph, sp, idx).unsqueeze(0)
+        return attn_fn(self, x.squeeze(0), graph, sp, idx).unsqueeze(0)
 
     def forward_ffn_checkpointed(self, x):
         if not (x.is_cuda and x.dtype == sp.dtype):
             return portable_ffn_ckpt(x)
-        return checkpoint(lambda t: ffn_fn(self, t[0]).unsqueeze(0), x, use_reentrant=False)
+        return checkpoint(lambda t: ffn_fn(self, t.squeeze(0)).unsqueeze(0), x, use_reentrant=False)
 
     def forward(self, x, attn_bias=None, edge_index=None, attn_type=None, **kw):
         if not usable(x, edge_index, attn_type, attn_bias):
             return portable_forward(x, attn_bias, edge_index, attn_type, **kw)
         graph = as_attn_graph(edge_index, sp.total_rows)
-        return ffn_fn(self, attn_fn(self, x[0], graph, sp, idx)).unsqueeze(0)
+        # squeeze/unsqueeze are views in both directions (indexing would zero-fill and copy a full activation in backward)
+        return ffn_fn(self, attn_fn(self, x.squeeze(0), graph, sp, idx)).unsqueeze(0)
 
     layer.forward = types.MethodType(forward, layer)
     layer.forward_attn_only = types.MethodType(forward_attn_only, layer)

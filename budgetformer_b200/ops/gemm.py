@@ -3,7 +3,7 @@
 ``gemm_tn`` is the raw call ``C = A @ W.T`` with the fused epilogue; ``fused_linear`` is the autograd
 function used by the models on B200: forward and the input-gradient GEMM run on the tcgen05 kernel,
 the weight gradient ``dW = dY^T X`` (a plain tall-skinny reduction without any fusion opportunity) uses
-the library GEMM.  Shapes the kernel does not cover (K not a multiple of 64, N not a multiple of 16,
+the library GEMM.  Shapes the kernel does not cover (K not a multiple of 8, N not a multiple of 16,
 fp32 operands) fall back to ``torch.nn.functional.linear``."""
 from __future__ import annotations
 
@@ -38,7 +38,7 @@ def check_status(device) -> None:
 
 
 def supported(m: int, n: int, k: int, dtype) -> bool:
-    return dtype in (torch.bfloat16, torch.float16) and m > 0 and k % 64 == 0 and k >= 64 and n % 16 == 0 and n >= 16
+    return dtype in (torch.bfloat16, torch.float16) and m > 0 and k % 8 == 0 and k >= 64 and n % 16 == 0 and n >= 16
 
 
 def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
@@ -93,7 +93,8 @@ class _FusedLinear(torch.autograd.Function):
         has_res, p, seed, wdtype, has_bias = ctx.cfg
         dy = dy.contiguous()
         g = hash_dropout(dy, seed, p) if p > 0 else dy
-        dx = gemm_tn(g, w16.t().contiguous())            # dx = g @ W, expressed as g @ (W^T)^T
+        # dx = g @ W, expressed as g @ (W^T)^T; skipped for leaf inputs such as the feature matrix
+        dx = gemm_tn(g, w16.t().contiguous()) if ctx.needs_input_grad[0] else None
         dw = torch.matmul(g.t(), x).to(wdtype)
         db = column_sum(g).to(wdtype) if has_bias else None
         return dx, dw, db, (dy if has_res else None), None, None

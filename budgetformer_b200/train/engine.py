@@ -106,6 +106,10 @@ class FullGraphTrainer:
                 # under mixed precision the first layer consumes the features in the compute dtype anyway: keep the
                 # host copy (and every upload) in that dtype instead of casting on the device every step
                 self.x_host = self.x_host.to(self.amp_dtype)
+                pad = (-self.x_host.size(1)) % 8
+                if pad and args.model in ("gt", "graphormer", "graphgps", "exphormer"):
+                    # 16-byte aligned feature rows (e.g. 269 -> 272 columns): the encoder pads its weight to match
+                    self.x_host = torch.nn.functional.pad(self.x_host, (0, pad))
             self.x_host = self.x_host.pin_memory()
         self.x_local = self.x_host.to(self.device, non_blocking=True)
         if args.model == "graphormer" and args.num_global_node > 0:
