@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "bf_kernels.h"
 
@@ -60,6 +61,32 @@ template <> __device__ __forceinline__ void store_vec<__half>(__half* p, const f
 template <> __device__ __forceinline__ void store_vec<float>(float* p, const float* f) {
   *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
 }
+
+// A gathered row slice kept packed (one 16-byte register quad) and widened element by element where it is used:
+// the dQ pass holds several gathered slices at once, and packed they cost half the registers (four resident
+// blocks per SM instead of three).
+template <typename T> struct Raw;
+template <> struct Raw<__nv_bfloat16> {
+  uint4 u;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ float get(int i) const {
+    const uint32_t w = (i >> 1) == 0 ? u.x : (i >> 1) == 1 ? u.y : (i >> 1) == 2 ? u.z : u.w;
+    return (i & 1) ? __uint_as_float(w & 0xFFFF0000u) : __uint_as_float(w << 16);
+  }
+};
+template <> struct Raw<__half> {
+  uint4 u;
+  __device__ __forceinline__ void load(const __half* p) { u = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ float get(int i) const {
+    const uint32_t w = (i >> 1) == 0 ? u.x : (i >> 1) == 1 ? u.y : (i >> 1) == 2 ? u.z : u.w;
+    return __half2float(__ushort_as_half((unsigned short)((i & 1) ? (w >> 16) : (w & 0xFFFFu))));
+  }
+};
+template <> struct Raw<float> {
+  float4 f;
+  __device__ __forceinline__ void load(const float* p) { f = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ float get(int i) const { return i == 0 ? f.x : i == 1 ? f.y : i == 2 ? f.z : f.w; }
+};
 
 template <typename T> __device__ __forceinline__ T from_float(float x);
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
@@ -355,26 +382,50 @@ __device__ __forceinline__ void dq_edge4(const BwdArgs& b, int e, int end, int h
     j[u] = ok[u] ? __ldg(a.col + e + u) : 0;
     ty[u] = (EXPH && ok[u]) ? a.etype[e + u] : 0;
   }
-  float kf[NB][VN], vf[NB][VN];
+  if constexpr (!EXPH) {
+    // gathered k | v slices stay packed until used (64 registers: four resident blocks per SM)
+    Raw<T> kr[NB], vr[NB];
 #pragma unroll
-  for (int u = 0; u < NB; ++u) {
-    load_vec<T>(static_cast<const T*>(a.k) + (long long)j[u] * a.ldk + off, kf[u]);
-    load_vec<T>(static_cast<const T*>(a.v) + (long long)j[u] * a.ldv + off, vf[u]);
-  }
+    for (int u = 0; u < NB; ++u) {
+      kr[u].load(static_cast<const T*>(a.k) + (long long)j[u] * a.ldk + off);
+      vr[u].load(static_cast<const T*>(a.v) + (long long)j[u] * a.ldv + off);
+    }
 #pragma unroll
-  for (int u = 0; u < NB; ++u) {
-    float d = 0.f, dv = 0.f;
+    for (int u = 0; u < NB; ++u) {
+      float d = 0.f, dv = 0.f;
 #pragma unroll
-    for (int i = 0; i < VN; ++i) { d += ((EXPH && ty[u]) ? qs1[i] : qs0[i]) * kf[u][i]; dv += dof[i] * vf[u][i]; }
-    d = head_sum<LPH>(d, hm);
-    dv = head_sum<LPH>(dv, hm);
-    const bool inr = (d > -kClamp) && (d < kClamp);
-    const float w = ok[u] ? __expf(fminf(fmaxf(d, -kClamp), kClamp)) : 0.f;
-    float mf = 1.f;
-    if (a.variant == 1 && a.thresh) mf = keep_edge(a.seed, (uint32_t)(e + u), (uint32_t)head, a.thresh) ? a.inv_keep : 0.f;
-    else if (a.variant == 1) mf = a.inv_keep;
-    const float ds = inr ? (dv * mf - dterm) * invz * w : 0.f;
-    if (EXPH) {
+      for (int i = 0; i < VN; ++i) { d += qs0[i] * kr[u].get(i); dv += dof[i] * vr[u].get(i); }
+      d = head_sum<LPH>(d, hm);
+      dv = head_sum<LPH>(dv, hm);
+      const bool inr = (d > -kClamp) && (d < kClamp);
+      const float w = ok[u] ? __expf(fminf(fmaxf(d, -kClamp), kClamp)) : 0.f;
+      float mf = 1.f;
+      if (a.variant == 1 && a.thresh) mf = keep_edge(a.seed, (uint32_t)(e + u), (uint32_t)head, a.thresh) ? a.inv_keep : 0.f;
+      else if (a.variant == 1) mf = a.inv_keep;
+      const float dss = inr ? (dv * mf - dterm) * invz * w * scale : 0.f;
+#pragma unroll
+      for (int i = 0; i < VN; ++i) dq[i] += dss * kr[u].get(i);
+    }
+  } else {
+    float kf[NB][VN], vf[NB][VN];
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      load_vec<T>(static_cast<const T*>(a.k) + (long long)j[u] * a.ldk + off, kf[u]);
+      load_vec<T>(static_cast<const T*>(a.v) + (long long)j[u] * a.ldv + off, vf[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      float d = 0.f, dv = 0.f;
+#pragma unroll
+      for (int i = 0; i < VN; ++i) { d += (ty[u] ? qs1[i] : qs0[i]) * kf[u][i]; dv += dof[i] * vf[u][i]; }
+      d = head_sum<LPH>(d, hm);
+      dv = head_sum<LPH>(dv, hm);
+      const bool inr = (d > -kClamp) && (d < kClamp);
+      const float w = ok[u] ? __expf(fminf(fmaxf(d, -kClamp), kClamp)) : 0.f;
+      float mf = 1.f;
+      if (a.variant == 1 && a.thresh) mf = keep_edge(a.seed, (uint32_t)(e + u), (uint32_t)head, a.thresh) ? a.inv_keep : 0.f;
+      else if (a.variant == 1) mf = a.inv_keep;
+      const float ds = inr ? (dv * mf - dterm) * invz * w : 0.f;
       const float* et = a.etab + (ty[u] ? a.hl * HN : 0) + off;
 #pragma unroll
       for (int i = 0; i < VN; ++i) {
@@ -383,15 +434,12 @@ __device__ __forceinline__ void dq_edge4(const BwdArgs& b, int e, int end, int h
         de0[i] += ty[u] ? 0.f : gg;
         de1[i] += ty[u] ? gg : 0.f;
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < VN; ++i) dq[i] += ds * scale * kf[u][i];
     }
   }
 }
 
 template <typename T, int HN, bool EXPH>
-__global__ void __launch_bounds__(256, 3) edge_attn_bwd_q_kernel(BwdArgs b) {
+__global__ void __launch_bounds__(256, EXPH ? 3 : 4) edge_attn_bwd_q_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
   constexpr int LPH = HN / VN;
   const AttnArgs& a = b.f;
@@ -547,8 +595,8 @@ __device__ __forceinline__ void dkv_edge(const BwdArgs& b, int te, int head, int
 // Four transposed edges at a time: all index and row loads are issued before any arithmetic so that a lane group
 // keeps 8 independent 16-byte gathers in flight (the pass is bound by gather latency, not by math).
 template <typename T, int HN, bool EXPH, int NB>
-__device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int head, int off, const float* kf,
-                                          const float* vf, float* dk, float* dv, unsigned hm) {
+__device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int head, int off, const Raw<T>& kf,
+                                          const Raw<T>& vf, float* dk, float* dv, unsigned hm) {
   constexpr int VN = Vec<T>::N;
   constexpr int LPH = HN / VN;
   const AttnArgs& a = b.f;
@@ -562,13 +610,13 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
     i_row[u] = ok[u] ? __ldg(b.t_row + te + u) : 0;
     eid[u] = ok[u] ? __ldg(b.t_eid + te + u) : 0;
   }
-  float qf[NB][VN], dof[NB][VN];
+  Raw<T> qr[NB], dr[NB];                      // gathered slices stay packed until used
   float2 zd[NB];
   int ty[NB];
 #pragma unroll
   for (int u = 0; u < NB; ++u) {
-    load_vec<T>(static_cast<const T*>(a.q) + (long long)i_row[u] * a.ldq + off, qf[u]);
-    load_vec<T>(static_cast<const T*>(b.dout) + (long long)i_row[u] * w_row + off, dof[u]);
+    qr[u].load(static_cast<const T*>(a.q) + (long long)i_row[u] * a.ldq + off);
+    dr[u].load(static_cast<const T*>(b.dout) + (long long)i_row[u] * w_row + off);
     zd[u] = __ldg(b.zd + (long long)i_row[u] * a.hl + head);
     ty[u] = (EXPH && ok[u]) ? a.etype[eid[u]] : 0;
   }
@@ -579,7 +627,7 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
     for (int i = 0; i < VN; ++i) et[i] = EXPH ? a.etab[(ty[u] ? w_row : 0) + off + i] : 1.f;
     float d = 0.f, dotv = 0.f;
 #pragma unroll
-    for (int i = 0; i < VN; ++i) { d += qf[u][i] * kf[i] * et[i]; dotv += dof[u][i] * vf[i]; }
+    for (int i = 0; i < VN; ++i) { d += qr[u].get(i) * kf.get(i) * et[i]; dotv += dr[u].get(i) * vf.get(i); }
     d = head_sum<LPH>(d, hm) * scale;
     dotv = head_sum<LPH>(dotv, hm);
     const bool inr = (d > -kClamp) && (d < kClamp);
@@ -590,16 +638,18 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
     const float ds = inr ? (dotv * mf - zd[u].y) * zd[u].x * w : 0.f;
     const float wn = w * mf * zd[u].x;
 #pragma unroll
+    const float dss = ds * scale;
+#pragma unroll
     for (int i = 0; i < VN; ++i) {
-      dk[i] += ds * scale * qf[u][i] * et[i];
-      dv[i] += wn * dof[u][i];
+      dk[i] += dss * qr[u].get(i) * et[i];
+      dv[i] += wn * dr[u].get(i);
     }
   }
 }
 
 // dK/dV over the balanced work list: one lane group per (work item, head chunk).
-template <typename T, int HN, bool EXPH>
-__global__ void __launch_bounds__(256, 3) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
+template <typename T, int HN, bool EXPH, int MINB>
+__global__ void __launch_bounds__(256, MINB) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
   constexpr int LPH = HN / VN;
   const AttnArgs& a = b.f;
@@ -620,9 +670,10 @@ __global__ void __launch_bounds__(256, 3) edge_attn_bwd_kv_task_kernel(BwdArgs b
   const int off = head * HN + (lt % LPH) * VN;
   const int4 it = __ldg(b.kv_task + item);
   const int row = it.x, beg = it.y, end = it.z, slot = it.w;
-  float kf[VN], vf[VN], dk[VN], dv[VN];
-  load_vec<T>(static_cast<const T*>(a.k) + (long long)row * a.ldk + off, kf);
-  load_vec<T>(static_cast<const T*>(a.v) + (long long)row * a.ldv + off, vf);
+  Raw<T> kf, vf;                              // this key's k | v slice stays packed for the whole task
+  float dk[VN], dv[VN];
+  kf.load(static_cast<const T*>(a.k) + (long long)row * a.ldk + off);
+  vf.load(static_cast<const T*>(a.v) + (long long)row * a.ldv + off);
 #pragma unroll
   for (int i = 0; i < VN; ++i) { dk[i] = 0.f; dv[i] = 0.f; }
   const unsigned hm = head_mask<LPH>();
@@ -784,8 +835,10 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
     const long long kv_warps = (kv_tasks + tpw - 1) / tpw;
     const long long kv_blocks = (kv_warps + 7) / 8;
     if (kv_blocks > 0) {
-      if (a.variant == 2) edge_attn_bwd_kv_task_kernel<T, HN, true><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
-      else edge_attn_bwd_kv_task_kernel<T, HN, false><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      static const int minb4 = [] { const char* e = getenv("BF_KV_MINB"); return e && atoi(e) == 4; }();
+      if (a.variant == 2) edge_attn_bwd_kv_task_kernel<T, HN, true, 3><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      else if (minb4) edge_attn_bwd_kv_task_kernel<T, HN, false, 4><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      else edge_attn_bwd_kv_task_kernel<T, HN, false, 3><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
     }
     if (b.n_kv_split > 0) edge_attn_bwd_kv_reduce_kernel<T><<<b.n_kv_split, 256, 0, st>>>(b, w_row);
     return cudaGetLastError();
