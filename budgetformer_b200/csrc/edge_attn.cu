@@ -647,7 +647,8 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
   }
 }
 
-// dK/dV over the balanced work list: one lane group per (work item, head chunk).
+// dK/dV over the balanced work list: one lane group per (work item, head chunk).  (Letting two lane groups share an
+// item and split its edges was measured slower: most items are short, and the shared form halves the items in flight.)
 template <typename T, int HN, bool EXPH, int MINB>
 __global__ void __launch_bounds__(256, MINB) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
@@ -688,24 +689,52 @@ __global__ void __launch_bounds__(256, MINB) edge_attn_bwd_kv_task_kernel(BwdArg
   }
 }
 
-// Adds the partials of every split key row in slot order (fixed order => bit-reproducible).
+// Adds the partials of every split key row (fixed association => bit-reproducible).  A hub key owns thousands of
+// slots, so a block spreads them over G thread groups (slot j goes to group j % G), every thread keeps 16 independent
+// sums in flight, and the groups' results meet in shared memory in group order.
+constexpr int KV_REDUCE_THREADS = 1024;
 template <typename T>
-__global__ void __launch_bounds__(256) edge_attn_bwd_kv_reduce_kernel(BwdArgs b, int w_row) {
+__global__ void __launch_bounds__(KV_REDUCE_THREADS) edge_attn_bwd_kv_reduce_kernel(BwdArgs b, int w_row) {
+  extern __shared__ float s_part[];           // [G, 2 * w_row]
   const int s = blockIdx.x;
   const int row = b.kv_split[3 * s], first = b.kv_split[3 * s + 1], n = b.kv_split[3 * s + 2];
-  for (int c = threadIdx.x; c < 2 * w_row; c += blockDim.x) {
-    // eight independent partial sums keep eight loads in flight (hub keys own thousands of slots)
-    float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    const float* pp = b.kv_partial + (long long)first * 2 * w_row + c;
-    int j = 0;
-    for (; j + 8 <= n; j += 8) {
+  const int ncol = 2 * w_row;
+  const int G = ncol <= KV_REDUCE_THREADS ? KV_REDUCE_THREADS / ncol : 1;
+  const int grp = ncol <= KV_REDUCE_THREADS ? (int)threadIdx.x / ncol : 0;
+  for (int c0 = 0; c0 < ncol; c0 += KV_REDUCE_THREADS) {
+    const int c = c0 + (ncol <= KV_REDUCE_THREADS ? (int)threadIdx.x % ncol : (int)threadIdx.x);
+    const bool act = c < ncol && grp < G;
+    float acc = 0.f;
+    if (act) {
+      float a16[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) a8[u] += pp[(long long)(j + u) * 2 * w_row];
+      for (int u = 0; u < 16; ++u) a16[u] = 0.f;
+      const float* pp = b.kv_partial + (long long)first * ncol + c;
+      int j = grp;
+      for (; j + 15 * G < n; j += 16 * G) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) a16[u] += pp[(long long)(j + u * G) * ncol];
+      }
+      for (; j < n; j += G) a16[0] += pp[(long long)j * ncol];
+#pragma unroll
+      for (int w = 8; w > 0; w >>= 1) {
+#pragma unroll
+        for (int u = 0; u < w; ++u) a16[u] += a16[u + w];
+      }
+      acc = a16[0];
     }
-    for (; j < n; ++j) a8[0] += pp[(long long)j * 2 * w_row];
-    const float acc = ((a8[0] + a8[1]) + (a8[2] + a8[3])) + ((a8[4] + a8[5]) + (a8[6] + a8[7]));
-    T* dst = c < w_row ? static_cast<T*>(b.dk) : static_cast<T*>(b.dv);
-    dst[(long long)row * b.ldg + (c < w_row ? c : c - w_row)] = from_float<T>(acc);
+    if (G > 1) {
+      if (act) s_part[grp * ncol + c] = acc;
+      __syncthreads();
+      if (act && grp == 0) {
+        for (int q = 1; q < G; ++q) acc += s_part[q * ncol + c];
+      }
+    }
+    if (act && grp == 0) {
+      T* dst = c < w_row ? static_cast<T*>(b.dk) : static_cast<T*>(b.dv);
+      dst[(long long)row * b.ldg + (c < w_row ? c : c - w_row)] = from_float<T>(acc);
+    }
+    if (G > 1) __syncthreads();
   }
 }
 
@@ -835,12 +864,14 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
     const long long kv_warps = (kv_tasks + tpw - 1) / tpw;
     const long long kv_blocks = (kv_warps + 7) / 8;
     if (kv_blocks > 0) {
-      static const int minb4 = [] { const char* e = getenv("BF_KV_MINB"); return e && atoi(e) == 4; }();
       if (a.variant == 2) edge_attn_bwd_kv_task_kernel<T, HN, true, 3><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
-      else if (minb4) edge_attn_bwd_kv_task_kernel<T, HN, false, 4><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
-      else edge_attn_bwd_kv_task_kernel<T, HN, false, 3><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      else edge_attn_bwd_kv_task_kernel<T, HN, false, 4><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
     }
-    if (b.n_kv_split > 0) edge_attn_bwd_kv_reduce_kernel<T><<<b.n_kv_split, 256, 0, st>>>(b, w_row);
+    if (b.n_kv_split > 0) {
+      const int ncol = 2 * w_row;
+      const int G = ncol <= KV_REDUCE_THREADS ? KV_REDUCE_THREADS / ncol : 1;
+      edge_attn_bwd_kv_reduce_kernel<T><<<b.n_kv_split, KV_REDUCE_THREADS, (size_t)G * ncol * sizeof(float), st>>>(b, w_row);
+    }
     return cudaGetLastError();
   }
   if (blocks > 0) edge_attn_bwd_kv_kernel<T, HN><<<(unsigned)blocks, 256, 0, st>>>(b);
