@@ -122,6 +122,13 @@ class AttnGraph:
                          f(self.t_row), f(self.t_eid), f(self.t_task), f(self.t_split), self.max_degree,
                          self.n_real, self.n_rw, self.kv_slots)
 
+    def record_stream(self, stream) -> None:
+        """Tell the caching allocator that ``stream`` uses every tensor of the graph (they were allocated on another)."""
+        for t in (self.rowptr, self.col, self.etype, self.t_rowptr, self.t_row, self.t_eid, self.t_task, self.t_split,
+                  getattr(self, "_totals", None)):
+            if t is not None and t.is_cuda:
+                t.record_stream(stream)
+
     def row_ids(self) -> torch.Tensor:
         """Query id of every edge (int64), i.e. ``edge_index[1]`` of the COO form."""
         deg = (self.rowptr[1:] - self.rowptr[:-1]).to(torch.int64)

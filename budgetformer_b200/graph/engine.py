@@ -111,6 +111,8 @@ class EdgeEngine:
         self._pool: Optional[ThreadPoolExecutor] = None
         self._future: Optional[Tuple[tuple, Future]] = None
         self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        self._build_stream = None                        # side stream of the device-side look-ahead build
+        self._dev_future: Optional[Tuple[tuple, Future]] = None
         self.last_build_s = 0.0
         self.last_prefetch_wait_s = 0.0
         self.last_graph_bytes = 0
@@ -163,8 +165,56 @@ class EdgeEngine:
                 self._cache.pop(next(iter(self._cache)))
             self._cache[key] = g
 
+    def uses_device_prefetch(self) -> bool:
+        """GPU policies: the next epoch's graph (construction, transposition, backward work list) is built one epoch
+        ahead on a side stream, driven by a worker thread, so that the host-side size reads of the build never stall
+        the thread that launches the training step."""
+        return (self.device.type == "cuda" and self.policy in ("gpu_persist", "gpu_ephemeral") and not self.fanout
+                and not self.force_broadcast
+                and not getattr(self.args, "disable_edge_prefetch", False)
+                and not getattr(self.args, "profile_sp_comm", False))
+
+    def _build_device_ahead(self, seed: int, state: BudgetState):
+        try:
+            torch.cuda.set_device(self.device)
+            if self._build_stream is None:
+                self._build_stream = torch.cuda.Stream(self.device)
+            with torch.cuda.stream(self._build_stream):
+                g = self._finalize(self._build_device(seed, state))
+                g.ensure_transpose()
+                done = torch.cuda.Event()
+                done.record(self._build_stream)
+            return g, done
+        except torch.cuda.OutOfMemoryError:
+            return None                                   # the step builds synchronously and reports the failure
+
+    def _take_device_prefetch(self, key: tuple) -> Optional[AttnGraph]:
+        if self._dev_future is None:
+            return None
+        fkey, fut = self._dev_future
+        self._dev_future = None
+        t0 = time.perf_counter()
+        res = fut.result()
+        self.last_prefetch_wait_s = time.perf_counter() - t0
+        if res is None or fkey != key:
+            return None
+        g, done = res
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(done)
+        g.record_stream(cur)                              # allocated on the side stream, consumed on this one
+        return g
+
     def submit_prefetch(self, seed: int, state: BudgetState) -> bool:
-        """Start building the next epoch's graph on a CPU thread (main_node_fullgraph_sp.py:512-636)."""
+        """Start building the next epoch's graph on a worker thread (main_node_fullgraph_sp.py:512-636): on the CPU
+        for the offload policies, on a side stream of the GPU for the device policies."""
+        if self.uses_device_prefetch():
+            key = self._key(seed, state)
+            if self._dev_future is not None and self._dev_future[0] == key:
+                return True
+            if self._pool is None:
+                self._pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="bf-edge-prefetch")
+            self._dev_future = (key, self._pool.submit(self._build_device_ahead, seed, state))
+            return True
         if not self.uses_prefetch():
             return False
         if self.policy == "cpu_broadcast_prefetch" and self.world > 1 and self.rank != 0:
@@ -193,6 +243,7 @@ class EdgeEngine:
             self._pool.shutdown(wait=True)
             self._pool = None
         self._future = None
+        self._dev_future = None
 
     # ------------------------------------------------------------------ builds
     def _build_host(self, seed: int, state: BudgetState) -> AttnGraph:
@@ -284,6 +335,13 @@ class EdgeEngine:
         key = self._key(seed, state)
         broadcast = self.world > 1 and (self.force_broadcast or self.policy in ("cpu_broadcast", "cpu_broadcast_prefetch"))
         g: Optional[AttnGraph] = None
+        ahead = self._take_device_prefetch(key)
+        if ahead is not None:
+            self.last_build_s = time.perf_counter() - t0
+            self.last_graph_bytes = ahead.nbytes()
+            if record:
+                record_scalar("edge_merged_edges", ahead.num_edges, reduce="max")
+            return ahead
         with self._cache_lock:
             host = self._cache.get(key)
         if host is None and self._future is not None:

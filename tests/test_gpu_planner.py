@@ -61,3 +61,29 @@ def test_adaptive_budget_with_deferred_planner_on_gpu():
     assert t.controller.frozen
     assert t.planner.state_name() != "DEFERRED"          # the frozen budget released the planner
     assert any("BudgetCtrl" in l for l in logs)
+
+
+def test_device_lookahead_build_matches_synchronous_build():
+    """The graph built one epoch ahead on the side stream is the graph a synchronous build of that epoch gives, and
+    training with the look-ahead reproduces training without it."""
+    losses = {}
+    for mode in ("ahead", "sync"):
+        extra = ["--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4"]
+        if mode == "sync":
+            extra.append("--disable_edge_prefetch")
+        torch.manual_seed(11)
+        t = _trainer(extra)
+        assert t.edge_engine.uses_device_prefetch() == (mode == "ahead")
+        vals = []
+        for epoch in range(1, 5):
+            out = t.train_step(epoch)
+            vals.append(out["loss"])
+            if mode == "ahead" and epoch >= 2:
+                g = t.last_graph
+                ref = t.edge_engine._finalize(t.edge_engine._build_device(t.edge_seed(epoch), t.budget_state()))
+                assert torch.equal(g.rowptr, ref.rowptr) and torch.equal(g.col, ref.col)
+                assert g.t_rowptr is not None                  # transposition came with the look-ahead build
+        t.edge_engine.shutdown()
+        losses[mode] = vals
+    gemm.check_status("cuda")
+    assert all(abs(a - b) < 2e-3 for a, b in zip(losses["ahead"], losses["sync"])), losses
