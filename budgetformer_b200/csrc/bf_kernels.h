@@ -117,6 +117,16 @@ int bf_peer_gather_cols(void* const* src, int world, long long row0, long long r
 int bf_peer_scatter_cols(void* const* dst, int world, long long row0, long long rows, int cols_bytes,
                          long long dst_ld_bytes, const void* src, long long src_ld_bytes, cudaStream_t st);
 
+// ---- by-key view of the attention graph + dK/dV work list (graph_transpose.cu) --------------------------
+size_t bf_graph_transpose_scratch(int n, long long n_edges);
+int bf_graph_transpose(const int* rowptr, const int* col, int n, long long n_edges, int* t_rowptr /* [n+1] */,
+                       int* t_row /* [E] */, int* t_eid /* [E] */, void* scratch, size_t scratch_bytes, cudaStream_t st);
+size_t bf_kv_task_scratch(int n);
+int bf_kv_task_counts(const int* t_rowptr, int n, int chunk, int* item_first /* [n+1] */, int* slot_first /* [n+1] */,
+                      int* split_first /* [n+1] */, void* scratch, size_t scratch_bytes, cudaStream_t st);
+int bf_kv_task_fill(const int* t_rowptr, const int* item_first, const int* slot_first, const int* split_first, int n,
+                    int chunk, int* tasks /* [T, 4] */, int* splits /* [S, 3] */, cudaStream_t st);
+
 // ---- row kernels (norm_fused.cu) -----------------------------------------------------------------
 int bf_layernorm_fwd(const void* x, long long ldx, const float* gamma, const float* beta, void* y, long long ldy,
                      float* stats /* [rows, 2] mean, rstd or NULL */, long long rows, int h, float eps, int dtype,

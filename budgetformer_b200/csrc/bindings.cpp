@@ -184,6 +184,42 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
   return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
 }
 
+// By-key view + balanced dK/dV work list of a device-resident attention graph.
+// Returns (t_rowptr [n+1], t_row [E], t_eid [E], tasks [T, 4], splits [S, 3], sizes int64 [3] = T, slots, S on the host).
+std::vector<Tensor> graph_transpose(Tensor rowptr, Tensor col, int64_t n, int64_t chunk) {
+  TORCH_CHECK(rowptr.is_cuda() && col.is_cuda() && rowptr.scalar_type() == torch::kInt && col.scalar_type() == torch::kInt);
+  TORCH_CHECK(rowptr.is_contiguous() && col.is_contiguous() && rowptr.numel() == n + 1 && chunk >= 1);
+  c10::cuda::CUDAGuard guard(col.device());
+  auto st = at::cuda::getCurrentCUDAStream();
+  auto iopt = col.options();
+  const int64_t n_edges = col.numel();
+  Tensor t_rowptr = torch::empty({n + 1}, iopt), t_row = torch::empty({n_edges}, iopt), t_eid = torch::empty({n_edges}, iopt);
+  {
+    const size_t bytes = bf_graph_transpose_scratch((int)n, n_edges);
+    Tensor scratch = torch::empty({(int64_t)bytes}, iopt.dtype(torch::kUInt8));
+    check_cuda(bf_graph_transpose(rowptr.data_ptr<int>(), col.data_ptr<int>(), (int)n, n_edges, t_rowptr.data_ptr<int>(),
+                                  t_row.data_ptr<int>(), t_eid.data_ptr<int>(), scratch.data_ptr(), bytes, st),
+               "graph_transpose");
+  }
+  Tensor firsts = torch::empty({3, n + 1}, iopt);
+  {
+    const size_t bytes = bf_kv_task_scratch((int)n);
+    Tensor scratch = torch::empty({(int64_t)bytes}, iopt.dtype(torch::kUInt8));
+    check_cuda(bf_kv_task_counts(t_rowptr.data_ptr<int>(), (int)n, (int)chunk, firsts[0].data_ptr<int>(),
+                                 firsts[1].data_ptr<int>(), firsts[2].data_ptr<int>(), scratch.data_ptr(), bytes, st),
+               "kv_task_counts");
+  }
+  // the three totals size the outputs: the one host read of this build
+  Tensor sizes = firsts.select(1, n).to(torch::kCPU).to(torch::kLong);
+  const int64_t n_tasks = sizes[0].item<int64_t>(), n_splits = sizes[2].item<int64_t>();
+  Tensor tasks = torch::empty({n_tasks, 4}, iopt), splits = torch::empty({n_splits, 3}, iopt);
+  check_cuda(bf_kv_task_fill(t_rowptr.data_ptr<int>(), firsts[0].data_ptr<int>(), firsts[1].data_ptr<int>(),
+                             firsts[2].data_ptr<int>(), (int)n, (int)chunk, tasks.data_ptr<int>(),
+                             splits.data_ptr<int>(), st),
+             "kv_task_fill");
+  return {t_rowptr, t_row, t_eid, tasks, splits, sizes};
+}
+
 // C = A * W^T with fused epilogue.  `dst_ptrs` holds one device pointer per destination (1 = plain output).
 void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, int64_t seed, OptTensor residual,
              OptTensor relu_mask, double out_scale, bool out_fp32, std::vector<int64_t> dst_ptrs, int64_t dst_row_offset,
@@ -357,6 +393,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("edge_attn_fwd", &edge_attn_fwd);
   m.def("edge_attn_bwd", &edge_attn_bwd);
   m.def("build_attn_graph", &build_attn_graph);
+  m.def("graph_transpose", &graph_transpose);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_supported", &gemm_supported);
   m.def("layernorm_fwd", &layernorm_fwd);

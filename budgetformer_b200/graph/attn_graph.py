@@ -146,6 +146,15 @@ class AttnGraph:
         """Build the by-key CSR (deterministic: stable sort keeps query order inside a key's row)."""
         if self.t_rowptr is not None:
             return self
+        if self.col.is_cuda and self.col.dtype == torch.int32 and self.rowptr.dtype == torch.int32:
+            # device graphs: radix sort over the node-id bits + compaction kernels (csrc/graph_transpose.cu)
+            from ..ops import _ext
+            t_rowptr, t_row, t_eid, tasks, splits, sizes = _ext.load().graph_transpose(
+                self.rowptr.contiguous(), self.col.contiguous(), int(self.num_rows), int(KV_TASK_EDGES))
+            _ext.count_launches(9)
+            self.t_rowptr, self.t_row, self.t_eid = t_rowptr, t_row, t_eid
+            self.t_task, self.t_split, self.kv_slots = tasks, splits, int(sizes[1])
+            return self
         col64 = self.col.to(torch.int64)
         _, perm = torch.sort(col64, stable=True)
         rows = self.row_ids()

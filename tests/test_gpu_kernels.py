@@ -112,3 +112,22 @@ def test_extension_is_loaded_from_tree():
     from budgetformer_b200.ops import _ext
     mod = _ext.load()
     assert "budgetformer_b200/csrc/build" in mod.__file__.replace("\\", "/")
+
+
+@pytest.mark.parametrize("hub", [False, True])
+def test_device_transpose_matches_torch_path(hub):
+    """csrc/graph_transpose.cu (radix sort over node-id bits + compaction) gives the same by-key view and the same
+    dK/dV work list as the PyTorch construction used for CPU graphs."""
+    from budgetformer_b200.graph.attn_graph import AttnGraph, add_virtual_node
+    n = 5000
+    g = random_attn_graph(n, 30000, hub_col=700, seed=3)
+    if hub:
+        g = add_virtual_node(g, n, n)                     # row 0 holds every node; key 0 is used by every query
+    ref = AttnGraph(g.num_rows, g.rowptr.cpu(), g.col.cpu(), None).ensure_transpose()
+    dev = AttnGraph(g.num_rows, g.rowptr.cuda(), g.col.cuda(), None).ensure_transpose()
+    for name in ("t_rowptr", "t_row", "t_eid", "t_task", "t_split"):
+        a, b = getattr(ref, name), getattr(dev, name).cpu()
+        assert a.shape == b.shape and torch.equal(a.to(b.dtype), b), name
+    assert ref.kv_slots == dev.kv_slots
+    if hub:
+        assert dev.kv_slots > 0 and dev.t_split.size(0) >= 1
