@@ -140,6 +140,15 @@ int bf_colsum(const void* x, long long ldx, long long rows, int cols /* % 8 == 0
 int bf_hash_dropout(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, uint32_t seed,
                     float p, int dtype, cudaStream_t st);
 
+// BatchNorm building blocks (cols % 8 == 0, 16-byte aligned rows): shifted one-pass statistics, the backward
+// reductions, and per-column affine maps y = x*a + b / y = in2*a + x*b + c0 (in2 == NULL selects the first form).
+int bf_bn_stats(const void* x, long long ldx, const float* shift /* [cols] or NULL */, long long rows, int cols,
+                float* s1 /* += sum (x - shift) */, float* s2 /* += sum (x - shift)^2 */, int dtype, cudaStream_t st);
+int bf_bn_bwd_reduce(const void* dy, long long lddy, const void* x, long long ldx, const float* mean, const float* rstd,
+                     long long rows, int cols, float* dbeta /* += */, float* dgamma /* += */, int dtype, cudaStream_t st);
+int bf_col_affine(const void* x, long long ldx, const void* in2, long long ld2, const float* a, const float* b,
+                  const float* c0, void* y, long long ldy, long long rows, int cols, int dtype, cudaStream_t st);
+
 // ---- optimizer on flat fp32 buckets (optim.cu) -----------------------------------------------------
 int bf_grad_sumsq(const float* g, long long n, float* out /* += sum g^2 */, cudaStream_t st);
 int bf_adamw_flat(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1, float beta2,

@@ -345,6 +345,43 @@ Tensor colsum(Tensor x) {
   return out;
 }
 
+// (sum (x - shift), sum (x - shift)^2) per column, fp32
+std::vector<Tensor> bn_stats(Tensor x, OptTensor shift) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto fopt = x.options().dtype(torch::kFloat);
+  Tensor s1 = torch::zeros({x.size(1)}, fopt), s2 = torch::zeros({x.size(1)}, fopt);
+  check_cuda(bf_bn_stats(x.data_ptr(), x.stride(0), shift.has_value() ? shift->data_ptr<float>() : nullptr, x.size(0),
+                         (int)x.size(1), s1.data_ptr<float>(), s2.data_ptr<float>(), dtype_code(x),
+                         at::cuda::getCurrentCUDAStream()), "bn_stats");
+  return {s1, s2};
+}
+
+// (sum dy, sum dy * (x - mean) * rstd) per column, fp32
+std::vector<Tensor> bn_bwd_reduce(Tensor dy, Tensor x, Tensor mean, Tensor rstd) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && dy.stride(1) == 1 && dy.scalar_type() == x.scalar_type());
+  c10::cuda::CUDAGuard guard(x.device());
+  auto fopt = x.options().dtype(torch::kFloat);
+  Tensor dbeta = torch::zeros({x.size(1)}, fopt), dgamma = torch::zeros({x.size(1)}, fopt);
+  check_cuda(bf_bn_bwd_reduce(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), mean.data_ptr<float>(),
+                              rstd.data_ptr<float>(), x.size(0), (int)x.size(1), dbeta.data_ptr<float>(),
+                              dgamma.data_ptr<float>(), dtype_code(x), at::cuda::getCurrentCUDAStream()), "bn_bwd_reduce");
+  return {dbeta, dgamma};
+}
+
+// y = x*a + b, or y = in2*a + x*b + c0 when in2 is given (per-column fp32 coefficients)
+Tensor col_affine(Tensor x, OptTensor in2, Tensor a, Tensor b, OptTensor c0) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1);
+  TORCH_CHECK(in2.has_value() == c0.has_value());
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty({x.size(0), x.size(1)}, x.options());
+  check_cuda(bf_col_affine(x.data_ptr(), x.stride(0), in2.has_value() ? in2->data_ptr() : nullptr,
+                           in2.has_value() ? in2->stride(0) : 0, a.data_ptr<float>(), b.data_ptr<float>(),
+                           c0.has_value() ? c0->data_ptr<float>() : nullptr, y.data_ptr(), y.stride(0), x.size(0),
+                           (int)x.size(1), dtype_code(x), at::cuda::getCurrentCUDAStream()), "col_affine");
+  return y;
+}
+
 Tensor hash_dropout(Tensor x, int64_t seed, double p) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1);
   c10::cuda::CUDAGuard guard(x.device());
@@ -399,6 +436,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("hash_dropout", &hash_dropout);
+  m.def("bn_stats", &bn_stats);
+  m.def("bn_bwd_reduce", &bn_bwd_reduce);
+  m.def("col_affine", &col_affine);
   m.def("colsum", &colsum);
   m.def("nll_fwd_bwd", &nll_fwd_bwd);
   m.def("grad_sumsq", &grad_sumsq);

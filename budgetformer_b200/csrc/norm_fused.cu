@@ -419,6 +419,128 @@ __global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ x, lo
   for (int i = threadIdx.x; i < cols; i += blockDim.x) atomicAdd(out + i, s_sum[i]);
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// BatchNorm over the rows of a [rows, cols] activation (16-bit or fp32), statistics in fp32.
+//   colstats<MODE 1>:  s1[c] += sum_r (x - shift[c]),  s2[c] += sum_r (x - shift[c])^2     (forward statistics;
+//                      the shift - the running mean - keeps the one-pass variance well conditioned)
+//   colstats<MODE 2>:  s1[c] += sum_r dy,              s2[c] += sum_r dy * (x - mean[c]) * rstd[c]   (dbeta, dgamma)
+//   affine1:           y  = x * a[c] + b[c]                        (normalise + scale + shift in one multiply-add)
+//   affine2:           dx = dy * a[c] + x * b[c] + c0[c]           (the whole BatchNorm input gradient)
+// Each thread owns 8 consecutive columns and strides over rows; partials meet in shared memory, then one atomic per
+// column and block.
+// ---------------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* f) {
+  if (sizeof(T) == 2) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const T* t = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = to_f<T>(t[i]);
+  } else {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* f) {
+  if (sizeof(T) == 2) {
+    uint4 u;
+    T* t = reinterpret_cast<T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = from_f<T>(f[i]);
+    *reinterpret_cast<uint4*>(p) = u;
+  } else {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) colstats_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ dy,
+                                                       long long lddy, const float* __restrict__ p0,
+                                                       const float* __restrict__ p1, long long rows, int cols,
+                                                       float* __restrict__ s1, float* __restrict__ s2) {
+  extern __shared__ float s_sum[];            // [2, cols]
+  for (int i = threadIdx.x; i < 2 * cols; i += blockDim.x) s_sum[i] = 0.f;
+  __syncthreads();
+  const int chunks = cols / 8;
+  const int row_lanes = blockDim.x / chunks;  // threads that share one column chunk
+  const int chunk = threadIdx.x % chunks;
+  const int rl = threadIdx.x / chunks;
+  if (rl < row_lanes) {
+    float a1[8], a2[8], q0[8], q1[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      a1[k] = 0.f; a2[k] = 0.f;
+      q0[k] = p0 ? p0[chunk * 8 + k] : 0.f;    // MODE 1: shift; MODE 2: mean
+      q1[k] = p1 ? p1[chunk * 8 + k] : 1.f;    // MODE 2: rstd
+    }
+    const long long rstride = (long long)gridDim.x * row_lanes;
+    long long r = (long long)blockIdx.x * row_lanes + rl;
+    // two rows per iteration: both loads are issued before either is used
+    for (; r + rstride < rows; r += 2 * rstride) {
+      float u[8], v[8], du[8], dv[8];
+      load8<T>(x + r * ldx + chunk * 8, u);
+      load8<T>(x + (r + rstride) * ldx + chunk * 8, v);
+      if (MODE == 2) {
+        load8<T>(dy + r * lddy + chunk * 8, du);
+        load8<T>(dy + (r + rstride) * lddy + chunk * 8, dv);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (MODE == 1) {
+          const float d0 = u[k] - q0[k], d1 = v[k] - q0[k];
+          a1[k] += d0 + d1;
+          a2[k] += d0 * d0 + d1 * d1;
+        } else {
+          a1[k] += du[k] + dv[k];
+          a2[k] += (du[k] * (u[k] - q0[k]) + dv[k] * (v[k] - q0[k])) * q1[k];
+        }
+      }
+    }
+    for (; r < rows; r += rstride) {
+      float u[8], du[8];
+      load8<T>(x + r * ldx + chunk * 8, u);
+      if (MODE == 2) load8<T>(dy + r * lddy + chunk * 8, du);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (MODE == 1) { const float d0 = u[k] - q0[k]; a1[k] += d0; a2[k] += d0 * d0; }
+        else { a1[k] += du[k]; a2[k] += du[k] * (u[k] - q0[k]) * q1[k]; }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      atomicAdd(&s_sum[chunk * 8 + k], a1[k]);
+      atomicAdd(&s_sum[cols + chunk * 8 + k], a2[k]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    atomicAdd(s1 + i, s_sum[i]);
+    atomicAdd(s2 + i, s_sum[cols + i]);
+  }
+}
+
+// TWO = false: y = x*a + b;  TWO = true: y = in2*a + x*b + c0
+template <typename T, bool TWO>
+__global__ void __launch_bounds__(256) col_affine_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ in2,
+                                                         long long ld2, const float* __restrict__ a,
+                                                         const float* __restrict__ b, const float* __restrict__ c0,
+                                                         T* __restrict__ y, long long ldy, long long rows, int cols) {
+  const int chunks = cols / 8;
+  const long long total = rows * chunks;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / chunks;
+    const int c = (int)(i - r * chunks) * 8;
+    float u[8], w[8], o[8];
+    load8<T>(x + r * ldx + c, u);
+    if (TWO) load8<T>(in2 + r * ld2 + c, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = TWO ? w[k] * a[c + k] + u[k] * b[c + k] + c0[c + k] : u[k] * a[c + k] + b[c + k];
+    store8<T>(y + r * ldy + c, o);
+  }
+}
+
 }  // namespace
 
 #define BF_DT_SWITCH(DT, CALL)                                          \
@@ -536,5 +658,61 @@ extern "C" int bf_colsum(const void* x, long long ldx, long long rows, int cols,
 #define CALL(T) colsum_kernel<T><<<(unsigned)blocks, 256, smem, st>>>((const T*)x, ldx, rows, cols, out)
   BF_DT_SWITCH(dtype, CALL)
 #undef CALL
+  return (int)cudaGetLastError();
+}
+
+static bool cols8_ok(int cols, int dtype, const void* p, long long ld) {
+  const int esz = dtype == BF_FP32 ? 4 : 2;
+  return cols % 8 == 0 && cols >= 8 && cols <= 2048 && ((uintptr_t)p) % 16 == 0 && (ld * esz) % 16 == 0;
+}
+
+extern "C" int bf_bn_stats(const void* x, long long ldx, const float* shift, long long rows, int cols, float* s1,
+                           float* s2, int dtype, cudaStream_t st) {
+  if (!cols8_ok(cols, dtype, x, ldx)) return (int)cudaErrorInvalidValue;
+  if (rows == 0) return 0;
+  const int row_lanes = 256 / (cols / 8);
+  if (row_lanes < 1) return (int)cudaErrorInvalidValue;
+  long long blocks = (rows + row_lanes * 16 - 1) / (row_lanes * 16);
+  if (blocks > 148 * 6) blocks = 148 * 6;
+  const size_t smem = sizeof(float) * 2 * cols;
+#define CALL(T) colstats_kernel<T, 1><<<(unsigned)blocks, 256, smem, st>>>((const T*)x, ldx, nullptr, 0, shift, nullptr, rows, cols, s1, s2)
+  BF_DT_SWITCH(dtype, CALL)
+#undef CALL
+  return (int)cudaGetLastError();
+}
+
+extern "C" int bf_bn_bwd_reduce(const void* dy, long long lddy, const void* x, long long ldx, const float* mean,
+                                const float* rstd, long long rows, int cols, float* dbeta, float* dgamma, int dtype,
+                                cudaStream_t st) {
+  if (!cols8_ok(cols, dtype, x, ldx) || !cols8_ok(cols, dtype, dy, lddy)) return (int)cudaErrorInvalidValue;
+  if (rows == 0) return 0;
+  const int row_lanes = 256 / (cols / 8);
+  if (row_lanes < 1) return (int)cudaErrorInvalidValue;
+  long long blocks = (rows + row_lanes * 16 - 1) / (row_lanes * 16);
+  if (blocks > 148 * 6) blocks = 148 * 6;
+  const size_t smem = sizeof(float) * 2 * cols;
+#define CALL(T) colstats_kernel<T, 2><<<(unsigned)blocks, 256, smem, st>>>((const T*)x, ldx, (const T*)dy, lddy, mean, rstd, rows, cols, dbeta, dgamma)
+  BF_DT_SWITCH(dtype, CALL)
+#undef CALL
+  return (int)cudaGetLastError();
+}
+
+extern "C" int bf_col_affine(const void* x, long long ldx, const void* in2, long long ld2, const float* a, const float* b,
+                             const float* c0, void* y, long long ldy, long long rows, int cols, int dtype,
+                             cudaStream_t st) {
+  if (!cols8_ok(cols, dtype, x, ldx) || !cols8_ok(cols, dtype, y, ldy) || (in2 && !cols8_ok(cols, dtype, in2, ld2)))
+    return (int)cudaErrorInvalidValue;
+  if (rows == 0) return 0;
+  long long blocks = (rows * (cols / 8) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (in2) {
+#define CALL(T) col_affine_kernel<T, true><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, (const T*)in2, ld2, a, b, c0, (T*)y, ldy, rows, cols)
+    BF_DT_SWITCH(dtype, CALL)
+#undef CALL
+  } else {
+#define CALL(T) col_affine_kernel<T, false><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, nullptr, 0, a, b, nullptr, (T*)y, ldy, rows, cols)
+    BF_DT_SWITCH(dtype, CALL)
+#undef CALL
+  }
   return (int)cudaGetLastError();
 }

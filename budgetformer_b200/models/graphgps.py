@@ -126,6 +126,10 @@ class EncoderLayer(nn.Module):
     @staticmethod
     def _bn(norm, x):
         b, n, c = x.shape
+        group = getattr(norm, "_bf_sync_group", None)
+        if group is not None:
+            from ..ops.norm import batch_norm
+            return batch_norm(x.reshape(b * n, c), norm, group).view(b, n, c)
         return norm(x.reshape(b * n, c)).view(b, n, c)
 
     def _ffn(self, h):

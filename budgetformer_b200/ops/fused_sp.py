@@ -31,7 +31,7 @@ from ..parallel import symm
 from . import _ext, gemm
 from .edge_attention import _VARIANTS
 from .ffn import fused_ffn
-from .norm import ColsumSlot, column_sum, hash_dropout, layer_norm, new_seed
+from .norm import ColsumSlot, batch_norm, column_sum, hash_dropout, layer_norm, new_seed
 
 
 class SPContext:
@@ -314,7 +314,7 @@ def _graphormer_ffn(layer, x):
 
 
 def _bn(norm, x):
-    return norm(x.float()).to(x.dtype)
+    return batch_norm(x, norm, getattr(norm, "_bf_sync_group", None))
 
 
 def _gps_attn(layer, x, graph, sp, idx):

@@ -210,6 +210,11 @@ class FullGraphTrainer:
 
     def _configure_fused_sp(self) -> None:
         """Switch the models to the fused projection + all-to-all kernels when running on GPUs."""
+        if bool(getattr(self.args, "sync_batchnorm", False)) and self.sp_world > 1:
+            # every rank holds N/P rows of the same "batch": sum the BatchNorm statistics over the SP group
+            for m in self.model.modules():
+                if isinstance(m, torch.nn.BatchNorm1d):
+                    m._bf_sync_group = self.sp_group
         mode = str(getattr(self.args, "fused_sp", "auto"))
         self.fused_sp = False
         if mode == "off" or self.device.type != "cuda":

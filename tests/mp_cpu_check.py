@@ -78,9 +78,35 @@ def mode_adaptive(out_path):
     json.dump({"ok": True}, open(out_path + f".{dist.get_rank()}", "w"))
 
 
+def mode_syncbn(out_path):
+    """--sync_batchnorm: training-mode GraphGPS on P ranks normalises with the statistics of all rows, so outputs and
+    gradients equal the single-process run (which sees all rows in one BatchNorm call)."""
+    t = make("graphgps", ["--sync_batchnorm"])
+    g = t.build_edges(1)
+    t.model.train()
+    loss, out = t._loss(g, t.local_idx["train"])
+    n_local = float(t.local_idx["train"].numel())
+    t.reducer.prepare_backward()
+    (loss * n_local).backward()
+    t.reducer.finalize_backward()
+    parts = [torch.empty_like(out) for _ in range(t.sp_world)]
+    gn = torch.tensor([n_local])
+    if dist.is_initialized():
+        dist.all_gather(parts, out.contiguous())
+        dist.all_reduce(gn)
+    else:
+        parts = [out]
+    named = dict(t.model.named_parameters())
+    keys = [k for k in named if "norm" in k][:4] + list(named)[:3]
+    grads = {k: (named[k].grad * t.sp_world / float(gn)).tolist() for k in keys}
+    rm = [m.running_mean.tolist() for m in t.model.modules() if isinstance(m, torch.nn.BatchNorm1d)][:2]
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        json.dump({"out": torch.cat(parts)[:8].tolist(), "grads": grads, "running_mean": rm}, open(out_path, "w"))
+
+
 if __name__ == "__main__":
     mode, out = sys.argv[1], sys.argv[2]
-    {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom}[mode](out)
+    {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom, "syncbn": mode_syncbn}[mode](out)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

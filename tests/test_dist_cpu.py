@@ -51,3 +51,15 @@ def test_voted_oom_recovery_is_symmetric(tmp_path):
     assert r0[2]["dropped"] == 1.0 and r1[2]["dropped"] == 1.0             # fault after backward on rank 1: both drop
     assert r0[2]["modes"] == ["recompute", "retain"]
     assert r0[3]["dropped"] == 0.0 and r0[3]["modes"] == r0[2]["modes"]
+
+
+def test_sync_batchnorm_two_ranks_equals_single_process(tmp_path):
+    one, two = str(tmp_path / "bn1.json"), str(tmp_path / "bn2.json")
+    _spawn(1, "syncbn", one, 29805)
+    _spawn(2, "syncbn", two, 29806)
+    a, b = json.load(open(one)), json.load(open(two))
+    assert torch.allclose(torch.tensor(a["out"]), torch.tensor(b["out"]), atol=5e-5)
+    assert torch.allclose(torch.tensor(a["running_mean"]), torch.tensor(b["running_mean"]), atol=1e-5)
+    for name in a["grads"]:
+        ga, gb = torch.tensor(a["grads"][name]), torch.tensor(b["grads"][name])
+        assert torch.allclose(ga, gb, atol=5e-5 + 2e-3 * float(ga.abs().max())), name

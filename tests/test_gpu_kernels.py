@@ -131,3 +131,36 @@ def test_device_transpose_matches_torch_path(hub):
     assert ref.kv_slots == dev.kv_slots
     if hub:
         assert dev.kv_slots > 0 and dev.t_split.size(0) >= 1
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_batch_norm_kernels_match_pytorch(dtype):
+    """Forward, running statistics and all three gradients of the row BatchNorm against nn.BatchNorm1d in fp32."""
+    from budgetformer_b200.ops.norm import batch_norm
+    torch.manual_seed(0)
+    rows, h = 5003, 64
+    x = (torch.randn(rows, h, device="cuda") * 1.7 + 0.6).to(dtype)
+    bn = torch.nn.BatchNorm1d(h).cuda()
+    ref = torch.nn.BatchNorm1d(h).cuda()
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5); bn.bias.uniform_(-0.5, 0.5)
+        ref.weight.copy_(bn.weight); ref.bias.copy_(bn.bias)
+    xa = x.clone().requires_grad_(True)
+    xb = x.float().clone().requires_grad_(True)
+    g = torch.randn(rows, h, device="cuda")
+    for _ in range(2):                                   # second call uses a non-zero running mean as the shift
+        ya = batch_norm(xa, bn)
+        yb = ref(xb)
+    (ya.float() * g).sum().backward()
+    (yb * g).sum().backward()
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert ya.dtype == dtype and (ya.float() - yb).abs().max() < tol
+    assert (bn.running_mean - ref.running_mean).abs().max() < 1e-3
+    assert (bn.running_var - ref.running_var).abs().max() < 2e-3
+    scale = xb.grad.abs().max()
+    assert (xa.grad.float() - xb.grad).abs().max() < (4e-2 if dtype == torch.bfloat16 else 1e-4) * max(1.0, float(scale))
+    ptol = 2e-2 if dtype == torch.bfloat16 else 2e-3
+    assert (bn.weight.grad - ref.weight.grad).abs().max() < ptol * ref.weight.grad.abs().max() + 5e-2
+    assert (bn.bias.grad - ref.bias.grad).abs().max() < ptol * ref.bias.grad.abs().max() + 5e-2
+    bn.eval(); ref.eval()
+    assert (batch_norm(x, bn).float() - ref(x.float())).abs().max() < tol
