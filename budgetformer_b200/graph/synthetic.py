@@ -33,50 +33,76 @@ def _power_law_weights(n: int, exponent: float, rng, w_min: float = 1.0) -> np.n
     return w_min * (1.0 - u) ** (-1.0 / (exponent - 1.0))
 
 
+def _unique_to_target(sample, target: int, rng) -> np.ndarray:
+    """Distinct int64 keys drawn with ``sample(m)`` until exactly ``target`` of them exist (heavy-tailed samplers
+    repeat hub pairs often, so one draw of ``target`` pairs falls well short after deduplication)."""
+    keys = np.unique(sample(int(target)))
+    for _ in range(64):
+        need = int(target) - keys.size
+        if need <= 0:
+            break
+        fresh = np.setdiff1d(np.unique(sample(int(need * 1.5) + 1024)), keys, assume_unique=True)
+        if fresh.size > need:
+            fresh = fresh[np.sort(rng.permutation(fresh.size)[:need])]
+        keys = np.union1d(keys, fresh)
+    return keys
+
+
 def chung_lu_edges(num_nodes: int, num_edges: int, exponent: float = 2.1, directed: bool = True, seed: int = 0,
                    chunk: int = 1 << 24) -> torch.Tensor:
-    """Sample ``num_edges`` (src, dst) pairs with endpoint probabilities proportional to power-law
-    weights (the Chung-Lu model in its fast multigraph form; duplicates and self loops dropped, so the
-    result has slightly fewer edges).  Undirected graphs return both directions."""
+    """``num_edges`` distinct (src, dst) pairs (no self loops) with endpoint probabilities proportional to power-law
+    weights: the Chung-Lu model in its fast form, topped up until the requested count is reached.  Undirected graphs
+    take ``num_edges`` node pairs and return both directions (``2 * num_edges`` columns)."""
     rng = np.random.default_rng(seed)
     n = int(num_nodes)
     w_out = _power_law_weights(n, exponent, rng)
     w_in = _power_law_weights(n, exponent, rng) if directed else w_out
     cdf_out = np.cumsum(w_out / w_out.sum())
     cdf_in = np.cumsum(w_in / w_in.sum())
-    parts = []
-    remaining = int(num_edges)
-    while remaining > 0:
-        m = min(remaining, chunk)
-        s = np.searchsorted(cdf_out, rng.random(m)).clip(0, n - 1)
-        d = np.searchsorted(cdf_in, rng.random(m)).clip(0, n - 1)
-        ok = s != d
-        parts.append((s[ok].astype(np.int64) * n + d[ok].astype(np.int64)))
-        remaining -= m
-    key = np.unique(np.concatenate(parts))
+
+    def sample(m: int) -> np.ndarray:
+        parts = []
+        while m > 0:
+            c = min(m, chunk)
+            s = np.searchsorted(cdf_out, rng.random(c)).clip(0, n - 1).astype(np.int64)
+            d = np.searchsorted(cdf_in, rng.random(c)).clip(0, n - 1).astype(np.int64)
+            ok = s != d
+            s, d = s[ok], d[ok]
+            if not directed:
+                s, d = np.minimum(s, d), np.maximum(s, d)
+            parts.append(s * n + d)
+            m -= c
+        return np.concatenate(parts)
+
+    key = _unique_to_target(sample, num_edges, rng)
     s, d = key // n, key % n
     if not directed:
-        key = np.unique(np.concatenate([s * n + d, d * n + s]))
+        key = np.sort(np.concatenate([s * n + d, d * n + s]))
         s, d = key // n, key % n
     return torch.from_numpy(np.stack([s, d]).astype(np.int64))
 
 
 def citation_dag_edges(num_nodes: int, num_edges: int, exponent: float = 2.2, seed: int = 0) -> torch.Tensor:
-    """Heterophilous citation-like DAG: node i cites uniformly chosen earlier nodes j < i; the number of
-    citations per node follows a power law scaled to ``num_edges`` in total."""
+    """Heterophilous citation-like DAG with exactly ``num_edges`` distinct edges: node i cites uniformly chosen
+    earlier nodes j < i; the number of citations per node follows a power law."""
     rng = np.random.default_rng(seed)
     n = int(num_nodes)
     w = _power_law_weights(n, exponent, rng)
-    out_deg = np.floor(w / w.sum() * num_edges).astype(np.int64)
+    w[0] = 0.0                                            # node 0 has no predecessor
+    p = w / w.sum()
+    cdf = np.cumsum(p)
+    out_deg = np.floor(p * num_edges).astype(np.int64)
     out_deg = np.minimum(out_deg, np.arange(n))           # node i has only i predecessors
-    short = int(num_edges - out_deg.sum())
-    if short > 0:
-        extra = rng.integers(1, n, size=short)
-        np.add.at(out_deg, extra, 1)
-        out_deg = np.minimum(out_deg, np.arange(n))
-    src = np.repeat(np.arange(n, dtype=np.int64), out_deg)
-    dst = (rng.random(src.size) * src).astype(np.int64)
-    key = np.unique(src * n + dst)
+    src0 = np.repeat(np.arange(n, dtype=np.int64), out_deg)
+    first = [src0 * n + (rng.random(src0.size) * src0).astype(np.int64)]
+
+    def sample(m: int) -> np.ndarray:
+        if first:
+            return first.pop()
+        src = np.searchsorted(cdf, rng.random(m)).clip(1, n - 1).astype(np.int64)
+        return src * n + (rng.random(m) * src).astype(np.int64)
+
+    key = _unique_to_target(sample, num_edges, rng)
     return torch.from_numpy(np.stack([key // n, key % n]).astype(np.int64))
 
 
