@@ -60,6 +60,7 @@ struct GemmArgs {
   int out_bufs;                  // staging buffers (1 to 3) when tma_store
   int bias_in_smem;              // bias copied to shared memory once per CTA (N <= 1024)
   int n_groups;                  // epilogue column groups in use (4, 2 or 1)
+  int panel_w;                   // columns per staged output panel: 64 (128-byte swizzle) or a destination's slice (unswizzled)
 };
 
 struct OutMaps {
@@ -340,6 +341,15 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     // the wait for the accumulator (one whole tile earlier when there are three buffers).
     const bool staged = pre_any && g.tma_store;
     const bool ahead = staged && g.out_bufs == 3;
+    // address of the 16-byte chunk holding columns [ct, ct + 8) of tile row `r` in a staging buffer.  64-column panels
+    // use the 128-byte swizzle of the TMA store (chunk c of row r at c ^ (r & 7)); panels as wide as one destination's
+    // column slice (fused all-to-all with slices that are not multiples of 64) are plain row-major.
+    const int pw = g.panel_w;
+    auto chunk_ptr = [&](uint8_t* buf, int r, int ct) -> uint8_t* {
+      if (pw == 64) return buf + (size_t)(ct >> 6) * (BLOCK_M * 128) + (size_t)r * 128 + ((((ct & 63) >> 3) ^ (r & 7)) << 4);
+      const int pn = ct / pw;
+      return buf + (size_t)pn * (BLOCK_M * pw * 2) + (size_t)r * (pw * 2) + (size_t)(ct - pn * pw) * 2;
+    };
     auto stage_operand = [&](int tile, uint8_t* buf) {
       const int mt = tile / g.n_chunks, nc = tile % g.n_chunks;
       const int L = cpg >> 3;                                     // 16-byte chunks per row of the block
@@ -351,12 +361,20 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const long long grow = (long long)mt * BLOCK_M + rr;
           if (grow < g.M) {
             const int ct = col_begin + cc * 8;
-            uint8_t* dstp = buf + (size_t)(ct >> 6) * (BLOCK_M * 128) + (size_t)rr * 128 + ((((ct & 63) >> 3) ^ (rr & 7)) << 4);
-            cp_async_16(dstp, pre_base + grow * pre_ld + nc * g.block_n + ct);
+            cp_async_16(chunk_ptr(buf, rr, ct), pre_base + grow * pre_ld + nc * g.block_n + ct);
           }
         }
       }
     };
+    // this thread's four possible 16-column slots inside a staging buffer (fixed for the whole kernel)
+    uint32_t soff0[4], soff1[4];
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int ct = col_begin + it * 16;
+      const bool in_tile = group_active && it * 16 < cpg && g.tma_store;
+      soff0[it] = in_tile ? (uint32_t)(chunk_ptr(smem_out, row_in_tile, ct) - smem_out) : 0u;
+      soff1[it] = in_tile ? (uint32_t)(chunk_ptr(smem_out, row_in_tile, ct + 8) - smem_out) : 0u;
+    }
     uint32_t acc = 0, acc_phase = 0;
     int out_sel = 0;
     bool ok = true;
@@ -400,10 +418,8 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tmem_ld_32x32b_x16(taddr + (uint32_t)c0, r);
         const int col0 = gcol_begin + c0;
         // where this thread's 16 results go in the staging buffer (and where a staged residual / mask waits)
-        const int ct0 = col_begin + c0;
-        uint8_t* panel = stage_out + (size_t)(ct0 >> 6) * (BLOCK_M * 128) + (size_t)row_in_tile * 128;
-        uint4* slot0 = reinterpret_cast<uint4*>(panel + ((((ct0 & 63) >> 3) ^ (row_in_tile & 7)) << 4));
-        uint4* slot1 = reinterpret_cast<uint4*>(panel + (((((ct0 & 63) >> 3) + 1) ^ (row_in_tile & 7)) << 4));
+        uint4* slot0 = reinterpret_cast<uint4*>(stage_out + soff0[it]);
+        uint4* slot1 = reinterpret_cast<uint4*>(stage_out + soff1[it]);
         uint4 pre0 = make_uint4(0, 0, 0, 0), pre1 = pre0;
         if (pre_any && row_ok) {
           if (staged) { pre0 = *slot0; pre1 = *slot1; }
@@ -486,8 +502,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         o1.x = pack2(v[8], v[9], is_fp16); o1.y = pack2(v[10], v[11], is_fp16);
         o1.z = pack2(v[12], v[13], is_fp16); o1.w = pack2(v[14], v[15], is_fp16);
         if (g.tma_store) {
-          // 16-bit result into the swizzled staging panel: 16-byte chunk c of row r lives at chunk (c ^ (r & 7))
-          *slot0 = o0;
+                *slot0 = o0;
           *slot1 = o1;
         } else {
           // route the 16 columns: they never straddle a destination because cols_per_dest % 16 == 0
@@ -507,11 +522,11 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (leader) {
           const int tile_col0 = n_chunk * g.block_n;
           const int y = (int)(g.dst_row_offset + (long long)m_tile * BLOCK_M);
-          for (int pnl = 0; pnl < g.block_n / 64; ++pnl) {
-            const int gc = tile_col0 + pnl * 64;
+          for (int pnl = 0; pnl < g.block_n / pw; ++pnl) {
+            const int gc = tile_col0 + pnl * pw;
             const int dest = g.n_dest > 1 ? gc / g.cols_per_dest : 0;
             const int dcol = g.n_dest > 1 ? gc - dest * g.cols_per_dest : gc;
-            tma_store_2d(&omaps.m[dest], stage_out + (size_t)pnl * (BLOCK_M * 128), dcol, y);
+            tma_store_2d(&omaps.m[dest], stage_out + (size_t)pnl * (BLOCK_M * pw * 2), dcol, y);
           }
           tma_store_commit();
         }
@@ -557,18 +572,20 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D row-major 16-bit tensor [rows, cols] with row stride ld (elements); box = [box_rows, 64 cols], swizzle 128B.
+// 2-D row-major 16-bit tensor [rows, cols] with row stride ld (elements); box = [box_rows, box_cols]; 64-column boxes
+// use the 128-byte swizzle, other widths are unswizzled.
 int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows,
-             int is_fp16) {
+             int is_fp16, int box_cols = BLOCK_K) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  box_cols == BLOCK_K ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
@@ -621,7 +638,16 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   g.bias_in_smem = (p->bias != nullptr && p->N <= 1024) ? 1 : 0;
   const size_t bias_bytes = g.bias_in_smem ? (size_t)p->N * 4 + 16 : 0;
   const size_t budget = 227 * 1024 - 1024 /*alignment slack*/ - sizeof(Control) - 64 - bias_bytes;
-  bool tma_ok = !p->out_fp32 && g.block_n % 64 == 0 && (p->n_dest == 1 || cols_per_dest % 64 == 0) &&
+  // staged output panels: 64 columns (swizzled) when every destination's slice is a multiple of 64 columns, else one
+  // panel per destination slice (e.g. 48 columns of q|k|v per rank with 8 ranks): a slice of a row tile is then one
+  // contiguous bulk store into the peer's buffer instead of 128 separate 32-byte stores
+  g.panel_w = 64;
+  bool slice_panels = false;
+  if (p->n_dest > 1 && cols_per_dest % 64 != 0) {
+    slice_panels = cols_per_dest % 16 == 0 && cols_per_dest <= 256 && g.block_n % cols_per_dest == 0;
+    if (slice_panels) g.panel_w = cols_per_dest;
+  }
+  bool tma_ok = !p->out_fp32 && g.block_n % 64 == 0 && (p->n_dest == 1 || cols_per_dest % 64 == 0 || slice_panels) &&
                 (p->ldc * 2) % 16 == 0;
   for (int i = 0; i < p->n_dest && tma_ok; ++i) tma_ok = ((uintptr_t)p->dst[i]) % 16 == 0;
   g.tma_store = 0; g.out_bufs = 0; g.stages = MAX_STAGES;
@@ -637,7 +663,7 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   if (g.tma_store) {
     for (int d = 0; d < p->n_dest; ++d) {
       // rows beyond this call's region are out of range for the map, so the tail of the last row tile is clipped
-      if (make_map(&omaps.m[d], p->dst[d], p->dst_row_offset + p->M, cols_per_dest, p->ldc, BLOCK_M, g.is_fp16) != 0) {
+      if (make_map(&omaps.m[d], p->dst[d], p->dst_row_offset + p->M, cols_per_dest, p->ldc, BLOCK_M, g.is_fp16, g.panel_w) != 0) {
         g.tma_store = 0; g.out_bufs = 0; g.stages = MAX_STAGES;
         break;
       }

@@ -193,3 +193,27 @@ def test_fused_nll_loss(dtype, classes):
     assert abs(float(loss) - float(ref)) < (2e-2 if dtype == torch.bfloat16 else 1e-5)
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-6
     assert torch.allclose(logits.grad.float(), ref_in.grad, atol=tol * float(ref_in.grad.abs().max()) + 1e-9)
+
+
+@pytest.mark.parametrize("n,n_dest,row0", [(384, 8, 0), (384, 4, 256), (384, 2, 0), (128, 8, 128), (128, 4, 0), (256, 8, 0)])
+def test_gemm_routes_column_slices_to_destinations(n, n_dest, row0):
+    """The fused all-to-all epilogue on one GPU: every destination is a local buffer here (peer pointers take the same
+    path).  Slices of 48 / 96 / 16 / 32 columns use destination-wide staged panels, 192 the swizzled 64-column ones."""
+    from budgetformer_b200.ops import _ext
+    torch.manual_seed(1)
+    m, k = 1000, 128
+    cpd = n // n_dest
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(n, device="cuda")
+    total_rows = row0 + m + 64
+    outs = [torch.full((total_rows, cpd), 7.0, device="cuda", dtype=torch.bfloat16) for _ in range(n_dest)]
+    _ext.load().gemm_tn(x, w, bias, 0, 0.0, 0, None, None, 1.0, False, [o.data_ptr() for o in outs], row0, cpd,
+                        gemm.status_tensor("cuda"))
+    gemm.check_status("cuda")
+    ref = x.float() @ w.float().t() + bias
+    for d, o in enumerate(outs):
+        got = o[row0:row0 + m].float()
+        assert (got - ref[:, d * cpd:(d + 1) * cpd]).abs().max() < 0.06, d
+        # rows outside this call's region stay untouched (the tail of the last row tile is clipped)
+        assert bool((o[:row0] == 7.0).all()) and bool((o[row0 + m:] == 7.0).all()), d
