@@ -110,6 +110,9 @@ _EXTRA = [
     (("--sync_batchnorm",), _STORE_TRUE, False, {"help": "all-reduce BatchNorm statistics over SP ranks"}),
     (("--metrics_jsonl",), str, "", {"help": "write one JSON line per epoch (device-timed)"}),
     (("--fault_inject",), str, "", {"help": "host-side fault injection spec, e.g. oom@fwd:3 or exit@7:rank1"}),
+    (("--nvtx",), _STORE_TRUE, False, {"help": "emit NVTX ranges for step phases and profiled calls"}),
+    (("--debug_checks",), _STORE_TRUE, False, {"help": "validate every attention graph, poison reusable symmetric "
+                                               "buffers after use and check losses/gradients for NaN (also BF_DEBUG=1)"}),
     (("--cuda_graph",), _STORE_TRUE, False, {"help": "capture the optimizer step in a CUDA graph"}),
 ]
 

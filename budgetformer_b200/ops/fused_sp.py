@@ -29,6 +29,7 @@ from torch.utils.checkpoint import checkpoint
 from ..graph.attn_graph import AttnGraph, as_attn_graph
 from ..parallel import symm
 from . import _ext, gemm
+from ..utils import debug
 from .edge_attention import _VARIANTS
 from .ffn import fused_ffn
 from .norm import ColsumSlot, batch_norm, column_sum, hash_dropout, layer_norm, new_seed
@@ -117,9 +118,12 @@ class _QKVPush(torch.autograd.Function):
             dres = dres.to(x.dtype).contiguous()
         dx = gemm.gemm_tn(dloc, w.t().contiguous(), residual=dres)
         dw = torch.matmul(dloc.t(), x).float()[sp.inv_perm]
+        db_src = column_sum(dloc) if ctx.has_bias else None
+        if debug.enabled():
+            debug.poison(buf.tensor)                  # consumed: whoever reads it before the next producer sees NaN
         dwq, dwk, dwv = (t.to(ctx.wdtype) for t in dw.split(sp.h, 0))
         if ctx.has_bias:
-            db = column_sum(dloc)[sp.inv_perm]
+            db = db_src[sp.inv_perm]
             dbq, dbk, dbv = (t.to(ctx.wdtype) for t in db.split(sp.h, 0))
         else:
             dbq = dbk = dbv = None
@@ -177,6 +181,8 @@ class _PackedEdgeAttention(torch.autograd.Function):
                           graph.etype, graph.t_rowptr, graph.t_row, graph.t_eid, etable if has_tab else None, detab,
                           variant_id, dropout_p, seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots))
         _ext.count_launches(3)
+        if debug.enabled() and dout.data_ptr() == sp.dctx.tensor.data_ptr():
+            debug.poison(sp.dctx.tensor)              # d(context) consumed; the next push must overwrite all of it
         return dbuf, (detab.to(etable.dtype) if has_tab else None), None, None, None, None, None, None
 
 

@@ -32,7 +32,7 @@ from ..parallel.initialize import (get_sequence_parallel_group, get_sequence_par
                                    get_sequence_parallel_src_rank, get_sequence_parallel_world_size,
                                    initialize_distributed, set_global_token_indices)
 from ..parallel.reducer import build_gradient_reducer, sync_params_and_buffers
-from ..utils import comm_profiler
+from ..utils import comm_profiler, debug
 from ..utils.fault import FaultInjector
 from ..utils.lr import build_lr_scheduler
 from ..utils.misc import (StepTimer, autocast_context, process_peak_rss_mib, process_rss_mib, resolve_amp_dtype,
@@ -82,6 +82,9 @@ class FullGraphTrainer:
         self.amp_dtype = resolve_amp_dtype(getattr(args, "amp_dtype", "none"), self.device)
         set_seed(int(args.seed))
         comm_profiler.enable_comm_profiler(bool(getattr(args, "profile_sp_comm", False)))
+        comm_profiler.enable_nvtx(bool(getattr(args, "nvtx", False)))
+        if bool(getattr(args, "debug_checks", False)):
+            debug.enable(True)
         self.fault = FaultInjector(getattr(args, "fault_inject", "") or "", self.rank)
 
         # ---- data -------------------------------------------------------------------------------
@@ -314,14 +317,16 @@ class FullGraphTrainer:
     def _fwd_bwd_opt(self, graph: AttnGraph, epoch: int, x_local, timers: Dict[str, float], sync_timers: bool):
         self.model.train()
         stage = {"bwd_started": False}
-        with StepTimer(self.device, sync_timers) as t_fwd:
+        if debug.enabled():
+            debug.validate_graph(graph)
+        with StepTimer(self.device, sync_timers) as t_fwd, comm_profiler.nvtx_range("forward"):
             self.fault.check("fwd", epoch)
             ctx = torch.autograd.graph.save_on_cpu(pin_memory=True) if (
                 getattr(self.args, "activation_cpu_offload", False) and self.planner is None
                 and self.device.type == "cuda") else _null()
             with ctx:
                 loss, _ = self._loss(graph, self.local_idx["train"], x_local)
-        with StepTimer(self.device, sync_timers) as t_bwd:
+        with StepTimer(self.device, sync_timers) as t_bwd, comm_profiler.nvtx_range("backward"):
             self.reducer.prepare_backward()
             stage["bwd_started"] = True
             self._stage = stage
@@ -331,7 +336,10 @@ class FullGraphTrainer:
             else:
                 loss.backward()
             self.reducer.finalize_backward()
-        with StepTimer(self.device, sync_timers) as t_opt:
+        if debug.enabled():
+            debug.assert_finite(f"the loss of epoch {epoch}", loss.detach())
+            debug.assert_finite(f"the gradients of epoch {epoch}", *[p.grad for p in self.model.parameters()])
+        with StepTimer(self.device, sync_timers) as t_opt, comm_profiler.nvtx_range("optimizer"):
             self.fault.check("opt", epoch)
             if self.scaler.is_enabled():
                 self.scaler.unscale_(self.optimizer)
@@ -421,7 +429,7 @@ class FullGraphTrainer:
         if x_host is not None:
             x_local = self._stage_input(x_host)
         self._align_ranks()
-        with StepTimer(self.device, sync_timers) as t_rw:
+        with StepTimer(self.device, sync_timers) as t_rw, comm_profiler.nvtx_range("edge_build"):
             graph = self.build_edges(epoch)
         timers["rw"] = t_rw.elapsed
         timers["prefetch_wait"] = self.edge_engine.last_prefetch_wait_s

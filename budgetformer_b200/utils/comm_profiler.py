@@ -13,6 +13,7 @@ from typing import Callable, Dict
 import torch
 
 _ENABLED = False
+_NVTX = False
 _TIMES: Dict[str, dict] = {}
 _SCALARS: Dict[str, float] = {}
 
@@ -32,6 +33,30 @@ def comm_profiler_enabled() -> bool:
     return _ENABLED
 
 
+def enable_nvtx(enabled: bool = True) -> None:
+    """NVTX ranges around every ``profile_call`` and every ``nvtx_range`` (visible in Nsight timelines); independent of
+    the timing registry, costs nothing when off."""
+    global _NVTX
+    _NVTX = bool(enabled) and torch.cuda.is_available()
+
+
+class nvtx_range:
+    """``with nvtx_range("fwd"): ...`` - a named range when NVTX output is enabled, otherwise a no-op."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _NVTX:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def reset_comm_profiler() -> None:
     _TIMES.clear()
     _SCALARS.clear()
@@ -48,6 +73,9 @@ def _slot(name: str) -> dict:
 def profile_call(name: str, fn: Callable, device=None, payload_bytes: int = 0):
     """Run ``fn()``; when profiling is on, time it under ``name``."""
     if not _ENABLED:
+        if _NVTX:
+            with nvtx_range(name):
+                return fn()
         return fn()
     slot = _slot(name)
     dev = torch.device(device) if device is not None else None

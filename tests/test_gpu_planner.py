@@ -87,3 +87,18 @@ def test_device_lookahead_build_matches_synchronous_build():
         losses[mode] = vals
     gemm.check_status("cuda")
     assert all(abs(a - b) < 2e-3 for a, b in zip(losses["ahead"], losses["sync"])), losses
+
+
+def test_training_with_debug_checks_and_nvtx_runs_clean():
+    """--debug_checks (graph validation, NaN-poisoned gradient buffers after use, finite checks) and --nvtx on the fused
+    path: four steps without a complaint and with a falling loss."""
+    from budgetformer_b200.utils import debug
+    t = _trainer(["--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4", "--debug_checks", "--nvtx"])
+    try:
+        assert debug.enabled() and t.fused_sp
+        losses = [t.train_step(e)["loss"] for e in range(1, 7)]
+    finally:
+        debug.enable(False)
+        t.edge_engine.shutdown()
+    gemm.check_status("cuda")
+    assert all(l == l for l in losses) and losses[-1] < losses[0]

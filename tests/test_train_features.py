@@ -131,3 +131,35 @@ def test_edge_policies_and_prefetch_agree():
     g4 = t.edge_engine.build(8, t.budget_state())
     assert torch.equal(g3.col, g4.col)
     t.edge_engine.shutdown()
+
+
+def test_debug_checks_validate_graphs_and_flag_nan():
+    """The sanitizer stand-in: broken graphs are named before a kernel could index with them, NaN is attributed."""
+    import pytest
+    from budgetformer_b200.graph.attn_graph import AttnGraph
+    from budgetformer_b200.utils import debug
+    from tests.helpers import random_attn_graph
+    g = random_attn_graph(100, 600, hub_col=80, seed=1).ensure_transpose()
+    debug.validate_graph(g)
+    bad = AttnGraph(g.num_rows, g.rowptr.clone(), g.col.clone(), None)
+    bad.col[5] = 100
+    with pytest.raises(ValueError, match="key ids outside"):
+        debug.validate_graph(bad)
+    bad = AttnGraph(g.num_rows, g.rowptr.clone(), g.col.clone(), None)
+    bad.rowptr[3] = bad.rowptr[4] + 1
+    with pytest.raises(ValueError, match="monotone"):
+        debug.validate_graph(bad)
+    bad = AttnGraph(g.num_rows, g.rowptr, g.col, None).ensure_transpose()
+    bad.t_task = bad.t_task.clone()
+    bad.t_task[0, 2] -= 1
+    with pytest.raises(ValueError, match="work items"):
+        debug.validate_graph(bad)
+    debug.enable(True)
+    try:
+        t = torch.ones(4)
+        debug.poison(t)
+        assert bool(torch.isnan(t).all())
+        with pytest.raises(FloatingPointError, match="epoch 3"):
+            debug.assert_finite("the gradients of epoch 3", torch.ones(2), t)
+    finally:
+        debug.enable(False)
