@@ -143,15 +143,43 @@ def make_bench_graph(name: str, seed: int = 42, scale: float = 1.0):
         x, y, ei = sbm_graph(n, feat_dim=cfg["feat"], seed=seed)
         return x, y, ei, cfg
     e = max(n, int(cfg["edges"] * scale))
-    if cfg["graph"] == "chung_lu_directed":
-        ei = chung_lu_edges(n, e, 2.1, True, seed)
-    elif cfg["graph"] == "chung_lu_undirected":
-        ei = chung_lu_edges(n, e, 2.1, False, seed)
-    else:
-        ei = citation_dag_edges(n, e, 2.2, seed)
+    ei = _cached_edges(f"{name}_{cfg['graph']}_{n}_{e}_{int(seed)}", lambda: _make_edges(cfg["graph"], n, e, seed))
     x = random_features(n, cfg["feat"], seed)
     y = random_labels(n, cfg["classes"], seed, 0.05 if cfg.get("multilabel") else None)
     return x, y, ei, cfg
+
+
+def _make_edges(kind: str, n: int, e: int, seed: int) -> torch.Tensor:
+    if kind == "chung_lu_directed":
+        return chung_lu_edges(n, e, 2.1, True, seed)
+    if kind == "chung_lu_undirected":
+        return chung_lu_edges(n, e, 2.1, False, seed)
+    return citation_dag_edges(n, e, 2.2, seed)
+
+
+def _cached_edges(tag: str, make) -> torch.Tensor:
+    """Edge lists of the large configurations take minutes of sorting to generate; consecutive benchmark runs on one
+    machine (1/2/4/8 ranks, both arms) share them through ``$BF_BENCH_CACHE`` (default: ``.bench_cache`` beside the
+    package; an empty value disables it).  Generation is deterministic, so concurrent writers produce identical files;
+    the rename is atomic."""
+    pkg_parent = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.environ.get("BF_BENCH_CACHE", os.path.join(pkg_parent, ".bench_cache"))
+    path = os.path.join(root, tag + ".pt")
+    if root and os.path.exists(path):
+        try:
+            return torch.load(path)
+        except Exception:
+            pass
+    ei = make()
+    if root and ei.numel() >= (1 << 20):
+        try:
+            os.makedirs(root, exist_ok=True)
+            tmp = f"{path}.{os.getpid()}.tmp"
+            torch.save(ei, tmp)
+            os.replace(tmp, path)
+        except OSError:
+            pass
+    return ei
 
 
 def write_dataset(root: str, name: str, x: torch.Tensor, y: torch.Tensor, edge_index: torch.Tensor) -> str:
