@@ -208,8 +208,9 @@ def run_ours(ns):
         if e2e_ms is not None:
             e_step = e2e_ms_max / ns.steps
             rec["e2e"] = {"value": n / (e_step / 1e3), "unit": "nodes/s", "ms_per_step": e_step,
-                          "h2d_bytes_per_step": int(trainer.x_host.numel() * trainer.x_host.element_size()),
-                          "d2h_bytes_per_step": 4}
+                          # whole job: every rank uploads its slice of the features and reads its loss back
+                          "h2d_bytes_per_step": int(trainer.x_host.numel() * trainer.x_host.element_size()) * world,
+                          "d2h_bytes_per_step": 4 * world}
         print(json.dumps(rec), flush=True)
     trainer.edge_engine.shutdown()
     if world > 1:
