@@ -63,7 +63,9 @@ __global__ void task_counts_kernel(const int* __restrict__ t_rowptr, int n, int 
   is_split[k] = c > 1 ? 1 : 0;
 }
 
-// One warp per key: lane l writes items l, l+32, ... (hub keys own thousands of items).
+// One warp per key: lane l writes items l, l+32, ... (hub keys own thousands of items).  The list starts with the
+// items of all split keys (full-length items: the long work is scheduled first and runs side by side in a warp),
+// followed by the single item of every other key in key order; an item of a split key sits at its partial-slot index.
 __global__ void task_fill_kernel(const int* __restrict__ t_rowptr, const int* __restrict__ item_first,
                                  const int* __restrict__ slot_first, const int* __restrict__ split_first, int n,
                                  int chunk, int4* __restrict__ tasks, int* __restrict__ splits) {
@@ -71,14 +73,18 @@ __global__ void task_fill_kernel(const int* __restrict__ t_rowptr, const int* __
   const int k = (int)(gt >> 5), lane = (int)(gt & 31);
   if (k >= n) return;
   const int beg = t_rowptr[k], end = t_rowptr[k + 1];
-  const int first = item_first[k], cnt = item_first[k + 1] - first;
+  const int cnt = item_first[k + 1] - item_first[k];
   const int s0 = slot_first[k];
+  const int total_slots = slot_first[n];
+  if (cnt == 1) {
+    if (lane == 0) tasks[total_slots + (k - split_first[k])] = make_int4(k, beg, end, -1);
+    return;
+  }
   for (int c = lane; c < cnt; c += 32) {
     const int b = beg + c * chunk;
     int e = b + chunk;
     if (e > end) e = end;
-    if (cnt == 1) e = end;
-    tasks[first + c] = make_int4(k, b, e, cnt > 1 ? s0 + c : -1);
+    tasks[s0 + c] = make_int4(k, b, e, s0 + c);
   }
   if (lane == 0 && cnt > 1) {
     const int s = split_first[k];

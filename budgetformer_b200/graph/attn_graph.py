@@ -21,7 +21,8 @@ from typing import Optional
 import torch
 
 HUB_DEGREE = 1024  # rows longer than this take the chunked hub path in the kernels
-KV_TASK_EDGES = 64  # edges per work item of the dK/dV pass
+import os as _os
+KV_TASK_EDGES = int(_os.environ.get('BF_KV_CHUNK', '64'))  # edges per work item of the dK/dV pass
 
 
 @dataclass
@@ -153,6 +154,9 @@ class AttnGraph:
                 self.rowptr.contiguous(), self.col.contiguous(), int(self.num_rows), int(KV_TASK_EDGES))
             _ext.count_launches(9)
             self.t_rowptr, self.t_row, self.t_eid = t_rowptr, t_row, t_eid
+            if _os.environ.get('BF_KV_SORT', '0') == '1' and tasks.numel():
+                order = torch.argsort(tasks[:, 2] - tasks[:, 1], descending=True, stable=True)
+                tasks = tasks[order].contiguous()
             self.t_task, self.t_split, self.kv_slots = tasks, splits, int(sizes[1])
             return self
         col64 = self.col.to(torch.int64)
@@ -186,7 +190,10 @@ class AttnGraph:
         is_split = split_row[rows]
         slot = torch.cumsum(is_split.to(torch.int64), 0) - 1
         slot = torch.where(is_split, slot, torch.full_like(slot, -1))
-        self.t_task = torch.stack([rows, beg, end, slot], 1).to(torch.int32).contiguous()
+        tasks = torch.stack([rows, beg, end, slot], 1)
+        # items of split keys first (long work is scheduled first), then one item per remaining key, both in key order
+        tasks = torch.cat([tasks[is_split], tasks[~is_split]], 0)
+        self.t_task = tasks.to(torch.int32).contiguous()
         srows = torch.nonzero(split_row).flatten()
         nsl = n_chunks[srows]
         sfirst = torch.cumsum(nsl, 0) - nsl

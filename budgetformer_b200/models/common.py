@@ -106,8 +106,8 @@ def apply_tier(layer, mode: str, x, **kwargs):
     return checkpoint(_full, x, use_reentrant=False)
 
 
-def encode_features(encoder: nn.Linear, x: torch.Tensor) -> torch.Tensor:
-    """``encoder(x)`` for a 2-D feature matrix whose columns may have been zero-padded by the caller.
+def encode_features(encoder: nn.Linear, x: torch.Tensor, dropout: Optional[nn.Dropout] = None) -> torch.Tensor:
+    """``dropout(encoder(x))`` for a 2-D feature matrix whose columns may have been zero-padded by the caller.
 
     Feature widths such as 269 leave rows unaligned, which sends the library GEMM to slow legacy kernels; the
     trainer therefore pads the feature matrix once to a multiple of 8 columns and the weight is padded to match
@@ -118,10 +118,14 @@ def encode_features(encoder: nn.Linear, x: torch.Tensor) -> torch.Tensor:
         raise ValueError(f"feature matrix has {x.size(-1)} columns, encoder expects {w.size(1)}")
     if extra:
         w = F.pad(w, (0, extra))
+    p = float(dropout.p) if (dropout is not None and dropout.training) else 0.0
     if x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16):
+        # input dropout runs in the GEMM epilogue (counter-based mask, regenerated in backward: no mask tensor)
         from ..ops.gemm import fused_linear
-        return fused_linear(x, w, encoder.bias)
-    return F.linear(x, w, encoder.bias)
+        from ..ops.norm import new_seed
+        return fused_linear(x, w, encoder.bias, dropout_p=p, dropout_seed=new_seed() if p > 0 else 0)
+    y = F.linear(x, w, encoder.bias)
+    return dropout(y) if dropout is not None else y
 
 
 class NodeModelBase(nn.Module):

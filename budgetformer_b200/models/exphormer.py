@@ -109,7 +109,7 @@ class Exphormer(NodeModelBase):
         self._init_ckpt_state()
 
     def forward_logits(self, x, attn_bias, edge_index, attn_type=None):
-        x = self.input_dropout(encode_features(self.node_encoder, x).unsqueeze(0))
+        x = encode_features(self.node_encoder, x, self.input_dropout).unsqueeze(0)
         x = self._run_layers(x, attn_bias=attn_bias, edge_index=edge_index, attn_type=attn_type)
         return self.output_proj(x.squeeze(0))
 

@@ -105,10 +105,10 @@ class GT(NodeModelBase):
         self._init_ckpt_state()
 
     def forward_logits(self, x, attn_bias, edge_index, perturb=None, attn_type=None):
-        x = encode_features(self.node_encoder, x).unsqueeze(0)
-        if perturb is not None:
-            x = x - perturb
-        x = self.input_dropout(x)
+        if perturb is None:
+            x = encode_features(self.node_encoder, x, self.input_dropout).unsqueeze(0)
+        else:
+            x = self.input_dropout(encode_features(self.node_encoder, x).unsqueeze(0) - perturb)
         x = self._run_layers(x, edge_index=edge_index, attn_type=attn_type)
         return self.MLP_layer(x.squeeze(0))
 
