@@ -58,6 +58,47 @@ class SparseCoreAttention(nn.Module):
     def edge_table(self) -> Optional[torch.Tensor]:
         return None
 
+    # ---- research analytics (models/gt_dist_node_level.py:75-139 in the reference); off unless enabled ----------
+    def enable_hop_mass_tracking(self, mass: float = 0.95, max_queries: int = 64, query_sampling: str = "random",
+                                 max_batches: int = 1, max_hop: int = 15) -> None:
+        from ..utils.analytics import HeadMassStats, HopMassTracker
+        self.hop_tracker = HopMassTracker(mass, max_hop, max_batches)
+        self.head_mass = HeadMassStats(self.num_attention_heads_per_partition)
+        self.hop_mass_max_queries, self.hop_mass_query_sampling = int(max_queries), str(query_sampling)
+        self.track_hop_mass = True
+
+    def disable_hop_mass_tracking(self) -> None:
+        self.track_hop_mass = False
+
+    def reset_hop_mass_stats(self) -> None:
+        if getattr(self, "hop_tracker", None) is not None:
+            self.hop_tracker.reset()
+
+    def reset_head_mass_stats(self) -> None:
+        if getattr(self, "head_mass", None) is not None:
+            self.head_mass.reset()
+
+    def get_hop_mass_stats(self):
+        t = getattr(self, "hop_tracker", None)
+        return t.summary() if (t is not None and getattr(self, "track_hop_mass", False)) else None
+
+    def get_head_mass_stats(self):
+        h = getattr(self, "head_mass", None)
+        return h.mean() if h is not None else None
+
+    def _track_sparse(self, q, k, graph: AttnGraph, edge_hops) -> None:
+        """Normalised edge weights of this call, restated in PyTorch (analytics only; the kernels do not store them)."""
+        import math
+        with torch.no_grad():
+            src, dst = graph.col.to(torch.int64), graph.row_ids()
+            s = (k[0].float()[src] * q[0].float()[dst]).sum(-1) / math.sqrt(q.size(-1))
+            w = torch.exp(s.clamp(-5.0, 5.0))
+            z = torch.zeros(q.size(1), q.size(2), device=q.device).index_add_(0, dst, w)
+            a = w / (z[dst] + 1e-6)
+            self.head_mass.add(a)
+            if edge_hops is not None:
+                self.hop_tracker.add_sparse(dst, edge_hops, a)
+
     def full_attention(self, q, k, v, attn_bias=None):
         q = q.transpose(1, 2)
         k = k.transpose(1, 2).transpose(2, 3)
@@ -75,6 +116,8 @@ class SparseCoreAttention(nn.Module):
         seed = self._next_dropout_seed() if p_drop > 0 else 0
         out = edge_attention(q[0], k[0], v[0], graph, variant=self.variant, etable=self.edge_table(),
                              edge_bias=edge_bias, dropout_p=p_drop, dropout_seed=seed)
+        if getattr(self, "track_hop_mass", False):
+            self._track_sparse(q, k, graph, getattr(self, "edge_hops", None))
         return out.unsqueeze(0)
 
     def forward(self, q, k, v, attn_bias=None, edge_index=None, attn_type=None, **kw):

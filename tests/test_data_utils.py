@@ -68,3 +68,56 @@ def test_split_discovery_layouts(tmp_path):
 def test_synthetic_dataset_cli(tmp_path):
     p = get_dataset("synthetic:sbm2k", str(tmp_path))
     assert torch.load(os.path.join(p, "x.pt")).shape == (2048, 128)
+
+
+def test_edge_set_analytics_and_legacy_samplers():
+    import torch
+    from budgetformer_b200.graph import legacy_samplers as ls
+    from budgetformer_b200.utils import analytics as an
+    a = torch.tensor([[0, 1, 2, 3, 3], [1, 2, 3, 0, 0]])
+    b = torch.tensor([[0, 1, 4], [1, 2, 0]])
+    assert an.edge_ids(a, 5).numel() == 4                              # duplicate (3, 0) counted once
+    assert abs(an.edge_index_jaccard(a, b, 5) - 2 / 5) < 1e-9
+    assert abs(an.edge_index_new_edge_ratio(a, b, 5) - 1 / 3) < 1e-9
+    assert an.slice_edge_index(a, 1, 4).tolist() == [[0, 1], [1, 2]]
+    assert abs(an.calculate_sparsity(a, 5) - (1 - 4 / 25)) < 1e-9
+    p2 = an.calc_power_edge_index(torch.tensor([[0, 1], [1, 2]]), 3, 2)
+    assert sorted(map(tuple, p2.t().tolist())) == [(0, 1), (0, 2), (1, 2)]
+    sc = an.make_strongly_connected(torch.tensor([[0], [2]]), 4)
+    assert an.calc_power_edge_index(sc, 4, 4).size(1) == 12            # every ordered pair reachable
+    hops = an.bfs_hop_matrix(torch.tensor([[1, 2], [0, 1]]), 3, torch.tensor([0]))
+    assert hops.tolist() == [[0, 1, 2]]
+    tr = an.HopMassTracker(mass=0.9, max_hop=4, max_batches=2)
+    tr.add_sparse(torch.tensor([0, 0, 0]), torch.tensor([0, 1, 2]), torch.tensor([0.5, 0.4, 0.1]))
+    s = tr.summary()
+    assert s["calls"] == 1 and abs(s["hop_mass"][1] - 0.4) < 1e-6 and s["hops_for_target_max"] == 1
+    # samplers / head views
+    e = torch.stack([torch.arange(10), torch.arange(10).flip(0)])
+    assert ls.IdentitySubgraphSampler().sample(e, None, 10) is e
+    kept = ls.EdgeDropSubgraphSampler(0.5, torch.Generator().manual_seed(0)).sample(e, None, 10)
+    assert 0 < kept.size(1) <= 10
+    views = ls.GroupedHeadSubgraphProvider(2).build(e, 4)
+    assert len(views) == 4 and views[0] is views[1] and views[2] is views[3]
+    assert bool((views[0][0] % 2 == 0).all()) and bool((views[2][0] % 2 == 1).all())
+    hop_views = ls.HopMappedHeadSubgraphProvider([0, 1], 2).build([e[:, :3], e[:, 3:]], 4)
+    assert hop_views[0].size(1) == 3 and hop_views[3].size(1) == 7
+    assert len(ls.SharedHeadSubgraphProvider().build([None, e], 3)) == 3
+
+
+def test_hop_mass_tracking_on_core_attention():
+    import torch
+    from budgetformer_b200.models.common import SparseCoreAttention
+    from tests.helpers import random_attn_graph
+    torch.manual_seed(0)
+    core = SparseCoreAttention(32, 0.0, 4)
+    core.enable_hop_mass_tracking(mass=0.9, max_batches=3, max_hop=8)
+    g = random_attn_graph(50, 300, seed=2)
+    core.edge_hops = torch.randint(0, 4, (g.num_edges,))
+    q, k, v = (torch.randn(1, 50, 4, 8) for _ in range(3))
+    out = core(q, k, v, edge_index=g)
+    assert out.shape == (1, 50, 32)
+    stats = core.get_hop_mass_stats()
+    assert stats is not None and abs(sum(stats["hop_mass"]) - 1.0) < 1e-5
+    assert core.get_head_mass_stats().shape == (4,)
+    core.disable_hop_mass_tracking()
+    assert core.get_hop_mass_stats() is None
