@@ -3,7 +3,7 @@
 # setup.py / pyproject.toml, so it is installed from a scratch copy that only adds a packaging stub.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-SRC="${1:-/root/reference}"
+SRC="${1:?usage: install_reference.sh <path of the reference checkout>}"
 TMP="$(mktemp -d /tmp/bf_ref_XXXX)"
 cp -r "$SRC"/. "$TMP"/
 rm -rf "$TMP/.git"
