@@ -69,10 +69,8 @@ def fused_ffn(x: torch.Tensor, w1, b1, w2, b2, *, act: str = "relu", residual: O
         hdn = F.gelu(z)
         if p1 > 0:
             hdn = hash_dropout(hdn, new_seed(), p1)
-        y = gemm.fused_linear(hdn, w2, b2)
-        if p2 > 0:
-            y = hash_dropout(y, new_seed(), p2)
-        return y if residual is None else residual + y
+        # second GEMM: bias, output dropout and the residual add all happen in its epilogue
+        return gemm.fused_linear(hdn, w2, b2, residual=residual, dropout_p=p2, dropout_seed=new_seed() if p2 > 0 else 0)
     hdn = F.linear(x, w1.to(x.dtype), None if b1 is None else b1.to(x.dtype))
     hdn = F.relu(hdn) if act == "relu" else F.gelu(hdn)
     hdn = F.dropout(hdn, p1, training and p1 > 0)
