@@ -217,3 +217,23 @@ def test_gemm_routes_column_slices_to_destinations(n, n_dest, row0):
         assert (got - ref[:, d * cpd:(d + 1) * cpd]).abs().max() < 0.06, d
         # rows outside this call's region stay untouched (the tail of the last row tile is clipped)
         assert bool((o[:row0] == 7.0).all()) and bool((o[row0 + m:] == 7.0).all()), d
+
+
+def test_gemm_routes_slices_with_dropout_epilogue():
+    """The d(context) push of the backward pass: no bias, the pre-projection dropout mask regenerated in the epilogue,
+    16-column slices to 8 destinations (generic epilogue instance + destination-wide staged panels)."""
+    from budgetformer_b200.ops import _ext
+    torch.manual_seed(2)
+    m, n, k, n_dest, p, seed = 777, 128, 128, 8, 0.25, 1234
+    cpd = n // n_dest
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    outs = [torch.zeros(m, cpd, device="cuda", dtype=torch.bfloat16) for _ in range(n_dest)]
+    _ext.load().gemm_tn(x, w, None, 0, p, seed, None, None, 1.0, False, [o.data_ptr() for o in outs], 0, cpd,
+                        gemm.status_tensor("cuda"))
+    gemm.check_status("cuda")
+    keep = gemm.hash_keep_mask(seed, m, n, p, "cuda")
+    ref = torch.where(keep, (x.float() @ w.float().t()) / (1 - p), torch.zeros(1, device="cuda"))
+    got = torch.cat([o.float() for o in outs], 1)
+    assert (got - ref).abs().max() < 0.06
+    assert abs(float((got == 0).float().mean()) - p) < 0.03
