@@ -3,15 +3,20 @@
 //   C[M, N] = A[M, K] * B[N, K]^T      bf16 / fp16 operands, fp32 accumulation in tensor memory
 //
 // * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, one 64-element K panel per
-//   stage) into a 4-deep shared-memory ring; one elected thread issues tcgen05.mma (M = 128, N = BLOCK_N
-//   <= 256, K = 16 per instruction) and releases ring stages with tcgen05.commit;
-// * two accumulators of BLOCK_N columns alternate in tensor memory, so the epilogue warps drain tile i
-//   (tcgen05.ld) while tile i+1 is being multiplied;
-// * epilogue (per thread = one output row): + bias, ReLU / GELU, counter-based dropout, + residual,
-//   ReLU-gradient mask, then 16-byte stores.  With `n_dest > 1` the columns of a tile are routed to the
-//   owning rank's buffer through peer pointers: this is the sequence-parallel nodes->heads all-to-all
-//   (3 projections + 3 all-to-alls + 6 copies in the reference: gt_sp/layer.py:35-41,264-266) executed
-//   by the GEMM itself, tile by tile, with plain st.global over NVLink;
+//   stage; a ragged last panel is zero-filled) into a 3- or 4-deep shared-memory ring; one elected thread
+//   issues tcgen05.mma (M = 128, N = BLOCK_N <= 256, K = 16 per instruction) and releases ring stages with
+//   tcgen05.commit;
+// * two accumulators of BLOCK_N columns alternate in tensor memory, so the sixteen epilogue warps drain
+//   tile i (tcgen05.ld) while tile i+1 is being multiplied;
+// * epilogue (per thread = one output row, four column groups): + bias, ReLU / GELU, counter-based dropout,
+//   + residual, ReLU-gradient mask (residual / mask tiles are fetched with cp.async one tile ahead), results
+//   staged in shared memory and written with bulk TMA stores.  With `n_dest > 1` the columns of a tile are
+//   routed to the owning rank's buffer through peer pointers: this is the sequence-parallel nodes->heads
+//   all-to-all (3 projections + 3 all-to-alls + 6 copies in the reference: gt_sp/layer.py:35-41,264-266)
+//   executed by the GEMM itself, tile by tile, over NVLink - one bulk store per destination slice of a row
+//   tile (plain 32-byte st.global only when a slice is not a multiple of 16 columns);
+// * the epilogue feature set is a template parameter for the combinations the layers use (bf16), a generic
+//   instance covers everything else;
 // * every mbarrier wait is bounded: on expiry the kernel records a status word, stops issuing work,
 //   lets copies in flight land, frees its tensor memory and returns.
 #include <cuda.h>
