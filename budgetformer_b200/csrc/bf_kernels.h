@@ -35,6 +35,14 @@ typedef struct {
   const int* hub_rows;              // rows with degree > BF_HUB_DEGREE (may be NULL when n_hub == 0)
   int n_hub, max_hub_degree;
   float* hub_scratch;               // zero-filled [n_hub, hl*hn + hl] fp32
+  // Optional dropout on the attention output, fused into the store (0 = off).  The keep decision of element
+  // (row, c) is that of bf_hash_dropout / the GEMM epilogue for (row % out_rows_local, out_col0 + c): the context
+  // rows a rank computes are consumed by the rank owning them, at this rank's column offset.  The backward pass
+  // reads the stored (dropped, rescaled) output and rescales <dout, out> by (1 - p).
+  float out_dropout_p;
+  uint32_t out_dropout_seed;
+  int out_rows_local;               // rows per owning rank (0 = n)
+  int out_col0;                     // column offset of this rank's head slice in the owner's row
 } bf_attn_params;
 
 typedef struct {

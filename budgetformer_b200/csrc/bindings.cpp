@@ -55,9 +55,16 @@ HubInfo find_hubs(const Tensor& rowptr, int64_t known_max) {
   return h;
 }
 
+// out_drop = {p, seed, rows per owning rank, column offset} or empty: dropout fused into the attention output
 void fill_common(bf_attn_params& p, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
                  const Tensor& z, const Tensor& rowptr, const Tensor& col, const OptTensor& etype,
-                 const OptTensor& etab, int64_t variant, double dropout_p, int64_t seed) {
+                 const OptTensor& etab, int64_t variant, double dropout_p, int64_t seed,
+                 const std::vector<double>& out_drop) {
+  if (!out_drop.empty()) {
+    TORCH_CHECK(out_drop.size() == 4 && out_drop[0] >= 0.0 && out_drop[0] < 1.0, "out_drop = [p, seed, rows_local, col0]");
+    p.out_dropout_p = (float)out_drop[0]; p.out_dropout_seed = (uint32_t)(int64_t)out_drop[1];
+    p.out_rows_local = (int)out_drop[2]; p.out_col0 = (int)out_drop[3];
+  }
   check_qkv(q, "q"); check_qkv(k, "k"); check_qkv(v, "v");
   TORCH_CHECK(out.is_contiguous() && z.is_contiguous());
   TORCH_CHECK(rowptr.scalar_type() == torch::kInt && col.scalar_type() == torch::kInt, "graph indices must be int32");
@@ -74,10 +81,11 @@ void fill_common(bf_attn_params& p, const Tensor& q, const Tensor& k, const Tens
 }
 
 void edge_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor rowptr, Tensor col, OptTensor etype,
-                   OptTensor etab, int64_t variant, double dropout_p, int64_t seed, int64_t known_max_degree) {
+                   OptTensor etab, int64_t variant, double dropout_p, int64_t seed, int64_t known_max_degree,
+                   std::vector<double> out_drop) {
   c10::cuda::CUDAGuard guard(q.device());
   bf_attn_params p{};
-  fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed);
+  fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed, out_drop);
   HubInfo hub = find_hubs(rowptr, known_max_degree);
   Tensor scratch;
   if (hub.n > 0) {
@@ -91,10 +99,11 @@ void edge_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor ro
 void edge_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor dout, Tensor dq, Tensor dk, Tensor dv,
                    Tensor zd, Tensor rowptr, Tensor col, OptTensor etype, Tensor t_rowptr, Tensor t_row, Tensor t_eid,
                    OptTensor etab, OptTensor detab, int64_t variant, double dropout_p, int64_t seed,
-                   int64_t known_max_degree, OptTensor kv_task, OptTensor kv_split, int64_t kv_slots) {
+                   int64_t known_max_degree, OptTensor kv_task, OptTensor kv_split, int64_t kv_slots,
+                   std::vector<double> out_drop) {
   c10::cuda::CUDAGuard guard(q.device());
   bf_attn_params p{};
-  fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed);
+  fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed, out_drop);
   TORCH_CHECK(dout.is_contiguous());
   check_qkv(dq, "dq"); check_qkv(dk, "dk"); check_qkv(dv, "dv");
   TORCH_CHECK(dq.stride(0) == dk.stride(0) && dq.stride(0) == dv.stride(0), "dq/dk/dv must share one row stride");

@@ -152,7 +152,21 @@ struct AttnArgs {
   const int* hub_rows;         // [n_hub]
   int n_hub, hub_chunk;
   float* hub_scratch;          // forward: [n_hub, Hl*HN + Hl]
+  // fused dropout on the stored output (out_thresh == 0: off)
+  uint32_t out_thresh, out_seed;
+  float out_inv_keep, out_keep;
+  int out_rows_local, out_col0;
 };
+
+// keep decision of ops.gemm.hash_keep_mask / bf_hash_dropout for element (row, col)
+__device__ __forceinline__ bool keep_out(const AttnArgs& a, int row, int c) {
+  const uint32_t r = (uint32_t)(a.out_rows_local > 0 ? row % a.out_rows_local : row);
+  uint32_t x = r * 0x9E3779B1u + (uint32_t)(a.out_col0 + c) * 0x85EBCA77u + a.out_seed;
+  x = (x ^ (x >> 16)) * 0x7FEB352Du;
+  x = (x ^ (x >> 15)) * 0x846CA68Bu;
+  x ^= x >> 16;
+  return x >= a.out_thresh;
+}
 
 // Two edges of one query for one task lane (second one optional).
 template <typename T, int HN>
@@ -240,6 +254,10 @@ __global__ void __launch_bounds__(256) edge_attn_fwd_kernel(AttnArgs a) {
     float o[VN];
 #pragma unroll
     for (int i = 0; i < VN; ++i) o[i] = acc[i] * inv;
+    if (a.out_thresh) {
+#pragma unroll
+      for (int i = 0; i < VN; ++i) o[i] = keep_out(a, row, off + i) ? o[i] * a.out_inv_keep : 0.f;
+    }
     store_vec<T>(static_cast<T*>(a.out) + (long long)row * a.hl * HN + off, o);
     if ((lt % LPH) == 0) a.z[(long long)row * a.hl + head] = zsum;
   }
@@ -297,7 +315,9 @@ __global__ void edge_attn_fwd_hub_finalize(AttnArgs a) {
     const float zs = scratch[w + head];
     float inv = 1.f / (zs + kEps);
     if (a.variant == 1) inv *= a.inv_keep;
-    static_cast<T*>(a.out)[(long long)row * w + c] = from_float<T>(scratch[c] * inv);
+    float ov = scratch[c] * inv;
+    if (a.out_thresh) ov = keep_out(a, row, c) ? ov * a.out_inv_keep : 0.f;
+    static_cast<T*>(a.out)[(long long)row * w + c] = from_float<T>(ov);
     if ((c % HN) == 0) a.z[(long long)row * a.hl + head] = zs;
   }
 }
@@ -476,6 +496,7 @@ __global__ void __launch_bounds__(256, EXPH ? 3 : 4) edge_attn_bwd_q_kernel(BwdA
   for (int i = 0; i < VN; ++i) { dterm += dof[i] * of[i]; dq[i] = 0.f; de0[i] = 0.f; de1[i] = 0.f; }
   const unsigned hm = head_mask<LPH>();
   dterm = head_sum<LPH>(dterm, hm);
+  if (a.out_thresh) dterm *= a.out_keep;        // the stored output is the dropped one, rescaled by 1 / (1 - p)
   float zsum = head_ok ? a.z[(long long)row * a.hl + hsafe] : 1.f;
   const float invz = 1.f / (zsum + kEps);
   if (head_ok && (lt % LPH) == 0) b.zd[(long long)row * a.hl + head] = make_float2(invz, dterm);
@@ -531,6 +552,7 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_q_hub_kernel(BwdArgs b, int
     for (int i = 0; i < VN; ++i) { dterm += dof[i] * of[i]; dq[i] = 0.f; de0[i] = 0.f; de1[i] = 0.f; }
     const unsigned hm = head_mask<LPH>();
     dterm = head_sum<LPH>(dterm, hm);
+    if (a.out_thresh) dterm *= a.out_keep;
     const float invz = 1.f / (a.z[(long long)row * a.hl + hsafe] + kEps);
     if (head_ok)
       for (int e = cbeg + stream; e < cend; e += streams)
@@ -891,6 +913,11 @@ AttnArgs to_args(const bf_attn_params& p) {
   a.inv_keep = p.dropout_p > 0.f ? 1.f / (1.f - p.dropout_p) : 1.f;
   a.thresh = p.dropout_p > 0.f ? (uint32_t)(p.dropout_p * 4294967296.0) : 0u;
   a.seed = p.dropout_seed;
+  a.out_thresh = p.out_dropout_p > 0.f ? (uint32_t)(p.out_dropout_p * 4294967296.0) : 0u;
+  a.out_seed = p.out_dropout_seed;
+  a.out_keep = 1.f - p.out_dropout_p;
+  a.out_inv_keep = p.out_dropout_p > 0.f ? 1.f / (1.f - p.out_dropout_p) : 1.f;
+  a.out_rows_local = p.out_rows_local; a.out_col0 = p.out_col0;
   a.hub_rows = p.hub_rows; a.n_hub = p.n_hub; a.hub_chunk = BF_HUB_CHUNK; a.hub_scratch = p.hub_scratch;
   return a;
 }

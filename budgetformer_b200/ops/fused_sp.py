@@ -35,6 +35,10 @@ from .ffn import fused_ffn
 from .norm import ColsumSlot, batch_norm, column_sum, hash_dropout, layer_norm, new_seed
 
 
+# context dropout inside the attention kernel's store (off: a separate hash_dropout pass over the pulled context)
+FUSE_CONTEXT_DROPOUT = True
+
+
 class SPContext:
     """Symmetric buffers and geometry shared by all layers of one model."""
 
@@ -134,7 +138,8 @@ class _PackedEdgeAttention(torch.autograd.Function):
     """Edge attention on the packed q|k|v buffer; context and gradients live in symmetric buffers."""
 
     @staticmethod
-    def forward(ctx, qkv, etable, graph: AttnGraph, sp: SPContext, layer: int, variant_id, dropout_p, seed):
+    def forward(ctx, qkv, etable, graph: AttnGraph, sp: SPContext, layer: int, variant_id, dropout_p, seed,
+                out_p=0.0, out_seed=0):
         ext = _ext.load()
         r, hlh, hn, hl = sp.total_rows, sp.hl_heads, sp.hn, sp.hl
         q = qkv[:, 0:hl].view(r, hlh, hn)
@@ -143,13 +148,17 @@ class _PackedEdgeAttention(torch.autograd.Function):
         out = sp.ctx[layer].tensor
         z = torch.empty((r, hlh), dtype=torch.float32, device=qkv.device)
         kmax = -1 if graph.max_degree is None else int(graph.max_degree)
+        # dropout on the context (GT applies it before the output projection) is fused into the store: the mask of
+        # element (row, c) is the one the owner of that row regenerates for (row - its first row, this rank's column)
+        out_drop = [float(out_p), int(out_seed), int(sp.rows_local), int(sp.rank * hl)] if out_p > 0 else []
         ext.edge_attn_fwd(q, k, v, out.view(r, hlh, hn), z, graph.rowptr, graph.col, graph.etype, etable,
-                          int(variant_id), float(dropout_p), int(seed), kmax)
+                          int(variant_id), float(dropout_p), int(seed), kmax, out_drop)
         _ext.count_launches(1)
         if sp.token_rows is not None and len(sp.token_rows) > 1:
             out[sp.token_rows[1:]] = out[sp.token_rows[0]].clone()  # copy_global_token0 (gt_sp/utils.py:2365-2386)
         ctx.sp, ctx.graph, ctx.layer = sp, graph, layer
         ctx.cfg = (int(variant_id), float(dropout_p), int(seed), etable is not None, kmax)
+        ctx.out_drop = out_drop
         ctx.save_for_backward(qkv, z, etable if etable is not None else qkv.new_empty(0))
         return out.detach()
 
@@ -179,11 +188,11 @@ class _PackedEdgeAttention(torch.autograd.Function):
         detab = torch.zeros(etable.shape, dtype=torch.float32, device=qkv.device) if has_tab else None
         ext.edge_attn_bwd(q, k, v, out.view(r, hlh, hn), z, dout.view(r, hlh, hn), dq, dk, dv, zd, graph.rowptr, graph.col,
                           graph.etype, graph.t_rowptr, graph.t_row, graph.t_eid, etable if has_tab else None, detab,
-                          variant_id, dropout_p, seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots))
+                          variant_id, dropout_p, seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots), ctx.out_drop)
         _ext.count_launches(3)
         if debug.enabled() and dout.data_ptr() == sp.dctx.tensor.data_ptr():
             debug.poison(sp.dctx.tensor)              # d(context) consumed; the next push must overwrite all of it
-        return dbuf, (detab.to(etable.dtype) if has_tab else None), None, None, None, None, None, None
+        return dbuf, (detab.to(etable.dtype) if has_tab else None), None, None, None, None, None, None, None, None
 
 
 class _CtxPullOutProj(torch.autograd.Function):
@@ -193,7 +202,8 @@ class _CtxPullOutProj(torch.autograd.Function):
     all head owners.  Without a projection (Exphormer) ``y = residual + drop_post(a)``."""
 
     @staticmethod
-    def forward(ctx, ctx_full, wo, bo, residual, sp: SPContext, p_pre, p_post, seed_pre, seed_post, slot=None):
+    def forward(ctx, ctx_full, wo, bo, residual, sp: SPContext, p_pre, p_post, seed_pre, seed_post, slot=None,
+                pre_applied: bool = False):
         dt = ctx_full.dtype
         if sp.P > 1:
             sp.sw.barrier(0)                                         # every head owner has written its context
@@ -203,7 +213,7 @@ class _CtxPullOutProj(torch.autograd.Function):
             _ext.count_launches(1)
         else:
             a = ctx_full
-        if p_pre > 0:
+        if p_pre > 0 and not pre_applied:           # pre_applied: the attention kernel already stored the dropped context
             a = hash_dropout(a, seed_pre, p_pre)
         if wo is not None:
             w = wo.to(dt)
@@ -241,7 +251,7 @@ class _CtxPullOutProj(torch.autograd.Function):
             _ext.load().peer_scatter_cols(dbuf.ptrs, sp.row0, sp.rows_local, sp.hl * esz, sp.hl * esz, da.contiguous())
             _ext.count_launches(1)
         sp.sw.barrier(0)                                             # all d(context) rows have landed
-        return dbuf.tensor, dw, db, (dy if has_res else None), None, None, None, None, None, None
+        return dbuf.tensor, dw, db, (dy if has_res else None), None, None, None, None, None, None, None
 
 
 def _ctx_ptrs_for(self, t):
@@ -262,7 +272,8 @@ def _core(layer):
     return getattr(d, "local_attn", d)
 
 
-def _attention(layer, x2d, graph: AttnGraph, sp: SPContext, idx: int, passthrough: bool = False):
+def _attention(layer, x2d, graph: AttnGraph, sp: SPContext, idx: int, passthrough: bool = False,
+               out_p: float = 0.0, out_seed: int = 0):
     """Context of the layer's attention; with ``passthrough`` also the input routed through the projection function
     (use it as the residual so that its gradient is added inside the input-gradient GEMM)."""
     mha = layer.self_attention
@@ -278,7 +289,8 @@ def _attention(layer, x2d, graph: AttnGraph, sp: SPContext, idx: int, passthroug
         variant, etab = "plain", None
     p_att = core.attention_dropout_rate if (variant == "gps" and layer.training) else 0.0
     tab = etab.to(torch.float32).contiguous() if etab is not None else None
-    out = _PackedEdgeAttention.apply(qkv, tab, graph, sp, idx, _VARIANTS[variant], p_att, new_seed() if p_att > 0 else 0)
+    out = _PackedEdgeAttention.apply(qkv, tab, graph, sp, idx, _VARIANTS[variant], p_att, new_seed() if p_att > 0 else 0,
+                                     float(out_p), int(out_seed))
     return (out, xr) if passthrough else out
 
 
@@ -287,10 +299,13 @@ def _p(module, training) -> float:
 
 
 def _gt_attn(layer, x, graph, sp, idx):
-    ctx, xr = _attention(layer, x, graph, sp, idx, passthrough=True)
     p = _p(layer.self_attention_dropout, layer.training)
+    seed = new_seed() if p > 0 else 0
+    # the dropout before the output projection is applied by the attention kernel when it stores the context
+    fuse = p > 0 and sp.token_rows is None and FUSE_CONTEXT_DROPOUT
+    ctx, xr = _attention(layer, x, graph, sp, idx, passthrough=True, out_p=p if fuse else 0.0, out_seed=seed)
     slot = ColsumSlot()                                   # LayerNorm backward -> bias gradient of the projection
-    s = _CtxPullOutProj.apply(ctx, layer.O.weight, layer.O.bias, xr, sp, p, 0.0, new_seed() if p > 0 else 0, 0, slot)
+    s = _CtxPullOutProj.apply(ctx, layer.O.weight, layer.O.bias, xr, sp, p, 0.0, seed, 0, slot, fuse)
     return layer_norm(s, layer.layer_norm1.weight, layer.layer_norm1.bias, layer.layer_norm1.eps, slot)
 
 

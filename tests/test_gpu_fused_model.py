@@ -94,3 +94,37 @@ def test_flat_adamw_matches_torch_adamw_with_clipping():
         opt_b.step()
     for pa, pb in zip(net_a.parameters(), net_b.parameters()):
         assert torch.allclose(pa, pb, atol=2e-6, rtol=2e-5), float((pa - pb).abs().max())
+
+
+def test_context_dropout_fused_into_attention_matches_separate_pass():
+    """GT applies dropout to the attention context before the output projection.  Fused into the attention kernel's
+    store (and undone in the <dout, out> term of its backward) it must reproduce the separate hash-dropout pass:
+    same counter-based mask, same loss, same gradients."""
+    from budgetformer_b200.ops import fused_sp, norm
+    results = {}
+    for fuse in (True, False):
+        torch.manual_seed(21)
+        t = _trainer("gt", fused=True, extra=["--dropout_rate", "0.3"])
+        graph = t.build_edges(1)
+        seeds = iter(range(1000, 2000))
+        old_flag, old_seed = fused_sp.FUSE_CONTEXT_DROPOUT, fused_sp.new_seed
+        fused_sp.FUSE_CONTEXT_DROPOUT = fuse
+        fused_sp.new_seed = lambda: next(seeds)          # identical seed sequence in both runs
+        try:
+            t.model.train()
+            loss, out = t._loss(graph, t.local_idx["train"])
+            t.reducer.prepare_backward()
+            loss.backward()
+        finally:
+            fused_sp.FUSE_CONTEXT_DROPOUT, fused_sp.new_seed = old_flag, old_seed
+            t.edge_engine.shutdown()
+        results[fuse] = (float(loss.detach()), out.float().clone(),
+                         {n: p.grad.float().clone() for n, p in t.model.named_parameters() if p.grad is not None})
+    gemm.check_status("cuda")
+    (la, oa, ga), (lb, ob, gb) = results[True], results[False]
+    assert abs(la - lb) < 5e-3, (la, lb)
+    assert (oa - ob).abs().max() < 5e-2
+    gmax = max(float(g.abs().max()) for g in gb.values())
+    for n in gb:
+        err = float((ga[n] - gb[n]).abs().max())
+        assert err <= 0.08 * max(float(gb[n].abs().max()), 1e-6) or err <= 4e-3 * gmax, (n, err)

@@ -190,8 +190,9 @@ def test_fused_nll_loss(dtype, classes):
     ref_in = logits.detach().float().requires_grad_(True)
     ref = torch.nn.functional.nll_loss(torch.log_softmax(ref_in[idx], 1), y[idx])
     ref.backward()
-    assert abs(float(loss) - float(ref)) < (2e-2 if dtype == torch.bfloat16 else 1e-5)
-    tol = 2e-2 if dtype == torch.bfloat16 else 1e-6
+    # fp32: fast exp/log intrinsics and an atomic (order-dependent) sum over the rows
+    assert abs(float(loss) - float(ref)) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-5
     assert torch.allclose(logits.grad.float(), ref_in.grad, atol=tol * float(ref_in.grad.abs().max()) + 1e-9)
 
 

@@ -24,7 +24,9 @@ class AttnParams(ctypes.Structure):
                 ("n", ctypes.c_int), ("hl", ctypes.c_int), ("hn", ctypes.c_int), ("dtype", ctypes.c_int),
                 ("variant", ctypes.c_int), ("dropout_p", ctypes.c_float), ("dropout_seed", ctypes.c_uint32),
                 ("hub_rows", ctypes.c_void_p), ("n_hub", ctypes.c_int), ("max_hub_degree", ctypes.c_int),
-                ("hub_scratch", ctypes.c_void_p)]
+                ("hub_scratch", ctypes.c_void_p),
+                ("out_dropout_p", ctypes.c_float), ("out_dropout_seed", ctypes.c_uint32),
+                ("out_rows_local", ctypes.c_int), ("out_col0", ctypes.c_int)]
 
 
 def _lib():
