@@ -162,6 +162,9 @@ int bf_grad_sumsq(const float* g, long long n, float* out /* += sum g^2 */, cuda
 int bf_adamw_flat(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1, float beta2,
                   float eps, float weight_decay, int step, const float* sumsq /* or NULL */, float max_norm,
                   cudaStream_t st);
+// Graph-capturable form: hyper = device float[3] {lr, 1 - beta1^t, sqrt(1 - beta2^t)} refreshed by the host each step.
+int bf_adamw_flat_dev(float* p, const float* g, float* m, float* v, long long n, float beta1, float beta2, float eps,
+                      float weight_decay, const float* hyper, const float* sumsq, float max_norm, cudaStream_t st);
 
 // ---- readout loss (loss.cu) ---------------------------------------------------------------------------
 // loss_sum += sum over rows with mask != 0 of -log softmax(logits[row])[y[row]]; when dlogits != NULL it receives

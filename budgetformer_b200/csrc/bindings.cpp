@@ -417,6 +417,18 @@ void adamw_flat(Tensor p, Tensor g, Tensor m, Tensor v, int64_t n, double lr, do
                            at::cuda::getCurrentCUDAStream()), "adamw_flat");
 }
 
+void adamw_flat_dev(Tensor p, Tensor g, Tensor m, Tensor v, int64_t n, double beta1, double beta2, double eps, double wd,
+                    Tensor hyper, OptTensor sumsq, double max_norm) {
+  for (const Tensor* t : {&p, &g, &m, &v, &hyper})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat && t->is_contiguous());
+  TORCH_CHECK(p.numel() >= n && g.numel() >= n && m.numel() >= n && v.numel() >= n && hyper.numel() >= 3);
+  c10::cuda::CUDAGuard guard(p.device());
+  check_cuda(bf_adamw_flat_dev(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), n,
+                               (float)beta1, (float)beta2, (float)eps, (float)wd, hyper.data_ptr<float>(),
+                               sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr, (float)max_norm,
+                               at::cuda::getCurrentCUDAStream()), "adamw_flat_dev");
+}
+
 // Returns (loss_sum [1] fp32, dlogits or empty).
 std::vector<Tensor> nll_fwd_bwd(Tensor logits, Tensor y, Tensor mask, bool want_grad, double grad_scale) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
@@ -452,6 +464,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("nll_fwd_bwd", &nll_fwd_bwd);
   m.def("grad_sumsq", &grad_sumsq);
   m.def("adamw_flat", &adamw_flat);
+  m.def("adamw_flat_dev", &adamw_flat_dev);
   m.def("peer_barrier", &peer_barrier);
   m.def("allreduce_mean", &allreduce_mean);
   m.def("peer_gather_cols", &peer_gather_cols);

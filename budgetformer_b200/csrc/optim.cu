@@ -53,6 +53,29 @@ __global__ void __launch_bounds__(512) adamw_flat_kernel(float* __restrict__ p, 
   }
 }
 
+// Same update with the step-dependent scalars (lr, 1 - beta1^t, sqrt(1 - beta2^t)) read from device memory, so that the
+// launch can sit in a CUDA graph that is replayed every step.
+__global__ void __launch_bounds__(512) adamw_flat_dev_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                             float* __restrict__ m, float* __restrict__ v, long long n,
+                                                             float beta1, float beta2, float eps, float wd,
+                                                             const float* __restrict__ hyper,
+                                                             const float* __restrict__ sumsq, float max_norm) {
+  const float lr = hyper[0], bc1 = hyper[1], bc2_sqrt = hyper[2];
+  float clip = 1.f;
+  if (sumsq != nullptr && max_norm > 0.f) clip = fminf(1.f, max_norm / (sqrtf(*sumsq) + 1e-6f));
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float gi = g[i] * clip;
+    float pi = p[i] * (1.f - lr * wd);
+    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
+    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    pi -= (lr / bc1) * mi / (sqrtf(vi) / bc2_sqrt + eps);
+    p[i] = pi;
+  }
+}
+
 int grid_for(long long n) {
   long long b = (n + 511) / 512;
   if (b < 1) b = 1;
@@ -76,5 +99,14 @@ extern "C" int bf_adamw_flat(float* p, const float* g, float* m, float* v, long 
   const float bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
   adamw_flat_kernel<<<grid_for(n), 512, 0, st>>>(p, g, m, v, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, sumsq,
                                                  max_norm);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int bf_adamw_flat_dev(float* p, const float* g, float* m, float* v, long long n, float beta1, float beta2,
+                                 float eps, float weight_decay, const float* hyper, const float* sumsq, float max_norm,
+                                 cudaStream_t st) {
+  if (n <= 0) return 0;
+  adamw_flat_dev_kernel<<<grid_for(n), 512, 0, st>>>(p, g, m, v, n, beta1, beta2, eps, weight_decay, hyper, sumsq,
+                                                     max_norm);
   return (int)cudaGetLastError();
 }

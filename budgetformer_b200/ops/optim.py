@@ -15,7 +15,8 @@ from . import _ext
 
 
 class FlatAdamW(torch.optim.Optimizer):
-    def __init__(self, buckets, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, max_grad_norm: float = 1.0):
+    def __init__(self, buckets, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, max_grad_norm: float = 1.0,
+                 cuda_graph: bool = False):
         params = [p for b in buckets for p in b.params]
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         self.buckets = buckets
@@ -34,6 +35,13 @@ class FlatAdamW(torch.optim.Optimizer):
             self._m.append(torch.zeros_like(flat))
             self._v.append(torch.zeros_like(flat))
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=buckets[0].flat.device)
+        # --cuda_graph: the whole step (zero, sum of squares, AdamW per bucket) is captured once and replayed; the
+        # step-dependent scalars travel through a 3-float device buffer refreshed from pinned memory before each replay
+        self._use_graph = bool(cuda_graph) and buckets[0].flat.is_cuda
+        self._graph = None
+        if self._use_graph:
+            self._hyper = torch.zeros(4, dtype=torch.float32, device=buckets[0].flat.device)
+            self._hyper_host = torch.zeros(8, 4, dtype=torch.float32).pin_memory()   # ring: a slot is rewritten 8 steps later
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -42,6 +50,17 @@ class FlatAdamW(torch.optim.Optimizer):
         g0 = self.param_groups[0]
         lr, (b1, b2), eps, wd = g0["lr"], g0["betas"], g0["eps"], g0["weight_decay"]
         clip = self.max_grad_norm > 0
+        if self._use_graph:
+            slot = self._hyper_host[self._step % self._hyper_host.size(0)]
+            slot[0] = float(lr)
+            slot[1] = 1.0 - float(b1) ** self._step
+            slot[2] = (1.0 - float(b2) ** self._step) ** 0.5
+            self._hyper.copy_(slot, non_blocking=True)
+            if self._graph is None:
+                self._capture(ext, b1, b2, eps, wd, clip)
+            self._graph.replay()
+            _ext.count_launches(len(self.buckets) * (2 if clip else 1))
+            return
         if clip:
             self._sumsq.zero_()
             for b in self.buckets:
@@ -50,6 +69,28 @@ class FlatAdamW(torch.optim.Optimizer):
             ext.adamw_flat(p, b.flat, m, v, int(b.n_valid), float(lr), float(b1), float(b2), float(eps), float(wd),
                            int(self._step), self._sumsq if clip else None, self.max_grad_norm)
         _ext.count_launches(len(self.buckets) * (2 if clip else 1))
+
+    def _launch_dev(self, ext, b1, b2, eps, wd, clip) -> None:
+        if clip:
+            self._sumsq.zero_()
+            for b in self.buckets:
+                ext.grad_sumsq(b.flat, self._sumsq)
+        for b, p, m, v in zip(self.buckets, self._flat_p, self._m, self._v):
+            ext.adamw_flat_dev(p, b.flat, m, v, int(b.n_valid), float(b1), float(b2), float(eps), float(wd), self._hyper,
+                               self._sumsq if clip else None, self.max_grad_norm)
+
+    def _capture(self, ext, b1, b2, eps, wd, clip) -> None:
+        """Record the step's launches into a CUDA graph (betas, eps, weight decay and the clip threshold are baked in;
+        lr and the bias corrections come from ``self._hyper``).  Capture does not execute, so nothing is applied twice."""
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(self._hyper.device)
+        side.wait_stream(torch.cuda.current_stream(self._hyper.device))
+        with torch.cuda.stream(side):
+            # thread-local capture mode: the look-ahead graph builder may allocate on its own thread meanwhile
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                self._launch_dev(ext, b1, b2, eps, wd, clip)
+        torch.cuda.current_stream(self._hyper.device).wait_stream(side)
+        self._graph = graph
 
     def grad_norm(self) -> torch.Tensor:
         """Device tensor holding the global gradient norm of the last step."""

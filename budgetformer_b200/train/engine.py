@@ -159,7 +159,8 @@ class FullGraphTrainer:
         if self.device.type == "cuda" and not self.scaler.is_enabled() and all(
                 b.flat.dtype == torch.float32 for b in self.reducer.buckets):
             from ..ops.optim import FlatAdamW
-            self.optimizer = FlatAdamW(self.reducer.buckets, lr=args.peak_lr, weight_decay=args.weight_decay, max_grad_norm=1.0)
+            self.optimizer = FlatAdamW(self.reducer.buckets, lr=args.peak_lr, weight_decay=args.weight_decay, max_grad_norm=1.0,
+                                       cuda_graph=bool(getattr(args, "cuda_graph", False)))
             self.flat_optimizer = True
         else:
             self.optimizer = torch.optim.AdamW(self.model.parameters(), lr=args.peak_lr, weight_decay=args.weight_decay)

@@ -74,17 +74,22 @@ def test_fused_path_with_activation_tiers():
         assert torch.allclose(pa.grad, pb.grad, atol=1e-3 + 0.02 * float(pa.grad.abs().max()))
 
 
-def test_flat_adamw_matches_torch_adamw_with_clipping():
+@pytest.mark.parametrize("graph", [False, True])
+def test_flat_adamw_matches_torch_adamw_with_clipping(graph):
+    """Eager launches and the CUDA-graph replay of the step (--cuda_graph) against torch.optim.AdamW + clip_grad_norm_,
+    with a learning rate that changes every step."""
     from budgetformer_b200.ops.optim import FlatAdamW
     from budgetformer_b200.parallel.reducer import GradientReducer
     torch.manual_seed(0)
     net_a = torch.nn.Sequential(torch.nn.Linear(37, 64), torch.nn.LayerNorm(64), torch.nn.Linear(64, 5)).cuda()
     net_b = copy.deepcopy(net_a)
     red = GradientReducer(net_a, None, world_size=1)
-    opt_a = FlatAdamW(red.buckets, lr=3e-3, weight_decay=0.05, max_grad_norm=0.5)
+    opt_a = FlatAdamW(red.buckets, lr=3e-3, weight_decay=0.05, max_grad_norm=0.5, cuda_graph=graph)
     opt_b = torch.optim.AdamW(net_b.parameters(), lr=3e-3, weight_decay=0.05)
     x = torch.randn(256, 37, device="cuda")
-    for _ in range(5):
+    for it in range(5):
+        for opt in (opt_a, opt_b):
+            opt.param_groups[0]["lr"] = 3e-3 * (1.0 - 0.1 * it)
         red.prepare_backward()
         (net_a(x) ** 2).sum().backward()
         opt_a.step()
