@@ -20,7 +20,7 @@ from budgetformer_b200.parallel.reducer import build_gradient_reducer, sync_para
 from budgetformer_b200.train.data import load_data
 from budgetformer_b200.train.engine import build_model
 from budgetformer_b200.train.legacy_batch import get_batch_blockize
-from budgetformer_b200.train.legacy_eval import sparse_eval_gpu
+from budgetformer_b200.train.legacy_eval import collect_hop_stats, sparse_eval_gpu
 from budgetformer_b200.utils.lr import PolynomialDecayLR
 from budgetformer_b200.utils.misc import autocast_context, resolve_amp_dtype, set_seed
 
@@ -66,7 +66,7 @@ def main(argv=None):
             loss.backward()
             reducer.finalize_backward()
             opt.step()
-            losses.append(float(loss))
+            losses.append(float(loss.detach()))
         sched.step()
         times.append(time.time() - t0)
         if rank == 0:
@@ -74,6 +74,11 @@ def main(argv=None):
         if epoch % max(1, int(args.eval_every)) == 0 or epoch == args.epochs:
             val = sparse_eval_gpu(args, model, data.x, data.y, data.split_idx["valid"], data.edge_index, n, device, topo)
             test = sparse_eval_gpu(args, model, data.x, data.y, data.split_idx["test"], data.edge_index, n, device, topo)
+            if getattr(args, "full_attn_hop_stats", False):
+                path = collect_hop_stats(args, model, data.x, data.y, data.split_idx["valid"], data.edge_index, n, device,
+                                         epoch, topo)
+                if rank == 0 and path:
+                    print(f"[hop_stats] wrote {path}", flush=True)
             if rank == 0:
                 print(f"  eval epoch {epoch:04d} | valid={val:.4f} test={test:.4f}", flush=True)
                 if val > best["valid"]:

@@ -163,3 +163,26 @@ def test_debug_checks_validate_graphs_and_flag_nan():
             debug.assert_finite("the gradients of epoch 3", torch.ones(2), t)
     finally:
         debug.enable(False)
+
+
+def test_mini_batch_driver_trains_and_writes_hop_stats(tmp_path):
+    """Legacy mini-batch SP driver end to end on CPU: two epochs over sequences of 256 nodes, validation, and the
+    per-epoch hop-mass statistics file (--full_attn_hop_stats)."""
+    import json
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import main_node_sp
+    from budgetformer_b200.graph.synthetic import sbm_graph, write_dataset
+    x, y, ei = sbm_graph(600, feat_dim=16, seed=1)
+    write_dataset(str(tmp_path), "toy", x, y, ei)
+    hop_dir = str(tmp_path / "hop")
+    best = main_node_sp.main(["--model", "gt", "--dataset", "toy", "--dataset_dir", str(tmp_path), "--seq_len", "256",
+                              "--epochs", "2", "--n_layers", "2", "--hidden_dim", "32", "--num_heads", "4", "--ffn_dim", "64",
+                              "--device", "cpu", "--eval_every", "1", "--force_random_split", "--full_attn_hop_stats",
+                              "--full_attn_hop_stats_dir", hop_dir, "--full_attn_hop_max_hop", "6"])
+    assert 0.0 <= best["valid"] <= 1.0 and best["epoch"] >= 1
+    files = sorted(os.listdir(os.path.join(hop_dir, "toy", "gt", "attn0.95_maxhop6")))
+    assert files == ["epoch_1.json", "epoch_2.json"]
+    stats = json.load(open(os.path.join(hop_dir, "toy", "gt", "attn0.95_maxhop6", files[0])))
+    assert len(stats["layers"]) == 2 and abs(sum(stats["layers"][0]["hop_mass"]) - 1.0) < 1e-4
