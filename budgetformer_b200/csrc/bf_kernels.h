@@ -125,6 +125,13 @@ int bf_peer_gather_cols(void* const* src, int world, long long row0, long long r
 int bf_peer_scatter_cols(void* const* dst, int world, long long row0, long long rows, int cols_bytes,
                          long long dst_ld_bytes, const void* src, long long src_ld_bytes, cudaStream_t st);
 
+// Fan-out k-hop candidate expansion on the CPU (cpu/edge_builder.cpp): two passes, count then fill.
+int bf_khop_count_cpu(const int* out_rowptr, const int* out_col, int n, const int* fanout, int n_hops, long long seed,
+                      long long* counts /* [n] */, int num_threads);
+int bf_khop_fill_cpu(const int* out_rowptr, const int* out_col, int n, const int* fanout, int n_hops, long long seed,
+                     const long long* offsets /* [n] exclusive prefix sums */, long long* src, long long* dst,
+                     int num_threads);
+
 // ---- by-key view of the attention graph + dK/dV work list (graph_transpose.cu) --------------------------
 size_t bf_graph_transpose_scratch(int n, long long n_edges);
 int bf_graph_transpose(const int* rowptr, const int* col, int n, long long n_edges, int* t_rowptr /* [n+1] */,

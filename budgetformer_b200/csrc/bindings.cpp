@@ -193,6 +193,26 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
   return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
 }
 
+// (src, dst) int64 candidates of the fan-out k-hop expansion over a CPU out-edge CSR.
+std::vector<Tensor> khop_candidates_cpu(Tensor out_rowptr, Tensor out_col, int64_t n, std::vector<int64_t> fanout,
+                                        int64_t seed, int64_t num_threads) {
+  TORCH_CHECK(!out_rowptr.is_cuda() && !out_col.is_cuda() && out_rowptr.scalar_type() == torch::kInt &&
+              out_col.scalar_type() == torch::kInt && out_rowptr.is_contiguous() && out_col.is_contiguous());
+  std::vector<int> fo(fanout.begin(), fanout.end());
+  Tensor counts = torch::zeros({n}, torch::kLong);
+  bf_khop_count_cpu(iptr(out_rowptr), iptr(out_col), (int)n, fo.data(), (int)fo.size(), seed,
+                    reinterpret_cast<long long*>(counts.data_ptr<int64_t>()), (int)num_threads);
+  Tensor incl = torch::cumsum(counts, 0);
+  const int64_t total = n > 0 ? incl[n - 1].item<int64_t>() : 0;
+  Tensor offsets = incl - counts;
+  Tensor src = torch::empty({total}, torch::kLong), dst = torch::empty({total}, torch::kLong);
+  bf_khop_fill_cpu(iptr(out_rowptr), iptr(out_col), (int)n, fo.data(), (int)fo.size(), seed,
+                   reinterpret_cast<const long long*>(offsets.data_ptr<int64_t>()),
+                   reinterpret_cast<long long*>(src.data_ptr<int64_t>()),
+                   reinterpret_cast<long long*>(dst.data_ptr<int64_t>()), (int)num_threads);
+  return {src, dst};
+}
+
 // By-key view + balanced dK/dV work list of a device-resident attention graph.
 // Returns (t_rowptr [n+1], t_row [E], t_eid [E], tasks [T, 4], splits [S, 3], sizes int64 [3] = T, slots, S on the host).
 std::vector<Tensor> graph_transpose(Tensor rowptr, Tensor col, int64_t n, int64_t chunk) {
@@ -451,6 +471,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("edge_attn_fwd", &edge_attn_fwd);
   m.def("edge_attn_bwd", &edge_attn_bwd);
   m.def("build_attn_graph", &build_attn_graph);
+  m.def("khop_candidates_cpu", &khop_candidates_cpu);
   m.def("graph_transpose", &graph_transpose);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_supported", &gemm_supported);

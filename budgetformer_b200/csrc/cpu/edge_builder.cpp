@@ -100,3 +100,90 @@ extern "C" int bf_ell_to_csr_cpu(const int* ell_col, const uint8_t* ell_type, co
   }
   return 0;
 }
+
+// -----------------------------------------------------------------------------------------------------
+// Fan-out k-hop expansion with origin tracking (`--rw_edge_mode dgl_neighbor`; the reference delegates it
+// to DGL's neighbour sampler, gt_sp/utils.py:1281-1384).  From every origin node, hop h keeps at most
+// fanout[h] out-neighbours of each frontier node (negative = all), ranked by a seeded hash so that the
+// choice is reproducible on every rank, and emits (reached node -> origin).  The next frontier is the set
+// of distinct reached nodes.  Origins are independent, so the expansion runs one origin per OpenMP task
+// in two passes (count, then fill at prefix-sum offsets); rows come out origin-major, hop-minor, node ids
+// ascending inside a hop.  Same candidate multiset as graph/builder_spec.py::khop_neighbor_candidates.
+// -----------------------------------------------------------------------------------------------------
+namespace {
+
+struct KhopScratch {
+  std::vector<int> frontier, next;
+  std::vector<std::pair<uint64_t, int>> ranked;   // (key, position in the CSR row) of one frontier node's neighbours
+};
+
+// Runs the expansion of one origin; `emit` receives every reached node of every hop.
+template <typename Emit>
+inline void khop_expand(const int* rowptr, const int* col, int origin, const int* fanout, int n_hops, long long seed,
+                        KhopScratch& s, Emit emit) {
+  s.frontier.assign(1, origin);
+  const uint64_t omix = ((uint64_t)origin * 2654435761ull) & 0x7FFFFFFFull;
+  for (int h = 0; h < n_hops && !s.frontier.empty(); ++h) {
+    s.next.clear();
+    const int f = fanout[h];
+    const long long hseed = seed + 101ll * (h + 1);
+    for (int node : s.frontier) {
+      const int beg = rowptr[node], deg = rowptr[node + 1] - beg;
+      if (f < 0 || deg <= f) {
+        s.next.insert(s.next.end(), col + beg, col + beg + deg);
+        continue;
+      }
+      s.ranked.clear();
+      for (int i = 0; i < deg; ++i) {
+        const uint64_t hash31 = bf_edge_composite((uint32_t)col[beg + i], (uint32_t)node, hseed) >> 32;
+        s.ranked.emplace_back(hash31 ^ omix, i);           // ties keep CSR order (pair comparison)
+      }
+      std::partial_sort(s.ranked.begin(), s.ranked.begin() + f, s.ranked.end());
+      for (int i = 0; i < f; ++i) s.next.push_back(col[beg + s.ranked[i].second]);
+    }
+    std::sort(s.next.begin(), s.next.end());
+    s.next.erase(std::unique(s.next.begin(), s.next.end()), s.next.end());
+    for (int v : s.next) emit(v);
+    s.frontier.swap(s.next);
+  }
+}
+
+}  // namespace
+
+// Pass 1: counts[origin] = number of candidates of that origin.
+extern "C" int bf_khop_count_cpu(const int* out_rowptr, const int* out_col, int n, const int* fanout, int n_hops,
+                                 long long seed, long long* counts, int num_threads) {
+#ifdef _OPENMP
+  if (num_threads > 0) omp_set_num_threads(num_threads);
+#endif
+#pragma omp parallel
+  {
+    KhopScratch s;
+#pragma omp for schedule(dynamic, 256)
+    for (int o = 0; o < n; ++o) {
+      long long c = 0;
+      khop_expand(out_rowptr, out_col, o, fanout, n_hops, seed, s, [&](int) { ++c; });
+      counts[o] = c;
+    }
+  }
+  return 0;
+}
+
+// Pass 2: offsets = exclusive prefix sums of the counts; src[offsets[o] + i] = i-th reached node, dst = origin.
+extern "C" int bf_khop_fill_cpu(const int* out_rowptr, const int* out_col, int n, const int* fanout, int n_hops,
+                                long long seed, const long long* offsets, long long* src, long long* dst,
+                                int num_threads) {
+#ifdef _OPENMP
+  if (num_threads > 0) omp_set_num_threads(num_threads);
+#endif
+#pragma omp parallel
+  {
+    KhopScratch s;
+#pragma omp for schedule(dynamic, 256)
+    for (int o = 0; o < n; ++o) {
+      long long w = offsets[o];
+      khop_expand(out_rowptr, out_col, o, fanout, n_hops, seed, s, [&](int v) { src[w] = v; dst[w] = o; ++w; });
+    }
+  }
+  return 0;
+}

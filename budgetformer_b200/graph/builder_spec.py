@@ -130,6 +130,22 @@ def khop_neighbor_candidates(topo: Topology, fanout, seed: int):
     return np.concatenate(srcs), np.concatenate(dsts)
 
 
+def khop_neighbor_candidates_native(topo: Topology, fanout, seed: int, num_threads: int = 0):
+    """The same candidate multiset from the C++/OpenMP expansion (csrc/cpu/edge_builder.cpp), origin-major; ``None``
+    when the extension is not available or the topology does not live on the CPU."""
+    if topo.out_rowptr.is_cuda:
+        return None
+    try:
+        from ..ops import _ext
+        ext = _ext.load()
+    except Exception:
+        return None
+    src, dst = ext.khop_candidates_cpu(topo.out_rowptr.to(torch.int32).contiguous(), topo.out_col.to(torch.int32).contiguous(),
+                                       int(topo.num_nodes), [int(f) if f is not None else -1 for f in fanout], int(seed),
+                                       int(num_threads))
+    return src.numpy(), dst.numpy()
+
+
 def parse_fanout(text) -> list:
     return [int(t) for t in str(text).split(",") if t.strip()]
 
@@ -157,7 +173,8 @@ def build_attn_graph_spec(
         rs, rd = np.zeros(0, np.int64), np.zeros(0, np.int64)
     if use_rw and walks_per_node > 0 and walk_length > 0 and (b_rw is None or b_rw > 0):
         if fanout:
-            ws, wd = khop_neighbor_candidates(topo, fanout, seed)
+            native = khop_neighbor_candidates_native(topo, fanout, seed)
+            ws, wd = native if native is not None else khop_neighbor_candidates(topo, fanout, seed)
         else:
             ws, wd = rw_candidates(random_walks(topo, walks_per_node, walk_length, seed))
         ws, wd = select_per_query(ws, wd, b_rw, int(seed) + RW_SEED_OFFSET)

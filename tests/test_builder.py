@@ -109,3 +109,27 @@ def test_coo_roundtrip_and_transpose():
     for key in range(4):
         sl = slice(int(g.t_rowptr[key]), int(g.t_rowptr[key + 1]))
         assert all(int(g.col[e]) == key for e in g.t_eid[sl].tolist())
+
+
+@pytest.mark.parametrize("fanout", [[3, 2], [-1, 2], [2, 2, 2]])
+def test_native_fanout_expansion_equals_spec(fanout):
+    """C++/OpenMP k-hop fan-out expansion (--rw_edge_mode dgl_neighbor) against the numpy specification: the same
+    candidate multiset, and therefore the same attention graph."""
+    import numpy as np
+    from budgetformer_b200.graph import builder_spec as spec
+    topo, _ = random_topology(400, 3000, hub_out=60, seed=4)
+    ws, wd = spec.khop_neighbor_candidates(topo, fanout, 77)
+    native = spec.khop_neighbor_candidates_native(topo, fanout, 77, num_threads=3)
+    assert native is not None
+    ns, nd = native
+    a = np.sort(wd.astype(np.int64) * 400 + ws.astype(np.int64))
+    b = np.sort(nd.astype(np.int64) * 400 + ns.astype(np.int64))
+    assert a.size == b.size and bool((a == b).all())
+    g1 = spec.build_attn_graph_spec(topo, 3, 4, 2, 3, 77, fanout=fanout)
+    orig = spec.khop_neighbor_candidates_native
+    spec.khop_neighbor_candidates_native = lambda *a, **k: None          # force the numpy expansion
+    try:
+        g2 = spec.build_attn_graph_spec(topo, 3, 4, 2, 3, 77, fanout=fanout)
+    finally:
+        spec.khop_neighbor_candidates_native = orig
+    assert torch.equal(g1.rowptr, g2.rowptr) and torch.equal(g1.col, g2.col)
