@@ -24,8 +24,9 @@ def trainer(model, fused, extra=()):
     n = 4096
     x, y, ei = sbm_graph(n, feat_dim=64, seed=3)
     data = GraphData(x, y, ei, random_split_idx(n, 3), n, 7)
-    argv = ["--model", model, "--dataset", "t", "--n_layers", "2", "--hidden_dim", "128", "--num_heads", "8",
-            "--ffn_dim", "256", "--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4",
+    hidden = int(os.environ.get("BF_TEST_HIDDEN", "128"))           # 64: column slices per rank that are not multiples of 64
+    argv = ["--model", model, "--dataset", "t", "--n_layers", "2", "--hidden_dim", str(hidden), "--num_heads", str(hidden // 16),
+            "--ffn_dim", str(2 * hidden), "--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4",
             "--amp_dtype", "bf16", "--force_random_split", "--fused_sp", "on" if fused else "off",
             "--dropout_rate", "0.0", "--attention_dropout_rate", "0.0", "--input_dropout_rate", "0.0", "--seed", "5"]
     return FullGraphTrainer(parse_fullgraph_args(argv + list(extra)), data=data, log=lambda *a, **k: None)

@@ -32,6 +32,16 @@ def test_fused_path_two_gpus_plain_peer_loads():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_path_two_gpus_narrow_column_slices():
+    """hidden 64 on 2 ranks: a rank's slice of q|k|v is 96 columns and of d(context) 32, so the GEMM epilogue stages
+    destination-wide (unswizzled) panels and bulk-stores them into the peer's buffer - the path 4 and 8 ranks take at
+    hidden 128."""
+    r = _run(2, "gt,graphgps", 29615, {"BF_TEST_HIDDEN": "64"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("OK ") == 2, r.stdout[-2000:]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_fused_path_four_gpus():
     r = _run(4, "gt,graphormer", 29613)
