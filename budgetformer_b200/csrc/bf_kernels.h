@@ -102,6 +102,13 @@ typedef struct {
   long long ldr;
   const void* relu_mask;            // [M, ldm] 16-bit: result zeroed where mask <= 0, or NULL
   long long ldm;
+  // The same mask as one bit per element, 16 columns per uint16 word, stored column-block major ([N/16, ldmb >= M]
+  // words, so that the 32 rows of a warp touch adjacent words; N % 16 == 0): written by a
+  // forward GEMM (bit = result > 0 after activation and dropout), consumed by the backward GEMM instead of re-reading
+  // the 16-bit activation.
+  void* relu_bits_out;
+  const void* relu_bits_in;
+  long long ldmb;
   float out_scale;                  // multiplies the accumulator (0 means 1)
   int out_fp32;                     // 1: fp32 output
   int n_dest;                       // >1: columns [d*N/n_dest, (d+1)*N/n_dest) go to dst[d] (peer buffers)

@@ -252,7 +252,7 @@ std::vector<Tensor> graph_transpose(Tensor rowptr, Tensor col, int64_t n, int64_
 // C = A * W^T with fused epilogue.  `dst_ptrs` holds one device pointer per destination (1 = plain output).
 void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, int64_t seed, OptTensor residual,
              OptTensor relu_mask, double out_scale, bool out_fp32, std::vector<int64_t> dst_ptrs, int64_t dst_row_offset,
-             int64_t ldc, Tensor status) {
+             int64_t ldc, Tensor status, OptTensor relu_bits_out, OptTensor relu_bits_in) {
   TORCH_CHECK(A.is_cuda() && W.is_cuda() && A.dim() == 2 && W.dim() == 2, "gemm_tn: A [M,K], W [N,K] on CUDA");
   TORCH_CHECK(A.scalar_type() == W.scalar_type() && (A.scalar_type() == torch::kBFloat16 || A.scalar_type() == torch::kHalf),
               "gemm_tn: bf16/fp16 operands");
@@ -277,6 +277,15 @@ void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, 
                 "gemm_tn: residual rows must be 16-byte aligned");
     p.residual = residual->data_ptr(); p.ldr = residual->stride(0);
   }
+  for (const OptTensor* bt : {&relu_bits_out, &relu_bits_in}) {
+    if (!bt->has_value()) continue;
+    const Tensor& t = **bt;
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kShort && t.dim() == 2 && t.stride(1) == 1 && t.size(1) == p.M &&
+                t.size(0) * 16 == p.N, "gemm_tn: ReLU bit mask must be int16 [N / 16, M]");
+    p.ldmb = t.stride(0);
+  }
+  if (relu_bits_out.has_value()) p.relu_bits_out = relu_bits_out->data_ptr();
+  if (relu_bits_in.has_value()) p.relu_bits_in = relu_bits_in->data_ptr();
   if (relu_mask.has_value()) {
     TORCH_CHECK(relu_mask->scalar_type() == A.scalar_type() && relu_mask->stride(1) == 1 && relu_mask->size(0) == p.M &&
                 relu_mask->size(1) == p.N && (relu_mask->stride(0) * 2) % 16 == 0 && ((uintptr_t)relu_mask->data_ptr()) % 16 == 0);

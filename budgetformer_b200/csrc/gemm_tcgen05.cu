@@ -51,6 +51,9 @@ struct GemmArgs {
   long long ldr;
   const void* relu_mask;         // [M, ldm] 16-bit: out = mask > 0 ? acc : 0
   long long ldm;
+  unsigned short* bits_out;      // [N/16, ldmb >= M] one bit per element, word (c, r) = columns 16c..16c+15 of row r: bit = result > 0
+  const unsigned short* bits_in; // same layout: out = bit ? acc : 0
+  long long ldmb;
   float out_scale;
   int out_fp32;
   // output routing
@@ -409,6 +412,13 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         stage_operand(t, stage_out);
         cp_async_commit();
       }
+      // mask words of this thread's (row, 16-column chunks): fetched before the wait for the accumulator
+      unsigned bits_pre[4] = {0u, 0u, 0u, 0u};
+      if (g.bits_in != nullptr && row_ok) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it)
+          if (it * 16 < cpg) bits_pre[it] = __ldg(g.bits_in + (long long)((gcol_begin >> 4) + it) * g.ldmb + row);
+      }
       if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       if (staged) {
@@ -468,6 +478,17 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             v[i] = keep_elem(g.dropout_seed, (uint32_t)row, (uint32_t)(col0 + i), thresh) ? v[i] * keep_scale : 0.f;
+        }
+        if (g.bits_in != nullptr && row_ok) {
+          const unsigned bits = bits_pre[it];          // [N/16, M] layout: a warp's 32 rows read adjacent words
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = ((bits >> i) & 1u) ? v[i] : 0.f;
+        }
+        if (g.bits_out != nullptr && row_ok) {
+          unsigned bits = 0;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) bits |= (v[i] > 0.f ? 1u : 0u) << i;
+          g.bits_out[(long long)(col0 >> 4) * g.ldmb + row] = (unsigned short)bits;
         }
         if (has_mask && row_ok) {
           uint4 m0, m1;
@@ -634,6 +655,9 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   g.is_fp16 = p->dtype == BF_FP16 ? 1 : 0;
   g.bias = p->bias; g.act = p->act; g.dropout_p = p->dropout_p; g.dropout_seed = p->dropout_seed;
   g.residual = p->residual; g.ldr = p->ldr; g.relu_mask = p->relu_mask; g.ldm = p->ldm;
+  g.bits_out = static_cast<unsigned short*>(p->relu_bits_out); g.bits_in = static_cast<const unsigned short*>(p->relu_bits_in);
+  g.ldmb = p->ldmb;
+  if ((g.bits_out || g.bits_in) && p->N % 16 != 0) return (int)cudaErrorInvalidValue;
   g.out_scale = p->out_scale == 0.f ? 1.f : p->out_scale;
   g.out_fp32 = p->out_fp32;
   g.n_dest = p->n_dest; g.cols_per_dest = cols_per_dest; g.dst_row_offset = p->dst_row_offset; g.ldc = p->ldc;
@@ -696,6 +720,7 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
     else if ((f | EPI_DROP) == (EPI_BIAS | EPI_DROP | EPI_RES)) epi = EPI_BIAS | EPI_DROP | EPI_RES;
     else if ((f | EPI_DROP) == (EPI_BIAS | EPI_RELU | EPI_DROP)) epi = EPI_BIAS | EPI_RELU | EPI_DROP;
     else if ((f | EPI_SCALE) == (EPI_MASK | EPI_SCALE)) epi = EPI_MASK | EPI_SCALE;
+    else if (f == EPI_SCALE) epi = EPI_SCALE;
   }
   void (*kern)(const CUtensorMap, const CUtensorMap, const OutMaps, const GemmArgs) = gemm_tn_tcgen05_kernel<-1>;
   switch (epi) {
@@ -704,12 +729,13 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
     case EPI_BIAS | EPI_DROP | EPI_RES: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_DROP | EPI_RES>; break;
     case EPI_BIAS | EPI_RELU | EPI_DROP: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_RELU | EPI_DROP>; break;
     case EPI_MASK | EPI_SCALE: kern = gemm_tn_tcgen05_kernel<EPI_MASK | EPI_SCALE>; break;
+    case EPI_SCALE: kern = gemm_tn_tcgen05_kernel<EPI_SCALE>; break;
     default: break;
   }
   {
     static bool attr_set[8] = {false, false, false, false, false, false, false, false};
     const int slot = epi < 0 ? 0 : epi == 0 ? 1 : epi == EPI_BIAS ? 2 : epi == (EPI_BIAS | EPI_DROP | EPI_RES) ? 3
-                     : epi == (EPI_BIAS | EPI_RELU | EPI_DROP) ? 4 : 5;
+                     : epi == (EPI_BIAS | EPI_RELU | EPI_DROP) ? 4 : epi == EPI_SCALE ? 6 : 5;
     if (!attr_set[slot]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
       if (e != cudaSuccess) return (int)e;

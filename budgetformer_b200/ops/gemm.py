@@ -44,8 +44,10 @@ def supported(m: int, n: int, k: int, dtype) -> bool:
 def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
             dropout_p: float = 0.0, dropout_seed: int = 0, residual: Optional[torch.Tensor] = None,
             relu_mask: Optional[torch.Tensor] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
-            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``act(dropout(a @ w.T * out_scale + bias)) [masked] + residual`` in one kernel."""
+            out_dtype: Optional[torch.dtype] = None, relu_bits_out: Optional[torch.Tensor] = None,
+            relu_bits_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(dropout(a @ w.T * out_scale + bias)) [masked] + residual`` in one kernel.  ``relu_bits_out`` (int16
+    ``[N / 16, M]``) receives one bit per element (result > 0); ``relu_bits_in`` zeroes the result where its bit is clear."""
     ext = _ext.load()
     m, n = a.size(0), w.size(0)
     fp32_out = (out_dtype or (out.dtype if out is not None else a.dtype)) == torch.float32
@@ -59,7 +61,7 @@ def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
             bias = bias.clone()
     ext.gemm_tn(a, w, bias, ACT[act], float(dropout_p), int(dropout_seed),
                 residual, relu_mask, float(out_scale), bool(fp32_out), [out.data_ptr()], 0, out.stride(0),
-                status_tensor(a.device))
+                status_tensor(a.device), relu_bits_out, relu_bits_in)
     _ext.count_launches(1)
     return out
 

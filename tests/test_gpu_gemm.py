@@ -210,7 +210,7 @@ def test_gemm_routes_column_slices_to_destinations(n, n_dest, row0):
     total_rows = row0 + m + 64
     outs = [torch.full((total_rows, cpd), 7.0, device="cuda", dtype=torch.bfloat16) for _ in range(n_dest)]
     _ext.load().gemm_tn(x, w, bias, 0, 0.0, 0, None, None, 1.0, False, [o.data_ptr() for o in outs], row0, cpd,
-                        gemm.status_tensor("cuda"))
+                        gemm.status_tensor("cuda"), None, None)
     gemm.check_status("cuda")
     ref = x.float() @ w.float().t() + bias
     for d, o in enumerate(outs):
@@ -231,10 +231,30 @@ def test_gemm_routes_slices_with_dropout_epilogue():
     w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
     outs = [torch.zeros(m, cpd, device="cuda", dtype=torch.bfloat16) for _ in range(n_dest)]
     _ext.load().gemm_tn(x, w, None, 0, p, seed, None, None, 1.0, False, [o.data_ptr() for o in outs], 0, cpd,
-                        gemm.status_tensor("cuda"))
+                        gemm.status_tensor("cuda"), None, None)
     gemm.check_status("cuda")
     keep = gemm.hash_keep_mask(seed, m, n, p, "cuda")
     ref = torch.where(keep, (x.float() @ w.float().t()) / (1 - p), torch.zeros(1, device="cuda"))
     got = torch.cat([o.float() for o in outs], 1)
     assert (got - ref).abs().max() < 0.06
     assert abs(float((got == 0).float().mean()) - p) < 0.03
+
+
+def test_gemm_relu_bitmask_round_trip():
+    """Forward epilogue writes one bit per element (result > 0 after ReLU and dropout); the backward epilogue masks with
+    the bits: identical to masking with the stored activation."""
+    torch.manual_seed(3)
+    m, n, k = 1500, 256, 128
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(n, device="cuda") * 0.1
+    bits = torch.zeros(n // 16, m, dtype=torch.int16, device="cuda")
+    h = gemm.gemm_tn(x, w, bias, "relu", dropout_p=0.2, dropout_seed=99, relu_bits_out=bits)
+    unpacked = ((bits.t().to(torch.int32).unsqueeze(-1) >> torch.arange(16, device="cuda")) & 1).reshape(m, n).bool()
+    assert torch.equal(unpacked, h > 0)
+    g = torch.randn(m, 128, device="cuda").bfloat16()
+    w2 = (torch.randn(n, 128, device="cuda") * 0.1).bfloat16()
+    a = gemm.gemm_tn(g, w2, relu_bits_in=bits, out_scale=1.25)
+    b = gemm.gemm_tn(g, w2, relu_mask=h, out_scale=1.25)
+    gemm.check_status("cuda")
+    assert torch.equal(a, b)
