@@ -422,6 +422,12 @@ class FullGraphTrainer:
         (the end-to-end measurement path); otherwise the resident device copy is used.  With ``read_loss``
         the loss is read back to the host (one 4-byte device -> host copy)."""
         self.epoch = epoch
+        if self.device.type == "cuda":
+            # bound the host's run-ahead to two steps: deeper queues only grow the caching allocator (blocks shared with
+            # the look-ahead stream are recycled late) and make its growth calls land inside later steps
+            pending = self.__dict__.setdefault("_step_done", [])
+            if len(pending) >= 2:
+                pending.pop(0).synchronize()
         sync_timers = bool(getattr(self.args, "profile_sp_comm", False)) or (
             self.planner is not None and self.planner.needs_precise_timing())
         timers: Dict[str, float] = {"rw": 0.0, "fwd": 0.0, "bwd": 0.0, "opt": 0.0, "prefetch_wait": 0.0}
@@ -454,6 +460,10 @@ class FullGraphTrainer:
             comm.barrier(self.sp_group)
         if self.planner is not None or getattr(self.model, "_comm_ckpt", None) is not None:
             self.model.comm_aware_notify_step_end(self.device, t_bwd=timers["bwd"], t_fwd=timers["fwd"])
+        if self.device.type == "cuda":
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream(self.device))
+            self._step_done.append(done)
         timers["total"] = time.perf_counter() - t0
         out.update({f"t_{k}": v for k, v in timers.items()})
         out["edges"] = float(graph.num_edges)
