@@ -258,3 +258,17 @@ def test_gemm_relu_bitmask_round_trip():
     b = gemm.gemm_tn(g, w2, relu_mask=h, out_scale=1.25)
     gemm.check_status("cuda")
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("k", [72, 200, 272])
+def test_gemm_ragged_k_panel_is_zero_filled(k):
+    """K only has to keep rows 16-byte aligned: the last 64-element panel of both operands is zero-filled by TMA
+    (the feature encoder runs with K = 272)."""
+    torch.manual_seed(4)
+    m, n = 1111, 128
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") / k ** 0.5).bfloat16()
+    bias = torch.randn(n, device="cuda")
+    out = gemm.gemm_tn(a, w, bias)
+    gemm.check_status("cuda")
+    _close(out, _ref(a, w, bias), torch.bfloat16)
