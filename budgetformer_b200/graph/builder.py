@@ -10,8 +10,6 @@ from __future__ import annotations
 
 from typing import Optional
 
-import torch
-
 from .attn_graph import AttnGraph, Topology, add_virtual_node
 from .builder_spec import build_attn_graph_spec
 

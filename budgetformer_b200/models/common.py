@@ -12,12 +12,7 @@ from torch.utils.checkpoint import checkpoint
 
 from ..graph.attn_graph import AttnGraph, as_attn_graph
 from ..ops.edge_attention import edge_attention
-from ..parallel import comm
-from ..parallel.initialize import (
-    get_sequence_parallel_group,
-    get_sequence_parallel_rank,
-    get_sequence_parallel_world_size,
-)
+from ..parallel.initialize import get_sequence_parallel_world_size
 
 
 def init_params(module: nn.Module, n_layers: int) -> None:

@@ -23,7 +23,6 @@ import types
 from typing import List, Optional
 
 import torch
-import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ..graph.attn_graph import AttnGraph, as_attn_graph

@@ -8,8 +8,6 @@ The fused GPU paths (``parallel/symm.py``) bypass this module and move data with
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 import torch.distributed as dist
 

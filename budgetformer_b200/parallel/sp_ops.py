@@ -11,8 +11,6 @@ models replace "projection + all-to-all" by the fused kernels in ``ops/fused_sp.
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 import torch.distributed as dist
 from torch import nn

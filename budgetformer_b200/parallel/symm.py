@@ -12,7 +12,7 @@ model path is identical at every scale.
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist

@@ -10,8 +10,6 @@ import os
 import random
 import time
 from dataclasses import dataclass
-from typing import Optional
-
 import numpy as np
 import torch
 

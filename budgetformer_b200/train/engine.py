@@ -12,8 +12,6 @@ from __future__ import annotations
 
 import gc
 import json
-import math
-import os
 import time
 from typing import Dict, List, Optional
 
