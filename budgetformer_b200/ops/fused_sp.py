@@ -44,6 +44,9 @@ class SPContext:
     def __init__(self, group, device, world: int, rows_local: int, hidden: int, heads: int, n_layers: int, dtype,
                  token_rows: Optional[List[int]] = None):
         self.sw = symm.get_world(group, device)
+        # seed shared by all ranks for masks that one rank generates and another regenerates (set by the trainer every
+        # step from the run seed and the epoch; None = not set)
+        self.step_seed: Optional[int] = None
         self.P, self.rank = self.sw.world, self.sw.rank
         assert self.P == world
         self.rows_local, self.total_rows = int(rows_local), int(rows_local) * self.P
@@ -70,6 +73,16 @@ class SPContext:
     @property
     def row0(self) -> int:
         return self.rank * self.rows_local
+
+    def shared_seed(self, layer: int, tag: int) -> Optional[int]:
+        """31-bit seed every rank derives identically for (step, layer, purpose), or None when no step seed is set.
+        A mask written on one rank and regenerated on another must not depend on each rank's private RNG state."""
+        if self.step_seed is None:
+            return None
+        x = (int(self.step_seed) * 0x9E3779B1 + (int(layer) + 1) * 0x85EBCA77 + (int(tag) + 1) * 0xC2B2AE3D) & 0xFFFFFFFF
+        x = ((x ^ (x >> 16)) * 0x7FEB352D) & 0xFFFFFFFF
+        x = ((x ^ (x >> 15)) * 0x846CA68B) & 0xFFFFFFFF
+        return (x ^ (x >> 16)) & 0x7FFFFFFF
 
 
 def _push_gemm(x, w, bias, dst_ptrs, row0, ldc, dropout_p=0.0, seed=0):
@@ -299,9 +312,12 @@ def _p(module, training) -> float:
 
 def _gt_attn(layer, x, graph, sp, idx):
     p = _p(layer.self_attention_dropout, layer.training)
-    seed = new_seed() if p > 0 else 0
-    # the dropout before the output projection is applied by the attention kernel when it stores the context
-    fuse = p > 0 and sp.token_rows is None and FUSE_CONTEXT_DROPOUT
+    shared = sp.shared_seed(idx, 0) if p > 0 else None
+    seed = (shared if shared is not None else new_seed()) if p > 0 else 0
+    # The dropout before the output projection is applied by the attention kernel when it stores the context.  With
+    # several ranks the head owner writes the mask and the row owner regenerates it in backward, so the seed has to be
+    # the shared per-step one; without it the separate (rank-local) dropout pass is used.
+    fuse = p > 0 and sp.token_rows is None and FUSE_CONTEXT_DROPOUT and (sp.P == 1 or shared is not None)
     ctx, xr = _attention(layer, x, graph, sp, idx, passthrough=True, out_p=p if fuse else 0.0, out_seed=seed)
     slot = ColsumSlot()                                   # LayerNorm backward -> bias gradient of the projection
     s = _CtxPullOutProj.apply(ctx, layer.O.weight, layer.O.bias, xr, sp, p, 0.0, seed, 0, slot, fuse)

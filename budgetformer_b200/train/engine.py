@@ -318,6 +318,9 @@ class FullGraphTrainer:
         stage = {"bwd_started": False}
         if debug.enabled():
             debug.validate_graph(graph)
+        sp_ctx = getattr(self.model, "_fused_sp_context", None)
+        if sp_ctx is not None:
+            sp_ctx.step_seed = (int(self.args.seed) * 1000003 + int(epoch)) & 0x7FFFFFFF     # identical on every rank
         with StepTimer(self.device, sync_timers) as t_fwd, comm_profiler.nvtx_range("forward"):
             self.fault.check("fwd", epoch)
             ctx = torch.autograd.graph.save_on_cpu(pin_memory=True) if (
