@@ -84,6 +84,10 @@ class FullGraphTrainer:
         if bool(getattr(args, "debug_checks", False)):
             debug.enable(True)
         self.fault = FaultInjector(getattr(args, "fault_inject", "") or "", self.rank)
+        from ..utils.watchdog import build_watchdog
+        self.watchdog = build_watchdog(args, self.rank, self.sp_world)
+        if self.watchdog is not None:
+            self.fault.on_exit = lambda: self.watchdog.leave("injected exit")
 
         # ---- data -------------------------------------------------------------------------------
         if data is None:
@@ -706,6 +710,11 @@ class FullGraphTrainer:
             if self.device.type == "cuda":
                 torch.cuda.reset_peak_memory_stats(self.device)
             self.fault.check("step", epoch)
+            if self.watchdog is not None:
+                # between steps, nothing of this rank in flight: post the heartbeat and learn of a lost peer on the
+                # host before the next launch (raises PeerLost on every surviving rank)
+                self.watchdog.beat(epoch)
+                self.watchdog.check()
             if self.planner is not None and self.planner.is_active() and not getattr(self, "_plan_applied", False):
                 self.sync_active_plan()
             t_ep = time.time()
@@ -754,6 +763,8 @@ class FullGraphTrainer:
                 if getattr(args, "save_model", False):
                     save_train_state(self)
         self.edge_engine.shutdown()
+        if self.watchdog is not None:
+            self.watchdog.stop()
         print_training_summary(self)
         if self._metrics_fh is not None:
             self._metrics_fh.close()

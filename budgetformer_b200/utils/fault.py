@@ -2,7 +2,8 @@
 
 A spec is a comma-separated list of ``<kind>@<phase>:<epoch>[:rank<k>]`` items, e.g.
 ``oom@fwd:3`` (raise an out-of-memory error in the forward of epoch 3 on every rank),
-``oom@bwd:4:rank1``, ``raise@edge:2``, ``exit@step:7:rank1``, ``delay@step:5:rank0``.
+``oom@bwd:4:rank1``, ``raise@edge:2``, ``exit@step:7:rank1``, ``delay@step:5:rank0``, ``stall@step:3:rank1``
+(the rank stops making progress without announcing it: sleeps until it is killed).
 Faults are raised by the Python process at phase boundaries, never by a kernel: no GPU is
 faulted, trapped or hung.  ``InjectedOOM`` derives from ``torch.cuda.OutOfMemoryError`` where that class can
 be subclassed so that the regular recovery path handles it."""
@@ -39,6 +40,7 @@ class _Fault:
 class FaultInjector:
     def __init__(self, spec: str = "", rank: int = 0):
         self.rank = int(rank)
+        self.on_exit = None                       # optional callable run before an injected exit (orderly departure)
         self.faults: List[_Fault] = []
         spec = spec or os.environ.get("BF_FAULT", "")
         for item in filter(None, (s.strip() for s in spec.split(","))):
@@ -46,7 +48,7 @@ class FaultInjector:
             parts = rest.split(":")
             phase, epoch = parts[0], int(parts[1])
             rk = int(parts[2].replace("rank", "")) if len(parts) > 2 else None
-            if kind not in ("oom", "raise", "exit", "delay"):
+            if kind not in ("oom", "raise", "exit", "delay", "stall"):
                 raise ValueError(f"unknown fault kind {kind!r}")
             self.faults.append(_Fault(kind, phase, epoch, rk))
 
@@ -64,5 +66,9 @@ class FaultInjector:
                 raise InjectedFailure(f"injected failure at {phase} epoch {epoch} rank {self.rank}")
             if f.kind == "delay":
                 time.sleep(1.0)
+            if f.kind == "stall":
+                time.sleep(float(os.environ.get("BF_FAULT_STALL_SECONDS", "3600")))
             if f.kind == "exit":
-                os._exit(17)
+                if self.on_exit is not None:
+                    self.on_exit()
+                os._exit(int(os.environ.get("BF_FAULT_EXIT_CODE", "17")))

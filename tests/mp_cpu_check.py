@@ -78,6 +78,22 @@ def mode_adaptive(out_path):
     json.dump({"ok": True}, open(out_path + f".{dist.get_rank()}", "w"))
 
 
+def mode_watchdog(out_path):
+    """A rank that leaves between steps (injected exit with an announcement) or stalls silently: the survivor learns of
+    it from the watchdog - PeerLost before its next step, or a clean process abort when it is stuck in a collective."""
+    from budgetformer_b200.utils.watchdog import PeerLost
+    kind = os.environ["BF_WD_CASE"]
+    fault = "exit@step:3:rank1" if kind == "leave" else "stall@step:3:rank1"
+    t = make("gt", ["--watchdog_seconds", "2", "--fault_inject", fault, "--epochs", "6", "--eval_every", "100"])
+    try:
+        t.fit()
+        result = {"outcome": "finished"}
+    except PeerLost as e:
+        result = {"outcome": "peer_lost", "message": str(e), "epoch": t.epoch}
+    json.dump(result, open(out_path + f".{dist.get_rank()}", "w"))
+    os._exit(0)                                    # the peer is gone: skip the collective teardown
+
+
 def mode_syncbn(out_path):
     """--sync_batchnorm: training-mode GraphGPS on P ranks normalises with the statistics of all rows, so outputs and
     gradients equal the single-process run (which sees all rows in one BatchNorm call)."""
@@ -106,7 +122,7 @@ def mode_syncbn(out_path):
 
 if __name__ == "__main__":
     mode, out = sys.argv[1], sys.argv[2]
-    {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom, "syncbn": mode_syncbn}[mode](out)
+    {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom, "syncbn": mode_syncbn, "watchdog": mode_watchdog}[mode](out)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

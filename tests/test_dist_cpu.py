@@ -63,3 +63,42 @@ def test_sync_batchnorm_two_ranks_equals_single_process(tmp_path):
     for name in a["grads"]:
         ga, gb = torch.tensor(a["grads"][name]), torch.tensor(b["grads"][name])
         assert torch.allclose(ga, gb, atol=5e-5 + 2e-3 * float(ga.abs().max())), name
+
+
+def _spawn_raw(nproc, mode, out, port, env_extra):
+    env = dict(os.environ)
+    env["OMP_NUM_THREADS"] = "2"
+    env.update(env_extra)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "mp_cpu_check.py"), mode, out]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+
+
+def _watchdog_outcome(out, r):
+    """Either the main thread raised PeerLost between steps (JSON written), or it was already inside a collective and
+    the watchdog thread ended the process with its message."""
+    if os.path.exists(out + ".0"):
+        res = json.load(open(out + ".0"))
+        assert res["outcome"] == "peer_lost", res
+        return res["message"]
+    assert "[watchdog] rank 0" in r.stderr, r.stderr[-2000:]
+    return r.stderr
+
+
+def test_watchdog_reports_a_rank_that_left_between_steps(tmp_path):
+    """Host-side failure only: rank 1 announces its departure before step 3 and exits (exit code 0, so that the
+    launcher leaves rank 0 alone); rank 0 learns of it from the store."""
+    out = str(tmp_path / "wd_leave.json")
+    r = _spawn_raw(2, "watchdog", out, 29807, {"BF_WD_CASE": "leave", "BF_FAULT_EXIT_CODE": "0"})
+    assert "rank 1 left" in _watchdog_outcome(out, r)
+    assert not os.path.exists(out + ".1")                                   # rank 1 exited inside the injected fault
+
+
+def test_watchdog_aborts_when_a_peer_stalls_silently(tmp_path):
+    """Rank 1 stops making progress without a word; rank 0 is already inside the step's collectives.  Its watchdog thread
+    sees the heartbeat stand still for the deadline and ends the process (or the main thread gets PeerLost first if it
+    was between steps)."""
+    out = str(tmp_path / "wd_stall.json")
+    r = _spawn_raw(2, "watchdog", out, 29808, {"BF_WD_CASE": "stall", "BF_FAULT_STALL_SECONDS": "40"})
+    msg = _watchdog_outcome(out, r)
+    assert "silent" in msg or "did not reach step" in msg, msg
