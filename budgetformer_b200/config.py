@@ -58,6 +58,7 @@ _COMMON = [
 
 _BATCH_SP = [
     (("--batch_subgraph_mode",), str, "induced", {"choices": ["induced", "seed_rw"]}),
+    (("--batch_reorder_parts",), int, 0, {}),
     (("--seed_batch_size",), int, None, {}),
     (("--seq_len",), int, 256000, {}),
     (("--full_attn_hop_stats",), _STORE_TRUE, False, {}),

@@ -132,6 +132,9 @@ int bf_peer_gather_cols(void* const* src, int world, long long row0, long long r
 int bf_peer_scatter_cols(void* const* dst, int world, long long row0, long long rows, int cols_bytes,
                          long long dst_ld_bytes, const void* src, long long src_ld_bytes, cudaStream_t st);
 
+// Balanced k-way partition of a symmetric CSR (cpu/partition.cpp: BFS ordering + boundary refinement); returns the
+// number of nodes the refinement moved, or -1 on bad arguments.
+long long bf_partition_cpu(const int* rowptr, const int* col, int n, int k, float imbalance, int refine_passes, int* part);
 // Fan-out k-hop candidate expansion on the CPU (cpu/edge_builder.cpp): two passes, count then fill.
 int bf_khop_count_cpu(const int* out_rowptr, const int* out_col, int n, const int* fanout, int n_hops, long long seed,
                       long long* counts /* [n] */, int num_threads);

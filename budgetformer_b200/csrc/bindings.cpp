@@ -193,6 +193,18 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
   return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
 }
 
+// Part id per node of a symmetric int32 CPU CSR; second tensor = number of nodes the refinement moved.
+std::vector<Tensor> partition_cpu(Tensor rowptr, Tensor col, int64_t n, int64_t k, double imbalance, int64_t passes) {
+  TORCH_CHECK(!rowptr.is_cuda() && !col.is_cuda() && rowptr.scalar_type() == torch::kInt &&
+              col.scalar_type() == torch::kInt && rowptr.is_contiguous() && col.is_contiguous());
+  TORCH_CHECK(rowptr.numel() == n + 1 && k >= 1);
+  Tensor part = torch::zeros({n}, torch::kInt);
+  const long long moved = bf_partition_cpu(iptr(rowptr), iptr(col), (int)n, (int)k, (float)imbalance, (int)passes,
+                                           part.data_ptr<int>());
+  TORCH_CHECK(moved >= 0, "bf_partition_cpu: bad arguments");
+  return {part, torch::tensor((int64_t)moved, torch::kLong)};
+}
+
 // (src, dst) int64 candidates of the fan-out k-hop expansion over a CPU out-edge CSR.
 std::vector<Tensor> khop_candidates_cpu(Tensor out_rowptr, Tensor out_col, int64_t n, std::vector<int64_t> fanout,
                                         int64_t seed, int64_t num_threads) {
@@ -481,6 +493,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("edge_attn_bwd", &edge_attn_bwd);
   m.def("build_attn_graph", &build_attn_graph);
   m.def("khop_candidates_cpu", &khop_candidates_cpu);
+  m.def("partition_cpu", &partition_cpu);
   m.def("graph_transpose", &graph_transpose);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_supported", &gemm_supported);

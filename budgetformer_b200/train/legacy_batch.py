@@ -4,7 +4,9 @@ The node set is cut into sequences of ``--seq_len`` nodes; each step trains on o
 over the SP ranks.  The attention graph of a step is the subgraph induced by the sequence
 (``--batch_subgraph_mode induced``) or by the sequence's seeds plus the nodes their random walks visit
 (``seed_rw``); restates ``get_batch_blockize`` / ``sample_seed_rw_subgraph`` / ``_compute_local_spd_bias``
-(gt_sp/utils.py:1669-1966, :939-1010, :64-110) on the CSR containers of this package."""
+(gt_sp/utils.py:1669-1966, :939-1010, :64-110) on the CSR containers of this package.  ``--batch_reorder_parts k``
+(``get_batch_reorder_blockize``, gt_sp/utils.py:1969-2090) first reorders the sequence so that each of k locality
+clusters is contiguous, which keeps most attention edges inside one rank's rows."""
 from __future__ import annotations
 
 from typing import Optional, Tuple
@@ -24,6 +26,15 @@ def induced_subgraph(edge_index: torch.Tensor, idx: torch.Tensor, num_nodes: int
     s, d = remap[edge_index[0]], remap[edge_index[1]]
     m = (s >= 0) & (d >= 0)
     return torch.stack([s[m], d[m]], 0)
+
+
+def reorder_by_partition(edge_index: torch.Tensor, idx: torch.Tensor, num_nodes: int, k: int) -> torch.Tensor:
+    """``idx`` permuted so that the k parts of its induced subgraph are contiguous.  The partitioner is
+    deterministic, so every rank computes the same order and nothing is broadcast."""
+    from ..graph.partition import reformat_graph
+    sub = induced_subgraph(edge_index, idx, num_nodes)
+    _edges, old_of_new = reformat_graph(sub, k, num_nodes=int(idx.numel()))
+    return idx[old_of_new]
 
 
 def sample_seed_rw_subgraph(topo: Topology, seeds: torch.Tensor, walk_length: int, walks_per_node: int, seed: int,
@@ -62,6 +73,9 @@ def get_batch_blockize(args, feature: torch.Tensor, y: torch.Tensor, idx_batch: 
                                         max_nodes=int(args.seq_len) if int(args.seq_len) > 0 else None)
     else:
         nodes = seeds
+        parts = int(getattr(args, "batch_reorder_parts", 0) or 0)
+        if parts > 1 and nodes.numel() > parts:
+            nodes = reorder_by_partition(edge_index_global, nodes, num_nodes, parts)
     n = int(nodes.numel())
     pad = (-n) % max(1, sp_world)
     ei = induced_subgraph(edge_index_global, nodes, num_nodes)
@@ -88,3 +102,14 @@ def get_batch_blockize(args, feature: torch.Tensor, y: torch.Tensor, idx_batch: 
     if getattr(args, "attn_bias_mode", "none") == "local_spd":
         attn_bias = compute_local_spd_bias(ei, n_pad, int(args.attn_bias_max_dist))[sl]
     return x[sl], yy[sl], graph, attn_bias, label_ok[sl]
+
+
+def get_batch_reorder_blockize(args, feature, y, idx_batch, edge_index_global, num_nodes, sp_rank, sp_world, k: int = 0,
+                               topo: Optional[Topology] = None, epoch_seed: int = 0):
+    """``get_batch_blockize`` on the sequence reordered into ``k`` locality clusters (``k <= 1``: unchanged order)."""
+    import copy
+    a = copy.copy(args)
+    a.batch_reorder_parts = int(k)
+    a.batch_subgraph_mode = "induced"
+    return get_batch_blockize(a, feature, y, idx_batch, edge_index_global, num_nodes, sp_rank, sp_world, topo=topo,
+                              epoch_seed=epoch_seed)
