@@ -28,6 +28,7 @@ import torch
 import torch.distributed as dist
 
 from ..utils.comm_profiler import profile_call, record_scalar
+from .device_budget import BUDGET
 from .attn_graph import AttnGraph, Topology, add_virtual_node
 from .builder import build_attn_graph, graph_totals
 
@@ -175,6 +176,8 @@ class EdgeEngine:
                 and not getattr(self.args, "profile_sp_comm", False))
 
     def _build_device_ahead(self, seed: int, state: BudgetState):
+        if self._gpu_build_ruled_out(state):
+            return None                                   # decided and reported by the synchronous path of build()
         try:
             torch.cuda.set_device(self.device)
             if self._build_stream is None:
@@ -358,6 +361,12 @@ class EdgeEngine:
                 host = profile_call("edge_build_local", lambda: self._build_host(seed, state), device="cpu")
                 self._store(key, host)
             g = self._upload(host)
+        elif self._gpu_build_ruled_out(state):
+            # proactive CPU build: the estimate does not fit under the registered memory cap, or the GPU build already
+            # failed in this run; the caller reports it to the planner like a run-time failure
+            self.gpu_build_failed = True
+            self.topo_gpu = None
+            g = self._upload(profile_call("edge_build_local", lambda: self._build_host(seed, state), device="cpu"))
         else:
             try:
                 g = profile_call("edge_build_local", lambda: self._build_device(seed, state), device=self.device)
@@ -365,6 +374,7 @@ class EdgeEngine:
                 # sticky CPU fallback, reported to the planner by the caller (utils/fullgraph_sp_support.py:1334-1491)
                 self.gpu_build_failed = True
                 self.topo_gpu = None
+                BUDGET.mark_infeasible(self.device, self.topo_cpu.num_edges)
                 torch.cuda.empty_cache()
                 host = self._build_host(seed, state)
                 g = self._upload(host)
@@ -374,6 +384,15 @@ class EdgeEngine:
         if record:
             record_scalar("edge_merged_edges", g.num_edges, reduce="max")
         return g
+
+    def _gpu_build_ruled_out(self, state: BudgetState) -> bool:
+        """Checked only when a per-process memory cap is registered or a GPU build failed before: without either the
+        build is simply tried (its out-of-memory error is caught), so the common path makes no driver query."""
+        if self.device.type != "cuda" or (BUDGET.cap_bytes <= 0 and not BUDGET.any_infeasible()):
+            return False
+        dev = BUDGET.safe_build_device(self.device, self.estimate_working_set_bytes(state), self.topo_cpu.num_edges,
+                                       log=print if self.rank == 0 else None)
+        return dev.type != "cuda"
 
     def estimate_working_set_bytes(self, state: BudgetState) -> int:
         """First-principles GPU footprint of one device build: topology + fixed-width rows + CSR

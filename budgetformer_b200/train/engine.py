@@ -242,6 +242,8 @@ class FullGraphTrainer:
         total = torch.cuda.get_device_properties(self.device).total_memory
         frac = min(1.0, limit * 2 ** 20 / total)
         torch.cuda.set_per_process_memory_fraction(frac, self.device)
+        from ..graph.device_budget import BUDGET
+        BUDGET.set_gpu_memory_cap(limit * 2 ** 20)      # the driver's free-memory figure does not know about the cap
         if self.planner is not None:
             self.planner.set_gpu_memory_limit_bytes(limit * 2 ** 20)
         self.log(f"[gpu-cap] per-process GPU memory limited to {limit} MiB ({frac:.1%} of device)")
@@ -697,6 +699,8 @@ class FullGraphTrainer:
         policy = EDGE_POLICY_ORDER[pol_id]
         p.override_active_plan(policy, [TIER_FROM_ID[t] for t in tiers])
         self.edge_engine.set_policy(policy, lock=True)
+        from ..graph.device_budget import BUDGET
+        BUDGET.set_force_gpu_build(policy.startswith("gpu") and p.rw_on_gpu)   # set on every (re-)plan, never stale
         self._plan_applied = True
 
     # ------------------------------------------------------------------------------------------ loop

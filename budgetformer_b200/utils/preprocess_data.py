@@ -6,7 +6,12 @@ Sources (utils/preprocess_data.py:161-427 in the reference): Planetoid, Citation
 Computers, Reddit, HeterophilousGraphDataset (PyG); ogbn-arxiv / products / papers100M (OGB); pokec, snap-patents,
 genius (LINKX ``.mat`` / ``.npz`` files placed under ``<dataset_dir>/raw``; genius gets five seeded 50/25/25
 splits); and ``synthetic:<config>`` which generates the benchmark graphs of this repository without any download.
-PyG / OGB are optional: when they are not importable the corresponding names fail with a clear message."""
+PyG / OGB are optional: when they are not importable the corresponding names fail with a clear message.
+
+The legacy dense-bias sequence files are kept as well (utils/preprocess_data.py:25-50,431-555 in the reference):
+``adj_normalize`` / ``column_normalize`` / ``eigenvector``, ``process_data`` (one sequence per node: the node plus
+``k1`` neighbours drawn from its personalised-PageRank row, with the powers of the normalised adjacency as attention
+bias) and ``rand_nodes_seq`` (disjoint random sequences of ``k1`` nodes); ``--sequences ppr|rand --k1 K``."""
 from __future__ import annotations
 
 import argparse
@@ -110,14 +115,102 @@ def get_dataset(name: str, root: str = "./dataset/", split_id: int = 0, seed: in
     raise SystemExit(f"unknown dataset {name!r}")
 
 
+# ----------------------------------------------------------------------------------------------- legacy sequence files
+def adjacency(edge_index, num_nodes: int):
+    import scipy.sparse as sp
+    ei = torch.as_tensor(edge_index).cpu().numpy()
+    return sp.coo_matrix((np.ones(ei.shape[1], dtype=np.float32), (ei[0], ei[1])), shape=(num_nodes, num_nodes)).tocsr()
+
+
+def adj_normalize(mx):
+    """``(D + I)^-1/2 (A + I) (D + I)^-1/2``."""
+    import scipy.sparse as sp
+    mx = (mx + sp.eye(mx.shape[0], dtype=np.float32)).tocsr()
+    deg = np.asarray(mx.sum(1)).reshape(-1)
+    scale = np.where(deg > 0, 1.0 / np.sqrt(np.maximum(deg, 1e-30)), 0.0)
+    return (sp.diags(scale) @ mx @ sp.diags(scale)).tocsr()
+
+
+def column_normalize(mx):
+    """``A D^-1`` with D the row sums."""
+    import scipy.sparse as sp
+    deg = np.asarray(mx.sum(1)).reshape(-1)
+    return (mx @ sp.diags(np.where(deg > 0, 1.0 / np.maximum(deg, 1e-30), 0.0))).tocsr()
+
+
+def eigenvector(lap, k: int = 10) -> torch.Tensor:
+    """Eigenvectors 1..k of a (small, dense-able) Laplacian in increasing eigenvalue order."""
+    val, vec = np.linalg.eig(np.asarray(lap.todense() if hasattr(lap, "todense") else lap))
+    order = np.argsort(val.real)
+    return torch.tensor(np.real(vec[:, order])[:, 1:k + 1], dtype=torch.float32)
+
+
+def power_adjacency_list(normalized_adj, depth: int = 6):
+    """``[A', A'^2, ..., A'^depth]``: the channels of the dense attention bias."""
+    out = [normalized_adj.tocsr()]
+    for _ in range(depth - 1):
+        out.append((out[0] @ out[-1]).tocsr())
+    return out
+
+
+def _sequence_record(powers, ids: torch.Tensor, y: torch.Tensor):
+    from ..train.legacy_utils import dense_bias_from_adjs
+    return [dense_bias_from_adjs(powers, ids), ids, y[ids].long()]
+
+
+def process_data(root: str, name: str, k1: int, restart: float = 0.15, seed: int = 0, bias_dim: int = 6) -> str:
+    """``data_s<k1>.pt``: for every node the sequence [node, neighbours sampled without replacement in proportion to
+    its personalised-PageRank row, topped up with the highest-ranked ones], its ``[k1+1, k1+1, bias_dim]`` bias and
+    labels.  The PPR matrix is a dense inverse, so this is for small graphs only."""
+    path = os.path.join(root, name)
+    x, y = torch.load(os.path.join(path, "x.pt")), torch.load(os.path.join(path, "y.pt"))
+    n = int(y.shape[0])
+    norm = adj_normalize(adjacency(torch.load(os.path.join(path, "edge_index.pt")), n))
+    powers = power_adjacency_list(norm, bias_dim)
+    ppr = restart * np.linalg.inv(np.eye(n) - (1.0 - restart) * np.asarray(norm.todense(), dtype=np.float64))
+    rng = np.random.default_rng(seed)
+    records = []
+    for v in range(n):
+        row = ppr[v].copy()
+        row[v] = -np.inf
+        top = np.argsort(row)[-k1:]                       # ascending: weakest of the top k1 first, like the reference
+        w = np.maximum(np.where(np.isfinite(row), row, 0.0), 0.0)
+        m = int(min(k1, (w > 0).sum()))
+        drawn = rng.choice(n, size=m, replace=False, p=w / w.sum()) if m > 0 else np.zeros(0, dtype=np.int64)
+        ids = torch.from_numpy(np.concatenate([[v], drawn, top[: k1 - m]]).astype(np.int64))
+        records.append([_sequence_record(powers, ids, y)])
+    out = os.path.join(path, f"data_s{k1}.pt")
+    torch.save(records, out)
+    return out
+
+
+def rand_nodes_seq(root: str, name: str, k1: int, seed: int = 0, bias_dim: int = 6) -> str:
+    """``data_rand<k1>.pt``: the shuffled node set cut into disjoint sequences of ``k1`` nodes (the last one shorter)."""
+    path = os.path.join(root, name)
+    y = torch.load(os.path.join(path, "y.pt"))
+    n = int(y.shape[0])
+    powers = power_adjacency_list(adj_normalize(adjacency(torch.load(os.path.join(path, "edge_index.pt")), n)), bias_dim)
+    order = torch.randperm(n, generator=torch.Generator().manual_seed(seed))
+    records = [[_sequence_record(powers, ids, y)] for ids in torch.split(order, int(k1))]
+    out = os.path.join(path, f"data_rand{k1}.pt")
+    if not os.path.exists(out):
+        torch.save(records, out)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--dataset", required=True)
     ap.add_argument("--dataset_dir", default="./dataset/")
     ap.add_argument("--split_id", type=int, default=0)
     ap.add_argument("--seed", type=int, default=42)
+    ap.add_argument("--sequences", choices=["none", "ppr", "rand"], default="none")
+    ap.add_argument("--k1", type=int, default=100)
     a = ap.parse_args(argv)
     print("wrote", get_dataset(a.dataset, a.dataset_dir, a.split_id, a.seed))
+    if a.sequences != "none":
+        fn = process_data if a.sequences == "ppr" else rand_nodes_seq
+        print("wrote", fn(a.dataset_dir, a.dataset, a.k1, seed=a.seed))
 
 
 if __name__ == "__main__":
