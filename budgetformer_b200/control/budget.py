@@ -214,6 +214,32 @@ def fixed_budget_controller(real: int, rw: int, walk_length: Optional[int] = Non
     return c
 
 
+def round_budget_to_block(value: int, block_size: int) -> int:
+    """``value`` rounded up to a multiple of the block (at least one block; 0 stays 0)."""
+    b = max(1, int(block_size))
+    return 0 if value <= 0 else max(b, -(-int(value) // b) * b)
+
+
+def floor_budget_to_block(value: int, block_size: int) -> int:
+    """``value`` rounded down to a multiple of the block (at least one block; 0 stays 0)."""
+    b = max(1, int(block_size))
+    return 0 if value <= 0 else max(b, (int(value) // b) * b)
+
+
+def auto_initial_budget_candidates(config: AdaptiveEdgeBudgetConfig) -> List[dict]:
+    """Start points for a budget search (utils/fullgraph_sp_support.py:2194-2235): (real, rw) pairs on block
+    multiples - 1, 2 and 4 blocks of real edges with none, as many or twice as many walk edges - that fit under the
+    ceiling, ordered by total and then by walk share."""
+    ceiling, b = int(config.max_total_edges_per_query), max(1, int(config.block_size))
+    if ceiling <= 0:
+        return []
+    grid = [(1, 0), (1, 1), (1, 2), (2, 0), (2, 1), (2, 2), (4, 0), (4, 2)]
+    pairs = sorted({(r * b, w * b) for r, w in grid if (r + w) * b <= ceiling}, key=lambda p: (p[0] + p[1], p[1]))
+    if not pairs:
+        pairs = [(min(ceiling, b), 0)]
+    return [{"real_edges_per_query": r, "rw_edges_per_query": w} for r, w in pairs]
+
+
 def _pair(state) -> tuple:
     return int(state.get("real_edges_per_query", 0)), int(state.get("rw_edges_per_query", 0))
 

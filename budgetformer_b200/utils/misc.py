@@ -81,3 +81,23 @@ class StepTimer:
             torch.cuda.synchronize(self.device)
         self.elapsed = time.perf_counter() - self._t0
         return False
+
+
+def clone_model_state_to_cpu(model) -> dict:
+    """Detached CPU copy of every entry of ``model.state_dict()`` (a snapshot that later training does not touch)."""
+    return {name: t.detach().cpu().clone() for name, t in model.state_dict().items()}
+
+
+@contextlib.contextmanager
+def dropout_disabled(model):
+    """Every ``nn.Dropout`` of ``model`` in eval mode inside the block, its previous mode restored afterwards
+    (``_set_dropout_eval`` / ``_restore_dropout``, utils/fullgraph_sp_support.py:3365-3376); BatchNorm and the rest of
+    the model keep their mode."""
+    saved = [(m, m.training) for m in model.modules() if isinstance(m, torch.nn.Dropout)]
+    for m, _ in saved:
+        m.eval()
+    try:
+        yield
+    finally:
+        for m, mode in saved:
+            m.train(mode)

@@ -213,3 +213,35 @@ def test_comm_aware_checkpointer_greedy_from_the_back():
         c.plan("cpu"); c.record_post_forward_memory("cpu"); c.notify_step_end("cpu")
     assert c.is_active()
     assert [c.mode(i) for i in range(4)] == ["layer", "layer", "keep_mha", "keep_mha"]   # 1000 + 2*300 <= 1710 < 1000 + 3*300
+
+
+def test_block_rounding_and_initial_candidates():
+    from budgetformer_b200.control.budget import (AdaptiveEdgeBudgetConfig, auto_initial_budget_candidates,
+                                                  floor_budget_to_block, round_budget_to_block)
+    assert [round_budget_to_block(v, 4) for v in (0, 1, 4, 5)] == [0, 4, 4, 8]
+    assert [floor_budget_to_block(v, 4) for v in (0, 1, 4, 7, 8)] == [0, 4, 4, 4, 8]
+    cfg = AdaptiveEdgeBudgetConfig(max_total_edges_per_query=8, block_size=2)
+    pairs = [(c["real_edges_per_query"], c["rw_edges_per_query"]) for c in auto_initial_budget_candidates(cfg)]
+    assert pairs == [(2, 0), (4, 0), (2, 2), (4, 2), (2, 4), (8, 0), (4, 4)]
+    assert all(r + w <= 8 for r, w in pairs)
+    tiny = AdaptiveEdgeBudgetConfig(max_total_edges_per_query=1, block_size=2)
+    assert auto_initial_budget_candidates(tiny) == [{"real_edges_per_query": 1, "rw_edges_per_query": 0}]
+    assert auto_initial_budget_candidates(AdaptiveEdgeBudgetConfig(max_total_edges_per_query=0)) == []
+
+
+def test_model_state_snapshot_and_dropout_scope():
+    import torch
+    from budgetformer_b200.utils.misc import clone_model_state_to_cpu, dropout_disabled
+    m = torch.nn.Sequential(torch.nn.Linear(3, 3), torch.nn.Dropout(0.5), torch.nn.BatchNorm1d(3))
+    snap = clone_model_state_to_cpu(m)
+    with torch.no_grad():
+        m[0].weight.add_(1.0)
+    assert not torch.equal(snap["0.weight"], m[0].weight) and snap["0.weight"].device.type == "cpu"
+    m.train()
+    with dropout_disabled(m):
+        assert not m[1].training and m[2].training and m.training
+    assert m[1].training
+    m[1].eval()
+    with dropout_disabled(m):
+        pass
+    assert not m[1].training                                 # the previous mode comes back, whatever it was
