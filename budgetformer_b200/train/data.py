@@ -62,9 +62,9 @@ def sample_induced_subgraph(x, y, edge_index, split_idx, ratio: float, seed: int
 
 def load_data(args, dist_module=None) -> GraphData:
     root = os.path.join(args.dataset_dir, args.dataset)
-    x = safe_torch_load(os.path.join(root, "x.pt")).float()
-    y = safe_torch_load(os.path.join(root, "y.pt"))
-    edge_index = safe_torch_load(os.path.join(root, "edge_index.pt")).to(torch.int64)
+    x = safe_torch_load(os.path.join(root, "x.pt"), mmap=True).float()      # no copy when already fp32
+    y = safe_torch_load(os.path.join(root, "y.pt"), mmap=True)
+    edge_index = safe_torch_load(os.path.join(root, "edge_index.pt"), mmap=True).to(torch.int64)
     multilabel = bool(getattr(args, "multilabel", False)) or (y.dim() == 2 and y.size(1) > 1)
     if not multilabel:
         y = y.reshape(-1).to(torch.long)

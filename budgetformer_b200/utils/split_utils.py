@@ -26,11 +26,20 @@ _MASK_TRIPLES = (
 )
 
 
-def safe_torch_load(path: str):
-    try:
-        return torch.load(path, map_location="cpu", weights_only=True)
-    except (TypeError, pickle.UnpicklingError, RuntimeError):
-        return torch.load(path, map_location="cpu", weights_only=False)
+def safe_torch_load(path: str, mmap: bool = False):
+    """CPU load that prefers the safe unpickler.  ``mmap=True`` first tries a memory-mapped load (the ranks of a node
+    then share one page-cache copy of a large feature matrix instead of holding one each; files in the old
+    non-zip format cannot be mapped and fall through), like the attempt ladder of the reference's loader
+    (utils/fullgraph_sp_support.py:692-715)."""
+    attempts = ([{"weights_only": True, "mmap": True}, {"weights_only": False, "mmap": True}] if mmap else []) + \
+        [{"weights_only": True}, {"weights_only": False}]
+    last = None
+    for kw in attempts:
+        try:
+            return torch.load(path, map_location="cpu", **kw)
+        except (TypeError, pickle.UnpicklingError, RuntimeError, ValueError) as exc:
+            last = exc
+    raise last
 
 
 def _as_idx(value) -> torch.Tensor:

@@ -121,3 +121,17 @@ def test_hop_mass_tracking_on_core_attention():
     assert core.get_head_mass_stats().shape == (4,)
     core.disable_hop_mass_tracking()
     assert core.get_hop_mass_stats() is None
+
+
+def test_memory_mapped_load_matches_plain_load(tmp_path):
+    from budgetformer_b200.utils.split_utils import safe_torch_load
+    p = str(tmp_path / "x.pt")
+    x = torch.randn(64, 8)
+    torch.save(x, p)
+    mapped = safe_torch_load(p, mmap=True)
+    assert torch.equal(mapped, x) and mapped.float() is mapped        # fp32 stays mapped, no second copy
+    mapped[0, 0] = 123.0                                              # private mapping: the file is not written
+    assert torch.equal(safe_torch_load(p), x)
+    old = str(tmp_path / "old.pt")
+    torch.save(x, old, _use_new_zipfile_serialization=False)          # cannot be mapped: falls back to a plain load
+    assert torch.equal(safe_torch_load(old, mmap=True), x)
