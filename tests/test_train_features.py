@@ -186,3 +186,18 @@ def test_mini_batch_driver_trains_and_writes_hop_stats(tmp_path):
     assert files == ["epoch_1.json", "epoch_2.json"]
     stats = json.load(open(os.path.join(hop_dir, "toy", "gt", "attn0.95_maxhop6", files[0])))
     assert len(stats["layers"]) == 2 and abs(sum(stats["layers"][0]["hop_mass"]) - 1.0) < 1e-4
+
+
+def test_mini_batch_driver_with_locality_reordering(tmp_path):
+    """--batch_reorder_parts: the driver trains on sequences reordered into locality clusters (native partitioner)."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import main_node_sp
+    from budgetformer_b200.graph.synthetic import sbm_graph, write_dataset
+    x, y, ei = sbm_graph(400, feat_dim=16, seed=2)
+    write_dataset(str(tmp_path), "toy", x, y, ei)
+    best = main_node_sp.main(["--model", "gt", "--dataset", "toy", "--dataset_dir", str(tmp_path), "--seq_len", "200",
+                              "--epochs", "2", "--n_layers", "1", "--hidden_dim", "32", "--num_heads", "4", "--ffn_dim", "64",
+                              "--device", "cpu", "--eval_every", "1", "--force_random_split", "--batch_reorder_parts", "4"])
+    assert 0.0 <= best["valid"] <= 1.0 and best["epoch"] >= 1
