@@ -113,6 +113,9 @@ _EXTRA = [
     (("--fault_inject",), str, "", {"help": "host-side fault injection spec, e.g. oom@fwd:3 or exit@7:rank1"}),
     (("--watchdog_seconds",), float, 0.0, {"help": "heartbeat watchdog: abort all ranks cleanly when a peer leaves or stays "
                                                    "silent for this many seconds (0 = off, NCCL's timeout only)"}),
+    (("--watchdog_step_seconds",), float, 0.0, {"help": "with --watchdog_seconds: also abort when this rank itself has "
+                                                        "not reached a step boundary for this long (a collective or "
+                                                        "kernel over its deadline; 0 = off)"}),
     (("--nvtx",), _STORE_TRUE, False, {"help": "emit NVTX ranges for step phases and profiled calls"}),
     (("--debug_checks",), _STORE_TRUE, False, {"help": "validate every attention graph, poison reusable symmetric "
                                                "buffers after use and check losses/gradients for NaN (also BF_DEBUG=1)"}),

@@ -10,7 +10,9 @@ every rank posts a heartbeat to the job's key-value store at each step boundary 
                    *before* their next launch;
 * the thread       covers the case where this rank is already blocked inside a collective: when a peer stays silent
                    for ``deadline_s`` it sets the abort flag (so every other rank aborts too) and ends this process
-                   with exit code ``EXIT_CODE`` after printing which rank was lost.
+                   with exit code ``EXIT_CODE`` after printing which rank was lost.  With ``step_deadline_s > 0`` it
+                   also ends the job when this rank itself has not reached a step boundary for that long (a
+                   collective or a kernel that exceeded its deadline while every rank sits in the same step).
 
 Nothing here touches a GPU; the failure modes are exercised with gloo ranks on the CPU.
 """
@@ -31,11 +33,13 @@ class PeerLost(RuntimeError):
 
 class StepWatchdog:
     def __init__(self, store, rank: int, world: int, deadline_s: float = 120.0, poll_s: float = 0.5,
-                 hard_exit: bool = True, startup_grace_s: float = 120.0):
+                 hard_exit: bool = True, startup_grace_s: float = 120.0, step_deadline_s: float = 0.0):
         self.store, self.rank, self.world = store, int(rank), int(world)
         self.deadline_s, self.poll_s, self.hard_exit = float(deadline_s), float(poll_s), bool(hard_exit)
         self.startup_grace_s = max(float(startup_grace_s), self.deadline_s)   # ranks reach their first step unevenly
+        self.step_deadline_s = max(0.0, float(step_deadline_s))
         self._beats = 0
+        self._beat_time = time.monotonic()
         self._step = -1
         self._last_seen = {r: (-1, time.monotonic()) for r in range(self.world)}
         self._stop = threading.Event()
@@ -48,6 +52,7 @@ class StepWatchdog:
     def beat(self, step: int) -> None:
         self._step = int(step)
         self.store.set(f"hb/{self.rank}", str(self._step))
+        self._beat_time = time.monotonic()
         self._beats += 1
         self._armed = True
 
@@ -117,6 +122,11 @@ class StepWatchdog:
                 self._poll_once()
             except Exception:
                 continue
+            if (self._lost is None and self._armed and self.step_deadline_s > 0
+                    and time.monotonic() - self._beat_time > self.step_deadline_s):
+                self._lost = (f"rank {self.rank} has not reached a step boundary for "
+                              f"{time.monotonic() - self._beat_time:.0f} s (step {self._step}): a collective or a "
+                              f"kernel exceeded its deadline")
             if self._lost is None:
                 waited_since = None
                 continue
@@ -140,4 +150,5 @@ def build_watchdog(args, rank: int, world: int):
     import torch.distributed as dist
     from torch.distributed.distributed_c10d import _get_default_store
     store = dist.PrefixStore("bf_watchdog", _get_default_store())
-    return StepWatchdog(store, rank, world, deadline_s=secs)
+    return StepWatchdog(store, rank, world, deadline_s=secs,
+                        step_deadline_s=float(getattr(args, "watchdog_step_seconds", 0) or 0))

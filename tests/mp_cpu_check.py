@@ -83,8 +83,9 @@ def mode_watchdog(out_path):
     it from the watchdog - PeerLost before its next step, or a clean process abort when it is stuck in a collective."""
     from budgetformer_b200.utils.watchdog import PeerLost
     kind = os.environ["BF_WD_CASE"]
-    fault = "exit@step:3:rank1" if kind == "leave" else "stall@step:3:rank1"
-    t = make("gt", ["--watchdog_seconds", "2", "--fault_inject", fault, "--epochs", "6", "--eval_every", "100"])
+    fault = {"leave": "exit@step:3:rank1", "stall": "stall@step:3:rank1", "midstep": "stall@bwd:3:rank1"}[kind]
+    extra = ["--watchdog_step_seconds", "6"] if kind == "midstep" else []
+    t = make("gt", ["--watchdog_seconds", "2", "--fault_inject", fault, "--epochs", "6", "--eval_every", "100"] + extra)
     try:
         t.fit()
         result = {"outcome": "finished"}

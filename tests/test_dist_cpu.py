@@ -102,3 +102,13 @@ def test_watchdog_aborts_when_a_peer_stalls_silently(tmp_path):
     r = _spawn_raw(2, "watchdog", out, 29808, {"BF_WD_CASE": "stall", "BF_FAULT_STALL_SECONDS": "40"})
     msg = _watchdog_outcome(out, r)
     assert "silent" in msg or "did not reach step" in msg, msg
+
+
+def test_watchdog_ends_a_step_that_exceeds_its_deadline(tmp_path):
+    """Rank 1 stalls in the middle of step 3, after its heartbeat: both ranks sit in the same step (rank 0 inside the
+    gradient collective), so no heartbeat is behind.  The step deadline ends the job with a message on every rank."""
+    out = str(tmp_path / "wd_mid.json")
+    r = _spawn_raw(2, "watchdog", out, 29809, {"BF_WD_CASE": "midstep", "BF_FAULT_STALL_SECONDS": "60"})
+    assert not os.path.exists(out + ".0") and not os.path.exists(out + ".1")
+    assert "has not reached a step boundary" in r.stderr or "abort requested" in r.stderr, r.stderr[-2000:]
+    assert "[watchdog] rank" in r.stderr
