@@ -25,5 +25,11 @@ def main(argv=None):
     return best
 
 
+def cli() -> int:
+    """Console-script entry point (the return value of ``main`` is a result dict, not an exit status)."""
+    main(sys.argv[1:])
+    return 0
+
+
 if __name__ == "__main__":
     main(sys.argv[1:])
