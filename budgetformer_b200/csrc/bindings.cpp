@@ -9,6 +9,8 @@
 extern "C" int bf_budget_select_cpu(const int*, const int*, const int*, const int*, int, int, int, int, int, int,
                                     long long, int, int*, uint8_t*, int*, unsigned long long*, int);
 extern "C" int bf_ell_to_csr_cpu(const int*, const uint8_t*, const int*, int, int, int*, uint8_t*);
+extern "C" int bf_budget_select_fanout_cpu(const int*, const int*, const int*, const int*, int, int, int, const int*, int,
+                                           int, long long, int, int*, uint8_t*, int*, unsigned long long*, int);
 
 namespace {
 
@@ -191,6 +193,35 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
                       exphormer ? etype.data_ptr<uint8_t>() : nullptr);
   }
   return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
+}
+
+// CPU build of the fan-out mode (`--rw_edge_mode dgl_neighbor`): same outputs as build_attn_graph.
+std::vector<Tensor> build_attn_graph_fanout_cpu(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col,
+                                                int64_t n, int64_t b_real, int64_t b_rw, std::vector<int64_t> fanout,
+                                                bool exphormer, int64_t seed, int64_t num_threads) {
+  for (const Tensor* t : {&in_rowptr, &in_src, &out_rowptr, &out_col})
+    TORCH_CHECK(!t->is_cuda() && t->scalar_type() == torch::kInt && t->is_contiguous(), "int32 contiguous CPU CSR expected");
+  TORCH_CHECK(b_real >= 0 && b_rw >= 0);
+  const int cap = std::max<int>((int)(b_real + b_rw + (exphormer ? 1 : 0)), 1);
+  auto iopt = torch::TensorOptions().dtype(torch::kInt);
+  Tensor ell_col = torch::empty({n, cap}, iopt);
+  Tensor ell_type = exphormer ? torch::empty({n, cap}, iopt.dtype(torch::kUInt8)) : Tensor();
+  Tensor ell_cnt = torch::zeros({n}, iopt);
+  Tensor totals = torch::zeros({2}, torch::kLong);
+  std::vector<int> fo(fanout.begin(), fanout.end());
+  bf_budget_select_fanout_cpu(iptr(in_rowptr), iptr(in_src), iptr(out_rowptr), iptr(out_col), (int)n, (int)b_real,
+                              (int)b_rw, fo.data(), (int)fo.size(), exphormer ? 1 : 0, seed, cap,
+                              ell_col.data_ptr<int>(), exphormer ? ell_type.data_ptr<uint8_t>() : nullptr,
+                              ell_cnt.data_ptr<int>(), reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>()),
+                              (int)num_threads);
+  Tensor rowptr = torch::zeros({n + 1}, iopt);
+  rowptr.slice(0, 1).copy_(torch::cumsum(ell_cnt, 0, torch::kInt));
+  const int64_t n_edges = n > 0 ? rowptr[n].item<int64_t>() : 0;
+  Tensor col = torch::empty({n_edges}, iopt);
+  Tensor etype = exphormer ? torch::empty({n_edges}, iopt.dtype(torch::kUInt8)) : torch::empty({0}, iopt.dtype(torch::kUInt8));
+  bf_ell_to_csr_cpu(ell_col.data_ptr<int>(), exphormer ? ell_type.data_ptr<uint8_t>() : nullptr, rowptr.data_ptr<int>(),
+                    (int)n, cap, col.data_ptr<int>(), exphormer ? etype.data_ptr<uint8_t>() : nullptr);
+  return {rowptr, col, etype, totals};
 }
 
 // Part id per node of a symmetric int32 CPU CSR; second tensor = number of nodes the refinement moved.
@@ -494,6 +525,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_attn_graph", &build_attn_graph);
   m.def("khop_candidates_cpu", &khop_candidates_cpu);
   m.def("partition_cpu", &partition_cpu);
+  m.def("build_attn_graph_fanout_cpu", &build_attn_graph_fanout_cpu);
   m.def("graph_transpose", &graph_transpose);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_supported", &gemm_supported);

@@ -14,6 +14,45 @@
 
 #include "../edge_spec.h"
 
+namespace {
+
+// Keep the k smallest composites (hash << 32 | source id) of one side.
+inline void keep_smallest(std::vector<uint64_t>& c, int k) {
+  if ((int)c.size() > k) {
+    std::nth_element(c.begin(), c.begin() + k, c.end());
+    c.resize(k);
+  }
+}
+
+// Merge the selected real and walk sources of query v into its fixed-width row.  Plain models: union, ascending,
+// duplicates removed.  Exphormer: real sources (type 0), walk sources (type 1), then the self loop (type 0), each
+// part ascending and nothing removed.
+inline int write_row(int v, const std::vector<uint64_t>& rc, const std::vector<uint64_t>& wc, bool exphormer,
+                     std::vector<uint32_t>& tmp, int* row, uint8_t* trow) {
+  int c = 0;
+  if (exphormer) {
+    tmp.clear();
+    for (uint64_t x : rc) tmp.push_back((uint32_t)x);
+    std::sort(tmp.begin(), tmp.end());
+    for (uint32_t s : tmp) { row[c] = (int)s; trow[c++] = 0; }
+    tmp.clear();
+    for (uint64_t x : wc) tmp.push_back((uint32_t)x);
+    std::sort(tmp.begin(), tmp.end());
+    for (uint32_t s : tmp) { row[c] = (int)s; trow[c++] = 1; }
+    row[c] = v; trow[c++] = 0;
+    return c;
+  }
+  tmp.clear();
+  for (uint64_t x : rc) tmp.push_back((uint32_t)x);
+  for (uint64_t x : wc) tmp.push_back((uint32_t)x);
+  std::sort(tmp.begin(), tmp.end());
+  tmp.erase(std::unique(tmp.begin(), tmp.end()), tmp.end());
+  for (uint32_t s : tmp) row[c++] = (int)s;
+  return c;
+}
+
+}  // namespace
+
 extern "C" int bf_budget_select_cpu(const int* in_rowptr, const int* in_src, const int* out_rowptr,
                                     const int* out_col, int n, int b_real, int b_rw, int walks, int walk_len,
                                     int exphormer, long long seed, int cap, int* ell_col, uint8_t* ell_type,
@@ -34,10 +73,7 @@ extern "C" int bf_budget_select_cpu(const int* in_rowptr, const int* in_src, con
         const int beg = in_rowptr[v], end = in_rowptr[v + 1];
         for (int e = beg; e < end; ++e)
           rc.push_back(bf_edge_composite((uint32_t)in_src[e], (uint32_t)v, seed + BF_REAL_SEED_OFFSET));
-        if ((int)rc.size() > b_real) {
-          std::nth_element(rc.begin(), rc.begin() + b_real, rc.end());
-          rc.resize(b_real);
-        }
+        keep_smallest(rc, b_real);
       }
       if (b_rw > 0 && walks > 0 && walk_len > 0) {
         for (int w = 0; w < walks; ++w) {
@@ -51,36 +87,12 @@ extern "C" int bf_budget_select_cpu(const int* in_rowptr, const int* in_src, con
             if (d == 1 || cur != prev) wc.push_back(bf_edge_composite((uint32_t)cur, (uint32_t)v, seed + BF_RW_SEED_OFFSET));
           }
         }
-        if ((int)wc.size() > b_rw) {
-          std::nth_element(wc.begin(), wc.begin() + b_rw, wc.end());
-          wc.resize(b_rw);
-        }
+        keep_smallest(wc, b_rw);
       }
       tot_r += rc.size();
       tot_w += wc.size();
-      int* row = ell_col + (long long)v * cap;
-      if (exphormer) {
-        uint8_t* trow = ell_type + (long long)v * cap;
-        int c = 0;
-        merged.clear();
-        for (uint64_t x : rc) merged.push_back((uint32_t)x);
-        std::sort(merged.begin(), merged.end());
-        for (uint32_t s : merged) { row[c] = (int)s; trow[c++] = 0; }
-        merged.clear();
-        for (uint64_t x : wc) merged.push_back((uint32_t)x);
-        std::sort(merged.begin(), merged.end());
-        for (uint32_t s : merged) { row[c] = (int)s; trow[c++] = 1; }
-        row[c] = v; trow[c++] = 0;
-        ell_cnt[v] = c;
-      } else {
-        merged.clear();
-        for (uint64_t x : rc) merged.push_back((uint32_t)x);
-        for (uint64_t x : wc) merged.push_back((uint32_t)x);
-        std::sort(merged.begin(), merged.end());
-        merged.erase(std::unique(merged.begin(), merged.end()), merged.end());
-        for (size_t i = 0; i < merged.size(); ++i) row[i] = (int)merged[i];
-        ell_cnt[v] = (int)merged.size();
-      }
+      ell_cnt[v] = write_row(v, rc, wc, exphormer != 0, merged, ell_col + (long long)v * cap,
+                             exphormer ? ell_type + (long long)v * cap : nullptr);
     }
   }
   totals[0] = tot_r;
@@ -185,5 +197,48 @@ extern "C" int bf_khop_fill_cpu(const int* out_rowptr, const int* out_col, int n
       khop_expand(out_rowptr, out_col, o, fanout, n_hops, seed, s, [&](int v) { src[w] = v; dst[w] = o; ++w; });
     }
   }
+  return 0;
+}
+
+// The whole build of `--rw_edge_mode dgl_neighbor` per query: top-b_real in-neighbours, top-b_rw of the nodes the
+// fan-out expansion reaches from the query (a multiset: a node reached in two hops counts twice, as in the
+// specification), merged into the fixed-width row.  Same output contract as bf_budget_select_cpu.
+extern "C" int bf_budget_select_fanout_cpu(const int* in_rowptr, const int* in_src, const int* out_rowptr,
+                                           const int* out_col, int n, int b_real, int b_rw, const int* fanout,
+                                           int n_hops, int exphormer, long long seed, int cap, int* ell_col,
+                                           uint8_t* ell_type, int* ell_cnt, unsigned long long* totals,
+                                           int num_threads) {
+  unsigned long long tot_r = 0, tot_w = 0;
+#ifdef _OPENMP
+  if (num_threads > 0) omp_set_num_threads(num_threads);
+#endif
+#pragma omp parallel reduction(+ : tot_r, tot_w)
+  {
+    std::vector<uint64_t> rc, wc;
+    std::vector<uint32_t> merged;
+    KhopScratch scratch;
+#pragma omp for schedule(dynamic, 256)
+    for (int v = 0; v < n; ++v) {
+      rc.clear();
+      wc.clear();
+      if (b_real > 0) {
+        for (int e = in_rowptr[v]; e < in_rowptr[v + 1]; ++e)
+          rc.push_back(bf_edge_composite((uint32_t)in_src[e], (uint32_t)v, seed + BF_REAL_SEED_OFFSET));
+        keep_smallest(rc, b_real);
+      }
+      if (b_rw > 0 && n_hops > 0) {
+        khop_expand(out_rowptr, out_col, v, fanout, n_hops, seed, scratch, [&](int u) {
+          wc.push_back(bf_edge_composite((uint32_t)u, (uint32_t)v, seed + BF_RW_SEED_OFFSET));
+        });
+        keep_smallest(wc, b_rw);
+      }
+      tot_r += rc.size();
+      tot_w += wc.size();
+      ell_cnt[v] = write_row(v, rc, wc, exphormer != 0, merged, ell_col + (long long)v * cap,
+                             exphormer ? ell_type + (long long)v * cap : nullptr);
+    }
+  }
+  totals[0] = tot_r;
+  totals[1] = tot_w;
   return 0;
 }

@@ -171,7 +171,7 @@ def build_attn_graph_spec(
         rs, rd = select_per_query(in_src, real_dst, b_real, int(seed) + REAL_SEED_OFFSET)
     else:
         rs, rd = np.zeros(0, np.int64), np.zeros(0, np.int64)
-    if use_rw and walks_per_node > 0 and walk_length > 0 and (b_rw is None or b_rw > 0):
+    if use_rw and (fanout or (walks_per_node > 0 and walk_length > 0)) and (b_rw is None or b_rw > 0):
         if fanout:
             native = khop_neighbor_candidates_native(topo, fanout, seed)
             ws, wd = native if native is not None else khop_neighbor_candidates(topo, fanout, seed)

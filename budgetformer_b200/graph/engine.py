@@ -57,20 +57,23 @@ def resolve_budget_state(args, controller_state: Optional[dict] = None) -> Budge
     * ``--random_edge_blocks --max_total_edges_per_query B`` -> ``(B+1)//2`` real, ``B//2`` walk
       (all ``B`` to real when ``walks_per_node == 0``);
     * otherwise -> all real edges iff ``--include_real_edges 1``, the full walk pool iff ``walks_per_node > 0``.
-    """
+
+    ``--rw_edge_mode dgl_neighbor`` builds its pool from the fan-out, so ``walks_per_node`` does not gate the walk
+    side there (:905-915)."""
     wl = int(getattr(args, "walk_length", 4))
     wpn = int(getattr(args, "walks_per_node", 0))
+    walks_on = wpn > 0 or str(getattr(args, "rw_edge_mode", "random_walk")) == "dgl_neighbor"
     if controller_state is not None:
         r = int(controller_state.get("real_edges_per_query", 0))
         w = int(controller_state.get("rw_edges_per_query", 0))
         wl = int(controller_state.get("walk_length", getattr(args, "fixed_walk_length", None) or wl))
-        return BudgetState(r > 0, w > 0 and wpn > 0, r, w, wl)
+        return BudgetState(r > 0, w > 0 and walks_on, r, w, wl)
     total = int(getattr(args, "max_total_edges_per_query", 0) or 0)
     if getattr(args, "random_edge_blocks", False) and total > 0:
         if wpn <= 0:
             return BudgetState(True, False, total, 0, wl)
         return BudgetState(True, True, (total + 1) // 2, total // 2, wl)
-    return BudgetState(bool(int(getattr(args, "include_real_edges", 0))), wpn > 0, None, None, wl)
+    return BudgetState(bool(int(getattr(args, "include_real_edges", 0))), walks_on, None, None, wl)
 
 
 def edge_seed_for_epoch(args, epoch: int, static_seed_epochs: int = 0) -> int:

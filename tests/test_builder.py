@@ -133,3 +133,40 @@ def test_native_fanout_expansion_equals_spec(fanout):
     finally:
         spec.khop_neighbor_candidates_native = orig
     assert torch.equal(g1.rowptr, g2.rowptr) and torch.equal(g1.col, g2.col)
+
+
+@pytest.mark.parametrize("exphormer", [False, True])
+@pytest.mark.parametrize("fanout,b_real,b_rw", [([3, 2], 3, 4), ([-1, 2], 0, 5), ([2, 2, 2], 4, 0), ([4], 2, 40)])
+def test_native_fanout_build_equals_spec(fanout, b_real, b_rw, exphormer):
+    """The one-pass C++ build of the fan-out mode (expansion + per-query top-K + merge) is bit-identical to the numpy
+    specification, type row and edge totals included."""
+    from budgetformer_b200.graph import builder_spec as spec
+    from budgetformer_b200.graph.builder import build_attn_graph
+    topo, _ = random_topology(400, 3000, hub_out=60, seed=9)
+    want = spec.build_attn_graph_spec(topo, b_real, b_rw, 2, 3, 123, exphormer=exphormer, fanout=fanout)
+    got = build_attn_graph(topo, b_real, b_rw, 2, 3, 123, exphormer=exphormer, fanout=fanout, num_threads=3)
+    assert got.max_degree is not None                                   # came from the native path
+    assert torch.equal(got.rowptr, want.rowptr) and torch.equal(got.col, want.col)
+    if exphormer:
+        assert torch.equal(got.etype, want.etype)
+    assert (got.n_real, got.n_rw) == (want.n_real, want.n_rw)
+    deg = got.rowptr[1:] - got.rowptr[:-1]
+    assert int(deg.max()) <= got.max_degree
+
+
+def test_fanout_mode_is_not_gated_by_walks_per_node():
+    """--rw_edge_mode dgl_neighbor builds its pool from the fan-out: walks_per_node = 0 keeps the walk side."""
+    import types
+    from budgetformer_b200.graph import builder_spec as spec
+    from budgetformer_b200.graph.builder import build_attn_graph
+    from budgetformer_b200.graph.engine import resolve_budget_state
+    args = types.SimpleNamespace(walk_length=4, walks_per_node=0, rw_edge_mode="dgl_neighbor", include_real_edges=1)
+    assert resolve_budget_state(args).use_rw
+    assert resolve_budget_state(args, {"real_edges_per_query": 2, "rw_edges_per_query": 3}).use_rw
+    args.rw_edge_mode = "random_walk"
+    assert not resolve_budget_state(args).use_rw
+    assert not resolve_budget_state(args, {"real_edges_per_query": 2, "rw_edges_per_query": 3}).use_rw
+    topo, _ = random_topology(200, 1200, seed=2)
+    g = build_attn_graph(topo, 2, 3, 0, 0, 5, fanout=[3, 2])
+    s = spec.build_attn_graph_spec(topo, 2, 3, 0, 0, 5, fanout=[3, 2])
+    assert g.n_rw > 0 and torch.equal(g.col, s.col) and torch.equal(g.rowptr, s.rowptr)
