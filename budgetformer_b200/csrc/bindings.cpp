@@ -9,8 +9,8 @@
 extern "C" int bf_budget_select_cpu(const int*, const int*, const int*, const int*, int, int, int, int, int, int,
                                     long long, int, int*, uint8_t*, int*, unsigned long long*, int);
 extern "C" int bf_ell_to_csr_cpu(const int*, const uint8_t*, const int*, int, int, int*, uint8_t*);
-extern "C" int bf_budget_select_fanout_cpu(const int*, const int*, const int*, const int*, int, int, int, const int*, int,
-                                           int, long long, int, int*, uint8_t*, int*, unsigned long long*, int);
+extern "C" int bf_build_rows_cpu(const int*, const int*, const int*, const int*, int, int, int, int, int, int, int, const int*,
+                                 int, int, long long, const long long*, long long*, int*, uint8_t*, unsigned long long*, int);
 
 namespace {
 
@@ -195,32 +195,35 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
   return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
 }
 
-// CPU build of the fan-out mode (`--rw_edge_mode dgl_neighbor`): same outputs as build_attn_graph.
-std::vector<Tensor> build_attn_graph_fanout_cpu(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col,
-                                                int64_t n, int64_t b_real, int64_t b_rw, std::vector<int64_t> fanout,
-                                                bool exphormer, int64_t seed, int64_t num_threads) {
+// General CPU build (rows of any length; a negative budget keeps every candidate of that side; an empty fan-out
+// list selects Philox walks).  Same outputs as build_attn_graph.
+std::vector<Tensor> build_attn_graph_rows_cpu(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col,
+                                              int64_t n, int64_t b_real, int64_t b_rw, bool use_real, bool use_rw,
+                                              int64_t walks, int64_t walk_len, std::vector<int64_t> fanout,
+                                              bool exphormer, int64_t seed, int64_t num_threads) {
   for (const Tensor* t : {&in_rowptr, &in_src, &out_rowptr, &out_col})
     TORCH_CHECK(!t->is_cuda() && t->scalar_type() == torch::kInt && t->is_contiguous(), "int32 contiguous CPU CSR expected");
-  TORCH_CHECK(b_real >= 0 && b_rw >= 0);
-  const int cap = std::max<int>((int)(b_real + b_rw + (exphormer ? 1 : 0)), 1);
-  auto iopt = torch::TensorOptions().dtype(torch::kInt);
-  Tensor ell_col = torch::empty({n, cap}, iopt);
-  Tensor ell_type = exphormer ? torch::empty({n, cap}, iopt.dtype(torch::kUInt8)) : Tensor();
-  Tensor ell_cnt = torch::zeros({n}, iopt);
-  Tensor totals = torch::zeros({2}, torch::kLong);
   std::vector<int> fo(fanout.begin(), fanout.end());
-  bf_budget_select_fanout_cpu(iptr(in_rowptr), iptr(in_src), iptr(out_rowptr), iptr(out_col), (int)n, (int)b_real,
-                              (int)b_rw, fo.data(), (int)fo.size(), exphormer ? 1 : 0, seed, cap,
-                              ell_col.data_ptr<int>(), exphormer ? ell_type.data_ptr<uint8_t>() : nullptr,
-                              ell_cnt.data_ptr<int>(), reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>()),
-                              (int)num_threads);
-  Tensor rowptr = torch::zeros({n + 1}, iopt);
-  rowptr.slice(0, 1).copy_(torch::cumsum(ell_cnt, 0, torch::kInt));
-  const int64_t n_edges = n > 0 ? rowptr[n].item<int64_t>() : 0;
+  Tensor counts = torch::zeros({n}, torch::kLong);
+  Tensor totals = torch::zeros({2}, torch::kLong);
+  auto run = [&](const long long* offsets, int* col, uint8_t* etype) {
+    bf_build_rows_cpu(iptr(in_rowptr), iptr(in_src), iptr(out_rowptr), iptr(out_col), (int)n, (int)b_real, (int)b_rw,
+                      use_real ? 1 : 0, use_rw ? 1 : 0, (int)walks, (int)walk_len, fo.data(), (int)fo.size(),
+                      exphormer ? 1 : 0, seed, offsets, reinterpret_cast<long long*>(counts.data_ptr<int64_t>()), col, etype,
+                      reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>()), (int)num_threads);
+  };
+  run(nullptr, nullptr, nullptr);
+  Tensor incl = torch::cumsum(counts, 0);
+  const int64_t n_edges = n > 0 ? incl[n - 1].item<int64_t>() : 0;
+  TORCH_CHECK(n_edges < (int64_t)INT32_MAX, "attention graph too large for int32 offsets: ", n_edges, " edges");
+  Tensor offsets = (incl - counts).contiguous();
+  auto iopt = torch::TensorOptions().dtype(torch::kInt);
   Tensor col = torch::empty({n_edges}, iopt);
   Tensor etype = exphormer ? torch::empty({n_edges}, iopt.dtype(torch::kUInt8)) : torch::empty({0}, iopt.dtype(torch::kUInt8));
-  bf_ell_to_csr_cpu(ell_col.data_ptr<int>(), exphormer ? ell_type.data_ptr<uint8_t>() : nullptr, rowptr.data_ptr<int>(),
-                    (int)n, cap, col.data_ptr<int>(), exphormer ? etype.data_ptr<uint8_t>() : nullptr);
+  run(reinterpret_cast<const long long*>(offsets.data_ptr<int64_t>()), col.data_ptr<int>(),
+      exphormer ? etype.data_ptr<uint8_t>() : nullptr);
+  Tensor rowptr = torch::zeros({n + 1}, iopt);
+  rowptr.slice(0, 1).copy_(incl.to(torch::kInt));
   return {rowptr, col, etype, totals};
 }
 
@@ -525,7 +528,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_attn_graph", &build_attn_graph);
   m.def("khop_candidates_cpu", &khop_candidates_cpu);
   m.def("partition_cpu", &partition_cpu);
-  m.def("build_attn_graph_fanout_cpu", &build_attn_graph_fanout_cpu);
+  m.def("build_attn_graph_rows_cpu", &build_attn_graph_rows_cpu);
   m.def("graph_transpose", &graph_transpose);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_supported", &gemm_supported);

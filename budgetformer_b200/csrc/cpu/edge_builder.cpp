@@ -200,14 +200,18 @@ extern "C" int bf_khop_fill_cpu(const int* out_rowptr, const int* out_col, int n
   return 0;
 }
 
-// The whole build of `--rw_edge_mode dgl_neighbor` per query: top-b_real in-neighbours, top-b_rw of the nodes the
-// fan-out expansion reaches from the query (a multiset: a node reached in two hops counts twice, as in the
-// specification), merged into the fixed-width row.  Same output contract as bf_budget_select_cpu.
-extern "C" int bf_budget_select_fanout_cpu(const int* in_rowptr, const int* in_src, const int* out_rowptr,
-                                           const int* out_col, int n, int b_real, int b_rw, const int* fanout,
-                                           int n_hops, int exphormer, long long seed, int cap, int* ell_col,
-                                           uint8_t* ell_type, int* ell_cnt, unsigned long long* totals,
-                                           int num_threads) {
+// -----------------------------------------------------------------------------------------------------
+// General CPU build with rows of any length: budgets above the fixed-width limit of the CUDA builder and
+// "no budget" (b < 0: keep every candidate - the reference's default without budget flags, all real edges and
+// the whole walk pool).  Two passes over the queries: `offsets == nullptr` counts the row lengths, otherwise the
+// rows are written at their prefix-sum offsets.  Walk candidates come from Philox walks (n_hops == 0) or from
+// the fan-out expansion (n_hops > 0).  Same selection and merge rules as the fixed-width builders above.
+// -----------------------------------------------------------------------------------------------------
+extern "C" int bf_build_rows_cpu(const int* in_rowptr, const int* in_src, const int* out_rowptr, const int* out_col,
+                                 int n, int b_real, int b_rw, int use_real, int use_rw, int walks, int walk_len,
+                                 const int* fanout, int n_hops, int exphormer, long long seed,
+                                 const long long* offsets, long long* counts, int* col, uint8_t* etype,
+                                 unsigned long long* totals, int num_threads) {
   unsigned long long tot_r = 0, tot_w = 0;
 #ifdef _OPENMP
   if (num_threads > 0) omp_set_num_threads(num_threads);
@@ -216,26 +220,50 @@ extern "C" int bf_budget_select_fanout_cpu(const int* in_rowptr, const int* in_s
   {
     std::vector<uint64_t> rc, wc;
     std::vector<uint32_t> merged;
+    std::vector<int> row;
+    std::vector<uint8_t> trow;
     KhopScratch scratch;
 #pragma omp for schedule(dynamic, 256)
     for (int v = 0; v < n; ++v) {
       rc.clear();
       wc.clear();
-      if (b_real > 0) {
+      if (use_real && b_real != 0) {
         for (int e = in_rowptr[v]; e < in_rowptr[v + 1]; ++e)
           rc.push_back(bf_edge_composite((uint32_t)in_src[e], (uint32_t)v, seed + BF_REAL_SEED_OFFSET));
-        keep_smallest(rc, b_real);
+        if (b_real > 0) keep_smallest(rc, b_real);
       }
-      if (b_rw > 0 && n_hops > 0) {
-        khop_expand(out_rowptr, out_col, v, fanout, n_hops, seed, scratch, [&](int u) {
-          wc.push_back(bf_edge_composite((uint32_t)u, (uint32_t)v, seed + BF_RW_SEED_OFFSET));
-        });
-        keep_smallest(wc, b_rw);
+      if (use_rw && b_rw != 0) {
+        auto add = [&](int u) { wc.push_back(bf_edge_composite((uint32_t)u, (uint32_t)v, seed + BF_RW_SEED_OFFSET)); };
+        if (n_hops > 0) {
+          khop_expand(out_rowptr, out_col, v, fanout, n_hops, seed, scratch, add);
+        } else {
+          for (int w = 0; w < walks; ++w) {
+            const uint64_t walk_id = (uint64_t)v * (uint64_t)walks + (uint64_t)w;
+            int cur = v;
+            for (int d = 1; d <= walk_len; ++d) {
+              const int prev = cur;
+              const int ob = out_rowptr[cur];
+              const uint32_t deg = (uint32_t)(out_rowptr[cur + 1] - ob);
+              if (deg > 0) cur = out_col[ob + (int)bf_mulhi32(bf_walk_uniform32(walk_id, (uint32_t)d, (uint64_t)seed), deg)];
+              if (d == 1 || cur != prev) add(cur);
+            }
+          }
+        }
+        if (b_rw > 0) keep_smallest(wc, b_rw);
       }
       tot_r += rc.size();
       tot_w += wc.size();
-      ell_cnt[v] = write_row(v, rc, wc, exphormer != 0, merged, ell_col + (long long)v * cap,
-                             exphormer ? ell_type + (long long)v * cap : nullptr);
+      const size_t width = rc.size() + wc.size() + 1;
+      row.resize(width);
+      trow.resize(width);
+      const int c = write_row(v, rc, wc, exphormer != 0, merged, row.data(), trow.data());
+      if (offsets == nullptr) {
+        counts[v] = c;
+      } else {
+        const long long o = offsets[v];
+        std::copy(row.begin(), row.begin() + c, col + o);
+        if (exphormer) std::copy(trow.begin(), trow.begin() + c, etype + o);
+      }
     }
   }
   totals[0] = tot_r;

@@ -44,10 +44,11 @@ def build_attn_graph(
     ``--include_real_edges`` path) and budgets above 32 per side fall back to the specification."""
     br = 0 if not use_real else b_real
     bw = 0 if (not use_rw or (not fanout and (walks_per_node <= 0 or walk_length <= 0))) else b_rw
-    if fanout and not force_spec and br is not None and bw is not None and topo.device.type == "cpu":
-        g = _build_fanout_native(topo, int(br), int(bw), fanout, seed, exphormer, num_threads)
+    if not force_spec and (fanout or not native_supported(br, bw, walk_length)):
+        g = _build_rows_native(topo, b_real, b_rw, walks_per_node, walk_length, seed, use_real, use_rw, exphormer,
+                               fanout, num_threads)
         if g is not None:
-            return g
+            return g.to(topo.device) if topo.device.type != "cpu" else g
     if force_spec or fanout or not native_supported(br, bw, walk_length):
         g = build_attn_graph_spec(topo, b_real, b_rw, walks_per_node, walk_length, seed,
                                   use_real=use_real, use_rw=use_rw, exphormer=exphormer, fanout=fanout)
@@ -65,22 +66,30 @@ def build_attn_graph(
     return g
 
 
-def _build_fanout_native(topo: Topology, br: int, bw: int, fanout, seed: int, exphormer: bool,
-                         num_threads: int) -> Optional[AttnGraph]:
-    """``--rw_edge_mode dgl_neighbor`` on the C++/OpenMP builder (expansion, per-query selection and merge in one pass
-    per query); ``None`` when the extension is not available."""
+def _build_rows_native(topo: Topology, b_real: Optional[int], b_rw: Optional[int], walks_per_node: int, walk_length: int,
+                       seed: int, use_real: bool, use_rw: bool, exphormer: bool, fanout, num_threads: int
+                       ) -> Optional[AttnGraph]:
+    """The cases the fixed-width builders do not take - a side without budget (``None``: every candidate) or above
+    ``MAX_SIDE_BUDGET``, walks longer than ``MAX_WALK_LEN`` - on the general two-pass C++/OpenMP builder.  It runs on
+    the CPU copy of the topology (the specification it replaces does too); ``None`` without the extension."""
     try:
         from ..ops import _ext
         ext = _ext.load()
     except Exception:
         return None
+    cpu = topo if topo.device.type == "cpu" else topo.to("cpu")
     i32 = lambda t: t.to(torch.int32).contiguous()
-    rowptr, col, etype, totals = ext.build_attn_graph_fanout_cpu(
-        i32(topo.in_rowptr), i32(topo.in_src), i32(topo.out_rowptr), i32(topo.out_col), int(topo.num_nodes), br, bw,
-        [int(f) if f is not None else -1 for f in fanout], bool(exphormer), int(seed), int(num_threads))
+    walk_side = bool(use_rw) and (bool(fanout) or (walks_per_node > 0 and walk_length > 0))
+    code = lambda b: -1 if b is None else int(b)
+    rowptr, col, etype, totals = ext.build_attn_graph_rows_cpu(
+        i32(cpu.in_rowptr), i32(cpu.in_src), i32(cpu.out_rowptr), i32(cpu.out_col), int(topo.num_nodes),
+        code(b_real), code(b_rw), bool(use_real), walk_side, int(walks_per_node), int(walk_length),
+        [int(f) if f is not None else -1 for f in (fanout or [])], bool(exphormer), int(seed), int(num_threads))
     r, w = (int(x) for x in totals.tolist())
-    return AttnGraph(int(topo.num_nodes), rowptr, col, etype if exphormer else None, n_real=r, n_rw=w,
-                     max_degree=br + bw + (1 if exphormer else 0))
+    bound = None
+    if b_real is not None and b_rw is not None:
+        bound = max(0, int(b_real)) + max(0, int(b_rw)) + (1 if exphormer else 0)
+    return AttnGraph(int(topo.num_nodes), rowptr, col, etype if exphormer else None, n_real=r, n_rw=w, max_degree=bound)
 
 
 def graph_totals(g: AttnGraph):

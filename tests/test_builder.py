@@ -170,3 +170,31 @@ def test_fanout_mode_is_not_gated_by_walks_per_node():
     g = build_attn_graph(topo, 2, 3, 0, 0, 5, fanout=[3, 2])
     s = spec.build_attn_graph_spec(topo, 2, 3, 0, 0, 5, fanout=[3, 2])
     assert g.n_rw > 0 and torch.equal(g.col, s.col) and torch.equal(g.rowptr, s.rowptr)
+
+
+@pytest.mark.parametrize("exphormer", [False, True])
+@pytest.mark.parametrize("b_real,b_rw,walks,length,fanout,use_real,use_rw", [
+    (None, None, 2, 3, None, True, True),        # the reference's default: all real edges + the whole walk pool
+    (None, 4, 2, 3, None, True, True),
+    (40, 50, 6, 10, None, True, True),           # above the fixed-width limit
+    (3, 3, 2, 20, None, True, True),             # walks longer than the CUDA builder takes
+    (None, None, 2, 3, [3, 2], True, True),      # fan-out pool without budget
+    (None, None, 2, 3, None, False, True),
+    (None, None, 0, 0, None, True, True),        # no walks at all
+    (0, None, 2, 3, None, True, True),
+])
+def test_general_native_build_equals_spec(b_real, b_rw, walks, length, fanout, use_real, use_rw, exphormer):
+    from budgetformer_b200.graph import builder_spec as spec
+    from budgetformer_b200.graph import builder
+    topo, _ = random_topology(300, 2500, hub_out=50, seed=11)
+    want = spec.build_attn_graph_spec(topo, b_real, b_rw, walks, length, 31, use_real=use_real, use_rw=use_rw,
+                                      exphormer=exphormer, fanout=fanout)
+    got = builder._build_rows_native(topo, b_real, b_rw, walks, length, 31, use_real, use_rw, exphormer, fanout, 3)
+    assert got is not None
+    assert torch.equal(got.rowptr, want.rowptr) and torch.equal(got.col, want.col)
+    if exphormer:
+        assert torch.equal(got.etype, want.etype)
+    assert (got.n_real, got.n_rw) == (want.n_real, want.n_rw)
+    via_dispatch = builder.build_attn_graph(topo, b_real, b_rw, walks, length, 31, use_real=use_real, use_rw=use_rw,
+                                            exphormer=exphormer, fanout=fanout)
+    assert torch.equal(via_dispatch.col, want.col)
