@@ -236,13 +236,14 @@ class FullGraphTrainer:
     def _apply_memory_limit(self) -> None:
         """``--multi_tier_gpu_memory_limit_mib``: cap the allocator and tell the planner
         (utils/fullgraph_sp_runtime.py:167-195)."""
+        from ..graph.device_budget import BUDGET
         limit = int(getattr(self.args, "multi_tier_gpu_memory_limit_mib", 0) or 0)
+        BUDGET.reset()                                  # process-wide state: a new trainer starts a new run
         if limit <= 0 or self.device.type != "cuda":
             return
         total = torch.cuda.get_device_properties(self.device).total_memory
         frac = min(1.0, limit * 2 ** 20 / total)
         torch.cuda.set_per_process_memory_fraction(frac, self.device)
-        from ..graph.device_budget import BUDGET
         BUDGET.set_gpu_memory_cap(limit * 2 ** 20)      # the driver's free-memory figure does not know about the cap
         if self.planner is not None:
             self.planner.set_gpu_memory_limit_bytes(limit * 2 ** 20)
