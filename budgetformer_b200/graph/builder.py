@@ -41,7 +41,9 @@ def build_attn_graph(
     fanout=None,
 ) -> AttnGraph:
     """Build on whatever device ``topo`` lives on.  ``None`` budgets (unsampled, the legacy
-    ``--include_real_edges`` path) and budgets above 32 per side fall back to the specification."""
+    ``--include_real_edges`` path), budgets above 32 per side, walks longer than 16 and the fan-out mode go to the
+    general C++ builder on the CPU (to the numpy specification only when the extension is missing or
+    ``force_spec`` asks for it)."""
     br = 0 if not use_real else b_real
     bw = 0 if (not use_rw or (not fanout and (walks_per_node <= 0 or walk_length <= 0))) else b_rw
     if not force_spec and (fanout or not native_supported(br, bw, walk_length)):
