@@ -94,6 +94,20 @@ class SparseCoreAttention(nn.Module):
             if edge_hops is not None:
                 self.hop_tracker.add_sparse(dst, edge_hops, a)
 
+    # ---- dense-attention research hooks (models/graphormer_dist_node_level.py:121-130,296-304 in the reference) ----
+    def set_full_attention_capture(self, enabled: bool = True) -> None:
+        """Keep the head-averaged probabilities ``[b, q, k]`` of the next dense call on the CPU."""
+        self.capture_full_attn = bool(enabled)
+        if not self.capture_full_attn:
+            self.last_full_attn_mean = None
+
+    def get_last_full_attention_mean(self):
+        return getattr(self, "last_full_attn_mean", None)
+
+    def set_full_attention_extra_bias(self, extra_bias) -> None:
+        """A tensor broadcastable to ``[b, heads, q, k]`` added to the dense scores before the softmax (``None`` = off)."""
+        self.full_attention_extra_bias = extra_bias
+
     def full_attention(self, q, k, v, attn_bias=None):
         q = q.transpose(1, 2)
         k = k.transpose(1, 2).transpose(2, 3)
@@ -101,7 +115,19 @@ class SparseCoreAttention(nn.Module):
         x = torch.matmul(q / self.scale, k)
         if attn_bias is not None:
             x = x + attn_bias
-        x = self.att_dropout(torch.softmax(x, dim=3))
+        extra = getattr(self, "full_attention_extra_bias", None)
+        if extra is not None:
+            x = x + extra.to(device=x.device, dtype=x.dtype)
+        probs = torch.softmax(x, dim=3)
+        if getattr(self, "capture_full_attn", False):
+            self.last_full_attn_mean = probs.mean(dim=1).detach().cpu()
+        if getattr(self, "track_hop_mass", False) and getattr(self, "hop_matrix", None) is not None:
+            # hop_matrix [Q, K] holds the hop distance from the sampled queries hop_queries [Q] to every key
+            with torch.no_grad():
+                rows = probs.mean(dim=1)[0].index_select(0, self.hop_queries.to(probs.device)).float()
+                self.hop_tracker.add_dense(rows, self.hop_matrix.to(probs.device))
+                self.head_mass.add(probs[0].permute(1, 2, 0).reshape(-1, probs.size(1)))
+        x = self.att_dropout(probs)
         return x.matmul(v).transpose(1, 2).contiguous()
 
     def sparse(self, q, k, v, graph: AttnGraph, edge_bias=None):
@@ -221,3 +247,50 @@ class NodeModelBase(nn.Module):
         for layer in self.layers:
             d = layer.self_attention.dist_attn
             yield getattr(d, "local_attn", d)
+
+    # ---- per-layer switches of the dense-attention hooks (models/graphormer_dist_node_level.py:1178-1228) --------
+    def _full_attention_layers(self, layer_mode: str = "all"):
+        n = len(self.layers)
+        mode = str(layer_mode).lower()
+        if mode not in ("all", "last"):
+            raise ValueError(f"unsupported full-attention layer mode: {layer_mode}")
+        return list(range(n)) if mode == "all" else ([n - 1] if n else [])
+
+    def set_full_attention_capture_layers(self, enabled: bool = True, layer_mode: str = "all") -> None:
+        chosen = set(self._full_attention_layers(layer_mode)) if enabled else set()
+        for i, core in enumerate(self.core_attention_modules()):
+            core.set_full_attention_capture(i in chosen)
+
+    def get_full_attention_means_per_layer(self, layer_mode: str = "all"):
+        cores = list(self.core_attention_modules())
+        return [cores[i].get_last_full_attention_mean() for i in self._full_attention_layers(layer_mode)]
+
+    def set_full_attention_extra_biases(self, extra_biases, layer_mode: str = "all") -> None:
+        chosen = self._full_attention_layers(layer_mode)
+        if extra_biases is not None and len(extra_biases) != len(chosen):
+            raise ValueError(f"expected {len(chosen)} extra bias tensors for layer_mode={layer_mode}, got {len(extra_biases)}")
+        by_layer = dict(zip(chosen, extra_biases)) if extra_biases is not None else {}
+        for i, core in enumerate(self.core_attention_modules()):
+            core.set_full_attention_extra_bias(by_layer.get(i))
+
+    def set_last_layer_full_attention_capture(self, enabled: bool = True) -> None:
+        self.set_full_attention_capture_layers(enabled, layer_mode="last")
+
+    def get_last_layer_full_attention_mean(self):
+        means = self.get_full_attention_means_per_layer(layer_mode="last")
+        return means[0] if means else None
+
+    def set_last_layer_full_attention_extra_bias(self, extra_bias) -> None:
+        self.set_full_attention_extra_biases([extra_bias], layer_mode="last")
+
+    def enable_hop_mass_tracking(self, mass: float = 0.95, max_queries: int = 64, query_sampling: str = "random",
+                                 max_batches: int = 1, max_hop: int = 15) -> None:
+        for core in self.core_attention_modules():
+            core.enable_hop_mass_tracking(mass, max_queries, query_sampling, max_batches, max_hop)
+
+    def disable_hop_mass_tracking(self) -> None:
+        for core in self.core_attention_modules():
+            core.disable_hop_mass_tracking()
+
+    def get_hop_mass_stats_per_layer(self):
+        return [core.get_hop_mass_stats() for core in self.core_attention_modules()]

@@ -107,3 +107,48 @@ def test_gt_rejects_dense_attention_and_init_scale():
     std = float(m.layers[0].O.weight.std())
     assert abs(std - 0.02 / 2 ** 0.5) < 0.004
     assert float(m.layers[0].O.bias.abs().sum()) == 0
+
+
+def test_dense_attention_capture_extra_bias_and_hop_mass():
+    """Research hooks of the dense path: per-layer capture of the head-averaged probabilities, an additive extra bias
+    per layer, and hop-mass tracking against a hop matrix of sampled queries."""
+    from budgetformer_b200.utils.analytics import bfs_hop_matrix
+    m, _ = _model("graphgps", ["--attn_type", "full"])
+    m.eval()
+    n = 12
+    x = torch.randn(n, 10)
+    ring = torch.stack([torch.arange(n), (torch.arange(n) + 1) % n])
+    m.set_full_attention_capture_layers(True, "all")
+    with torch.no_grad():
+        base = m(x, None, ring, attn_type="full")
+    means = m.get_full_attention_means_per_layer("all")
+    assert len(means) == 2 and all(a.shape == (1, n, n) for a in means)
+    assert torch.allclose(means[0].sum(-1), torch.ones(1, n), atol=1e-5)
+    assert m.get_last_layer_full_attention_mean() is means[1]
+    # a bias that forbids every key but the query itself makes the captured attention the identity
+    mask = torch.full((n, n), -1e9)
+    mask.fill_diagonal_(0.0)
+    m.set_last_layer_full_attention_extra_bias(mask)
+    with torch.no_grad():
+        biased = m(x, None, ring, attn_type="full")
+    last = m.get_last_layer_full_attention_mean()
+    assert torch.allclose(last[0], torch.eye(n), atol=1e-6) and not torch.allclose(biased, base)
+    first = m.get_full_attention_means_per_layer("all")[0]
+    assert torch.allclose(first, means[0], atol=1e-6)                    # only the last layer got the bias
+    with pytest.raises(ValueError):
+        m.set_full_attention_extra_biases([mask], "all")
+    m.set_full_attention_extra_biases(None)
+    m.set_full_attention_capture_layers(False)
+    assert m.get_last_layer_full_attention_mean() is None
+    # hop mass on the dense path
+    queries = torch.tensor([0, 5])
+    hop = bfs_hop_matrix(ring, n, queries, max_hop=6)
+    m.enable_hop_mass_tracking(mass=0.9, max_batches=4, max_hop=6)
+    for core in m.core_attention_modules():
+        core.hop_queries, core.hop_matrix = queries, hop
+    with torch.no_grad():
+        m(x, None, ring, attn_type="full")
+    stats = m.get_hop_mass_stats_per_layer()
+    assert len(stats) == 2 and abs(sum(stats[0]["hop_mass"]) - 1.0) < 1e-4
+    m.disable_hop_mass_tracking()
+    assert m.get_hop_mass_stats_per_layer() == [None, None]
