@@ -141,11 +141,34 @@ class SparseCoreAttention(nn.Module):
             self._track_sparse(q, k, graph, getattr(self, "edge_hops", None))
         return out.unsqueeze(0)
 
+    def sparse_head_groups(self, q, k, v, edge_sets, edge_bias=None):
+        """One edge set per head group (models/graphormer_dist_node_level.py:175-214, models/gt_dist_node_level.py:195-221):
+        with G sets, consecutive blocks of ceil(Hl / G) local heads attend over set g; the heads of a missing or empty
+        set output zero.  ``edge_bias``, when given, is a list with one ``[E_g, heads of the group]`` tensor per set.
+        Every group uses the score rule of the single-set path."""
+        b, s, hl, hn = q.shape
+        groups = max(1, len(edge_sets))
+        per = -(-hl // groups)
+        out = q.new_zeros(b, s, hl, hn)
+        for g, edges in enumerate(edge_sets):
+            h0, h1 = g * per, min((g + 1) * per, hl)
+            if h0 >= h1 or edges is None or (isinstance(edges, torch.Tensor) and edges.numel() == 0):
+                continue
+            graph = as_attn_graph(edges, s)
+            if graph.num_edges == 0:
+                continue
+            sl = lambda t: t[:, :, h0:h1].contiguous()
+            out[:, :, h0:h1] = self.sparse(sl(q), sl(k), sl(v), graph.to(q.device),
+                                           edge_bias=None if edge_bias is None else edge_bias[g])
+        return out
+
     def forward(self, q, k, v, attn_bias=None, edge_index=None, attn_type=None, **kw):
         b, s = q.size(0), q.size(1)
         attn_type = "sparse" if attn_type is None else str(attn_type).lower()
         if attn_type == "full":
             x = self.full_attention(q, k, v, attn_bias)
+        elif attn_type == "sparse" and isinstance(edge_index, (list, tuple)):
+            x = self.sparse_head_groups(q, k, v, edge_index, edge_bias=kw.get("edge_bias"))
         elif attn_type == "sparse":
             graph = as_attn_graph(edge_index, s)
             x = self.sparse(q, k, v, graph, edge_bias=kw.get("edge_bias"))

@@ -41,6 +41,17 @@ class CoreAttention(SparseCoreAttention):
             from flash_attn import flash_attn_func
             return flash_attn_func(q, k, v, self.attention_dropout_rate if self.training else 0.0).reshape(
                 q.size(0), q.size(1), -1)
+        if attn_type == "sparse" and attn_bias is not None and isinstance(edge_index, (list, tuple)):
+            # one edge set per head group: the bias of set g is read at its own edges for the heads of the group
+            from ..graph.attn_graph import as_attn_graph
+            hl, groups = q.size(2), max(1, len(edge_index))
+            per = -(-hl // groups)
+            graphs = [None if (e is None or (isinstance(e, torch.Tensor) and e.numel() == 0)) else as_attn_graph(e, q.size(1))
+                      for e in edge_index]
+            eb = [None if g is None else
+                  attn_bias[0][i * per:min((i + 1) * per, hl)][:, g.row_ids(), g.col.long()].transpose(0, 1)
+                  for i, g in enumerate(graphs)]
+            return super().forward(q, k, v, None, graphs, "sparse", edge_bias=eb)
         if attn_type == "sparse" and attn_bias is not None:
             from ..graph.attn_graph import as_attn_graph
             g = as_attn_graph(edge_index, q.size(1))

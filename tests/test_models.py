@@ -152,3 +152,48 @@ def test_dense_attention_capture_extra_bias_and_hop_mass():
     assert len(stats) == 2 and abs(sum(stats[0]["hop_mass"]) - 1.0) < 1e-4
     m.disable_hop_mass_tracking()
     assert m.get_hop_mass_stats_per_layer() == [None, None]
+
+
+@pytest.mark.parametrize("name", ["gt", "graphormer"])
+def test_one_edge_set_per_head_group(name):
+    """A list of edge sets: consecutive head groups attend over their own set (the legacy per-head subgraph views).
+    Two identical sets reproduce the single-set output; with one set missing its heads contribute nothing."""
+    from budgetformer_b200.graph.legacy_samplers import GroupedHeadSubgraphProvider
+    m, _ = _model(name, ["--num_global_node", "0"] if name == "graphormer" else [])
+    m.eval()
+    n = 16
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(n, 10, generator=g)
+    ei = torch.cat([torch.randint(0, n, (2, 60), generator=g), torch.arange(n).repeat(2, 1)], 1)
+    with torch.no_grad():
+        single = m(x, None, ei, attn_type="sparse")
+        twice = m(x, None, [ei, ei], attn_type="sparse")
+        half = m(x, None, [ei, None], attn_type="sparse")
+        views = GroupedHeadSubgraphProvider(2).build(ei, 4)                # 4 heads in 2 groups, edges split by source id
+        grouped = m(x, None, [views[0], views[2]], attn_type="sparse")
+    assert torch.allclose(single, twice, atol=1e-5)
+    assert torch.isfinite(half).all() and torch.isfinite(grouped).all()
+    # group-wise check at the attention module: heads 0-1 over set A, heads 2-3 over set B
+    core = next(iter(m.core_attention_modules()))
+    q, k, v = (torch.randn(1, n, 4, 8, generator=g) for _ in range(3))
+    a, b = views[0], views[2]
+    both = core(q, k, v, None, [a, b], "sparse").reshape(1, n, 4, 8)
+    only_a = core(q[:, :, :2].contiguous(), k[:, :, :2].contiguous(), v[:, :, :2].contiguous(), None, a, "sparse").reshape(1, n, 2, 8)
+    only_b = core(q[:, :, 2:].contiguous(), k[:, :, 2:].contiguous(), v[:, :, 2:].contiguous(), None, b, "sparse").reshape(1, n, 2, 8)
+    assert torch.allclose(both[:, :, :2], only_a, atol=1e-6) and torch.allclose(both[:, :, 2:], only_b, atol=1e-6)
+    missing = core(q, k, v, None, [a, None], "sparse").reshape(1, n, 4, 8)
+    assert torch.allclose(missing[:, :, :2], only_a, atol=1e-6) and float(missing[:, :, 2:].abs().sum()) == 0.0
+
+
+def test_graphormer_head_group_sets_with_dense_bias():
+    m, _ = _model("graphormer", ["--num_global_node", "0"])
+    core = next(iter(m.core_attention_modules()))
+    n = 10
+    g = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(1, n, 4, 8, generator=g) for _ in range(3))
+    ei = torch.cat([torch.randint(0, n, (2, 30), generator=g), torch.arange(n).repeat(2, 1)], 1)
+    bias = torch.randn(1, 4, n, n, generator=g)
+    one = core(q, k, v, bias, ei, "sparse")
+    two = core(q, k, v, bias, [ei, ei], "sparse")
+    assert torch.allclose(one, two, atol=1e-5)
+    assert not torch.allclose(one, core(q, k, v, None, ei, "sparse"), atol=1e-4)
