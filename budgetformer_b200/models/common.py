@@ -141,6 +141,27 @@ class SparseCoreAttention(nn.Module):
             self._track_sparse(q, k, graph, getattr(self, "edge_hops", None))
         return out.unsqueeze(0)
 
+    # ---- two-phase form of the sparse path (models/graphormer_dist_node_level.py:515-587): the edge weights need only
+    # q and k, so a caller can compute them while v is still in flight, then aggregate.  Plain PyTorch; the fused
+    # kernels keep both phases in one pass because their v arrives with q and k in one packed transfer.
+    def sparse_score_phase(self, q, k, edge_index, edge_bias=None):
+        """``exp(clamp(q.k / sqrt(hn), -5, 5) [+ bias])`` per edge and head, with what the second phase needs."""
+        graph = as_attn_graph(edge_index, q.size(1)).to(q.device)
+        src, dst = graph.col.to(torch.int64), graph.row_ids()
+        s = (k[0].float()[src] * q[0].float()[dst]).sum(-1) / self.scale
+        s = s.clamp(-5.0, 5.0)
+        if edge_bias is not None:
+            s = s + edge_bias.float()
+        return {"score": torch.exp(s), "src": src, "dst": dst, "num_nodes": q.size(1), "dtype": q.dtype}
+
+    def sparse_aggregate_phase(self, score_ctx, v):
+        """``sum_e w_e v_src(e) / (sum_e w_e + 1e-6)`` per query; returns ``[1, n, Hl, hn]``."""
+        w, src, dst, n = score_ctx["score"], score_ctx["src"], score_ctx["dst"], score_ctx["num_nodes"]
+        vv = v[0].float()
+        wv = torch.zeros(n, vv.size(1), vv.size(2), device=vv.device).index_add_(0, dst, vv[src] * w.unsqueeze(-1))
+        z = torch.zeros(n, vv.size(1), device=vv.device).index_add_(0, dst, w)
+        return (wv / (z.unsqueeze(-1) + 1e-6)).to(score_ctx["dtype"]).unsqueeze(0)
+
     def sparse_head_groups(self, q, k, v, edge_sets, edge_bias=None):
         """One edge set per head group (models/graphormer_dist_node_level.py:175-214, models/gt_dist_node_level.py:195-221):
         with G sets, consecutive blocks of ceil(Hl / G) local heads attend over set g; the heads of a missing or empty

@@ -197,3 +197,16 @@ def test_graphormer_head_group_sets_with_dense_bias():
     two = core(q, k, v, bias, [ei, ei], "sparse")
     assert torch.allclose(one, two, atol=1e-5)
     assert not torch.allclose(one, core(q, k, v, None, ei, "sparse"), atol=1e-4)
+
+
+def test_two_phase_sparse_attention_equals_one_pass():
+    m, _ = _model("graphormer", ["--num_global_node", "0"])
+    core = next(iter(m.core_attention_modules()))
+    n = 14
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(1, n, 4, 8, generator=g) for _ in range(3))
+    ei = torch.cat([torch.randint(0, n, (2, 50), generator=g), torch.arange(n - 2).repeat(2, 1)], 1)   # two queries without edges
+    ctx = core.sparse_score_phase(q, k, ei)
+    two = core.sparse_aggregate_phase(ctx, v).reshape(1, n, -1)
+    one = core(q, k, v, None, ei, "sparse")
+    assert torch.allclose(one, two, atol=1e-5)
