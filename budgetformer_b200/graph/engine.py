@@ -125,14 +125,14 @@ class EdgeEngine:
     # ------------------------------------------------------------------ policy
     def _initial_policy(self) -> str:
         dev = str(getattr(self.args, "edge_build_device", "gpu")).lower()
-        if self.device.type != "cuda" or dev == "cpu":
-            return "cpu_rank_local_prefetch"
+        if self.device.type != "cuda" or dev == "cpu" or self.fanout:
+            return "cpu_rank_local_prefetch"      # fan-out graphs are built by the C++ builder: prefetch hides it
         return "gpu_persist"
 
     def set_policy(self, policy: str, lock: bool = False) -> None:
         if policy not in EDGE_POLICY_CHOICES:
             raise ValueError(f"unknown edge policy {policy!r}")
-        if self.device.type != "cuda" and policy.startswith("gpu"):
+        if (self.device.type != "cuda" or self.fanout) and policy.startswith("gpu"):
             policy = "cpu_rank_local_prefetch"
         if policy != self.policy:
             self.clear_cache()
