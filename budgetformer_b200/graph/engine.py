@@ -30,7 +30,7 @@ import torch.distributed as dist
 from ..utils.comm_profiler import profile_call, record_scalar
 from .device_budget import BUDGET
 from .attn_graph import AttnGraph, Topology, add_virtual_node
-from .builder import build_attn_graph, graph_totals
+from .builder import build_attn_graph, graph_totals, native_supported
 
 EDGE_POLICY_CHOICES = ("gpu_persist", "gpu_ephemeral", "cpu_rank_local_prefetch", "cpu_broadcast_prefetch",
                        "cpu_broadcast")
@@ -278,7 +278,12 @@ class EdgeEngine:
         return topo
 
     def _build_device(self, seed: int, state: BudgetState) -> AttnGraph:
-        if self.fanout:                                 # fan-out sampling runs through the CPU specification
+        walks = int(getattr(self.args, "walks_per_node", 0))
+        br = 0 if not state.use_real else state.b_real
+        bw = 0 if (not state.use_rw or walks <= 0 or state.walk_length <= 0) else state.b_rw
+        if self.fanout or not native_supported(br, bw, state.walk_length):
+            # fan-out sampling, sides without budget and budgets beyond the fixed-width kernels are built by the general
+            # C++ builder from the host copy of the topology (no topology transfer in either direction)
             return self._upload(self._build_host(seed, state))
         topo = self._topology_on_device()
         return build_attn_graph(topo, state.b_real, state.b_rw, int(getattr(self.args, "walks_per_node", 0)),
