@@ -116,6 +116,8 @@ _EXTRA = [
     (("--watchdog_step_seconds",), float, 0.0, {"help": "with --watchdog_seconds: also abort when this rank itself has "
                                                         "not reached a step boundary for this long (a collective or "
                                                         "kernel over its deadline; 0 = off)"}),
+    (("--shard_cpu_edge_build",), _STORE_TRUE, False, {"help": "cpu_rank_local_prefetch policy: each rank builds the rows "
+                                                             "of its own queries and the shards are all-gathered"}),
     (("--nvtx",), _STORE_TRUE, False, {"help": "emit NVTX ranges for step phases and profiled calls"}),
     (("--debug_checks",), _STORE_TRUE, False, {"help": "validate every attention graph, poison reusable symmetric "
                                                "buffers after use and check losses/gradients for NaN (also BF_DEBUG=1)"}),

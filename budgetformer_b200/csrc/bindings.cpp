@@ -9,8 +9,9 @@
 extern "C" int bf_budget_select_cpu(const int*, const int*, const int*, const int*, int, int, int, int, int, int,
                                     long long, int, int*, uint8_t*, int*, unsigned long long*, int);
 extern "C" int bf_ell_to_csr_cpu(const int*, const uint8_t*, const int*, int, int, int*, uint8_t*);
-extern "C" int bf_build_rows_cpu(const int*, const int*, const int*, const int*, int, int, int, int, int, int, int, const int*,
-                                 int, int, long long, const long long*, long long*, int*, uint8_t*, unsigned long long*, int);
+extern "C" int bf_build_rows_cpu(const int*, const int*, const int*, const int*, int, int, int, int, int, int, int, int,
+                                 const int*, int, int, long long, const long long*, long long*, int*, uint8_t*,
+                                 unsigned long long*, int);
 
 namespace {
 
@@ -200,21 +201,26 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
 std::vector<Tensor> build_attn_graph_rows_cpu(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col,
                                               int64_t n, int64_t b_real, int64_t b_rw, bool use_real, bool use_rw,
                                               int64_t walks, int64_t walk_len, std::vector<int64_t> fanout,
-                                              bool exphormer, int64_t seed, int64_t num_threads) {
+                                              bool exphormer, int64_t seed, int64_t num_threads, int64_t row_begin,
+                                              int64_t row_end) {
   for (const Tensor* t : {&in_rowptr, &in_src, &out_rowptr, &out_col})
     TORCH_CHECK(!t->is_cuda() && t->scalar_type() == torch::kInt && t->is_contiguous(), "int32 contiguous CPU CSR expected");
   std::vector<int> fo(fanout.begin(), fanout.end());
-  Tensor counts = torch::zeros({n}, torch::kLong);
+  if (row_end < 0) row_end = n;                       // default: every query
+  TORCH_CHECK(0 <= row_begin && row_begin <= row_end && row_end <= n, "bad row range");
+  const int64_t rows = row_end - row_begin;
+  Tensor counts = torch::zeros({rows}, torch::kLong);
   Tensor totals = torch::zeros({2}, torch::kLong);
   auto run = [&](const long long* offsets, int* col, uint8_t* etype) {
-    bf_build_rows_cpu(iptr(in_rowptr), iptr(in_src), iptr(out_rowptr), iptr(out_col), (int)n, (int)b_real, (int)b_rw,
+    bf_build_rows_cpu(iptr(in_rowptr), iptr(in_src), iptr(out_rowptr), iptr(out_col), (int)row_begin, (int)row_end,
+                      (int)b_real, (int)b_rw,
                       use_real ? 1 : 0, use_rw ? 1 : 0, (int)walks, (int)walk_len, fo.data(), (int)fo.size(),
                       exphormer ? 1 : 0, seed, offsets, reinterpret_cast<long long*>(counts.data_ptr<int64_t>()), col, etype,
                       reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>()), (int)num_threads);
   };
   run(nullptr, nullptr, nullptr);
   Tensor incl = torch::cumsum(counts, 0);
-  const int64_t n_edges = n > 0 ? incl[n - 1].item<int64_t>() : 0;
+  const int64_t n_edges = rows > 0 ? incl[rows - 1].item<int64_t>() : 0;
   TORCH_CHECK(n_edges < (int64_t)INT32_MAX, "attention graph too large for int32 offsets: ", n_edges, " edges");
   Tensor offsets = (incl - counts).contiguous();
   auto iopt = torch::TensorOptions().dtype(torch::kInt);
@@ -222,7 +228,7 @@ std::vector<Tensor> build_attn_graph_rows_cpu(Tensor in_rowptr, Tensor in_src, T
   Tensor etype = exphormer ? torch::empty({n_edges}, iopt.dtype(torch::kUInt8)) : torch::empty({0}, iopt.dtype(torch::kUInt8));
   run(reinterpret_cast<const long long*>(offsets.data_ptr<int64_t>()), col.data_ptr<int>(),
       exphormer ? etype.data_ptr<uint8_t>() : nullptr);
-  Tensor rowptr = torch::zeros({n + 1}, iopt);
+  Tensor rowptr = torch::zeros({rows + 1}, iopt);
   rowptr.slice(0, 1).copy_(incl.to(torch::kInt));
   return {rowptr, col, etype, totals};
 }

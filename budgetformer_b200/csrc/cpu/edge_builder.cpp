@@ -203,12 +203,14 @@ extern "C" int bf_khop_fill_cpu(const int* out_rowptr, const int* out_col, int n
 // -----------------------------------------------------------------------------------------------------
 // General CPU build with rows of any length: budgets above the fixed-width limit of the CUDA builder and
 // "no budget" (b < 0: keep every candidate - the reference's default without budget flags, all real edges and
-// the whole walk pool).  Two passes over the queries: `offsets == nullptr` counts the row lengths, otherwise the
-// rows are written at their prefix-sum offsets.  Walk candidates come from Philox walks (n_hops == 0) or from
+// the whole walk pool).  Two passes over the queries [row_begin, row_end) - a rank may build only its own rows, they
+// do not depend on one another: `offsets == nullptr` counts the row lengths, otherwise the rows are written at
+// their prefix-sum offsets (counts and offsets are indexed from row_begin).  Walk candidates come from Philox walks (n_hops == 0) or from
 // the fan-out expansion (n_hops > 0).  Same selection and merge rules as the fixed-width builders above.
 // -----------------------------------------------------------------------------------------------------
 extern "C" int bf_build_rows_cpu(const int* in_rowptr, const int* in_src, const int* out_rowptr, const int* out_col,
-                                 int n, int b_real, int b_rw, int use_real, int use_rw, int walks, int walk_len,
+                                 int row_begin, int row_end, int b_real, int b_rw, int use_real, int use_rw, int walks,
+                                 int walk_len,
                                  const int* fanout, int n_hops, int exphormer, long long seed,
                                  const long long* offsets, long long* counts, int* col, uint8_t* etype,
                                  unsigned long long* totals, int num_threads) {
@@ -224,7 +226,7 @@ extern "C" int bf_build_rows_cpu(const int* in_rowptr, const int* in_src, const 
     std::vector<uint8_t> trow;
     KhopScratch scratch;
 #pragma omp for schedule(dynamic, 256)
-    for (int v = 0; v < n; ++v) {
+    for (int v = row_begin; v < row_end; ++v) {
       rc.clear();
       wc.clear();
       if (use_real && b_real != 0) {
@@ -258,9 +260,9 @@ extern "C" int bf_build_rows_cpu(const int* in_rowptr, const int* in_src, const 
       trow.resize(width);
       const int c = write_row(v, rc, wc, exphormer != 0, merged, row.data(), trow.data());
       if (offsets == nullptr) {
-        counts[v] = c;
+        counts[v - row_begin] = c;
       } else {
-        const long long o = offsets[v];
+        const long long o = offsets[v - row_begin];
         std::copy(row.begin(), row.begin() + c, col + o);
         if (exphormer) std::copy(trow.begin(), trow.begin() + c, etype + o);
       }

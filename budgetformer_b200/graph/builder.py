@@ -69,11 +69,13 @@ def build_attn_graph(
 
 
 def _build_rows_native(topo: Topology, b_real: Optional[int], b_rw: Optional[int], walks_per_node: int, walk_length: int,
-                       seed: int, use_real: bool, use_rw: bool, exphormer: bool, fanout, num_threads: int
-                       ) -> Optional[AttnGraph]:
+                       seed: int, use_real: bool, use_rw: bool, exphormer: bool, fanout, num_threads: int,
+                       rows: Optional[tuple] = None) -> Optional[AttnGraph]:
     """The cases the fixed-width builders do not take - a side without budget (``None``: every candidate) or above
     ``MAX_SIDE_BUDGET``, walks longer than ``MAX_WALK_LEN`` - on the general two-pass C++/OpenMP builder.  It runs on
-    the CPU copy of the topology (the specification it replaces does too); ``None`` without the extension."""
+    the CPU copy of the topology (the specification it replaces does too); ``None`` without the extension.
+    ``rows = (begin, end)`` builds only those queries: the result has ``end - begin`` rows (keys keep their global ids),
+    which is what a rank contributes to a sharded build (``build_attn_graph_shard``)."""
     try:
         from ..ops import _ext
         ext = _ext.load()
@@ -86,12 +88,30 @@ def _build_rows_native(topo: Topology, b_real: Optional[int], b_rw: Optional[int
     rowptr, col, etype, totals = ext.build_attn_graph_rows_cpu(
         i32(cpu.in_rowptr), i32(cpu.in_src), i32(cpu.out_rowptr), i32(cpu.out_col), int(topo.num_nodes),
         code(b_real), code(b_rw), bool(use_real), walk_side, int(walks_per_node), int(walk_length),
-        [int(f) if f is not None else -1 for f in (fanout or [])], bool(exphormer), int(seed), int(num_threads))
+        [int(f) if f is not None else -1 for f in (fanout or [])], bool(exphormer), int(seed), int(num_threads),
+        int(rows[0]) if rows else 0, int(rows[1]) if rows else -1)
     r, w = (int(x) for x in totals.tolist())
     bound = None
     if b_real is not None and b_rw is not None:
         bound = max(0, int(b_real)) + max(0, int(b_rw)) + (1 if exphormer else 0)
-    return AttnGraph(int(topo.num_nodes), rowptr, col, etype if exphormer else None, n_real=r, n_rw=w, max_degree=bound)
+    n_rows = int(rows[1] - rows[0]) if rows else int(topo.num_nodes)
+    return AttnGraph(n_rows, rowptr, col, etype if exphormer else None, n_real=r, n_rw=w, max_degree=bound)
+
+
+def build_attn_graph_shard(topo: Topology, rows: tuple, b_real: Optional[int], b_rw: Optional[int], walks_per_node: int,
+                           walk_length: int, seed: int, *, use_real: bool = True, use_rw: bool = True,
+                           exphormer: bool = False, num_threads: int = 0, fanout=None) -> AttnGraph:
+    """The rows ``[rows[0], rows[1])`` of the graph ``build_attn_graph`` would return, as a graph over those queries
+    only.  Rows are independent of one another, so the shards of all ranks concatenate to the full graph."""
+    g = _build_rows_native(topo, b_real, b_rw, walks_per_node, walk_length, seed, use_real, use_rw, exphormer, fanout,
+                           num_threads, rows=rows)
+    if g is not None:
+        return g
+    full = build_attn_graph_spec(topo, b_real, b_rw, walks_per_node, walk_length, seed, use_real=use_real,
+                                 use_rw=use_rw, exphormer=exphormer, fanout=fanout)          # no extension: cut it out
+    lo, hi = int(full.rowptr[rows[0]]), int(full.rowptr[rows[1]])
+    return AttnGraph(int(rows[1] - rows[0]), (full.rowptr[rows[0]:rows[1] + 1] - lo).contiguous(), full.col[lo:hi].contiguous(),
+                     None if full.etype is None else full.etype[lo:hi].contiguous(), max_degree=full.max_degree)
 
 
 def graph_totals(g: AttnGraph):
@@ -103,4 +123,4 @@ def graph_totals(g: AttnGraph):
     return g.n_real, g.n_rw
 
 
-__all__ = ["build_attn_graph", "graph_totals", "add_virtual_node", "native_supported"]
+__all__ = ["build_attn_graph", "build_attn_graph_shard", "graph_totals", "add_virtual_node", "native_supported"]

@@ -30,7 +30,7 @@ import torch.distributed as dist
 from ..utils.comm_profiler import profile_call, record_scalar
 from .device_budget import BUDGET
 from .attn_graph import AttnGraph, Topology, add_virtual_node
-from .builder import build_attn_graph, graph_totals, native_supported
+from .builder import build_attn_graph, build_attn_graph_shard, graph_totals, native_supported
 
 EDGE_POLICY_CHOICES = ("gpu_persist", "gpu_ephemeral", "cpu_rank_local_prefetch", "cpu_broadcast_prefetch",
                        "cpu_broadcast")
@@ -252,10 +252,25 @@ class EdgeEngine:
         self._dev_future = None
 
     # ------------------------------------------------------------------ builds
+    def sharded_host_build(self) -> bool:
+        """``--shard_cpu_edge_build`` under the rank-local CPU policy: every rank builds only the rows of its own
+        queries (1/P of the work, and the ranks of a node stop competing for the same cores) and the shards are
+        all-gathered on the training device.  Rows do not depend on one another, so the result is the same graph."""
+        return (bool(getattr(self.args, "shard_cpu_edge_build", False)) and self.world > 1
+                and self.policy == "cpu_rank_local_prefetch" and not self.force_broadcast
+                and self.num_nodes % self.world == 0)
+
     def _build_host(self, seed: int, state: BudgetState) -> AttnGraph:
-        g = build_attn_graph(self.topo_cpu, state.b_real, state.b_rw, int(getattr(self.args, "walks_per_node", 0)),
-                             state.walk_length, seed, use_real=state.use_real, use_rw=state.use_rw,
-                             exphormer=self.exphormer and self.expander_edges is None, fanout=self.fanout)
+        kw = dict(use_real=state.use_real, use_rw=state.use_rw, exphormer=self.exphormer and self.expander_edges is None,
+                  fanout=self.fanout)
+        walks = int(getattr(self.args, "walks_per_node", 0))
+        if self.sharded_host_build():
+            per = self.num_nodes // self.world
+            rows = (self.rank * per, (self.rank + 1) * per)
+            g = build_attn_graph_shard(self.topo_cpu, rows, state.b_real, state.b_rw, walks, state.walk_length, seed, **kw)
+            g.shard_rows = rows
+        else:
+            g = build_attn_graph(self.topo_cpu, state.b_real, state.b_rw, walks, state.walk_length, seed, **kw)
         graph_totals(g)
         if self.device.type == "cuda":
             for name in ("rowptr", "col", "etype"):
@@ -324,6 +339,44 @@ class EdgeEngine:
         etype = _bc(g.etype if is_src else None, (n_edges,), torch.uint8) if has_type else None
         return AttnGraph(n_rows, rowptr, col, etype, max_degree=None if maxdeg < 0 else maxdeg)
 
+    def _gather_shards(self, shard: AttnGraph) -> AttnGraph:
+        """All ranks hold the rows of their own queries; concatenate them in rank order on the collective's device
+        (sizes first, then row offsets, keys and types padded to the longest shard)."""
+        nccl = dist.get_backend(self.group) == "nccl"
+        dev = self.device if nccl else torch.device("cpu")
+        local = self._upload(shard) if dev.type == "cuda" else shard
+        p = self.world
+        sizes = torch.tensor([local.num_edges, max(local.n_real, 0), max(local.n_rw, 0),
+                              -1 if local.max_degree is None else local.max_degree], dtype=torch.int64, device=dev)
+        all_sizes = [torch.empty_like(sizes) for _ in range(p)]
+        dist.all_gather(all_sizes, sizes, group=self.group)
+        all_sizes = torch.stack(all_sizes).cpu()
+        edges = [int(v) for v in all_sizes[:, 0].tolist()]
+        longest = max(max(edges), 1)
+
+        def gather(t: torch.Tensor, length: int) -> list:
+            buf = torch.zeros(length, dtype=t.dtype, device=dev)
+            buf[: t.numel()] = t.to(dev)
+            out = [torch.empty_like(buf) for _ in range(p)]
+            dist.all_gather(out, buf, group=self.group)
+            return out
+
+        rowptrs = gather(local.rowptr, local.num_rows + 1)
+        cols = gather(local.col, longest)
+        types = gather(local.etype, longest) if local.etype is not None else None
+        offsets, total = [], 0
+        for e in edges:
+            offsets.append(total)
+            total += e
+        rowptr = torch.cat([rp[:-1] + off for rp, off in zip(rowptrs, offsets)]
+                           + [torch.tensor([total], dtype=torch.int32, device=dev)]).to(torch.int32)
+        col = torch.cat([c[:e] for c, e in zip(cols, edges)])
+        etype = torch.cat([t[:e] for t, e in zip(types, edges)]) if types is not None else None
+        degs = all_sizes[:, 3]
+        g = AttnGraph(self.num_nodes, rowptr, col, etype, n_real=int(all_sizes[:, 1].sum()), n_rw=int(all_sizes[:, 2].sum()),
+                      max_degree=None if bool((degs < 0).any()) else int(degs.max()))
+        return g if g.device == self.device else self._upload(g)
+
     def _finalize(self, g: AttnGraph) -> AttnGraph:
         """Model-specific assembly on the final device."""
         if self.exphormer and self.expander_edges is not None:
@@ -365,10 +418,13 @@ class EdgeEngine:
             if g.device != self.device:
                 g = self._upload(g)
         elif self.policy in _CPU_POLICIES or self.device.type != "cuda":
-            if host is None:
+            if host is None or (getattr(host, "shard_rows", None) is not None) != self.sharded_host_build():
                 host = profile_call("edge_build_local", lambda: self._build_host(seed, state), device="cpu")
                 self._store(key, host)
-            g = self._upload(host)
+            if getattr(host, "shard_rows", None) is not None:
+                g = profile_call("edge_shard_gather", lambda: self._gather_shards(host), device=self.device)
+            else:
+                g = self._upload(host)
         elif self._gpu_build_ruled_out(state):
             # proactive CPU build: the estimate does not fit under the registered memory cap, or the GPU build already
             # failed in this run; the caller reports it to the planner like a run-time failure

@@ -95,6 +95,33 @@ def mode_watchdog(out_path):
     os._exit(0)                                    # the peer is gone: skip the collective teardown
 
 
+def mode_shard(out_path):
+    """--shard_cpu_edge_build: the graph all-gathered from per-rank shards equals the graph one process builds, for the
+    plain, the typed (Exphormer), the virtual-node (Graphormer), the unbudgeted and the fan-out case; and training on
+    it runs (prefetch thread included)."""
+    from budgetformer_b200.graph.engine import resolve_budget_state
+    res = {}
+    cases = {"gt": [], "exphormer": [], "graphormer": [],
+             "gt_fanout": ["--rw_edge_mode", "dgl_neighbor", "--fanout", "3,2"]}
+    for name, extra in cases.items():
+        model = name.split("_")[0]
+        sharded = make(model, ["--shard_cpu_edge_build"] + extra)
+        assert sharded.edge_engine.sharded_host_build() == (sharded.sp_world > 1)
+        g = sharded.build_edges(1)
+        whole = make(model, extra)
+        w = whole.build_edges(1)
+        res[name] = {"equal": bool(torch.equal(g.rowptr, w.rowptr) and torch.equal(g.col, w.col)
+                                   and (g.etype is None or torch.equal(g.etype, w.etype))),
+                     "edges": g.num_edges, "totals": [g.n_real, g.n_rw], "totals_whole": [w.n_real, w.n_rw]}
+        sharded.edge_engine.shutdown()
+        whole.edge_engine.shutdown()
+    t = make("gt", ["--shard_cpu_edge_build", "--peak_lr", "5e-3"], n=1024)
+    best = t.fit()
+    res["fit"] = {"epochs": len(t.epoch_times), "valid": best["valid"]}
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        json.dump(res, open(out_path, "w"))
+
+
 def mode_syncbn(out_path):
     """--sync_batchnorm: training-mode GraphGPS on P ranks normalises with the statistics of all rows, so outputs and
     gradients equal the single-process run (which sees all rows in one BatchNorm call)."""
@@ -123,7 +150,8 @@ def mode_syncbn(out_path):
 
 if __name__ == "__main__":
     mode, out = sys.argv[1], sys.argv[2]
-    {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom, "syncbn": mode_syncbn, "watchdog": mode_watchdog}[mode](out)
+    {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom, "syncbn": mode_syncbn, "watchdog": mode_watchdog,
+     "shard": mode_shard}[mode](out)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

@@ -112,3 +112,15 @@ def test_watchdog_ends_a_step_that_exceeds_its_deadline(tmp_path):
     assert not os.path.exists(out + ".0") and not os.path.exists(out + ".1")
     assert "has not reached a step boundary" in r.stderr or "abort requested" in r.stderr, r.stderr[-2000:]
     assert "[watchdog] rank" in r.stderr
+
+
+def test_sharded_cpu_edge_build_equals_whole_build(tmp_path):
+    """Two gloo ranks each build the rows of their own queries; the all-gathered graph is the graph of a whole build
+    (typed, virtual-node and fan-out variants included) and a training run on it completes."""
+    out = str(tmp_path / "shard.json")
+    _spawn(2, "shard", out, 29811)
+    res = json.load(open(out))
+    for name in ("gt", "exphormer", "graphormer", "gt_fanout"):
+        assert res[name]["equal"], (name, res[name])
+        assert res[name]["totals"] == res[name]["totals_whole"], (name, res[name])
+    assert res["fit"]["epochs"] == 4 and 0.0 <= res["fit"]["valid"] <= 1.0
