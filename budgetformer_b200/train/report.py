@@ -29,7 +29,8 @@ def print_training_header(t) -> None:
           f"(padded {t.num_nodes:,}) edges={t.data.edge_index.size(1):,}")
     t.log(f"  layers={a.n_layers} hidden={a.hidden_dim} heads={a.num_heads} ffn={a.ffn_dim} classes={t.data.output_dim} "
           f"amp={a.amp_dtype} ckpt={a.activation_checkpoint_mode}")
-    t.log(f"  sp_world={t.sp_world} nodes/rank={t.nodes_per_rank:,} device={t.device} backend={a.distributed_backend} "
+    backend = dist.get_backend() if dist.is_initialized() else "none (single process)"
+    t.log(f"  sp_world={t.sp_world} nodes/rank={t.nodes_per_rank:,} device={t.device} backend={backend} "
           f"fused_sp={'on' if t.fused_sp else 'off'}")
     t.log(f"  edges: policy={t.edge_engine.policy} real={st.b_real if st.use_real else 0} "
           f"rw={st.b_rw if st.use_rw else 0} walk_length={st.walk_length} walks_per_node={a.walks_per_node} "
