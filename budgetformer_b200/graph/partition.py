@@ -3,9 +3,10 @@
 ``reformat_graph(edge_index, k)`` has the return contract of the reference (gt_sp/utils.py:787-819: edges relabelled
 and sorted by new source id, plus the old node ids in new order), and ``gen_sub_edge_index`` that of
 gt_sp/utils.py:761-773 (edges among the nodes of one batch, relabelled to positions in the batch).  The reference
-gets its partition from METIS through DGL; here it comes from the native partitioner (csrc/cpu/partition.cpp:
-breadth-first ordering from pseudo-peripheral roots cut into k ranges, refined by balance-constrained boundary
-moves), with a SciPy reverse-Cuthill-McKee ordering as the stand-in when the extension is not built.
+gets its partition from METIS through DGL; here it comes from the native multilevel partitioner
+(csrc/cpu/partition.cpp: heavy-edge-matching coarsening, breadth-first initial partition of the coarsest graph,
+balance-constrained boundary refinement at every level), with a SciPy reverse-Cuthill-McKee ordering as the stand-in
+when the extension is not built.
 """
 from __future__ import annotations
 
