@@ -116,6 +116,8 @@ _EXTRA = [
     (("--watchdog_step_seconds",), float, 0.0, {"help": "with --watchdog_seconds: also abort when this rank itself has "
                                                         "not reached a step boundary for this long (a collective or "
                                                         "kernel over its deadline; 0 = off)"}),
+    (("--locality_reorder_parts",), int, 0, {"help": "relabel nodes at load time into this many locality clusters "
+                                                     "(multilevel partition; 0 = keep the dataset's order)"}),
     (("--shard_cpu_edge_build",), _STORE_TRUE, False, {"help": "cpu_rank_local_prefetch policy: each rank builds the rows "
                                                              "of its own queries and the shards are all-gathered"}),
     (("--nvtx",), _STORE_TRUE, False, {"help": "emit NVTX ranges for step phases and profiled calls"}),

@@ -9,7 +9,8 @@ from __future__ import annotations
 import os
 import random
 import time
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
+from typing import Optional
 import numpy as np
 import torch
 
@@ -25,6 +26,7 @@ class GraphData:
     num_nodes: int          # before padding
     output_dim: int
     multilabel: bool = False
+    node_order: Optional[torch.Tensor] = None   # set by reorder_for_locality: original id of every (new) node id
 
 
 def random_split_idx(num_nodes: int, seed: int, frac_train: float = 0.6, frac_valid: float = 0.2) -> dict:
@@ -82,7 +84,28 @@ def load_data(args, dist_module=None) -> GraphData:
     if split is None:
         split = random_split_idx(n, args.seed)
     out_dim = int(y.size(1)) if multilabel else int(y.max().item()) + 1
-    return GraphData(x, y, edge_index, split, n, out_dim, multilabel)
+    data = GraphData(x, y, edge_index, split, n, out_dim, multilabel)
+    parts = int(getattr(args, "locality_reorder_parts", 0) or 0)
+    return reorder_for_locality(data, parts) if parts > 1 else data
+
+
+def reorder_for_locality(data: GraphData, parts: int, imbalance: float = 0.03) -> GraphData:
+    """``--locality_reorder_parts K``: relabel the nodes once, at load time, so that each of K clusters of the
+    multilevel partition (graph/partition.py) owns a contiguous id range.  Neighbours then sit close together in the
+    feature / key / value matrices, which is what the edge-attention gathers read; the model sees an isomorphic
+    graph, so accuracy is unaffected (the sampled attention edges differ, since their hash ranks node ids).
+    ``node_order[new] = old`` maps results back."""
+    from ..graph.partition import partition_assignment
+    n = int(data.num_nodes)
+    part = partition_assignment(data.edge_index, n, int(parts), imbalance)
+    old_of_new = torch.argsort(part, stable=True)
+    new_of_old = torch.empty(n, dtype=torch.long)
+    new_of_old[old_of_new] = torch.arange(n, dtype=torch.long)
+    tail = torch.arange(n, data.x.size(0), dtype=torch.long)           # padding rows (if any) stay at the end
+    rows = torch.cat([old_of_new, tail])
+    split = {k: new_of_old[v.long()] for k, v in data.split_idx.items()} if data.split_idx is not None else None
+    return replace(data, x=data.x[rows], y=data.y[rows], edge_index=new_of_old[data.edge_index.long()], split_idx=split,
+                   node_order=old_of_new)
 
 
 def pad_to_sequence_parallel_world(data: GraphData, world: int) -> GraphData:
@@ -96,7 +119,7 @@ def pad_to_sequence_parallel_world(data: GraphData, world: int) -> GraphData:
         y = torch.cat([data.y, data.y.new_zeros((pad, data.y.size(1)))], 0)
     else:
         y = torch.cat([data.y, data.y.new_full((pad,), -1)], 0)
-    return GraphData(x, y, data.edge_index, data.split_idx, data.num_nodes, data.output_dim, data.multilabel)
+    return replace(data, x=x, y=y)
 
 
 def _bidirected_self_loop_coo(edge_index: torch.Tensor, n: int):
@@ -162,7 +185,7 @@ def preprocess_hop_features(args, data: GraphData, rank: int = 0) -> GraphData:
     flat = mh.reshape(mh.size(0), -1)
     if n_pad > flat.size(0):
         flat = torch.cat([flat, flat.new_zeros(n_pad - flat.size(0), flat.size(1))], 0)
-    return GraphData(flat, data.y, data.edge_index, data.split_idx, data.num_nodes, data.output_dim, data.multilabel)
+    return replace(data, x=flat)
 
 
 def generate_expander_edges(num_nodes: int, degree: int, seed: int = 0) -> torch.Tensor:

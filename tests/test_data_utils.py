@@ -135,3 +135,34 @@ def test_memory_mapped_load_matches_plain_load(tmp_path):
     old = str(tmp_path / "old.pt")
     torch.save(x, old, _use_new_zipfile_serialization=False)          # cannot be mapped: falls back to a plain load
     assert torch.equal(safe_torch_load(old, mmap=True), x)
+
+
+def test_locality_reordering_is_an_isomorphism(tmp_path):
+    import types
+    from budgetformer_b200.graph.partition import edge_cut
+    from budgetformer_b200.graph.synthetic import sbm_graph, write_dataset
+    from budgetformer_b200.train.data import load_data, reorder_for_locality
+    n = 1200
+    x, y, ei = sbm_graph(n, blocks=4, p_in=0.03, p_out=0.001, feat_dim=6, seed=2)
+    perm = torch.randperm(n, generator=torch.Generator().manual_seed(1))      # hide the block structure in the ids
+    inv = torch.empty(n, dtype=torch.long)
+    inv[perm] = torch.arange(n)
+    write_dataset(str(tmp_path), "g", x[inv], y[inv], perm[ei])
+    ns = lambda k: types.SimpleNamespace(dataset_dir=str(tmp_path), dataset="g", force_random_split=True, seed=3,
+                                         locality_reorder_parts=k)
+    plain, re = load_data(ns(0)), load_data(ns(4))
+    assert plain.node_order is None and torch.equal(torch.sort(re.node_order).values, torch.arange(n))
+    # features, labels and splits follow their nodes
+    assert torch.equal(re.x, plain.x[re.node_order]) and torch.equal(re.y, plain.y[re.node_order])
+    for k in plain.split_idx:
+        assert torch.equal(torch.sort(re.node_order[re.split_idx[k]]).values, torch.sort(plain.split_idx[k]).values)
+    # the same edge set in the old ids
+    back = re.node_order[re.edge_index]
+    assert torch.equal(torch.unique(back[0] * n + back[1]), torch.unique(plain.edge_index[0] * n + plain.edge_index[1]))
+    # contiguous id ranges are now clusters: far fewer edges cross the four ranges
+    ranges = lambda m: torch.arange(m) * 4 // m
+    assert edge_cut(re.edge_index, ranges(n)) < 0.25 * edge_cut(plain.edge_index, ranges(n))
+    # padded rows stay where they are
+    padded = pad_to_sequence_parallel_world(plain, 7)
+    again = reorder_for_locality(padded, 4)
+    assert again.x.size(0) == padded.x.size(0) and float(again.x[n:].abs().sum()) == 0.0
