@@ -118,6 +118,8 @@ _EXTRA = [
                                                         "kernel over its deadline; 0 = off)"}),
     (("--locality_reorder_parts",), int, 0, {"help": "relabel nodes at load time into this many locality clusters "
                                                      "(multilevel partition; 0 = keep the dataset's order)"}),
+    (("--edge_build_threads",), int, 0, {"help": "OpenMP threads of a host-side edge build (0 = usable cores / ranks "
+                                                 "on this node)"}),
     (("--shard_cpu_edge_build",), _STORE_TRUE, False, {"help": "cpu_rank_local_prefetch policy: each rank builds the rows "
                                                              "of its own queries and the shards are all-gathered"}),
     (("--nvtx",), _STORE_TRUE, False, {"help": "emit NVTX ranges for step phases and profiled calls"}),

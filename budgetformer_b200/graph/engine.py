@@ -18,6 +18,7 @@ need no communication; broadcast exists for parity and for ``--force_edge_broadc
 """
 from __future__ import annotations
 
+import os
 import threading
 import time
 from concurrent.futures import Future, ThreadPoolExecutor
@@ -121,6 +122,21 @@ class EdgeEngine:
         self.last_prefetch_wait_s = 0.0
         self.last_graph_bytes = 0
         self.gpu_build_failed = False
+        self.build_threads = self._resolve_build_threads()
+
+    def _resolve_build_threads(self) -> int:
+        """OpenMP threads of a host-side build: ``--edge_build_threads`` or the cores this process may use divided by
+        the ranks on this node.  Launchers export OMP_NUM_THREADS=1 for multi-process jobs, which would otherwise
+        make every host build single-threaded."""
+        n = int(getattr(self.args, "edge_build_threads", 0) or 0)
+        if n > 0:
+            return n
+        try:
+            cores = len(os.sched_getaffinity(0))
+        except (AttributeError, OSError):
+            cores = os.cpu_count() or 1
+        local = int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0) or max(1, self.world)
+        return max(1, cores // max(1, local))
 
     # ------------------------------------------------------------------ policy
     def _initial_policy(self) -> str:
@@ -262,7 +278,7 @@ class EdgeEngine:
 
     def _build_host(self, seed: int, state: BudgetState) -> AttnGraph:
         kw = dict(use_real=state.use_real, use_rw=state.use_rw, exphormer=self.exphormer and self.expander_edges is None,
-                  fanout=self.fanout)
+                  fanout=self.fanout, num_threads=self.build_threads)
         walks = int(getattr(self.args, "walks_per_node", 0))
         if self.sharded_host_build():
             per = self.num_nodes // self.world
