@@ -201,7 +201,7 @@ void rebalance(const Graph& g, int k, double eps, std::vector<int>& part) {
   for (int v = 0; v < g.n; ++v) size[part[v]] += g.vw[v];
   const long long max_size = (long long)((1.0 + eps) * (double)g.total_vw / k) + 1;
   std::vector<long long> conn(k, 0);
-  for (int round = 0; round < 4; ++round) {
+  for (int sweep = 0; sweep < 4; ++sweep) {
     bool over = false;
     for (int p = 0; p < k; ++p) over |= size[p] > max_size;
     if (!over) return;

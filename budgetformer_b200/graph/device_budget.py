@@ -94,7 +94,7 @@ class DeviceBuildBudget:
         self._logged.clear()
 
     def clear_decision_log(self) -> None:
-        """Forget which decisions were already printed (called before a new round of policy profiling)."""
+        """Forget which decisions were already printed (called before the policies are profiled again)."""
         self._logged.clear()
 
     # ---- the decision -----------------------------------------------------------------------------
