@@ -133,6 +133,8 @@ class StepWatchdog:
             # give the main thread one deadline to notice at its next check(); if it is stuck in a collective, end the job
             if waited_since is None:
                 waited_since = time.monotonic()
+                # said at once: a launcher that notices the dead rank first may end this process before the grace is over
+                print(f"[watchdog] rank {self.rank}: {self._lost}", file=sys.stderr, flush=True)
                 try:
                     self.store.set("abort", self._lost)
                 except Exception:
