@@ -207,10 +207,12 @@ def main(argv=None):
     ap.add_argument("--sequences", choices=["none", "ppr", "rand"], default="none")
     ap.add_argument("--k1", type=int, default=100)
     a = ap.parse_args(argv)
-    print("wrote", get_dataset(a.dataset, a.dataset_dir, a.split_id, a.seed))
+    path = get_dataset(a.dataset, a.dataset_dir, a.split_id, a.seed)
+    print("wrote", path)
     if a.sequences != "none":
         fn = process_data if a.sequences == "ppr" else rand_nodes_seq
-        print("wrote", fn(a.dataset_dir, a.dataset, a.k1, seed=a.seed))
+        root, name = os.path.split(os.path.normpath(path))          # the folder written above (synthetic:<x> -> <x>)
+        print("wrote", fn(root, name, a.k1, seed=a.seed))
 
 
 if __name__ == "__main__":

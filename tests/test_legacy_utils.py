@@ -196,3 +196,11 @@ def test_legacy_sequence_files(tmp_path):
     powers = pd.power_adjacency_list(norm, 6)
     xi, yi, b = L.get_batch(args, torch.randn(n, 4), s % 3, recs[0][0][1], powers)
     assert torch.allclose(b, recs[0][0][0])
+
+
+def test_preprocess_cli_writes_sequence_files(tmp_path):
+    import os
+    from budgetformer_b200.utils import preprocess_data as pd
+    pd.main(["--dataset", "synthetic:sbm2k", "--dataset_dir", str(tmp_path), "--sequences", "rand", "--k1", "512"])
+    recs = torch.load(os.path.join(str(tmp_path), "sbm2k", "data_rand512.pt"))
+    assert len(recs) == 4 and recs[0][0][0].shape == (512, 512, 6)
