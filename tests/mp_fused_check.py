@@ -32,7 +32,31 @@ def trainer(model, fused, extra=()):
     return FullGraphTrainer(parse_fullgraph_args(argv + list(extra)), data=data, log=lambda *a, **k: None)
 
 
+def check_sharded_host_build():
+    """--shard_cpu_edge_build over NCCL: the graph all-gathered from the per-rank shards (device tensors) equals the
+    graph every rank builds whole, for a plain and a typed (Exphormer) model."""
+    for model in ("gt", "exphormer"):
+        whole = trainer(model, fused=False, extra=["--edge_build_device", "cpu"])
+        shard = trainer(model, fused=False, extra=["--edge_build_device", "cpu", "--shard_cpu_edge_build"])
+        assert shard.edge_engine.sharded_host_build() and not whole.edge_engine.sharded_host_build()
+        a, b = whole.build_edges(1), shard.build_edges(1)
+        torch.cuda.synchronize()
+        assert b.rowptr.is_cuda and torch.equal(a.rowptr, b.rowptr) and torch.equal(a.col, b.col), f"{model}: graphs differ"
+        assert a.etype is None or torch.equal(a.etype, b.etype)
+        loss = shard.train_step(1)["loss"]
+        assert loss == loss
+        whole.edge_engine.shutdown()
+        shard.edge_engine.shutdown()
+    if dist.get_rank() == 0:
+        print("OK sharded host build", flush=True)
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "sharded_build":
+        check_sharded_host_build()
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     models = sys.argv[1].split(",") if len(sys.argv) > 1 else ["gt"]
     first = trainer(models[0], fused=False)
     rank, world, dev = first.rank, first.sp_world, first.device

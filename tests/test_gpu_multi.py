@@ -42,6 +42,15 @@ def test_fused_path_two_gpus_narrow_column_slices():
     assert r.stdout.count("OK ") == 2, r.stdout[-2000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_cpu_edge_build_two_gpus():
+    """Each rank builds the rows of its own queries on the CPU; the shards are all-gathered as device tensors over NCCL
+    and give the graph of a whole build."""
+    r = _run(2, "sharded_build", 29616)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "OK sharded host build" in r.stdout, r.stdout[-2000:]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_fused_path_four_gpus():
     r = _run(4, "gt,graphormer", 29613)
