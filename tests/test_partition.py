@@ -123,3 +123,14 @@ def test_multilevel_partition_recovers_planted_communities():
     sizes = torch.bincount(part, minlength=blocks)
     assert int(sizes.max()) <= int(1.03 * n / blocks) + 1 and int(sizes.min()) >= int(0.97 * n / blocks) - 1
     assert P.edge_cut(ei, part) <= 1.1 * P.edge_cut(ei, truth)
+
+
+def test_host_bench_cases_run(capsys):
+    import json
+    from budgetformer_b200.utils import host_bench
+    host_bench.main(["build", "--nodes", "3000", "--edges", "12000", "--iters", "1", "--spec"])
+    host_bench.main(["partition", "--nodes", "4000", "--parts", "4"])
+    lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert len(lines) == 8 and all(l["seconds"] >= 0 for l in lines)
+    assert all(l["identical"] for l in lines if "identical" in l)
+    assert lines[-2]["cut"] < lines[-2]["cut_id_order"]
