@@ -204,3 +204,24 @@ def test_preprocess_cli_writes_sequence_files(tmp_path):
     pd.main(["--dataset", "synthetic:sbm2k", "--dataset_dir", str(tmp_path), "--sequences", "rand", "--k1", "512"])
     recs = torch.load(os.path.join(str(tmp_path), "sbm2k", "data_rand512.pt"))
     assert len(recs) == 4 and recs[0][0][0].shape == (512, 512, 6)
+
+
+def test_hop_buckets_feed_the_per_head_group_attention_path():
+    """Legacy per-head subgraphs end to end: random-walk hop buckets -> hop-mapped head views -> a GT forward whose
+    head groups attend over their own bucket."""
+    from budgetformer_b200.config import parse_fullgraph_args
+    from budgetformer_b200.graph.legacy_samplers import HopMappedHeadSubgraphProvider
+    from budgetformer_b200.train.engine import build_model
+    topo, ei = _ring_topology(32)
+    n = topo.num_nodes
+    buckets = L.compute_hops_random_walk(topo, walk_length=4, walks_per_node=2, num_groups=2, seed=4)
+    loops = torch.arange(n).repeat(2, 1)
+    # walk edges are (start, reached): the start node is the query, so flip them into (key, query) and add self loops
+    buckets = [torch.cat([b.flip(0), loops], 1) for b in buckets]
+    views = HopMappedHeadSubgraphProvider([0, 1], 2).build(buckets, 4)
+    assert len(views) == 4 and views[0] is views[1] and views[2] is views[3] and views[0] is not views[2]
+    a = parse_fullgraph_args(["--dataset", "x", "--model", "gt", "--n_layers", "1", "--hidden_dim", "32", "--num_heads", "4"])
+    m = build_model(a, 6, 3).eval()
+    with torch.no_grad():
+        out = m(torch.randn(n, 6), None, [views[0], views[2]], attn_type="sparse")
+    assert out.shape == (n, 3) and torch.isfinite(out).all()
