@@ -3,7 +3,8 @@ global-token plumbing, per-group random-walk subgraphs and the attention-graph s
 
 Restates, on this package's containers, the helper families of the reference's utility library
 (gt_sp/utils.py): ``fixed_random_seed[_cpu]`` (:497-537), the ``pad_*`` family (:620-743), ``get_batch`` (:822-866),
-``compute_hops_random_walk`` (:1013-1071), ``compute_group_nodes_random_walk`` (:1476-1536),
+``compute_hops_random_walk`` (:1013-1071), ``compute_hop_buckets_random_walk`` / ``build_head_hop_edges`` (:1074-1278),
+``compute_group_nodes_random_walk`` (:1476-1536),
 ``get_batch_papers100m`` / ``get_batch_from_loader[_malnet]`` (:2082-2233), ``split_tensor_along_second_dim`` /
 ``merge_global_token[0]`` / ``extend_global_token[0]`` (:2236-2362), ``broadcast_data`` (:2389-2406) and
 ``check_conditions`` (:2494-2515; here on SciPy's connected components, the reference's version needs a module it
@@ -313,6 +314,26 @@ def compute_hops_random_walk(topo: Topology, walk_length: int = 6, walks_per_nod
         if fresh.any():
             out[g].append(np.stack([src[fresh], dst[fresh]]))
     return [torch.from_numpy(np.concatenate(e, 1)) if e else torch.zeros(2, 0, dtype=torch.long) for e in out]
+
+
+def compute_hop_buckets_random_walk(topo: Topology, num_buckets: int, walk_length: int = 4, walks_per_node: int = 2,
+                                    min_hop: int = 1, seed: int = 0) -> List[torch.Tensor]:
+    """The walk edges ``(node reached at hop d, start node)`` grouped by hop: bucket ``min(d - 1, num_buckets - 1)``
+    holds hop d, for d from ``min_hop`` (2 = only nodes at least two steps away) to ``walk_length``
+    (gt_sp/utils.py:1074-1248).  Row 0 is the key / value node, row 1 the query, as attention expects."""
+    length, buckets = max(1, int(walk_length)), max(1, int(num_buckets))
+    walks = random_walks(topo, max(1, int(walks_per_node)), length, seed)
+    out: List[List[np.ndarray]] = [[] for _ in range(buckets)]
+    for d in range(max(1, int(min_hop)), length + 1):
+        ok = _emitted(walks, d)
+        out[min(d - 1, buckets - 1)].append(np.stack([walks[ok, d], walks[ok, 0]]))
+    return [torch.from_numpy(np.concatenate(e, 1)) if e else torch.zeros(2, 0, dtype=torch.long) for e in out]
+
+
+def build_head_hop_edges(topo: Topology, walk_length: int = 4, walks_per_node: int = 2, min_hop: int = 1,
+                         seed: int = 0) -> torch.Tensor:
+    """One walk-edge pool shared by all heads (gt_sp/utils.py:1251-1278): the single bucket of the function above."""
+    return compute_hop_buckets_random_walk(topo, 1, walk_length, walks_per_node, min_hop, seed)[0]
 
 
 def compute_group_nodes_random_walk(topo: Topology, walk_length: int = 6, walks_per_node: int = 2, num_groups: int = 4,

@@ -225,3 +225,17 @@ def test_hop_buckets_feed_the_per_head_group_attention_path():
     with torch.no_grad():
         out = m(torch.randn(n, 6), None, [views[0], views[2]], attn_type="sparse")
     assert out.shape == (n, 3) and torch.isfinite(out).all()
+
+
+def test_hop_buckets_and_shared_pool_match_the_builder_candidates():
+    import numpy as np
+    from budgetformer_b200.graph.builder_spec import random_walks, rw_candidates
+    topo, _ = _ring_topology(40)
+    pool = L.build_head_hop_edges(topo, walk_length=4, walks_per_node=2, seed=9)
+    src, dst = rw_candidates(random_walks(topo, 2, 4, 9))               # what the full-graph builder samples from
+    key = lambda s, d: np.sort(np.asarray(d) * 40 + np.asarray(s))
+    assert np.array_equal(key(pool[0].numpy(), pool[1].numpy()), key(src, dst))
+    buckets = L.compute_hop_buckets_random_walk(topo, 3, walk_length=4, walks_per_node=2, seed=9)
+    assert len(buckets) == 3 and sum(b.size(1) for b in buckets) == pool.size(1)
+    far = L.build_head_hop_edges(topo, walk_length=4, walks_per_node=2, min_hop=2, seed=9)
+    assert far.size(1) == pool.size(1) - buckets[0].size(1)             # hop 1 left out
