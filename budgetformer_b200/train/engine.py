@@ -672,9 +672,20 @@ class FullGraphTrainer:
         if self._budget_frozen_notified or not self.controller.frozen:
             return
         self._budget_frozen_notified = True
+        self._release_probe_memory()
         self.model.comm_aware_notify_budget_frozen(reuse_deferred_baseline=True)
         if self.planner is not None and not self.edge_engine.policy_locked:
             self.profile_edge_policies()
+
+    def _release_probe_memory(self) -> None:
+        """The budget search is over: drop the host-side graphs it left in the cache and hand freed heap pages back to
+        the system, so that the resident set the planner calibrates against is the steady-state one
+        (``_release_probe_caches_on_freeze``, utils/fullgraph_sp_support.py:3142-3168)."""
+        import gc
+        from ..utils.misc import glibc_malloc_trim
+        self.edge_engine.clear_cache()
+        gc.collect()
+        glibc_malloc_trim()
 
     def profile_edge_policies(self) -> None:
         """Measure each placement policy once (cold + warm build with a bumped seed) and hand the profiles to
