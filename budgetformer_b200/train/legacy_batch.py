@@ -28,6 +28,17 @@ def induced_subgraph(edge_index: torch.Tensor, idx: torch.Tensor, num_nodes: int
     return torch.stack([s[m], d[m]], 0)
 
 
+def map_global_nodes_to_local(nodes_global: torch.Tensor, sampled_nodes: torch.Tensor) -> torch.Tensor:
+    """Position in ``sampled_nodes`` of every id of ``nodes_global`` (which must all be sampled) by binary search over
+    the sorted sample: no table of the size of the whole graph is needed (gt_sp/utils.py:939-948)."""
+    sample, ids = sampled_nodes.long(), nodes_global.long()
+    if ids.numel() == 0:
+        return torch.empty(0, dtype=torch.long, device=sample.device)
+    ordered, order = torch.sort(sample)
+    pos = torch.searchsorted(ordered, ids).clamp_(max=max(int(ordered.numel()) - 1, 0))
+    return order[pos]
+
+
 def reorder_by_partition(edge_index: torch.Tensor, idx: torch.Tensor, num_nodes: int, k: int) -> torch.Tensor:
     """``idx`` permuted so that the k parts of its induced subgraph are contiguous.  The partitioner is
     deterministic, so every rank computes the same order and nothing is broadcast."""

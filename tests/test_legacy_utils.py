@@ -239,3 +239,10 @@ def test_hop_buckets_and_shared_pool_match_the_builder_candidates():
     assert len(buckets) == 3 and sum(b.size(1) for b in buckets) == pool.size(1)
     far = L.build_head_hop_edges(topo, walk_length=4, walks_per_node=2, min_hop=2, seed=9)
     assert far.size(1) == pool.size(1) - buckets[0].size(1)             # hop 1 left out
+
+
+def test_map_global_nodes_to_local():
+    from budgetformer_b200.train.legacy_batch import map_global_nodes_to_local
+    sample = torch.tensor([40, 7, 19, 3])
+    assert map_global_nodes_to_local(torch.tensor([3, 40, 19, 19, 7]), sample).tolist() == [3, 0, 2, 2, 1]
+    assert map_global_nodes_to_local(torch.zeros(0, dtype=torch.long), sample).numel() == 0
