@@ -73,10 +73,17 @@ def case_gemm(a):
     gemm.check_status(dev)
 
 
-def _graph(nodes, degree, seed=0):
+def _graph(nodes, degree, seed=0, key_window=0):
+    """``degree`` keys per query, uniform over all nodes, or (``key_window > 0``) within that many ids of the query:
+    the gather pattern of a graph whose nodes were relabelled by locality (``--locality_reorder_parts``)."""
     from ..graph.attn_graph import AttnGraph
     g = torch.Generator(device="cuda").manual_seed(seed)
-    col = torch.randint(0, nodes, (nodes * degree,), device="cuda", generator=g, dtype=torch.int32)
+    if key_window > 0:
+        rows = torch.arange(nodes, device="cuda", dtype=torch.int64).repeat_interleave(degree)
+        off = torch.randint(-int(key_window), int(key_window) + 1, (nodes * degree,), device="cuda", generator=g)
+        col = ((rows + off) % nodes).to(torch.int32)
+    else:
+        col = torch.randint(0, nodes, (nodes * degree,), device="cuda", generator=g, dtype=torch.int32)
     rowptr = torch.arange(0, nodes * degree + 1, degree, device="cuda", dtype=torch.int32)
     return AttnGraph(nodes, rowptr, col, None, max_degree=degree).ensure_transpose()
 
@@ -84,7 +91,7 @@ def _graph(nodes, degree, seed=0):
 def case_attn(a):
     from ..ops.edge_attention import edge_attention
     n, hl, hn = a.nodes, a.heads, a.head_dim
-    g = _graph(n, a.degree)
+    g = _graph(n, a.degree, key_window=a.key_window)
     qkv = torch.randn(n, 3, hl, hn, device="cuda").bfloat16()
     q, k, v = (qkv[:, i].detach().requires_grad_(True) for i in range(3))
     e = n * a.degree
@@ -251,6 +258,8 @@ def main(argv=None):
             p.add_argument("--heads", type=int, default=8)
             p.add_argument("--head_dim", type=int, default=16)
             p.add_argument("--degree", type=int, default=8)
+            p.add_argument("--key_window", type=int, default=0,
+                           help="keys within this many ids of the query (0 = uniform over all nodes)")
         elif name == "sp":
             p.add_argument("--nodes", type=int, default=2_923_920)
             p.add_argument("--hidden", type=int, default=128)
