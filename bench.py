@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--fused_sp", default="auto")
     ap.add_argument("--ckpt", default="", help="activation checkpoint mode (default none = retain everything)")
     ap.add_argument("--no_e2e", action="store_true")
+    ap.add_argument("--kernel_events", type=int, default=0,
+                    help="after the timed loops run this many extra steps with CUDA events around every call into the "
+                         "extension and print rank 0's per-kernel device times (a breakdown, not a benchmark value)")
     return ap.parse_args()
 
 
@@ -190,6 +193,9 @@ def run_ours(ns):
         e2e_ms = start.elapsed_time(end)
     if rank == 0:
         sampler.stop()
+    if ns.kernel_events > 0:
+        _kernel_breakdown(ns, trainer, epoch, sync, rank, world)
+        epoch += ns.kernel_events
     peak = torch.cuda.max_memory_allocated(dev) / 2 ** 20
     vals = torch.tensor([ms, e2e_ms or 0.0, peak], dtype=torch.float64, device=dev)
     if world > 1:
@@ -225,6 +231,43 @@ def run_ours(ns):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _kernel_breakdown(ns, trainer, epoch, sync, rank, world):
+    """Per-entry-point device time of ``ns.kernel_events`` steps on rank 0 (CUDA-event pairs around every call into
+    the extension; the device barriers' time is the wait for the slowest rank).  Written to stderr."""
+    import torch
+
+    from budgetformer_b200.ops import _ext
+    _ext.enable_kernel_events(True)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    t0 = time.perf_counter()
+    start.record()
+    host_s = 0.0
+    for _ in range(ns.kernel_events):
+        epoch += 1
+        h0 = time.perf_counter()
+        trainer.train_step(epoch, read_loss=False)
+        host_s += time.perf_counter() - h0
+    end.record()
+    sync()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    table = _ext.kernel_event_summary()
+    _ext.enable_kernel_events(False)
+    if rank != 0:
+        return
+    k = ns.kernel_events
+    step_ms = start.elapsed_time(end) / k
+    rows = sorted(table.items(), key=lambda kv: -kv[1][1])
+    total = sum(ms for _c, ms in table.values()) / k
+    print(f"[kernel_events] world={world} step={step_ms:.3f} ms (events on), host time in train_step={host_s / k * 1e3:.3f} ms, "
+          f"wall={wall_ms / k:.3f} ms, sum of bracketed calls={total:.3f} ms (side-stream graph build included)",
+          file=sys.stderr)
+    print("[kernel_events] | share of step | ms/step | calls/step | entry point |", file=sys.stderr)
+    for name, (calls, ms) in rows:
+        print(f"[kernel_events] | {ms / k / step_ms:6.1%} | {ms / k:8.3f} | {calls / k:6.1f} | {name} |", file=sys.stderr)
+    sys.stderr.flush()
 
 
 def run_reference(ns):

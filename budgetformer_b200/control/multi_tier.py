@@ -1,21 +1,26 @@
 """Multi-Tier Execution Planner: profile -> plan -> execute under an HBM cap.
 
-Jointly chooses (a) where the per-epoch attention graph is built (``gpu_persist`` |
-``gpu_ephemeral`` | ``cpu_rank_local_prefetch`` | ``cpu_broadcast_prefetch``) and (b) a per-layer
-activation layout ``[recompute]*a + [keep_mha]*b + [retain]*c``.  The state machine, the cost /
-memory model and the public methods follow the reference's ``gt_sp/multi_tier.py``
-(``_MultiTierResourceManager`` :60-1562): DEFERRED -> WARMUP_RECOMPUTE -> CALIBRATE_MHA
-[-> MHA_FRONT] -> CALIBRATE_RETAIN [-> RETAIN_FRONT] -> ACTIVE.
+Jointly chooses (a) where the per-epoch attention graph is built (``gpu_persist`` | ``gpu_ephemeral`` |
+``cpu_rank_local_prefetch`` | ``cpu_broadcast_prefetch``) and (b) a per-layer activation layout
+``[recompute]*a + [keep_mha]*b + [retain]*c``.  It behaves like the reference's planner
+(gt_sp/multi_tier.py:60-1562): phases DEFERRED -> WARMUP_RECOMPUTE -> CALIBRATE_MHA [-> MHA_FRONT] ->
+CALIBRATE_RETAIN [-> RETAIN_FRONT] -> ACTIVE, one probed layer per calibration step, then a search over
+(policy, layout) for the fastest estimated step that fits.
 
-Re-grounding for B200: memory is read through a ``MemoryProbe`` so that (1) bytes held in
-symmetric (peer-mapped) buffers, which live outside PyTorch's caching allocator, are charged to the
-plan, and (2) the whole state machine runs on a CPU box against a scripted probe.  Cross-rank
-agreement uses one packed MAX all-reduce per step instead of one blocking call per scalar.
+Structure.  Measurements are immutable records (``StepReading``, ``TierProbe``, ``Calibration``, ``EdgeCost``);
+the phase order is a table (``_PHASE_PROBE``) read by ``advance``; the cost model is a set of pure functions
+(``tier_costs``, ``layout_bytes``, ``layout_times``, ``search_plans``) that take those records as data, so the
+decision tables can be tested without a device.  ``ExecutionPlanner`` is the object the model and the trainer
+talk to: it reads memory through a ``MemoryProbe`` (which adds peer-mapped symmetric buffers that live outside
+PyTorch's caching allocator, and can be scripted on a CPU box), MAX-reduces each step's readings over the ranks
+in one packed collective, and installs what ``search_plans`` returns.
 """
 from __future__ import annotations
 
 import os
-from typing import Callable, Dict, List, Optional, Sequence
+import enum
+from dataclasses import dataclass, field, replace
+from typing import Callable, Dict, Iterator, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -35,8 +40,9 @@ EDGE_POLICY_ORDER = (EDGE_GPU_PERSIST, EDGE_GPU_EPHEMERAL, EDGE_CPU_RANK_LOCAL_P
 TIER_IDS = {T0_RECOMPUTE: 0, T1_KEEP_MHA: 1, T4_RETAIN: 2}
 TIER_FROM_ID = {v: k for k, v in TIER_IDS.items()}
 
-_FRAG_FACTOR = 0.05          # per additional kept layer (reference :1064)
-_RECONSIDER_THRESHOLD_S = 0.5
+FRAGMENTATION_PER_EXTRA_LAYER = 0.05   # each kept layer beyond the first inflates the per-layer bytes by this much
+SWITCH_TO_GPU_AFTER_WAIT_S = 0.5       # a CPU policy is reconsidered when its wait exceeds a GPU build by this
+HEADROOM = 0.1                         # fraction of the (capped) device memory the plan must leave free
 
 
 class MemoryProbe:
@@ -116,308 +122,428 @@ def _sync_max(values: Sequence[float], device) -> List[float]:
     return [float(x) for x in t.tolist()]
 
 
-class _MultiTierResourceManager:
-    T0_RECOMPUTE, T1_KEEP_MHA, T2_OFFLOAD, T4_RETAIN = T0_RECOMPUTE, T1_KEEP_MHA, T2_OFFLOAD, T4_RETAIN
-    EDGE_GPU_PERSIST, EDGE_GPU_EPHEMERAL, EDGE_CPU_BROADCAST = EDGE_GPU_PERSIST, EDGE_GPU_EPHEMERAL, EDGE_CPU_BROADCAST
-    EDGE_CPU_RANK_LOCAL_PREFETCH = EDGE_CPU_RANK_LOCAL_PREFETCH
-    EDGE_CPU_BROADCAST_PREFETCH = EDGE_CPU_BROADCAST_PREFETCH
+# ---------------------------------------------------------------------------------------------------------
+# records
+# ---------------------------------------------------------------------------------------------------------
+class Phase(enum.Enum):
+    DEFERRED = "DEFERRED"
+    WARMUP_RECOMPUTE = "WARMUP_RECOMPUTE"
+    CALIBRATE_MHA = "CALIBRATE_MHA"
+    CALIBRATE_MHA_FRONT = "CALIBRATE_MHA_FRONT"
+    CALIBRATE_RETAIN = "CALIBRATE_RETAIN"
+    CALIBRATE_RETAIN_FRONT = "CALIBRATE_RETAIN_FRONT"
+    ACTIVE = "ACTIVE"
 
-    _DEFERRED, _WARMUP_RECOMPUTE, _CALIBRATE_MHA, _CALIBRATE_MHA_FRONT = -1, 0, 1, 2
-    _CALIBRATE_RETAIN, _CALIBRATE_RETAIN_FRONT, _ACTIVE = 3, 4, 5
-    _STATE_NAMES = {-1: "DEFERRED", 0: "WARMUP_RECOMPUTE", 1: "CALIBRATE_MHA", 2: "CALIBRATE_MHA_FRONT",
-                    3: "CALIBRATE_RETAIN", 4: "CALIBRATE_RETAIN_FRONT", 5: "ACTIVE"}
 
-    def __init__(self, n_layers: int, safety_margin: float = 0.1, deferred: bool = False,
+# calibration phase -> (tier under test, probed layer: -1 last / 0 first, phase after it, phase when the probe of the
+# first layer is skipped or this was it)
+_PHASE_PROBE = {
+    Phase.CALIBRATE_MHA: (T1_KEEP_MHA, -1, Phase.CALIBRATE_MHA_FRONT, Phase.CALIBRATE_RETAIN),
+    Phase.CALIBRATE_MHA_FRONT: (T1_KEEP_MHA, 0, None, Phase.CALIBRATE_RETAIN),
+    Phase.CALIBRATE_RETAIN: (T4_RETAIN, -1, Phase.CALIBRATE_RETAIN_FRONT, Phase.ACTIVE),
+    Phase.CALIBRATE_RETAIN_FRONT: (T4_RETAIN, 0, None, Phase.ACTIVE),
+}
+
+
+@dataclass(frozen=True)
+class StepReading:
+    """One training step as the planner sees it (already MAX-reduced over ranks)."""
+    peak: int = 0               # allocator peak of the step (+ symmetric buffers)
+    live: int = 0               # bytes alive right after the forward pass
+    t_fwd: float = 0.0
+    t_bwd: float = 0.0
+
+
+@dataclass(frozen=True)
+class TierProbe:
+    """What one tier costs, from probing a single layer at the back and (optionally) at the front of the stack."""
+    last: Optional[StepReading] = None
+    front: Optional[StepReading] = None
+    impossible: bool = False        # the tier ran out of memory even on one layer
+    last_layer_only: bool = False   # a second layer of this tier cannot fit (front probe skipped or failed)
+
+    def worst(self) -> StepReading:
+        rs = [r for r in (self.last, self.front) if r is not None]
+        if not rs:
+            return StepReading()
+        return StepReading(max(r.peak for r in rs), max(r.live for r in rs), max(r.t_fwd for r in rs),
+                           max(r.t_bwd for r in rs))
+
+
+@dataclass(frozen=True)
+class Calibration:
+    n_layers: int
+    baseline: StepReading = StepReading()       # every layer recomputed
+    keep: TierProbe = TierProbe()
+    retain: TierProbe = TierProbe()
+
+    def probe(self, tier: str) -> TierProbe:
+        return self.keep if tier == T1_KEEP_MHA else self.retain
+
+    def with_probe(self, tier: str, p: TierProbe) -> "Calibration":
+        return replace(self, keep=p) if tier == T1_KEEP_MHA else replace(self, retain=p)
+
+
+@dataclass(frozen=True)
+class EdgeCost:
+    """Measured cost of one graph-placement policy."""
+    policy: str
+    prep_s: float = 0.0
+    serial_s: float = 0.0           # part of the build the step has to wait for
+    overlap_s: float = 0.0          # part hidden behind the model step (prefetch)
+    build_peak: int = 0             # device peak during the build
+    host_bytes: int = 0             # resident-set growth on the host
+    resident_bytes: int = 0         # device bytes that stay alive between epochs (persistent topology)
+    walk_gpu_extra: int = 0         # extra device bytes if the walks are forced onto the GPU
+
+
+@dataclass(frozen=True)
+class TierCost:
+    t_fwd: float                    # per layer
+    t_bwd: float
+    bytes_deepest: int              # charged to the deepest layer of the tier when it is the last layer of the model
+    bytes_each: int                 # charged to every further layer of the tier
+
+
+@dataclass(frozen=True)
+class Layout:
+    n_recompute: int
+    n_keep: int
+    n_retain: int
+
+    def tiers(self) -> List[str]:
+        return [T0_RECOMPUTE] * self.n_recompute + [T1_KEEP_MHA] * self.n_keep + [T4_RETAIN] * self.n_retain
+
+    @property
+    def kept_score(self) -> int:    # tie-break: more retained state first
+        return 2 * self.n_retain + self.n_keep
+
+
+@dataclass(frozen=True)
+class PlanChoice:
+    policy: str
+    layout: Layout
+    walks_on_gpu: bool
+    t_step: float
+    t_model: float
+    t_edge: float
+    peak: int
+
+
+# ---------------------------------------------------------------------------------------------------------
+# phase transitions
+# ---------------------------------------------------------------------------------------------------------
+def probe_layout(phase: Phase, n_layers: int) -> List[str]:
+    """Tier of every layer while ``phase`` runs: all recomputed, except the one layer a calibration phase tests."""
+    modes = [T0_RECOMPUTE] * n_layers
+    if phase in _PHASE_PROBE and n_layers > 0:
+        tier, where, _nxt, _skip = _PHASE_PROBE[phase]
+        modes[where] = tier
+    return modes
+
+
+def warmup_baseline(samples: Sequence[StepReading]) -> StepReading:
+    """Baseline from the warm-up steps: the first one is discarded when there are several (allocator warm-up); peak is
+    the maximum, times are means."""
+    used = list(samples[1:]) if len(samples) > 1 else list(samples)
+    n = float(len(used))
+    return StepReading(max(r.peak for r in used), max(r.live for r in used), sum(r.t_fwd for r in used) / n,
+                       sum(r.t_bwd for r in used) / n)
+
+
+def advance(phase: Phase, cal: Calibration, reading: StepReading, peak_limit: int) -> Tuple[Phase, Calibration]:
+    """Record a calibration step and name the next phase.  The first-layer probe of a tier is skipped when a second
+    layer of it cannot fit on top of the baseline (the tier is then usable on the last layer only)."""
+    tier, where, nxt, skip_to = _PHASE_PROBE[phase]
+    p = cal.probe(tier)
+    if where == -1:
+        p = replace(p, last=reading)
+        per_layer = max(0, reading.live - cal.baseline.live)
+        second_fits = cal.baseline.peak + per_layer <= peak_limit
+        if cal.n_layers <= 1:
+            return skip_to, cal.with_probe(tier, p)
+        if not second_fits:
+            return skip_to, cal.with_probe(tier, replace(p, last_layer_only=True))
+        return nxt, cal.with_probe(tier, p)
+    return skip_to, cal.with_probe(tier, replace(p, front=reading))
+
+
+def after_failed_probe(phase: Phase, cal: Calibration) -> Optional[Tuple[Phase, Calibration]]:
+    """A calibration step ran out of memory: a failed last-layer probe rules the tier out, a failed first-layer probe
+    restricts it to the last layer.  ``None`` outside calibration."""
+    if phase not in _PHASE_PROBE:
+        return None
+    tier, where, _nxt, skip_to = _PHASE_PROBE[phase]
+    p = cal.probe(tier)
+    p = replace(p, impossible=True) if where == -1 else replace(p, last_layer_only=True)
+    return skip_to, cal.with_probe(tier, p)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# cost model
+# ---------------------------------------------------------------------------------------------------------
+def tier_costs(cal: Calibration) -> Dict[str, TierCost]:
+    """Per-layer time and memory of each tier.  A probe changes one layer, so its step time differs from the
+    baseline's by (tier layer - recomputed layer): ``t_tier = T_base / L + (T_probe - T_base)``, then forced into the
+    physical order retain <= keep_mha <= recompute.  Memory: the deepest kept layer costs what the last-layer probe
+    added to the step peak; any further layer costs the bytes the probe left alive after the forward pass."""
+    n = max(1, cal.n_layers)
+    base = cal.baseline
+    rec = TierCost(base.t_fwd / n, base.t_bwd / n, 0, 0)
+    out = {T0_RECOMPUTE: rec}
+    ceiling = rec
+    for tier in (T1_KEEP_MHA, T4_RETAIN):
+        pr = cal.probe(tier)
+        w = pr.worst()
+        t_f = min(max(rec.t_fwd + (w.t_fwd - base.t_fwd), 0.0), ceiling.t_fwd)
+        t_b = min(max(rec.t_bwd + (w.t_bwd - base.t_bwd), 0.0), ceiling.t_bwd)
+        deepest = max(0, (pr.last.peak if pr.last is not None else 0) - base.peak)
+        each = max(0, w.live - base.live) if pr.last is not None else 0
+        out[tier] = ceiling = TierCost(t_f, t_b, deepest, each)
+    return out
+
+
+def stacked_bytes(n_layers: int, bytes_each: int) -> int:
+    """``n_layers`` further layers of one tier; every layer beyond the first adds 5 % for fragmentation."""
+    return n_layers * int(bytes_each * (1.0 + FRAGMENTATION_PER_EXTRA_LAYER * max(0, n_layers - 1)))
+
+
+def layout_bytes(layout: Layout, costs: Dict[str, TierCost]) -> int:
+    """Activation bytes a layout adds to the all-recompute peak.  The model's last layer is the deepest kept one and
+    is charged the measured last-layer delta of its tier; the others are stacked per tier."""
+    keep, ret = costs[T1_KEEP_MHA], costs[T4_RETAIN]
+    if layout.n_retain > 0:
+        return ret.bytes_deepest + stacked_bytes(layout.n_retain - 1, ret.bytes_each) + stacked_bytes(layout.n_keep, keep.bytes_each)
+    if layout.n_keep > 0:
+        return keep.bytes_deepest + stacked_bytes(layout.n_keep - 1, keep.bytes_each)
+    return 0
+
+
+def layout_times(layout: Layout, costs: Dict[str, TierCost]) -> Tuple[float, float]:
+    counts = ((T0_RECOMPUTE, layout.n_recompute), (T1_KEEP_MHA, layout.n_keep), (T4_RETAIN, layout.n_retain))
+    return (sum(k * costs[t].t_fwd for t, k in counts), sum(k * costs[t].t_bwd for t, k in counts))
+
+
+def admissible_layouts(cal: Calibration) -> Iterator[Layout]:
+    """Every ``[recompute]*a + [keep_mha]*b + [retain]*c`` the probes did not rule out."""
+    n = cal.n_layers
+    for n_keep in range(n + 1):
+        for n_ret in range(n - n_keep + 1):
+            if n_keep and cal.keep.impossible:
+                continue
+            if n_ret and cal.retain.impossible:
+                continue
+            if cal.keep.last_layer_only and n_keep and (n_keep > 1 or n_ret > 0):
+                continue                                   # keep_mha only as the model's last layer
+            if cal.retain.last_layer_only and n_ret > 1:
+                continue
+            yield Layout(n - n_keep - n_ret, n_keep, n_ret)
+
+
+def search_plans(cal: Calibration, edge_costs: Sequence[EdgeCost], peak_limit: int, host_budget: int,
+                 excluded: Sequence[str] = ()):
+    """Fastest feasible (policy, layout).  Returns ``(best, best_without_resident_topology, report)``; ``report`` maps
+    each policy to ``("ok", best ms)`` or ``("skip:<why>", None)``.
+
+    feasible:  max(build peak, baseline peak + resident topology + layout bytes) <= peak_limit
+    step time: model + serial build + the part of the overlapped build the model step does not hide
+    order:     time, then more kept activations, then no resident topology, then less host memory, then lower build peak"""
+    costs = tier_costs(cal)
+    layouts = [(lay, layout_bytes(lay, costs), layout_times(lay, costs)) for lay in admissible_layouts(cal)] \
+        if cal.baseline.t_bwd > 0 else []
+    best = best_free = None
+    best_key = best_free_key = None
+    report: Dict[str, tuple] = {}
+    for ec in edge_costs:
+        if ec.policy in excluded:
+            report[ec.policy] = ("skip:gpu_infeasible", None)
+            continue
+        if ec.host_bytes > host_budget:
+            report[ec.policy] = ("skip:cpu_budget", None)
+            continue
+        variants = [(ec.build_peak, ec.overlap_s, False, ec.host_bytes)]
+        if ec.policy == EDGE_GPU_PERSIST and ec.walk_gpu_extra > 0:
+            # walks forced onto the GPU: nothing left to overlap, no host memory, a larger build peak
+            variants.append((max(ec.build_peak, ec.resident_bytes + ec.walk_gpu_extra), 0.0, True, 0))
+        fastest = float("inf")
+        for build_peak, overlap, walks_gpu, host in variants:
+            for lay, extra, (t_f, t_b) in layouts:
+                peak = max(int(build_peak), cal.baseline.peak + ec.resident_bytes + extra)
+                if peak > peak_limit:
+                    continue
+                t_model = t_f + t_b
+                t_edge = ec.serial_s + max(0.0, overlap - t_model)
+                t_step = t_model + t_edge
+                fastest = min(fastest, t_step)
+                key = (t_step, -lay.kept_score, int(ec.resident_bytes > 0), host, build_peak)
+                choice = PlanChoice(ec.policy, lay, walks_gpu, t_step, t_model, t_edge, peak)
+                if best_key is None or key < best_key:
+                    best_key, best = key, choice
+                if ec.resident_bytes == 0 and (best_free_key is None or key < best_free_key):
+                    best_free_key, best_free = key, choice
+        report[ec.policy] = ("ok", fastest * 1e3) if fastest < float("inf") else ("skip:no_feasible_tier", None)
+    return best, best_free, report
+
+
+def demoted(modes: Sequence[str]) -> Optional[List[str]]:
+    """One tier down on the shallowest layer that still keeps anything (retain -> keep_mha -> recompute); ``None``
+    when every layer is already recomputed."""
+    ids = [TIER_IDS[m] for m in modes]
+    for i, t in enumerate(ids):
+        if t > 0:
+            ids[i] = t - 1
+            return [TIER_FROM_ID[j] for j in ids]
+    return None
+
+
+def _count(tiers) -> dict:
+    out: Dict[str, int] = {}
+    for t in tiers:
+        out[t] = out.get(t, 0) + 1
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the planner object
+# ---------------------------------------------------------------------------------------------------------
+_NEUTRAL_EDGE_COST = EdgeCost(EDGE_GPU_EPHEMERAL)      # no profile yet: tiers can still be planned
+
+
+class ExecutionPlanner:
+    def __init__(self, n_layers: int, safety_margin: float = HEADROOM, deferred: bool = False,
                  probe: Optional[MemoryProbe] = None, verbose: bool = True):
         self.n_layers = int(n_layers)
-        self.safety_margin = float(safety_margin)
+        self.headroom = float(safety_margin)
         self.probe = probe if probe is not None else MemoryProbe()
         self.verbose = verbose
-        self._state = self._DEFERRED if deferred else self._WARMUP_RECOMPUTE
-        self._modes: List[str] = [T0_RECOMPUTE] * self.n_layers
-        self._warmup_target = 1 if deferred else 3
-        self._warmup_samples: List[tuple] = []            # (peak, t_fwd, t_bwd)
-        self._deferred_baseline = None                    # (peak, fwd_live, t_fwd, t_bwd)
-        self._fwd_live: Dict[int, int] = {}
-        self._peak: Dict[int, int] = {}
-        self._t_fwd: Dict[int, float] = {}
-        self._t_bwd: Dict[int, float] = {}
-        self._peak_warmup = 0
-        self._peak_mha_last = self._peak_mha = 0
-        self._peak_retain_last = self._peak_retain = 0
-        self._m_layer_mha = self._m_layer_full = 0
-        self._t_fwd_recompute = self._t_bwd_recompute = 0.0
-        self._t_fwd_mha = self._t_bwd_mha = 0.0
-        self._t_fwd_retain = self._t_bwd_retain = 0.0
-        self._edge_bytes, self._t_h2d_edge = 0, 0.0
-        self._edge_profiles: Dict[str, dict] = {}
-        self._gpu_memory_limit_bytes = 0
-        self._t1_infeasible = self._t4_infeasible = False
-        self._t1_nonlast_infeasible = self._t4_nonlast_infeasible = False
-        self._gpu_infeasible_policies: set = set()
-        self._active_peak_limit = 0
-        self._cache_edge = False
-        self._rw_on_gpu = False
-        self._edge_policy = EDGE_GPU_EPHEMERAL
-        self._best_nonpersistent_edge_policy = EDGE_GPU_EPHEMERAL
-        self._best_nonpersistent_tiers: List[str] = [T0_RECOMPUTE] * self.n_layers
+        self.phase = Phase.DEFERRED if deferred else Phase.WARMUP_RECOMPUTE
+        self.calibration = Calibration(self.n_layers)
+        self.edge_costs: Dict[str, EdgeCost] = {}
+        self.excluded_policies: set = set()
+        self.memory_cap_bytes = 0
         self.last_plan_log: Dict[str, tuple] = {}
+        self._warmup_steps_wanted = 1 if deferred else 3
+        self._warmup: List[StepReading] = []
+        self._deferred_reading: Optional[StepReading] = None
+        self._live_after_forward = 0
+        self._modes: List[str] = [T0_RECOMPUTE] * self.n_layers
+        self._choice = PlanChoice(EDGE_GPU_EPHEMERAL, Layout(self.n_layers, 0, 0), False, float("inf"), 0.0, 0.0, 0)
+        self._fallback = (EDGE_GPU_EPHEMERAL, [T0_RECOMPUTE] * self.n_layers)   # best plan without a resident topology
+        self._topology_bytes, self._topology_h2d_s = 0, 0.0
 
-    # ------------------------------------------------------------------ utilities
+    # ------------------------------------------------------------------ small helpers
     def _log(self, msg: str) -> None:
         if self.verbose and _is_rank0():
             print(f"[MultiTierManager] {msg}")
 
-    def set_gpu_memory_limit_bytes(self, limit_bytes: int) -> None:
-        self._gpu_memory_limit_bytes = max(0, int(limit_bytes))
-
-    def _effective_total_gpu_bytes(self, real_total: int) -> int:
-        if self._gpu_memory_limit_bytes > 0:
-            return min(int(real_total), self._gpu_memory_limit_bytes)
-        return int(real_total)
-
-    def _model_peak_limit_bytes(self, total_gpu: int) -> int:
-        return int(total_gpu * (1.0 - self.safety_margin))
-
-    def set_edge_info(self, edge_bytes: int, t_h2d: float) -> None:
-        self._edge_bytes, self._t_h2d_edge = int(edge_bytes), float(t_h2d)
-
-    def set_edge_policy_profile(self, policy: str, prep_time_s: float, gpu_peak_bytes: int, cpu_delta_bytes: int,
-                                live_edge_bytes: int = 0, serial_time_s=None, overlap_time_s: float = 0.0,
-                                rw_gpu_extra_bytes: int = 0, enabled: bool = True) -> None:
-        policy = str(policy)
-        if policy not in EDGE_POLICY_ORDER:
-            raise ValueError(f"Unsupported edge policy profile: {policy!r}")
-        if not enabled:
-            self._edge_profiles.pop(policy, None)
-            return
-        self._edge_profiles[policy] = {
-            "prep_time_s": max(0.0, float(prep_time_s)),
-            "serial_time_s": max(0.0, float(serial_time_s if serial_time_s is not None else prep_time_s)),
-            "overlap_time_s": max(0.0, float(overlap_time_s)),
-            "gpu_peak_bytes": max(0, int(gpu_peak_bytes)),
-            "cpu_delta_bytes": max(0, int(cpu_delta_bytes)),
-            "live_edge_bytes": max(0, int(live_edge_bytes)),
-            "rw_gpu_extra_bytes": max(0, int(rw_gpu_extra_bytes)),
-        }
-
-    def _edge_policy_profiles(self):
-        if not self._edge_profiles:
-            # no profile: a neutral ephemeral-GPU entry so that tiers can still be planned
-            return [(EDGE_GPU_EPHEMERAL, {"prep_time_s": 0.0, "serial_time_s": 0.0, "overlap_time_s": 0.0,
-                                          "gpu_peak_bytes": 0, "cpu_delta_bytes": 0, "live_edge_bytes": 0,
-                                          "rw_gpu_extra_bytes": 0})]
-        return [(p, self._edge_profiles[p]) for p in EDGE_POLICY_ORDER if p in self._edge_profiles]
-
-    # ------------------------------------------------------------------ state machine
-    def notify_budget_frozen(self, reuse_deferred_baseline: bool = False) -> None:
-        if self._state != self._DEFERRED:
-            return
-        self._state = self._WARMUP_RECOMPUTE
-        self._warmup_samples = []
-        if reuse_deferred_baseline and self._deferred_baseline is not None:
-            peak, live, t_f, t_b = self._deferred_baseline
-            self._warmup_samples.append((peak, t_f, t_b))
-            self._fwd_live[self._WARMUP_RECOMPUTE] = live
-            self._warmup_target = 1
-            self._finish_warmup()
-        self._log(f"edge budget frozen -> {self.state_name()}")
-
-    def _set_modes(self, modes: List[str]) -> None:
+    def _install(self, modes: Sequence[str]) -> None:
         self._modes = list(modes)
         if isinstance(self.probe, ScriptedMemoryProbe):
             self.probe.modes = self._modes
 
+    def _device_bytes(self, device) -> int:
+        total = int(self.probe.total(device))
+        return min(total, self.memory_cap_bytes) if self.memory_cap_bytes > 0 else total
+
+    def _peak_limit(self, device) -> int:
+        return int(self._device_bytes(device) * (1.0 - self.headroom))
+
+    # ------------------------------------------------------------------ inputs
+    def set_gpu_memory_limit_bytes(self, limit_bytes: int) -> None:
+        self.memory_cap_bytes = max(0, int(limit_bytes))
+
+    def set_edge_info(self, edge_bytes: int, t_h2d: float) -> None:
+        self._topology_bytes, self._topology_h2d_s = int(edge_bytes), float(t_h2d)
+
+    def set_edge_policy_profile(self, policy: str, prep_time_s: float, gpu_peak_bytes: int, cpu_delta_bytes: int,
+                                live_edge_bytes: int = 0, serial_time_s=None, overlap_time_s: float = 0.0,
+                                rw_gpu_extra_bytes: int = 0, enabled: bool = True) -> None:
+        if policy not in EDGE_POLICY_ORDER:
+            raise ValueError(f"Unsupported edge policy profile: {policy!r}")
+        if not enabled:
+            self.edge_costs.pop(policy, None)
+            return
+        nn = lambda v: max(0, int(v))
+        self.edge_costs[policy] = EdgeCost(
+            policy, prep_s=max(0.0, float(prep_time_s)),
+            serial_s=max(0.0, float(prep_time_s if serial_time_s is None else serial_time_s)),
+            overlap_s=max(0.0, float(overlap_time_s)), build_peak=nn(gpu_peak_bytes), host_bytes=nn(cpu_delta_bytes),
+            resident_bytes=nn(live_edge_bytes), walk_gpu_extra=nn(rw_gpu_extra_bytes))
+
+    def _ordered_edge_costs(self) -> List[EdgeCost]:
+        if not self.edge_costs:
+            return [_NEUTRAL_EDGE_COST]
+        return [self.edge_costs[p] for p in EDGE_POLICY_ORDER if p in self.edge_costs]
+
+    # ------------------------------------------------------------------ per-step protocol
+    def notify_budget_frozen(self, reuse_deferred_baseline: bool = False) -> None:
+        """The edge budget stopped moving: leave DEFERRED.  The last deferred step (all layers recomputed) can serve as
+        the warm-up sample, so calibration starts at once."""
+        if self.phase is not Phase.DEFERRED:
+            return
+        self.phase, self._warmup = Phase.WARMUP_RECOMPUTE, []
+        if reuse_deferred_baseline and self._deferred_reading is not None:
+            self._warmup = [self._deferred_reading]
+            self._close_warmup()
+        self._log(f"edge budget frozen -> {self.state_name()}")
+
     def plan(self, device) -> None:
-        if not self.probe.available():
+        """Called at the top of every forward pass: sets the layer tiers of this step."""
+        if not self.probe.available() or self.phase is Phase.ACTIVE:
             return
-        s = self._state
-        if s == self._ACTIVE:
-            return
-        modes = [T0_RECOMPUTE] * self.n_layers
-        if s == self._CALIBRATE_MHA:
-            modes[-1] = T1_KEEP_MHA
-        elif s == self._CALIBRATE_MHA_FRONT:
-            modes[0] = T1_KEEP_MHA
-        elif s == self._CALIBRATE_RETAIN:
-            modes[-1] = T4_RETAIN
-        elif s == self._CALIBRATE_RETAIN_FRONT:
-            modes[0] = T4_RETAIN
-        self._set_modes(modes)
+        self._install(probe_layout(self.phase, self.n_layers))
         self.probe.reset_peak(device)
-        if s != self._DEFERRED:
-            self._log(f"{self.state_name()}: tiers={self._tier_counts(modes)}")
+        if self.phase is not Phase.DEFERRED:
+            self._log(f"{self.state_name()}: tiers={_count(self._modes)}")
 
     def record_post_forward_memory(self, device) -> None:
-        if not self.probe.available() or self._state == self._ACTIVE:
-            return
-        self._fwd_live[self._state] = int(self.probe.live(device))
+        if self.probe.available() and self.phase is not Phase.ACTIVE:
+            self._live_after_forward = int(self.probe.live(device))
 
     def notify_step_end(self, device, t_bwd: float = None, t_fwd: float = None) -> None:
-        if not self.probe.available() or self._state == self._ACTIVE:
+        if not self.probe.available() or self.phase is Phase.ACTIVE:
             return
-        s = self._state
-        peak, live, t_f, t_b = _sync_max(
-            [self.probe.peak(device), self._fwd_live.get(s, 0), t_fwd or 0.0, t_bwd or 0.0], device)
-        peak, live = int(peak), int(live)
-        self._fwd_live[s] = live
-        total = self._effective_total_gpu_bytes(self.probe.total(device))
-        limit = self._model_peak_limit_bytes(total)
-        if s == self._DEFERRED:
-            self._deferred_baseline = (peak, live, t_f, t_b)
-            return
-        if s == self._WARMUP_RECOMPUTE:
-            self._warmup_samples.append((peak, t_f, t_b))
-            if len(self._warmup_samples) >= self._warmup_target:
-                self._finish_warmup()
-            return
-        self._peak[s], self._t_fwd[s], self._t_bwd[s] = peak, t_f, t_b
-        base_live = self._fwd_live.get(self._WARMUP_RECOMPUTE, 0)
-        if s == self._CALIBRATE_MHA:
-            self._peak_mha_last = self._peak_mha = peak
-            self._m_layer_mha = max(0, live - base_live)
-            self._t_fwd_mha, self._t_bwd_mha = t_f, t_b
-            if self.n_layers > 1 and self._peak_warmup + self._m_layer_mha > limit:
-                self._t1_nonlast_infeasible = True          # skip the FRONT probe (reference :594-611)
-                self._state = self._CALIBRATE_RETAIN
-            else:
-                self._state = self._CALIBRATE_MHA_FRONT if self.n_layers > 1 else self._CALIBRATE_RETAIN
-        elif s == self._CALIBRATE_MHA_FRONT:
-            self._peak_mha = max(self._peak_mha_last, peak)
-            self._m_layer_mha = max(self._m_layer_mha, live - base_live)
-            self._t_fwd_mha, self._t_bwd_mha = max(self._t_fwd_mha, t_f), max(self._t_bwd_mha, t_b)
-            self._state = self._CALIBRATE_RETAIN
-        elif s == self._CALIBRATE_RETAIN:
-            self._peak_retain_last = self._peak_retain = peak
-            self._m_layer_full = max(0, live - base_live)
-            self._t_fwd_retain, self._t_bwd_retain = t_f, t_b
-            if self.n_layers > 1 and self._peak_warmup + self._m_layer_full > limit:
-                self._t4_nonlast_infeasible = True
-                self._run_active_plan(device, total)
-            elif self.n_layers > 1:
-                self._state = self._CALIBRATE_RETAIN_FRONT
-            else:
-                self._run_active_plan(device, total)
-        elif s == self._CALIBRATE_RETAIN_FRONT:
-            self._peak_retain = max(self._peak_retain_last, peak)
-            self._m_layer_full = max(self._m_layer_full, live - base_live)
-            self._t_fwd_retain, self._t_bwd_retain = max(self._t_fwd_retain, t_f), max(self._t_bwd_retain, t_b)
-            self._run_active_plan(device, total)
+        peak, live, t_f, t_b = _sync_max([self.probe.peak(device), self._live_after_forward, t_fwd or 0.0, t_bwd or 0.0],
+                                         device)
+        reading = StepReading(int(peak), int(live), t_f, t_b)
+        if self.phase is Phase.DEFERRED:
+            self._deferred_reading = reading
+        elif self.phase is Phase.WARMUP_RECOMPUTE:
+            self._warmup.append(reading)
+            if len(self._warmup) >= self._warmup_steps_wanted:
+                self._close_warmup()
+        else:
+            self.phase, self.calibration = advance(self.phase, self.calibration, reading, self._peak_limit(device))
+            if self.phase is Phase.ACTIVE:
+                self._choose(device)
 
-    def _finish_warmup(self) -> None:
-        samples = self._warmup_samples[1:] if len(self._warmup_samples) > 1 else self._warmup_samples
-        self._peak_warmup = max(s[0] for s in samples)
-        self._t_fwd_recompute = sum(s[1] for s in samples) / len(samples)
-        self._t_bwd_recompute = sum(s[2] for s in samples) / len(samples)
-        self._state = self._CALIBRATE_MHA
-        self._log(f"warm-up done: peak={self._peak_warmup / 2**20:.0f} MiB "
-                  f"t_fwd={self._t_fwd_recompute * 1e3:.1f} ms t_bwd={self._t_bwd_recompute * 1e3:.1f} ms")
+    def _close_warmup(self) -> None:
+        base = warmup_baseline(self._warmup)
+        self.calibration = replace(self.calibration, baseline=base)
+        self.phase = Phase.CALIBRATE_MHA
+        self._log(f"warm-up done: peak={base.peak / 2**20:.0f} MiB t_fwd={base.t_fwd * 1e3:.1f} ms "
+                  f"t_bwd={base.t_bwd * 1e3:.1f} ms")
 
     # ------------------------------------------------------------------ planning
-    def _enumerate_structured_plans(self, peak_limit: int, cpu_budget: int, edge_peak: int, build_peak: int = 0):
-        L = self.n_layers
-        if L == 0 or self._t_bwd_recompute <= 0:
-            return []
-        t_f_r = self._t_fwd_recompute / L
-        t_f_k = max(t_f_r + (self._t_fwd_mha - self._t_fwd_recompute), 0.0)
-        t_f_n = max(t_f_r + (self._t_fwd_retain - self._t_fwd_recompute), 0.0)
-        t_r = self._t_bwd_recompute / L
-        t_k = max(t_r + (self._t_bwd_mha - self._t_bwd_recompute), 0.0)
-        t_n = max(t_r + (self._t_bwd_retain - self._t_bwd_recompute), 0.0)
-        t_k, t_f_k = min(t_k, t_r), min(t_f_k, t_f_r)          # physical ordering retain <= keep <= recompute
-        t_n, t_f_n = min(t_n, t_k), min(t_f_n, t_f_k)
-        m_full, m_mha = int(self._m_layer_full), int(self._m_layer_mha)
-        mha_delta_last = max(self._peak_mha_last - self._peak_warmup, 0)
-        retain_delta_last = max(self._peak_retain_last - self._peak_warmup, 0)
-        out = []
-        for k_keep in range(L + 1):
-            if k_keep > 0 and self._t1_infeasible:
-                continue
-            for k_ret in range(L - k_keep + 1):
-                if k_ret > 0 and self._t4_infeasible:
-                    continue
-                k_rec = L - k_keep - k_ret
-                if self._t1_nonlast_infeasible and k_keep > 0 and not (k_keep == 1 and k_ret == 0):
-                    continue
-                if self._t4_nonlast_infeasible and k_ret > 1:
-                    continue
-                if k_ret > 0:
-                    nr, nk = k_ret - 1, k_keep
-                    retain_extra = retain_delta_last + nr * int(m_full * (1.0 + _FRAG_FACTOR * max(0, nr - 1)))
-                    mha_extra = nk * int(m_mha * (1.0 + _FRAG_FACTOR * max(0, nk - 1)))
-                elif k_keep > 0:
-                    nk = k_keep - 1
-                    mha_extra = mha_delta_last + nk * int(m_mha * (1.0 + _FRAG_FACTOR * max(0, nk - 1)))
-                    retain_extra = 0
-                else:
-                    mha_extra = retain_extra = 0
-                peak_est = max(int(build_peak), self._peak_warmup + edge_peak + max(0, mha_extra + retain_extra))
-                if peak_est > peak_limit:
-                    continue
-                tiers = [T0_RECOMPUTE] * k_rec + [T1_KEEP_MHA] * k_keep + [T4_RETAIN] * k_ret
-                t_fwd_est = k_rec * t_f_r + k_keep * t_f_k + k_ret * t_f_n
-                t_bwd_est = k_rec * t_r + k_keep * t_k + k_ret * t_n
-                out.append((tiers, -(2 * k_ret + k_keep), 0, peak_est, t_fwd_est, t_bwd_est, t_fwd_est + t_bwd_est))
-        return out
-
-    def _run_active_plan(self, device, total_gpu: int) -> None:
-        cpu_budget = self.probe.cpu_available()
-        peak_limit = self._model_peak_limit_bytes(total_gpu)
-        self._active_peak_limit = peak_limit
-        best_key = best_np_key = None
-        best = {"policy": EDGE_GPU_EPHEMERAL, "tiers": [T0_RECOMPUTE] * self.n_layers, "rw_gpu": False,
-                "t_step": float("inf"), "t_model": 0.0, "t_edge": 0.0}
-        best_np = (EDGE_GPU_EPHEMERAL, [T0_RECOMPUTE] * self.n_layers)
-        log: Dict[str, tuple] = {}
-        for policy, prof in self._edge_policy_profiles():
-            if policy in self._gpu_infeasible_policies:
-                log[policy] = ("skip:gpu_infeasible", None)
-                continue
-            if prof["cpu_delta_bytes"] > cpu_budget:
-                log[policy] = ("skip:cpu_budget", None)
-                continue
-            edge_peak = int(prof["live_edge_bytes"])
-            variants = [(prof["gpu_peak_bytes"], prof["serial_time_s"], prof["overlap_time_s"], False,
-                         prof["cpu_delta_bytes"])]
-            if policy == EDGE_GPU_PERSIST and prof["rw_gpu_extra_bytes"] > 0:
-                variants.append((max(prof["gpu_peak_bytes"], edge_peak + prof["rw_gpu_extra_bytes"]),
-                                 prof["serial_time_s"], 0.0, True, 0))
-            policy_best = float("inf")
-            for v_peak, v_serial, v_overlap, v_gpu, v_cpu in variants:
-                for tiers, tie, cpu_est, peak_est, t_f, t_b, t_model in self._enumerate_structured_plans(
-                        peak_limit, cpu_budget, edge_peak, v_peak):
-                    t_edge = v_serial + max(0.0, v_overlap - t_model)
-                    t_est = t_model + t_edge
-                    policy_best = min(policy_best, t_est)
-                    key = (t_est, tie, cpu_est, int(edge_peak > 0), v_cpu, v_peak)
-                    if best_key is None or key < best_key:
-                        best_key = key
-                        best = {"policy": policy, "tiers": tiers, "rw_gpu": v_gpu, "t_step": t_est,
-                                "t_model": t_model, "t_edge": t_edge}
-                    if edge_peak == 0 and (best_np_key is None or key < best_np_key):
-                        best_np_key, best_np = key, (policy, tiers)
-            log[policy] = ("ok", policy_best * 1e3) if policy_best < float("inf") else ("skip:no_feasible_tier", None)
-        self.last_plan_log = log
-        self._edge_policy = best["policy"]
-        self._best_nonpersistent_edge_policy, self._best_nonpersistent_tiers = best_np
-        self._cache_edge = best["policy"] == EDGE_GPU_PERSIST
-        self._rw_on_gpu = bool(best["rw_gpu"])
-        self._set_modes(best["tiers"])
-        self._state = self._ACTIVE
-        parts = [f"{p}:{v[1]:.0f}ms{' [SELECTED]' if p == best['policy'] else ''}" if v[0] == "ok" else f"{p}:{v[0]}"
-                 for p, v in log.items()]
-        self._log(f"ACTIVE plan: edge_policy={best['policy']} rw_device={'GPU' if self._rw_on_gpu else 'auto'} "
-                  f"tiers={self._tier_counts(best['tiers'])} peak_limit={peak_limit / 2**20:.0f} MiB "
-                  f"est_T_step={best['t_step'] * 1e3 if best['t_step'] < float('inf') else 0:.0f} ms "
-                  f"(model={best['t_model'] * 1e3:.0f} ms edge_prep={best['t_edge'] * 1e3:.0f} ms)")
-        self._log("  policy candidates: " + " | ".join(parts))
-
-    @staticmethod
-    def _tier_counts(tiers) -> dict:
-        out: Dict[str, int] = {}
-        for t in tiers:
-            out[t] = out.get(t, 0) + 1
-        return out
+    def _choose(self, device) -> None:
+        limit = self._peak_limit(device) if self.probe.available() else 0
+        best, best_free, report = search_plans(self.calibration, self._ordered_edge_costs(), limit,
+                                               self.probe.cpu_available(), tuple(self.excluded_policies))
+        self.last_plan_log = report
+        if best is None:
+            best = PlanChoice(EDGE_GPU_EPHEMERAL, Layout(self.n_layers, 0, 0), False, float("inf"), 0.0, 0.0, 0)
+        self._choice = best
+        self._fallback = (best_free.policy, best_free.layout.tiers()) if best_free is not None else \
+            (EDGE_GPU_EPHEMERAL, [T0_RECOMPUTE] * self.n_layers)
+        self._install(best.layout.tiers())
+        self.phase = Phase.ACTIVE
+        shown = [f"{p}:{v[1]:.0f}ms{' [SELECTED]' if p == best.policy else ''}" if v[0] == "ok" else f"{p}:{v[0]}"
+                 for p, v in report.items()]
+        t_ms = best.t_step * 1e3 if best.t_step < float("inf") else 0.0
+        self._log(f"ACTIVE plan: edge_policy={best.policy} rw_device={'GPU' if best.walks_on_gpu else 'auto'} "
+                  f"tiers={_count(self._modes)} peak_limit={limit / 2**20:.0f} MiB est_T_step={t_ms:.0f} ms "
+                  f"(model={best.t_model * 1e3:.0f} ms edge_prep={best.t_edge * 1e3:.0f} ms)")
+        self._log("  policy candidates: " + " | ".join(shown))
 
     # ------------------------------------------------------------------ accessors
     def mode(self, layer_idx: int) -> str:
@@ -427,134 +553,116 @@ class _MultiTierResourceManager:
         return list(self._modes)
 
     def is_active(self) -> bool:
-        return self._state == self._ACTIVE
+        return self.phase is Phase.ACTIVE
 
     def state_name(self) -> str:
-        return self._STATE_NAMES[self._state]
+        return self.phase.value
 
     def needs_precise_timing(self) -> bool:
-        return self._state not in (self._ACTIVE, self._DEFERRED)
-
-    @property
-    def cache_edge(self) -> bool:
-        return self._cache_edge
+        return self.phase not in (Phase.ACTIVE, Phase.DEFERRED)
 
     @property
     def edge_policy(self) -> str:
-        return self._edge_policy
+        return self._choice.policy
+
+    @property
+    def cache_edge(self) -> bool:
+        return self._choice.policy == EDGE_GPU_PERSIST
 
     @property
     def rw_on_gpu(self) -> bool:
-        return self._rw_on_gpu
+        return self._choice.walks_on_gpu
 
     @property
     def best_nonpersistent_edge_policy(self) -> str:
-        return self._best_nonpersistent_edge_policy
+        return self._fallback[0]
 
     @property
     def best_nonpersistent_tiers(self) -> list:
-        return list(self._best_nonpersistent_tiers)
+        return list(self._fallback[1])
 
     def override_cache_decision(self, cache: bool) -> None:
-        self._cache_edge = bool(cache)
-        if not cache and self._edge_policy == EDGE_GPU_PERSIST:
-            self._edge_policy = self._best_nonpersistent_edge_policy
-            self._set_modes(self._best_nonpersistent_tiers)
+        """Giving up the resident topology moves the plan to the best one that never needed it."""
+        if not cache and self.cache_edge:
+            policy, tiers = self._fallback
+            self._choice = replace(self._choice, policy=policy, walks_on_gpu=False)
+            self._install(tiers)
 
     def override_active_plan(self, edge_policy: str, modes: List[str]) -> None:
         """Install an externally agreed plan (cross-rank consensus or ``--force_multi_tier_plan``)."""
         if len(modes) != self.n_layers:
             raise ValueError(f"plan has {len(modes)} tiers for {self.n_layers} layers")
-        for m in modes:
-            if m not in TIER_IDS:
-                raise ValueError(f"unknown tier {m!r}")
-        self._edge_policy = str(edge_policy)
-        self._cache_edge = edge_policy == EDGE_GPU_PERSIST
-        self._set_modes(list(modes))
-        self._state = self._ACTIVE
-        self._log(f"ACTIVE plan (override): edge_policy={edge_policy} tiers={self._tier_counts(modes)}")
+        unknown = [m for m in modes if m not in TIER_IDS]
+        if unknown:
+            raise ValueError(f"unknown tier {unknown[0]!r}")
+        self._choice = replace(self._choice, policy=str(edge_policy),
+                               walks_on_gpu=self._choice.walks_on_gpu and edge_policy == EDGE_GPU_PERSIST)
+        self._install(modes)
+        self.phase = Phase.ACTIVE
+        self._log(f"ACTIVE plan (override): edge_policy={edge_policy} tiers={_count(modes)}")
 
-    # ------------------------------------------------------------------ runtime feedback
+    # ------------------------------------------------------------------ run-time feedback
     def reconsider_with_actual_timing(self, device, t_model_actual: float, t_edge_wait_actual: float,
                                       gpu_policy_serial_s: Optional[float] = None) -> Optional[str]:
-        """One-way CPU -> GPU switch: when the measured wait for a CPU-built graph exceeds what a GPU build
-        would cost by more than 0.5 s, re-plan with the CPU policy's overlap replaced by the measurement
-        (reference :1230-1379).  Returns the new policy name or ``None``."""
-        if not self.is_active() or self._edge_policy not in (EDGE_CPU_RANK_LOCAL_PREFETCH, EDGE_CPU_BROADCAST_PREFETCH):
+        """One-way CPU -> GPU switch.  Under a CPU prefetch policy, when the step waited for its graph more than
+        0.5 s longer than the cheapest admissible GPU build would take, the policy's overlap figure is replaced by what
+        was measured (model + wait) and the search runs again.  Returns the new policy when it changed."""
+        current = self.edge_costs.get(self.edge_policy)
+        if (not self.is_active() or current is None
+                or self.edge_policy not in (EDGE_CPU_RANK_LOCAL_PREFETCH, EDGE_CPU_BROADCAST_PREFETCH)):
             return None
-        cur = self._edge_profiles.get(self._edge_policy)
-        if cur is None:
+        gpu = [self.edge_costs[p] for p in (EDGE_GPU_PERSIST, EDGE_GPU_EPHEMERAL)
+               if p in self.edge_costs and p not in self.excluded_policies]
+        if not gpu:
             return None
-        gpu_candidates = [p for p in (EDGE_GPU_PERSIST, EDGE_GPU_EPHEMERAL)
-                          if p in self._edge_profiles and p not in self._gpu_infeasible_policies]
-        if not gpu_candidates:
+        gpu_build_s = min(c.serial_s for c in gpu) if gpu_policy_serial_s is None else float(gpu_policy_serial_s)
+        if t_edge_wait_actual - gpu_build_s <= SWITCH_TO_GPU_AFTER_WAIT_S:
             return None
-        best_gpu = min(gpu_candidates, key=lambda p: self._edge_profiles[p]["serial_time_s"])
-        gpu_cost = gpu_policy_serial_s if gpu_policy_serial_s is not None else self._edge_profiles[best_gpu]["serial_time_s"]
-        if t_edge_wait_actual - gpu_cost <= _RECONSIDER_THRESHOLD_S:
+        self.edge_costs[current.policy] = replace(current, overlap_s=float(t_model_actual + t_edge_wait_actual))
+        before = self.edge_policy
+        self._choose(device)
+        if self.edge_policy == before:
             return None
-        cur["overlap_time_s"] = float(t_model_actual + t_edge_wait_actual)
-        old = self._edge_policy
-        total = self._effective_total_gpu_bytes(self.probe.total(device))
-        self._run_active_plan(device, total)
-        if self._edge_policy != old:
-            self._log(f"timing feedback: {old} waited {t_edge_wait_actual:.2f}s -> switched to {self._edge_policy}")
-            return self._edge_policy
-        return None
+        self._log(f"timing feedback: {before} waited {t_edge_wait_actual:.2f}s -> switched to {self.edge_policy}")
+        return self.edge_policy
 
     def report_runtime_edge_gpu_infeasible(self, device) -> bool:
-        """The GPU edge build fell back at run time: exclude GPU policies and re-plan (reference :1381-1431)."""
-        changed = False
-        for p in (EDGE_GPU_EPHEMERAL, EDGE_GPU_PERSIST):
-            if p not in self._gpu_infeasible_policies:
-                self._gpu_infeasible_policies.add(p)
-                changed = True
-        if changed and self.is_active():
-            total = self._effective_total_gpu_bytes(self.probe.total(device))
-            self._run_active_plan(device, total)
-        return changed
+        """A GPU graph build fell back to the CPU at run time: GPU policies leave the search for good."""
+        gpu = {EDGE_GPU_EPHEMERAL, EDGE_GPU_PERSIST}
+        if gpu <= self.excluded_policies:
+            return False
+        self.excluded_policies |= gpu
+        if self.is_active():
+            self._choose(device)
+        return True
 
     def mark_current_calibration_infeasible(self, device) -> bool:
-        """A CALIBRATE_* step ran out of memory: disable that tier and move on (reference :1456-1517)."""
-        s = self._state
-        total = self._effective_total_gpu_bytes(self.probe.total(device)) if self.probe.available() else 0
-        if s == self._CALIBRATE_MHA:
-            self._t1_infeasible = True
-            self._state = self._CALIBRATE_RETAIN
-        elif s == self._CALIBRATE_MHA_FRONT:
-            self._t1_nonlast_infeasible = True
-            self._state = self._CALIBRATE_RETAIN
-        elif s == self._CALIBRATE_RETAIN:
-            self._t4_infeasible = True
-            self._run_active_plan(device, total)
-        elif s == self._CALIBRATE_RETAIN_FRONT:
-            self._t4_nonlast_infeasible = True
-            self._run_active_plan(device, total)
-        else:
+        """The calibration step in flight ran out of memory."""
+        moved = after_failed_probe(self.phase, self.calibration)
+        if moved is None:
             return False
+        self.phase, self.calibration = moved
+        if self.phase is Phase.ACTIVE:
+            self._choose(device)
         self._log(f"calibration step ran out of memory -> {self.state_name()}")
         return True
 
     def apply_oom_fallback(self, device, sp_group=None, sp_world_size: int = 1) -> bool:
-        """Demote one tier (retain -> keep_mha -> recompute, shallowest kept layer first) and make all
-        ranks agree by taking the element-wise minimum tier (reference :1519-1562)."""
-        ids = [TIER_IDS[m] for m in self._modes]
-        for i, t in enumerate(ids):
-            if t > 0:
-                ids[i] = t - 1
-                break
-        else:
-            if self._cache_edge:
+        """An ACTIVE step ran out of memory: demote one layer by one tier and agree on the element-wise minimum over
+        the ranks; with nothing left to demote, give up the resident topology; else report failure."""
+        lower = demoted(self._modes)
+        if lower is None:
+            if self.cache_edge:
                 self.override_cache_decision(False)
                 return True
             return False
         if sp_world_size > 1 and dist.is_initialized():
             dev = torch.device(device) if dist.get_backend(sp_group) == "nccl" else torch.device("cpu")
-            t = torch.tensor(ids, dtype=torch.int64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=sp_group)
-            ids = [int(x) for x in t.tolist()]
-        self._set_modes([TIER_FROM_ID[i] for i in ids])
-        self._log(f"OOM fallback -> tiers={self._tier_counts(self._modes)}")
+            ids = torch.tensor([TIER_IDS[m] for m in lower], dtype=torch.int64, device=dev)
+            dist.all_reduce(ids, op=dist.ReduceOp.MIN, group=sp_group)
+            lower = [TIER_FROM_ID[int(i)] for i in ids.tolist()]
+        self._install(lower)
+        self._log(f"OOM fallback -> tiers={_count(self._modes)}")
         return True
 
 

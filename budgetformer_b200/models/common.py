@@ -255,8 +255,8 @@ class NodeModelBase(nn.Module):
         self.activation_checkpoint = enabled
         self.activation_checkpoint_mode = resolved if enabled else "none"
         if self.activation_checkpoint_mode == "multi_tier":
-            from ..control.multi_tier import _MultiTierResourceManager
-            self._comm_ckpt = _MultiTierResourceManager(len(self.layers), deferred=deferred)
+            from ..control.multi_tier import ExecutionPlanner
+            self._comm_ckpt = ExecutionPlanner(len(self.layers), deferred=deferred)
         elif self.activation_checkpoint_mode == "comm_aware":
             from ..control.multi_tier import CommAwareCheckpointer
             self._comm_ckpt = CommAwareCheckpointer(len(self.layers))

@@ -113,7 +113,7 @@ def load():
     """Import the built extension, building it first when it is missing or stale."""
     global _MOD
     if _MOD is not None:
-        return _MOD
+        return _TIMED if _EVENTS_ON else _MOD
     with _LOCK:
         if _MOD is not None:
             return _MOD
@@ -127,7 +127,7 @@ def load():
             _MOD = None
             return build()
         _MOD = _import_so()
-        return _MOD
+        return _TIMED if _EVENTS_ON else _MOD
 
 
 def available() -> bool:
@@ -155,3 +155,54 @@ def launch_count() -> int:
 def reset_launch_count() -> None:
     global _LAUNCHES
     _LAUNCHES = 0
+
+
+# ---- per-kernel device times (CUDA events around every extension call) ---------------------------------
+# ``enable_kernel_events(True)`` makes ``load()`` hand out a proxy that brackets each extension call with two CUDA
+# events on the current stream; ``kernel_event_summary()`` resolves them to milliseconds per entry point.  The time of
+# a call is what the stream spent between the two markers: its kernels plus, for the device barriers, the wait for the
+# slowest rank.  Off by default (two event records per call); used by ``bench.py --kernel_events``.
+_EVENTS_ON = False
+_EVENT_LOG = []
+
+
+class _TimedModule:
+    def __getattr__(self, name):
+        fn = getattr(_MOD, name)
+        if not callable(fn):
+            return fn
+
+        def timed(*args, **kw):
+            import torch
+            if not torch.cuda.is_available():
+                return fn(*args, **kw)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = fn(*args, **kw)
+            e.record()
+            _EVENT_LOG.append((name, s, e))
+            return out
+
+        return timed
+
+
+_TIMED = _TimedModule()
+
+
+def enable_kernel_events(on: bool = True) -> None:
+    global _EVENTS_ON
+    _EVENTS_ON = bool(on)
+    _EVENT_LOG.clear()
+
+
+def kernel_event_summary() -> dict:
+    """{entry point: (calls, total ms)} since ``enable_kernel_events``; synchronises the device."""
+    import torch
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    out = {}
+    for name, s, e in _EVENT_LOG:
+        calls, ms = out.get(name, (0, 0.0))
+        out[name] = (calls + 1, ms + s.elapsed_time(e))
+    _EVENT_LOG.clear()
+    return out

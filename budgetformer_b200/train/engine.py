@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from ..control.budget import (AdaptiveEdgeBudgetController, decide_budget_move, fixed_budget_controller,
+from ..control.budget import (BudgetSearch, decide_budget_move, fixed_budget_controller,
                               resolve_adaptive_edge_budget_config)
 from ..control.multi_tier import parse_force_multi_tier_plan, TIER_FROM_ID, TIER_IDS, EDGE_POLICY_ORDER
 from ..graph.attn_graph import AttnGraph
@@ -136,10 +136,10 @@ class FullGraphTrainer:
                                                       getattr(args, "fixed_walk_length", None))
             self._controller_drives_budget = True
         elif self.budget_cfg.enabled:
-            self.controller = AdaptiveEdgeBudgetController(self.budget_cfg)
+            self.controller = BudgetSearch(self.budget_cfg)
             self._controller_drives_budget = True
         else:
-            self.controller = AdaptiveEdgeBudgetController(self.budget_cfg)   # disabled => frozen
+            self.controller = BudgetSearch(self.budget_cfg)   # disabled => frozen
             self._controller_drives_budget = False
         self.probe_local_idx = self._select_probe_nodes()
         self._static_seed_epochs = self._resolve_static_seed_epochs()
@@ -633,7 +633,7 @@ class FullGraphTrainer:
         if n_probe <= 0:
             c.frozen = True
             return
-        if c._over_budget:
+        if c.over_limit:
             ns = c.force_shrink() or c.current_state()
             self.log(f"  ↳ BudgetCtrl shrink epoch={epoch} (peak over GPU limit) "
                      f"new_budget=({ns['real_edges_per_query']},{ns['rw_edges_per_query']})")
