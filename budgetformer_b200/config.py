@@ -110,7 +110,7 @@ _EXTRA = [
                                      "help": "fused projection + all-to-all kernels over symmetric memory"}),
     (("--sync_batchnorm",), _STORE_TRUE, False, {"help": "all-reduce BatchNorm statistics over SP ranks"}),
     (("--metrics_jsonl",), str, "", {"help": "write one JSON line per epoch (device-timed)"}),
-    (("--fault_inject",), str, "", {"help": "host-side fault injection spec, e.g. oom@fwd:3 or exit@7:rank1"}),
+    (("--fault_inject",), str, "", {"help": "host-side fault injection spec, <kind>@<phase>:<epoch>[:rank<k>], e.g. oom@fwd:3 or exit@step:7:rank1"}),
     (("--watchdog_seconds",), float, 0.0, {"help": "heartbeat watchdog: abort all ranks cleanly when a peer leaves or stays "
                                                    "silent for this many seconds (0 = off, NCCL's timeout only)"}),
     (("--watchdog_step_seconds",), float, 0.0, {"help": "with --watchdog_seconds: also abort when this rank itself has "

@@ -43,6 +43,9 @@ __global__ void peer_barrier_kernel(PeerPtrs flag_pages, int rank, int world, in
     uint32_t* remote = static_cast<uint32_t*>(flag_pages.p[t]) + channel * BF_MAX_PEERS + rank;
     st_release_sys(remote, epoch);
     const uint32_t* mine = static_cast<const uint32_t*>(flag_pages.p[rank]) + channel * BF_MAX_PEERS + t;
+    // an earlier wait of this process already gave up: the host will discard everything queued behind it, so raise
+    // the flag for the peers and return without spending another bound here
+    if (*reinterpret_cast<volatile int*>(status) != 0) return;
     bool ok = false;
     for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
       // epochs only grow; signed distance handles wrap-around

@@ -69,10 +69,10 @@ def initialize_distributed(args) -> None:
             torch.cuda.set_device(args.device)
         else:
             args.device = "cpu"
+    timeout = datetime.timedelta(minutes=int(getattr(args, "distributed_timeout_minutes", 10)))
     if not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")
-        timeout = datetime.timedelta(minutes=int(getattr(args, "distributed_timeout_minutes", 10)))
         kwargs = {}
         if backend == "nccl":
             kwargs["device_id"] = torch.device(args.device)
@@ -80,6 +80,30 @@ def initialize_distributed(args) -> None:
         _STATE.owns_process_group = True
     args.sequence_parallel_size = world
     initialize_sequence_parallel(getattr(args, "seq_len", 0), 1, 1, world)
+    if backend == "nccl" and os.getenv("BF_HOST_CONTROL_PLANE", "1") != "0":
+        _create_control_group(timeout)
+
+
+def _create_control_group(timeout) -> None:
+    """Host-side (gloo) twin of the SP group for control scalars.  The reference sends every vote through NCCL and
+    reads it with ``.item()`` (e.g. main_node_fullgraph_sp.py:1313-1318), which empties the GPU queue each time; with
+    the twin the training stream is never synchronised by the control plane.  Creation is collective; when gloo cannot
+    come up on this host every rank sees the same failure and the votes stay on NCCL."""
+    from . import comm
+    if _STATE.group is None or comm.control_group(_STATE.group) is not None:
+        return
+    try:
+        if os.environ.get("MASTER_ADDR", "") in ("127.0.0.1", "localhost"):
+            os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")
+        kw = {"timeout": timeout} if timeout is not None else {}
+        twin = dist.new_group(backend="gloo", **kw)
+        probe = torch.zeros(1)
+        dist.all_reduce(probe, group=twin)
+        comm.register_control_group(_STATE.group, twin)
+    except Exception as e:  # pragma: no cover - depends on the host's network setup
+        if dist.get_rank() == 0:
+            print(f"[init] host-side control group unavailable ({type(e).__name__}: {e}); votes use the device group",
+                  flush=True)
 
 
 def initialize_sequence_parallel(seq_len: int = 0, tensor_model_parallel_size: int = 1,
@@ -119,6 +143,8 @@ def destroy_distributed() -> None:
 
 def reset_state() -> None:
     global _STATE
+    from . import comm
+    comm._CONTROL_TWIN.clear()
     _STATE.__init__()
 
 

@@ -79,9 +79,25 @@ class SymmWorld:
         if self.world == 1:
             return
         self._epoch += 1
-        _ext.load().peer_barrier(self.flags.ptrs, self.rank, int(channel), self._epoch & 0x7FFFFFFF,
+        # the kernel compares epochs by signed 32-bit distance, so the counter wraps over the full 32 bits
+        _ext.load().peer_barrier(self.flags.ptrs, self.rank, int(channel), self._epoch & 0xFFFFFFFF,
                                  status_tensor(self.device))
         _ext.count_launches(1)
+
+    def resync(self) -> None:
+        """Bring every rank's barrier epoch back together after a step that some rank abandoned on the host (it issued
+        fewer barriers than its peers, so its counter lags and its next barriers would pass at once on flags that are
+        already ahead).  Drains this rank's queue (barriers still waiting for the rank that stopped give up after
+        their bound; once the status word is set the remaining ones return immediately), clears the status word, takes
+        the maximum counter over the ranks on the host and meets the others there."""
+        if self.world == 1:
+            return
+        torch.cuda.synchronize(self.device)
+        status_tensor(self.device).zero_()
+        dev = comm.comm_device(self.group, self.device)
+        self._epoch = int(comm.all_reduce_scalar(float(self._epoch), "max", self.group, dev))
+        torch.cuda.synchronize(self.device)
+        comm.barrier(self.group)
 
 
 def get_world(group, device) -> SymmWorld:

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import gc
 import json
+import os
 import time
 from typing import Dict, List, Optional
 
@@ -68,6 +69,7 @@ class FullGraphTrainer:
     def __init__(self, args, data: Optional[GraphData] = None, log=print):
         self.args = args
         self._log_fn = log
+        self._guard_rank_departure(args)
         initialize_distributed(args)
         self.rank = int(args.rank)
         self.device = torch.device(args.device)
@@ -186,6 +188,21 @@ class FullGraphTrainer:
             load_train_state(self, args.resume)
 
     # ------------------------------------------------------------------------------------------ helpers
+    @staticmethod
+    def _guard_rank_departure(args) -> None:
+        """A run in which a rank may leave or freeze on purpose (the heartbeat watchdog ends the process; ``exit`` /
+        ``stall`` faults are injected) must not have its buffers bound to an NVSwitch multicast object: a rank that dies
+        while bound raises NVLink faults on the other ranks' GPUs.  So, before the process group and the symmetric
+        buffers exist, in-switch reduction is turned off for NCCL and for this package's own all-reduce (which then
+        uses plain peer loads and stores)."""
+        spec = str(getattr(args, "fault_inject", "") or os.environ.get("BF_FAULT", ""))
+        wd = float(getattr(args, "watchdog_seconds", 0) or 0) > 0 or float(getattr(args, "watchdog_step_seconds", 0) or 0) > 0
+        if wd or "exit@" in spec or "stall@" in spec:
+            os.environ["NCCL_NVLS_ENABLE"] = "0"
+            os.environ["BF_DISABLE_MULTIMEM"] = "1"
+            if int(os.environ.get("RANK", "0")) == 0:
+                print("[init] watchdog / departure faults requested: NVLS and multimem are off for this run", flush=True)
+
     def log(self, msg: str) -> None:
         if self.rank == 0:
             self._log_fn(msg, flush=True)
@@ -320,7 +337,8 @@ class FullGraphTrainer:
             torch.cuda.empty_cache()
         gc.collect()
 
-    def _fwd_bwd_opt(self, graph: AttnGraph, epoch: int, x_local, timers: Dict[str, float], sync_timers: bool):
+    def _fwd_bwd(self, graph: AttnGraph, epoch: int, x_local, timers: Dict[str, float], sync_timers: bool):
+        """Forward, backward and gradient reduction of one step; everything that can fail on one rank only."""
         self.model.train()
         stage = {"bwd_started": False}
         if debug.enabled():
@@ -348,8 +366,14 @@ class FullGraphTrainer:
         if debug.enabled():
             debug.assert_finite(f"the loss of epoch {epoch}", loss.detach())
             debug.assert_finite(f"the gradients of epoch {epoch}", *[p.grad for p in self.model.parameters()])
+        self.fault.check("opt", epoch)          # last point at which a one-rank failure can still be voted on
+        timers.update(fwd=t_fwd.elapsed, bwd=t_bwd.elapsed)
+        return loss
+
+    def _optimizer_step(self, timers: Dict[str, float], sync_timers: bool) -> None:
+        """Clip + AdamW + schedule.  Runs only after every rank voted that its forward and backward went through, so a
+        rank can never apply an update that the others drop."""
         with StepTimer(self.device, sync_timers) as t_opt, comm_profiler.nvtx_range("optimizer"):
-            self.fault.check("opt", epoch)
             if self.scaler.is_enabled():
                 self.scaler.unscale_(self.optimizer)
                 torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)
@@ -361,13 +385,14 @@ class FullGraphTrainer:
                 torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)
                 self.optimizer.step()
             self.lr_scheduler.step()
-        timers.update(fwd=t_fwd.elapsed, bwd=t_bwd.elapsed, opt=t_opt.elapsed)
-        return loss
+        timers.update(opt=t_opt.elapsed)
 
     def _step_with_oom_recovery(self, graph, epoch, x_local, timers, sync_timers):
-        """Voted OOM protocol (main_node_fullgraph_sp.py:1320-1507): every attempt ends with a MAX vote; on a
-        failure all ranks clean up and then either demote one activation tier (plan ACTIVE), mark the tier
-        under calibration infeasible, or abort; a failure after backward started drops the step."""
+        """Voted OOM protocol (main_node_fullgraph_sp.py:1320-1507).  Every attempt ends with one packed MAX vote
+        (failed here?, had backward started?, did a device-side wait expire?) taken after the gradient reduction has
+        been launched and before the optimizer: on a failure all ranks clean up and then either demote one activation
+        tier (plan ACTIVE), mark the tier under calibration infeasible, or abort; a failure after backward started
+        drops the step.  The vote travels over the host-side group, so it does not drain the GPU queue."""
         from torch.utils.checkpoint import CheckpointError
         attempt = 0
         while True:
@@ -376,15 +401,20 @@ class FullGraphTrainer:
             self._stage = {"bwd_started": False}
             loss = None
             try:
-                loss = self._fwd_bwd_opt(graph, epoch, x_local, timers, sync_timers)
+                loss = self._fwd_bwd(graph, epoch, x_local, timers, sync_timers)
             except (torch.cuda.OutOfMemoryError, CheckpointError) as e:
                 failed, err = True, e
-            if not self._any_rank(failed):
+            expired = self._take_device_status()
+            any_failed, bwd_started, any_expired = self._vote(failed, self._stage.get("bwd_started", False), expired != 0)
+            if any_expired:
+                self._abort_on_expired_wait(expired)
+            if not any_failed:
+                self._optimizer_step(timers, sync_timers)
                 self.consecutive_dropped = 0
                 return loss
             del loss
-            bwd_started = self._any_rank(self._stage.get("bwd_started", False))
             self._cleanup_after_oom()
+            self._resync_device_barriers()
             self.log(f"[oom] step failed on some rank (attempt {attempt}, bwd_started={bwd_started}): "
                      f"{type(err).__name__ if err else 'remote'}")
             if self.planner is None:
@@ -399,6 +429,62 @@ class FullGraphTrainer:
                 if self.consecutive_dropped >= MAX_CONSECUTIVE_DROPPED:
                     raise RuntimeError(f"{MAX_CONSECUTIVE_DROPPED} consecutive steps dropped after OOM") from err
                 raise StepDropped()
+
+    def _vote(self, *flags: bool):
+        """Element-wise OR over the SP ranks of several flags in one collective."""
+        if self.sp_world == 1:
+            return tuple(bool(f) for f in flags)
+        dev = comm.comm_device(self.sp_group, self.device)
+        vals = comm.all_reduce_scalars([1.0 if f else 0.0 for f in flags], "max", self.sp_group, dev)
+        return tuple(v > 0.5 for v in vals)
+
+    # ---- device-side status word ----------------------------------------------------------------------------
+    # Kernels with bounded waits (the peer barrier, the GEMM's mbarrier waits) report an expired wait by writing a
+    # status word and returning; what they computed after that is invalid.  The word is copied to pinned host memory
+    # at the end of every step without stalling the launch queue and examined once that copy has landed, which the
+    # run-ahead bound of two steps guarantees before the step after next is launched.
+    def _queue_device_status_read(self) -> None:
+        if self.device.type != "cuda" or not self.fused_sp:
+            return
+        from ..ops.gemm import status_tensor
+        pipe = self.__dict__.setdefault("_status_pipe", {"host": torch.zeros(2, 4, dtype=torch.int32).pin_memory(),
+                                                         "events": [None, None], "slot": 0})
+        slot = pipe["slot"]
+        pipe["host"][slot].copy_(status_tensor(self.device), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        pipe["events"][slot] = ev
+        pipe["slot"] = slot ^ 1
+
+    def _take_device_status(self) -> int:
+        """Status word of the most recent step whose copy has completed (0 = healthy)."""
+        pipe = self.__dict__.get("_status_pipe")
+        if pipe is None:
+            return 0
+        code = 0
+        for slot in (0, 1):
+            ev = pipe["events"][slot]
+            if ev is not None and ev.query():
+                code = code or int(pipe["host"][slot][0])
+                pipe["events"][slot] = None
+        return code
+
+    def _abort_on_expired_wait(self, local_code: int) -> None:
+        """Some rank saw a bounded device-side wait give up: the steps launched since then computed on data a peer had
+        not finished writing.  The reference's NCCL collectives would have blocked until their time-out and ended the
+        job; so does this - on every rank, after the same vote."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        raise RuntimeError(
+            f"a device-side bounded wait expired on {'this rank' if local_code else 'another rank'} "
+            f"(status {local_code}): a peer did not reach a barrier in time, results since then are invalid")
+
+    def _resync_device_barriers(self) -> None:
+        """After a step that failed on the host of some rank the ranks have issued different numbers of device
+        barriers; bring the epoch counters back together before anything is launched again."""
+        if self.fused_sp and self.sp_world > 1 and self.device.type == "cuda":
+            from ..parallel import symm
+            symm.get_world(self.sp_group, self.device).resync()
 
     def build_edges(self, epoch: int) -> AttnGraph:
         """Build (or fetch the prefetched) attention graph of ``epoch`` with a voted retry on failure
@@ -443,7 +529,6 @@ class FullGraphTrainer:
         x_local = None
         if x_host is not None:
             x_local = self._stage_input(x_host)
-        self._align_ranks()
         with StepTimer(self.device, sync_timers) as t_rw, comm_profiler.nvtx_range("edge_build"):
             graph = self.build_edges(epoch)
         timers["rw"] = t_rw.elapsed
@@ -469,6 +554,7 @@ class FullGraphTrainer:
         if self.planner is not None or getattr(self.model, "_comm_ckpt", None) is not None:
             self.model.comm_aware_notify_step_end(self.device, t_bwd=timers["bwd"], t_fwd=timers["fwd"])
         if self.device.type == "cuda":
+            self._queue_device_status_read()
             done = torch.cuda.Event()
             done.record(torch.cuda.current_stream(self.device))
             self._step_done.append(done)
@@ -539,9 +625,11 @@ class FullGraphTrainer:
         return x
 
     def _align_ranks(self) -> None:
-        """Stream-ordered NCCL rendezvous before a fused forward.  The in-kernel barriers of the fused path use
-        bounded spins (a few seconds); this keeps host-side skew between ranks (evaluation on rank 0, logging, a
-        slow CPU edge build) out of those spins, leaving NCCL's own watchdog as the detector for a lost rank."""
+        """Stream-ordered NCCL rendezvous before a fused forward outside the training step (evaluation, budget
+        probes).  The in-kernel barriers of the fused path use bounded spins (a few seconds); this keeps host-side
+        skew between ranks (metrics on rank 0, logging) out of those spins.  The training step needs none: the
+        host-side vote on the graph build, taken by every rank right before it launches the step, already is a
+        rendezvous of the hosts, and it queues nothing on the GPU."""
         if self.fused_sp and self.sp_world > 1:
             if not hasattr(self, "_align_buf"):
                 self._align_buf = torch.zeros(1, device=self.device)

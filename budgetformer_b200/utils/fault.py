@@ -44,13 +44,26 @@ class FaultInjector:
         self.faults: List[_Fault] = []
         spec = spec or os.environ.get("BF_FAULT", "")
         for item in filter(None, (s.strip() for s in spec.split(","))):
+            self.faults.append(self._parse(item))
+
+    GRAMMAR = "<kind>@<phase>:<epoch>[:rank<k>] with kind in oom|raise|exit|delay|stall, e.g. exit@step:7:rank1"
+
+    @classmethod
+    def _parse(cls, item: str) -> _Fault:
+        try:
             kind, rest = item.split("@", 1)
             parts = rest.split(":")
             phase, epoch = parts[0], int(parts[1])
-            rk = int(parts[2].replace("rank", "")) if len(parts) > 2 else None
-            if kind not in ("oom", "raise", "exit", "delay", "stall"):
-                raise ValueError(f"unknown fault kind {kind!r}")
-            self.faults.append(_Fault(kind, phase, epoch, rk))
+            rk = None
+            if len(parts) > 2:
+                if not parts[2].startswith("rank") or len(parts) > 3:
+                    raise ValueError(parts[2])
+                rk = int(parts[2][4:])
+            if kind not in ("oom", "raise", "exit", "delay", "stall") or not phase:
+                raise ValueError(kind)
+        except (ValueError, IndexError) as e:
+            raise ValueError(f"malformed fault spec {item!r}: expected {cls.GRAMMAR}") from e
+        return _Fault(kind, phase, epoch, rk)
 
     def __bool__(self) -> bool:
         return bool(self.faults)

@@ -67,7 +67,10 @@ def mode_oom(out_path):
     log = []
     for epoch in (1, 2, 3, 4):
         s = t.train_step(epoch)
-        log.append({"epoch": epoch, "dropped": s["dropped"], "loss": s["loss"], "modes": t.planner.modes()})
+        # replicated weights must stay identical: a rank that did not fail may not apply a step the others drop
+        digest = float(sum(p.detach().double().sum() for p in t.model.parameters()))
+        log.append({"epoch": epoch, "dropped": s["dropped"], "loss": s["loss"], "modes": t.planner.modes(),
+                    "weights": digest})
     json.dump(log, open(out_path + f".{dist.get_rank()}", "w"))
 
 

@@ -51,6 +51,8 @@ def test_voted_oom_recovery_is_symmetric(tmp_path):
     assert r0[2]["dropped"] == 1.0 and r1[2]["dropped"] == 1.0             # fault after backward on rank 1: both drop
     assert r0[2]["modes"] == ["recompute", "retain"]
     assert r0[3]["dropped"] == 0.0 and r0[3]["modes"] == r0[2]["modes"]
+    assert [e["weights"] for e in r0] == [e["weights"] for e in r1]        # no rank applied an update the other dropped
+    assert r0[2]["weights"] == r0[1]["weights"] and r0[3]["weights"] != r0[2]["weights"]
 
 
 def test_sync_batchnorm_two_ranks_equals_single_process(tmp_path):
