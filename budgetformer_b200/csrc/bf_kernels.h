@@ -116,6 +116,16 @@ typedef struct {
   long long ldc;                    // destination row stride (elements)
   void* dst[BF_MAX_PEERS];
   int* status;                      // device int[4]; non-zero after a bounded wait expired
+  // Gathered A operand (n_src > 1; A / lda are then ignored and K = n_src * cols_per_src): columns
+  // [s * cols_per_src, (s + 1) * cols_per_src) of row r are row (src_row_offset + r) of src[s], a 16-bit matrix with
+  // row stride src_ld (elements) that may live in another GPU's memory (peer mapping).  cols_per_src % 16 == 0.
+  int n_src;
+  int cols_per_src;
+  const void* src[BF_MAX_PEERS];
+  long long src_row_offset;
+  long long src_ld;
+  void* a_copy;                     // optional local [M, K] matrix (row stride ld_copy) that receives the gathered operand
+  long long ld_copy;
 } bf_gemm_params;
 
 int bf_gemm_supported(int M, int N, int K);

@@ -355,6 +355,48 @@ void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, 
   check_cuda(bf_gemm_tn(&p, at::cuda::getCurrentCUDAStream()), "gemm_tn");
 }
 
+// C = gathered(A) @ W^T with the A operand pulled from `src_ptrs` (peer mappings) inside the GEMM; see bf_gemm_params.
+void gemm_tn_pull(std::vector<int64_t> src_ptrs, int64_t src_row_offset, int64_t src_ld, int64_t cols_per_src, int64_t M,
+                  Tensor W, OptTensor a_copy, OptTensor bias, double dropout_p, int64_t seed, OptTensor residual,
+                  double out_scale, Tensor out, Tensor status) {
+  TORCH_CHECK(W.is_cuda() && W.dim() == 2 && W.stride(1) == 1 &&
+              (W.scalar_type() == torch::kBFloat16 || W.scalar_type() == torch::kHalf), "gemm_tn_pull: W [N,K] 16-bit on CUDA");
+  TORCH_CHECK(src_ptrs.size() >= 2 && (int)src_ptrs.size() <= BF_MAX_PEERS, "gemm_tn_pull: 2..", BF_MAX_PEERS, " sources");
+  TORCH_CHECK((int64_t)src_ptrs.size() * cols_per_src == W.size(1), "gemm_tn_pull: sources x columns must equal K");
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(0) == M && out.size(1) == W.size(0) &&
+              out.scalar_type() == W.scalar_type(), "gemm_tn_pull: out [M,N] in the operand dtype");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt && status.numel() >= 4);
+  c10::cuda::CUDAGuard guard(W.device());
+  bf_gemm_params p{};
+  p.B = W.data_ptr(); p.ldb = W.stride(0);
+  p.M = (int)M; p.N = (int)W.size(0); p.K = (int)W.size(1);
+  p.dtype = dtype_code(W);
+  p.n_src = (int)src_ptrs.size(); p.cols_per_src = (int)cols_per_src; p.src_row_offset = src_row_offset; p.src_ld = src_ld;
+  for (size_t i = 0; i < src_ptrs.size(); ++i) p.src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+  if (a_copy.has_value()) {
+    TORCH_CHECK(a_copy->is_cuda() && a_copy->dim() == 2 && a_copy->stride(1) == 1 && a_copy->size(0) == M &&
+                a_copy->size(1) == W.size(1) && a_copy->scalar_type() == W.scalar_type(), "gemm_tn_pull: a_copy [M,K]");
+    p.a_copy = a_copy->data_ptr(); p.ld_copy = a_copy->stride(0);
+  }
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == torch::kFloat && bias->is_contiguous() && bias->numel() == p.N &&
+                ((uintptr_t)bias->data_ptr()) % 16 == 0, "gemm_tn_pull: bias must be contiguous fp32 [N], 16-byte aligned");
+    p.bias = bias->data_ptr<float>();
+  }
+  p.dropout_p = (float)dropout_p; p.dropout_seed = (uint32_t)seed;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == W.scalar_type() && residual->stride(1) == 1 && residual->size(0) == M &&
+                residual->size(1) == p.N && ((uintptr_t)residual->data_ptr()) % 16 == 0 && (residual->stride(0) * 2) % 16 == 0,
+                "gemm_tn_pull: residual [M,N], 16-byte aligned rows");
+    p.residual = residual->data_ptr(); p.ldr = residual->stride(0);
+  }
+  p.out_scale = (float)out_scale;
+  p.n_dest = 1; p.ldc = out.stride(0); p.dst[0] = out.data_ptr();
+  TORCH_CHECK((p.ldc * 2) % 16 == 0 && ((uintptr_t)p.dst[0]) % 16 == 0, "gemm_tn_pull: output rows must be 16-byte aligned");
+  p.status = status.data_ptr<int>();
+  check_cuda(bf_gemm_tn(&p, at::cuda::getCurrentCUDAStream()), "gemm_tn_pull");
+}
+
 std::vector<void*> as_ptrs(const std::vector<int64_t>& v) {
   std::vector<void*> o(BF_MAX_PEERS, nullptr);
   TORCH_CHECK(v.size() <= BF_MAX_PEERS, "at most ", BF_MAX_PEERS, " peers");
@@ -537,6 +579,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_attn_graph_rows_cpu", &build_attn_graph_rows_cpu);
   m.def("graph_transpose", &graph_transpose);
   m.def("gemm_tn", &gemm_tn);
+  m.def("gemm_tn_pull", &gemm_tn_pull);
   m.def("gemm_supported", &gemm_supported);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);

@@ -9,10 +9,13 @@ copies), the edge attention, a fourth all-to-all and the output projection
                 rank's packed ``[N, 3*h/P]`` buffer over NVLink — the nodes->heads all-to-all *is* the epilogue;
 ``attention``   the edge-attention kernels read q|k|v from that packed buffer and write the context into a
                 second symmetric buffer;
-``ctx pull``    each rank pulls its rows of every peer's context with peer loads and feeds the output
-                projection GEMM (bias, dropout and residual fused in its epilogue);
+``ctx pull``    the output-projection GEMM fetches its A operand - this rank's rows of every peer's context - with TMA
+                loads from the peers' memory while it multiplies the previous tile (bias, dropout and residual fused
+                in its epilogue): the heads->nodes all-to-all *is* the operand load.  A local copy of the pulled rows
+                is written from the same shared-memory stages only when the backward pass will need it;
 backward        mirrors it: the d(context) GEMM pushes to the head owners, the attention backward writes
-                dq|dk|dv packed, and the input-gradient GEMM consumes the pulled rows.
+                dq|dk|dv packed, and the input-gradient GEMM pulls its rows of every peer's dq|dk|dv the same way
+                (keeping the local copy that the weight-gradient GEMM reads).
 
 Device-side barriers (bounded spins) order producers and consumers; no host synchronisation and no NCCL
 call happens inside a layer.
@@ -85,6 +88,33 @@ class SPContext:
         return (x ^ (x >> 16)) & 0x7FFFFFFF
 
 
+# the pulled operand is fetched inside the GEMM (off: a separate peer-load gather kernel into a local matrix first)
+FUSE_PULL = True
+
+
+def _pull_gemm(src_ptrs, row0, src_ld, cols_per_src, rows, w, *, bias=None, residual=None, dropout_p=0.0, seed=0,
+               keep_copy=False):
+    """``y = drop(gathered @ w.T + bias) + residual`` where ``gathered[r, s*c:(s+1)*c] = src_s[row0 + r, :c]`` is pulled
+    from the sources inside the kernel.  Returns ``(y, gathered or None)``."""
+    ext = _ext.load()
+    k = len(src_ptrs) * cols_per_src
+    y = torch.empty((rows, w.size(0)), dtype=w.dtype, device=w.device)
+    copy = torch.empty((rows, k), dtype=w.dtype, device=w.device) if keep_copy else None
+    if bias is not None:
+        bias = bias.float().contiguous()
+        if bias.data_ptr() % 16:
+            bias = bias.clone()
+    ext.gemm_tn_pull(list(src_ptrs), int(row0), int(src_ld), int(cols_per_src), int(rows), w, copy, bias, float(dropout_p),
+                     int(seed), residual, 1.0, y, gemm.status_tensor(w.device))
+    _ext.count_launches(1)
+    return y, copy
+
+
+def _can_pull(sp, cols_per_src: int, rows: int, k: int, n: int, dtype) -> bool:
+    return (FUSE_PULL and sp.P > 1 and cols_per_src % 16 == 0 and gemm.supported(rows, n, k, dtype)
+            and _ext.load().gemm_supported(rows, n, k))
+
+
 def _push_gemm(x, w, bias, dst_ptrs, row0, ldc, dropout_p=0.0, seed=0):
     ext = _ext.load()
     if bias is not None:
@@ -121,7 +151,20 @@ class _QKVPush(torch.autograd.Function):
         buf = sp.dqkv
         if dqkv.data_ptr() != buf.tensor.data_ptr():
             buf.tensor.copy_(dqkv)
-        if sp.P > 1:
+        if dres is not None:
+            dres = dres.to(x.dtype).contiguous()
+        wt = w.t().contiguous()
+        dx = None
+        if _can_pull(sp, 3 * sp.hl, sp.rows_local, 3 * sp.h, sp.h, x.dtype):
+            # dX = pulled(dq|dk|dv) W: the rows arrive inside the GEMM; the local copy feeds the weight gradient.
+            # No barrier after the reads: the next writer of this buffer is the attention backward of the layer
+            # below, and every rank reaches the barrier that follows that layer's d(context) push (or scatter) only
+            # after this GEMM, so no peer can overwrite rows that are still being fetched.
+            sp.sw.barrier(0)                                         # every rank's dq|dk|dv is complete
+            dx, dloc = _pull_gemm(buf.ptrs, sp.row0, 3 * sp.hl, 3 * sp.hl, sp.rows_local, wt, residual=dres, keep_copy=True)
+            if debug.enabled():
+                sp.sw.barrier(0)                                     # poisoning below must wait for the peers' reads
+        elif sp.P > 1:
             sp.sw.barrier(0)                                         # every rank's dq|dk|dv is complete
             dloc = torch.empty((sp.rows_local, 3 * sp.h), dtype=x.dtype, device=x.device)
             _ext.load().peer_gather_cols(buf.ptrs, sp.row0, sp.rows_local, 3 * sp.hl * x.element_size(),
@@ -130,9 +173,8 @@ class _QKVPush(torch.autograd.Function):
             sp.sw.barrier(0)                                         # all reads done before the buffer is reused
         else:
             dloc = buf.tensor
-        if dres is not None:
-            dres = dres.to(x.dtype).contiguous()
-        dx = gemm.gemm_tn(dloc, w.t().contiguous(), residual=dres)
+        if dx is None:
+            dx = gemm.gemm_tn(dloc, wt, residual=dres)
         dw = torch.matmul(dloc.t(), x).float()[sp.inv_perm]
         db_src = column_sum(dloc) if ctx.has_bias else None
         if debug.enabled():
@@ -217,25 +259,35 @@ class _CtxPullOutProj(torch.autograd.Function):
     def forward(ctx, ctx_full, wo, bo, residual, sp: SPContext, p_pre, p_post, seed_pre, seed_post, slot=None,
                 pre_applied: bool = False):
         dt = ctx_full.dtype
-        if sp.P > 1:
-            sp.sw.barrier(0)                                         # every head owner has written its context
-            a = torch.empty((sp.rows_local, sp.h), dtype=dt, device=ctx_full.device)
-            esz = ctx_full.element_size()
-            _ext.load().peer_gather_cols(sp.ctx_ptrs_for(ctx_full), sp.row0, sp.rows_local, sp.hl * esz, sp.hl * esz, a)
-            _ext.count_launches(1)
-        else:
-            a = ctx_full
-        if p_pre > 0 and not pre_applied:           # pre_applied: the attention kernel already stored the dropped context
-            a = hash_dropout(a, seed_pre, p_pre)
-        if wo is not None:
+        pre_pending = p_pre > 0 and not pre_applied   # pre_applied: the attention kernel already stored the dropped context
+        if wo is not None and not pre_pending and _can_pull(sp, sp.hl, sp.rows_local, sp.h, wo.size(0), dt):
+            # the projection GEMM pulls its operand itself; a local copy is written only when a backward pass will
+            # read it (weight gradient)
             w = wo.to(dt)
-            y = gemm.gemm_tn(a, w, bo, None, dropout_p=p_post, dropout_seed=seed_post, residual=residual)
-            ctx.save_for_backward(a, w)
+            sp.sw.barrier(0)                                         # every head owner has written its context
+            y, a = _pull_gemm(sp.ctx_ptrs_for(ctx_full), sp.row0, sp.hl, sp.hl, sp.rows_local, w, bias=bo, residual=residual,
+                              dropout_p=p_post, seed=seed_post, keep_copy=any(ctx.needs_input_grad[:3]))
+            ctx.save_for_backward(a if a is not None else ctx_full.new_empty(0), w)
         else:
-            y = hash_dropout(a, seed_post, p_post) if p_post > 0 else a
-            if residual is not None:
-                y = y + residual
-            ctx.save_for_backward()
+            if sp.P > 1:
+                sp.sw.barrier(0)                                     # every head owner has written its context
+                a = torch.empty((sp.rows_local, sp.h), dtype=dt, device=ctx_full.device)
+                esz = ctx_full.element_size()
+                _ext.load().peer_gather_cols(sp.ctx_ptrs_for(ctx_full), sp.row0, sp.rows_local, sp.hl * esz, sp.hl * esz, a)
+                _ext.count_launches(1)
+            else:
+                a = ctx_full
+            if pre_pending:
+                a = hash_dropout(a, seed_pre, p_pre)
+            if wo is not None:
+                w = wo.to(dt)
+                y = gemm.gemm_tn(a, w, bo, None, dropout_p=p_post, dropout_seed=seed_post, residual=residual)
+                ctx.save_for_backward(a, w)
+            else:
+                y = hash_dropout(a, seed_post, p_post) if p_post > 0 else a
+                if residual is not None:
+                    y = y + residual
+                ctx.save_for_backward()
         ctx.sp, ctx.slot = sp, slot
         ctx.cfg = (float(p_pre), float(p_post), int(seed_pre), int(seed_post), residual is not None, wo is not None,
                    bo is not None, wo.dtype if wo is not None else None)
