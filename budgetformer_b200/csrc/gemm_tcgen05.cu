@@ -19,11 +19,12 @@
 //   instance covers everything else;
 // * with `n_src > 1` the A operand itself is gathered over NVLink: columns [s*K/n_src, (s+1)*K/n_src) of a row
 //   tile are this rank's rows of source s's buffer (the heads->nodes all-to-all of gt_sp/layer.py:280 and its
-//   backward twin).  The producer fetches them with plain (non-multicast) TMA loads from the peers' memory, one
-//   16-column box per MMA K step, straight into 32-byte-swizzled K-major operand panels, so the transfer of tile
-//   i+1 overlaps the multiplication of tile i and no gathered [M, K] matrix exists unless the caller asks for it:
-//   `a_copy` makes one more warp write every landed operand stage to a local row-major matrix with bulk stores
-//   (what the weight-gradient GEMM of the backward pass reads);
+//   backward twin).  One loader warp per ring stage fetches them with 16-byte asynchronous copies (cp.async from the
+//   peers' memory, lanes running along each source's contiguous rows so that a request covers whole 128-byte lines)
+//   straight to their place in the 128-byte-swizzled operand stage, so the transfer of tile i+1 overlaps the
+//   multiplication of tile i and no gathered [M, K] matrix exists unless the caller asks for it: `a_copy` makes one
+//   more warp write every landed operand stage to a local row-major matrix with bulk stores (what the
+//   weight-gradient GEMM of the backward pass reads);
 // * every mbarrier wait is bounded: on expiry the kernel records a status word, stops issuing work,
 //   lets copies in flight land, frees its tensor memory and returns.
 #include <cuda.h>
@@ -43,9 +44,10 @@ constexpr int BLOCK_K = 64;          // one 128-byte swizzle panel of 16-bit ele
 constexpr int UMMA_K = 16;
 constexpr int MAX_STAGES = 4;
 constexpr int NUM_THREADS = 576;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-17: epilogue (four column groups)
-constexpr int NUM_THREADS_COPY = 608;  // + warp 18: writes landed A stages to the local copy (gathered operand only)
-constexpr int PANEL_K = 16;          // columns of one gathered operand panel = one MMA K step (32-byte swizzle)
-constexpr uint32_t PANEL_BYTES = BLOCK_M * PANEL_K * 2;
+// gathered operand: + warp 18 (writes landed A stages to the local copy) + warps 19-22 (one loader per ring stage)
+constexpr int COPY_WARP = 18;
+constexpr int FIRST_LOADER_WARP = 19;
+constexpr int NUM_THREADS_PULL = (FIRST_LOADER_WARP + MAX_STAGES) * 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 struct GemmArgs {
@@ -82,18 +84,15 @@ struct GemmArgs {
   int panel_w;                   // columns per staged output panel: 64 (128-byte swizzle) or a destination's slice (unswizzled)
   // gathered A operand
   int n_src;                     // 1 = A is one local matrix
-  int cols_per_src;              // K / n_src, a multiple of 16
+  int cols_per_src;              // K / n_src, a multiple of 8
   long long src_row_offset;      // first row of this rank's block inside every source buffer
-  int a_copy;                    // 1: warp 18 stores every landed A stage to the local copy
+  long long src_ld;              // row stride of the source buffers (elements)
+  const void* src[BF_MAX_PEERS];
+  int a_copy;                    // 1: the copy warp stores every landed A stage to the local copy
 };
 
 struct OutMaps {
   CUtensorMap m[BF_MAX_PEERS];   // one per destination; row extent = dst_row_offset + M so that tail rows are clipped
-};
-
-struct SrcMaps {
-  CUtensorMap m[BF_MAX_PEERS];   // one per source of a gathered A operand: [src_row_offset + M, K / n_src], 16 x 128 boxes
-  CUtensorMap copy;              // local [M, K] copy of the gathered operand (same boxes)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -140,17 +139,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
   d |= (uint64_t)1 << 46;                               // descriptor version (sm_100)
   d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
-  return d;
-}
-
-// K-major operand panel of 16 columns, 32-byte swizzle: rows at 32-byte pitch, 8-row groups 256 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc_sw32(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(256 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)6 << 61;                               // SWIZZLE_32B
   return d;
 }
 
@@ -254,10 +242,10 @@ struct Control {
 // them from the arguments at run time (any dtype, any combination).
 constexpr int EPI_BIAS = 1, EPI_RELU = 2, EPI_GELU = 4, EPI_DROP = 8, EPI_RES = 16, EPI_MASK = 32, EPI_SCALE = 64;
 
-template <int EPI>
-__global__ void __launch_bounds__(NUM_THREADS_COPY, 1)
+template <int EPI, bool PULL>
+__global__ void __launch_bounds__(PULL ? NUM_THREADS_PULL : NUM_THREADS, 1)
 gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                       const __grid_constant__ OutMaps omaps, const __grid_constant__ SrcMaps smaps, const GemmArgs g) {
+                       const __grid_constant__ OutMaps omaps, const __grid_constant__ CUtensorMap map_copy, const GemmArgs g) {
   constexpr bool GEN = EPI < 0;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
@@ -280,8 +268,12 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             : (2 * g.block_n <= 256) ? 256 : 512;
 
   if (threadIdx.x == 0) {
-    // a stage is free again when its MMAs have retired and, with a local copy, when the copy warp has read it
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1 + (g.a_copy ? 1 : 0)); }
+    // gathered operand: a stage is full when the TMA bytes of B have landed and its loader warp has arrived; it is
+    // free again when its MMAs have retired and, with a local copy, when the copy warp has read it
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl->full[s], PULL ? 2 : 1);
+      mbar_init(&ctl->empty[s], 1 + ((PULL && g.a_copy) ? 1 : 0));
+    }
     for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 4 * g.n_groups); }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -310,18 +302,8 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const int m_tile = t / g.n_chunks, n_chunk = t % g.n_chunks;
         for (int kp = 0; kp < k_panels; ++kp) {
           if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          if (g.n_src > 1) {
-            // gathered operand: one 16-column box per K step, each from the source that owns those columns
-            const int k0 = kp * BLOCK_K;
-            const int n_pan = min(BLOCK_K, g.K - k0) / PANEL_K;
-            mbar_expect_tx(&ctl->full[stage], (uint32_t)n_pan * PANEL_BYTES + b_stage_bytes);
-            const int y = (int)(g.src_row_offset + (long long)m_tile * BLOCK_M);
-            for (int pn = 0; pn < n_pan; ++pn) {
-              const int col = k0 + pn * PANEL_K;
-              const int src = col / g.cols_per_src;
-              tma_load_2d(smem_a + stage * a_stage_bytes + pn * PANEL_BYTES, &smaps.m[src], &ctl->full[stage],
-                          col - src * g.cols_per_src, y);
-            }
+          if (PULL) {
+            mbar_expect_tx(&ctl->full[stage], b_stage_bytes);            // A arrives through the loader warps
           } else {
             mbar_expect_tx(&ctl->full[stage], a_stage_bytes + b_stage_bytes);
             tma_load_2d(smem_a + stage * a_stage_bytes, &map_a, &ctl->full[stage], kp * BLOCK_K, m_tile * BLOCK_M);
@@ -346,20 +328,13 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           if (!mbar_wait(&ctl->full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * b_stage_bytes));
-          if (g.n_src > 1) {
-            // gathered operand: every K step has its own 32-byte-swizzled panel; a short last stage has fewer of them
-            const int n_pan = min(BLOCK_K, g.K - kp * BLOCK_K) / PANEL_K;
-            for (int kk = 0; kk < n_pan; ++kk) {
-              const uint64_t adesc = make_smem_desc_sw32(smem_u32(smem_a + stage * a_stage_bytes + kk * PANEL_BYTES));
-              umma_f16(tmem_d, adesc, bdesc + 2 * kk, idesc, (kp > 0 || kk > 0) ? 1u : 0u);
-            }
-          } else {
-            const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * a_stage_bytes));
+          const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * a_stage_bytes));
+          // a gathered operand has no zero-filled tail: a short last stage issues fewer K steps
+          const int k_steps = PULL ? min(BLOCK_K, g.K - kp * BLOCK_K) / UMMA_K : BLOCK_K / UMMA_K;
 #pragma unroll
-            for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-              // advance 32 bytes (16 elements) along K inside the swizzle atom: +2 in 16-byte units
-              umma_f16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kp > 0 || kk > 0) ? 1u : 0u);
-            }
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            // advance 32 bytes (16 elements) along K inside the swizzle atom: +2 in 16-byte units
+            if (kk < k_steps) umma_f16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kp > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(&ctl->empty[stage]);
           if (++stage == (uint32_t)STAGES) { stage = 0; phase ^= 1u; }
@@ -370,7 +345,7 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       }
       if (!ok) { *abort_flag = 1; atomicExch(g.status, 2); }
     }
-  } else if (warp == 18) {
+  } else if (PULL && warp == COPY_WARP) {
     // ------------------------------------------------------------------ local copy of the gathered A operand
     if (lane == 0 && g.a_copy) {
       uint32_t stage = 0, phase = 0;
@@ -379,12 +354,10 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const int m_tile = t / g.n_chunks, n_chunk = t % g.n_chunks;
         for (int kp = 0; kp < k_panels; ++kp) {
           if (!mbar_wait(&ctl->full[stage], phase, abort_flag)) { ok = false; break; }
-          // the same row tile is fetched once per column chunk of the output: only the first visit is written out
+          // a row tile is fetched once per column chunk of the output: only the first visit is written out; columns
+          // past K and rows past M are outside the map and are clipped
           if (n_chunk == 0) {
-            const int k0 = kp * BLOCK_K;
-            const int n_pan = min(BLOCK_K, g.K - k0) / PANEL_K;
-            for (int pn = 0; pn < n_pan; ++pn)
-              tma_store_2d(&smaps.copy, smem_a + stage * a_stage_bytes + pn * PANEL_BYTES, k0 + pn * PANEL_K, m_tile * BLOCK_M);
+            tma_store_2d(&map_copy, smem_a + stage * a_stage_bytes, kp * BLOCK_K, m_tile * BLOCK_M);
             tma_store_commit();
             tma_store_wait_read<0>();
           }
@@ -394,6 +367,50 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       }
       tma_store_wait_all();
       if (!ok) { *abort_flag = 1; atomicExch(g.status, 4); }
+    }
+  } else if (PULL && warp >= FIRST_LOADER_WARP) {
+    // ------------------------------------------------------------------ loaders of the gathered A operand
+    // Loader j owns ring stage j (a waiter on a phase parity may never be more than one phase behind, so a stage is
+    // not shared between loaders).  Within a stage the 64 columns fall into segments that belong to one source each;
+    // the lanes run along a segment's rows, which are contiguous in the source when the segment is a whole row.
+    const int lw = warp - FIRST_LOADER_WARP;
+    if (lw < STAGES) {
+      bool ok = true;
+      long long it = 0;                                      // stage counter of this CTA
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m_tile = t / g.n_chunks;
+        const long long row_base = g.src_row_offset + (long long)m_tile * BLOCK_M;
+        const int rows_valid = min(BLOCK_M, g.M - m_tile * BLOCK_M);
+        for (int kp = 0; kp < k_panels; ++kp, ++it) {
+          if ((int)(it % STAGES) != lw) continue;
+          const uint32_t phase = (uint32_t)((it / STAGES) & 1);
+          if (!mbar_wait(&ctl->empty[lw], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* dst = smem_a + lw * a_stage_bytes;
+          const int k0 = kp * BLOCK_K;
+          const int k_end = min(g.K, k0 + BLOCK_K);
+          for (int col = k0; col < k_end;) {
+            const int src = col / g.cols_per_src;
+            const int seg_end = min(k_end, (src + 1) * g.cols_per_src);
+            const int wch = (seg_end - col) >> 3;            // 16-byte chunks per row of this segment
+            const int c0 = (col - k0) >> 3;                  // its first chunk inside the stage row
+            const unsigned short* base = static_cast<const unsigned short*>(g.src[src]) + (col - src * g.cols_per_src);
+            const int n = BLOCK_M * wch;
+            for (int q = lane; q < n; q += 32) {
+              const int r = q / wch, cc = q - r * wch;
+              // rows past M (tail tile) repeat the last valid row: their products are clipped by the epilogue
+              const int rr = r < rows_valid ? r : rows_valid - 1;
+              const int c = c0 + cc;
+              cp_async_16(dst + r * 128 + ((c ^ (r & 7)) << 4), base + (row_base + rr) * g.src_ld + cc * 8);
+            }
+            col = seg_end;
+          }
+          cp_async_wait_all();
+          fence_async_smem();                                // generic-proxy writes -> visible to the MMA and the bulk store
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->full[lw]);
+        }
+      }
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(g.status, 5); }
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (2..17)
@@ -682,7 +699,7 @@ EncodeTiledFn get_encode_fn() {
 // 2-D row-major 16-bit tensor [rows, cols] with row stride ld (elements); box = [box_rows, box_cols]; 64-column boxes
 // use the 128-byte swizzle, other widths are unswizzled.
 int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows,
-             int is_fp16, int box_cols = BLOCK_K, bool swizzle32 = false) {
+             int is_fp16, int box_cols = BLOCK_K) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -691,8 +708,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle32 ? CU_TENSOR_MAP_SWIZZLE_32B
-                            : box_cols == BLOCK_K ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  box_cols == BLOCK_K ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -2;
 }
@@ -714,7 +730,7 @@ extern "C" int bf_gemm_supported(int M, int N, int K) {
 extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   const bool gathered = p->n_src > 1;
   if (gathered) {
-    if (p->n_src > BF_MAX_PEERS || p->cols_per_src <= 0 || p->cols_per_src % PANEL_K != 0 ||
+    if (p->n_src > BF_MAX_PEERS || p->cols_per_src <= 0 || p->cols_per_src % 8 != 0 || p->K % UMMA_K != 0 ||
         p->K != p->n_src * p->cols_per_src || (p->src_ld * 2) % 16 != 0 || p->src_row_offset < 0)
       return (int)cudaErrorInvalidValue;
     for (int i = 0; i < p->n_src; ++i)
@@ -764,16 +780,14 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   g.src_row_offset = gathered ? p->src_row_offset : 0;
   g.a_copy = (gathered && p->a_copy) ? 1 : 0;
   CUtensorMap map_a, map_b;
-  SrcMaps smaps;
-  memset(&smaps, 0, sizeof(smaps));
+  CUtensorMap map_copy;
+  memset(&map_copy, 0, sizeof(map_copy));
   memset(&map_a, 0, sizeof(map_a));
+  g.src_ld = gathered ? p->src_ld : 0;
+  for (int i = 0; i < BF_MAX_PEERS; ++i) g.src[i] = (gathered && i < p->n_src) ? p->src[i] : nullptr;
   if (gathered) {
-    // rows past this rank's block are outside the map: the tail of the last row tile reads zeros
-    for (int i = 0; i < p->n_src; ++i)
-      if (make_map(&smaps.m[i], p->src[i], p->src_row_offset + p->M, p->cols_per_src, p->src_ld, BLOCK_M, g.is_fp16,
-                   PANEL_K, true) != 0)
-        return (int)cudaErrorNotSupported;
-    if (g.a_copy && make_map(&smaps.copy, p->a_copy, p->M, p->K, p->ld_copy, BLOCK_M, g.is_fp16, PANEL_K, true) != 0)
+    // 64-column boxes with the 128-byte swizzle of the operand stage; rows past M and columns past K are clipped
+    if (g.a_copy && make_map(&map_copy, p->a_copy, p->M, p->K, p->ld_copy, BLOCK_M, g.is_fp16) != 0)
       return (int)cudaErrorNotSupported;
   } else if (make_map(&map_a, p->A, p->M, p->K, p->lda, BLOCK_M, g.is_fp16) != 0) {
     return (int)cudaErrorNotSupported;
@@ -835,23 +849,31 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
     else if ((f | EPI_SCALE) == (EPI_MASK | EPI_SCALE)) epi = EPI_MASK | EPI_SCALE;
     else if (f == EPI_SCALE) epi = EPI_SCALE;
   }
-  void (*kern)(const CUtensorMap, const CUtensorMap, const OutMaps, const SrcMaps, const GemmArgs) = gemm_tn_tcgen05_kernel<-1>;
-  switch (epi) {
-    case 0: kern = gemm_tn_tcgen05_kernel<0>; break;
-    case EPI_BIAS: kern = gemm_tn_tcgen05_kernel<EPI_BIAS>; break;
-    case EPI_BIAS | EPI_DROP | EPI_RES: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_DROP | EPI_RES>; break;
-    case EPI_BIAS | EPI_RELU | EPI_DROP: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_RELU | EPI_DROP>; break;
-    case EPI_MASK | EPI_SCALE: kern = gemm_tn_tcgen05_kernel<EPI_MASK | EPI_SCALE>; break;
-    case EPI_SCALE: kern = gemm_tn_tcgen05_kernel<EPI_SCALE>; break;
-    default: break;
+  using Kern = void (*)(const CUtensorMap, const CUtensorMap, const OutMaps, const CUtensorMap, const GemmArgs);
+  Kern kern = gemm_tn_tcgen05_kernel<-1, false>;
+  if (gathered) {
+    // gathered operand: the output projection's epilogue is specialised, the input-gradient GEMM takes the generic one
+    if (epi != (EPI_BIAS | EPI_DROP | EPI_RES)) epi = -1;
+    kern = epi < 0 ? (Kern)gemm_tn_tcgen05_kernel<-1, true> : (Kern)gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_DROP | EPI_RES, true>;
+  } else {
+    switch (epi) {
+      case 0: kern = gemm_tn_tcgen05_kernel<0, false>; break;
+      case EPI_BIAS: kern = gemm_tn_tcgen05_kernel<EPI_BIAS, false>; break;
+      case EPI_BIAS | EPI_DROP | EPI_RES: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_DROP | EPI_RES, false>; break;
+      case EPI_BIAS | EPI_RELU | EPI_DROP: kern = gemm_tn_tcgen05_kernel<EPI_BIAS | EPI_RELU | EPI_DROP, false>; break;
+      case EPI_MASK | EPI_SCALE: kern = gemm_tn_tcgen05_kernel<EPI_MASK | EPI_SCALE, false>; break;
+      case EPI_SCALE: kern = gemm_tn_tcgen05_kernel<EPI_SCALE, false>; break;
+      default: break;
+    }
   }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   {
     // the attribute belongs to (function, device): remember it per device, not per process
     constexpr int MAX_DEV = 64;
-    static bool attr_set[MAX_DEV][8] = {};
-    const int slot = epi < 0 ? 0 : epi == 0 ? 1 : epi == EPI_BIAS ? 2 : epi == (EPI_BIAS | EPI_DROP | EPI_RES) ? 3
+    static bool attr_set[MAX_DEV][10] = {};
+    const int slot = gathered ? (epi < 0 ? 8 : 9)
+                     : epi < 0 ? 0 : epi == 0 ? 1 : epi == EPI_BIAS ? 2 : epi == (EPI_BIAS | EPI_DROP | EPI_RES) ? 3
                      : epi == (EPI_BIAS | EPI_RELU | EPI_DROP) ? 4 : epi == EPI_SCALE ? 6 : 5;
     if (dev < 0 || dev >= MAX_DEV || !attr_set[dev][slot]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -862,6 +884,6 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int total = g.m_tiles * g.n_chunks;
   const int grid = total < sms ? total : sms;
-  kern<<<grid, g.a_copy ? NUM_THREADS_COPY : NUM_THREADS, smem, st>>>(map_a, map_b, omaps, smaps, g);
+  kern<<<grid, gathered ? NUM_THREADS_PULL : NUM_THREADS, smem, st>>>(map_a, map_b, omaps, map_copy, g);
   return (int)cudaGetLastError();
 }
