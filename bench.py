@@ -30,6 +30,25 @@ GRAPH_DESC = {"dag": "citation-like DAG (power-law out-degree)", "chung_lu_direc
               "chung_lu_undirected": "Chung-Lu power-law undirected graph", "sbm": "stochastic block model"}
 sys.path.insert(0, REPO)
 
+# Epoch time of the reference arm (unmodified reference + pure-PyTorch stand-ins for its native wheels, its own NCCL
+# and cuBLAS path) on configuration patents_like, driver-measured on this pool's B200s with this file's
+# `--impl reference` (20 timed epochs): ms per epoch by number of GPUs.  The reference publishes no numbers of its
+# own, so `vs_baseline` is this arm's epoch time over ours at the same GPU count.
+REFERENCE_EPOCH_MS = {"patents_like": {1: 5089.0, 2: 3388.5, 4: 1707.0, 8: 1455.5}}
+
+
+def config_record(name, cfg, n_nodes, n_edges, feat_dim, world, ckpt, scale):
+    """The `config` object of the JSON line; both arms emit exactly these keys."""
+    b = int(cfg["budget"])
+    return {"name": name,
+            "model": f"{MODEL_NAMES.get(cfg['model'], cfg['model'])} L{cfg['n_layers']} h{cfg['hidden_dim']} H{cfg['num_heads']}",
+            "nodes": int(n_nodes), "edges": int(n_edges), "global_batch": int(n_nodes), "seq_len": int(n_nodes),
+            "feat_dim": int(feat_dim),
+            "budget": f"{(b + 1) // 2} real + {b // 2} random-walk per query (B={b} ceiling of the adaptive search), "
+                      f"rebuilt every epoch",
+            "parallelism": f"sp{world}", "activation_checkpoint": ckpt or "none (retain)", "scale": scale,
+            "l2": "working set per step (>= 750 MB activations per layer) exceeds the 126 MB L2; no flush needed"}
+
 
 def parse():
     ap = argparse.ArgumentParser()
@@ -208,18 +227,16 @@ def run_ours(ns):
             "n_gpus": world, "steps": ns.steps, "warmup": max(3, ns.warmup), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": f"synthetic {GRAPH_DESC.get(cfg['graph'], cfg['graph'])}, N(0,1) features, random-init weights",
-            "impl": "ours",
-            "config": {"name": ns.config, "model": f"{MODEL_NAMES.get(cfg['model'], cfg['model'])} L{cfg['n_layers']} "
-                                                  f"h{cfg['hidden_dim']} H{cfg['num_heads']}", "nodes": n,
-                       "edges": int(ei.size(1)), "global_batch": n, "seq_len": n, "feat_dim": int(x.size(1)),
-                       "budget": f"{(int(cfg['budget']) + 1) // 2} real + {int(cfg['budget']) // 2} random-walk per query "
-                                 f"(B={cfg['budget']} ceiling of the adaptive search), rebuilt every epoch",
-                       "parallelism": f"sp{world}", "fused_sp": bool(trainer.fused_sp),
-                       "activation_checkpoint": ns.ckpt or "none (retain)", "scale": ns.scale,
-                       "l2": "working set per step (>= 750 MB activations per layer) exceeds the 126 MB L2; no flush needed"},
+            "impl": "ours", "fused_sp": bool(trainer.fused_sp),
+            "config": config_record(ns.config, cfg, n, int(ei.size(1)), int(x.size(1)), world, ns.ckpt, ns.scale),
             "epoch_ms": ms_step, "peak_hbm_mib_per_gpu": peak, "gpu_launches": launches,
             "clocks": sampler.summary(t_begin, t_end),
         }
+        ref_ms = REFERENCE_EPOCH_MS.get(ns.config, {}).get(world) if ns.scale == 1.0 else None
+        if ref_ms:
+            rec["vs_baseline"] = ref_ms / ms_step
+            rec["baseline_source"] = (f"reference arm of this file (unmodified reference + stand-ins for its native wheels) "
+                                      f"at {world} GPU(s): {ref_ms} ms per epoch; the reference publishes no numbers")
         if e2e_ms is not None:
             e_step = e2e_ms_max / ns.steps
             rec["e2e"] = {"value": n / (e_step / 1e3), "unit": "nodes/s", "ms_per_step": e_step,
@@ -276,7 +293,7 @@ def run_reference(ns):
     except Exception as e:  # pragma: no cover
         print(json.dumps({"impl": "reference", "unavailable": f"baseline harness not importable: {type(e).__name__}: {e}"}))
         return
-    run(ns)
+    run(ns, config_record)
 
 
 if __name__ == "__main__":

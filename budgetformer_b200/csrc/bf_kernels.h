@@ -131,6 +131,28 @@ typedef struct {
 int bf_gemm_supported(int M, int N, int K);
 int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st);
 
+// ---- tcgen05 weight-gradient GEMM (gemm_dw_tcgen05.cu) ----------------------------------------------
+// dW[N, K] (= or +=) scale * dY[M, N]^T X[M, K]; dbias[N] (= or +=) scale * column sums of dY (optional).
+typedef struct {
+  const void* dY;                   // [M, N] 16-bit, row stride ldy (elements), 16-byte aligned rows
+  const void* X;                    // [M, K] 16-bit, row stride ldx
+  long long ldy, ldx;
+  long long M;
+  int N, K;                         // both multiples of 8
+  int dtype;                        // BF_BF16 or BF_FP16
+  float* dW;                        // [N, K] fp32 contiguous
+  float* dbias;                     // [N] fp32 or NULL; needs bf_gemm_dw_bias_supported(K)
+  int accumulate;                   // 0: overwrite, 1: add to what dW / dbias hold
+  float scale;                      // 0 means 1
+  void* scratch;                    // bf_gemm_dw_scratch_bytes(M, N, K) bytes of device memory
+  int* status;                      // device int[4]; non-zero after a bounded wait expired
+} bf_gemm_dw_params;
+
+int bf_gemm_dw_supported(long long M, int N, int K);
+int bf_gemm_dw_bias_supported(int K);
+size_t bf_gemm_dw_scratch_bytes(long long M, int N, int K);
+int bf_gemm_dw(const bf_gemm_dw_params* p, cudaStream_t st);
+
 // ---- peer-memory collectives (symm_comm.cu) ----------------------------------------------------
 // `flag_pages[r]` / `bufs[r]` are this process's mappings of rank r's symmetric allocation.
 int bf_peer_barrier(void* const* flag_pages, int rank, int world, int channel, uint32_t epoch, int* status,

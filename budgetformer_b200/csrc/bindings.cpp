@@ -397,6 +397,36 @@ void gemm_tn_pull(std::vector<int64_t> src_ptrs, int64_t src_row_offset, int64_t
   check_cuda(bf_gemm_tn(&p, at::cuda::getCurrentCUDAStream()), "gemm_tn_pull");
 }
 
+// dW = dY^T X (fp32 [N, K]) and, with `want_bias`, the column sums of dY (fp32 [N]) from the same kernel.
+std::vector<Tensor> gemm_dw(Tensor dY, Tensor X, bool want_bias, Tensor status) {
+  TORCH_CHECK(dY.is_cuda() && X.is_cuda() && dY.dim() == 2 && X.dim() == 2 && dY.size(0) == X.size(0), "gemm_dw: dY [M,N], X [M,K]");
+  TORCH_CHECK(dY.scalar_type() == X.scalar_type() && (dY.scalar_type() == torch::kBFloat16 || dY.scalar_type() == torch::kHalf),
+              "gemm_dw: bf16/fp16 operands");
+  TORCH_CHECK(dY.stride(1) == 1 && X.stride(1) == 1, "gemm_dw: feature-contiguous operands");
+  c10::cuda::CUDAGuard guard(dY.device());
+  bf_gemm_dw_params p{};
+  p.dY = dY.data_ptr(); p.X = X.data_ptr(); p.ldy = dY.stride(0); p.ldx = X.stride(0);
+  p.M = dY.size(0); p.N = (int)dY.size(1); p.K = (int)X.size(1);
+  p.dtype = dtype_code(dY);
+  TORCH_CHECK(bf_gemm_dw_supported(p.M, p.N, p.K), "gemm_dw: unsupported shape");
+  TORCH_CHECK(!want_bias || bf_gemm_dw_bias_supported(p.K), "gemm_dw: bias gradient not available for K = ", p.K);
+  auto f32 = torch::TensorOptions().dtype(torch::kFloat).device(dY.device());
+  Tensor dW = torch::empty({p.N, p.K}, f32);
+  Tensor db = want_bias ? torch::empty({p.N}, f32) : Tensor();
+  Tensor scratch = torch::empty({(int64_t)(bf_gemm_dw_scratch_bytes(p.M, p.N, p.K) / 4)}, f32);
+  p.dW = dW.data_ptr<float>();
+  p.dbias = want_bias ? db.data_ptr<float>() : nullptr;
+  p.scratch = scratch.data_ptr();
+  p.status = status.data_ptr<int>();
+  check_cuda(bf_gemm_dw(&p, at::cuda::getCurrentCUDAStream()), "gemm_dw");
+  if (want_bias) return {dW, db};
+  return {dW};
+}
+
+bool gemm_dw_supported(int64_t M, int64_t N, int64_t K, bool want_bias) {
+  return bf_gemm_dw_supported(M, (int)N, (int)K) != 0 && (!want_bias || bf_gemm_dw_bias_supported((int)K) != 0);
+}
+
 std::vector<void*> as_ptrs(const std::vector<int64_t>& v) {
   std::vector<void*> o(BF_MAX_PEERS, nullptr);
   TORCH_CHECK(v.size() <= BF_MAX_PEERS, "at most ", BF_MAX_PEERS, " peers");
@@ -580,6 +610,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("graph_transpose", &graph_transpose);
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_tn_pull", &gemm_tn_pull);
+  m.def("gemm_dw", &gemm_dw);
+  m.def("gemm_dw_supported", &gemm_dw_supported);
   m.def("gemm_supported", &gemm_supported);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);

@@ -13,7 +13,7 @@ import torch
 import torch.nn.functional as F
 
 from . import gemm
-from .norm import column_sum, hash_dropout, new_seed
+from .norm import hash_dropout, new_seed
 
 
 # the ReLU mask travels from forward to backward as one bit per hidden element (off: the backward re-reads h)
@@ -51,13 +51,15 @@ class _FusedFFNRelu(torch.autograd.Function):
         else:
             dh = gemm.gemm_tn(g2, w2h.t().contiguous(), relu_mask=h, out_scale=scale)
         dx = gemm.gemm_tn(dh, w1h.t().contiguous(), residual=dy if res_is_x else None)
-        dw2 = torch.matmul(g2.t(), h).to(wdtype)
-        dw1 = torch.matmul(dh.t(), x).to(wdtype)
+        # weight gradients on the tcgen05 reduction kernel; a bias gradient rides along as one more accumulator column
+        # unless the LayerNorm behind this block already produced it (handed) or the kernel has no column to spare
+        need_db2 = has_b2 and not (handed is not None and p2 == 0)
+        dw2, db2 = gemm.weight_grad(g2, h, need_db2)
+        dw1, db1 = gemm.weight_grad(dh, x, has_b1)
+        dw2, dw1 = dw2.to(wdtype), dw1.to(wdtype)
         if has_b2:
-            db2 = (handed if (handed is not None and p2 == 0) else column_sum(g2)).to(wdtype)
-        else:
-            db2 = None
-        db1 = column_sum(dh).to(wdtype) if has_b1 else None
+            db2 = (db2 if need_db2 else handed).to(wdtype)
+        db1 = db1.to(wdtype) if has_b1 else None
         dres = dy if (has_res and not res_is_x) else None
         return dx, dw1, db1, dw2, db2, dres, None, None, None, None, None
 

@@ -175,8 +175,8 @@ class _QKVPush(torch.autograd.Function):
             dloc = buf.tensor
         if dx is None:
             dx = gemm.gemm_tn(dloc, wt, residual=dres)
-        dw = torch.matmul(dloc.t(), x).float()[sp.inv_perm]
-        db_src = column_sum(dloc) if ctx.has_bias else None
+        dw, db_src = gemm.weight_grad(dloc, x, ctx.has_bias)
+        dw = dw[sp.inv_perm]
         if debug.enabled():
             debug.poison(buf.tensor)                  # consumed: whoever reads it before the next producer sees NaN
         dwq, dwk, dwv = (t.to(ctx.wdtype) for t in dw.split(sp.h, 0))
@@ -306,9 +306,11 @@ class _CtxPullOutProj(torch.autograd.Function):
             a, w = ctx.saved_tensors
             # d(context) = (g W_o) [* pre-dropout mask], pushed to the head owners by the GEMM epilogue
             _push_gemm(g, w.t().contiguous(), None, dbuf.ptrs, sp.row0, sp.hl, dropout_p=p_pre, seed=seed_pre)
-            dw = torch.matmul(g.t(), a).to(wdtype)
+            need_db = has_b and not (handed is not None and p_post == 0)
+            dw, db = gemm.weight_grad(g, a, need_db)
+            dw = dw.to(wdtype)
             if has_b:
-                db = (handed if (handed is not None and p_post == 0) else column_sum(g)).to(wdtype)
+                db = (db if need_db else handed).to(wdtype)
         else:
             da = hash_dropout(g, seed_pre, p_pre) if p_pre > 0 else g
             esz = da.element_size()

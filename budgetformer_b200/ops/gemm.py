@@ -1,10 +1,9 @@
-"""Linear layers on the tcgen05 GEMM (``csrc/gemm_tcgen05.cu``).
+"""Linear layers on the tcgen05 GEMMs (``csrc/gemm_tcgen05.cu``, ``csrc/gemm_dw_tcgen05.cu``).
 
-``gemm_tn`` is the raw call ``C = A @ W.T`` with the fused epilogue; ``fused_linear`` is the autograd
-function used by the models on B200: forward and the input-gradient GEMM run on the tcgen05 kernel,
-the weight gradient ``dW = dY^T X`` (a plain tall-skinny reduction without any fusion opportunity) uses
-the library GEMM.  Shapes the kernel does not cover (K not a multiple of 8, N not a multiple of 16,
-fp32 operands) fall back to ``torch.nn.functional.linear``."""
+``gemm_tn`` is the raw call ``C = A @ W.T`` with the fused epilogue; ``weight_grad`` is ``dW = dY^T X`` together
+with the bias gradient (column sums of ``dY``) from one pass over the operands; ``fused_linear`` is the autograd
+function used by the models on B200: forward, input gradient and weight gradient all run on the tcgen05 kernels.
+Shapes the kernels do not cover (features not a multiple of 8 / 16, fp32 operands) fall back to PyTorch."""
 from __future__ import annotations
 
 from typing import Optional
@@ -66,6 +65,29 @@ def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     return out
 
 
+def weight_grad(dy: torch.Tensor, x: torch.Tensor, want_bias: bool = False):
+    """``(dy.T @ x, dy.sum(0) or None)`` in fp32.  One tcgen05 kernel reads both operands once (MN-major tiles straight
+    from the row-major matrices) and leaves per-row-slice partial tiles that a second kernel adds in a fixed order; the
+    bias gradient is one more accumulator column of the same kernel.  Falls back to PyTorch for shapes outside the
+    kernel's reach (features not a multiple of 8, operands that are not 16-bit)."""
+    ext = _ext.load()
+    m, n, k = dy.size(0), dy.size(1), x.size(1)
+    ok = (dy.is_cuda and dy.dtype in (torch.bfloat16, torch.float16) and x.dtype == dy.dtype and m > 0
+          and dy.stride(1) == 1 and x.stride(1) == 1 and (dy.stride(0) * 2) % 16 == 0 and (x.stride(0) * 2) % 16 == 0
+          and dy.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0 and ext.gemm_dw_supported(m, n, k, False))
+    if not ok:
+        dw = torch.matmul(dy.t(), x).float()
+        return dw, (dy.float().sum(0) if want_bias else None)
+    fused_bias = bool(want_bias and ext.gemm_dw_supported(m, n, k, True))
+    out = ext.gemm_dw(dy, x, fused_bias, status_tensor(dy.device))
+    _ext.count_launches(3 if fused_bias else 2)
+    db = out[1] if fused_bias else None
+    if want_bias and db is None:
+        from .norm import column_sum
+        db = column_sum(dy)
+    return out[0], db
+
+
 def hash_keep_mask(seed: int, rows: int, cols: int, p: float, device) -> torch.Tensor:
     """The epilogue's dropout keep mask, restated in PyTorch (tests and the fallback path)."""
     r = torch.arange(rows, device=device, dtype=torch.int64)[:, None]
@@ -78,7 +100,7 @@ def hash_keep_mask(seed: int, rows: int, cols: int, p: float, device) -> torch.T
 
 
 class _FusedLinear(torch.autograd.Function):
-    """y = residual + dropout(x W^T + b): one GEMM forward, one GEMM (dx) + one library GEMM (dW) backward."""
+    """y = residual + dropout(x W^T + b): one GEMM forward; input-gradient GEMM + weight-gradient GEMM backward."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, residual, dropout_p, dropout_seed):
@@ -90,16 +112,15 @@ class _FusedLinear(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from .norm import column_sum, hash_dropout
+        from .norm import hash_dropout
         x, w16 = ctx.saved_tensors
         has_res, p, seed, wdtype, has_bias = ctx.cfg
         dy = dy.contiguous()
         g = hash_dropout(dy, seed, p) if p > 0 else dy
         # dx = g @ W, expressed as g @ (W^T)^T; skipped for leaf inputs such as the feature matrix
         dx = gemm_tn(g, w16.t().contiguous()) if ctx.needs_input_grad[0] else None
-        dw = torch.matmul(g.t(), x).to(wdtype)
-        db = column_sum(g).to(wdtype) if has_bias else None
-        return dx, dw, db, (dy if has_res else None), None, None
+        dw, db = weight_grad(g, x, has_bias)
+        return dx, dw.to(wdtype), (db.to(wdtype) if has_bias else None), (dy if has_res else None), None, None
 
 
 def fused_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,

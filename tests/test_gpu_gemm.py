@@ -308,3 +308,46 @@ def test_gemm_pulls_operand_column_slices_from_sources(n_src, cps, n, row0, copy
     assert (out.float() - ref).abs().max() < 0.06
     if copy:
         assert torch.equal(a_copy, gathered)
+
+
+@pytest.mark.parametrize("m,n,k,bias", [
+    (5000, 384, 128, True),      # packed q|k|v projection: three 128-feature tiles of dY
+    (3333, 128, 128, True),      # output projection, ragged row count
+    (4097, 256, 128, True),      # first FFN layer
+    (2500, 128, 256, False),     # second FFN layer: 256 features of X leave no accumulator column for the bias
+    (1111, 128, 272, True),      # feature encoder: two column chunks of X (256 + 16), bias rides with the second
+    (777, 64, 128, True),        # readout: fewer than 128 features of dY (the tile's upper half is zero-filled)
+    (50, 32, 64, True),          # fewer rows than one ring stage
+    (200000, 128, 192, True),    # many row slices; 192 features of X is the widest chunk that still carries the bias
+])
+def test_weight_gradient_gemm_matches_fp32_reference(m, n, k, bias):
+    """dW = dY^T X (+ column sums of dY) on the MN-major tcgen05 kernel against a float32 matmul of the same bf16
+    operands.  fp32 accumulation in both: the difference is summation order."""
+    torch.manual_seed(5)
+    dy = torch.randn(m, n, device="cuda").bfloat16()
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    dw, db = gemm.weight_grad(dy, x, bias)
+    gemm.check_status("cuda")
+    ref = dy.float().t() @ x.float()
+    tol = 2e-3 * (m ** 0.5) + 1e-3
+    assert dw.dtype == torch.float32 and dw.shape == (n, k)
+    assert (dw - ref).abs().max() < tol, float((dw - ref).abs().max())
+    if bias:
+        assert (db - dy.float().sum(0)).abs().max() < tol
+    else:
+        assert db is None
+    # bit-reproducible: slices are added in a fixed order
+    dw2, _ = gemm.weight_grad(dy, x, bias)
+    assert torch.equal(dw, dw2)
+
+
+def test_weight_gradient_gemm_on_strided_views():
+    """Operands that are column slices of wider matrices (row stride > width), as the packed q|k|v gradients are."""
+    torch.manual_seed(6)
+    m = 3000
+    big = torch.randn(m, 512, device="cuda").bfloat16()
+    dy, x = big[:, 128:256], big[:, 256:384]
+    dw, db = gemm.weight_grad(dy, x, True)
+    gemm.check_status("cuda")
+    assert (dw - dy.float().t() @ x.float()).abs().max() < 0.2
+    assert (db - dy.float().sum(0)).abs().max() < 0.2

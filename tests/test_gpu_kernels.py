@@ -164,3 +164,32 @@ def test_batch_norm_kernels_match_pytorch(dtype):
     assert (bn.bias.grad - ref.bias.grad).abs().max() < ptol * ref.bias.grad.abs().max() + 5e-2
     bn.eval(); ref.eval()
     assert (batch_norm(x, bn).float() - ref(x.float())).abs().max() < tol
+
+
+@pytest.mark.parametrize("variant", ["plain", "gps", "exphormer"])
+def test_edge_attention_kernels_against_coo_oracle(variant):
+    """Forward and backward of the CUDA kernels against the float32 oracle written on the reference's COO layout
+    (hub row and hub key included)."""
+    from budgetformer_b200 import oracle
+    from tests.helpers import random_attn_graph
+    torch.manual_seed(12)
+    n, h, hn = 700, 4, 16
+    g = random_attn_graph(n, 5000, hub_row=1500, hub_col=1400, seed=8, typed=variant == "exphormer").to("cuda")
+    ei = g.edge_index()
+    q, k, v = (torch.randn(n, h, hn, device="cuda", requires_grad=True) for _ in range(3))
+    emb = torch.randn(2, h * hn, device="cuda")
+    proj = torch.randn(h * hn, h * hn, device="cuda") * 0.1
+    table = (emb @ proj.t()).view(2, h, hn) if variant == "exphormer" else None
+    out = edge_attention(q, k, v, g, variant=variant, etable=table)
+    if variant == "plain":
+        ref = oracle.attention.sparse_attention(q, k, v, ei)
+    elif variant == "gps":
+        ref = oracle.attention.gps_attention(q, k, v, ei)
+    else:
+        ref = oracle.attention.exphormer_attention(q, k, v, ei, emb, proj)
+    assert torch.allclose(out, ref, atol=2e-4, rtol=2e-4), float((out - ref).abs().max())
+    dout = torch.randn_like(out)
+    got = torch.autograd.grad(out, (q, k, v), dout)
+    want = torch.autograd.grad(ref, (q, k, v), dout)
+    for a, b, name in zip(got, want, "qkv"):
+        assert torch.allclose(a, b, atol=5e-4, rtol=1e-3), (name, float((a - b).abs().max()))
