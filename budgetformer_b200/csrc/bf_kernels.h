@@ -62,6 +62,11 @@ typedef struct {
   const int* kv_split;              // [n_kv_split, 3] int32: key row, first slot, slot count
   int n_kv_split;
   float* kv_partial;                // [total slots, 2*hl*hn] fp32 scratch
+  // Optional workspace for narrow rows (hl*hn elements of 64 bytes or less), used with kv_task: the dQ pass leaves one
+  // contiguous record [q | dout / (Z + eps)] per (row, head) in qg and D / (Z + eps) in cz, and the dK/dV pass gathers
+  // those instead of q, dout and zd separately.
+  void* qg;                         // [n, hl, 2, hn] in the operand dtype, or NULL
+  float* cz;                        // [n, hl] fp32, or NULL
 } bf_attn_bwd_params;
 
 int bf_edge_attn_fwd(const bf_attn_params* p, cudaStream_t st);

@@ -1,8 +1,8 @@
 // Allocation-free entry point.  This has no counterpart in the reference implementation (which is pure
 // Python and lets PyTorch allocate everything); it exists for hosts that embed these kernels but must not
-// allocate device memory themselves at call time: code running while a CUDA graph is being replayed under a
-// fixed memory plan, a serving loop whose memory pool is sized and frozen at start-up, or a plugin that is only
-// handed pre-allocated tensors by its host application and has no allocator of its own.
+// allocate device memory themselves at call time: a serving loop whose memory pool is sized and frozen at
+// start-up, or a plugin that is only handed pre-allocated tensors by its host application and has no allocator
+// of its own.
 //
 //   int bf_edge_attn_fwd_noalloc(const bf_attn_params* p, cudaStream_t stream);
 //
@@ -15,6 +15,8 @@
 // Limits (rejected with BF_NOALLOC_ERR_TOO_LARGE, nothing is launched):
 //   p->n_hub            <= BF_NOALLOC_MAX_HUBS
 //   p->hl * p->hn       <= BF_NOALLOC_MAX_WIDTH   (and p->hl <= BF_NOALLOC_MAX_HEADS)
+// Arguments the kernels cannot take (an unsupported dtype or head size, n_hub > 0 without hub_rows or without
+// max_hub_degree) return cudaErrorInvalidValue, also before anything is queued on the stream.
 // The array occupies BF_NOALLOC_SCRATCH_BYTES (about 272 KiB) on every GPU that loads the library, until the
 // process exits.
 //
@@ -46,6 +48,10 @@ int bf_edge_attn_fwd_noalloc(const bf_attn_params* p, cudaStream_t stream);
 
 // Human-readable text for a return value of bf_edge_attn_fwd_noalloc.
 const char* bf_noalloc_strerror(int code);
+
+// sizeof(bf_attn_params) as this library was compiled: a caller that mirrors the struct by hand (ctypes, another
+// language's FFI) can check its own layout against it before the first call.
+size_t bf_attn_params_size(void);
 
 #ifdef __cplusplus
 }

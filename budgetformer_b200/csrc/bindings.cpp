@@ -120,7 +120,13 @@ void edge_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor do
   HubInfo hub = find_hubs(rowptr, known_max_degree);
   const bool use_tasks = kv_task.has_value() && kv_task->numel() > 0;
   HubInfo thub = use_tasks ? HubInfo() : find_hubs(t_rowptr, -1);
-  Tensor sq, skv, partial;
+  Tensor sq, skv, partial, qg, cz;
+  if (use_tasks && (int64_t)p.hl * p.hn * q.element_size() <= 64) {
+    // narrow rows: one packed record per (query, head) for the dK/dV pass (see bf_attn_bwd_params)
+    qg = torch::empty({q.size(0), (int64_t)p.hl, 2, (int64_t)p.hn}, q.options());
+    cz = torch::empty({q.size(0), (int64_t)p.hl}, q.options().dtype(torch::kFloat));
+    b.qg = qg.data_ptr(); b.cz = cz.data_ptr<float>();
+  }
   if (use_tasks) {
     TORCH_CHECK(kv_task->scalar_type() == torch::kInt && kv_task->is_contiguous() && kv_task->size(1) == 4 &&
                 ((uintptr_t)kv_task->data_ptr()) % 16 == 0, "kv_task must be contiguous int32 [T, 4]");

@@ -343,6 +343,11 @@ struct BwdArgs {
   const int* kv_split;         // [n_kv_split, 3]: key row, first slot, number of slots
   int n_kv_split;
   float* kv_partial;           // [slots, 2*Hl*HN] fp32
+  // Packed query records for narrow rows (optional): the dQ pass writes, per (row, head), [q | dout / (Z + eps)] next to
+  // each other plus one float D / (Z + eps); the dK/dV pass then gathers one contiguous record per edge instead of
+  // three separate short rows (q, dout, (1/Z, D)), which matters when a row of q is only 32 or 64 bytes.
+  void* qg;                    // [n, Hl, 2, HN] in the operand dtype, or null
+  float* cz;                   // [n, Hl]
 };
 
 // One edge of the dQ pass for one task lane.
@@ -500,6 +505,15 @@ __global__ void __launch_bounds__(256, EXPH ? 3 : 4) edge_attn_bwd_q_kernel(BwdA
   float zsum = head_ok ? a.z[(long long)row * a.hl + hsafe] : 1.f;
   const float invz = 1.f / (zsum + kEps);
   if (head_ok && (lt % LPH) == 0) b.zd[(long long)row * a.hl + head] = make_float2(invz, dterm);
+  if (b.qg != nullptr && head_ok) {
+    T* rec = static_cast<T*>(b.qg) + ((long long)row * a.hl + head) * 2 * HN + (lt % LPH) * VN;
+    float gz[VN];
+#pragma unroll
+    for (int i = 0; i < VN; ++i) gz[i] = dof[i] * invz;
+    store_vec<T>(rec, qraw);
+    store_vec<T>(rec + HN, gz);
+    if ((lt % LPH) == 0) b.cz[(long long)row * a.hl + head] = dterm * invz;
+  }
   if (hub) end = beg;
   for (int e = beg; e < end; e += 2)
     dq_edge4<T, HN, EXPH, 2>(b, e, end, hsafe, off, qs0, qs1, qraw, dof, invz, dterm, dq, de0, de1, hm);
@@ -616,7 +630,7 @@ __device__ __forceinline__ void dkv_edge(const BwdArgs& b, int te, int head, int
 
 // Four transposed edges at a time: all index and row loads are issued before any arithmetic so that a lane group
 // keeps 8 independent 16-byte gathers in flight (the pass is bound by gather latency, not by math).
-template <typename T, int HN, bool EXPH, int NB>
+template <typename T, int HN, bool EXPH, int NB, bool PACKED>
 __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int head, int off, const Raw<T>& kf,
                                           const Raw<T>& vf, float* dk, float* dv, unsigned hm) {
   constexpr int VN = Vec<T>::N;
@@ -637,9 +651,17 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
   int ty[NB];
 #pragma unroll
   for (int u = 0; u < NB; ++u) {
-    qr[u].load(static_cast<const T*>(a.q) + (long long)i_row[u] * a.ldq + off);
-    dr[u].load(static_cast<const T*>(b.dout) + (long long)i_row[u] * w_row + off);
-    zd[u] = __ldg(b.zd + (long long)i_row[u] * a.hl + head);
+    if constexpr (PACKED) {
+      // one contiguous record per (query, head): q, then dout already divided by the normaliser; zd = (1, D / (Z + eps))
+      const T* rec = static_cast<const T*>(b.qg) + ((long long)i_row[u] * a.hl + head) * 2 * HN + (off - head * HN);
+      qr[u].load(rec);
+      dr[u].load(rec + HN);
+      zd[u] = make_float2(1.f, __ldg(b.cz + (long long)i_row[u] * a.hl + head));
+    } else {
+      qr[u].load(static_cast<const T*>(a.q) + (long long)i_row[u] * a.ldq + off);
+      dr[u].load(static_cast<const T*>(b.dout) + (long long)i_row[u] * w_row + off);
+      zd[u] = __ldg(b.zd + (long long)i_row[u] * a.hl + head);
+    }
     ty[u] = (EXPH && ok[u]) ? a.etype[eid[u]] : 0;
   }
 #pragma unroll
@@ -671,7 +693,7 @@ __device__ __forceinline__ void dkv_edge4(const BwdArgs& b, int te, int end, int
 
 // dK/dV over the balanced work list: one lane group per (work item, head chunk).  (Letting two lane groups share an
 // item and split its edges was measured slower: most items are short, and the shared form halves the items in flight.)
-template <typename T, int HN, bool EXPH, int MINB>
+template <typename T, int HN, bool EXPH, int MINB, bool PACKED>
 __global__ void __launch_bounds__(256, MINB) edge_attn_bwd_kv_task_kernel(BwdArgs b) {
   constexpr int VN = Vec<T>::N;
   constexpr int LPH = HN / VN;
@@ -700,7 +722,7 @@ __global__ void __launch_bounds__(256, MINB) edge_attn_bwd_kv_task_kernel(BwdArg
 #pragma unroll
   for (int i = 0; i < VN; ++i) { dk[i] = 0.f; dv[i] = 0.f; }
   const unsigned hm = head_mask<LPH>();
-  for (int e = beg; e < end; e += 2) dkv_edge4<T, HN, EXPH, 2>(b, e, end, head, off, kf, vf, dk, dv, hm);
+  for (int e = beg; e < end; e += 2) dkv_edge4<T, HN, EXPH, 2, PACKED>(b, e, end, head, off, kf, vf, dk, dv, hm);
   if (slot < 0) {
     store_vec<T>(static_cast<T*>(b.dk) + (long long)row * b.ldg + off, dk);
     store_vec<T>(static_cast<T*>(b.dv) + (long long)row * b.ldg + off, dv);
@@ -886,8 +908,13 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
     const long long kv_warps = (kv_tasks + tpw - 1) / tpw;
     const long long kv_blocks = (kv_warps + 7) / 8;
     if (kv_blocks > 0) {
-      if (a.variant == 2) edge_attn_bwd_kv_task_kernel<T, HN, true, 3><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
-      else edge_attn_bwd_kv_task_kernel<T, HN, false, 4><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      if (a.variant == 2) {
+        if (b.qg) edge_attn_bwd_kv_task_kernel<T, HN, true, 3, true><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+        else edge_attn_bwd_kv_task_kernel<T, HN, true, 3, false><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      } else {
+        if (b.qg) edge_attn_bwd_kv_task_kernel<T, HN, false, 4, true><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+        else edge_attn_bwd_kv_task_kernel<T, HN, false, 4, false><<<(unsigned)kv_blocks, 256, 0, st>>>(b);
+      }
     }
     if (b.n_kv_split > 0) {
       const int ncol = 2 * w_row;
@@ -961,6 +988,9 @@ extern "C" int bf_edge_attn_bwd(const bf_attn_params* p, const bf_attn_bwd_param
   b.hub_scratch_q = q->hub_scratch_q; b.hub_scratch_kv = q->hub_scratch_kv;
   b.kv_task = reinterpret_cast<const int4*>(q->kv_task); b.n_kv_task = q->n_kv_task;
   b.kv_split = q->kv_split; b.n_kv_split = q->n_kv_split; b.kv_partial = q->kv_partial;
+  // the packed records serve the work-list form of the dK/dV pass only
+  b.qg = (q->kv_task != nullptr && q->qg != nullptr && q->cz != nullptr) ? q->qg : nullptr;
+  b.cz = b.qg ? q->cz : nullptr;
   const int cq = p->max_hub_degree > 0 ? (p->max_hub_degree + BF_HUB_CHUNK - 1) / BF_HUB_CHUNK : 1;
   const int ckv = q->max_t_hub_degree > 0 ? (q->max_t_hub_degree + BF_HUB_CHUNK - 1) / BF_HUB_CHUNK : 1;
 #define CALL_BWD(T, H) (int)launch_bwd_t<T, H>(b, cq, ckv, st)
@@ -1007,6 +1037,11 @@ extern "C" int bf_edge_attn_fwd_noalloc(const bf_attn_params* p, cudaStream_t st
   const long long width = (long long)p->hl * p->hn;
   if (p->n_hub < 0 || p->n_hub > BF_NOALLOC_MAX_HUBS || width > BF_NOALLOC_MAX_WIDTH || p->hl > BF_NOALLOC_MAX_HEADS)
     return BF_NOALLOC_ERR_TOO_LARGE;
+  // everything the launcher would reject is rejected here, before anything is queued on the stream
+  const bool hn_ok = p->hn == 8 || p->hn == 16 || p->hn == 32 || p->hn == 64 || p->hn == 128;
+  const bool dtype_ok = p->dtype == BF_BF16 || p->dtype == BF_FP16 || p->dtype == BF_FP32;
+  if (!hn_ok || !dtype_ok || p->n <= 0 || p->hl <= 0) return (int)cudaErrorInvalidValue;
+  if (p->n_hub > 0 && (p->hub_rows == nullptr || p->max_hub_degree <= 0)) return (int)cudaErrorInvalidValue;
   bf_attn_params q = *p;
   q.hub_scratch = nullptr;
   if (p->n_hub > 0) {
@@ -1021,6 +1056,8 @@ extern "C" int bf_edge_attn_fwd_noalloc(const bf_attn_params* p, cudaStream_t st
   }
   return bf_edge_attn_fwd(&q, stream);
 }
+
+extern "C" size_t bf_attn_params_size(void) { return sizeof(bf_attn_params); }
 
 extern "C" const char* bf_noalloc_strerror(int code) {
   switch (code) {

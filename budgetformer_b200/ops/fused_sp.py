@@ -59,14 +59,18 @@ class SPContext:
         self.hl = self.hl_heads * self.hn                 # columns of one head slice
         self.dtype = dtype
         self.token_rows = token_rows
-        self.qkv = [self.sw.alloc((self.total_rows, 3 * self.hl), dtype) for _ in range(n_layers)]
+        # A node's packed row is k | v | q: the attention kernels gather k and v of a key together, so the pair comes
+        # first, and the row pitch is padded to a multiple of 128 bytes so that a narrow pair (64 bytes with one head of
+        # 16 per rank) never straddles two DRAM bursts.
+        self.qkv_ld = (3 * self.hl + 63) // 64 * 64
+        self.qkv = [self.sw.alloc((self.total_rows, self.qkv_ld), dtype) for _ in range(n_layers)]
         self.ctx = [self.sw.alloc((self.total_rows, self.hl), dtype) for _ in range(n_layers)]
-        self.dqkv = self.sw.alloc((self.total_rows, 3 * self.hl), dtype)
+        self.dqkv = self.sw.alloc((self.total_rows, self.qkv_ld), dtype)
         self.dctx = self.sw.alloc((self.total_rows, self.hl), dtype)
-        # row permutation of the packed [Wq;Wk;Wv]: destination-rank major, then q|k|v, then head columns
+        # row permutation of the packed [Wq;Wk;Wv]: destination-rank major, then k|v|q, then head columns
         idx = []
         for r in range(self.P):
-            for part in range(3):
+            for part in (1, 2, 0):
                 base = part * self.h + r * self.hl
                 idx.extend(range(base, base + self.hl))
         self.perm = torch.tensor(idx, dtype=torch.long, device=device)
@@ -76,6 +80,12 @@ class SPContext:
     @property
     def row0(self) -> int:
         return self.rank * self.rows_local
+
+    def split_packed(self, t: torch.Tensor):
+        """(q, k, v) views ``[rows, heads, hn]`` of a packed ``[rows, qkv_ld]`` buffer (column order k | v | q)."""
+        r, hl = t.size(0), self.hl
+        part = lambda i: t[:, i * hl:(i + 1) * hl].view(r, self.hl_heads, self.hn)
+        return part(2), part(0), part(1)
 
     def shared_seed(self, layer: int, tag: int) -> Optional[int]:
         """31-bit seed every rank derives identically for (step, layer, purpose), or None when no step seed is set.
@@ -134,7 +144,7 @@ class _QKVPush(torch.autograd.Function):
         if bq is not None:
             b = torch.cat([bq, bk, bv], 0).float()[sp.perm].contiguous()
         buf = sp.qkv[layer]
-        _push_gemm(x, w, b, buf.ptrs, sp.row0, 3 * sp.hl)
+        _push_gemm(x, w, b, buf.ptrs, sp.row0, sp.qkv_ld)
         sp.sw.barrier(0)
         ctx.sp, ctx.has_bias, ctx.wdtype = sp, bq is not None, wq.dtype
         ctx.save_for_backward(x, w)
@@ -161,18 +171,18 @@ class _QKVPush(torch.autograd.Function):
             # below, and every rank reaches the barrier that follows that layer's d(context) push (or scatter) only
             # after this GEMM, so no peer can overwrite rows that are still being fetched.
             sp.sw.barrier(0)                                         # every rank's dq|dk|dv is complete
-            dx, dloc = _pull_gemm(buf.ptrs, sp.row0, 3 * sp.hl, 3 * sp.hl, sp.rows_local, wt, residual=dres, keep_copy=True)
+            dx, dloc = _pull_gemm(buf.ptrs, sp.row0, sp.qkv_ld, 3 * sp.hl, sp.rows_local, wt, residual=dres, keep_copy=True)
             if debug.enabled():
                 sp.sw.barrier(0)                                     # poisoning below must wait for the peers' reads
         elif sp.P > 1:
             sp.sw.barrier(0)                                         # every rank's dq|dk|dv is complete
             dloc = torch.empty((sp.rows_local, 3 * sp.h), dtype=x.dtype, device=x.device)
             _ext.load().peer_gather_cols(buf.ptrs, sp.row0, sp.rows_local, 3 * sp.hl * x.element_size(),
-                                         3 * sp.hl * x.element_size(), dloc)
+                                         sp.qkv_ld * x.element_size(), dloc)
             _ext.count_launches(1)
             sp.sw.barrier(0)                                         # all reads done before the buffer is reused
         else:
-            dloc = buf.tensor
+            dloc = buf.tensor[:, :3 * sp.h]
         if dx is None:
             dx = gemm.gemm_tn(dloc, wt, residual=dres)
         dw, db_src = gemm.weight_grad(dloc, x, ctx.has_bias)
@@ -196,9 +206,7 @@ class _PackedEdgeAttention(torch.autograd.Function):
                 out_p=0.0, out_seed=0):
         ext = _ext.load()
         r, hlh, hn, hl = sp.total_rows, sp.hl_heads, sp.hn, sp.hl
-        q = qkv[:, 0:hl].view(r, hlh, hn)
-        k = qkv[:, hl:2 * hl].view(r, hlh, hn)
-        v = qkv[:, 2 * hl:3 * hl].view(r, hlh, hn)
+        q, k, v = sp.split_packed(qkv)
         out = sp.ctx[layer].tensor
         z = torch.empty((r, hlh), dtype=torch.float32, device=qkv.device)
         kmax = -1 if graph.max_degree is None else int(graph.max_degree)
@@ -230,14 +238,10 @@ class _PackedEdgeAttention(torch.autograd.Function):
             dout[sp.token_rows[0]] += dout[sp.token_rows[1:]].sum(0)
             dout[sp.token_rows[1:]] = 0
         out = sp.ctx[ctx.layer].tensor
-        q = qkv[:, 0:hl].view(r, hlh, hn)
-        k = qkv[:, hl:2 * hl].view(r, hlh, hn)
-        v = qkv[:, 2 * hl:3 * hl].view(r, hlh, hn)
+        q, k, v = sp.split_packed(qkv)
         # gradients land packed in the symmetric buffer so that peers can pull their rows
         dbuf = sp.dqkv.tensor
-        dq = dbuf[:, 0:hl].view(r, hlh, hn)
-        dk = dbuf[:, hl:2 * hl].view(r, hlh, hn)
-        dv = dbuf[:, 2 * hl:3 * hl].view(r, hlh, hn)
+        dq, dk, dv = sp.split_packed(dbuf)
         zd = torch.empty((r, hlh, 2), dtype=torch.float32, device=qkv.device)
         detab = torch.zeros(etable.shape, dtype=torch.float32, device=qkv.device) if has_tab else None
         ext.edge_attn_bwd(q, k, v, out.view(r, hlh, hn), z, dout.view(r, hlh, hn), dq, dk, dv, zd, graph.rowptr, graph.col,
