@@ -122,6 +122,9 @@ _EXTRA = [
                                                  "on this node)"}),
     (("--shard_cpu_edge_build",), _STORE_TRUE, False, {"help": "cpu_rank_local_prefetch policy: each rank builds the rows "
                                                              "of its own queries and the shards are all-gathered"}),
+    (("--replicate_gpu_edge_build",), _STORE_TRUE, False, {"help": "GPU edge policies on several ranks: every rank builds the "
+                                                                 "whole attention graph itself instead of building the rows of "
+                                                                 "its own queries and fetching the other shards over NVLink"}),
     (("--nvtx",), _STORE_TRUE, False, {"help": "emit NVTX ranges for step phases and profiled calls"}),
     (("--debug_checks",), _STORE_TRUE, False, {"help": "validate every attention graph, poison reusable symmetric "
                                                "buffers after use and check losses/gradients for NaN (also BF_DEBUG=1)"}),

@@ -86,6 +86,10 @@ typedef struct {
   uint8_t* ell_type;                // [n, cap] (exphormer) or NULL
   int* ell_cnt;                     // [n]
   unsigned long long* totals;       // zero-filled [2]: selected real / walk edges
+  // Optional row range (row_count > 0): only the queries [row_begin, row_begin + row_count) are built and their rows are
+  // stored at index (query - row_begin) of ell_col / ell_type / ell_cnt - one rank's shard of a build that the
+  // sequence-parallel ranks split between them.  row_count == 0 builds all n queries.
+  int row_begin, row_count;
 } bf_build_params;
 
 int bf_budget_select(const bf_build_params* p, cudaStream_t st);
@@ -168,6 +172,8 @@ int bf_peer_gather_cols(void* const* src, int world, long long row0, long long r
                         long long src_ld_bytes, void* dst, long long dst_ld_bytes, cudaStream_t st);
 int bf_peer_scatter_cols(void* const* dst, int world, long long row0, long long rows, int cols_bytes,
                          long long dst_ld_bytes, const void* src, long long src_ld_bytes, cudaStream_t st);
+// dst[r * n_elem + i] = src[r][i] for every rank r: equal-length shards fetched with peer loads and laid end to end.
+int bf_peer_concat(void* const* src, int world, long long n_elem, int elem_bytes /* 1, 4 or 8 */, void* dst, cudaStream_t st);
 
 // Balanced k-way partition of a symmetric CSR (cpu/partition.cpp: BFS ordering + boundary refinement); returns the
 // number of nodes the refinement moved, or -1 on bad arguments.

@@ -202,6 +202,64 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
   return {rowptr, col, exphormer ? etype : torch::empty({0}, iopt.dtype(torch::kUInt8)), totals};
 }
 
+// One rank's shard of a device build: fixed-width rows of the queries [row_begin, row_begin + row_count) written into
+// caller-provided buffers (symmetric memory, so that the peers can fetch them): ell_col [row_count, cap] int32,
+// ell_cnt [row_count] int32, ell_type [row_count, cap] uint8 (typed rows only), totals [2] int64 (zeroed here).
+void budget_select_rows(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col, int64_t n, int64_t b_real,
+                        int64_t b_rw, int64_t walks, int64_t walk_len, bool exphormer, int64_t seed, int64_t row_begin,
+                        int64_t row_count, Tensor ell_col, Tensor ell_cnt, OptTensor ell_type, Tensor totals) {
+  TORCH_CHECK(b_real >= 0 && b_rw >= 0 && b_real <= 32 && b_rw <= 32, "per-side budgets must be in [0, 32]");
+  TORCH_CHECK(walk_len <= 16, "walk_length must be <= 16");
+  for (const Tensor* t : {&in_rowptr, &in_src, &out_rowptr, &out_col})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kInt && t->is_contiguous(), "topology must be contiguous int32 on CUDA");
+  const int cap = std::max((int)(b_real + b_rw + (exphormer ? 1 : 0)), 1);
+  TORCH_CHECK(ell_col.is_cuda() && ell_col.scalar_type() == torch::kInt && ell_col.is_contiguous() &&
+              ell_col.numel() >= row_count * cap && ell_cnt.scalar_type() == torch::kInt && ell_cnt.numel() >= row_count);
+  TORCH_CHECK(!exphormer || (ell_type.has_value() && ell_type->scalar_type() == torch::kUInt8 && ell_type->numel() >= row_count * cap));
+  TORCH_CHECK(totals.scalar_type() == torch::kLong && totals.numel() >= 2);
+  c10::cuda::CUDAGuard guard(in_src.device());
+  totals.zero_();
+  bf_build_params p{};
+  p.in_rowptr = iptr(in_rowptr); p.in_src = iptr(in_src); p.out_rowptr = iptr(out_rowptr); p.out_col = iptr(out_col);
+  p.n = (int)n; p.b_real = (int)b_real; p.b_rw = (int)b_rw; p.walks = (int)walks; p.walk_len = (int)walk_len;
+  p.exphormer = exphormer ? 1 : 0; p.seed = seed; p.cap = cap;
+  p.ell_col = ell_col.data_ptr<int>(); p.ell_type = exphormer ? ell_type->data_ptr<uint8_t>() : nullptr;
+  p.ell_cnt = ell_cnt.data_ptr<int>();
+  p.totals = reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>());
+  p.row_begin = (int)row_begin; p.row_count = (int)row_count;
+  check_cuda(bf_budget_select(&p, at::cuda::getCurrentCUDAStream()), "budget_select_rows");
+}
+
+// Fixed-width rows of all n queries -> CSR (rowptr, col, etype or empty): prefix sum of the counts, one host read of
+// the edge count, compaction.
+std::vector<Tensor> ell_rows_to_csr(Tensor ell_col, Tensor ell_cnt, OptTensor ell_type, int64_t n, int64_t cap) {
+  TORCH_CHECK(ell_col.is_cuda() && ell_col.scalar_type() == torch::kInt && ell_col.is_contiguous() && ell_col.numel() >= n * cap);
+  TORCH_CHECK(ell_cnt.scalar_type() == torch::kInt && ell_cnt.is_contiguous() && ell_cnt.numel() >= n);
+  c10::cuda::CUDAGuard guard(ell_col.device());
+  auto iopt = ell_col.options();
+  const bool typed = ell_type.has_value();
+  Tensor rowptr = torch::zeros({n + 1}, iopt);
+  rowptr.slice(0, 1).copy_(torch::cumsum(ell_cnt.slice(0, 0, n), 0, torch::kInt));
+  const int64_t n_edges = n > 0 ? rowptr[n].item<int64_t>() : 0;
+  Tensor col = torch::empty({n_edges}, iopt);
+  Tensor etype = typed ? torch::empty({n_edges}, iopt.dtype(torch::kUInt8)) : torch::empty({0}, iopt.dtype(torch::kUInt8));
+  check_cuda(bf_ell_to_csr(ell_col.data_ptr<int>(), typed ? ell_type->data_ptr<uint8_t>() : nullptr, rowptr.data_ptr<int>(),
+                           (int)n, (int)cap, col.data_ptr<int>(), typed ? etype.data_ptr<uint8_t>() : nullptr,
+                           at::cuda::getCurrentCUDAStream()), "ell_to_csr");
+  return {rowptr, col, etype};
+}
+
+// dst[r * n + i] = src_r[i]: the shards of all ranks (n elements of dst's dtype each), fetched with peer loads and laid
+// end to end.
+void peer_concat(std::vector<int64_t> src, int64_t n_elem, Tensor dst) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  TORCH_CHECK(dst.is_contiguous() && dst.numel() >= (int64_t)src.size() * n_elem && src.size() <= BF_MAX_PEERS, "peer_concat: bad sizes");
+  std::vector<void*> p(BF_MAX_PEERS, nullptr);
+  for (size_t i = 0; i < src.size(); ++i) p[i] = reinterpret_cast<void*>(src[i]);
+  check_cuda(bf_peer_concat(p.data(), (int)src.size(), n_elem, (int)dst.element_size(), dst.data_ptr(),
+                            at::cuda::getCurrentCUDAStream()), "peer_concat");
+}
+
 // General CPU build (rows of any length; a negative budget keeps every candidate of that side; an empty fan-out
 // list selects Philox walks).  Same outputs as build_attn_graph.
 std::vector<Tensor> build_attn_graph_rows_cpu(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col,
@@ -610,6 +668,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("edge_attn_fwd", &edge_attn_fwd);
   m.def("edge_attn_bwd", &edge_attn_bwd);
   m.def("build_attn_graph", &build_attn_graph);
+  m.def("budget_select_rows", &budget_select_rows);
+  m.def("ell_rows_to_csr", &ell_rows_to_csr);
+  m.def("peer_concat", &peer_concat);
   m.def("khop_candidates_cpu", &khop_candidates_cpu);
   m.def("partition_cpu", &partition_cpu);
   m.def("build_attn_graph_rows_cpu", &build_attn_graph_rows_cpu);

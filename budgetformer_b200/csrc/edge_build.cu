@@ -51,6 +51,7 @@ __device__ __forceinline__ void group_insert(uint64_t& list, int K, bool valid, 
 struct BuildArgs {
   const int *in_rowptr, *in_src, *out_rowptr, *out_col;
   int n;
+  int row_begin;       // first query of this launch; rows are stored at index (query - row_begin)
   int b_real, b_rw, walks, walk_len, exphormer;
   long long seed;
   int cap;
@@ -68,8 +69,9 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
   const int lane = threadIdx.x & 31;
   const int gl = lane & (WIDTH - 1);                       // lane inside the group
   const unsigned gm = group_mask<WIDTH>(lane);
-  const long long v = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / WIDTH;
-  if (v < a.n) {
+  const long long slot = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / WIDTH;   // row of the output
+  const long long v = slot + a.row_begin;                                              // query node
+  if (slot < a.n) {
     const uint32_t q = (uint32_t)v;
     // ---- real edges ----
     uint64_t rlist = kInf;
@@ -117,7 +119,7 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
     // ---- merge ----
     const bool has_r = gl < r_cnt, has_w = gl < w_cnt;
     const uint32_t sr = (uint32_t)rlist, sw = (uint32_t)wlist;
-    int* row = a.ell_col + (long long)v * a.cap;
+    int* row = a.ell_col + slot * a.cap;
     if (a.exphormer) {
       int rank_r = 0, rank_w = 0;
       for (int t = 0; t < WIDTH; ++t) {
@@ -126,10 +128,10 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
         if (t < r_cnt && (yr < sr || (yr == sr && t < gl))) ++rank_r;
         if (t < w_cnt && (yw < sw || (yw == sw && t < gl))) ++rank_w;
       }
-      uint8_t* trow = a.ell_type + (long long)v * a.cap;
+      uint8_t* trow = a.ell_type + slot * a.cap;
       if (has_r) { row[rank_r] = (int)sr; trow[rank_r] = 0; }
       if (has_w) { row[r_cnt + rank_w] = (int)sw; trow[r_cnt + rank_w] = 1; }
-      if (gl == 0) { row[r_cnt + w_cnt] = (int)v; trow[r_cnt + w_cnt] = 0; a.ell_cnt[v] = r_cnt + w_cnt + 1; }
+      if (gl == 0) { row[r_cnt + w_cnt] = (int)v; trow[r_cnt + w_cnt] = 0; a.ell_cnt[slot] = r_cnt + w_cnt + 1; }
     } else {
       bool dup_r = false, dup_w = false;
       for (int t = 0; t < WIDTH; ++t) {
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
       if (keep_r) row[rank_r] = (int)sr;
       if (keep_w) row[rank_w] = (int)sw;
       const int total = __popc(group_ballot<WIDTH>(gm, lane, keep_r)) + __popc(group_ballot<WIDTH>(gm, lane, keep_w));
-      if (gl == 0) a.ell_cnt[v] = total;
+      if (gl == 0) a.ell_cnt[slot] = total;
     }
     if (gl == 0) { atomicAdd(&s_tot[0], (unsigned)r_cnt); atomicAdd(&s_tot[1], (unsigned)w_cnt); }
   }
@@ -181,14 +183,16 @@ extern "C" int bf_budget_select(const bf_build_params* p, cudaStream_t st) {
     return (int)cudaErrorInvalidValue;
   BuildArgs a;
   a.in_rowptr = p->in_rowptr; a.in_src = p->in_src; a.out_rowptr = p->out_rowptr; a.out_col = p->out_col;
-  a.n = p->n; a.b_real = p->b_real; a.b_rw = p->b_rw; a.walks = p->walks; a.walk_len = p->walk_len;
+  a.n = p->row_count > 0 ? p->row_count : p->n; a.row_begin = p->row_count > 0 ? p->row_begin : 0;
+  if (a.row_begin < 0 || (long long)a.row_begin + a.n > p->n) return (int)cudaErrorInvalidValue;
+  a.b_real = p->b_real; a.b_rw = p->b_rw; a.walks = p->walks; a.walk_len = p->walk_len;
   a.exphormer = p->exphormer; a.seed = p->seed; a.cap = p->cap;
   a.ell_col = p->ell_col; a.ell_type = p->ell_type; a.ell_cnt = p->ell_cnt;
   a.totals = reinterpret_cast<unsigned long long*>(p->totals);
   // eight lanes per query when both budgets and the walk count fit in eight slots, else a full warp
   const bool narrow = p->b_real <= 8 && p->b_rw <= 8 && p->walks <= 8;
   const int width = narrow ? 8 : 32;
-  const long long blocks = ((long long)p->n * width + 255) / 256;
+  const long long blocks = ((long long)a.n * width + 255) / 256;
   if (blocks > 0) {
     if (narrow) budget_select_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(a);
     else budget_select_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(a);

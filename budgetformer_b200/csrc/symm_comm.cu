@@ -130,6 +130,17 @@ __global__ void __launch_bounds__(256) peer_scatter_cols_kernel(PeerPtrs dst, in
   }
 }
 
+// dst[r * n + i] = src_r[i]: the ranks' shards laid end to end (element-wise, so that shards of any length line up)
+template <typename T>
+__global__ void __launch_bounds__(256) peer_concat_kernel(PeerPtrs src, int world, long long n, T* dst) {
+  const long long total = n * world;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int r = (int)(i / n);
+    dst[i] = static_cast<const T*>(src.p[r])[i - (long long)r * n];
+  }
+}
+
 PeerPtrs to_ptrs(void* const* p, int world) {
   PeerPtrs o;
   for (int i = 0; i < BF_MAX_PEERS; ++i) o.p[i] = i < world ? p[i] : nullptr;
@@ -189,5 +200,16 @@ extern "C" int bf_peer_scatter_cols(void* const* dst, int world, long long row0,
   peer_scatter_cols_kernel<<<grid_for(total, 256), 256, 0, st>>>(to_ptrs(dst, world), world, row0, rows, vpr,
                                                                  dst_ld_bytes / 16, static_cast<const uint4*>(src),
                                                                  src_ld_bytes / 16);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int bf_peer_concat(void* const* src, int world, long long n_elem, int elem_bytes, void* dst, cudaStream_t st) {
+  if (world < 1 || world > BF_MAX_PEERS || n_elem < 0 || (elem_bytes != 1 && elem_bytes != 4 && elem_bytes != 8))
+    return (int)cudaErrorInvalidValue;
+  if (n_elem == 0) return 0;
+  const int grid = grid_for(n_elem * world, 256);
+  if (elem_bytes == 4) peer_concat_kernel<uint32_t><<<grid, 256, 0, st>>>(to_ptrs(src, world), world, n_elem, static_cast<uint32_t*>(dst));
+  else if (elem_bytes == 8) peer_concat_kernel<uint64_t><<<grid, 256, 0, st>>>(to_ptrs(src, world), world, n_elem, static_cast<uint64_t*>(dst));
+  else peer_concat_kernel<uint8_t><<<grid, 256, 0, st>>>(to_ptrs(src, world), world, n_elem, static_cast<uint8_t*>(dst));
   return (int)cudaGetLastError();
 }

@@ -114,6 +114,80 @@ def build_attn_graph_shard(topo: Topology, rows: tuple, b_real: Optional[int], b
                      None if full.etype is None else full.etype[lo:hi].contiguous(), max_degree=full.max_degree)
 
 
+class ShardedDeviceBuild:
+    """Device build split over the sequence-parallel ranks by query range.
+
+    Every rank runs the selection kernel (hash-ranked real edges, Philox walks, merge) for its own ``N / P`` queries
+    only and leaves the fixed-width rows in a symmetric buffer; after one device barrier each rank fetches all shards
+    with coalesced peer loads and finishes locally (prefix sum, compaction to CSR).  Rows do not depend on one another,
+    so the result is bit-identical to the whole build - the reference reaches the same end by broadcasting the edge
+    list from one rank (utils/fullgraph_sp_support.py:3262-3338); here the work is divided instead of repeated.
+
+    Two shard buffers alternate: a rank overwrites a buffer only after it has passed the barrier of the build in
+    between, which every peer reaches after it finished fetching, so no second barrier is needed.  One instance serves
+    one host thread and one barrier channel (the ranks must issue its builds in the same order)."""
+
+    def __init__(self, world, channel: int):
+        self.sw, self.channel = world, int(channel)
+        self.bufs = [None, None]
+        self.nbytes = 0
+        self.turn = 0
+
+    @staticmethod
+    def _layout(rows: int, cap: int):
+        a16 = lambda b: (b + 15) // 16 * 16
+        col, cnt, typ = a16(rows * cap * 4), a16(rows * 4), a16(rows * cap)
+        return col, cnt, typ, col + cnt + typ + 16
+
+    def ensure(self, rows: int, cap: int) -> None:
+        """Make the two shard buffers large enough for ``rows`` x ``cap``.  Allocation is a collective of the group:
+        call it from the thread that owns the group's other collectives, with the same arguments on every rank."""
+        need = self._layout(rows, cap)[3]
+        if need > self.nbytes:
+            self.bufs = [self.sw.alloc((need,), torch.uint8) for _ in range(2)]
+            self.nbytes, self.turn = need, 0
+
+    def ready(self, rows: int, cap: int) -> bool:
+        return self._layout(rows, cap)[3] <= self.nbytes
+
+    def build(self, topo: Topology, br: int, bw: int, walks_per_node: int, walk_length: int, seed: int,
+              exphormer: bool) -> AttnGraph:
+        from ..ops import _ext
+        ext = _ext.load()
+        sw = self.sw
+        n, p = int(topo.num_nodes), sw.world
+        rows = n // p
+        cap = max(int(br) + int(bw) + (1 if exphormer else 0), 1)
+        buf = self.bufs[self.turn]
+        self.turn ^= 1
+        o_col, o_cnt, o_typ, _total = self._layout(rows, cap)
+        t = buf.tensor
+        ell_col = t[:rows * cap * 4].view(torch.int32)
+        ell_cnt = t[o_col:o_col + rows * 4].view(torch.int32)
+        ell_typ = t[o_col + o_cnt:o_col + o_cnt + rows * cap] if exphormer else None
+        totals = t[o_col + o_cnt + o_typ:o_col + o_cnt + o_typ + 16].view(torch.int64)
+        ext.budget_select_rows(topo.in_rowptr, topo.in_src, topo.out_rowptr, topo.out_col, n, int(br), int(bw),
+                               int(walks_per_node), int(walk_length), bool(exphormer), int(seed), sw.rank * rows, rows,
+                               ell_col, ell_cnt, ell_typ, totals)
+        sw.barrier(self.channel)                                  # every rank's shard is complete
+        dev = t.device
+        full_col = torch.empty(n * cap, dtype=torch.int32, device=dev)
+        full_cnt = torch.empty(n, dtype=torch.int32, device=dev)
+        ext.peer_concat(buf.ptrs, rows * cap, full_col)
+        ext.peer_concat([ptr + o_col for ptr in buf.ptrs], rows, full_cnt)
+        full_typ = None
+        if exphormer:
+            full_typ = torch.empty(n * cap, dtype=torch.uint8, device=dev)
+            ext.peer_concat([ptr + o_col + o_cnt for ptr in buf.ptrs], rows * cap, full_typ)
+        all_tot = torch.empty(2 * p, dtype=torch.int64, device=dev)
+        ext.peer_concat([ptr + o_col + o_cnt + o_typ for ptr in buf.ptrs], 2, all_tot)
+        rowptr, col, etype = ext.ell_rows_to_csr(full_col, full_cnt, full_typ, n, cap)
+        _ext.count_launches(7 if exphormer else 6)
+        g = AttnGraph(n, rowptr, col, etype if exphormer else None, max_degree=int(br) + int(bw) + (1 if exphormer else 0))
+        g._totals = all_tot.view(p, 2).sum(0)
+        return g
+
+
 def graph_totals(g: AttnGraph):
     """(selected real edges, selected walk edges) of a natively built graph."""
     t = getattr(g, "_totals", None)
@@ -123,4 +197,5 @@ def graph_totals(g: AttnGraph):
     return g.n_real, g.n_rw
 
 
-__all__ = ["build_attn_graph", "build_attn_graph_shard", "graph_totals", "add_virtual_node", "native_supported"]
+__all__ = ["build_attn_graph", "build_attn_graph_shard", "graph_totals", "add_virtual_node", "native_supported",
+           "ShardedDeviceBuild"]

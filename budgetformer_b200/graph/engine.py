@@ -31,7 +31,7 @@ import torch.distributed as dist
 from ..utils.comm_profiler import profile_call, record_scalar
 from .device_budget import BUDGET
 from .attn_graph import AttnGraph, Topology, add_virtual_node
-from .builder import build_attn_graph, build_attn_graph_shard, graph_totals, native_supported
+from .builder import ShardedDeviceBuild, build_attn_graph, build_attn_graph_shard, graph_totals, native_supported
 
 EDGE_POLICY_CHOICES = ("gpu_persist", "gpu_ephemeral", "cpu_rank_local_prefetch", "cpu_broadcast_prefetch",
                        "cpu_broadcast")
@@ -123,6 +123,8 @@ class EdgeEngine:
         self.last_graph_bytes = 0
         self.gpu_build_failed = False
         self.build_threads = self._resolve_build_threads()
+        # device builds split over the ranks: one instance (and barrier channel) per host thread that builds
+        self._shard_builds = {}
 
     def _resolve_build_threads(self) -> int:
         """OpenMP threads of a host-side build: ``--edge_build_threads`` or the cores this process may use divided by
@@ -202,7 +204,7 @@ class EdgeEngine:
             if self._build_stream is None:
                 self._build_stream = torch.cuda.Stream(self.device)
             with torch.cuda.stream(self._build_stream):
-                g = self._finalize(self._build_device(seed, state))
+                g = self._finalize(self._build_device(seed, state, who="ahead"))
                 g.ensure_transpose()
                 done = torch.cuda.Event()
                 done.record(self._build_stream)
@@ -233,6 +235,7 @@ class EdgeEngine:
             key = self._key(seed, state)
             if self._dev_future is not None and self._dev_future[0] == key:
                 return True
+            self._prepare_sharded(state)
             if self._pool is None:
                 self._pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="bf-edge-prefetch")
             self._dev_future = (key, self._pool.submit(self._build_device_ahead, seed, state))
@@ -308,15 +311,53 @@ class EdgeEngine:
             self.topo_gpu = topo
         return topo
 
-    def _build_device(self, seed: int, state: BudgetState) -> AttnGraph:
+    SHARD_CHANNELS = {"step": 3, "ahead": 2}          # barrier channels of the sharded device build, per building thread
+
+    def _device_budgets(self, state: BudgetState):
         walks = int(getattr(self.args, "walks_per_node", 0))
         br = 0 if not state.use_real else state.b_real
         bw = 0 if (not state.use_rw or walks <= 0 or state.walk_length <= 0) else state.b_rw
+        return br, bw
+
+    def sharded_device_build(self, state: BudgetState) -> bool:
+        """GPU policies on several ranks: each rank selects the rows of its own queries and fetches the others' over
+        NVLink (``graph/builder.py::ShardedDeviceBuild``) unless ``--replicate_gpu_edge_build`` asks for local builds."""
+        if (self.world <= 1 or self.device.type != "cuda" or self.fanout or self.force_broadcast
+                or bool(getattr(self.args, "replicate_gpu_edge_build", False)) or self.policy not in ("gpu_persist", "gpu_ephemeral")):
+            return False
+        br, bw = self._device_budgets(state)
+        if not native_supported(br, bw, state.walk_length):
+            return False
+        return self.num_nodes % self.world == 0
+
+    def _prepare_sharded(self, state: BudgetState) -> None:
+        """Size the shard buffers of both building threads (a collective allocation: main thread only)."""
+        if not self.sharded_device_build(state):
+            return
+        from ..parallel import symm
+        br, bw = self._device_budgets(state)
+        cap = max(int(br) + int(bw) + (1 if self.exphormer and self.expander_edges is None else 0), 1)
+        rows = self.num_nodes // self.world
+        for who, channel in self.SHARD_CHANNELS.items():
+            sb = self._shard_builds.get(who)
+            if sb is None:
+                sb = self._shard_builds[who] = ShardedDeviceBuild(symm.get_world(self.group, self.device), channel)
+            sb.ensure(rows, cap)
+
+    def _build_device(self, seed: int, state: BudgetState, who: str = "step") -> AttnGraph:
+        walks = int(getattr(self.args, "walks_per_node", 0))
+        br, bw = self._device_budgets(state)
         if self.fanout or not native_supported(br, bw, state.walk_length):
             # fan-out sampling, sides without budget and budgets beyond the fixed-width kernels are built by the general
             # C++ builder from the host copy of the topology (no topology transfer in either direction)
             return self._upload(self._build_host(seed, state))
         topo = self._topology_on_device()
+        typed = self.exphormer and self.expander_edges is None
+        sb = self._shard_builds.get(who)
+        if sb is not None and self.sharded_device_build(state):
+            cap = max(int(br) + int(bw) + (1 if typed else 0), 1)
+            if sb.ready(self.num_nodes // self.world, cap):
+                return sb.build(topo, br, bw, walks, state.walk_length, seed, typed)
         return build_attn_graph(topo, state.b_real, state.b_rw, int(getattr(self.args, "walks_per_node", 0)),
                                 state.walk_length, seed, use_real=state.use_real, use_rw=state.use_rw,
                                 exphormer=self.exphormer and self.expander_edges is None)
@@ -413,6 +454,7 @@ class EdgeEngine:
         t0 = time.perf_counter()
         self.last_prefetch_wait_s = 0.0
         key = self._key(seed, state)
+        self._prepare_sharded(state)
         broadcast = self.world > 1 and (self.force_broadcast or self.policy in ("cpu_broadcast", "cpu_broadcast_prefetch"))
         g: Optional[AttnGraph] = None
         ahead = self._take_device_prefetch(key)

@@ -23,12 +23,13 @@ USE_RELU_BITS = True
 class _FusedFFNRelu(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2, residual, p1, p2, seed1, seed2, slot=None):
-        w1h, w2h = w1.to(x.dtype), w2.to(x.dtype)
+        w1h, w2h = gemm.operand_copy(w1, x.dtype), gemm.operand_copy(w2, x.dtype)
         # one bit per hidden element (h > 0, after dropout): the backward masks with it instead of re-reading h
         bits = torch.empty((w1.size(0) // 16, x.size(0)), dtype=torch.int16, device=x.device) if (USE_RELU_BITS and w1.size(0) % 16 == 0) else None
         h = gemm.gemm_tn(x, w1h, b1, "relu", dropout_p=p1, dropout_seed=seed1, relu_bits_out=bits)
         y = gemm.gemm_tn(h, w2h, b2, None, dropout_p=p2, dropout_seed=seed2, residual=residual)
-        ctx.save_for_backward(x, h, w1h, w2h, bits if bits is not None else x.new_empty(0))
+        ctx.weights = (w1, w2)
+        ctx.save_for_backward(x, h, bits if bits is not None else x.new_empty(0))
         # residual FFN (the residual is the input itself): backward adds the pass-through gradient in the epilogue of
         # the input-gradient GEMM instead of leaving a separate full-size addition to autograd
         res_is_x = residual is not None and residual.data_ptr() == x.data_ptr() and residual.shape == x.shape \
@@ -40,17 +41,19 @@ class _FusedFFNRelu(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x, h, w1h, w2h, bits = ctx.saved_tensors
+        x, h, bits = ctx.saved_tensors
+        w1t = gemm.operand_copy(ctx.weights[0], x.dtype, transpose=True)
+        w2t = gemm.operand_copy(ctx.weights[1], x.dtype, transpose=True)
         p1, p2, seed1, seed2, has_res, wdtype, has_b1, has_b2, res_is_x = ctx.cfg
         handed = ctx.slot.take(dy) if ctx.slot is not None else None
         dy = dy.contiguous()
         g2 = hash_dropout(dy, seed2, p2) if p2 > 0 else dy
         scale = 1.0 / (1.0 - p1) if p1 > 0 else 1.0
         if bits.numel():
-            dh = gemm.gemm_tn(g2, w2h.t().contiguous(), relu_bits_in=bits, out_scale=scale)
+            dh = gemm.gemm_tn(g2, w2t, relu_bits_in=bits, out_scale=scale)
         else:
-            dh = gemm.gemm_tn(g2, w2h.t().contiguous(), relu_mask=h, out_scale=scale)
-        dx = gemm.gemm_tn(dh, w1h.t().contiguous(), residual=dy if res_is_x else None)
+            dh = gemm.gemm_tn(g2, w2t, relu_mask=h, out_scale=scale)
+        dx = gemm.gemm_tn(dh, w1t, residual=dy if res_is_x else None)
         # weight gradients on the tcgen05 reduction kernel; a bias gradient rides along as one more accumulator column
         # unless the LayerNorm behind this block already produced it (handed) or the kernel has no column to spare
         need_db2 = has_b2 and not (handed is not None and p2 == 0)

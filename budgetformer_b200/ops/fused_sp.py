@@ -50,6 +50,7 @@ class SPContext:
         # seed shared by all ranks for masks that one rank generates and another regenerates (set by the trainer every
         # step from the run seed and the epoch; None = not set)
         self.step_seed: Optional[int] = None
+        self._packs = {}                                  # layer -> (stamp, packed W, packed bias, packed W transposed)
         self.P, self.rank = self.sw.world, self.sw.rank
         assert self.P == world
         self.rows_local, self.total_rows = int(rows_local), int(rows_local) * self.P
@@ -80,6 +81,22 @@ class SPContext:
     @property
     def row0(self) -> int:
         return self.rank * self.rows_local
+
+    def packed_projection(self, layer: int, wq, wk, wv, bq, bk, bv, dtype):
+        """``[Wq; Wk; Wv]`` with its rows in the order of ``perm`` (and the bias likewise), in the activation dtype.  The
+        pack is rebuilt only when one of the six tensors changed since it was made."""
+        parts = [t for t in (wq, wk, wv, bq, bk, bv) if t is not None]
+        stamp = (gemm._WEIGHT_GEN, dtype) + tuple((t._version, t.data_ptr()) for t in parts)
+        hit = self._packs.get(layer)
+        if hit is None or hit[0] != stamp:
+            w = torch.cat([wq, wk, wv], 0).detach().to(dtype)[self.perm].contiguous()
+            b = None if bq is None else torch.cat([bq, bk, bv], 0).detach().float()[self.perm].contiguous()
+            hit = self._packs[layer] = (stamp, w, b, w.t().contiguous())
+        return hit[1], hit[2]
+
+    def transposed_projection(self, layer: int, w: torch.Tensor) -> torch.Tensor:
+        hit = self._packs.get(layer)
+        return hit[3] if (hit is not None and hit[1] is w) else w.t().contiguous()
 
     def split_packed(self, t: torch.Tensor):
         """(q, k, v) views ``[rows, heads, hn]`` of a packed ``[rows, qkv_ld]`` buffer (column order k | v | q)."""
@@ -139,14 +156,11 @@ def _push_gemm(x, w, bias, dst_ptrs, row0, ldc, dropout_p=0.0, seed=0):
 class _QKVPush(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, wq, wk, wv, bq, bk, bv, sp: SPContext, layer: int, passthrough: bool = False):
-        w = torch.cat([wq, wk, wv], 0).to(x.dtype)[sp.perm].contiguous()
-        b = None
-        if bq is not None:
-            b = torch.cat([bq, bk, bv], 0).float()[sp.perm].contiguous()
+        w, b = sp.packed_projection(layer, wq, wk, wv, bq, bk, bv, x.dtype)
         buf = sp.qkv[layer]
         _push_gemm(x, w, b, buf.ptrs, sp.row0, sp.qkv_ld)
         sp.sw.barrier(0)
-        ctx.sp, ctx.has_bias, ctx.wdtype = sp, bq is not None, wq.dtype
+        ctx.sp, ctx.has_bias, ctx.wdtype, ctx.layer = sp, bq is not None, wq.dtype, layer
         ctx.save_for_backward(x, w)
         if passthrough:
             # the input doubles as the residual of the output projection: handing it through this function routes the
@@ -163,7 +177,7 @@ class _QKVPush(torch.autograd.Function):
             buf.tensor.copy_(dqkv)
         if dres is not None:
             dres = dres.to(x.dtype).contiguous()
-        wt = w.t().contiguous()
+        wt = sp.transposed_projection(ctx.layer, w)
         dx = None
         if _can_pull(sp, 3 * sp.hl, sp.rows_local, 3 * sp.h, sp.h, x.dtype):
             # dX = pulled(dq|dk|dv) W: the rows arrive inside the GEMM; the local copy feeds the weight gradient.
@@ -267,7 +281,7 @@ class _CtxPullOutProj(torch.autograd.Function):
         if wo is not None and not pre_pending and _can_pull(sp, sp.hl, sp.rows_local, sp.h, wo.size(0), dt):
             # the projection GEMM pulls its operand itself; a local copy is written only when a backward pass will
             # read it (weight gradient)
-            w = wo.to(dt)
+            w = gemm.operand_copy(wo, dt)
             sp.sw.barrier(0)                                         # every head owner has written its context
             y, a = _pull_gemm(sp.ctx_ptrs_for(ctx_full), sp.row0, sp.hl, sp.hl, sp.rows_local, w, bias=bo, residual=residual,
                               dropout_p=p_post, seed=seed_post, keep_copy=any(ctx.needs_input_grad[:3]))
@@ -284,7 +298,7 @@ class _CtxPullOutProj(torch.autograd.Function):
             if pre_pending:
                 a = hash_dropout(a, seed_pre, p_pre)
             if wo is not None:
-                w = wo.to(dt)
+                w = gemm.operand_copy(wo, dt)
                 y = gemm.gemm_tn(a, w, bo, None, dropout_p=p_post, dropout_seed=seed_post, residual=residual)
                 ctx.save_for_backward(a, w)
             else:
@@ -292,7 +306,7 @@ class _CtxPullOutProj(torch.autograd.Function):
                 if residual is not None:
                     y = y + residual
                 ctx.save_for_backward()
-        ctx.sp, ctx.slot = sp, slot
+        ctx.sp, ctx.slot, ctx.wo = sp, slot, wo
         ctx.cfg = (float(p_pre), float(p_post), int(seed_pre), int(seed_post), residual is not None, wo is not None,
                    bo is not None, wo.dtype if wo is not None else None)
         return y
@@ -309,7 +323,8 @@ class _CtxPullOutProj(torch.autograd.Function):
         if has_w:
             a, w = ctx.saved_tensors
             # d(context) = (g W_o) [* pre-dropout mask], pushed to the head owners by the GEMM epilogue
-            _push_gemm(g, w.t().contiguous(), None, dbuf.ptrs, sp.row0, sp.hl, dropout_p=p_pre, seed=seed_pre)
+            _push_gemm(g, gemm.operand_copy(ctx.wo, w.dtype, transpose=True), None, dbuf.ptrs, sp.row0, sp.hl,
+                       dropout_p=p_pre, seed=seed_pre)
             need_db = has_b and not (handed is not None and p_post == 0)
             dw, db = gemm.weight_grad(g, a, need_db)
             dw = dw.to(wdtype)

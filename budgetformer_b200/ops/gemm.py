@@ -15,6 +15,40 @@ from . import _ext
 ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
 _STATUS = {}
 
+# ---- operand copies of the weights ------------------------------------------------------------------------
+# The kernels take weights in the activation dtype (and the input-gradient GEMM takes them transposed).  Those copies
+# only change when the weights do: they are kept per parameter and rebuilt when the parameter's version counter moves
+# (in-place updates by PyTorch optimizers, ``load_state_dict``) or when an optimizer that writes the storage directly
+# announces a step through ``weights_changed()`` (``ops.optim.FlatAdamW``).
+_WEIGHT_GEN = 0
+_WEIGHT_COPIES = {}
+
+
+def weights_changed() -> None:
+    global _WEIGHT_GEN
+    _WEIGHT_GEN += 1
+
+
+def operand_copy(weight: torch.Tensor, dtype, transpose: bool = False, index: Optional[torch.Tensor] = None,
+                 tag: str = "") -> torch.Tensor:
+    """``weight[index].to(dtype)`` (``.t()`` when ``transpose``), contiguous, cached until the weight changes."""
+    key = (id(weight), dtype, bool(transpose), tag)
+    stamp = (_WEIGHT_GEN, weight._version, weight.data_ptr())
+    hit = _WEIGHT_COPIES.get(key)
+    if hit is not None and hit[0] == stamp and hit[2]() is weight:
+        return hit[1]
+    import weakref
+    w = weight.detach()
+    if index is not None:
+        w = w[index]
+    w = w.to(dtype)
+    w = w.t().contiguous() if transpose else w.contiguous()
+    _WEIGHT_COPIES[key] = (stamp, w, weakref.ref(weight))
+    if len(_WEIGHT_COPIES) > 4096:                     # parameters of discarded models: drop what is dead
+        for k in [k for k, v in _WEIGHT_COPIES.items() if v[2]() is None]:
+            del _WEIGHT_COPIES[k]
+    return w
+
 
 def status_tensor(device) -> torch.Tensor:
     """Per-device int32[4] written by kernels whose bounded waits expired (0 = healthy)."""
@@ -104,21 +138,22 @@ class _FusedLinear(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, bias, residual, dropout_p, dropout_seed):
-        w16 = weight.to(x.dtype)
+        w16 = operand_copy(weight, x.dtype)
         y = gemm_tn(x, w16, bias, None, dropout_p=dropout_p, dropout_seed=dropout_seed, residual=residual)
         ctx.cfg = (residual is not None, float(dropout_p), int(dropout_seed), weight.dtype, bias is not None)
-        ctx.save_for_backward(x, w16)
+        ctx.weight = weight
+        ctx.save_for_backward(x)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         from .norm import hash_dropout
-        x, w16 = ctx.saved_tensors
+        (x,) = ctx.saved_tensors
         has_res, p, seed, wdtype, has_bias = ctx.cfg
         dy = dy.contiguous()
         g = hash_dropout(dy, seed, p) if p > 0 else dy
         # dx = g @ W, expressed as g @ (W^T)^T; skipped for leaf inputs such as the feature matrix
-        dx = gemm_tn(g, w16.t().contiguous()) if ctx.needs_input_grad[0] else None
+        dx = gemm_tn(g, operand_copy(ctx.weight, x.dtype, transpose=True)) if ctx.needs_input_grad[0] else None
         dw, db = weight_grad(g, x, has_bias)
         return dx, dw.to(wdtype), (db.to(wdtype) if has_bias else None), (dy if has_res else None), None, None
 

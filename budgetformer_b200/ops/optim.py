@@ -47,6 +47,8 @@ class FlatAdamW(torch.optim.Optimizer):
     def step(self, closure=None):
         ext = _ext.load()
         self._step += 1
+        from .gemm import weights_changed
+        weights_changed()                              # the kernels below rewrite the parameters' storage directly
         g0 = self.param_groups[0]
         lr, (b1, b2), eps, wd = g0["lr"], g0["betas"], g0["eps"], g0["weight_decay"]
         clip = self.max_grad_norm > 0

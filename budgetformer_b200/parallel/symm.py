@@ -45,7 +45,8 @@ class SymmWorld:
         if self.world > MAX_PEERS:
             raise RuntimeError(f"symmetric-memory kernels support up to {MAX_PEERS} ranks, got {self.world}")
         self.bytes_allocated = 0
-        self._epoch = 0
+        # one counter per channel: a channel is driven by one host thread and sees the same sequence on every rank
+        self._epochs = [0] * FLAG_CHANNELS
         self.use_multimem = os.environ.get("BF_DISABLE_MULTIMEM", "0") != "1"
         self.flags = self.alloc((FLAG_CHANNELS * MAX_PEERS,), torch.int32, zero=True)
         if self.world > 1:
@@ -78,15 +79,15 @@ class SymmWorld:
         """Device-side barrier over all ranks on the current stream (no host synchronisation)."""
         if self.world == 1:
             return
-        self._epoch += 1
+        self._epochs[channel] += 1
         # the kernel compares epochs by signed 32-bit distance, so the counter wraps over the full 32 bits
-        _ext.load().peer_barrier(self.flags.ptrs, self.rank, int(channel), self._epoch & 0xFFFFFFFF,
+        _ext.load().peer_barrier(self.flags.ptrs, self.rank, int(channel), self._epochs[channel] & 0xFFFFFFFF,
                                  status_tensor(self.device))
         _ext.count_launches(1)
 
     def resync(self) -> None:
         """Bring every rank's barrier epoch back together after a step that some rank abandoned on the host (it issued
-        fewer barriers than its peers, so its counter lags and its next barriers would pass at once on flags that are
+        fewer barriers than its peers, so its counters lag and its next barriers would pass at once on flags that are
         already ahead).  Drains this rank's queue (barriers still waiting for the rank that stopped give up after
         their bound; once the status word is set the remaining ones return immediately), clears the status word, takes
         the maximum counter over the ranks on the host and meets the others there."""
@@ -95,7 +96,7 @@ class SymmWorld:
         torch.cuda.synchronize(self.device)
         status_tensor(self.device).zero_()
         dev = comm.comm_device(self.group, self.device)
-        self._epoch = int(comm.all_reduce_scalar(float(self._epoch), "max", self.group, dev))
+        self._epochs = [int(v) for v in comm.all_reduce_scalars([float(e) for e in self._epochs], "max", self.group, dev)]
         torch.cuda.synchronize(self.device)
         comm.barrier(self.group)
 

@@ -51,6 +51,15 @@ def test_sharded_cpu_edge_build_two_gpus():
     assert "OK sharded host build" in r.stdout, r.stdout[-2000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_device_edge_build_two_gpus():
+    """Each rank selects the rows of its own queries on its GPU and fetches the other shards through symmetric memory:
+    the graph equals the one every rank would build whole, in the step and one epoch ahead on the side stream."""
+    r = _run(2, "sharded_device_build", 29617)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "OK sharded device build" in r.stdout, r.stdout[-2000:]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_fused_path_four_gpus():
     r = _run(4, "gt,graphormer", 29613)
