@@ -3,9 +3,13 @@
 ``python -m budgetformer_b200.utils.preprocess_data --dataset <name> [--dataset_dir ./dataset/] [--split_id 0]``
 
 Sources (utils/preprocess_data.py:161-427 in the reference): Planetoid, CitationFull, Coauthor, Amazon Photo /
-Computers, Reddit, HeterophilousGraphDataset (PyG); ogbn-arxiv / products / papers100M (OGB); pokec, snap-patents,
-genius (LINKX ``.mat`` / ``.npz`` files placed under ``<dataset_dir>/raw``; genius gets five seeded 50/25/25
-splits); and ``synthetic:<config>`` which generates the benchmark graphs of this repository without any download.
+Computers, HeterophilousGraphDataset (PyG); ogbn-arxiv / products / papers100M (OGB); and, converted offline from raw
+files that are already on disk (searched in ``<dataset_dir>/<name>/``, ``<dataset_dir>/raw/<name>/``,
+``<dataset_dir>/raw/``): ``aminer`` (pickled scipy adjacency / features / one-hot labels), ``reddit`` and ``Amazon2M``
+(``<name>_adj.npz``, ``<name>_feat.npy``, ``<name>_labels.npy``), ``amazon`` (GraphSAINT ``adj_full.npz`` / ``feats.npy``
+/ ``labels.npy`` with the official ``role.json`` split), ``pokec`` / ``snap-patents`` / ``genius`` (LINKX ``.mat``
+files; genius gets five seeded 50/25/25 splits over its labelled nodes, all of them in ``split_idx_all.pt``); and
+``synthetic:<config>`` which generates the benchmark graphs of this repository without any download.
 PyG / OGB are optional: when they are not importable the corresponding names fail with a clear message.
 
 The legacy dense-bias sequence files are kept as well (utils/preprocess_data.py:25-50,431-555 in the reference):
@@ -25,7 +29,7 @@ PYG_SETS = {
     "cora": ("Planetoid", "Cora"), "citeseer": ("Planetoid", "CiteSeer"), "pubmed": ("Planetoid", "PubMed"),
     "dblp": ("CitationFull", "DBLP"), "cora_full": ("CitationFull", "Cora"),
     "cs": ("Coauthor", "CS"), "physics": ("Coauthor", "Physics"),
-    "photo": ("Amazon", "Photo"), "computers": ("Amazon", "Computers"), "reddit": ("Reddit", None),
+    "photo": ("Amazon", "Photo"), "computers": ("Amazon", "Computers"),
     "roman-empire": ("HeterophilousGraphDataset", "Roman-empire"), "amazon-ratings": ("HeterophilousGraphDataset", "Amazon-ratings"),
     "minesweeper": ("HeterophilousGraphDataset", "Minesweeper"), "tolokers": ("HeterophilousGraphDataset", "Tolokers"),
     "questions": ("HeterophilousGraphDataset", "Questions"),
@@ -81,14 +85,89 @@ def _from_ogb(name: str, root: str):
     return graph["node_feat"], torch.as_tensor(label).reshape(-1), graph["edge_index"], split
 
 
+def find_raw(root: str, name: str, files) -> str:
+    """Folder that holds every file of ``files`` for dataset ``name``; exits with the list of places searched."""
+    places = [os.path.join(root, name), os.path.join(root, "raw", name), os.path.join(root, "raw")]
+    for d in places:
+        if all(os.path.exists(os.path.join(d, f)) for f in files):
+            return d
+    raise SystemExit(f"dataset {name!r}: put {', '.join(files)} into one of {places}")
+
+
+def _edges_of(adj) -> torch.Tensor:
+    """Sorted, duplicate-free ``[2, E]`` int64 edge list of a scipy sparse adjacency (row = source)."""
+    coo = adj.tocoo()
+    n = max(adj.shape)
+    key = np.unique(coo.row.astype(np.int64) * n + coo.col.astype(np.int64))
+    return torch.from_numpy(np.stack([key // n, key % n]))
+
+
+def _class_ids(labels) -> torch.Tensor:
+    """Class id per node from one-hot (or multi-hot: first set column wins, as ``argmax`` does) rows, or from ids."""
+    y = torch.as_tensor(np.asarray(labels))
+    return y.argmax(-1).long() if y.dim() == 2 and y.size(1) > 1 else y.reshape(-1).long()
+
+
+def _from_pickles(name: str, root: str):
+    """``aminer``: ``<name>.adj.sp.pkl`` (scipy sparse), ``<name>.features.pkl``, ``<name>.labels.pkl`` (one-hot)."""
+    import pickle
+    files = [f"{name}.adj.sp.pkl", f"{name}.features.pkl", f"{name}.labels.pkl"]
+    d = find_raw(root, name, files)
+    adj, feat, lab = (pickle.load(open(os.path.join(d, f), "rb")) for f in files)
+    feat = feat.todense() if hasattr(feat, "todense") else feat
+    return torch.as_tensor(np.asarray(feat), dtype=torch.float32), _class_ids(lab), _edges_of(adj), None
+
+
+def _from_npz_triplet(name: str, root: str, files):
+    """``reddit`` / ``Amazon2M`` / GraphSAINT ``amazon``: a scipy ``.npz`` adjacency plus feature and label ``.npy`` files."""
+    import scipy.sparse as sp
+    d = find_raw(root, name, files)
+    adj = sp.load_npz(os.path.join(d, files[0]))
+    x = torch.as_tensor(np.load(os.path.join(d, files[1])), dtype=torch.float32)
+    return x, _class_ids(np.load(os.path.join(d, files[2]))), _edges_of(adj), d
+
+
+def _graphsaint_split(raw_dir: str, out_dir: str) -> dict:
+    """GraphSAINT's ``role.json`` (keys tr / va / te) is the official 80/5/15 split of AmazonProducts; it is also
+    copied next to the converted tensors, where the split loader accepts it as well."""
+    import json
+    import shutil
+    src = os.path.join(raw_dir, "role.json")
+    if not os.path.exists(src):
+        raise SystemExit(f"amazon: role.json (the official GraphSAINT split) is missing from {raw_dir}")
+    with open(src, encoding="utf-8") as fh:
+        role = json.load(fh)
+    os.makedirs(out_dir, exist_ok=True)
+    dst = os.path.join(out_dir, "role.json")
+    if os.path.abspath(dst) != os.path.abspath(src):
+        shutil.copyfile(src, dst)
+    return {"train": torch.as_tensor(role["tr"]).long(), "valid": torch.as_tensor(role["va"]).long(),
+            "test": torch.as_tensor(role["te"]).long()}
+
+
 def _from_linkx_mat(name: str, root: str):
     import scipy.io
-    path = os.path.join(root, "raw", f"{name}.mat")
-    if not os.path.exists(path):
-        raise SystemExit(f"place the LINKX file for {name!r} at {path}")
+    fname = {"snap-patents": "snap_patents.mat"}.get(name, f"{name}.mat")
+    alts = [fname, f"{name}.mat"]
+    path = None
+    for f in alts:
+        for d in (os.path.join(root, name), os.path.join(root, "raw", name), os.path.join(root, "raw")):
+            if os.path.exists(os.path.join(d, f)):
+                path = os.path.join(d, f)
+    if path is None:
+        raise SystemExit(f"place the LINKX file {fname} for {name!r} under {os.path.join(root, 'raw')}")
     m = scipy.io.loadmat(path)
     y = np.asarray(m["label"] if "label" in m else m["years"]).reshape(-1)
-    return m["node_feat"], torch.as_tensor(y).long(), m["edge_index"], None
+    feat = m["node_feat"]
+    feat = feat.todense() if hasattr(feat, "todense") else feat
+    return torch.as_tensor(np.asarray(feat), dtype=torch.float32), torch.as_tensor(y).long(), m["edge_index"], None
+
+
+def labelled_random_split(y: torch.Tensor, train_prop: float = 0.5, valid_prop: float = 0.25, seed: int = 0) -> dict:
+    """LINKX-style random split: only labelled nodes (label != -1) are distributed."""
+    labelled = torch.nonzero(torch.as_tensor(y).reshape(-1) != -1).reshape(-1)
+    part = rand_train_test_idx(int(labelled.numel()), train_prop, valid_prop, seed)
+    return {k: labelled[v] for k, v in part.items()}
 
 
 def get_dataset(name: str, root: str = "./dataset/", split_id: int = 0, seed: int = 42) -> str:
@@ -104,9 +183,23 @@ def get_dataset(name: str, root: str = "./dataset/", split_id: int = 0, seed: in
     if key.startswith("ogbn-"):
         x, y, ei, split = _from_ogb(key, root)
         return save_dataset(root, name, x, y, ei, split)
+    if key == "aminer":
+        x, y, ei, _ = _from_pickles(key, root)
+        return save_dataset(root, name, x, y, ei)
+    if key in ("reddit", "amazon2m"):
+        raw = name if key == "reddit" else "Amazon2M"
+        x, y, ei, _ = _from_npz_triplet(raw, root, [f"{raw}_adj.npz", f"{raw}_feat.npy", f"{raw}_labels.npy"])
+        return save_dataset(root, name, x, y, ei)
+    if key == "amazon":
+        x, y, ei, raw_dir = _from_npz_triplet(key, root, ["adj_full.npz", "feats.npy", "labels.npy"])
+        return save_dataset(root, name, x, y, ei, _graphsaint_split(raw_dir, os.path.join(root, name)))
     if key in ("pokec", "snap-patents", "genius"):
         x, y, ei, _ = _from_linkx_mat(key, root)
-        splits = [rand_train_test_idx(len(y), 0.5, 0.25, seed=s) for s in range(5)] if key == "genius" else None
+        splits = None
+        if key == "genius":
+            if not 0 <= split_id < 5:
+                raise SystemExit(f"split_id={split_id} out of range for the 5 genius splits")
+            splits = [labelled_random_split(y, 0.5, 0.25, seed=s) for s in range(5)]
         path = save_dataset(root, name, x, y, ei, splits[split_id] if splits else None, splits)
         if key == "snap-patents":
             from .prepare_snap_patents import prepare_labels

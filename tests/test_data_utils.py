@@ -1,6 +1,7 @@
 import os
 
 import numpy as np
+import pytest
 import torch
 
 from budgetformer_b200.train.data import (GraphData, compute_multihop_features, generate_expander_edges,
@@ -166,3 +167,78 @@ def test_locality_reordering_is_an_isomorphism(tmp_path):
     padded = pad_to_sequence_parallel_world(plain, 7)
     again = reorder_for_locality(padded, 4)
     assert again.x.size(0) == padded.x.size(0) and float(again.x[n:].abs().sum()) == 0.0
+
+
+# ---------------------------------------------------------------------------------------------- offline converters
+def _tiny_raw(n=30, classes=4, seed=0):
+    import numpy as np
+    import scipy.sparse as sp
+    rng = np.random.default_rng(seed)
+    rows, cols = rng.integers(0, n, 120), rng.integers(0, n, 120)
+    adj = sp.coo_matrix((np.ones(120, dtype=np.float32), (rows, cols)), shape=(n, n)).tocsr()   # duplicates get summed
+    feat = rng.normal(size=(n, 6)).astype(np.float32)
+    cls = rng.integers(0, classes, n)
+    onehot = np.eye(classes, dtype=np.float32)[cls]
+    return adj, feat, cls, onehot
+
+
+def _check_written(path, adj, feat, cls):
+    import numpy as np
+    x, y, ei = (torch.load(os.path.join(path, f)) for f in ("x.pt", "y.pt", "edge_index.pt"))
+    assert torch.allclose(x, torch.as_tensor(feat)) and y.tolist() == cls.tolist() and ei.dtype == torch.int64
+    want = sorted(set(zip(*adj.nonzero())))
+    assert sorted(zip(ei[0].tolist(), ei[1].tolist())) == [(int(a), int(b)) for a, b in want]     # coalesced
+
+
+def test_offline_converters_from_raw_files(tmp_path):
+    import json
+    import pickle
+    import numpy as np
+    import scipy.io
+    import scipy.sparse as sp
+    from budgetformer_b200.utils.preprocess_data import get_dataset
+    root = str(tmp_path)
+    adj, feat, cls, onehot = _tiny_raw()
+    # aminer: pickles next to the output
+    d = tmp_path / "aminer"; d.mkdir()
+    for name, obj in (("adj.sp", adj), ("features", feat), ("labels", onehot)):
+        pickle.dump(obj, open(d / f"aminer.{name}.pkl", "wb"))
+    _check_written(get_dataset("aminer", root), adj, feat, cls)
+    # reddit / Amazon2M: npz + npy under raw/<name>
+    for name in ("reddit", "Amazon2M"):
+        d = tmp_path / "raw" / name; d.mkdir(parents=True)
+        sp.save_npz(d / f"{name}_adj.npz", adj); np.save(d / f"{name}_feat.npy", feat); np.save(d / f"{name}_labels.npy", onehot)
+        _check_written(get_dataset(name, root), adj, feat, cls)
+    # GraphSAINT amazon with its role.json split
+    d = tmp_path / "raw" / "amazon"; d.mkdir(parents=True)
+    sp.save_npz(d / "adj_full.npz", adj); np.save(d / "feats.npy", feat); np.save(d / "labels.npy", onehot)
+    role = {"tr": list(range(0, 24)), "va": [24, 25], "te": [26, 27, 28, 29]}
+    json.dump(role, open(d / "role.json", "w"))
+    path = get_dataset("amazon", root)
+    _check_written(path, adj, feat, cls)
+    split = torch.load(os.path.join(path, "split_idx.pt"))
+    assert split["train"].tolist() == role["tr"] and split["valid"].tolist() == role["va"] and split["test"].tolist() == role["te"]
+    assert json.load(open(os.path.join(path, "role.json"))) == role
+    # LINKX .mat files: pokec as is, genius with five seeded splits over its labelled nodes
+    coo = adj.tocoo()
+    ei = np.stack([coo.row, coo.col]).astype(np.int64)
+    lab = cls.copy(); lab[:5] = -1
+    d = tmp_path / "raw"
+    scipy.io.savemat(d / "pokec.mat", {"edge_index": ei, "node_feat": feat, "label": lab.reshape(1, -1)})
+    scipy.io.savemat(d / "genius.mat", {"edge_index": ei, "node_feat": feat, "label": lab.reshape(1, -1)})
+    p = get_dataset("pokec", root)
+    assert torch.load(os.path.join(p, "y.pt")).tolist() == lab.tolist() and not os.path.exists(os.path.join(p, "split_idx.pt"))
+    g = get_dataset("genius", root, split_id=3)
+    all_splits = torch.load(os.path.join(g, "split_idx_all.pt"))
+    assert len(all_splits) == 5
+    chosen = torch.load(os.path.join(g, "split_idx.pt"))
+    assert chosen["train"].tolist() == all_splits[3]["train"].tolist()
+    for s in all_splits:
+        ids = torch.cat([s["train"], s["valid"], s["test"]])
+        assert sorted(ids.tolist()) == list(range(5, 30))                    # unlabelled nodes are in no part
+        assert len(s["train"]) == 12 and len(s["valid"]) == 6                # 50 / 25 / 25 of the 25 labelled nodes
+    assert all_splits[0]["train"].tolist() != all_splits[1]["train"].tolist()
+    with pytest.raises(SystemExit):
+        get_dataset("genius", root, split_id=7)
+    with pytest.raises(SystemExit):
+        get_dataset("aminer", str(tmp_path / "nowhere"))
