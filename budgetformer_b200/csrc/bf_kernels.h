@@ -166,8 +166,13 @@ int bf_gemm_dw(const bf_gemm_dw_params* p, cudaStream_t st);
 // `flag_pages[r]` / `bufs[r]` are this process's mappings of rank r's symmetric allocation.
 int bf_peer_barrier(void* const* flag_pages, int rank, int world, int channel, uint32_t epoch, int* status,
                     cudaStream_t st);
+// In-place mean over ranks of a symmetric fp32 buffer.  Optional gradient-norm by-product (both NULL = off):
+// norm_scratch = local float[bf_allreduce_mean_grid(n_floats, world) + 1], zero before the first use;
+// norm_parts[r] = rank r's float[world] array (symmetric): slot `rank` of every array receives the sum of squares of the
+// slice this rank reduced, so after the collective every rank holds the `world` slice totals of the averaged buffer.
+int bf_allreduce_mean_grid(long long n_floats, int world);
 int bf_allreduce_mean(void* const* bufs, float* multicast_ptr, int rank, int world, long long n_floats,
-                      cudaStream_t st);
+                      float* norm_scratch, void* const* norm_parts, cudaStream_t st);
 int bf_peer_gather_cols(void* const* src, int world, long long row0, long long rows, int cols_bytes,
                         long long src_ld_bytes, void* dst, long long dst_ld_bytes, cudaStream_t st);
 int bf_peer_scatter_cols(void* const* dst, int world, long long row0, long long rows, int cols_bytes,
@@ -219,12 +224,15 @@ int bf_col_affine(const void* x, long long ldx, const void* in2, long long ld2, 
 
 // ---- optimizer on flat fp32 buckets (optim.cu) -----------------------------------------------------
 int bf_grad_sumsq(const float* g, long long n, float* out /* += sum g^2 */, cudaStream_t st);
+// sumsq: n_sumsq floats whose sum is the squared global gradient norm (one float from bf_grad_sumsq, or the per-rank
+// slice totals left by bf_allreduce_mean), or NULL for no clipping.
 int bf_adamw_flat(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1, float beta2,
-                  float eps, float weight_decay, int step, const float* sumsq /* or NULL */, float max_norm,
+                  float eps, float weight_decay, int step, const float* sumsq /* or NULL */, int n_sumsq, float max_norm,
                   cudaStream_t st);
 // Graph-capturable form: hyper = device float[3] {lr, 1 - beta1^t, sqrt(1 - beta2^t)} refreshed by the host each step.
 int bf_adamw_flat_dev(float* p, const float* g, float* m, float* v, long long n, float beta1, float beta2, float eps,
-                      float weight_decay, const float* hyper, const float* sumsq, float max_norm, cudaStream_t st);
+                      float weight_decay, const float* hyper, const float* sumsq, int n_sumsq, float max_norm,
+                      cudaStream_t st);
 
 // ---- readout loss (loss.cu) ---------------------------------------------------------------------------
 // loss_sum += sum over rows with mask != 0 of -log softmax(logits[row])[y[row]]; when dlogits != NULL it receives

@@ -505,10 +505,20 @@ void peer_barrier(std::vector<int64_t> flag_pages, int64_t rank, int64_t channel
                              status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()), "peer_barrier");
 }
 
-void allreduce_mean(std::vector<int64_t> bufs, int64_t multicast_ptr, int64_t rank, int64_t n_floats, Tensor anchor) {
+// norm_scratch / norm_parts: optional by-product, see bf_allreduce_mean (pass an empty list and None to skip it).
+void allreduce_mean(std::vector<int64_t> bufs, int64_t multicast_ptr, int64_t rank, int64_t n_floats, Tensor anchor,
+                    OptTensor norm_scratch, std::vector<int64_t> norm_parts) {
   c10::cuda::CUDAGuard guard(anchor.device());
   auto p = as_ptrs(bufs);
+  const bool with_norm = norm_scratch.has_value() && !norm_parts.empty();
+  std::vector<void*> parts;
+  if (with_norm) {
+    TORCH_CHECK(norm_parts.size() == bufs.size() && norm_scratch->scalar_type() == torch::kFloat && norm_scratch->is_contiguous() &&
+                norm_scratch->numel() >= bf_allreduce_mean_grid(n_floats, (int)bufs.size()) + 1, "allreduce_mean: norm scratch too small");
+    parts = as_ptrs(norm_parts);
+  }
   check_cuda(bf_allreduce_mean(p.data(), reinterpret_cast<float*>(multicast_ptr), (int)rank, (int)bufs.size(), n_floats,
+                               with_norm ? norm_scratch->data_ptr<float>() : nullptr, with_norm ? parts.data() : nullptr,
                                at::cuda::getCurrentCUDAStream()), "allreduce_mean");
 }
 
@@ -630,8 +640,8 @@ void adamw_flat(Tensor p, Tensor g, Tensor m, Tensor v, int64_t n, double lr, do
   c10::cuda::CUDAGuard guard(p.device());
   check_cuda(bf_adamw_flat(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), n, (float)lr,
                            (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
-                           sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr, (float)max_norm,
-                           at::cuda::getCurrentCUDAStream()), "adamw_flat");
+                           sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr, sumsq.has_value() ? (int)sumsq->numel() : 0,
+                           (float)max_norm, at::cuda::getCurrentCUDAStream()), "adamw_flat");
 }
 
 void adamw_flat_dev(Tensor p, Tensor g, Tensor m, Tensor v, int64_t n, double beta1, double beta2, double eps, double wd,
@@ -642,7 +652,8 @@ void adamw_flat_dev(Tensor p, Tensor g, Tensor m, Tensor v, int64_t n, double be
   c10::cuda::CUDAGuard guard(p.device());
   check_cuda(bf_adamw_flat_dev(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), n,
                                (float)beta1, (float)beta2, (float)eps, (float)wd, hyper.data_ptr<float>(),
-                               sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr, (float)max_norm,
+                               sumsq.has_value() ? sumsq->data_ptr<float>() : nullptr,
+                               sumsq.has_value() ? (int)sumsq->numel() : 0, (float)max_norm,
                                at::cuda::getCurrentCUDAStream()), "adamw_flat_dev");
 }
 
@@ -693,6 +704,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_flat_dev", &adamw_flat_dev);
   m.def("peer_barrier", &peer_barrier);
   m.def("allreduce_mean", &allreduce_mean);
+  m.def("allreduce_mean_grid", [](int64_t n_floats, int64_t world) { return (int64_t)bf_allreduce_mean_grid(n_floats, (int)world); });
   m.def("peer_gather_cols", &peer_gather_cols);
   m.def("peer_scatter_cols", &peer_scatter_cols);
 }

@@ -30,16 +30,20 @@ __global__ void __launch_bounds__(512) sumsq_kernel(const float* __restrict__ g,
   }
 }
 
+// Squared gradient norm from its parts, added in index order by every thread alike (a handful of floats).
+__device__ __forceinline__ float total_sumsq(const float* __restrict__ parts, int n) {
+  float t = 0.f;
+  for (int i = 0; i < n; ++i) t += parts[i];
+  return t;
+}
+
 __global__ void __launch_bounds__(512) adamw_flat_kernel(float* __restrict__ p, const float* __restrict__ g,
                                                          float* __restrict__ m, float* __restrict__ v, long long n,
                                                          float lr, float beta1, float beta2, float eps, float wd,
                                                          float bc1, float bc2_sqrt, const float* __restrict__ sumsq,
-                                                         float max_norm) {
+                                                         int n_sumsq, float max_norm) {
   float clip = 1.f;
-  if (sumsq != nullptr && max_norm > 0.f) {
-    const float norm = sqrtf(*sumsq);
-    clip = fminf(1.f, max_norm / (norm + 1e-6f));
-  }
+  if (sumsq != nullptr && max_norm > 0.f) clip = fminf(1.f, max_norm / (sqrtf(total_sumsq(sumsq, n_sumsq)) + 1e-6f));
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     const float gi = g[i] * clip;
@@ -59,10 +63,10 @@ __global__ void __launch_bounds__(512) adamw_flat_dev_kernel(float* __restrict__
                                                              float* __restrict__ m, float* __restrict__ v, long long n,
                                                              float beta1, float beta2, float eps, float wd,
                                                              const float* __restrict__ hyper,
-                                                             const float* __restrict__ sumsq, float max_norm) {
+                                                             const float* __restrict__ sumsq, int n_sumsq, float max_norm) {
   const float lr = hyper[0], bc1 = hyper[1], bc2_sqrt = hyper[2];
   float clip = 1.f;
-  if (sumsq != nullptr && max_norm > 0.f) clip = fminf(1.f, max_norm / (sqrtf(*sumsq) + 1e-6f));
+  if (sumsq != nullptr && max_norm > 0.f) clip = fminf(1.f, max_norm / (sqrtf(total_sumsq(sumsq, n_sumsq)) + 1e-6f));
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     const float gi = g[i] * clip;
@@ -92,21 +96,21 @@ extern "C" int bf_grad_sumsq(const float* g, long long n, float* out, cudaStream
 }
 
 extern "C" int bf_adamw_flat(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1,
-                             float beta2, float eps, float weight_decay, int step, const float* sumsq, float max_norm,
-                             cudaStream_t st) {
+                             float beta2, float eps, float weight_decay, int step, const float* sumsq, int n_sumsq,
+                             float max_norm, cudaStream_t st) {
   if (n <= 0) return 0;
   const float bc1 = 1.f - powf(beta1, (float)step);
   const float bc2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
   adamw_flat_kernel<<<grid_for(n), 512, 0, st>>>(p, g, m, v, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, sumsq,
-                                                 max_norm);
+                                                 n_sumsq, max_norm);
   return (int)cudaGetLastError();
 }
 
 extern "C" int bf_adamw_flat_dev(float* p, const float* g, float* m, float* v, long long n, float beta1, float beta2,
-                                 float eps, float weight_decay, const float* hyper, const float* sumsq, float max_norm,
-                                 cudaStream_t st) {
+                                 float eps, float weight_decay, const float* hyper, const float* sumsq, int n_sumsq,
+                                 float max_norm, cudaStream_t st) {
   if (n <= 0) return 0;
   adamw_flat_dev_kernel<<<grid_for(n), 512, 0, st>>>(p, g, m, v, n, beta1, beta2, eps, weight_decay, hyper, sumsq,
-                                                     max_norm);
+                                                     n_sumsq, max_norm);
   return (int)cudaGetLastError();
 }

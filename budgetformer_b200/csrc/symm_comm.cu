@@ -8,7 +8,9 @@
 //                          stores the scaled result into slice r of every peer's bucket (two-shot,
 //                          bandwidth optimal: each byte crosses NVLink once in and once out).
 //                          With an NVSwitch multicast mapping the same slice is reduced inside the
-//                          switch (multimem.ld_reduce) and broadcast with multimem.st;
+//                          switch (multimem.ld_reduce) and broadcast with multimem.st.  The same kernel
+//                          leaves the sum of squares of the reduced slice with every rank, so that global-norm
+//                          clipping needs no further pass over the gradients;
 //  * bf_peer_gather_cols - heads->nodes all-to-all as a pull: this rank's rows of every peer's
 //                          [N, h/P] context buffer are copied into a local [N/P, h] matrix.
 // Replaces the reference's NCCL all_reduce with three elementwise passes (gt_sp/reducer.py:120-146)
@@ -56,13 +58,47 @@ __global__ void peer_barrier_kernel(PeerPtrs flag_pages, int rank, int world, in
   }
 }
 
+// Sum of squares of the values this rank reduced, finished by the last block to arrive: block partials go to
+// `scratch[0 .. gridDim.x)`, the counter behind them elects the last block, which adds the partials in a fixed order
+// and stores the slice total into slot `rank` of every rank's `parts` array (gradient-norm clipping needs the norm of
+// the whole reduced bucket: the optimizer adds the P slice totals).  Resets the counter for the next launch.
+__device__ void finish_sumsq(float sq, float* scratch, PeerPtrs parts, int rank, int world) {
+  __shared__ float s_warp[16];
+  __shared__ int s_last;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) v += s_warp[w];
+    scratch[blockIdx.x] = v;
+    __threadfence();
+    unsigned* counter = reinterpret_cast<unsigned*>(scratch + gridDim.x);
+    s_last = (atomicAdd(counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < 32) {
+    __threadfence();
+    float v = 0.f;
+    for (int b = threadIdx.x; b < (int)gridDim.x; b += 32) v += *reinterpret_cast<volatile float*>(scratch + b);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) {
+      for (int r = 0; r < world; ++r) static_cast<float*>(parts.p[r])[rank] = v;
+      *reinterpret_cast<unsigned*>(scratch + gridDim.x) = 0u;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(512) allreduce_mean_kernel(PeerPtrs bufs, int rank, int world, long long n_vec4,
-                                                             float scale) {
+                                                             float scale, float* norm_scratch, PeerPtrs norm_parts) {
   // slice of 16-byte vectors owned by this rank
   const long long per = (n_vec4 + world - 1) / world;
   const long long beg = per * rank;
   const long long end = beg + per < n_vec4 ? beg + per : n_vec4;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  float sq = 0.f;
   for (long long i = beg + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end; i += stride) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -73,18 +109,22 @@ __global__ void __launch_bounds__(512) allreduce_mean_kernel(PeerPtrs bufs, int 
       }
     }
     acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
 #pragma unroll
     for (int r = 0; r < BF_MAX_PEERS; ++r)
       if (r < world) static_cast<float4*>(bufs.p[(rank + r) % world])[i] = acc;
   }
+  if (norm_scratch != nullptr) finish_sumsq(sq, norm_scratch, norm_parts, rank, world);
 }
 
 __global__ void __launch_bounds__(512) allreduce_mean_multimem_kernel(float* mc_ptr, int rank, int world,
-                                                                      long long n_vec4, float scale) {
+                                                                      long long n_vec4, float scale, float* norm_scratch,
+                                                                      PeerPtrs norm_parts) {
   const long long per = (n_vec4 + world - 1) / world;
   const long long beg = per * rank;
   const long long end = beg + per < n_vec4 ? beg + per : n_vec4;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  float sq = 0.f;
   for (long long i = beg + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end; i += stride) {
     float* addr = mc_ptr + 4 * i;
     float x, y, z, w;
@@ -93,10 +133,12 @@ __global__ void __launch_bounds__(512) allreduce_mean_multimem_kernel(float* mc_
                  : "l"(addr)
                  : "memory");
     x *= scale; y *= scale; z *= scale; w *= scale;
+    sq += x * x + y * y + z * z + w * w;
     asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z),
                  "f"(w)
                  : "memory");
   }
+  if (norm_scratch != nullptr) finish_sumsq(sq, norm_scratch, norm_parts, rank, world);
 }
 
 // dst[row, r*cols + c] = peer_r[(row0 + row), c]   (16-byte vectors; cols*elem_size % 16 == 0)
@@ -163,17 +205,24 @@ extern "C" int bf_peer_barrier(void* const* flag_pages, int rank, int world, int
   return (int)cudaGetLastError();
 }
 
+extern "C" int bf_allreduce_mean_grid(long long n_floats, int world) {
+  if (world < 1 || n_floats <= 0) return 1;
+  const long long per = (n_floats / 4 + world - 1) / world;
+  return grid_for(per, 512);
+}
+
 extern "C" int bf_allreduce_mean(void* const* bufs, float* multicast_ptr, int rank, int world, long long n_floats,
-                                 cudaStream_t st) {
+                                 float* norm_scratch, void* const* norm_parts, cudaStream_t st) {
   if (world < 1 || world > BF_MAX_PEERS || n_floats % 4 != 0) return (int)cudaErrorInvalidValue;
+  if ((norm_scratch == nullptr) != (norm_parts == nullptr)) return (int)cudaErrorInvalidValue;
   const long long n_vec4 = n_floats / 4;
-  const long long per = (n_vec4 + world - 1) / world;
-  const int grid = grid_for(per, 512);
+  const int grid = bf_allreduce_mean_grid(n_floats, world);
   const float scale = 1.0f / (float)world;
+  PeerPtrs parts = norm_parts ? to_ptrs(norm_parts, world) : PeerPtrs{};
   if (multicast_ptr)
-    allreduce_mean_multimem_kernel<<<grid, 512, 0, st>>>(multicast_ptr, rank, world, n_vec4, scale);
+    allreduce_mean_multimem_kernel<<<grid, 512, 0, st>>>(multicast_ptr, rank, world, n_vec4, scale, norm_scratch, parts);
   else
-    allreduce_mean_kernel<<<grid, 512, 0, st>>>(to_ptrs(bufs, world), rank, world, n_vec4, scale);
+    allreduce_mean_kernel<<<grid, 512, 0, st>>>(to_ptrs(bufs, world), rank, world, n_vec4, scale, norm_scratch, parts);
   return (int)cudaGetLastError();
 }
 

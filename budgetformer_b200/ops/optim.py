@@ -63,14 +63,26 @@ class FlatAdamW(torch.optim.Optimizer):
             self._graph.replay()
             _ext.count_launches(len(self.buckets) * (2 if clip else 1))
             return
-        if clip:
+        sumsq = self._fused_norm_parts() if clip else None
+        fused = sumsq is not None
+        if clip and not fused:
             self._sumsq.zero_()
             for b in self.buckets:
                 ext.grad_sumsq(b.flat, self._sumsq)
+            sumsq = self._sumsq
+        self._last_sumsq = sumsq
         for b, p, m, v in zip(self.buckets, self._flat_p, self._m, self._v):
             ext.adamw_flat(p, b.flat, m, v, int(b.n_valid), float(lr), float(b1), float(b2), float(eps), float(wd),
-                           int(self._step), self._sumsq if clip else None, self.max_grad_norm)
-        _ext.count_launches(len(self.buckets) * (2 if clip else 1))
+                           int(self._step), sumsq, self.max_grad_norm)
+        _ext.count_launches(len(self.buckets) * (2 if (clip and not fused) else 1))
+
+    def _fused_norm_parts(self):
+        """The gradient all-reduce of this step left the squared norm of every reduced slice with every rank
+        (``parallel.symm.bucket_all_reduce_mean``): clip on their sum, no further pass over the gradients."""
+        norms = [getattr(b, "norm", None) for b in self.buckets]
+        if norms and all(n is not None and n["ready"] for n in norms):
+            return norms[0]["all"]
+        return None
 
     def _launch_dev(self, ext, b1, b2, eps, wd, clip) -> None:
         if clip:
@@ -96,7 +108,8 @@ class FlatAdamW(torch.optim.Optimizer):
 
     def grad_norm(self) -> torch.Tensor:
         """Device tensor holding the global gradient norm of the last step."""
-        return self._sumsq.sqrt()
+        src = getattr(self, "_last_sumsq", None)
+        return (self._sumsq if src is None else src.sum().reshape(1)).sqrt()
 
     def state_dict(self):
         return {"step": self._step, "m": [t.cpu() for t in self._m], "v": [t.cpu() for t in self._v],

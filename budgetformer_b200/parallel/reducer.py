@@ -113,6 +113,8 @@ class GradientReducer:
                     b._bind()
                     break
             b.flat.zero_()
+            if getattr(b, "norm", None) is not None:
+                b.norm["ready"] = False
 
     def finalize_backward(self) -> None:
         if self.world_size <= 1:

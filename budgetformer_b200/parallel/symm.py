@@ -126,12 +126,21 @@ def attach_buckets(buckets, group) -> bool:
     if not buckets or buckets[0].flat.device.type != "cuda" or comm.group_size(group) == 1:
         return False
     world = get_world(group, buckets[0].flat.device)
-    for b in buckets:
+    # one array of squared-norm parts for all buckets: row i holds, after bucket i's all-reduce, the sum of squares of
+    # the slice each rank reduced (unused slots stay zero), so the optimizer clips on the sum of the whole array
+    parts = world.alloc((len(buckets) * MAX_PEERS,), torch.float32, zero=True)
+    for i, b in enumerate(buckets):
         if b.flat.dtype != torch.float32:
             continue
         sb = world.alloc((b.flat.numel(),), torch.float32, zero=True)
         b.rebind_to(sb.tensor)
         b.symm = (world, sb)
+        grid = int(_ext.load().allreduce_mean_grid(b.flat.numel(), world.world))
+        b.norm = {"scratch": torch.zeros(grid + 1, dtype=torch.float32, device=b.flat.device),
+                  "ptrs": [p + 4 * i * MAX_PEERS for p in parts.ptrs], "all": parts.tensor, "ready": False}
+    if world.world > 1:
+        torch.cuda.synchronize(world.device)
+        dist.barrier(group=world.group)                # every rank's parts array is zero before anyone writes into it
     return True
 
 
@@ -140,7 +149,11 @@ def bucket_all_reduce_mean(bucket) -> None:
     multimem) all-reduce, barrier."""
     world, sb = bucket.symm
     ext = _ext.load()
+    norm = getattr(bucket, "norm", None)
     world.barrier(1)                       # every rank's gradients are complete
-    ext.allreduce_mean(sb.ptrs, sb.multicast_ptr, world.rank, sb.tensor.numel(), sb.tensor)
+    ext.allreduce_mean(sb.ptrs, sb.multicast_ptr, world.rank, sb.tensor.numel(), sb.tensor,
+                       norm["scratch"] if norm else None, norm["ptrs"] if norm else [])
     _ext.count_launches(1)
-    world.barrier(1)                       # every slice has been written everywhere
+    world.barrier(1)                       # every slice (and every rank's norm part) has been written everywhere
+    if norm:
+        norm["ready"] = True

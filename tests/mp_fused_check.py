@@ -113,6 +113,12 @@ def main():
         a.reducer.finalize_backward(); f.reducer.finalize_backward()
         torch.cuda.synchronize()
         gemm.check_status(dev)
+        # the all-reduce kernel also leaves the squared norm of the averaged gradients (one part per rank) everywhere
+        norms = [getattr(b, "norm", None) for b in f.reducer.buckets]
+        assert all(n is not None and n["ready"] for n in norms), "fused gradient norm missing"
+        got = float(norms[0]["all"].double().sum())
+        want = sum(float((b.flat.double() ** 2).sum()) for b in f.reducer.buckets)
+        assert abs(got - want) <= 1e-4 * max(want, 1e-12), f"{m}: fused grad norm^2 {got} vs {want} on rank {rank}"
         gmax = max(float(p.grad.abs().max()) for p in a.model.parameters())
         nmax = max(float(p.grad.float().norm()) for p in a.model.parameters())
         for (na, pa), (_, pf) in zip(a.model.named_parameters(), f.model.named_parameters()):
