@@ -161,6 +161,8 @@ def run_ours(ns):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local_rank % torch.cuda.device_count())     # large graphs are generated on this rank's GPU
     x, y, ei, cfg = make_bench_graph(ns.config, seed=42, scale=ns.scale)
     n = x.size(0)
     data = GraphData(x, y, ei, random_split_idx(n, 42), n, int(cfg["classes"]), bool(cfg.get("multilabel")))

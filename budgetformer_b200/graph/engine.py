@@ -100,7 +100,16 @@ class EdgeEngine:
             from .builder_spec import parse_fanout
             self.fanout = parse_fanout(getattr(args, "fanout", "10,5"))
         t0 = time.perf_counter()
-        self.topo_cpu = Topology.from_edge_index(edge_index_global.cpu(), self.num_nodes)
+        if self.device.type == "cuda" and edge_index_global.size(1) >= 20_000_000:
+            # the two CSR forms need a sort and a unique over all edges: seconds on the GPU, minutes on the host
+            try:
+                self.topo_cpu = Topology.from_edge_index(edge_index_global.to(self.device), self.num_nodes).to("cpu")
+                torch.cuda.empty_cache()
+            except torch.cuda.OutOfMemoryError:
+                torch.cuda.empty_cache()
+                self.topo_cpu = Topology.from_edge_index(edge_index_global.cpu(), self.num_nodes)
+        else:
+            self.topo_cpu = Topology.from_edge_index(edge_index_global.cpu(), self.num_nodes)
         if self.device.type == "cuda":
             try:
                 self.topo_cpu = self.topo_cpu.pin_memory()

@@ -242,3 +242,17 @@ def test_offline_converters_from_raw_files(tmp_path):
         get_dataset("genius", root, split_id=7)
     with pytest.raises(SystemExit):
         get_dataset("aminer", str(tmp_path / "nowhere"))
+
+
+def test_device_chung_lu_generator_gives_the_requested_graph():
+    from budgetformer_b200.graph.synthetic import chung_lu_edges_device
+    n, e = 5000, 40000
+    ei = chung_lu_edges_device(n, e, 2.1, True, 7, "cpu")
+    assert ei.shape == (2, e) and ei.dtype == torch.int64 and int((ei[0] == ei[1]).sum()) == 0
+    assert torch.unique(ei[0] * n + ei[1]).numel() == e                       # distinct pairs, exactly the requested count
+    assert torch.equal(ei, chung_lu_edges_device(n, e, 2.1, True, 7, "cpu"))   # deterministic in the seed
+    assert int(torch.bincount(ei[1], minlength=n).max()) > 50 * e // n        # heavy tail: a hub far above the mean degree
+    und = chung_lu_edges_device(n, e // 2, 2.1, False, 7, "cpu")
+    assert und.shape == (2, e)
+    fwd = set(zip(und[0].tolist(), und[1].tolist()))
+    assert all((b, a) in fwd for a, b in fwd)                                 # both directions present
