@@ -89,7 +89,7 @@ class FullGraphTrainer:
         from ..utils.watchdog import build_watchdog
         self.watchdog = build_watchdog(args, self.rank, self.sp_world)
         if self.watchdog is not None:
-            self.fault.on_exit = lambda: self.watchdog.leave("injected exit")
+            self.fault.on_exit = self._depart
 
         # ---- data -------------------------------------------------------------------------------
         if data is None:
@@ -200,8 +200,16 @@ class FullGraphTrainer:
         if wd or "exit@" in spec or "stall@" in spec:
             os.environ["NCCL_NVLS_ENABLE"] = "0"
             os.environ["BF_DISABLE_MULTIMEM"] = "1"
+            os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"     # symmetric allocations are not bound to a multicast object
             if int(os.environ.get("RANK", "0")) == 0:
                 print("[init] watchdog / departure faults requested: NVLS and multimem are off for this run", flush=True)
+
+    def _depart(self) -> None:
+        """Orderly departure of this rank between steps: let every kernel it has queued finish first (its peers' kernels
+        of the same step wait for flags that only those kernels raise), then tell the others through the store."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self.watchdog.leave("injected exit")
 
     def log(self, msg: str) -> None:
         if self.rank == 0:

@@ -75,7 +75,40 @@ def check_sharded_device_build():
         print("OK sharded device build", flush=True)
 
 
+def check_watchdog_departure():
+    """A rank leaves between steps (host-injected exit, nothing of it in flight); the survivor learns of it on the host
+    before its next launch.  The trainer switches NVLS and multimem off for such a run before any group exists."""
+    from budgetformer_b200.utils.watchdog import PeerLost
+    import json
+    t = trainer("gt", fused=True, extra=["--watchdog_seconds", "5", "--fault_inject", "exit@step:3:rank1", "--epochs", "6",
+                                        "--eval_every", "100"])
+    assert os.environ.get("NCCL_NVLS_ENABLE") == "0" and os.environ.get("BF_DISABLE_MULTIMEM") == "1"
+    sw = symm.get_world(t.sp_group, t.device)
+    assert t.fused_sp and not sw.use_multimem
+    # a rank may only leave when no allocation of the job is bound to an NVSwitch multicast object: verify it on every
+    # rank before anything departs; if a binding is still there, nobody leaves and the parent skips the test
+    bound = torch.tensor([1.0 if bool(getattr(sw.flags.handle, "has_multicast_support", False)) else 0.0], device=t.device)
+    dist.all_reduce(bound, op=dist.ReduceOp.MAX)
+    if float(bound) > 0:
+        print("WATCHDOG " + json.dumps({"outcome": "multicast_bound"}), flush=True)
+        t.edge_engine.shutdown()
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+    try:
+        t.fit()
+        out = {"outcome": "finished"}
+    except PeerLost as e:
+        torch.cuda.synchronize()                     # the survivor's own queue drains: nothing waits for the lost rank
+        code = int(gemm.status_tensor(t.device)[0])
+        out = {"outcome": "peer_lost", "message": str(e), "epoch": t.epoch, "status": code}
+    print("WATCHDOG " + json.dumps(out), flush=True)
+    os._exit(0)                                      # the peer is gone: skip the collective teardown
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "watchdog_leave":
+        return check_watchdog_departure()
     if len(sys.argv) > 1 and sys.argv[1] in ("sharded_build", "sharded_device_build"):
         check_sharded_host_build() if sys.argv[1] == "sharded_build" else check_sharded_device_build()
         dist.barrier()

@@ -60,6 +60,22 @@ def test_sharded_device_edge_build_two_gpus():
     assert "OK sharded device build" in r.stdout, r.stdout[-2000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_watchdog_rank_leaves_between_steps_two_gpus():
+    """Rank 1 finishes step 2, drains its queue, announces its departure and exits (code 0, so that the launcher leaves
+    rank 0 alone); rank 0 gets PeerLost at its next step boundary, with a clean device status.  Host-side failure only:
+    no kernel or collective is in flight when the rank leaves, NVLS and multimem are off."""
+    import json
+    r = _run(2, "watchdog_leave", 29618, {"BF_FAULT_EXIT_CODE": "0"})
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("WATCHDOG ")]
+    assert lines, r.stdout[-2000:] + r.stderr[-3000:]
+    out = json.loads(lines[0][len("WATCHDOG "):])
+    if out["outcome"] == "multicast_bound":
+        pytest.skip("symmetric allocations are still bound to a multicast object on this machine: no rank may leave")
+    assert out["outcome"] == "peer_lost" and "rank 1 left" in out["message"], out
+    assert out["epoch"] == 2 and out["status"] == 0, out
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_fused_path_four_gpus():
     r = _run(4, "gt,graphormer", 29613)
