@@ -167,7 +167,8 @@ class GraphGPS(NodeModelBase):
     def forward_logits(self, x, attn_bias, edge_index, attn_type=None):
         x = encode_features(self.node_encoder, x).unsqueeze(0)
         x = self._run_layers(x, attn_bias=attn_bias, edge_index=edge_index, attn_type=attn_type)
-        return self.output_proj(x.squeeze(0))
+        from ..ops.gemm import readout_linear
+        return readout_linear(x.squeeze(0), self.output_proj.weight, self.output_proj.bias)
 
     def forward(self, x, attn_bias, edge_index, attn_type=None):
         return F.log_softmax(self.forward_logits(x, attn_bias, edge_index, attn_type), dim=1)

@@ -150,7 +150,8 @@ class Graphormer(NodeModelBase):
         bias = self._graph_attn_bias(attn_bias, x.device)
         x = self._run_layers(x, attn_bias=bias, edge_index=edge_index, attn_type=attn_type)
         x = self.final_ln(x)
-        return self.downstream_out_proj(x[0, int(self.num_global_node):, :])
+        from ..ops.gemm import readout_linear
+        return readout_linear(x[0, int(self.num_global_node):, :], self.downstream_out_proj.weight, self.downstream_out_proj.bias)
 
     def forward(self, x, attn_bias, edge_index, perturb=None, attn_type=None):
         return F.log_softmax(self.forward_logits(x, attn_bias, edge_index, perturb, attn_type), dim=1)

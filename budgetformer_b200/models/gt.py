@@ -85,10 +85,11 @@ class MLPReadout(nn.Module):
         self.L = L
 
     def forward(self, x):
+        from ..ops.gemm import readout_linear
         y = x
         for l in range(self.L):
-            y = F.relu(self.FC_layers[l](y))
-        return self.FC_layers[self.L](y)
+            y = F.relu(readout_linear(y, self.FC_layers[l].weight, self.FC_layers[l].bias))
+        return readout_linear(y, self.FC_layers[self.L].weight, self.FC_layers[self.L].bias)
 
 
 class GT(NodeModelBase):

@@ -169,3 +169,21 @@ def fused_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
         keep = hash_keep_mask(dropout_seed, y.size(0), y.size(1), dropout_p, y.device)
         y = torch.where(keep, y / (1.0 - dropout_p), torch.zeros_like(y))
     return y if residual is None else y + residual
+
+
+def readout_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weight.T + bias`` for the small output layers (h -> classes).  The tcgen05 kernels want the output width
+    to be a multiple of 16: a narrower layer is run with zero rows appended to the weight (and zeros to the bias) and
+    the extra columns are cut off again, so its forward, input gradient and weight gradient stay off the library GEMM.
+    Inputs the kernels cannot take (fp32 activations, fewer than 64 input features) use ``torch.nn.functional.linear``."""
+    n, k = weight.shape
+    usable = (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and k >= 64 and k % 8 == 0
+              and x.stride(1) == 1 and (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0)
+    if not usable:
+        return torch.nn.functional.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
+    pad = (-n) % 16
+    if pad == 0:
+        return fused_linear(x, weight, bias)
+    w = torch.cat([weight, weight.new_zeros(pad, k)], 0)
+    b = None if bias is None else torch.cat([bias, bias.new_zeros(pad)], 0)
+    return fused_linear(x, w, b)[:, :n]

@@ -817,6 +817,12 @@ class FullGraphTrainer:
         from .report import print_training_header, print_training_summary
         args = self.args
         print_training_header(self)
+        if (self.planner is not None and self.controller.frozen and not self.edge_engine.policy_locked
+                and not self.planner.is_active() and not self.planner.edge_costs):
+            # the budget never moves (fixed split, or a resumed run whose search is over): the placement policies are
+            # measured once before the first step, as the reference does at its first epoch with a frozen budget
+            # (main_node_fullgraph_sp.py:665-988)
+            self.profile_edge_policies()
         start_epoch = self.epoch + 1
         for epoch in range(start_epoch, int(args.epochs) + 1):
             if self.device.type == "cuda":

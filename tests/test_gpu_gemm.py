@@ -351,3 +351,26 @@ def test_weight_gradient_gemm_on_strided_views():
     gemm.check_status("cuda")
     assert (dw - dy.float().t() @ x.float()).abs().max() < 0.2
     assert (db - dy.float().sum(0)).abs().max() < 0.2
+
+
+@pytest.mark.parametrize("n_out,k", [(5, 128), (40, 128), (47, 256), (64, 128), (5, 32)])
+def test_readout_linear_pads_narrow_outputs(n_out, k):
+    """Output layers narrower than the kernels' 16-column granule run with zero rows appended to the weight: forward and
+    all three gradients equal the float32 reference; inputs with fewer than 64 features fall back to the library."""
+    torch.manual_seed(13)
+    m = 2000
+    x = torch.randn(m, k, device="cuda").bfloat16().requires_grad_(True)
+    lin = torch.nn.Linear(k, n_out).cuda()
+    y = gemm.readout_linear(x, lin.weight, lin.bias)
+    assert y.shape == (m, n_out)
+    dy = torch.randn(m, n_out, device="cuda").bfloat16()
+    y.backward(dy)
+    gemm.check_status("cuda")
+    x2 = x.detach().float().requires_grad_(True)
+    w2, b2 = lin.weight.detach().clone().requires_grad_(True), lin.bias.detach().clone().requires_grad_(True)
+    ref = x2 @ w2.t() + b2
+    ref.backward(dy.float())
+    assert (y.float() - ref).abs().max() < 0.05
+    assert (x.grad.float() - x2.grad).abs().max() < 0.05 * max(1.0, float(x2.grad.abs().max()))
+    assert (lin.weight.grad - w2.grad).abs().max() < 2e-3 * m ** 0.5 + 1e-2
+    assert (lin.bias.grad - b2.grad).abs().max() < 2e-3 * m ** 0.5 + 1e-2
