@@ -239,8 +239,9 @@ __global__ void __launch_bounds__(256) edge_attn_fwd_kernel(AttnArgs a) {
   const int off = hsafe * HN + (lt % LPH) * VN;
   int beg = 0, end = 0;
   if (head_ok) { beg = a.rowptr[row]; end = a.rowptr[row + 1]; }
-  const bool hub = (end - beg) > BF_HUB_DEGREE;
-  if (hub) end = beg;  // handled by the hub kernels
+  // long rows go to the hub kernels when the caller listed them; without a list they are walked here (slow, complete)
+  const bool hub = a.n_hub > 0 && (end - beg) > BF_HUB_DEGREE;
+  if (hub) end = beg;
   float qs0[VN], qs1[VN], acc[VN];
   float zsum = 0.f;
 #pragma unroll
@@ -270,11 +271,8 @@ __global__ void __launch_bounds__(256) edge_attn_fwd_hub_kernel(AttnArgs a, int 
   constexpr int LPH = HN / VN;
   const Geo g = make_geo<T, HN>(a.hl);
   const int hub_i = blockIdx.x / chunks_per_hub;
-  const int chunk = blockIdx.x % chunks_per_hub;
   const int row = a.hub_rows[hub_i];
   const int rbeg = a.rowptr[row], rend = a.rowptr[row + 1];
-  const int cbeg = rbeg + chunk * a.hub_chunk;
-  const int cend = min(rend, cbeg + a.hub_chunk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int tpw = 32 / g.tl;
   const int lt = lane % g.tl;
@@ -282,6 +280,11 @@ __global__ void __launch_bounds__(256) edge_attn_fwd_hub_kernel(AttnArgs a, int 
   const int streams = nwarp * tpw;
   const int stream = warp * tpw + sub_task;
   float* scratch = a.hub_scratch + (long long)hub_i * (a.hl * HN + a.hl);
+  // a block walks the row's chunks with stride chunks_per_hub: a row longer than the caller's bound costs parallelism,
+  // never edges
+  for (int chunk = blockIdx.x % chunks_per_hub; (long long)chunk * a.hub_chunk < rend - rbeg; chunk += chunks_per_hub) {
+  const int cbeg = rbeg + chunk * a.hub_chunk;
+  const int cend = min(rend, cbeg + a.hub_chunk);
   for (int hc = 0; hc < g.n_hc; ++hc) {
     const int head = hc * g.hpt + lt / LPH;
     const bool head_ok = head < a.hl;
@@ -301,6 +304,7 @@ __global__ void __launch_bounds__(256) edge_attn_fwd_hub_kernel(AttnArgs a, int 
       for (int i = 0; i < VN; ++i) atomicAdd(scratch + off + i, acc[i]);
       if ((lt % LPH) == 0) atomicAdd(scratch + a.hl * HN + head, zsum);
     }
+  }
   }
 }
 
@@ -490,7 +494,7 @@ __global__ void __launch_bounds__(256, EXPH ? 3 : 4) edge_attn_bwd_q_kernel(BwdA
   const int off = hsafe * HN + (lt % LPH) * VN;
   int beg = 0, end = 0;
   if (head_ok) { beg = a.rowptr[row]; end = a.rowptr[row + 1]; }
-  const bool hub = (end - beg) > BF_HUB_DEGREE;
+  const bool hub = a.n_hub > 0 && (end - beg) > BF_HUB_DEGREE;
   float qs0[VN], qs1[VN], qraw[VN], dof[VN], of[VN], dq[VN], de0[VN], de1[VN];
   load_q_scaled<T, HN>(a, row, hsafe, off, qs0, qs1);
   load_vec<T>(static_cast<const T*>(a.q) + (long long)row * a.ldq + off, qraw);
@@ -540,17 +544,17 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_q_hub_kernel(BwdArgs b, int
   const Geo g = make_geo<T, HN>(a.hl);
   const int w_row = a.hl * HN;
   const int hub_i = blockIdx.x / chunks_per_hub;
-  const int chunk = blockIdx.x % chunks_per_hub;
   const int row = a.hub_rows[hub_i];
   const int rbeg = a.rowptr[row], rend = a.rowptr[row + 1];
-  const int cbeg = rbeg + chunk * a.hub_chunk;
-  const int cend = min(rend, cbeg + a.hub_chunk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int tpw = 32 / g.tl;
   const int lt = lane % g.tl;
   const int streams = nwarp * tpw;
   const int stream = warp * tpw + lane / g.tl;
   float* scratch = b.hub_scratch_q + (long long)hub_i * w_row;
+  for (int chunk = blockIdx.x % chunks_per_hub; (long long)chunk * a.hub_chunk < rend - rbeg; chunk += chunks_per_hub) {
+  const int cbeg = rbeg + chunk * a.hub_chunk;
+  const int cend = min(rend, cbeg + a.hub_chunk);
   for (int hc = 0; hc < g.n_hc; ++hc) {
     const int head = hc * g.hpt + lt / LPH;
     const bool head_ok = head < a.hl;
@@ -582,6 +586,7 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_q_hub_kernel(BwdArgs b, int
         }
       }
     }
+  }
   }
 }
 
@@ -804,7 +809,7 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_kernel(BwdArgs b) {
   const int off = hsafe * HN + (lt % LPH) * VN;
   int beg = 0, end = 0;
   if (head_ok) { beg = b.t_rowptr[row]; end = b.t_rowptr[row + 1]; }
-  const bool hub = (end - beg) > BF_HUB_DEGREE;
+  const bool hub = b.n_t_hub > 0 && (end - beg) > BF_HUB_DEGREE;
   if (hub) end = beg;
   float kf[VN], vf[VN], dk[VN], dv[VN];
   load_vec<T>(static_cast<const T*>(a.k) + (long long)row * a.ldk + off, kf);
@@ -827,17 +832,17 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_hub_kernel(BwdArgs b, in
   const Geo g = make_geo<T, HN>(a.hl);
   const int w_row = a.hl * HN;
   const int hub_i = blockIdx.x / chunks_per_hub;
-  const int chunk = blockIdx.x % chunks_per_hub;
   const int row = b.t_hub_rows[hub_i];
   const int rbeg = b.t_rowptr[row], rend = b.t_rowptr[row + 1];
-  const int cbeg = rbeg + chunk * a.hub_chunk;
-  const int cend = min(rend, cbeg + a.hub_chunk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int tpw = 32 / g.tl;
   const int lt = lane % g.tl;
   const int streams = nwarp * tpw;
   const int stream = warp * tpw + lane / g.tl;
   float* scratch = b.hub_scratch_kv + (long long)hub_i * 2 * w_row;
+  for (int chunk = blockIdx.x % chunks_per_hub; (long long)chunk * a.hub_chunk < rend - rbeg; chunk += chunks_per_hub) {
+  const int cbeg = rbeg + chunk * a.hub_chunk;
+  const int cend = min(rend, cbeg + a.hub_chunk);
   for (int hc = 0; hc < g.n_hc; ++hc) {
     const int head = hc * g.hpt + lt / LPH;
     const bool head_ok = head < a.hl;
@@ -858,6 +863,7 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_hub_kernel(BwdArgs b, in
         atomicAdd(scratch + w_row + off + i, dv[i]);
       }
     }
+  }
   }
 }
 

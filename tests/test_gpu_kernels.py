@@ -193,3 +193,24 @@ def test_edge_attention_kernels_against_coo_oracle(variant):
     want = torch.autograd.grad(ref, (q, k, v), dout)
     for a, b, name in zip(got, want, "qkv"):
         assert torch.allclose(a, b, atol=5e-4, rtol=1e-3), (name, float((a - b).abs().max()))
+
+
+def test_edge_attention_with_understated_degree_bound():
+    """``max_degree`` is a hint from the graph builder.  A hint below the true maximum must not drop edges: rows longer
+    than the hint are either walked by the regular kernels (no hub list) or by hub blocks that stride over their chunks."""
+    from tests.helpers import random_attn_graph
+    torch.manual_seed(3)
+    n, hl, hn = 3000, 2, 16
+    g = random_attn_graph(n, 6000, hub_row=20000, hub_col=2500, seed=5).to("cuda")
+    q, k, v = (torch.randn(n, hl, hn, device="cuda") for _ in range(3))
+    ref = edge_attention_reference(q, k, v, g)
+    for wrong in (8, 1500):                     # below the hub threshold (no hub list at all) / above it but far too small
+        g.max_degree = wrong
+        qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+        out = edge_attention(qq, kk, vv, g)
+        assert torch.allclose(out, ref, atol=2e-4, rtol=2e-4), (wrong, float((out - ref).abs().max()))
+        out.sum().backward()
+        q2, k2, v2 = (t.clone().requires_grad_(True) for t in (q, k, v))
+        edge_attention_reference(q2, k2, v2, g).sum().backward()
+        for a, b in ((qq, q2), (kk, k2), (vv, v2)):
+            assert torch.allclose(a.grad, b.grad, atol=1e-3, rtol=1e-3), wrong
