@@ -303,4 +303,5 @@ if __name__ == "__main__":
     if ns.impl == "reference":
         run_reference(ns)
     else:
-        run_ours(ns)
+        from budgetformer_b200.utils.rank_main import run_rank_main
+        run_rank_main(run_ours, ns)

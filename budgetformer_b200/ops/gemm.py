@@ -153,7 +153,12 @@ class _FusedLinear(torch.autograd.Function):
         dy = dy.contiguous()
         g = hash_dropout(dy, seed, p) if p > 0 else dy
         # dx = g @ W, expressed as g @ (W^T)^T; skipped for leaf inputs such as the feature matrix
-        dx = gemm_tn(g, operand_copy(ctx.weight, x.dtype, transpose=True)) if ctx.needs_input_grad[0] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if supported(g.size(0), x.size(1), g.size(1), g.dtype):
+                dx = gemm_tn(g, operand_copy(ctx.weight, x.dtype, transpose=True))
+            else:                                      # output layers narrower than one 64-wide K panel
+                dx = torch.matmul(g, operand_copy(ctx.weight, x.dtype))
         dw, db = weight_grad(g, x, has_bias)
         return dx, dw.to(wdtype), (db.to(wdtype) if has_bias else None), (dy if has_res else None), None, None
 
@@ -174,7 +179,8 @@ def fused_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
 def readout_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ weight.T + bias`` for the small output layers (h -> classes).  The tcgen05 kernels want the output width
     to be a multiple of 16: a narrower layer is run with zero rows appended to the weight (and zeros to the bias) and
-    the extra columns are cut off again, so its forward, input gradient and weight gradient stay off the library GEMM.
+    the extra columns are cut off again, so its forward and weight gradient stay off the library GEMM; the input
+    gradient does too when the (padded) output is at least 64 wide, which is the kernels' smallest reduction depth.
     Inputs the kernels cannot take (fp32 activations, fewer than 64 input features) use ``torch.nn.functional.linear``."""
     n, k = weight.shape
     usable = (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and k >= 64 and k % 8 == 0

@@ -10,6 +10,7 @@ from budgetformer_b200.config import parse_fullgraph_args
 from budgetformer_b200.parallel.initialize import destroy_distributed
 from budgetformer_b200.train.engine import FullGraphTrainer
 from budgetformer_b200.train.report import print_git_version
+from budgetformer_b200.utils.rank_main import run_rank_main
 
 
 def main(argv=None):
@@ -21,15 +22,15 @@ def main(argv=None):
         best = trainer.fit()
     finally:
         trainer.edge_engine.shutdown()
-        destroy_distributed()
+    destroy_distributed()                        # collective: only after a run that every rank finished
     return best
 
 
 def cli() -> int:
     """Console-script entry point (the return value of ``main`` is a result dict, not an exit status)."""
-    main(sys.argv[1:])
+    run_rank_main(main, sys.argv[1:])
     return 0
 
 
 if __name__ == "__main__":
-    main(sys.argv[1:])
+    run_rank_main(main, sys.argv[1:])

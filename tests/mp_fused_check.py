@@ -176,4 +176,5 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    from budgetformer_b200.utils.rank_main import run_rank_main
+    run_rank_main(main)

@@ -353,7 +353,7 @@ def test_weight_gradient_gemm_on_strided_views():
     assert (db - dy.float().sum(0)).abs().max() < 0.2
 
 
-@pytest.mark.parametrize("n_out,k", [(5, 128), (40, 128), (47, 256), (64, 128), (5, 32)])
+@pytest.mark.parametrize("n_out,k", [(5, 128), (40, 128), (47, 256), (64, 128), (32, 64), (5, 32)])
 def test_readout_linear_pads_narrow_outputs(n_out, k):
     """Output layers narrower than the kernels' 16-column granule run with zero rows appended to the weight: forward and
     all three gradients equal the float32 reference; inputs with fewer than 64 features fall back to the library."""

@@ -15,7 +15,7 @@ def _run(nproc, models, port, env_extra=None):
     env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_fused_check.py"), models]
-    return subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
