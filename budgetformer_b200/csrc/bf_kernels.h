@@ -90,7 +90,16 @@ typedef struct {
   // stored at index (query - row_begin) of ell_col / ell_type / ell_cnt - one rank's shard of a build that the
   // sequence-parallel ranks split between them.  row_count == 0 builds all n queries.
   int row_begin, row_count;
+  // Optional list of the queries whose in-edge row is longer than BF_BUILD_HUB_DEGREE (ascending ids, n_hub of them) and
+  // scratch of 32 * n_hub 64-bit words: those rows are ranked by one thread block each before the row-per-lane-group
+  // kernel runs, which then reads the ranked list instead of streaming the row.  Same rows out either way; queries
+  // missing from the list are streamed as before.
+  const int* hub_rows;
+  int n_hub;
+  unsigned long long* hub_top;
 } bf_build_params;
+
+#define BF_BUILD_HUB_DEGREE 4096
 
 int bf_budget_select(const bf_build_params* p, cudaStream_t st);
 int bf_ell_to_csr(const int* ell_col, const uint8_t* ell_type, const int* rowptr, int n, int cap, int* col,

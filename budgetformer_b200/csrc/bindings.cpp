@@ -152,9 +152,23 @@ void edge_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor do
 }
 
 // Returns (rowptr int32 [n+1], col int32 [E], etype uint8 [E] or empty, totals int64 [2]).
+// The caller's list of long in-edge rows (ascending int32 ids on the topology's device) and the scratch their ranked
+// candidates go to; the returned tensor owns the scratch until the launch is queued (the caching allocator keeps it
+// valid for work already in the stream).
+Tensor attach_hub_rows(bf_build_params& p, const OptTensor& hub_rows, const Tensor& like) {
+  if (!hub_rows.has_value() || hub_rows->numel() == 0) return Tensor();
+  TORCH_CHECK(hub_rows->is_cuda() && hub_rows->scalar_type() == torch::kInt && hub_rows->is_contiguous() &&
+              hub_rows->device() == like.device(), "hub_rows: contiguous int32 on the topology's device");
+  Tensor top = torch::empty({hub_rows->numel() * 32}, like.options().dtype(torch::kLong));
+  p.hub_rows = hub_rows->data_ptr<int>();
+  p.n_hub = (int)hub_rows->numel();
+  p.hub_top = reinterpret_cast<unsigned long long*>(top.data_ptr<int64_t>());
+  return top;
+}
+
 std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col, int64_t n,
                                      int64_t b_real, int64_t b_rw, int64_t walks, int64_t walk_len, bool exphormer,
-                                     int64_t seed, int64_t num_threads) {
+                                     int64_t seed, int64_t num_threads, OptTensor hub_rows) {
   TORCH_CHECK(b_real >= 0 && b_rw >= 0 && b_real <= 32 && b_rw <= 32, "per-side budgets must be in [0, 32]");
   TORCH_CHECK(walk_len <= 16, "walk_length must be <= 16");
   for (const Tensor* t : {&in_rowptr, &in_src, &out_rowptr, &out_col})
@@ -175,6 +189,7 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
     p.ell_col = ell_col.data_ptr<int>(); p.ell_type = exphormer ? ell_type.data_ptr<uint8_t>() : nullptr;
     p.ell_cnt = ell_cnt.data_ptr<int>();
     p.totals = reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>());
+    Tensor hub_top = attach_hub_rows(p, hub_rows, in_src);
     check_cuda(bf_budget_select(&p, at::cuda::getCurrentCUDAStream()), "budget_select");
   } else {
     bf_budget_select_cpu(iptr(in_rowptr), iptr(in_src), iptr(out_rowptr), iptr(out_col), (int)n, (int)b_real,
@@ -207,7 +222,8 @@ std::vector<Tensor> build_attn_graph(Tensor in_rowptr, Tensor in_src, Tensor out
 // ell_cnt [row_count] int32, ell_type [row_count, cap] uint8 (typed rows only), totals [2] int64 (zeroed here).
 void budget_select_rows(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tensor out_col, int64_t n, int64_t b_real,
                         int64_t b_rw, int64_t walks, int64_t walk_len, bool exphormer, int64_t seed, int64_t row_begin,
-                        int64_t row_count, Tensor ell_col, Tensor ell_cnt, OptTensor ell_type, Tensor totals) {
+                        int64_t row_count, Tensor ell_col, Tensor ell_cnt, OptTensor ell_type, Tensor totals,
+                        OptTensor hub_rows) {
   TORCH_CHECK(b_real >= 0 && b_rw >= 0 && b_real <= 32 && b_rw <= 32, "per-side budgets must be in [0, 32]");
   TORCH_CHECK(walk_len <= 16, "walk_length must be <= 16");
   for (const Tensor* t : {&in_rowptr, &in_src, &out_rowptr, &out_col})
@@ -227,6 +243,7 @@ void budget_select_rows(Tensor in_rowptr, Tensor in_src, Tensor out_rowptr, Tens
   p.ell_cnt = ell_cnt.data_ptr<int>();
   p.totals = reinterpret_cast<unsigned long long*>(totals.data_ptr<int64_t>());
   p.row_begin = (int)row_begin; p.row_count = (int)row_count;
+  Tensor hub_top = attach_hub_rows(p, hub_rows, in_src);
   check_cuda(bf_budget_select(&p, at::cuda::getCurrentCUDAStream()), "budget_select_rows");
 }
 
@@ -678,6 +695,7 @@ bool gemm_supported(int64_t M, int64_t N, int64_t K) { return bf_gemm_supported(
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("edge_attn_fwd", &edge_attn_fwd);
   m.def("edge_attn_bwd", &edge_attn_bwd);
+  m.attr("BUILD_HUB_DEGREE") = (int64_t)BF_BUILD_HUB_DEGREE;
   m.def("build_attn_graph", &build_attn_graph);
   m.def("budget_select_rows", &budget_select_rows);
   m.def("ell_rows_to_csr", &ell_rows_to_csr);

@@ -59,7 +59,40 @@ struct BuildArgs {
   uint8_t* ell_type;   // [n, cap] or null
   int* ell_cnt;        // [n]
   unsigned long long* totals;  // [2] selected real / rw edges (with multiplicity)
+  const int* hub_rows;         // ascending ids of queries with more than BF_BUILD_HUB_DEGREE in-edges, or null
+  int n_hub;
+  unsigned long long* hub_top; // [n_hub, 32] ranked real candidates of those queries
 };
+
+// Real-edge ranking of the long rows: one block per listed query.  Each warp keeps the b_real smallest composites of
+// its share of the row (chunks of 32 edges, strided by the block), warp 0 merges the eight lists.  The b_real smallest
+// of a multiset do not depend on the order of insertion, so the result equals the single stream of the main kernel.
+__global__ void __launch_bounds__(256) budget_hub_topk_kernel(BuildArgs a) {
+  __shared__ uint64_t s_list[8][32];
+  const int row = a.hub_rows[blockIdx.x];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool mine = row >= a.row_begin && (long long)row < (long long)a.row_begin + a.n;   // uniform over the block
+  uint64_t list = kInf;
+  if (mine) {
+    const int beg = a.in_rowptr[row], end = a.in_rowptr[row + 1];
+    const int64_t rs = a.seed + BF_REAL_SEED_OFFSET;
+    for (long long base = (long long)beg + warp * 32; base < end; base += 256) {
+      const long long e = base + lane;
+      const bool valid = e < end;
+      const uint32_t s = valid ? (uint32_t)__ldg(a.in_src + e) : 0u;
+      group_insert<32>(list, a.b_real, valid, valid ? bf_edge_composite(s, (uint32_t)row, rs) : kInf, lane, 0xffffffffu, lane);
+    }
+  }
+  s_list[warp][lane] = list;
+  __syncthreads();
+  if (warp == 0 && mine) {
+    for (int w = 1; w < 8; ++w) {
+      const uint64_t c = s_list[w][lane];
+      group_insert<32>(list, a.b_real, c != kInf, c, lane, 0xffffffffu, lane);
+    }
+    a.hub_top[(long long)blockIdx.x * 32 + lane] = list;
+  }
+}
 
 template <int WIDTH>
 __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
@@ -79,11 +112,24 @@ __global__ void __launch_bounds__(256) budget_select_kernel(BuildArgs a) {
     if (a.b_real > 0) {
       const int beg = a.in_rowptr[v], end = a.in_rowptr[v + 1];
       const int64_t rs = a.seed + BF_REAL_SEED_OFFSET;
-      for (int base = beg; base < end; base += WIDTH) {
-        const int e = base + gl;
-        const bool valid = e < end;
-        const uint32_t s = valid ? (uint32_t)__ldg(a.in_src + e) : 0u;
-        group_insert<WIDTH>(rlist, a.b_real, valid, valid ? bf_edge_composite(s, q, rs) : kInf, gl, gm, lane);
+      int hub = -1;
+      if (a.n_hub > 0 && end - beg > BF_BUILD_HUB_DEGREE) {   // ranked by budget_hub_topk_kernel if the caller listed it
+        int lo = 0, hi = a.n_hub - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (a.hub_rows[mid] < (int)v) lo = mid + 1; else hi = mid;
+        }
+        if (a.hub_rows[lo] == (int)v) hub = lo;
+      }
+      if (hub >= 0) {
+        rlist = gl < a.b_real ? (uint64_t)a.hub_top[(long long)hub * 32 + gl] : kInf;
+      } else {
+        for (int base = beg; base < end; base += WIDTH) {
+          const int e = base + gl;
+          const bool valid = e < end;
+          const uint32_t s = valid ? (uint32_t)__ldg(a.in_src + e) : 0u;
+          group_insert<WIDTH>(rlist, a.b_real, valid, valid ? bf_edge_composite(s, q, rs) : kInf, gl, gm, lane);
+        }
       }
       r_cnt = min(end - beg, a.b_real);
     }
@@ -193,6 +239,9 @@ extern "C" int bf_budget_select(const bf_build_params* p, cudaStream_t st) {
   const bool narrow = p->b_real <= 8 && p->b_rw <= 8 && p->walks <= 8;
   const int width = narrow ? 8 : 32;
   const long long blocks = ((long long)a.n * width + 255) / 256;
+  const bool hubs = p->hub_rows != nullptr && p->hub_top != nullptr && p->n_hub > 0 && p->b_real > 0;
+  a.hub_rows = hubs ? p->hub_rows : nullptr; a.n_hub = hubs ? p->n_hub : 0; a.hub_top = hubs ? p->hub_top : nullptr;
+  if (blocks > 0 && hubs) budget_hub_topk_kernel<<<(unsigned)p->n_hub, 256, 0, st>>>(a);
   if (blocks > 0) {
     if (narrow) budget_select_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(a);
     else budget_select_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(a);

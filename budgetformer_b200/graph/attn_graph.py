@@ -55,6 +55,16 @@ class Topology:
     def nbytes(self) -> int:
         return sum(int(t.numel()) * t.element_size() for t in (self.out_rowptr, self.out_col, self.in_rowptr, self.in_src))
 
+    def in_hub_rows(self, min_degree: int) -> Optional[torch.Tensor]:
+        """Ascending int32 ids of the nodes with more than ``min_degree`` in-edges (``None`` when there are none).  The
+        topology does not change during a run, so the list is computed once per threshold and kept."""
+        cache = self.__dict__.setdefault("_hub_rows", {})
+        if min_degree not in cache:
+            deg = self.in_rowptr[1:] - self.in_rowptr[:-1]
+            rows = torch.nonzero(deg > int(min_degree)).flatten().to(torch.int32).contiguous()
+            cache[min_degree] = rows if rows.numel() > 0 else None
+        return cache[min_degree]
+
     @staticmethod
     def from_edge_index(edge_index: torch.Tensor, num_nodes: int) -> "Topology":
         """Build both CSRs from an int64 COO ``[2, E]`` (row 0 = source, row 1 = destination)."""

@@ -59,13 +59,24 @@ def build_attn_graph(
     ext = _ext.load()
     rowptr, col, etype, totals = ext.build_attn_graph(
         topo.in_rowptr, topo.in_src, topo.out_rowptr, topo.out_col, int(topo.num_nodes),
-        int(br), int(bw), int(walks_per_node), int(walk_length), bool(exphormer), int(seed), int(num_threads))
+        int(br), int(bw), int(walks_per_node), int(walk_length), bool(exphormer), int(seed), int(num_threads),
+        _long_rows(topo, ext))
     if topo.device.type == "cuda":
         _ext.count_launches(2)
     g = AttnGraph(int(topo.num_nodes), rowptr, col, etype if exphormer else None,
                   max_degree=int(br) + int(bw) + (1 if exphormer else 0))
     g._totals = totals  # device tensor; read lazily to avoid a sync on the hot path
     return g
+
+
+def _long_rows(topo: Topology, ext) -> Optional[torch.Tensor]:
+    """Queries whose in-edge row the device builder ranks with a whole thread block instead of one lane group (power-law
+    graphs have rows of 10^5 - 10^6 in-edges that would otherwise be the tail of the selection kernel).
+    ``BF_BUILD_HUB_BLOCKS=0`` switches the pre-pass off (measurements)."""
+    import os
+    if topo.device.type != "cuda" or os.environ.get("BF_BUILD_HUB_BLOCKS", "1") == "0":
+        return None
+    return topo.in_hub_rows(int(ext.BUILD_HUB_DEGREE))
 
 
 def _build_rows_native(topo: Topology, b_real: Optional[int], b_rw: Optional[int], walks_per_node: int, walk_length: int,
@@ -168,7 +179,7 @@ class ShardedDeviceBuild:
         totals = t[o_col + o_cnt + o_typ:o_col + o_cnt + o_typ + 16].view(torch.int64)
         ext.budget_select_rows(topo.in_rowptr, topo.in_src, topo.out_rowptr, topo.out_col, n, int(br), int(bw),
                                int(walks_per_node), int(walk_length), bool(exphormer), int(seed), sw.rank * rows, rows,
-                               ell_col, ell_cnt, ell_typ, totals)
+                               ell_col, ell_cnt, ell_typ, totals, _long_rows(topo, ext))
         sw.barrier(self.channel)                                  # every rank's shard is complete
         dev = t.device
         full_col = torch.empty(n * cap, dtype=torch.int32, device=dev)

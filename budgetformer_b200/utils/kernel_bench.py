@@ -128,15 +128,22 @@ def case_ln(a):
 def case_build(a):
     from ..graph.attn_graph import Topology
     from ..graph.builder import build_attn_graph
-    from ..graph.synthetic import citation_dag_edges
-    ei = citation_dag_edges(a.nodes, a.edges, seed=1)
-    topo = Topology.from_edge_index(ei, a.nodes).to("cuda")
+    from ..graph.synthetic import chung_lu_edges_device, citation_dag_edges
+    if a.graph == "dag":
+        ei = citation_dag_edges(a.nodes, a.edges, seed=1)
+    else:                                       # power-law graphs of the large configurations: in-degrees up to 10^5 - 10^6
+        ei = chung_lu_edges_device(a.nodes, a.edges, 2.1, a.graph == "chung_lu_directed", 1, torch.device("cuda"))
+    topo = Topology.from_edge_index(ei.to("cuda"), a.nodes)
+    indeg = topo.in_rowptr[1:] - topo.in_rowptr[:-1]
     seeds = iter(range(10 ** 6))
     fn = lambda: build_attn_graph(topo, a.b_real, a.b_rw, a.walks, a.walk_len, next(seeds))
     ms = timed(fn, a.warmup, 1 if a.once else a.iters)
     g = fn()
     report("budget_select+ell_to_csr", ms, topo.nbytes() + g.nbytes(), 0, {"nodes": a.nodes, "raw_edges": int(ei.size(1)),
-                                                                             "graph_edges": g.num_edges})
+                                                                             "graph_edges": g.num_edges,
+                                                                             "max_in_degree": int(indeg.max()),
+                                                                             "block_ranked_rows": int((indeg > 4096).sum()),
+                                                                             "block_prepass": os.environ.get("BF_BUILD_HUB_BLOCKS", "1") != "0"})
     ms = timed(lambda: build_attn_graph(topo, a.b_real, a.b_rw, a.walks, a.walk_len, 7).ensure_transpose(), a.warmup, a.iters)
     report("build+transpose+kv_tasks", ms, 0, 0, {"nodes": a.nodes})
 
@@ -274,6 +281,7 @@ def main(argv=None):
             p.add_argument("--b_rw", type=int, default=4)
             p.add_argument("--walks", type=int, default=2)
             p.add_argument("--walk_len", type=int, default=4)
+            p.add_argument("--graph", default="dag", choices=["dag", "chung_lu_directed", "chung_lu_undirected"])
     a = ap.parse_args(argv)
     {"gemm": case_gemm, "attn": case_attn, "ln": case_ln, "build": case_build, "sp": case_sp}[a.case](a)
 

@@ -2,6 +2,7 @@
 import pytest
 import torch
 
+from budgetformer_b200.graph.attn_graph import Topology
 from budgetformer_b200.graph.builder import build_attn_graph
 from budgetformer_b200.ops.edge_attention import edge_attention, edge_attention_reference
 from tests.helpers import random_attn_graph, random_topology
@@ -96,6 +97,49 @@ def test_gpu_builder_matches_cpu_builder(cfg, exph):
     if exph:
         assert torch.equal(cpu.etype, gpu.etype.cpu())
     assert cpu._totals.tolist() == gpu._totals.cpu().tolist()
+
+
+@pytest.mark.parametrize("exph", [False, True])
+@pytest.mark.parametrize("cfg", [(4, 4, 2, 4), (8, 8, 2, 4), (32, 16, 4, 6), (1, 0, 2, 4)])
+def test_gpu_builder_ranks_long_rows_with_a_block_per_row(cfg, exph, monkeypatch):
+    """Queries with more in-edges than the block threshold (one of 30,000 with many repeated sources, one just above
+    the threshold, one just below it) are ranked by a thread block each: same graph as the CPU builder, as the device
+    builder with the pre-pass switched off, and as a build of row ranges that cut between the long rows."""
+    from budgetformer_b200.ops import _ext
+    br, bw, w, l = cfg
+    thr = int(_ext.load().BUILD_HUB_DEGREE)
+    g = torch.Generator().manual_seed(5)
+    n = 3000
+    ei = torch.randint(0, n, (2, 20000), generator=g)
+    extra = [torch.stack([torch.randint(0, 500, (30000,), generator=g), torch.full((30000,), 0)]),
+             torch.stack([torch.randint(0, n, (thr + 1,), generator=g), torch.full((thr + 1,), 1700)]),
+             torch.stack([torch.randint(0, n, (thr - 30,), generator=g), torch.full((thr - 30,), 2999)])]
+    topo = Topology.from_edge_index(torch.cat([ei] + extra, 1), n)
+    dev = topo.to("cuda")
+    assert dev.in_hub_rows(thr).tolist() == [0, 1700]
+    cpu = build_attn_graph(topo, br, bw, w, l, 91, exphormer=exph)
+    gpu = build_attn_graph(dev, br, bw, w, l, 91, exphormer=exph)
+    assert torch.equal(cpu.rowptr, gpu.rowptr.cpu()) and torch.equal(cpu.col, gpu.col.cpu())
+    if exph:
+        assert torch.equal(cpu.etype, gpu.etype.cpu())
+    assert cpu._totals.tolist() == gpu._totals.cpu().tolist()
+    # row ranges (what one rank of a sharded build selects): [0, 1500) holds the first long row, [1500, 3000) the second
+    ext = _ext.load()
+    cap = max(br + bw + (1 if exph else 0), 1)
+    cols, cnts = [], []
+    for begin in (0, 1500):
+        ell_col = torch.empty(1500 * cap, dtype=torch.int32, device="cuda")
+        ell_cnt = torch.empty(1500, dtype=torch.int32, device="cuda")
+        ell_typ = torch.empty(1500 * cap, dtype=torch.uint8, device="cuda") if exph else None
+        totals = torch.zeros(2, dtype=torch.int64, device="cuda")
+        ext.budget_select_rows(dev.in_rowptr, dev.in_src, dev.out_rowptr, dev.out_col, n, br, bw, w, l, exph, 91, begin, 1500,
+                               ell_col, ell_cnt, ell_typ, totals, dev.in_hub_rows(thr))
+        cols.append(ell_col); cnts.append(ell_cnt)
+    rowptr, col, _ = ext.ell_rows_to_csr(torch.cat(cols), torch.cat(cnts), None, n, cap)
+    assert torch.equal(rowptr.cpu(), cpu.rowptr) and torch.equal(col.cpu(), cpu.col)
+    monkeypatch.setenv("BF_BUILD_HUB_BLOCKS", "0")
+    plain = build_attn_graph(dev, br, bw, w, l, 91, exphormer=exph)
+    assert torch.equal(plain.col, gpu.col) and torch.equal(plain.rowptr, gpu.rowptr)
 
 
 def test_gpu_builder_seed_changes_graph_and_is_reproducible():
