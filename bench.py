@@ -61,6 +61,12 @@ def parse():
     ap.add_argument("--fused_sp", default="auto")
     ap.add_argument("--ckpt", default="", help="activation checkpoint mode (default none = retain everything)")
     ap.add_argument("--no_e2e", action="store_true")
+    ap.add_argument("--fit_epochs", type=int, default=0,
+                    help="instead of the timed steps: run FullGraphTrainer.fit for this many epochs on the named configuration "
+                         "(adaptive budget search, planner and evaluation included), log on stderr, one JSON summary line")
+    ap.add_argument("--fit_flags", default="",
+                    help="extra command-line flags of the training driver for --fit_epochs, e.g. "
+                         "'--adaptive_edge_budget --max_total_edges_per_query 8 --activation_checkpoint_mode multi_tier'")
     ap.add_argument("--kernel_events", type=int, default=0,
                     help="after the timed loops run this many extra steps with CUDA events around every call into the "
                          "extension and print rank 0's per-kernel device times (a breakdown, not a benchmark value)")
@@ -125,20 +131,77 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def bench_args(cfg: dict, ns):
+def bench_args(cfg: dict, ns, extra=()):
     from budgetformer_b200.config import parse_fullgraph_args
 
     b = int(cfg["budget"])
     argv = ["--model", cfg["model"], "--dataset", ns.config, "--n_layers", str(cfg["n_layers"]),
             "--hidden_dim", str(cfg["hidden_dim"]), "--num_heads", str(cfg["num_heads"]), "--ffn_dim", str(2 * cfg["hidden_dim"]),
             "--amp_dtype", "bf16", "--walk_length", str(cfg["walk_length"]), "--walks_per_node", str(cfg["walks_per_node"]),
-            "--fixed_real_edges_per_query", str((b + 1) // 2), "--fixed_rw_edges_per_query", str(b // 2),
-            "--epochs", "100000", "--force_random_split", "--fused_sp", ns.fused_sp]
+            "--force_random_split", "--fused_sp", ns.fused_sp]
+    if "--adaptive_edge_budget" in extra:
+        argv += ["--max_total_edges_per_query", str(b)]
+    else:
+        argv += ["--fixed_real_edges_per_query", str((b + 1) // 2), "--fixed_rw_edges_per_query", str(b // 2)]
+    argv += ["--epochs", str(ns.fit_epochs) if ns.fit_epochs > 0 else "100000"]
     if cfg.get("multilabel"):
         argv.append("--multilabel")
     if ns.ckpt:
         argv += ["--activation_checkpoint_mode", ns.ckpt]
-    return parse_fullgraph_args(argv)
+    return parse_fullgraph_args(argv + list(extra))
+
+
+def _plan_record(planner):
+    if planner is None or not hasattr(planner, "modes"):
+        return None
+    return {"state": planner.state_name(), "active": bool(planner.is_active()), "tiers": list(planner.modes()),
+            "edge_policy": planner.edge_policy() if planner.is_active() else None}
+
+
+def run_fit(ns):
+    """The training loop a user runs (``FullGraphTrainer.fit``: budget search with its probe steps, execution planner,
+    evaluation) on a named configuration; the trainer's own log goes to stderr."""
+    import shlex
+
+    import torch
+
+    from budgetformer_b200.graph.synthetic import make_bench_graph
+    from budgetformer_b200.train.data import GraphData, random_split_idx
+    from budgetformer_b200.train.engine import FullGraphTrainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local_rank % torch.cuda.device_count())
+    x, y, ei, cfg = make_bench_graph(ns.config, seed=42, scale=ns.scale)
+    n = x.size(0)
+    data = GraphData(x, y, ei, random_split_idx(n, 42), n, int(cfg["classes"]), bool(cfg.get("multilabel")))
+    extra = shlex.split(ns.fit_flags)
+    log = (lambda *a, **k: print(*a, file=sys.stderr, flush=True)) if rank == 0 else (lambda *a, **k: None)
+    trainer = FullGraphTrainer(bench_args(cfg, ns, extra), data=data, log=log)
+    t0 = time.time()
+    best = trainer.fit()
+    if trainer.device.type == "cuda":
+        torch.cuda.synchronize(trainer.device)
+    wall = time.time() - t0
+    if rank == 0:
+        c = trainer.controller
+        times = list(trainer.epoch_times)
+        tail = times[len(times) // 2:] or times
+        rec = {"mode": "fit", "impl": "ours", "n_gpus": world, "epochs": ns.fit_epochs, "wall_s": wall,
+               "epoch_ms_median_second_half": 1e3 * sorted(tail)[len(tail) // 2] if tail else None,
+               "epoch_ms_first": [round(1e3 * t, 1) for t in times[:12]],
+               "budget": {"real": c.real_budget, "rw": c.rw_budget, "frozen": bool(c.frozen)},
+               "plan": _plan_record(getattr(trainer, "planner", None)),
+               "edge_policy": getattr(trainer.edge_engine, "policy", None),
+               "peak_hbm_mib": (torch.cuda.max_memory_allocated(trainer.device) / 2 ** 20 if trainer.device.type == "cuda" else 0.0),
+               "best": best, "fit_flags": ns.fit_flags,
+               "config": config_record(ns.config, cfg, n, int(ei.size(1)), int(x.size(1)), world, ns.ckpt, ns.scale)}
+        print(json.dumps(rec, default=str), flush=True)
+    if world > 1:
+        from budgetformer_b200.parallel.initialize import destroy_distributed
+        destroy_distributed()
 
 
 def run_ours(ns):
@@ -304,4 +367,4 @@ if __name__ == "__main__":
         run_reference(ns)
     else:
         from budgetformer_b200.utils.rank_main import run_rank_main
-        run_rank_main(run_ours, ns)
+        run_rank_main(run_fit if ns.fit_epochs > 0 else run_ours, ns)

@@ -33,7 +33,7 @@ def _data(kind: str, scale: float, seed: int):
             dict(hidden_dim=cfg["hidden_dim"], num_heads=cfg["num_heads"], n_layers=cfg["n_layers"]))
 
 
-def _run(kind: str, scale: float, seed: int, epochs: int, fused: bool, lr: float):
+def _run(kind: str, scale: float, seed: int, epochs: int, fused: bool, lr: float, device: str = "cuda:0"):
     from ..config import parse_fullgraph_args
     from ..train.engine import FullGraphTrainer
     data, shape = _data(kind, scale, seed)
@@ -41,10 +41,10 @@ def _run(kind: str, scale: float, seed: int, epochs: int, fused: bool, lr: float
             "--num_heads", str(shape["num_heads"]), "--ffn_dim", str(2 * shape["hidden_dim"]), "--amp_dtype", "bf16",
             "--fixed_real_edges_per_query", "4", "--fixed_rw_edges_per_query", "4", "--force_random_split",
             "--epochs", str(epochs), "--peak_lr", str(lr), "--warmup_updates", "10", "--seed", str(seed),
-            "--fused_sp", "on" if fused else "off", "--device", "cuda:0"]
+            "--fused_sp", "on" if fused else "off", "--device", device]
     torch.manual_seed(seed)
     t = FullGraphTrainer(parse_fullgraph_args(argv), data=data, log=lambda *a, **k: None)
-    assert bool(t.fused_sp) == fused
+    assert bool(t.fused_sp) == fused or not device.startswith("cuda")      # a CPU run has only the portable path
     keep = sorted({1, 2, 5, 10, 20, 50, 100, 150, 200, 250, epochs} & set(range(1, epochs + 1)))
     curve, best = {}, {"valid": -1.0, "test": -1.0, "epoch": 0}
     for epoch in range(1, epochs + 1):
@@ -66,10 +66,11 @@ def main(argv=None):
     ap.add_argument("--epochs", type=int, default=300)
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--lr", type=float, default=2e-3)
+    ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)
     rec = {"graph": a.graph, "scale": a.scale if a.graph == "patents" else 1.0, "epochs": a.epochs, "seed": a.seed,
-           "fused": _run(a.graph, a.scale, a.seed, a.epochs, True, a.lr),
-           "portable": _run(a.graph, a.scale, a.seed, a.epochs, False, a.lr)}
+           "fused": _run(a.graph, a.scale, a.seed, a.epochs, True, a.lr, a.device),
+           "portable": _run(a.graph, a.scale, a.seed, a.epochs, False, a.lr, a.device)}
     rec["best_valid_gap"] = round(rec["fused"]["best"]["valid"] - rec["portable"]["best"]["valid"], 4)
     print(json.dumps(rec), flush=True)
 

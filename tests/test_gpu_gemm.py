@@ -372,5 +372,7 @@ def test_readout_linear_pads_narrow_outputs(n_out, k):
     ref.backward(dy.float())
     assert (y.float() - ref).abs().max() < 0.05
     assert (x.grad.float() - x2.grad).abs().max() < 0.05 * max(1.0, float(x2.grad.abs().max()))
-    assert (lin.weight.grad - w2.grad).abs().max() < 2e-3 * m ** 0.5 + 1e-2
-    assert (lin.bias.grad - b2.grad).abs().max() < 2e-3 * m ** 0.5 + 1e-2
+    # the kernels leave fp32 gradients; the library fallback (k < 64) rounds them to bf16
+    wtol = 2e-3 * m ** 0.5 + 1e-2 if k >= 64 else 2 ** -7 * float(w2.grad.abs().max())
+    assert (lin.weight.grad - w2.grad).abs().max() < wtol
+    assert (lin.bias.grad - b2.grad).abs().max() < (2e-3 * m ** 0.5 + 1e-2 if k >= 64 else 2 ** -7 * float(b2.grad.abs().max()) + 1e-2)
