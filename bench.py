@@ -155,7 +155,7 @@ def _plan_record(planner):
     if planner is None or not hasattr(planner, "modes"):
         return None
     return {"state": planner.state_name(), "active": bool(planner.is_active()), "tiers": list(planner.modes()),
-            "edge_policy": planner.edge_policy() if planner.is_active() else None}
+            "edge_policy": planner.edge_policy if planner.is_active() else None}
 
 
 def run_fit(ns):

@@ -120,6 +120,7 @@ typedef struct {
   long long ldr;
   const void* relu_mask;            // [M, ldm] 16-bit: result zeroed where mask <= 0, or NULL
   long long ldm;
+  int mask_mode;                    // 0: as above (ReLU gradient); 1: result *= gelu'(mask), mask = the pre-activation
   // The same mask as one bit per element, 16 columns per uint16 word, stored column-block major ([N/16, ldmb >= M]
   // words, so that the 32 rows of a warp touch adjacent words; N % 16 == 0): written by a
   // forward GEMM (bit = result > 0 after activation and dropout), consumed by the backward GEMM instead of re-reading
@@ -220,6 +221,8 @@ int bf_layernorm_bwd(const void* dy, long long lddy, const void* x, long long ld
 int bf_colsum(const void* x, long long ldx, long long rows, int cols /* % 8 == 0 */, float* out /* += */, int dtype,
               cudaStream_t st);
 int bf_hash_dropout(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, uint32_t seed,
+                    float p, int dtype, cudaStream_t st);
+int bf_gelu_dropout(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, uint32_t seed,
                     float p, int dtype, cudaStream_t st);
 
 // BatchNorm building blocks (cols % 8 == 0, 16-byte aligned rows): shifted one-pass statistics, the backward

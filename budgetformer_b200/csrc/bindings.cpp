@@ -385,7 +385,7 @@ std::vector<Tensor> graph_transpose(Tensor rowptr, Tensor col, int64_t n, int64_
 // C = A * W^T with fused epilogue.  `dst_ptrs` holds one device pointer per destination (1 = plain output).
 void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, int64_t seed, OptTensor residual,
              OptTensor relu_mask, double out_scale, bool out_fp32, std::vector<int64_t> dst_ptrs, int64_t dst_row_offset,
-             int64_t ldc, Tensor status, OptTensor relu_bits_out, OptTensor relu_bits_in) {
+             int64_t ldc, Tensor status, OptTensor relu_bits_out, OptTensor relu_bits_in, int64_t mask_mode) {
   TORCH_CHECK(A.is_cuda() && W.is_cuda() && A.dim() == 2 && W.dim() == 2, "gemm_tn: A [M,K], W [N,K] on CUDA");
   TORCH_CHECK(A.scalar_type() == W.scalar_type() && (A.scalar_type() == torch::kBFloat16 || A.scalar_type() == torch::kHalf),
               "gemm_tn: bf16/fp16 operands");
@@ -423,6 +423,8 @@ void gemm_tn(Tensor A, Tensor W, OptTensor bias, int64_t act, double dropout_p, 
     TORCH_CHECK(relu_mask->scalar_type() == A.scalar_type() && relu_mask->stride(1) == 1 && relu_mask->size(0) == p.M &&
                 relu_mask->size(1) == p.N && (relu_mask->stride(0) * 2) % 16 == 0 && ((uintptr_t)relu_mask->data_ptr()) % 16 == 0);
     p.relu_mask = relu_mask->data_ptr(); p.ldm = relu_mask->stride(0);
+    TORCH_CHECK(mask_mode == 0 || mask_mode == 1, "gemm_tn: mask_mode 0 (ReLU gradient) or 1 (GELU gradient)");
+    p.mask_mode = (int)mask_mode;
   }
   p.out_scale = (float)out_scale; p.out_fp32 = out_fp32 ? 1 : 0;
   p.n_dest = (int)dst_ptrs.size(); p.dst_row_offset = dst_row_offset; p.ldc = ldc;
@@ -644,6 +646,16 @@ Tensor hash_dropout(Tensor x, int64_t seed, double p) {
   return y;
 }
 
+// dropout(gelu(x), p) in one pass (the FFN's GELU path); p = 0 gives plain GELU
+Tensor gelu_dropout(Tensor x, int64_t seed, double p) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && p >= 0.0 && p < 1.0);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty({x.size(0), x.size(1)}, x.options());
+  check_cuda(bf_gelu_dropout(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.size(0), (int)x.size(1),
+                             (uint32_t)seed, (float)p, dtype_code(x), at::cuda::getCurrentCUDAStream()), "gelu_dropout");
+  return y;
+}
+
 void grad_sumsq(Tensor g, Tensor out) {
   TORCH_CHECK(g.is_cuda() && g.scalar_type() == torch::kFloat && g.is_contiguous() && out.scalar_type() == torch::kFloat);
   c10::cuda::CUDAGuard guard(g.device());
@@ -712,6 +724,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("hash_dropout", &hash_dropout);
+  m.def("gelu_dropout", &gelu_dropout);
   m.def("bn_stats", &bn_stats);
   m.def("bn_bwd_reduce", &bn_bwd_reduce);
   m.def("col_affine", &col_affine);

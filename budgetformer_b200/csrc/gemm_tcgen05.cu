@@ -63,6 +63,7 @@ struct GemmArgs {
   long long ldr;
   const void* relu_mask;         // [M, ldm] 16-bit: out = mask > 0 ? acc : 0
   long long ldm;
+  int mask_mode;                 // 1: out = acc * gelu'(mask) instead (mask holds the pre-activation)
   unsigned short* bits_out;      // [N/16, ldmb >= M] one bit per element, word (c, r) = columns 16c..16c+15 of row r: bit = result > 0
   const unsigned short* bits_in; // same layout: out = bit ? acc : 0
   long long ldmb;
@@ -119,6 +120,10 @@ __device__ __forceinline__ bool keep_elem(uint32_t seed, uint32_t row, uint32_t 
 }
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+// d/dx of the above: Phi(x) + x * phi(x)
+__device__ __forceinline__ float gelu_erf_grad(float x) {
+  return 0.5f * (1.f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
 
 // the two 16-bit floats packed in one 32-bit word, widened
 __device__ __forceinline__ float lo16_as_float(uint32_t w, bool is_fp16) {
@@ -511,11 +516,23 @@ gemm_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           }
           const unsigned short* ms0 = reinterpret_cast<const unsigned short*>(&m0);
           const unsigned short* ms1 = reinterpret_cast<const unsigned short*>(&m1);
+          if (GEN && g.mask_mode == 1) {
+            // GELU backward: the mask operand is the pre-activation z, the result is scaled by gelu'(z)
+            const uint32_t z0[4] = {m0.x, m0.y, m0.z, m0.w}, z1[4] = {m1.x, m1.y, m1.z, m1.w};
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            // positive in either 16-bit float format: sign bit clear and magnitude non-zero
-            if (!((ms0[i] & 0x8000u) == 0 && (ms0[i] & 0x7FFFu) != 0)) v[i] = 0.f;
-            if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
+            for (int i = 0; i < 4; ++i) {
+              v[2 * i] *= gelu_erf_grad(lo16_as_float(z0[i], is_fp16));
+              v[2 * i + 1] *= gelu_erf_grad(hi16_as_float(z0[i], is_fp16));
+              v[8 + 2 * i] *= gelu_erf_grad(lo16_as_float(z1[i], is_fp16));
+              v[8 + 2 * i + 1] *= gelu_erf_grad(hi16_as_float(z1[i], is_fp16));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              // positive in either 16-bit float format: sign bit clear and magnitude non-zero
+              if (!((ms0[i] & 0x8000u) == 0 && (ms0[i] & 0x7FFFu) != 0)) v[i] = 0.f;
+              if (!((ms1[i] & 0x8000u) == 0 && (ms1[i] & 0x7FFFu) != 0)) v[8 + i] = 0.f;
+            }
           }
         }
         if (has_res && row_ok) {
@@ -650,6 +667,7 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
   g.is_fp16 = p->dtype == BF_FP16 ? 1 : 0;
   g.bias = p->bias; g.act = p->act; g.dropout_p = p->dropout_p; g.dropout_seed = p->dropout_seed;
   g.residual = p->residual; g.ldr = p->ldr; g.relu_mask = p->relu_mask; g.ldm = p->ldm;
+  g.mask_mode = (p->relu_mask != nullptr && p->mask_mode == 1) ? 1 : 0;
   g.bits_out = static_cast<unsigned short*>(p->relu_bits_out); g.bits_in = static_cast<const unsigned short*>(p->relu_bits_in);
   g.ldmb = p->ldmb;
   if ((g.bits_out || g.bits_in) && p->N % 16 != 0) return (int)cudaErrorInvalidValue;
@@ -731,6 +749,7 @@ extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {
     else if ((f | EPI_DROP) == (EPI_BIAS | EPI_RELU | EPI_DROP)) epi = EPI_BIAS | EPI_RELU | EPI_DROP;
     else if ((f | EPI_SCALE) == (EPI_MASK | EPI_SCALE)) epi = EPI_MASK | EPI_SCALE;
     else if (f == EPI_SCALE) epi = EPI_SCALE;
+    if (g.mask_mode == 1) epi = -1;                 // the GELU-gradient mask lives in the generic kernel only
   }
   using Kern = void (*)(const CUtensorMap, const CUtensorMap, const OutMaps, const CUtensorMap, const GemmArgs);
   Kern kern = gemm_tn_tcgen05_kernel<-1, false>;

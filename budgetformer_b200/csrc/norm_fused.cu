@@ -350,7 +350,10 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   return x ^ (x >> 16);
 }
 
-template <typename T>
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+// y = dropout(GELU ? gelu(x) : x): the keep mask is the GEMM epilogue's hash of (seed, row, column)
+template <typename T, bool GELU>
 __global__ void __launch_bounds__(256) hash_dropout_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ y,
                                                            long long ldy, long long rows, int cols, uint32_t seed,
                                                            uint32_t thresh, float scale) {
@@ -371,13 +374,15 @@ __global__ void __launch_bounds__(256) hash_dropout_kernel(const T* __restrict__
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const bool keep = mix32(rh + (uint32_t)(c0 + k) * 0x85EBCA77u) >= thresh;
-        tmp[k] = from_f<T>(keep ? to_f<T>(tmp[k]) * scale : 0.f);
+        const float val = GELU ? gelu_erf_f(to_f<T>(tmp[k])) : to_f<T>(tmp[k]);
+        tmp[k] = from_f<T>(keep ? val * scale : 0.f);
       }
       *reinterpret_cast<uint4*>(yp) = *reinterpret_cast<const uint4*>(tmp);
     } else {
       for (int k = 0; k < 8 && c0 + k < cols; ++k) {
         const bool keep = mix32(rh + (uint32_t)(c0 + k) * 0x85EBCA77u) >= thresh;
-        yp[k] = from_f<T>(keep ? to_f<T>(xp[k]) * scale : 0.f);
+        const float val = GELU ? gelu_erf_f(to_f<T>(xp[k])) : to_f<T>(xp[k]);
+        yp[k] = from_f<T>(keep ? val * scale : 0.f);
       }
     }
   }
@@ -637,7 +642,22 @@ extern "C" int bf_hash_dropout(const void* x, long long ldx, void* y, long long 
   const float scale = 1.f / (1.f - p);
   long long blocks = (rows * ((cols + 7) / 8) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-#define CALL(T) hash_dropout_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, (T*)y, ldy, rows, cols, seed, thresh, scale)
+#define CALL(T) hash_dropout_kernel<T, false><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, (T*)y, ldy, rows, cols, seed, thresh, scale)
+  BF_DT_SWITCH(dtype, CALL)
+#undef CALL
+  return (int)cudaGetLastError();
+}
+
+// y = dropout(gelu(x), p) in one pass (p = 0: plain GELU); same keep mask as bf_hash_dropout
+extern "C" int bf_gelu_dropout(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols,
+                               uint32_t seed, float p, int dtype, cudaStream_t st) {
+  if (rows * cols == 0) return 0;
+  if (p < 0.f || p >= 1.f) return (int)cudaErrorInvalidValue;
+  const uint32_t thresh = (uint32_t)(p * 4294967296.0);
+  const float scale = 1.f / (1.f - p);
+  long long blocks = (rows * ((cols + 7) / 8) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+#define CALL(T) hash_dropout_kernel<T, true><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, ldx, (T*)y, ldy, rows, cols, seed, thresh, scale)
   BF_DT_SWITCH(dtype, CALL)
 #undef CALL
   return (int)cudaGetLastError();

@@ -3,7 +3,7 @@
 Forward is two kernels (activation + dropout in the first epilogue, bias + dropout + residual in the
 second).  Backward for ReLU uses the mask epilogue: ``dh = (g W2) * [h > 0] / (1 - p1)`` comes out of
 the GEMM directly, so the hidden gradient is never touched by a separate elementwise pass.  GELU keeps
-the pre-activation and differentiates it with PyTorch.  Replaces Linear -> act -> Dropout -> Linear ->
+the pre-activation and the same GEMM's epilogue multiplies by ``gelu'(z)`` (``_FusedFFNGelu``).  Replaces Linear -> act -> Dropout -> Linear ->
 Dropout -> add of the reference layers (e.g. models/gt_dist_node_level.py:655-660)."""
 from __future__ import annotations
 
@@ -67,6 +67,50 @@ class _FusedFFNRelu(torch.autograd.Function):
         return dx, dw1, db1, dw2, db2, dres, None, None, None, None, None
 
 
+class _FusedFFNGelu(torch.autograd.Function):
+    """GELU form (Graphormer).  Forward: GEMM (bias) -> z, one pass ``h = dropout(gelu(z))``, GEMM (bias, dropout,
+    residual).  Backward: the hidden gradient ``dz = (g W2) * keep / (1 - p1) * gelu'(z)`` comes out of the GEMM's
+    epilogue (dropout mask regenerated from its seed, derivative evaluated on the saved pre-activation), so neither the
+    GELU derivative nor the dropout mask is a separate pass over the ``[rows, ffn]`` gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, residual, p1, p2, seed1, seed2, slot=None):
+        from .norm import gelu_dropout
+        w1h, w2h = gemm.operand_copy(w1, x.dtype), gemm.operand_copy(w2, x.dtype)
+        z = gemm.gemm_tn(x, w1h, b1)
+        h = gelu_dropout(z, seed1, p1)
+        y = gemm.gemm_tn(h, w2h, b2, None, dropout_p=p2, dropout_seed=seed2, residual=residual)
+        ctx.weights = (w1, w2)
+        ctx.save_for_backward(x, z, h)
+        res_is_x = residual is not None and residual.data_ptr() == x.data_ptr() and residual.shape == x.shape \
+            and residual.stride() == x.stride()
+        ctx.cfg = (float(p1), float(p2), int(seed1), int(seed2), residual is not None, w1.dtype,
+                   b1 is not None, b2 is not None, res_is_x)
+        ctx.slot = slot
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, z, h = ctx.saved_tensors
+        w1t = gemm.operand_copy(ctx.weights[0], x.dtype, transpose=True)
+        w2t = gemm.operand_copy(ctx.weights[1], x.dtype, transpose=True)
+        p1, p2, seed1, seed2, has_res, wdtype, has_b1, has_b2, res_is_x = ctx.cfg
+        handed = ctx.slot.take(dy) if ctx.slot is not None else None
+        dy = dy.contiguous()
+        g2 = hash_dropout(dy, seed2, p2) if p2 > 0 else dy
+        dz = gemm.gemm_tn(g2, w2t, dropout_p=p1, dropout_seed=seed1, gelu_grad_of=z)
+        dx = gemm.gemm_tn(dz, w1t, residual=dy if res_is_x else None) if ctx.needs_input_grad[0] else None
+        need_db2 = has_b2 and not (handed is not None and p2 == 0)
+        dw2, db2 = gemm.weight_grad(g2, h, need_db2)
+        dw1, db1 = gemm.weight_grad(dz, x, has_b1)
+        dw2, dw1 = dw2.to(wdtype), dw1.to(wdtype)
+        if has_b2:
+            db2 = (db2 if need_db2 else handed).to(wdtype)
+        db1 = db1.to(wdtype) if has_b1 else None
+        dres = dy if (has_res and not res_is_x) else None
+        return dx, dw1, db1, dw2, db2, dres, None, None, None, None, None
+
+
 def fused_ffn(x: torch.Tensor, w1, b1, w2, b2, *, act: str = "relu", residual: Optional[torch.Tensor] = None,
               p1: float = 0.0, p2: float = 0.0, training: bool = True, out_grad_colsum=None) -> torch.Tensor:
     """2-D ``x`` ``[rows, h]``; ``residual`` is added last (pass ``x`` for a residual FFN).  ``out_grad_colsum`` is an
@@ -80,12 +124,8 @@ def fused_ffn(x: torch.Tensor, w1, b1, w2, b2, *, act: str = "relu", residual: O
         return _FusedFFNRelu.apply(x, w1, b1, w2, b2, residual, p1, p2, new_seed() if p1 > 0 else 0,
                                    new_seed() if p2 > 0 else 0, out_grad_colsum)
     if ok and act == "gelu":
-        z = gemm.fused_linear(x, w1, b1)
-        hdn = F.gelu(z)
-        if p1 > 0:
-            hdn = hash_dropout(hdn, new_seed(), p1)
-        # second GEMM: bias, output dropout and the residual add all happen in its epilogue
-        return gemm.fused_linear(hdn, w2, b2, residual=residual, dropout_p=p2, dropout_seed=new_seed() if p2 > 0 else 0)
+        return _FusedFFNGelu.apply(x, w1, b1, w2, b2, residual, p1, p2, new_seed() if p1 > 0 else 0,
+                                   new_seed() if p2 > 0 else 0, out_grad_colsum)
     hdn = F.linear(x, w1.to(x.dtype), None if b1 is None else b1.to(x.dtype))
     hdn = F.relu(hdn) if act == "relu" else F.gelu(hdn)
     hdn = F.dropout(hdn, p1, training and p1 > 0)

@@ -149,7 +149,7 @@ def _push_gemm(x, w, bias, dst_ptrs, row0, ldc, dropout_p=0.0, seed=0):
         if bias.data_ptr() % 16:
             bias = bias.clone()
     ext.gemm_tn(x, w, bias, 0, float(dropout_p), int(seed), None, None,
-                1.0, False, dst_ptrs, int(row0), int(ldc), gemm.status_tensor(x.device), None, None)
+                1.0, False, dst_ptrs, int(row0), int(ldc), gemm.status_tensor(x.device), None, None, 0)
     _ext.count_launches(1)
 
 

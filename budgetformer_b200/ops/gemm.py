@@ -78,9 +78,14 @@ def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
             dropout_p: float = 0.0, dropout_seed: int = 0, residual: Optional[torch.Tensor] = None,
             relu_mask: Optional[torch.Tensor] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
             out_dtype: Optional[torch.dtype] = None, relu_bits_out: Optional[torch.Tensor] = None,
-            relu_bits_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+            relu_bits_in: Optional[torch.Tensor] = None, gelu_grad_of: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``act(dropout(a @ w.T * out_scale + bias)) [masked] + residual`` in one kernel.  ``relu_bits_out`` (int16
-    ``[N / 16, M]``) receives one bit per element (result > 0); ``relu_bits_in`` zeroes the result where its bit is clear."""
+    ``[N / 16, M]``) receives one bit per element (result > 0); ``relu_bits_in`` zeroes the result where its bit is clear;
+    ``gelu_grad_of`` (``[M, N]`` pre-activations) multiplies the result by ``gelu'(z)`` after the dropout mask - the
+    hidden gradient of a GELU feed-forward block straight out of the GEMM."""
+    if gelu_grad_of is not None:
+        assert relu_mask is None, "one mask operand per call"
+        relu_mask = gelu_grad_of
     ext = _ext.load()
     m, n = a.size(0), w.size(0)
     fp32_out = (out_dtype or (out.dtype if out is not None else a.dtype)) == torch.float32
@@ -94,7 +99,7 @@ def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
             bias = bias.clone()
     ext.gemm_tn(a, w, bias, ACT[act], float(dropout_p), int(dropout_seed),
                 residual, relu_mask, float(out_scale), bool(fp32_out), [out.data_ptr()], 0, out.stride(0),
-                status_tensor(a.device), relu_bits_out, relu_bits_in)
+                status_tensor(a.device), relu_bits_out, relu_bits_in, 1 if gelu_grad_of is not None else 0)
     _ext.count_launches(1)
     return out
 

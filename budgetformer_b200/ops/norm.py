@@ -92,6 +92,19 @@ def hash_dropout(x: torch.Tensor, seed: int, p: float) -> torch.Tensor:
     return torch.where(keep, x / (1.0 - p), torch.zeros_like(x))
 
 
+def gelu_dropout(x: torch.Tensor, seed: int, p: float) -> torch.Tensor:
+    """``dropout(gelu(x), p)`` in one pass over ``x`` with the hash keep mask of ``hash_dropout`` (no autograd: the caller
+    differentiates it, see ``ops.ffn._FusedFFNGelu``)."""
+    if x.is_cuda and x.dim() == 2 and x.stride(1) == 1:
+        _ext.count_launches(1)
+        return _ext.load().gelu_dropout(x, int(seed), float(p))
+    y = torch.nn.functional.gelu(x.float()).to(x.dtype)
+    if p <= 0.0:
+        return y
+    keep = hash_keep_mask(seed, x.size(0), x.size(1), p, x.device)
+    return torch.where(keep, y / (1.0 - p), torch.zeros_like(y))
+
+
 def new_seed() -> int:
     """31-bit seed from torch's CPU generator (reproducible under ``torch.manual_seed``, no device sync)."""
     return int(torch.randint(0, 2 ** 31 - 1, (1,)).item())

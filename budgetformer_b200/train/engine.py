@@ -431,6 +431,18 @@ class FullGraphTrainer:
                 if not self.planner.apply_oom_fallback(self.device, self.sp_group, self.sp_world):
                     raise RuntimeError("out of memory with every layer already recomputed") from err
             elif not self.planner.mark_current_calibration_infeasible(self.device):
+                # warm-up (every layer recomputed) does not fit.  What can still be given back is the memory of a GPU
+                # edge policy - the resident topology and the build's working set: GPU policies leave the planner's
+                # search, the graph build moves to the CPU with prefetch and the step is retried from the next epoch
+                # (the reference marks gpu_persist infeasible at this point too, main_node_fullgraph_sp.py:1431-1444)
+                if self.edge_engine.policy.startswith("gpu") and not self.edge_engine.policy_locked \
+                        and self.planner.report_runtime_edge_gpu_infeasible(self.device):
+                    self.edge_engine.set_policy("cpu_rank_local_prefetch")
+                    self._cleanup_after_oom()
+                    self.log("[multi_tier] out of memory during warm-up under a GPU edge policy: "
+                             "edge build moved to cpu_rank_local_prefetch, step dropped")
+                    self.consecutive_dropped += 1
+                    raise StepDropped() from err
                 raise RuntimeError("out of memory during warm-up with every layer recomputed") from err
             if bwd_started or attempt >= MAX_STEP_RETRIES:
                 self.consecutive_dropped += 1
@@ -559,7 +571,8 @@ class FullGraphTrainer:
         except StepDropped:
             out["dropped"], out["loss"] = 1.0, float("nan")
             comm.barrier(self.sp_group)
-        if self.planner is not None or getattr(self.model, "_comm_ckpt", None) is not None:
+        if not out["dropped"] and (self.planner is not None or getattr(self.model, "_comm_ckpt", None) is not None):
+            # a dropped step measured nothing the planner may use (its peak is the failed allocation's)
             self.model.comm_aware_notify_step_end(self.device, t_bwd=timers["bwd"], t_fwd=timers["fwd"])
         if self.device.type == "cuda":
             self._queue_device_status_read()

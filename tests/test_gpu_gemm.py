@@ -130,6 +130,61 @@ def test_fused_ffn_autograd():
     gemm.check_status("cuda")
 
 
+@pytest.mark.parametrize("p1,p2", [(0.0, 0.0), (0.2, 0.1)])
+def test_fused_gelu_ffn_autograd(p1, p2):
+    """GELU feed-forward block (Graphormer): one pass gelu + dropout forward, and a backward whose hidden gradient
+    (dropout mask regenerated, times gelu'(z)) comes out of the GEMM epilogue - against a float32 restatement with the
+    same masks, rounded to bf16 where the fused path stores bf16."""
+    from budgetformer_b200.ops.ffn import fused_ffn
+    from budgetformer_b200.ops import norm as bnorm
+    torch.manual_seed(5)
+    m, h = 2500, 128
+    x = torch.randn(m, h, device="cuda").bfloat16().requires_grad_(True)
+    l1, l2 = torch.nn.Linear(h, 2 * h).cuda(), torch.nn.Linear(2 * h, h).cuda()
+    torch.manual_seed(17)
+    y = fused_ffn(x, l1.weight, l1.bias, l2.weight, l2.bias, act="gelu", residual=x, p1=p1, p2=p2, training=True)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    gemm.check_status("cuda")
+    torch.manual_seed(17)
+    s1 = bnorm.new_seed() if p1 > 0 else 0
+    s2 = bnorm.new_seed() if p2 > 0 else 0
+    x2 = x.detach().float().requires_grad_(True)
+    w1 = l1.weight.detach().bfloat16().float().requires_grad_(True)
+    w2 = l2.weight.detach().bfloat16().float().requires_grad_(True)
+    b1, b2 = l1.bias.detach().clone().requires_grad_(True), l2.bias.detach().clone().requires_grad_(True)
+    z = x2 @ w1.t() + b1
+    z = z + (z.bfloat16().float() - z).detach()                     # the fused path stores z in bf16
+    hdn = torch.nn.functional.gelu(z)
+    if p1 > 0:
+        hdn = torch.where(gemm.hash_keep_mask(s1, m, 2 * h, p1, "cuda"), hdn / (1 - p1), torch.zeros(1, device="cuda"))
+    hdn = hdn + (hdn.bfloat16().float() - hdn).detach()
+    o = hdn @ w2.t() + b2
+    if p2 > 0:
+        o = torch.where(gemm.hash_keep_mask(s2, m, h, p2, "cuda"), o / (1 - p2), torch.zeros(1, device="cuda"))
+    o = o + x2
+    o.backward(dy.float())
+    _close(y.detach(), o.detach(), torch.bfloat16)
+    _close(x.grad, x2.grad, torch.bfloat16)
+    for got, want in ((l1.weight.grad, w1.grad), (l2.weight.grad, w2.grad), (l1.bias.grad, b1.grad), (l2.bias.grad, b2.grad)):
+        assert torch.allclose(got, want, atol=0.03 * float(want.abs().max()), rtol=5e-2)
+    # the one-pass kernel by itself, and the epilogue's derivative against autograd of the exact GELU
+    zz = (torch.randn(1001, 264, device="cuda") * 2).bfloat16()
+    got = bnorm.gelu_dropout(zz, 1234, 0.3).float()
+    want = torch.where(gemm.hash_keep_mask(1234, 1001, 264, 0.3, "cuda"), torch.nn.functional.gelu(zz.float()) / 0.7,
+                       torch.zeros(1, device="cuda"))
+    assert (got - want).abs().max() < 0.03 * max(1.0, float(want.abs().max()))
+    a = torch.randn(777, 128, device="cuda").bfloat16()
+    w = (torch.randn(256, 128, device="cuda") * 0.1).bfloat16()
+    pre = (torch.randn(777, 256, device="cuda") * 1.5).bfloat16()
+    got = gemm.gemm_tn(a, w, gelu_grad_of=pre).float()
+    pf = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(pf).sum().backward()
+    want = (a.float() @ w.float().t()) * pf.grad
+    assert (got - want).abs().max() < 0.03 * max(1.0, float(want.abs().max()))
+    gemm.check_status("cuda")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("h", [64, 128, 200, 512])
 def test_layernorm_kernel(dtype, h):
@@ -210,7 +265,7 @@ def test_gemm_routes_column_slices_to_destinations(n, n_dest, row0):
     total_rows = row0 + m + 64
     outs = [torch.full((total_rows, cpd), 7.0, device="cuda", dtype=torch.bfloat16) for _ in range(n_dest)]
     _ext.load().gemm_tn(x, w, bias, 0, 0.0, 0, None, None, 1.0, False, [o.data_ptr() for o in outs], row0, cpd,
-                        gemm.status_tensor("cuda"), None, None)
+                        gemm.status_tensor("cuda"), None, None, 0)
     gemm.check_status("cuda")
     ref = x.float() @ w.float().t() + bias
     for d, o in enumerate(outs):
@@ -231,7 +286,7 @@ def test_gemm_routes_slices_with_dropout_epilogue():
     w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
     outs = [torch.zeros(m, cpd, device="cuda", dtype=torch.bfloat16) for _ in range(n_dest)]
     _ext.load().gemm_tn(x, w, None, 0, p, seed, None, None, 1.0, False, [o.data_ptr() for o in outs], 0, cpd,
-                        gemm.status_tensor("cuda"), None, None)
+                        gemm.status_tensor("cuda"), None, None, 0)
     gemm.check_status("cuda")
     keep = gemm.hash_keep_mask(seed, m, n, p, "cuda")
     ref = torch.where(keep, (x.float() @ w.float().t()) / (1 - p), torch.zeros(1, device="cuda"))

@@ -201,3 +201,29 @@ def test_mini_batch_driver_with_locality_reordering(tmp_path):
                               "--epochs", "2", "--n_layers", "1", "--hidden_dim", "32", "--num_heads", "4", "--ffn_dim", "64",
                               "--device", "cpu", "--eval_every", "1", "--force_random_split", "--batch_reorder_parts", "4"])
     assert 0.0 <= best["valid"] <= 1.0 and best["epoch"] >= 1
+
+
+def test_warmup_oom_under_gpu_edge_policy_moves_the_build_to_the_cpu():
+    """Warm-up (every layer recomputed) runs out of memory while a GPU edge policy holds the topology and the build's
+    working set: GPU policies leave the planner's search, the build moves to cpu_rank_local_prefetch, the step is
+    dropped without feeding the planner, and training goes on.  A second failure under the CPU policy ends the run."""
+    from budgetformer_b200.control.multi_tier import EDGE_GPU_EPHEMERAL, EDGE_GPU_PERSIST, Phase, ScriptedMemoryProbe
+    logs = []
+    t = _trainer(["--model", "gt", "--epochs", "4", "--activation_checkpoint_mode", "multi_tier",
+                  "--fault_inject", "oom@fwd:1"] + FIXED, logs=logs)
+    t.planner.probe = ScriptedMemoryProbe(1 << 34, lambda modes: {"peak": 1 << 30, "live": 1 << 29})
+    t.edge_engine.policy = "gpu_persist"            # a CPU test machine: set past the device check of set_policy
+    assert t.planner.phase is Phase.WARMUP_RECOMPUTE
+    out = t.train_step(1)
+    assert out["dropped"] == 1.0 and out["loss"] != out["loss"]
+    assert t.edge_engine.policy == "cpu_rank_local_prefetch"
+    assert {EDGE_GPU_PERSIST, EDGE_GPU_EPHEMERAL} <= set(t.planner.excluded_policies)
+    assert t.planner.phase is Phase.WARMUP_RECOMPUTE and not t.planner._warmup       # the failed step fed nothing
+    assert any("edge build moved to cpu_rank_local_prefetch" in l for l in logs)
+    out = t.train_step(2)
+    assert out["dropped"] == 0.0 and out["loss"] == out["loss"]
+    u = _trainer(["--model", "gt", "--epochs", "4", "--activation_checkpoint_mode", "multi_tier",
+                  "--fault_inject", "oom@fwd:1"] + FIXED)
+    u.planner.probe = ScriptedMemoryProbe(1 << 34, lambda modes: {"peak": 1 << 30, "live": 1 << 29})
+    with pytest.raises(RuntimeError, match="warm-up with every layer recomputed"):
+        u.train_step(1)                               # already on the CPU policy: nothing left to give back
