@@ -4,6 +4,8 @@
     python -m budgetformer_b200.utils.kernel_bench attn --nodes 2923922 --heads 8 --head_dim 16 --degree 8
     python -m budgetformer_b200.utils.kernel_bench ln --rows 2923922 --hidden 128
     python -m budgetformer_b200.utils.kernel_bench build --nodes 2923922 --edges 13975788
+    python -m budgetformer_b200.utils.kernel_bench dw --m 2923922 --n 128 --k 128 --compare
+    python -m budgetformer_b200.utils.kernel_bench pull --m 800000 --n 128 --k 128 --sources 8
 
 Each case runs ``--warmup`` untimed and ``--iters`` timed launches bracketed by CUDA events on the launching
 stream, with operands larger than the 126 MB L2 (or ``--flush_l2``), and prints one JSON line: milliseconds,
@@ -71,6 +73,38 @@ def case_gemm(a):
         ms2 = timed(lambda: torch.nn.functional.linear(x, w, bias.bfloat16()), a.warmup, a.iters)
         report("cublas_linear", ms2, nbytes, 2.0 * a.m * a.n * a.k, {"m": a.m, "n": a.n, "k": a.k})
     gemm.check_status(dev)
+
+
+def case_dw(a):
+    """Weight-gradient GEMM dW = dY^T X (+ bias gradient) against the bytes of its two operands."""
+    from ..ops import gemm
+    dy = torch.randn(a.m, a.n, device="cuda").bfloat16()
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    fn = lambda: gemm.weight_grad(dy, x, want_bias=True)
+    ms = timed(fn, a.warmup, 1 if a.once else a.iters)
+    report("gemm_dw_tcgen05", ms, 2 * a.m * (a.n + a.k), 2.0 * a.m * a.n * a.k, {"m": a.m, "n": a.n, "k": a.k})
+    if a.compare:
+        ms2 = timed(lambda: (torch.matmul(dy.t(), x), dy.float().sum(0)), a.warmup, a.iters)
+        report("library matmul + column sum", ms2, 2 * a.m * (a.n + a.k), 2.0 * a.m * a.n * a.k, {"m": a.m, "n": a.n, "k": a.k})
+    gemm.check_status("cuda")
+
+
+def case_pull(a):
+    """Gathered-operand GEMM on one GPU: the sources are local buffers standing in for the peers' (same kernel, same
+    loader warps; the bytes cross HBM instead of NVLink), so the kernel's own counters can be read under a profiler."""
+    from ..ops import fused_sp, gemm
+    cps = a.k // a.sources
+    srcs = [torch.randn(a.m, cps, device="cuda").bfloat16() for _ in range(a.sources)]
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.05).bfloat16()
+    bias = torch.zeros(a.n, device="cuda")
+    res = torch.randn(a.m, a.n, device="cuda").bfloat16()
+    ptrs = [t.data_ptr() for t in srcs]
+    fn = lambda: fused_sp._pull_gemm(ptrs, 0, cps, cps, a.m, w, bias=bias, residual=res, keep_copy=bool(a.keep_copy))
+    ms = timed(fn, a.warmup, 1 if a.once else a.iters)
+    nbytes = 2 * (a.m * a.k * (2 if a.keep_copy else 1) + a.n * a.k + 2 * a.m * a.n)
+    report("gemm_tn_pull (local sources)", ms, nbytes, 2.0 * a.m * a.n * a.k,
+           {"m": a.m, "n": a.n, "k": a.k, "sources": a.sources, "keep_copy": bool(a.keep_copy)})
+    gemm.check_status("cuda")
 
 
 def _graph(nodes, degree, seed=0, key_window=0):
@@ -248,12 +282,19 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="case", required=True)
     common = dict(warmup=3, iters=10)
-    for name in ("gemm", "attn", "ln", "build", "sp"):
+    for name in ("gemm", "attn", "ln", "build", "sp", "dw", "pull"):
         p = sub.add_parser(name)
         p.add_argument("--warmup", type=int, default=common["warmup"])
         p.add_argument("--iters", type=int, default=common["iters"])
         p.add_argument("--once", action="store_true")
-        if name == "gemm":
+        if name in ("dw", "pull"):
+            p.add_argument("--m", type=int, default=1_000_000)
+            p.add_argument("--n", type=int, default=128)
+            p.add_argument("--k", type=int, default=128)
+            p.add_argument("--compare", action="store_true")
+            p.add_argument("--sources", type=int, default=8)
+            p.add_argument("--keep_copy", type=int, default=1)
+        elif name == "gemm":
             p.add_argument("--m", type=int, default=1_000_000)
             p.add_argument("--n", type=int, default=384)
             p.add_argument("--k", type=int, default=128)
@@ -283,7 +324,8 @@ def main(argv=None):
             p.add_argument("--walk_len", type=int, default=4)
             p.add_argument("--graph", default="dag", choices=["dag", "chung_lu_directed", "chung_lu_undirected"])
     a = ap.parse_args(argv)
-    {"gemm": case_gemm, "attn": case_attn, "ln": case_ln, "build": case_build, "sp": case_sp}[a.case](a)
+    {"gemm": case_gemm, "attn": case_attn, "ln": case_ln, "build": case_build, "sp": case_sp, "dw": case_dw,
+     "pull": case_pull}[a.case](a)
 
 
 if __name__ == "__main__":
