@@ -176,6 +176,9 @@ class Calibration:
     baseline: StepReading = StepReading()       # every layer recomputed
     keep: TierProbe = TierProbe()
     retain: TierProbe = TierProbe()
+    # device bytes of a resident topology that were alive while the baseline was measured (the warm-up runs under
+    # whatever edge policy is active then): taken out of the baseline before a policy's own residency is added
+    resident_in_baseline: int = 0
 
     def probe(self, tier: str) -> TierProbe:
         return self.keep if tier == T1_KEEP_MHA else self.retain
@@ -345,7 +348,8 @@ def search_plans(cal: Calibration, edge_costs: Sequence[EdgeCost], peak_limit: i
     """Fastest feasible (policy, layout).  Returns ``(best, best_without_resident_topology, report)``; ``report`` maps
     each policy to ``("ok", best ms)`` or ``("skip:<why>", None)``.
 
-    feasible:  max(build peak, baseline peak + resident topology + layout bytes) <= peak_limit
+    feasible:  max(build peak, baseline peak without the topology that was resident while it was measured
+                                + this policy's resident topology + layout bytes) <= peak_limit
     step time: model + serial build + the part of the overlapped build the model step does not hide
     order:     time, then more kept activations, then no resident topology, then less host memory, then lower build peak"""
     costs = tier_costs(cal)
@@ -354,6 +358,7 @@ def search_plans(cal: Calibration, edge_costs: Sequence[EdgeCost], peak_limit: i
     best = best_free = None
     best_key = best_free_key = None
     report: Dict[str, tuple] = {}
+    model_peak = max(0, cal.baseline.peak - cal.resident_in_baseline)
     for ec in edge_costs:
         if ec.policy in excluded:
             report[ec.policy] = ("skip:gpu_infeasible", None)
@@ -368,7 +373,7 @@ def search_plans(cal: Calibration, edge_costs: Sequence[EdgeCost], peak_limit: i
         fastest = float("inf")
         for build_peak, overlap, walks_gpu, host in variants:
             for lay, extra, (t_f, t_b) in layouts:
-                peak = max(int(build_peak), cal.baseline.peak + ec.resident_bytes + extra)
+                peak = max(int(build_peak), model_peak + ec.resident_bytes + extra)
                 if peak > peak_limit:
                     continue
                 t_model = t_f + t_b
@@ -430,6 +435,8 @@ class ExecutionPlanner:
         self._choice = PlanChoice(EDGE_GPU_EPHEMERAL, Layout(self.n_layers, 0, 0), False, float("inf"), 0.0, 0.0, 0)
         self._fallback = (EDGE_GPU_EPHEMERAL, [T0_RECOMPUTE] * self.n_layers)   # best plan without a resident topology
         self._topology_bytes, self._topology_h2d_s = 0, 0.0
+        # set by the trainer: names the edge policy the steps currently run under (None: unknown)
+        self.active_edge_policy_fn: Optional[Callable[[], str]] = None
 
     # ------------------------------------------------------------------ small helpers
     def _log(self, msg: str) -> None:
@@ -519,7 +526,9 @@ class ExecutionPlanner:
 
     def _close_warmup(self) -> None:
         base = warmup_baseline(self._warmup)
-        self.calibration = replace(self.calibration, baseline=base)
+        under = self.active_edge_policy_fn() if self.active_edge_policy_fn is not None else None
+        resident = self.edge_costs[under].resident_bytes if under in self.edge_costs else 0
+        self.calibration = replace(self.calibration, baseline=base, resident_in_baseline=int(resident))
         self.phase = Phase.CALIBRATE_MHA
         self._log(f"warm-up done: peak={base.peak / 2**20:.0f} MiB t_fwd={base.t_fwd * 1e3:.1f} ms "
                   f"t_bwd={base.t_bwd * 1e3:.1f} ms")
@@ -531,7 +540,11 @@ class ExecutionPlanner:
                                                self.probe.cpu_available(), tuple(self.excluded_policies))
         self.last_plan_log = report
         if best is None:
-            best = PlanChoice(EDGE_GPU_EPHEMERAL, Layout(self.n_layers, 0, 0), False, float("inf"), 0.0, 0.0, 0)
+            # nothing fits the model's estimate: every layer recomputed under the cheapest policy still in the search
+            left = [p for p in (EDGE_GPU_EPHEMERAL, EDGE_CPU_RANK_LOCAL_PREFETCH, EDGE_CPU_BROADCAST_PREFETCH, EDGE_GPU_PERSIST)
+                    if p not in self.excluded_policies]
+            best = PlanChoice(left[0] if left else EDGE_CPU_RANK_LOCAL_PREFETCH, Layout(self.n_layers, 0, 0), False,
+                              float("inf"), 0.0, 0.0, 0)
         self._choice = best
         self._fallback = (best_free.policy, best_free.layout.tiers()) if best_free is not None else \
             (EDGE_GPU_EPHEMERAL, [T0_RECOMPUTE] * self.n_layers)

@@ -152,6 +152,8 @@ class FullGraphTrainer:
         budget_moving = self.budget_cfg.enabled and not self.controller.frozen
         self.model.set_activation_checkpoint(ckpt_mode is not None, ckpt_mode, deferred=budget_moving)
         self.planner = self.model._comm_ckpt if ckpt_mode == "multi_tier" else None
+        if self.planner is not None:
+            self.planner.active_edge_policy_fn = lambda: self.edge_engine.policy
         self._configure_fused_sp()
         if self.planner is not None and self.sp_world > 1 and self.device.type == "cuda":
             from ..parallel import symm

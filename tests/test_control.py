@@ -521,6 +521,45 @@ def test_plan_search_ordering_table():
     assert best.walks_on_gpu and best.t_edge == 0.0
 
 
+def test_plan_search_takes_the_warmup_policys_topology_out_of_the_baseline():
+    """The warm-up ran under gpu_persist, so its peak holds the resident topology: a policy without one gets that memory
+    back, gpu_persist is charged it once (not twice), and under a limit between the two the CPU-offloaded build wins."""
+    from dataclasses import replace
+    from budgetformer_b200.control.multi_tier import EdgeCost, search_plans
+    cal = replace(_cal(), resident_in_baseline=200 * MIB)            # baseline peak 1000 MiB, of which 200 MiB topology
+    big = 10 ** 15
+    persist = EdgeCost("gpu_persist", serial_s=0.001, resident_bytes=200 * MIB, build_peak=300 * MIB)
+    cpu = EdgeCost("cpu_rank_local_prefetch", overlap_s=0.001, build_peak=100 * MIB, host_bytes=MIB)
+    # 950 MiB: the model alone (800) fits, the model with the topology (1000) does not
+    best, _, rep = search_plans(cal, [persist, cpu], 950 * MIB, big)
+    assert rep["gpu_persist"] == ("skip:no_feasible_tier", None) and best.policy == "cpu_rank_local_prefetch"
+    assert best.peak <= 950 * MIB and best.layout.n_keep + best.layout.n_retain >= 1      # 150 MiB left for activations
+    # 1000 MiB: gpu_persist fits exactly as measured (800 + 200), with every layer recomputed
+    best, _, rep = search_plans(cal, [persist], 1000 * MIB, big)
+    assert rep["gpu_persist"][0] == "ok" and best.peak == 1000 * MIB and best.layout.n_recompute == 4
+    # without the correction the same limit would have ruled it out (1000 + 200)
+    best, _, rep = search_plans(_cal(), [persist], 1000 * MIB, big)
+    assert best is None and rep["gpu_persist"] == ("skip:no_feasible_tier", None)
+
+
+def test_planner_falls_back_inside_the_policies_left_in_the_search():
+    planner = ExecutionPlanner(2, probe=ScriptedMemoryProbe(1000 * MIB, lambda modes: {"peak": 990 * MIB, "live": 10 * MIB}),
+                               verbose=False)
+    planner.set_edge_policy_profile(EDGE_GPU_PERSIST, 0.01, 100 * MIB, 0, live_edge_bytes=50 * MIB)
+    planner.set_edge_policy_profile(EDGE_CPU_RANK_LOCAL_PREFETCH, 0.2, 10 * MIB, MIB, serial_time_s=0.0, overlap_time_s=0.2)
+    planner.active_edge_policy_fn = lambda: EDGE_GPU_PERSIST
+    dev = "cpu"
+    for _ in range(8):
+        if planner.is_active():
+            break
+        planner.plan(dev)
+        planner.record_post_forward_memory(dev)
+        planner.notify_step_end(dev, t_bwd=0.02, t_fwd=0.01)
+    assert planner.is_active() and planner.calibration.resident_in_baseline == 50 * MIB
+    planner.report_runtime_edge_gpu_infeasible(dev)                  # nothing fits 900 MiB: the fallback must not name a GPU policy
+    assert planner.edge_policy == EDGE_CPU_RANK_LOCAL_PREFETCH and planner.modes() == ["recompute", "recompute"]
+
+
 def test_demotion_table():
     from budgetformer_b200.control.multi_tier import demoted
     assert demoted(["retain", "retain"]) == ["keep_mha", "retain"]
