@@ -48,6 +48,7 @@ class SymmWorld:
         # one counter per channel: a channel is driven by one host thread and sees the same sequence on every rank
         self._epochs = [0] * FLAG_CHANNELS
         self.use_multimem = os.environ.get("BF_DISABLE_MULTIMEM", "0") != "1"
+        self._live = []                    # weak references to every buffer handed out (multicast_bound walks them)
         self.flags = self.alloc((FLAG_CHANNELS * MAX_PEERS,), torch.int32, zero=True)
         if self.world > 1:
             # every rank must have zeroed its flag page before anyone raises a flag in it
@@ -69,11 +70,22 @@ class SymmWorld:
                 t.zero_()
             hdl = symm_mem.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
             ptrs = [int(p) for p in hdl.buffer_ptrs]
-            mc = int(hdl.multicast_ptr) if (self.use_multimem and getattr(hdl, "has_multicast_support", False)
-                                            and hdl.multicast_ptr) else 0
+            mc = int(hdl.multicast_ptr) if (self.use_multimem and hdl.multicast_ptr) else 0
             buf = SymmBuffer(t.view(*shape), ptrs, mc, hdl)
         self.bytes_allocated += buf.nbytes()
+        import weakref
+        self._live.append(weakref.ref(buf))
         return buf
+
+    def multicast_bound(self) -> bool:
+        """Is any live allocation of this world bound to an NVSwitch multicast object (whether or not the kernels use
+        it)?  A rank must not leave the job while one is: ``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` before the first
+        allocation keeps them unbound."""
+        for ref in self._live:
+            buf = ref()
+            if buf is not None and buf.handle is not None and int(getattr(buf.handle, "multicast_ptr", 0) or 0) != 0:
+                return True
+        return False
 
     def barrier(self, channel: int = 0) -> None:
         """Device-side barrier over all ranks on the current stream (no host synchronisation)."""

@@ -209,6 +209,7 @@ class FullGraphTrainer:
     def _depart(self) -> None:
         """Orderly departure of this rank between steps: let every kernel it has queued finish first (its peers' kernels
         of the same step wait for flags that only those kernels raise), then tell the others through the store."""
+        self.edge_engine.shutdown()                  # the look-ahead worker has queued all of its build (or never will)
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         self.watchdog.leave("injected exit")

@@ -87,7 +87,7 @@ def check_watchdog_departure():
     assert t.fused_sp and not sw.use_multimem
     # a rank may only leave when no allocation of the job is bound to an NVSwitch multicast object: verify it on every
     # rank before anything departs; if a binding is still there, nobody leaves and the parent skips the test
-    bound = torch.tensor([1.0 if bool(getattr(sw.flags.handle, "has_multicast_support", False)) else 0.0], device=t.device)
+    bound = torch.tensor([1.0 if sw.multicast_bound() else 0.0], device=t.device)
     dist.all_reduce(bound, op=dist.ReduceOp.MAX)
     if float(bound) > 0:
         print("WATCHDOG " + json.dumps({"outcome": "multicast_bound"}), flush=True)
