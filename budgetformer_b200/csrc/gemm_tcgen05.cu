@@ -623,8 +623,10 @@ int pick_block_n(int n, int cap) {
 }  // namespace
 
 extern "C" int bf_gemm_supported(int M, int N, int K) {
-  // K only has to keep rows 16-byte aligned: the tensor maps zero-fill the tail of the last 64-element panel
-  return (M > 0 && K >= BLOCK_K && K % 8 == 0 && N >= 16 && pick_block_n(N, 256) > 0) ? 1 : 0;
+  // K only has to keep rows 16-byte aligned: the tensor maps zero-fill the tail of the last 64-element panel, and a
+  // matrix narrower than one panel (K = 16 or 32: the small output layers and their input gradients) is a single
+  // panel that is mostly zero-fill
+  return (M > 0 && K >= 16 && K % 8 == 0 && N >= 16 && pick_block_n(N, 256) > 0) ? 1 : 0;
 }
 
 extern "C" int bf_gemm_tn(const bf_gemm_params* p, cudaStream_t st) {

@@ -71,7 +71,7 @@ def check_status(device) -> None:
 
 
 def supported(m: int, n: int, k: int, dtype) -> bool:
-    return dtype in (torch.bfloat16, torch.float16) and m > 0 and k % 8 == 0 and k >= 64 and n % 16 == 0 and n >= 16
+    return dtype in (torch.bfloat16, torch.float16) and m > 0 and k % 8 == 0 and k >= 16 and n % 16 == 0 and n >= 16
 
 
 def gemm_tn(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
@@ -162,7 +162,7 @@ class _FusedLinear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             if supported(g.size(0), x.size(1), g.size(1), g.dtype):
                 dx = gemm_tn(g, operand_copy(ctx.weight, x.dtype, transpose=True))
-            else:                                      # output layers narrower than one 64-wide K panel
+            else:                                      # fewer than 16 outputs (never through readout_linear, which pads)
                 dx = torch.matmul(g, operand_copy(ctx.weight, x.dtype))
         dw, db = weight_grad(g, x, has_bias)
         return dx, dw.to(wdtype), (db.to(wdtype) if has_bias else None), (dy if has_res else None), None, None
@@ -184,11 +184,11 @@ def fused_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
 def readout_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ weight.T + bias`` for the small output layers (h -> classes).  The tcgen05 kernels want the output width
     to be a multiple of 16: a narrower layer is run with zero rows appended to the weight (and zeros to the bias) and
-    the extra columns are cut off again, so its forward and weight gradient stay off the library GEMM; the input
-    gradient does too when the (padded) output is at least 64 wide, which is the kernels' smallest reduction depth.
-    Inputs the kernels cannot take (fp32 activations, fewer than 64 input features) use ``torch.nn.functional.linear``."""
+    the extra columns are cut off again, so its forward, input gradient and weight gradient stay off the library GEMM
+    (the kernels reduce over as few as 16 features: a narrower operand is one mostly zero-filled 64-wide panel).
+    Inputs the kernels cannot take (fp32 activations, fewer than 16 input features) use ``torch.nn.functional.linear``."""
     n, k = weight.shape
-    usable = (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and k >= 64 and k % 8 == 0
+    usable = (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and k >= 16 and k % 8 == 0
               and x.stride(1) == 1 and (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0)
     if not usable:
         return torch.nn.functional.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))

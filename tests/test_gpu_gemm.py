@@ -35,7 +35,8 @@ def _close(got, want, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (1000, 384, 128), (333, 256, 256), (4096, 768, 256),
-                                   (129, 64, 64), (70000, 128, 256), (257, 192, 512), (64, 16, 64), (5000, 48, 128)])
+                                   (129, 64, 64), (70000, 128, 256), (257, 192, 512), (64, 16, 64), (5000, 48, 128),
+                                   (3000, 64, 32), (3000, 32, 16), (777, 128, 40)])
 def test_gemm_plain(m, n, k, dtype):
     torch.manual_seed(0)
     a = torch.randn(m, k, device="cuda").to(dtype)
@@ -369,11 +370,11 @@ def test_gemm_pulls_operand_column_slices_from_sources(n_src, cps, n, row0, copy
     (5000, 384, 128, True),      # packed q|k|v projection: three 128-feature tiles of dY
     (3333, 128, 128, True),      # output projection, ragged row count
     (4097, 256, 128, True),      # first FFN layer
-    (2500, 128, 256, False),     # second FFN layer: 256 features of X leave no accumulator column for the bias
-    (1111, 128, 272, True),      # feature encoder: two column chunks of X (256 + 16), bias rides with the second
+    (2500, 128, 256, True),      # second FFN layer: two 128-feature chunks of X side by side, bias with the second
+    (1111, 128, 272, True),      # feature encoder: three column chunks of X (128 + 128 + 16), bias rides with the last
     (777, 64, 128, True),        # readout: fewer than 128 features of dY (the tile's upper half is zero-filled)
     (50, 32, 64, True),          # fewer rows than one ring stage
-    (200000, 128, 192, True),    # many row slices; 192 features of X is the widest chunk that still carries the bias
+    (200000, 128, 192, True),    # many row slices; chunks of 128 + 64 features
 ])
 def test_weight_gradient_gemm_matches_fp32_reference(m, n, k, bias):
     """dW = dY^T X (+ column sums of dY) on the MN-major tcgen05 kernel against a float32 matmul of the same bf16
@@ -408,10 +409,11 @@ def test_weight_gradient_gemm_on_strided_views():
     assert (db - dy.float().sum(0)).abs().max() < 0.2
 
 
-@pytest.mark.parametrize("n_out,k", [(5, 128), (40, 128), (47, 256), (64, 128), (32, 64), (5, 32)])
+@pytest.mark.parametrize("n_out,k", [(5, 128), (40, 128), (47, 256), (64, 128), (32, 64), (5, 32), (7, 16), (5, 8)])
 def test_readout_linear_pads_narrow_outputs(n_out, k):
     """Output layers narrower than the kernels' 16-column granule run with zero rows appended to the weight: forward and
-    all three gradients equal the float32 reference; inputs with fewer than 64 features fall back to the library."""
+    all three gradients equal the float32 reference, down to 16 input features (one mostly zero-filled operand panel);
+    inputs with fewer than 16 features fall back to the library."""
     torch.manual_seed(13)
     m = 2000
     x = torch.randn(m, k, device="cuda").bfloat16().requires_grad_(True)
@@ -427,7 +429,7 @@ def test_readout_linear_pads_narrow_outputs(n_out, k):
     ref.backward(dy.float())
     assert (y.float() - ref).abs().max() < 0.05
     assert (x.grad.float() - x2.grad).abs().max() < 0.05 * max(1.0, float(x2.grad.abs().max()))
-    # the kernels leave fp32 gradients; the library fallback (k < 64) rounds them to bf16
-    wtol = 2e-3 * m ** 0.5 + 1e-2 if k >= 64 else 2 ** -7 * float(w2.grad.abs().max())
+    # the kernels leave fp32 gradients; the library fallback (k < 16) rounds them to bf16
+    wtol = 2e-3 * m ** 0.5 + 1e-2 if k >= 16 else 2 ** -7 * float(w2.grad.abs().max())
     assert (lin.weight.grad - w2.grad).abs().max() < wtol
-    assert (lin.bias.grad - b2.grad).abs().max() < (2e-3 * m ** 0.5 + 1e-2 if k >= 64 else 2 ** -7 * float(b2.grad.abs().max()) + 1e-2)
+    assert (lin.bias.grad - b2.grad).abs().max() < (2e-3 * m ** 0.5 + 1e-2 if k >= 16 else 2 ** -7 * float(b2.grad.abs().max()) + 1e-2)
