@@ -45,6 +45,17 @@ typedef struct {
   int out_col0;                     // column offset of this rank's head slice in the owner's row
 } bf_attn_params;
 
+// Result rows delivered to the rank that owns the node (sequence parallelism: the heads->nodes all-to-all done by the
+// stores of the attention kernels).  Destination d = row / rows_per holds one slab of rows_per rows per source rank:
+// row lands at base[d] + ((slab_row0 + row - d * rows_per) * ld + column) elements.  n_dest == 0: off.
+typedef struct {
+  void* base[BF_MAX_PEERS];         // 16-byte aligned buffer base per destination (peer mappings)
+  int n_dest;                       // n_dest * rows_per must equal the row count of the call
+  int rows_per;
+  long long ld;                     // destination row stride in elements, a multiple of 8
+  long long slab_row0;              // this (source) rank's slab: source index * rows_per
+} bf_attn_route;
+
 typedef struct {
   const void* dout;                 // [n, hl, hn] contiguous
   void *dq, *dk, *dv;               // [n, hl, hn], common row stride ldg (elements; 0 = hl*hn)
@@ -67,9 +78,15 @@ typedef struct {
   // those instead of q, dout and zd separately.
   void* qg;                         // [n, hl, 2, hn] in the operand dtype, or NULL
   float* cz;                        // [n, hl] fp32, or NULL
+  // Optional: dq / dk / dv rows go to the owner of each row (route.n_dest > 0) at column offsets route_cq / _ck / _cv
+  // (multiples of 8) of the destination's row, instead of into dq / dk / dv
+  bf_attn_route route;
+  int route_cq, route_ck, route_cv;
 } bf_attn_bwd_params;
 
 int bf_edge_attn_fwd(const bf_attn_params* p, cudaStream_t st);
+// as above; additionally every output row is stored into its owner's buffer (route may be NULL)
+int bf_edge_attn_fwd_routed(const bf_attn_params* p, const bf_attn_route* route, cudaStream_t st);
 int bf_edge_attn_bwd(const bf_attn_params* p, const bf_attn_bwd_params* q, cudaStream_t st);
 
 // ---- attention-graph construction (edge_build.cu) -------------------------------------------

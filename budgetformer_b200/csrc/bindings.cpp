@@ -83,9 +83,21 @@ void fill_common(bf_attn_params& p, const Tensor& q, const Tensor& k, const Tens
   TORCH_CHECK(variant != 2 || (p.etype && p.etab), "exphormer variant needs edge types and a type table");
 }
 
+// route = {} or {rows per destination, first row of this rank's slab, destination row stride (elements),
+// base pointer of destination 0, 1, ...}: see bf_attn_route
+bf_attn_route parse_route(const std::vector<int64_t>& route, size_t header) {
+  bf_attn_route r{};
+  if (route.empty()) return r;
+  TORCH_CHECK(route.size() > header && route.size() - header <= BF_MAX_PEERS, "route: header + 1..", BF_MAX_PEERS, " destinations");
+  r.rows_per = (int)route[0]; r.slab_row0 = route[1]; r.ld = route[2];
+  r.n_dest = (int)(route.size() - header);
+  for (int i = 0; i < r.n_dest; ++i) r.base[i] = reinterpret_cast<void*>(route[header + i]);
+  return r;
+}
+
 void edge_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor rowptr, Tensor col, OptTensor etype,
                    OptTensor etab, int64_t variant, double dropout_p, int64_t seed, int64_t known_max_degree,
-                   std::vector<double> out_drop) {
+                   std::vector<double> out_drop, std::vector<int64_t> route) {
   c10::cuda::CUDAGuard guard(q.device());
   bf_attn_params p{};
   fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed, out_drop);
@@ -96,14 +108,15 @@ void edge_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor ro
     p.hub_rows = iptr(hub.rows); p.n_hub = hub.n; p.max_hub_degree = hub.max_deg;
     p.hub_scratch = scratch.data_ptr<float>();
   }
-  check_cuda(bf_edge_attn_fwd(&p, at::cuda::getCurrentCUDAStream()), "edge_attn_fwd");
+  const bf_attn_route r = parse_route(route, 3);
+  check_cuda(bf_edge_attn_fwd_routed(&p, &r, at::cuda::getCurrentCUDAStream()), "edge_attn_fwd");
 }
 
 void edge_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor dout, Tensor dq, Tensor dk, Tensor dv,
                    Tensor zd, Tensor rowptr, Tensor col, OptTensor etype, Tensor t_rowptr, Tensor t_row, Tensor t_eid,
                    OptTensor etab, OptTensor detab, int64_t variant, double dropout_p, int64_t seed,
                    int64_t known_max_degree, OptTensor kv_task, OptTensor kv_split, int64_t kv_slots,
-                   std::vector<double> out_drop) {
+                   std::vector<double> out_drop, std::vector<int64_t> route) {
   c10::cuda::CUDAGuard guard(q.device());
   bf_attn_params p{};
   fill_common(p, q, k, v, out, z, rowptr, col, etype, etab, variant, dropout_p, seed, out_drop);
@@ -147,6 +160,12 @@ void edge_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor z, Tensor do
     skv = torch::zeros({thub.n, 2 * w}, q.options().dtype(torch::kFloat));
     b.t_hub_rows = iptr(thub.rows); b.n_t_hub = thub.n; b.max_t_hub_degree = thub.max_deg;
     b.hub_scratch_kv = skv.data_ptr<float>();
+  }
+  if (!route.empty()) {
+    // {rows per destination, slab row, row stride, column of dq, of dk, of dv, destination pointers...}
+    TORCH_CHECK(route.size() > 6, "route: six header fields + destinations");
+    b.route = parse_route(route, 6);
+    b.route_cq = (int)route[3]; b.route_ck = (int)route[4]; b.route_cv = (int)route[5];
   }
   check_cuda(bf_edge_attn_bwd(&p, &b, at::cuda::getCurrentCUDAStream()), "edge_attn_bwd");
 }

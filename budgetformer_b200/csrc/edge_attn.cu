@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "bf_kernels.h"
 
@@ -135,6 +136,25 @@ template <int LPH> __device__ __forceinline__ float head_sum(float x, unsigned m
   return x;
 }
 
+// Routed rows: the result row of query / key `row` belongs to the rank that owns that node (row / rows_per) and is
+// stored straight into that rank's buffer - the heads->nodes all-to-all of sequence parallelism done by the stores of
+// the kernel that produces the rows.  Every destination holds one slab of `rows_per` rows per source rank
+// ([n_dest * rows_per, ld] elements); `slab_row0` = this rank's slab.  n_dest == 0: off.
+struct Route {
+  unsigned long long base[BF_MAX_PEERS];   // buffer base address on every destination (peer mappings)
+  int n_dest;
+  int rows_per;
+  long long ld;                            // row stride of the destination buffers (elements)
+  long long slab_row0;                     // source rank * rows_per
+};
+
+template <typename T>
+__device__ __forceinline__ T* routed(const Route& r, long long row, int col) {
+  const int d = (int)(row / r.rows_per);
+  const long long lr = row - (long long)d * r.rows_per + r.slab_row0;
+  return reinterpret_cast<T*>(r.base[d]) + lr * r.ld + col;
+}
+
 struct AttnArgs {
   const void *q, *k, *v;       // [n, Hl, HN] with row strides ldq/ldk/ldv (elements)
   long long ldq, ldk, ldv;
@@ -156,6 +176,7 @@ struct AttnArgs {
   uint32_t out_thresh, out_seed;
   float out_inv_keep, out_keep;
   int out_rows_local, out_col0;
+  Route route_out;             // second copy of every output row, delivered to the row's owner (n_dest == 0: none)
 };
 
 // keep decision of ops.gemm.hash_keep_mask / bf_hash_dropout for element (row, col)
@@ -260,6 +281,7 @@ __global__ void __launch_bounds__(256) edge_attn_fwd_kernel(AttnArgs a) {
       for (int i = 0; i < VN; ++i) o[i] = keep_out(a, row, off + i) ? o[i] * a.out_inv_keep : 0.f;
     }
     store_vec<T>(static_cast<T*>(a.out) + (long long)row * a.hl * HN + off, o);
+    if (a.route_out.n_dest) store_vec<T>(routed<T>(a.route_out, row, off), o);
     if ((lt % LPH) == 0) a.z[(long long)row * a.hl + head] = zsum;
   }
 }
@@ -322,6 +344,7 @@ __global__ void edge_attn_fwd_hub_finalize(AttnArgs a) {
     float ov = scratch[c] * inv;
     if (a.out_thresh) ov = keep_out(a, row, c) ? ov * a.out_inv_keep : 0.f;
     static_cast<T*>(a.out)[(long long)row * w + c] = from_float<T>(ov);
+    if (a.route_out.n_dest) *routed<T>(a.route_out, row, c) = from_float<T>(ov);
     if ((c % HN) == 0) a.z[(long long)row * a.hl + head] = zs;
   }
 }
@@ -352,7 +375,18 @@ struct BwdArgs {
   // three separate short rows (q, dout, (1/Z, D)), which matters when a row of q is only 32 or 64 bytes.
   void* qg;                    // [n, Hl, 2, HN] in the operand dtype, or null
   float* cz;                   // [n, Hl]
+  // Routed gradients (route.n_dest > 0): dq / dk / dv rows go to the owner of the row instead of the local buffers, at
+  // column offsets cq / ck / cv of the destination's packed row
+  Route route;
+  int cq, ck, cv;
 };
+
+// first element of gradient row `row`: in the local buffer, or in the row owner's slab when the gradients are routed
+template <typename T>
+__device__ __forceinline__ T* grad_row(const BwdArgs& b, void* local, int col0, long long row) {
+  if (b.route.n_dest == 0) return static_cast<T*>(local) + row * b.ldg;
+  return routed<T>(b.route, row, col0);
+}
 
 // One edge of the dQ pass for one task lane.
 template <typename T, int HN>
@@ -521,7 +555,7 @@ __global__ void __launch_bounds__(256, EXPH ? 3 : 4) edge_attn_bwd_q_kernel(BwdA
   if (hub) end = beg;
   for (int e = beg; e < end; e += 2)
     dq_edge4<T, HN, EXPH, 2>(b, e, end, hsafe, off, qs0, qs1, qraw, dof, invz, dterm, dq, de0, de1, hm);
-  if (head_ok && !hub) store_vec<T>(static_cast<T*>(b.dq) + (long long)row * b.ldg + off, dq);
+  if (head_ok && !hub) store_vec<T>(grad_row<T>(b, b.dq, b.cq, row) + off, dq);
   if (EXPH) {
     if (head_ok) {
 #pragma unroll
@@ -729,8 +763,8 @@ __global__ void __launch_bounds__(256, MINB) edge_attn_bwd_kv_task_kernel(BwdArg
   const unsigned hm = head_mask<LPH>();
   for (int e = beg; e < end; e += 2) dkv_edge4<T, HN, EXPH, 2, PACKED>(b, e, end, head, off, kf, vf, dk, dv, hm);
   if (slot < 0) {
-    store_vec<T>(static_cast<T*>(b.dk) + (long long)row * b.ldg + off, dk);
-    store_vec<T>(static_cast<T*>(b.dv) + (long long)row * b.ldg + off, dv);
+    store_vec<T>(grad_row<T>(b, b.dk, b.ck, row) + off, dk);
+    store_vec<T>(grad_row<T>(b, b.dv, b.cv, row) + off, dv);
   } else {
     float* pp = b.kv_partial + (long long)slot * 2 * w_row;
 #pragma unroll
@@ -780,8 +814,8 @@ __global__ void __launch_bounds__(KV_REDUCE_THREADS) edge_attn_bwd_kv_reduce_ker
       }
     }
     if (act && grp == 0) {
-      T* dst = c < w_row ? static_cast<T*>(b.dk) : static_cast<T*>(b.dv);
-      dst[(long long)row * b.ldg + (c < w_row ? c : c - w_row)] = from_float<T>(acc);
+      T* dst = c < w_row ? grad_row<T>(b, b.dk, b.ck, row) : grad_row<T>(b, b.dv, b.cv, row);
+      dst[c < w_row ? c : c - w_row] = from_float<T>(acc);
     }
     if (G > 1) __syncthreads();
   }
@@ -819,8 +853,8 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_kernel(BwdArgs b) {
   const unsigned hm = head_mask<LPH>();
   for (int e = beg; e < end; ++e) dkv_edge<T, HN>(b, e, hsafe, off, kf, vf, dk, dv, hm);
   if (head_ok && !hub) {
-    store_vec<T>(static_cast<T*>(b.dk) + (long long)row * b.ldg + off, dk);
-    store_vec<T>(static_cast<T*>(b.dv) + (long long)row * b.ldg + off, dv);
+    store_vec<T>(grad_row<T>(b, b.dk, b.ck, row) + off, dk);
+    store_vec<T>(grad_row<T>(b, b.dv, b.cv, row) + off, dv);
   }
 }
 
@@ -868,12 +902,13 @@ __global__ void __launch_bounds__(256) edge_attn_bwd_kv_hub_kernel(BwdArgs b, in
 }
 
 template <typename T>
-__global__ void hub_scatter_rows(const float* scratch, int scratch_ld, int scratch_off, const int* rows, T* dst,
-                                 int width, long long ld_dst) {
+__global__ void hub_scatter_rows(const float* scratch, int scratch_ld, int scratch_off, const int* rows, BwdArgs b, void* local,
+                                 int col0, int width) {
   const int hub_i = blockIdx.x;
   const int row = rows[hub_i];
+  T* dst = grad_row<T>(b, local, col0, row);
   for (int c = threadIdx.x; c < width; c += blockDim.x)
-    dst[(long long)row * ld_dst + c] = from_float<T>(scratch[(long long)hub_i * scratch_ld + scratch_off + c]);
+    dst[c] = from_float<T>(scratch[(long long)hub_i * scratch_ld + scratch_off + c]);
 }
 
 template <typename T, int HN>
@@ -907,7 +942,7 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
   }
   if (a.n_hub > 0) {
     edge_attn_bwd_q_hub_kernel<T, HN><<<a.n_hub * chunks_q, 256, 0, st>>>(b, chunks_q);
-    hub_scatter_rows<T><<<a.n_hub, 256, 0, st>>>(b.hub_scratch_q, w_row, 0, a.hub_rows, static_cast<T*>(b.dq), w_row, b.ldg);
+    hub_scatter_rows<T><<<a.n_hub, 256, 0, st>>>(b.hub_scratch_q, w_row, 0, a.hub_rows, b, b.dq, b.cq, w_row);
   }
   if (b.kv_task) {
     const long long kv_tasks = (long long)b.n_kv_task * g.n_hc;
@@ -932,8 +967,8 @@ cudaError_t launch_bwd_t(const BwdArgs& b, int chunks_q, int chunks_kv, cudaStre
   if (blocks > 0) edge_attn_bwd_kv_kernel<T, HN><<<(unsigned)blocks, 256, 0, st>>>(b);
   if (b.n_t_hub > 0) {
     edge_attn_bwd_kv_hub_kernel<T, HN><<<b.n_t_hub * chunks_kv, 256, 0, st>>>(b, chunks_kv);
-    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, 0, b.t_hub_rows, static_cast<T*>(b.dk), w_row, b.ldg);
-    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, w_row, b.t_hub_rows, static_cast<T*>(b.dv), w_row, b.ldg);
+    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, 0, b.t_hub_rows, b, b.dk, b.ck, w_row);
+    hub_scatter_rows<T><<<b.n_t_hub, 256, 0, st>>>(b.hub_scratch_kv, 2 * w_row, w_row, b.t_hub_rows, b, b.dv, b.cv, w_row);
   }
   return cudaGetLastError();
 }
@@ -952,7 +987,23 @@ AttnArgs to_args(const bf_attn_params& p) {
   a.out_inv_keep = p.out_dropout_p > 0.f ? 1.f / (1.f - p.out_dropout_p) : 1.f;
   a.out_rows_local = p.out_rows_local; a.out_col0 = p.out_col0;
   a.hub_rows = p.hub_rows; a.n_hub = p.n_hub; a.hub_chunk = BF_HUB_CHUNK; a.hub_scratch = p.hub_scratch;
+  memset(&a.route_out, 0, sizeof(a.route_out));
   return a;
+}
+
+// Validated copy of a caller's route for `n` rows of `width` elements each; false = reject the call.
+bool to_route(const bf_attn_route* r, int n, long long width, Route* out) {
+  memset(out, 0, sizeof(*out));
+  if (r == nullptr || r->n_dest <= 0) return true;
+  if (r->n_dest > BF_MAX_PEERS || r->rows_per <= 0 || (long long)r->rows_per * r->n_dest != n || r->ld < width || r->ld % 8 != 0 ||
+      r->slab_row0 < 0 || r->slab_row0 + r->rows_per > (long long)r->rows_per * r->n_dest)
+    return false;
+  for (int i = 0; i < r->n_dest; ++i) {
+    if (r->base[i] == nullptr || ((uintptr_t)r->base[i]) % 16 != 0) return false;
+    out->base[i] = (unsigned long long)(uintptr_t)r->base[i];
+  }
+  out->n_dest = r->n_dest; out->rows_per = r->rows_per; out->ld = r->ld; out->slab_row0 = r->slab_row0;
+  return true;
 }
 
 }  // namespace
@@ -973,6 +1024,16 @@ AttnArgs to_args(const bf_attn_params& p) {
       if (HN == 128) return CALL(float, 128);                                               \
     }                                                                                       \
   } while (0)
+
+extern "C" int bf_edge_attn_fwd_routed(const bf_attn_params* p, const bf_attn_route* route, cudaStream_t st) {
+  AttnArgs a = to_args(*p);
+  if (!to_route(route, p->n, (long long)p->hl * p->hn, &a.route_out)) return (int)cudaErrorInvalidValue;
+  const int chunks = p->max_hub_degree > 0 ? (p->max_hub_degree + BF_HUB_CHUNK - 1) / BF_HUB_CHUNK : 1;
+#define CALL_FWD(T, H) (int)launch_fwd_t<T, H>(a, chunks, st)
+  BF_DISPATCH(p->dtype, p->hn, CALL_FWD);
+#undef CALL_FWD
+  return (int)cudaErrorInvalidValue;
+}
 
 extern "C" int bf_edge_attn_fwd(const bf_attn_params* p, cudaStream_t st) {
   AttnArgs a = to_args(*p);
@@ -997,6 +1058,15 @@ extern "C" int bf_edge_attn_bwd(const bf_attn_params* p, const bf_attn_bwd_param
   // the packed records serve the work-list form of the dK/dV pass only
   b.qg = (q->kv_task != nullptr && q->qg != nullptr && q->cz != nullptr) ? q->qg : nullptr;
   b.cz = b.qg ? q->cz : nullptr;
+  b.cq = q->route_cq; b.ck = q->route_ck; b.cv = q->route_cv;
+  {
+    // a routed row is [.. ck: dk .. cv: dv .. cq: dq ..]: every part must fit the destination's row stride
+    const long long w = (long long)p->hl * p->hn;
+    const long long hi = (long long)(b.cq > b.ck ? (b.cq > b.cv ? b.cq : b.cv) : (b.ck > b.cv ? b.ck : b.cv)) + w;
+    if (!to_route(&q->route, p->n, q->route.n_dest > 0 ? hi : w, &b.route)) return (int)cudaErrorInvalidValue;
+    if (b.route.n_dest > 0 && (b.cq < 0 || b.ck < 0 || b.cv < 0 || ((b.cq | b.ck | b.cv) % 8) != 0))
+      return (int)cudaErrorInvalidValue;
+  }
   const int cq = p->max_hub_degree > 0 ? (p->max_hub_degree + BF_HUB_CHUNK - 1) / BF_HUB_CHUNK : 1;
   const int ckv = q->max_t_hub_degree > 0 ? (q->max_t_hub_degree + BF_HUB_CHUNK - 1) / BF_HUB_CHUNK : 1;
 #define CALL_BWD(T, H) (int)launch_bwd_t<T, H>(b, cq, ckv, st)

@@ -99,7 +99,7 @@ class _EdgeAttentionCUDA(torch.autograd.Function):
         z = torch.empty((n, hl), dtype=torch.float32, device=q.device)
         kmax = -1 if graph.max_degree is None else int(graph.max_degree)
         ext.edge_attn_fwd(q, k, v, out, z, graph.rowptr, graph.col, graph.etype,
-                          etable, int(variant_id), float(dropout_p), int(dropout_seed), kmax, [])
+                          etable, int(variant_id), float(dropout_p), int(dropout_seed), kmax, [], [])
         _ext.count_launches(1)
         ctx.save_for_backward(q, k, v, out, z, etable if etable is not None else q.new_empty(0))
         ctx.graph = graph
@@ -124,7 +124,7 @@ class _EdgeAttentionCUDA(torch.autograd.Function):
                           graph.rowptr, graph.col, graph.etype,
                           graph.t_rowptr, graph.t_row, graph.t_eid,
                           etable if has_tab else None, detab,
-                          variant_id, dropout_p, dropout_seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots), [])
+                          variant_id, dropout_p, dropout_seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots), [], [])
         _ext.count_launches(3)
         return dq, dk, dv, (detab.to(etable.dtype) if has_tab else None), None, None, None, None
 

@@ -9,19 +9,25 @@ copies), the edge attention, a fourth all-to-all and the output projection
                 rank's packed ``[N, 3*h/P]`` buffer over NVLink — the nodes->heads all-to-all *is* the epilogue;
 ``attention``   the edge-attention kernels read q|k|v from that packed buffer and write the context into a
                 second symmetric buffer;
-``ctx pull``    the output-projection GEMM fetches its A operand - this rank's rows of every peer's context - with TMA
-                loads from the peers' memory while it multiplies the previous tile (bias, dropout and residual fused
-                in its epilogue): the heads->nodes all-to-all *is* the operand load.  A local copy of the pulled rows
-                is written from the same shared-memory stages only when the backward pass will need it;
+``ctx``         heads->nodes, two forms.  *Routed stores* (default where the model has no virtual-node rows): the
+                attention kernels store every context row a second time, straight into the buffer of the rank that
+                owns the node (one slab per source rank), so the all-to-all rides on the attention kernel's stores
+                and is hidden behind its gathers; the output-projection GEMM then gathers its A operand from the
+                local slabs.  *Pull*: the GEMM's loader warps fetch this rank's rows of every peer's context from the
+                peers' memory while the previous tile is multiplied.  Either way bias, dropout and residual are fused
+                in the GEMM's epilogue and a local copy of the gathered rows is written from the same shared-memory
+                stages only when the backward pass will need it;
 backward        mirrors it: the d(context) GEMM pushes to the head owners, the attention backward writes
-                dq|dk|dv packed, and the input-gradient GEMM pulls its rows of every peer's dq|dk|dv the same way
-                (keeping the local copy that the weight-gradient GEMM reads).
+                dq|dk|dv packed - routed to the row owners' slabs, or locally for the pull form - and the
+                input-gradient GEMM gathers its rows of every source's dq|dk|dv the same way (keeping the local copy
+                that the weight-gradient GEMM reads).
 
 Device-side barriers (bounded spins) order producers and consumers; no host synchronisation and no NCCL
 call happens inside a layer.
 """
 from __future__ import annotations
 
+import os
 import types
 from typing import List, Optional
 
@@ -39,13 +45,15 @@ from .norm import ColsumSlot, batch_norm, column_sum, hash_dropout, layer_norm, 
 
 # context dropout inside the attention kernel's store (off: a separate hash_dropout pass over the pulled context)
 FUSE_CONTEXT_DROPOUT = True
+# heads->nodes by routed stores of the attention kernels (off, or a model with virtual-node rows: the GEMMs pull)
+ROUTE_ATTENTION_ROWS = os.environ.get("BF_ROUTE_ATTENTION_ROWS", "1") != "0"
 
 
 class SPContext:
     """Symmetric buffers and geometry shared by all layers of one model."""
 
     def __init__(self, group, device, world: int, rows_local: int, hidden: int, heads: int, n_layers: int, dtype,
-                 token_rows: Optional[List[int]] = None):
+                 token_rows: Optional[List[int]] = None, routed: Optional[bool] = None):
         self.sw = symm.get_world(group, device)
         # seed shared by all ranks for masks that one rank generates and another regenerates (set by the trainer every
         # step from the run seed and the epoch; None = not set)
@@ -68,6 +76,13 @@ class SPContext:
         self.ctx = [self.sw.alloc((self.total_rows, self.hl), dtype) for _ in range(n_layers)]
         self.dqkv = self.sw.alloc((self.total_rows, self.qkv_ld), dtype)
         self.dctx = self.sw.alloc((self.total_rows, self.hl), dtype)
+        # Routed form: ``ctx[l]`` and ``dqkv`` are indexed (source rank, row of this rank) - P slabs of rows_local rows
+        # that the peers' attention kernels fill - instead of (global row); the head owner keeps its own context of all
+        # rows in a plain local tensor for its backward pass.
+        want = ROUTE_ATTENTION_ROWS if routed is None else bool(routed)
+        self.routed = bool(want and self.P > 1 and token_rows is None and self.hl % 8 == 0)
+        self.ctx_local = ([torch.empty((self.total_rows, self.hl), dtype=dtype, device=device) for _ in range(n_layers)]
+                          if self.routed else None)
         # row permutation of the packed [Wq;Wk;Wv]: destination-rank major, then k|v|q, then head columns
         idx = []
         for r in range(self.P):
@@ -81,6 +96,16 @@ class SPContext:
     @property
     def row0(self) -> int:
         return self.rank * self.rows_local
+
+    def slab_ptrs(self, buf, row_bytes: int) -> List[int]:
+        """Base address of every source rank's slab inside this rank's own copy of a routed buffer."""
+        base = buf.tensor.data_ptr()
+        return [base + s * self.rows_local * row_bytes for s in range(self.P)]
+
+    def route(self, buf, ld: int, extra=()) -> List[int]:
+        """Route descriptor of the attention bindings: rows per destination, this rank's slab, row stride, ``extra``
+        header fields, then every destination's buffer base."""
+        return [self.rows_local, self.rank * self.rows_local, int(ld)] + [int(v) for v in extra] + [int(p) for p in buf.ptrs]
 
     def packed_projection(self, layer: int, wq, wk, wv, bq, bk, bv, dtype):
         """``[Wq; Wk; Wv]`` with its rows in the order of ``perm`` (and the bias likewise), in the activation dtype.  The
@@ -185,13 +210,17 @@ class _QKVPush(torch.autograd.Function):
             # below, and every rank reaches the barrier that follows that layer's d(context) push (or scatter) only
             # after this GEMM, so no peer can overwrite rows that are still being fetched.
             sp.sw.barrier(0)                                         # every rank's dq|dk|dv is complete
-            dx, dloc = _pull_gemm(buf.ptrs, sp.row0, sp.qkv_ld, 3 * sp.hl, sp.rows_local, wt, residual=dres, keep_copy=True)
+            # routed: the peers' attention kernels have delivered this rank's rows into its own slabs
+            src = sp.slab_ptrs(buf, sp.qkv_ld * x.element_size()) if sp.routed else buf.ptrs
+            dx, dloc = _pull_gemm(src, 0 if sp.routed else sp.row0, sp.qkv_ld, 3 * sp.hl, sp.rows_local, wt, residual=dres,
+                                  keep_copy=True)
             if debug.enabled():
                 sp.sw.barrier(0)                                     # poisoning below must wait for the peers' reads
         elif sp.P > 1:
             sp.sw.barrier(0)                                         # every rank's dq|dk|dv is complete
             dloc = torch.empty((sp.rows_local, 3 * sp.h), dtype=x.dtype, device=x.device)
-            _ext.load().peer_gather_cols(buf.ptrs, sp.row0, sp.rows_local, 3 * sp.hl * x.element_size(),
+            src = sp.slab_ptrs(buf, sp.qkv_ld * x.element_size()) if sp.routed else buf.ptrs
+            _ext.load().peer_gather_cols(src, 0 if sp.routed else sp.row0, sp.rows_local, 3 * sp.hl * x.element_size(),
                                          sp.qkv_ld * x.element_size(), dloc)
             _ext.count_launches(1)
             sp.sw.barrier(0)                                         # all reads done before the buffer is reused
@@ -221,14 +250,17 @@ class _PackedEdgeAttention(torch.autograd.Function):
         ext = _ext.load()
         r, hlh, hn, hl = sp.total_rows, sp.hl_heads, sp.hn, sp.hl
         q, k, v = sp.split_packed(qkv)
-        out = sp.ctx[layer].tensor
+        # routed: the kernel keeps this rank's copy of all rows in a local tensor (its backward reads it) and stores
+        # every row a second time into the owner's slab of the symmetric buffer
+        out = sp.ctx_local[layer] if sp.routed else sp.ctx[layer].tensor
+        route = sp.route(sp.ctx[layer], hl) if sp.routed else []
         z = torch.empty((r, hlh), dtype=torch.float32, device=qkv.device)
         kmax = -1 if graph.max_degree is None else int(graph.max_degree)
         # dropout on the context (GT applies it before the output projection) is fused into the store: the mask of
         # element (row, c) is the one the owner of that row regenerates for (row - its first row, this rank's column)
         out_drop = [float(out_p), int(out_seed), int(sp.rows_local), int(sp.rank * hl)] if out_p > 0 else []
         ext.edge_attn_fwd(q, k, v, out.view(r, hlh, hn), z, graph.rowptr, graph.col, graph.etype, etable,
-                          int(variant_id), float(dropout_p), int(seed), kmax, out_drop)
+                          int(variant_id), float(dropout_p), int(seed), kmax, out_drop, route)
         _ext.count_launches(1)
         if sp.token_rows is not None and len(sp.token_rows) > 1:
             out[sp.token_rows[1:]] = out[sp.token_rows[0]].clone()  # copy_global_token0 (gt_sp/utils.py:2365-2386)
@@ -251,16 +283,19 @@ class _PackedEdgeAttention(torch.autograd.Function):
             dout = dout.clone()
             dout[sp.token_rows[0]] += dout[sp.token_rows[1:]].sum(0)
             dout[sp.token_rows[1:]] = 0
-        out = sp.ctx[ctx.layer].tensor
+        out = sp.ctx_local[ctx.layer] if sp.routed else sp.ctx[ctx.layer].tensor
         q, k, v = sp.split_packed(qkv)
-        # gradients land packed in the symmetric buffer so that peers can pull their rows
+        # gradients land packed in the symmetric buffer: in this rank's copy so that peers can pull their rows, or
+        # (routed) straight in the row owners' slabs at the k | v | q column offsets of a packed row
         dbuf = sp.dqkv.tensor
         dq, dk, dv = sp.split_packed(dbuf)
+        route = sp.route(sp.dqkv, sp.qkv_ld, extra=(2 * hl, 0, hl)) if sp.routed else []
         zd = torch.empty((r, hlh, 2), dtype=torch.float32, device=qkv.device)
         detab = torch.zeros(etable.shape, dtype=torch.float32, device=qkv.device) if has_tab else None
         ext.edge_attn_bwd(q, k, v, out.view(r, hlh, hn), z, dout.view(r, hlh, hn), dq, dk, dv, zd, graph.rowptr, graph.col,
                           graph.etype, graph.t_rowptr, graph.t_row, graph.t_eid, etable if has_tab else None, detab,
-                          variant_id, dropout_p, seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots), ctx.out_drop)
+                          variant_id, dropout_p, seed, kmax, graph.t_task, graph.t_split, int(graph.kv_slots), ctx.out_drop,
+                          route)
         _ext.count_launches(3)
         if debug.enabled() and dout.data_ptr() == sp.dctx.tensor.data_ptr():
             debug.poison(sp.dctx.tensor)              # d(context) consumed; the next push must overwrite all of it
@@ -283,15 +318,16 @@ class _CtxPullOutProj(torch.autograd.Function):
             # read it (weight gradient)
             w = gemm.operand_copy(wo, dt)
             sp.sw.barrier(0)                                         # every head owner has written its context
-            y, a = _pull_gemm(sp.ctx_ptrs_for(ctx_full), sp.row0, sp.hl, sp.hl, sp.rows_local, w, bias=bo, residual=residual,
-                              dropout_p=p_post, seed=seed_post, keep_copy=any(ctx.needs_input_grad[:3]))
+            y, a = _pull_gemm(sp.ctx_ptrs_for(ctx_full), 0 if sp.routed else sp.row0, sp.hl, sp.hl, sp.rows_local, w, bias=bo,
+                              residual=residual, dropout_p=p_post, seed=seed_post, keep_copy=any(ctx.needs_input_grad[:3]))
             ctx.save_for_backward(a if a is not None else ctx_full.new_empty(0), w)
         else:
             if sp.P > 1:
                 sp.sw.barrier(0)                                     # every head owner has written its context
                 a = torch.empty((sp.rows_local, sp.h), dtype=dt, device=ctx_full.device)
                 esz = ctx_full.element_size()
-                _ext.load().peer_gather_cols(sp.ctx_ptrs_for(ctx_full), sp.row0, sp.rows_local, sp.hl * esz, sp.hl * esz, a)
+                _ext.load().peer_gather_cols(sp.ctx_ptrs_for(ctx_full), 0 if sp.routed else sp.row0, sp.rows_local, sp.hl * esz,
+                                             sp.hl * esz, a)
                 _ext.count_launches(1)
             else:
                 a = ctx_full
@@ -340,10 +376,17 @@ class _CtxPullOutProj(torch.autograd.Function):
 
 
 def _ctx_ptrs_for(self, t):
-    for b in self.ctx:
-        if b.tensor.data_ptr() == t.data_ptr():
-            return b.ptrs
-    raise RuntimeError("context tensor is not one of the symmetric context buffers")
+    """Source pointers of the heads->nodes gather for the context tensor an attention call returned: the peers' buffers
+    (pull form), or the slabs of this rank's own buffer that the peers' attention kernels have filled (routed form)."""
+    if self.routed:
+        for i, loc in enumerate(self.ctx_local):
+            if loc.data_ptr() == t.data_ptr():
+                return self.slab_ptrs(self.ctx[i], self.hl * t.element_size())
+    else:
+        for b in self.ctx:
+            if b.tensor.data_ptr() == t.data_ptr():
+                return b.ptrs
+    raise RuntimeError("context tensor is not one of the context buffers")
 
 
 SPContext.ctx_ptrs_for = _ctx_ptrs_for

@@ -194,7 +194,10 @@ def case_sp(a):
         dist.init_process_group("nccl", device_id=dev)
     n_loc = a.nodes // world
     h, heads = a.hidden, a.heads
-    sp = fused_sp.SPContext(dist.group.WORLD if world > 1 else None, dev, world, n_loc, h, heads, 1, torch.bfloat16)
+    # the pull form of heads->nodes is what this case times (the routed form has no kernel of its own to time: its
+    # transfer rides on the attention kernels' stores)
+    sp = fused_sp.SPContext(dist.group.WORLD if world > 1 else None, dev, world, n_loc, h, heads, 1, torch.bfloat16,
+                            routed=False)
     x = torch.randn(n_loc, h, device=dev).bfloat16()
     wq, wk, wv = (torch.randn(h, h, device=dev) * 0.05 for _ in range(3))
     wo = (torch.randn(h, h, device=dev) * 0.05)

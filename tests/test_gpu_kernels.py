@@ -62,6 +62,65 @@ def test_edge_attention_hub_rows(variant):
     _run(variant, torch.bfloat16, 1, 16, hub_row=20000, hub_col=3000, n=4500, e=9000)
 
 
+@pytest.mark.parametrize("variant,hl,hn", [("plain", 2, 16), ("plain", 1, 16), ("gps", 4, 16), ("exphormer", 2, 32)])
+def test_edge_attention_routed_rows_match_local_rows(variant, hl, hn):
+    """Routed stores on one GPU (the "destinations" are local buffers standing in for the peers' mappings): every context
+    row also lands in its owner's slab, and routed dq / dk / dv rows equal the unrouted gradients - regular rows, a
+    5,000-edge query row, a key used by 4,000 queries (split into work items), typed edges."""
+    from budgetformer_b200.ops import _ext
+    from budgetformer_b200.ops.edge_attention import _VARIANTS
+    ext = _ext.load()
+    dev = torch.device("cuda")
+    torch.manual_seed(2)
+    n_dest, rows_per = 4, 1200
+    n = n_dest * rows_per
+    g = random_attn_graph(n, 9000, hub_row=5000, hub_col=4000, seed=9, typed=(variant == "exphormer")).to(dev).ensure_transpose()
+    w = hl * hn
+    q, k, v = (torch.randn(n, hl, hn, device=dev).bfloat16() for _ in range(3))
+    etab = (torch.randn(2, hl, hn, device=dev) * 0.5 + 1.0) if variant == "exphormer" else None
+    vid = _VARIANTS[variant]
+    src = 2                                                          # this "rank" is source 2 of 4
+    out = torch.empty(n, hl, hn, device=dev, dtype=torch.bfloat16)
+    z = torch.empty(n, hl, device=dev)
+    slabs = [torch.full((n_dest * rows_per, w), 7.0, device=dev, dtype=torch.bfloat16) for _ in range(n_dest)]
+    route = [rows_per, src * rows_per, w] + [t.data_ptr() for t in slabs]
+    ext.edge_attn_fwd(q, k, v, out, z, g.rowptr, g.col, g.etype, etab, vid, 0.0, 0, -1, [], route)
+    torch.cuda.synchronize()
+    for d in range(n_dest):
+        mine = slabs[d][src * rows_per:(src + 1) * rows_per]
+        assert torch.equal(mine, out.view(n, w)[d * rows_per:(d + 1) * rows_per]), f"context rows of destination {d}"
+        other = torch.cat([slabs[d][:src * rows_per], slabs[d][(src + 1) * rows_per:]])
+        assert float((other - 7.0).abs().max()) == 0.0               # nobody else's slab was touched
+    # backward: unrouted into a packed [n, ld] buffer, routed into slabs of the same row layout (k | v | q)
+    ld = (3 * w + 63) // 64 * 64
+    dout = torch.randn(n, hl, hn, device=dev).bfloat16()
+    def grads(route):
+        buf = torch.full((n, ld), 3.0, device=dev, dtype=torch.bfloat16)
+        part = lambda i: buf[:, i * w:(i + 1) * w].view(n, hl, hn)
+        zd = torch.empty(n, hl, 2, device=dev)
+        detab = torch.zeros(2, hl, hn, device=dev) if etab is not None else None
+        ext.edge_attn_bwd(q, k, v, out, z, dout, part(2), part(0), part(1), zd, g.rowptr, g.col, g.etype, g.t_rowptr, g.t_row,
+                          g.t_eid, etab, detab, vid, 0.0, 0, -1, g.t_task, g.t_split, int(g.kv_slots), [], route)
+        torch.cuda.synchronize()
+        return buf
+    plain = grads([])
+    gslabs = [torch.full((n_dest * rows_per, ld), 5.0, device=dev, dtype=torch.bfloat16) for _ in range(n_dest)]
+    untouched = grads([rows_per, src * rows_per, ld, 2 * w, 0, w] + [t.data_ptr() for t in gslabs])
+    assert float((untouched - 3.0).abs().max()) == 0.0               # routed gradients never touch the local buffer
+    for d in range(n_dest):
+        got = gslabs[d][src * rows_per:(src + 1) * rows_per, :3 * w]
+        want = plain[d * rows_per:(d + 1) * rows_per, :3 * w]
+        # (the 5,000-edge query row adds its dq partials with atomics: last-bit differences between two runs)
+        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), f"gradient rows of destination {d}"
+        if 3 * w < ld:                                               # the padding columns of a packed row stay untouched
+            assert float((gslabs[d][src * rows_per:(src + 1) * rows_per, 3 * w:] - 5.0).abs().max()) == 0.0
+        other = torch.cat([gslabs[d][:src * rows_per], gslabs[d][(src + 1) * rows_per:]])
+        assert float((other - 5.0).abs().max()) == 0.0
+    # a route that does not cover the rows is refused before anything is launched
+    with pytest.raises(RuntimeError):
+        ext.edge_attn_fwd(q, k, v, out, z, g.rowptr, g.col, g.etype, etab, vid, 0.0, 0, -1, [], [rows_per + 1, 0, w] + [t.data_ptr() for t in slabs])
+
+
 def test_edge_attention_strided_qkv_views():
     dev = torch.device("cuda")
     n, hl, hn = 300, 4, 16
