@@ -9,7 +9,8 @@ copies), the edge attention, a fourth all-to-all and the output projection
                 rank's packed ``[N, 3*h/P]`` buffer over NVLink — the nodes->heads all-to-all *is* the epilogue;
 ``attention``   the edge-attention kernels read q|k|v from that packed buffer and write the context into a
                 second symmetric buffer;
-``ctx``         heads->nodes, two forms.  *Routed stores* (default where the model has no virtual-node rows): the
+``ctx``         heads->nodes, two forms.  *Routed stores* (default where a rank's slice of a row is at least 128 bytes
+                and the model has no virtual-node rows): the
                 attention kernels store every context row a second time, straight into the buffer of the rank that
                 owns the node (one slab per source rank), so the all-to-all rides on the attention kernel's stores
                 and is hidden behind its gathers; the output-projection GEMM then gathers its A operand from the
@@ -45,7 +46,8 @@ from .norm import ColsumSlot, batch_norm, column_sum, hash_dropout, layer_norm, 
 
 # context dropout inside the attention kernel's store (off: a separate hash_dropout pass over the pulled context)
 FUSE_CONTEXT_DROPOUT = True
-# heads->nodes by routed stores of the attention kernels (off, or a model with virtual-node rows: the GEMMs pull)
+# heads->nodes by routed stores of the attention kernels (off, narrow row slices, or a model with virtual-node rows:
+# the GEMMs pull); BF_ROUTE_ATTENTION_ROWS=0 switches the form off, =force takes it whatever the row width
 ROUTE_ATTENTION_ROWS = os.environ.get("BF_ROUTE_ATTENTION_ROWS", "1") != "0"
 
 
@@ -79,7 +81,14 @@ class SPContext:
         # Routed form: ``ctx[l]`` and ``dqkv`` are indexed (source rank, row of this rank) - P slabs of rows_local rows
         # that the peers' attention kernels fill - instead of (global row); the head owner keeps its own context of all
         # rows in a plain local tensor for its backward pass.
-        want = ROUTE_ATTENTION_ROWS if routed is None else bool(routed)
+        # Measured on the 2.9 M-node benchmark (GT, h = 128): with 128-byte rows per rank (2 ranks) the routed form is
+        # 0.9 ms per step faster than the pull form (43.5 against 44.5 ms); with 64-byte rows (4 ranks) the attention
+        # kernels' scattered remote stores cost more than the pulls they replace (31.1 against 29.4 ms).  Default: routed
+        # when a rank's slice of a row is at least one 128-byte line.
+        wide = self.hl * torch.empty((), dtype=dtype).element_size() >= 128
+        if os.environ.get("BF_ROUTE_ATTENTION_ROWS", "") == "force":
+            wide = True
+        want = (ROUTE_ATTENTION_ROWS and wide) if routed is None else bool(routed)
         self.routed = bool(want and self.P > 1 and token_rows is None and self.hl % 8 == 0)
         self.ctx_local = ([torch.empty((self.total_rows, self.hl), dtype=dtype, device=device) for _ in range(n_layers)]
                           if self.routed else None)
