@@ -31,10 +31,10 @@ GRAPH_DESC = {"dag": "citation-like DAG (power-law out-degree)", "chung_lu_direc
 sys.path.insert(0, REPO)
 
 # Epoch time of the reference arm (unmodified reference + pure-PyTorch stand-ins for its native wheels, its own NCCL
-# and cuBLAS path) on configuration patents_like, driver-measured on this pool's B200s with this file's
-# `--impl reference` (20 timed epochs): ms per epoch by number of GPUs.  The reference publishes no numbers of its
-# own, so `vs_baseline` is this arm's epoch time over ours at the same GPU count.
-REFERENCE_EPOCH_MS = {"patents_like": {1: 5089.0, 2: 3388.5, 4: 1707.0, 8: 1455.5}}
+# and cuBLAS path), measured on this pool's B200s with this file's `--impl reference`: ms per epoch by number of GPUs
+# (patents_like: 20 timed epochs per GPU count; arxiv_like: 3 timed epochs on one GPU).  The reference publishes no
+# numbers of its own, so `vs_baseline` is this arm's epoch time over ours at the same GPU count.
+REFERENCE_EPOCH_MS = {"patents_like": {1: 5089.0, 2: 3388.5, 4: 1707.0, 8: 1455.5}, "arxiv_like": {1: 3156.7}}
 
 
 def config_record(name, cfg, n_nodes, n_edges, feat_dim, world, ckpt, scale):
