@@ -19,7 +19,7 @@ from __future__ import annotations
 
 import os
 import enum
-from dataclasses import dataclass, field, replace
+from dataclasses import dataclass, replace
 from typing import Callable, Dict, Iterator, List, Optional, Sequence, Tuple
 
 import torch

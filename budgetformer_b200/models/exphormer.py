@@ -7,7 +7,6 @@ The reference evaluates ``edge_proj`` on an ``[E_m, h]`` matrix that has only tw
 the two rows are projected once and the kernels look them up by edge type."""
 from __future__ import annotations
 
-import torch
 from torch import nn
 from torch.nn import functional as F
 from torch.utils.checkpoint import checkpoint

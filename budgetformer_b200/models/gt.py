@@ -6,7 +6,6 @@ output projection ``O``, ReLU FFN of width 2h and one dropout module reused in b
 (:631-684), ``MLPReadout`` h -> h/2 -> h/4 -> C (:687-702)."""
 from __future__ import annotations
 
-import torch
 from torch import nn
 from torch.nn import functional as F
 from torch.utils.checkpoint import checkpoint

@@ -41,7 +41,7 @@ from . import _ext, gemm
 from ..utils import debug
 from .edge_attention import _VARIANTS
 from .ffn import fused_ffn
-from .norm import ColsumSlot, batch_norm, column_sum, hash_dropout, layer_norm, new_seed
+from .norm import ColsumSlot, batch_norm, hash_dropout, layer_norm, new_seed
 
 
 # context dropout inside the attention kernel's store (off: a separate hash_dropout pass over the pulled context)

@@ -102,7 +102,6 @@ def mode_shard(out_path):
     """--shard_cpu_edge_build: the graph all-gathered from per-rank shards equals the graph one process builds, for the
     plain, the typed (Exphormer), the virtual-node (Graphormer), the unbudgeted and the fan-out case; and training on
     it runs (prefetch thread included)."""
-    from budgetformer_b200.graph.engine import resolve_budget_state
     res = {}
     cases = {"gt": [], "exphormer": [], "graphormer": [],
              "gt_fanout": ["--rw_edge_mode", "dgl_neighbor", "--fanout", "3,2"]}

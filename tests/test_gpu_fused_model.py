@@ -105,7 +105,7 @@ def test_context_dropout_fused_into_attention_matches_separate_pass():
     """GT applies dropout to the attention context before the output projection.  Fused into the attention kernel's
     store (and undone in the <dout, out> term of its backward) it must reproduce the separate hash-dropout pass:
     same counter-based mask, same loss, same gradients."""
-    from budgetformer_b200.ops import fused_sp, norm
+    from budgetformer_b200.ops import fused_sp
     results = {}
     for fuse in (True, False):
         torch.manual_seed(21)

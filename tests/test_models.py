@@ -4,7 +4,6 @@ import torch
 
 from budgetformer_b200.config import parse_fullgraph_args
 from budgetformer_b200.graph.attn_graph import AttnGraph, add_virtual_node
-from budgetformer_b200.models import MODEL_REGISTRY
 from budgetformer_b200.train.checkpoint import normalize_state_dict_keys
 from budgetformer_b200.train.engine import build_model
 

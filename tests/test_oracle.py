@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from budgetformer_b200 import oracle
-from budgetformer_b200.graph.attn_graph import AttnGraph, Topology, add_virtual_node
+from budgetformer_b200.graph.attn_graph import AttnGraph, add_virtual_node
 from budgetformer_b200.graph.builder import build_attn_graph
 from budgetformer_b200.graph.builder_spec import random_walks
 from budgetformer_b200.ops.edge_attention import dropout_keep_mask, edge_attention_reference
