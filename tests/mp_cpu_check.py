@@ -150,10 +150,26 @@ def mode_syncbn(out_path):
         json.dump({"out": torch.cat(parts)[:8].tolist(), "grads": grads, "running_mean": rm}, open(out_path, "w"))
 
 
-if __name__ == "__main__":
+def mode_raise(out_path):
+    """Every rank trains two steps, then rank 1 raises: the entry-point guard prints the traceback and ends the process
+    with status 1 (no collective teardown, no wait in interpreter shutdown), so the launcher can end the job."""
+    t = make("gt", [])
+    t.train_step(1)
+    t.train_step(2)
+    if t.rank == 1:
+        raise RuntimeError("injected failure on rank 1")
+    t.train_step(3)                                   # rank 0 goes on and would wait for its peer in the next collective
+
+
+def _dispatch():
     mode, out = sys.argv[1], sys.argv[2]
     {"equiv": mode_equiv, "train": mode_train, "oom": mode_oom, "syncbn": mode_syncbn, "watchdog": mode_watchdog,
-     "shard": mode_shard}[mode](out)
+     "shard": mode_shard, "raise": mode_raise}[mode](out)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    from budgetformer_b200.utils.rank_main import run_rank_main
+    run_rank_main(_dispatch)

@@ -125,3 +125,18 @@ def test_sharded_cpu_edge_build_equals_whole_build(tmp_path):
         assert res[name]["equal"], (name, res[name])
         assert res[name]["totals"] == res[name]["totals_whole"], (name, res[name])
     assert res["fit"]["epochs"] == 4 and 0.0 <= res["fit"]["valid"] <= 1.0
+
+
+def test_a_raising_rank_ends_the_job_promptly(tmp_path):
+    """Rank 1 raises after two steps while rank 0 walks into the next step's collectives: the failing rank must leave
+    with status 1 at once (traceback on stderr), and the launcher then ends the job - no hang until a timeout."""
+    import time
+    env = dict(os.environ)
+    env["OMP_NUM_THREADS"] = "2"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29811", os.path.join(HERE, "mp_cpu_check.py"), "raise", str(tmp_path / "unused.json")]
+    t0 = time.time()
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=env)
+    assert r.returncode != 0
+    assert "injected failure on rank 1" in r.stderr
+    assert time.time() - t0 < 120

@@ -227,3 +227,22 @@ def test_warmup_oom_under_gpu_edge_policy_moves_the_build_to_the_cpu():
     u.planner.probe = ScriptedMemoryProbe(1 << 34, lambda modes: {"peak": 1 << 30, "live": 1 << 29})
     with pytest.raises(RuntimeError, match="warm-up with every layer recomputed"):
         u.train_step(1)                               # already on the CPU policy: nothing left to give back
+
+
+def test_bench_fit_mode_runs_the_user_loop_on_cpu(capsys, monkeypatch):
+    """``bench.py --fit_epochs``: the training loop a user runs (budget search with probes, execution planner,
+    evaluation) on a named configuration, one JSON summary line on stdout."""
+    import json
+    import sys
+    monkeypatch.setenv("BF_BENCH_CACHE", "")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    monkeypatch.syspath_prepend(root)
+    import bench
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--config", "sbm2k", "--fit_epochs", "12", "--fit_flags",
+                                      "--adaptive_edge_budget --activation_checkpoint_mode multi_tier --device cpu --eval_every 6"])
+    ns = bench.parse()
+    bench.run_fit(ns)
+    lines = [ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    rec = json.loads(lines[-1])
+    assert rec["mode"] == "fit" and rec["epochs"] == 12 and len(rec["epoch_ms_first"]) == 12
+    assert rec["budget"]["real"] + rec["budget"]["rw"] <= 8 and rec["plan"]["tiers"] and rec["best"]["epoch"] in (6, 12)
