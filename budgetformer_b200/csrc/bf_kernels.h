@@ -122,6 +122,28 @@ int bf_budget_select(const bf_build_params* p, cudaStream_t st);
 int bf_ell_to_csr(const int* ell_col, const uint8_t* ell_type, const int* rowptr, int n, int cap, int* col,
                   uint8_t* etype, cudaStream_t st);
 
+// ---- feed-forward block with the hidden tile kept on chip (ffn_fused_tcgen05.cu) ----------------
+typedef struct {
+  const void* X;                    // [M, hidden] 16-bit, row stride ldx (elements)
+  void* Y;                          // [M, hidden] 16-bit, row stride ldy
+  long long ldx, ldy;
+  const void* W1;                   // [ffn, hidden] contiguous (nn.Linear layout)
+  const void* W2;                   // [hidden, ffn] contiguous
+  const float* b1;                  // [ffn] fp32 or NULL
+  const float* b2;                  // [hidden] fp32 or NULL
+  long long M;
+  int hidden, ffn;                  // supported: 128 / 256 (bf_ffn_fused_supported)
+  int dtype;                        // BF_BF16 or BF_FP16
+  int act;                          // 1 ReLU, 2 GELU (erf)
+  float dropout1, dropout2;         // on the hidden tile / on the output before the residual; masks = hash(seed, row, col)
+  uint32_t seed1, seed2;
+  int residual;                     // 1: Y = X + ...
+  int* status;                      // [4] device status words (0 = ok)
+} bf_ffn_params;
+
+int bf_ffn_fused_supported(long long M, int hidden, int ffn);
+int bf_ffn_fused_fwd(const bf_ffn_params* p, cudaStream_t st);
+
 // ---- tcgen05 GEMM with fused epilogue / fused nodes->heads all-to-all (gemm_tcgen05.cu) ---------
 typedef struct {
   const void* A;                    // [M, K] 16-bit, row stride lda (elements)

@@ -499,6 +499,39 @@ void gemm_tn_pull(std::vector<int64_t> src_ptrs, int64_t src_row_offset, int64_t
   check_cuda(bf_gemm_tn(&p, at::cuda::getCurrentCUDAStream()), "gemm_tn_pull");
 }
 
+// y = [x +] drop2(act(x W1^T + b1) W2^T + b2) with the hidden tile kept on chip (no autograd: forward-only uses)
+Tensor ffn_fused_fwd(Tensor x, Tensor w1, OptTensor b1, Tensor w2, OptTensor b2, int64_t act, bool residual, double p1,
+                     int64_t seed1, double p2, int64_t seed2, Tensor status) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 &&
+              (x.scalar_type() == torch::kBFloat16 || x.scalar_type() == torch::kHalf), "ffn_fused_fwd: x [M, h] 16-bit on CUDA");
+  TORCH_CHECK(w1.is_cuda() && w2.is_cuda() && w1.is_contiguous() && w2.is_contiguous() && w1.scalar_type() == x.scalar_type() &&
+              w2.scalar_type() == x.scalar_type() && w1.dim() == 2 && w2.dim() == 2 && w1.size(1) == x.size(1) &&
+              w2.size(0) == x.size(1) && w2.size(1) == w1.size(0), "ffn_fused_fwd: W1 [f, h], W2 [h, f] contiguous in the dtype of x");
+  TORCH_CHECK(bf_ffn_fused_supported(x.size(0), (int)x.size(1), (int)w1.size(0)), "ffn_fused_fwd: unsupported shape");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt && status.numel() >= 4);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty({x.size(0), x.size(1)}, x.options());
+  bf_ffn_params p{};
+  p.X = x.data_ptr(); p.Y = y.data_ptr(); p.ldx = x.stride(0); p.ldy = y.stride(0);
+  p.W1 = w1.data_ptr(); p.W2 = w2.data_ptr();
+  for (const OptTensor* bt : {&b1, &b2}) {
+    if (!bt->has_value()) continue;
+    TORCH_CHECK((*bt)->scalar_type() == torch::kFloat && (*bt)->is_contiguous() && ((uintptr_t)(*bt)->data_ptr()) % 16 == 0,
+                "ffn_fused_fwd: biases must be contiguous fp32, 16-byte aligned");
+  }
+  TORCH_CHECK(!b1.has_value() || b1->numel() == w1.size(0));
+  TORCH_CHECK(!b2.has_value() || b2->numel() == w2.size(0));
+  p.b1 = b1.has_value() ? b1->data_ptr<float>() : nullptr;
+  p.b2 = b2.has_value() ? b2->data_ptr<float>() : nullptr;
+  p.M = x.size(0); p.hidden = (int)x.size(1); p.ffn = (int)w1.size(0);
+  p.dtype = dtype_code(x); p.act = (int)act;
+  p.dropout1 = (float)p1; p.dropout2 = (float)p2; p.seed1 = (uint32_t)seed1; p.seed2 = (uint32_t)seed2;
+  p.residual = residual ? 1 : 0;
+  p.status = status.data_ptr<int>();
+  check_cuda(bf_ffn_fused_fwd(&p, at::cuda::getCurrentCUDAStream()), "ffn_fused_fwd");
+  return y;
+}
+
 // dW = dY^T X (fp32 [N, K]) and, with `want_bias`, the column sums of dY (fp32 [N]) from the same kernel.
 std::vector<Tensor> gemm_dw(Tensor dY, Tensor X, bool want_bias, Tensor status) {
   TORCH_CHECK(dY.is_cuda() && X.is_cuda() && dY.dim() == 2 && X.dim() == 2 && dY.size(0) == X.size(0), "gemm_dw: dY [M,N], X [M,K]");
@@ -738,6 +771,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_tn", &gemm_tn);
   m.def("gemm_tn_pull", &gemm_tn_pull);
   m.def("gemm_dw", &gemm_dw);
+  m.def("ffn_fused_fwd", &ffn_fused_fwd);
+  m.def("ffn_fused_supported", [](int64_t M, int64_t h, int64_t f) { return bf_ffn_fused_supported(M, (int)h, (int)f) != 0; });
   m.def("gemm_dw_supported", &gemm_dw_supported);
   m.def("gemm_supported", &gemm_supported);
   m.def("layernorm_fwd", &layernorm_fwd);

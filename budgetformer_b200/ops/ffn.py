@@ -1,12 +1,14 @@
 """Feed-forward block on the tcgen05 GEMM: ``y = residual + drop2(W2 drop1(act(W1 x + b1)) + b2)``.
 
 Forward is two kernels (activation + dropout in the first epilogue, bias + dropout + residual in the
-second).  Backward for ReLU uses the mask epilogue: ``dh = (g W2) * [h > 0] / (1 - p1)`` comes out of
+second); forward passes without a backward (evaluation) run as one kernel with the hidden tile kept on chip
+(``ffn_onchip``).  Backward for ReLU uses the mask epilogue: ``dh = (g W2) * [h > 0] / (1 - p1)`` comes out of
 the GEMM directly, so the hidden gradient is never touched by a separate elementwise pass.  GELU keeps
 the pre-activation and the same GEMM's epilogue multiplies by ``gelu'(z)`` (``_FusedFFNGelu``).  Replaces Linear -> act -> Dropout -> Linear ->
 Dropout -> add of the reference layers (e.g. models/gt_dist_node_level.py:655-660)."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -18,6 +20,38 @@ from .norm import hash_dropout, new_seed
 
 # the ReLU mask travels from forward to backward as one bit per hidden element (off: the backward re-reads h)
 USE_RELU_BITS = True
+# Forward passes that no backward will follow run the whole block in one kernel with the hidden tile kept on chip
+# (csrc/ffn_fused_tcgen05.cu; model width 128, hidden width 256).  "1": evaluation passes (model.eval() under no_grad);
+# "all": also the first forward of recomputed layers (its hash dropout masks are reproduced by the recomputation);
+# "0": off.
+ONCHIP_FFN = os.environ.get("BF_FFN_ONCHIP", "1")
+
+
+def ffn_onchip(x: torch.Tensor, w1, b1, w2, b2, *, act: str, residual: bool, p1: float = 0.0, seed1: int = 0,
+               p2: float = 0.0, seed2: int = 0) -> torch.Tensor:
+    """``[x +] drop2(act(x W1^T + b1) W2^T + b2)`` in one kernel; the ``[rows, ffn]`` hidden matrix never reaches HBM.
+    No autograd.  Shapes: see ``onchip_supported``."""
+    from . import _ext
+    ext = _ext.load()
+
+    def f32(b):
+        if b is None:
+            return None
+        b = b.detach().float().contiguous()
+        return b.clone() if b.data_ptr() % 16 else b
+    y = ext.ffn_fused_fwd(x, gemm.operand_copy(w1, x.dtype), f32(b1), gemm.operand_copy(w2, x.dtype), f32(b2),
+                          gemm.ACT[act], bool(residual), float(p1), int(seed1), float(p2), int(seed2),
+                          gemm.status_tensor(x.device))
+    _ext.count_launches(1)
+    return y
+
+
+def onchip_supported(x: torch.Tensor, w1, w2) -> bool:
+    if not (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and x.stride(1) == 1
+            and (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0 and x.size(0) > 0):
+        return False
+    from . import _ext
+    return bool(_ext.load().ffn_fused_supported(x.size(0), x.size(1), w1.size(0))) and tuple(w2.shape) == (x.size(1), w1.size(0))
 
 
 class _FusedFFNRelu(torch.autograd.Function):
@@ -120,6 +154,15 @@ def fused_ffn(x: torch.Tensor, w1, b1, w2, b2, *, act: str = "relu", residual: O
     n1, k1 = w1.shape
     ok = x.is_cuda and x.stride(1) == 1 and gemm.supported(x.size(0), n1, k1, x.dtype) \
         and gemm.supported(x.size(0), w2.size(0), w2.size(1), x.dtype)
+    res_is_x = residual is not None and residual.data_ptr() == x.data_ptr() and residual.shape == x.shape \
+        and residual.stride() == x.stride()
+    forward_only = not torch.is_grad_enabled() and (not training or ONCHIP_FFN == "all")
+    if ok and forward_only and ONCHIP_FFN != "0" and act in ("relu", "gelu") and (residual is None or res_is_x) \
+            and onchip_supported(x, w1, w2):
+        # same order of seed draws as the two-GEMM forms below, so that a recomputation reproduces the masks
+        s1 = new_seed() if p1 > 0 else 0
+        s2 = new_seed() if p2 > 0 else 0
+        return ffn_onchip(x, w1, b1, w2, b2, act=act, residual=res_is_x, p1=p1, seed1=s1, p2=p2, seed2=s2)
     if ok and act == "relu":
         return _FusedFFNRelu.apply(x, w1, b1, w2, b2, residual, p1, p2, new_seed() if p1 > 0 else 0,
                                    new_seed() if p2 > 0 else 0, out_grad_colsum)

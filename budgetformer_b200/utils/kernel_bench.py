@@ -6,6 +6,7 @@
     python -m budgetformer_b200.utils.kernel_bench build --nodes 2923922 --edges 13975788
     python -m budgetformer_b200.utils.kernel_bench dw --m 2923922 --n 128 --k 128 --compare
     python -m budgetformer_b200.utils.kernel_bench pull --m 800000 --n 128 --k 128 --sources 8
+    python -m budgetformer_b200.utils.kernel_bench ffn --m 2923922 --compare
 
 Each case runs ``--warmup`` untimed and ``--iters`` timed launches bracketed by CUDA events on the launching
 stream, with operands larger than the 126 MB L2 (or ``--flush_l2``), and prints one JSON line: milliseconds,
@@ -86,6 +87,29 @@ def case_dw(a):
     if a.compare:
         ms2 = timed(lambda: (torch.matmul(dy.t(), x), dy.float().sum(0)), a.warmup, a.iters)
         report("library matmul + column sum", ms2, 2 * a.m * (a.n + a.k), 2.0 * a.m * a.n * a.k, {"m": a.m, "n": a.n, "k": a.k})
+    gemm.check_status("cuda")
+
+
+def case_ffn(a):
+    """Forward feed-forward block (model width 128, hidden 256): one kernel with the hidden tile on chip against the two
+    GEMM launches that write and re-read the hidden matrix.  Algorithmic bytes = X in + Y out."""
+    from ..ops import ffn as ffn_mod, gemm
+    x = torch.randn(a.m, 128, device="cuda").bfloat16()
+    l1, l2 = torch.nn.Linear(128, 256).cuda(), torch.nn.Linear(256, 128).cuda()
+    act = a.act or "relu"
+    nbytes = 2 * 2 * a.m * 128
+    flops = 2.0 * a.m * 128 * 256 * 2
+    with torch.no_grad():
+        fn = lambda: ffn_mod.ffn_onchip(x, l1.weight, l1.bias, l2.weight, l2.bias, act=act, residual=True)
+        ms = timed(fn, a.warmup, 1 if a.once else a.iters)
+        report("ffn_fused_tcgen05 (hidden tile on chip)", ms, nbytes, flops, {"m": a.m, "act": act})
+        if a.compare:
+            w1, w2 = gemm.operand_copy(l1.weight, x.dtype), gemm.operand_copy(l2.weight, x.dtype)
+            def two():
+                h = gemm.gemm_tn(x, w1, l1.bias, act)
+                return gemm.gemm_tn(h, w2, l2.bias, None, residual=x)
+            ms2 = timed(two, a.warmup, a.iters)
+            report("two tcgen05 GEMMs (hidden matrix through HBM)", ms2, nbytes, flops, {"m": a.m, "act": act})
     gemm.check_status("cuda")
 
 
@@ -285,12 +309,16 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="case", required=True)
     common = dict(warmup=3, iters=10)
-    for name in ("gemm", "attn", "ln", "build", "sp", "dw", "pull"):
+    for name in ("gemm", "attn", "ln", "build", "sp", "dw", "pull", "ffn"):
         p = sub.add_parser(name)
         p.add_argument("--warmup", type=int, default=common["warmup"])
         p.add_argument("--iters", type=int, default=common["iters"])
         p.add_argument("--once", action="store_true")
-        if name in ("dw", "pull"):
+        if name == "ffn":
+            p.add_argument("--m", type=int, default=1_000_000)
+            p.add_argument("--act", default="relu")
+            p.add_argument("--compare", action="store_true")
+        elif name in ("dw", "pull"):
             p.add_argument("--m", type=int, default=1_000_000)
             p.add_argument("--n", type=int, default=128)
             p.add_argument("--k", type=int, default=128)
@@ -328,7 +356,7 @@ def main(argv=None):
             p.add_argument("--graph", default="dag", choices=["dag", "chung_lu_directed", "chung_lu_undirected"])
     a = ap.parse_args(argv)
     {"gemm": case_gemm, "attn": case_attn, "ln": case_ln, "build": case_build, "sp": case_sp, "dw": case_dw,
-     "pull": case_pull}[a.case](a)
+     "pull": case_pull, "ffn": case_ffn}[a.case](a)
 
 
 if __name__ == "__main__":
