@@ -21,10 +21,10 @@ from .norm import hash_dropout, new_seed
 # the ReLU mask travels from forward to backward as one bit per hidden element (off: the backward re-reads h)
 USE_RELU_BITS = True
 # Forward passes that no backward will follow run the whole block in one kernel with the hidden tile kept on chip
-# (csrc/ffn_fused_tcgen05.cu; model width 128, hidden width 256).  "1": evaluation passes (model.eval() under no_grad);
-# "all": also the first forward of recomputed layers (its hash dropout masks are reproduced by the recomputation);
-# "0": off.
-ONCHIP_FFN = os.environ.get("BF_FFN_ONCHIP", "1")
+# (csrc/ffn_fused_tcgen05.cu; model width 128, hidden width 256).  "all" (default): evaluation passes and the first
+# forward of recomputed layers (recompute / keep_mha tiers; its hash dropout masks are reproduced by the recomputation,
+# which runs the two-GEMM form because the backward needs the hidden matrix); "1": evaluation passes only; "0": off.
+ONCHIP_FFN = os.environ.get("BF_FFN_ONCHIP", "all")
 
 
 def ffn_onchip(x: torch.Tensor, w1, b1, w2, b2, *, act: str, residual: bool, p1: float = 0.0, seed1: int = 0,
