@@ -139,6 +139,12 @@ typedef struct {
   uint32_t seed1, seed2;
   int residual;                     // 1: Y = X + ...
   int* status;                      // [4] device status words (0 = ok)
+  // Optional (training forward): the hidden matrix after activation and dropout, written from the on-chip operand, and
+  // one bit per hidden element (value > 0) in the layout of bf_gemm_params.relu_bits_out
+  void* H_out;                      // [M, ffn] 16-bit, row stride ldh (elements), or NULL
+  long long ldh;
+  void* relu_bits_out;              // uint16 [ffn / 16, ldmb >= M] or NULL
+  long long ldmb;
 } bf_ffn_params;
 
 int bf_ffn_fused_supported(long long M, int hidden, int ffn);

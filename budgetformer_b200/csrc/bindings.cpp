@@ -501,7 +501,7 @@ void gemm_tn_pull(std::vector<int64_t> src_ptrs, int64_t src_row_offset, int64_t
 
 // y = [x +] drop2(act(x W1^T + b1) W2^T + b2) with the hidden tile kept on chip (no autograd: forward-only uses)
 Tensor ffn_fused_fwd(Tensor x, Tensor w1, OptTensor b1, Tensor w2, OptTensor b2, int64_t act, bool residual, double p1,
-                     int64_t seed1, double p2, int64_t seed2, Tensor status) {
+                     int64_t seed1, double p2, int64_t seed2, Tensor status, OptTensor h_out, OptTensor relu_bits_out) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 &&
               (x.scalar_type() == torch::kBFloat16 || x.scalar_type() == torch::kHalf), "ffn_fused_fwd: x [M, h] 16-bit on CUDA");
   TORCH_CHECK(w1.is_cuda() && w2.is_cuda() && w1.is_contiguous() && w2.is_contiguous() && w1.scalar_type() == x.scalar_type() &&
@@ -528,6 +528,17 @@ Tensor ffn_fused_fwd(Tensor x, Tensor w1, OptTensor b1, Tensor w2, OptTensor b2,
   p.dropout1 = (float)p1; p.dropout2 = (float)p2; p.seed1 = (uint32_t)seed1; p.seed2 = (uint32_t)seed2;
   p.residual = residual ? 1 : 0;
   p.status = status.data_ptr<int>();
+  if (h_out.has_value()) {
+    TORCH_CHECK(h_out->is_cuda() && h_out->dim() == 2 && h_out->stride(1) == 1 && h_out->size(0) == x.size(0) &&
+                h_out->size(1) == w1.size(0) && h_out->scalar_type() == x.scalar_type(), "ffn_fused_fwd: h_out [M, f] in the dtype of x");
+    p.H_out = h_out->data_ptr(); p.ldh = h_out->stride(0);
+  }
+  if (relu_bits_out.has_value()) {
+    const Tensor& t = *relu_bits_out;
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kShort && t.dim() == 2 && t.stride(1) == 1 && t.size(1) == x.size(0) &&
+                t.size(0) * 16 == w1.size(0), "ffn_fused_fwd: ReLU bit mask must be int16 [f / 16, M]");
+    p.relu_bits_out = t.data_ptr(); p.ldmb = t.stride(0);
+  }
   check_cuda(bf_ffn_fused_fwd(&p, at::cuda::getCurrentCUDAStream()), "ffn_fused_fwd");
   return y;
 }

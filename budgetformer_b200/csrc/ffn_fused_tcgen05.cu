@@ -18,7 +18,10 @@
 //
 // The [M, 256] hidden matrix is neither written to nor read from HBM: the kernel moves X in and Y out (256 bytes per
 // row each) where the two-GEMM form moves 4 x that.  Used where no backward pass needs the hidden matrix (evaluation,
-// budget probes, the first forward of recomputed layers).  Dropout masks are the hash masks of the GEMM epilogues, so a
+// budget probes, the first forward of recomputed layers).  A training forward that retains activations can ask for the
+// hidden matrix as a side output: a further warp bulk-stores each half from the operand buffer the second GEMM reads
+// (and the epilogue leaves one bit per element, value > 0, for the backward's mask), so the matrix is written once and
+// never read back by the forward pass.  Dropout masks are the hash masks of the GEMM epilogues, so a
 // recomputation on the two-GEMM path reproduces them.  Every mbarrier wait is bounded (status word, early return,
 // tensor memory freed).  Replaces Linear -> act -> Dropout -> Linear -> Dropout -> add of the reference layers
 // (models/gt_dist_node_level.py:655-660, models/graphormer_dist_node_level.py:48-60).
@@ -41,7 +44,8 @@ constexpr int FF_HC = 128;           // hidden columns per half
 constexpr int FF_NHC = FF_F / FF_HC; // 2
 constexpr int FF_PANEL = FF_M * 128; // bytes of one 64-column panel of 128 rows
 constexpr int FF_EPI_WARPS = 16;
-constexpr int FF_THREADS = 32 * (2 + FF_EPI_WARPS);
+constexpr int FF_STORE_WARP = 2 + FF_EPI_WARPS;       // writes the hidden halves out when the caller keeps them
+constexpr int FF_THREADS = 32 * (3 + FF_EPI_WARPS);
 constexpr int FF_UMMA_K = 16;
 
 struct FfnArgs {
@@ -56,13 +60,18 @@ struct FfnArgs {
   int residual;                  // 1: Y += X
   int is_fp16;
   int* status;
+  // training forward: the hidden matrix is also written out (the backward pass needs it for the weight gradient),
+  // from the same shared-memory operand the second GEMM reads, together with one bit per element (value > 0)
+  int store_h;
+  unsigned short* bits_out;      // [256 / 16, ldmb >= M] or null
+  long long ldmb;
 };
 
 struct FfnControl {
   uint64_t w_full;
   uint64_t x_full[2], x_empty[2];
   uint64_t acc1_full[2], acc1_empty[2];
-  uint64_t hs_full, hs_empty;
+  uint64_t hs_full, hs_empty, hs_stored;
   uint64_t acc2_full, acc2_empty;
   uint32_t tmem_base;
   int abort_flag;
@@ -113,7 +122,7 @@ __device__ __forceinline__ uint8_t* ff_chunk(uint8_t* tile, int r, int col) {
 __global__ void __launch_bounds__(FF_THREADS, 1)
 ffn_fused_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                          const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_y,
-                         const FfnArgs g) {
+                         const __grid_constant__ CUtensorMap map_h, const FfnArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_x = smem;                                    // [2 buffers][2 panels][128 rows][128 B]
@@ -135,6 +144,7 @@ ffn_fused_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     }
     mbar_init(&ctl->hs_full, FF_EPI_WARPS);
     mbar_init(&ctl->hs_empty, 1);
+    mbar_init(&ctl->hs_stored, 1);
     mbar_init(&ctl->acc2_full, 1);
     mbar_init(&ctl->acc2_empty, FF_EPI_WARPS);
     ctl->abort_flag = 0;
@@ -216,6 +226,23 @@ ffn_fused_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       }
       if (!ok) { *abort_flag = 1; atomicExch(g.status, 10); }
     }
+  } else if (warp == FF_STORE_WARP) {
+    // ------------------------------------------------------------------ hidden halves -> HBM (training forward only)
+    if (lane == 0 && g.store_h) {
+      bool ok = true;
+      int i = 0;
+      for (int t = blockIdx.x; t < g.m_tiles && ok; t += gridDim.x, ++i) {
+        for (int c = 0; c < FF_NHC && ok; ++c) {
+          if (!mbar_wait(&ctl->hs_full, (uint32_t)(c & 1), abort_flag)) { ok = false; break; }   // every warp has written its part
+          for (int p = 0; p < 2; ++p) tma_store_2d(&map_h, s_h + p * FF_PANEL, c * FF_HC + p * 64, t * FF_M);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+          mbar_arrive(&ctl->hs_stored);                     // the operand buffer may be overwritten as far as this copy goes
+        }
+      }
+      tma_store_wait_all();
+      if (!ok) { *abort_flag = 1; atomicExch(g.status, 12); }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps (2..17)
     const int quarter = warp & 3;                          // TMEM lane quarter this warp may read
@@ -267,6 +294,12 @@ ffn_fused_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             for (int e = 0; e < 16; ++e)
               v[e] = ff_keep(g.seed1, (uint32_t)row, (uint32_t)(hcol + e), g.thresh1) ? v[e] * g.scale1 : 0.f;
           }
+          if (g.bits_out != nullptr && row < g.M) {
+            unsigned bits = 0;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) bits |= (v[e] > 0.f ? 1u : 0u) << e;
+            g.bits_out[(long long)(hcol >> 4) * g.ldmb + row] = (unsigned short)bits;
+          }
           packed[it][0] = make_uint4(ff_pack2(v[0], v[1], is_fp16), ff_pack2(v[2], v[3], is_fp16),
                                      ff_pack2(v[4], v[5], is_fp16), ff_pack2(v[6], v[7], is_fp16));
           packed[it][1] = make_uint4(ff_pack2(v[8], v[9], is_fp16), ff_pack2(v[10], v[11], is_fp16),
@@ -274,6 +307,8 @@ ffn_fused_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         }
         // the operand buffer is free once the GEMM2 of the previous half (use index 2 i + c - 1) has retired
         if (!mbar_wait(&ctl->hs_empty, (uint32_t)((c & 1) ^ 1), abort_flag)) { ok = false; break; }
+        // ... and, when the halves are kept, once the bulk store of the previous half has read it
+        if (g.store_h && !mbar_wait(&ctl->hs_stored, (uint32_t)((c & 1) ^ 1), abort_flag)) { ok = false; break; }
 #pragma unroll
         for (int it = 0; it < 2; ++it) {
           const int kcol = group * 32 + it * 16;                        // column inside the half = K index of GEMM2
@@ -383,7 +418,14 @@ extern "C" int bf_ffn_fused_fwd(const bf_ffn_params* p, cudaStream_t st) {
   g.residual = p->residual ? 1 : 0;
   g.is_fp16 = p->dtype == BF_FP16 ? 1 : 0;
   g.status = p->status;
-  CUtensorMap map_x, map_w1, map_w2, map_y;
+  g.store_h = p->H_out != nullptr ? 1 : 0;
+  g.bits_out = static_cast<unsigned short*>(p->relu_bits_out);
+  g.ldmb = p->ldmb;
+  if (g.store_h && (((uintptr_t)p->H_out) % 16 != 0 || (p->ldh * 2) % 16 != 0 || p->ldh < FF_F)) return (int)cudaErrorInvalidValue;
+  if (g.bits_out != nullptr && p->ldmb < p->M) return (int)cudaErrorInvalidValue;
+  CUtensorMap map_x, map_w1, map_w2, map_y, map_h;
+  memset(&map_h, 0, sizeof(map_h));
+  if (g.store_h && make_map(&map_h, p->H_out, p->M, FF_F, p->ldh, FF_M, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
   if (make_map(&map_x, p->X, p->M, FF_H, p->ldx, FF_M, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
   if (make_map(&map_w1, p->W1, FF_F, FF_H, FF_H, FF_HC, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
   if (make_map(&map_w2, p->W2, FF_H, FF_F, FF_F, FF_H, g.is_fp16) != 0) return (int)cudaErrorNotSupported;
@@ -402,6 +444,6 @@ extern "C" int bf_ffn_fused_fwd(const bf_ffn_params* p, cudaStream_t st) {
   }
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = g.m_tiles < sms ? g.m_tiles : sms;
-  ffn_fused_tcgen05_kernel<<<grid, FF_THREADS, smem, st>>>(map_x, map_w1, map_w2, map_y, g);
+  ffn_fused_tcgen05_kernel<<<grid, FF_THREADS, smem, st>>>(map_x, map_w1, map_w2, map_y, map_h, g);
   return (int)cudaGetLastError();
 }

@@ -110,6 +110,18 @@ def case_ffn(a):
                 return gemm.gemm_tn(h, w2, l2.bias, None, residual=x)
             ms2 = timed(two, a.warmup, a.iters)
             report("two tcgen05 GEMMs (hidden matrix through HBM)", ms2, nbytes, flops, {"m": a.m, "act": act})
+            # training forward: hidden matrix and ReLU bits kept for the backward pass
+            hbuf = torch.empty(a.m, 256, device="cuda", dtype=torch.bfloat16)
+            bits = torch.empty(16, a.m, device="cuda", dtype=torch.int16)
+            fn3 = lambda: ffn_mod.ffn_onchip(x, l1.weight, l1.bias, l2.weight, l2.bias, act=act, residual=True, p1=0.1, seed1=5,
+                                             h_out=hbuf, relu_bits_out=bits)
+            ms3 = timed(fn3, a.warmup, a.iters)
+            report("ffn_fused_tcgen05 + hidden matrix and ReLU bits as side outputs", ms3, nbytes + 2 * a.m * 256, flops, {"m": a.m})
+            def two_train():
+                h = gemm.gemm_tn(x, w1, l1.bias, act, dropout_p=0.1, dropout_seed=5, relu_bits_out=bits)
+                return gemm.gemm_tn(h, w2, l2.bias, None, residual=x)
+            ms4 = timed(two_train, a.warmup, a.iters)
+            report("two tcgen05 GEMMs, training forward (bits written)", ms4, nbytes + 2 * a.m * 256, flops, {"m": a.m})
     gemm.check_status("cuda")
 
 

@@ -102,9 +102,13 @@ def test_fused_linear_autograd():
     assert torch.allclose(lin.bias.grad, b2.grad, atol=0.03 * float(b2.grad.abs().max()), rtol=5e-2)
 
 
-def test_fused_ffn_autograd():
+@pytest.mark.parametrize("onchip_train", [False, True])
+def test_fused_ffn_autograd(onchip_train, monkeypatch):
+    from budgetformer_b200.ops import ffn as ffn_mod
     from budgetformer_b200.ops.ffn import fused_ffn
     from budgetformer_b200.ops import norm as bnorm
+    # True: the training forward runs on the one-kernel form with the hidden matrix and the ReLU bits as side outputs
+    monkeypatch.setattr(ffn_mod, "ONCHIP_FFN_TRAIN", onchip_train)
     torch.manual_seed(3)
     m, h = 2000, 128
     x = torch.randn(m, h, device="cuda").bfloat16().requires_grad_(True)
@@ -225,6 +229,29 @@ def test_ffn_with_the_hidden_tile_on_chip_matches_reference(act, residual, p1, p
             ffn_mod.ONCHIP_FFN = old
     assert (a.float() - b.float()).abs().max() < 0.06 * max(1.0, float(b.float().abs().max()))
     gemm.check_status("cuda")
+
+
+def test_ffn_on_chip_side_outputs_equal_the_two_gemm_form():
+    """Training variant of the one-kernel block: the hidden matrix written from the on-chip operand and the ReLU bit mask
+    equal what the first GEMM of the two-GEMM form writes (same masks, same rounding), over a ragged row count."""
+    from budgetformer_b200.ops.ffn import ffn_onchip
+    torch.manual_seed(8)
+    m, h = 128 * 170 + 77, 128
+    x = torch.randn(m, h, device="cuda").bfloat16()
+    l1, l2 = torch.nn.Linear(h, 2 * h).cuda(), torch.nn.Linear(2 * h, h).cuda()
+    w1, w2 = l1.weight.detach().bfloat16(), l2.weight.detach().bfloat16()
+    bits_a = torch.zeros(2 * h // 16, m, dtype=torch.int16, device="cuda")
+    h_a = gemm.gemm_tn(x, w1, l1.bias.detach(), "relu", dropout_p=0.2, dropout_seed=41, relu_bits_out=bits_a)
+    y_a = gemm.gemm_tn(h_a, w2, l2.bias.detach(), None, dropout_p=0.1, dropout_seed=43, residual=x)
+    h_b = torch.full((m, 2 * h), 9.0, device="cuda", dtype=torch.bfloat16)
+    bits_b = torch.zeros_like(bits_a)
+    y_b = ffn_onchip(x, l1.weight, l1.bias, l2.weight, l2.bias, act="relu", residual=True, p1=0.2, seed1=41, p2=0.1, seed2=43,
+                     h_out=h_b, relu_bits_out=bits_b)
+    gemm.check_status("cuda")
+    assert (h_a.float() - h_b.float()).abs().max() < 2e-2 * max(1.0, float(h_a.float().abs().max()))
+    mismatch = (bits_a != bits_b).float().mean()          # a sign can flip where a value rounds to or from zero
+    assert float(mismatch) < 1e-3, float(mismatch)
+    _close(y_b, y_a.float(), torch.bfloat16)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
