@@ -52,7 +52,8 @@ def ffn_onchip(x: torch.Tensor, w1, b1, w2, b2, *, act: str, residual: bool, p1:
 
 
 def onchip_supported(x: torch.Tensor, w1, w2) -> bool:
-    if not (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and x.stride(1) == 1
+    # bf16 only: the fp16 instantiation of the kernel exists but is not covered by the GPU tests
+    if not (x.is_cuda and x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1
             and (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0 and x.size(0) > 0):
         return False
     from . import _ext
